@@ -1,0 +1,844 @@
+// GraphPipeline: operator recording, validation, fusion and constant upload.
+//
+// Attribute layout of OpDesc::i per kind (the reference keeps these in per-op push-constant
+// structs, graph/compute_graph_op.hpp):
+//   CONV2D, DEPTHWISE_CONV2D  i[0..3] pad(top,bottom,left,right) i[4..5] stride i[6..7] dilation
+//                             i[8] inputZeroPoint i[9] weightZeroPoint i[10] accType
+//                             in = {input, weights, biases}
+//   MATMUL                    i[0] zeroPoint1 i[1] zeroPoint2            in = {input1, input2}
+//   RESCALE                   i[0] inputZeroPoint i[1] outputZeroPoint i[2] scale32 i[3] doubleRound
+//                             i[4] perChannel i[5] inputUnsigned i[6] outputUnsigned
+//                             in = {input, multiplier, shift}
+//   AVG_POOL2D                i[0..1] kernel i[2..3] stride i[4..7] pad i[8] inZp i[9] outZp i[10] accType
+//   MAX_POOL2D                i[0..1] kernel i[2..3] stride i[4..7] pad i[8] nanMode
+//   TABLE                     in = {input, table}
+//   TRANSPOSE                 i[0..rank-1] perms
+//   CONCAT                    i[0] axis i[1] offset      (one op per input, compute_graph_op.cpp:2607-2615)
+//   CLAMP                     d[0] min d[1] max i[0] nanMode
+//   BINARY / UNARY / REDUCE   sub = operator; BINARY i[0] nanMode; REDUCE i[0] axis i[1] nanMode
+//   MUL                       i[0] shift
+//   SLICE                     i[0..rank-1] start
+//   PAD                       d[0] padConst i[0] padConstInt    in = {input, padding}
+//   ARITHMETIC_RIGHT_SHIFT    i[0] round
+//   NEGATE                    i[0] inputZeroPoint i[1] outputZeroPoint
+//   SELECT                    in = {condition, input2, input3}
+#include "graph_pipeline.hpp"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <queue>
+#include <set>
+
+namespace mlel {
+
+int elemSize(int32_t dtype) {
+    switch (dtype) {
+    case MLEL_BOOL:
+    case MLEL_I8:
+    case MLEL_U8:
+        return 1;
+    case MLEL_I16:
+    case MLEL_U16:
+    case MLEL_F16:
+    case MLEL_BF16:
+        return 2;
+    case MLEL_I32:
+    case MLEL_U32:
+    case MLEL_F32:
+        return 4;
+    case MLEL_I64:
+        return 8;
+    default:
+        return 0;
+    }
+}
+
+int64_t TensorDescriptor::numel() const {
+    int64_t n = 1;
+    for (auto d : dims) {
+        n *= d;
+    }
+    return n;
+}
+
+uint64_t TensorDescriptor::sizeBytes() const {
+    if (dims.empty()) {
+        return uint64_t(elemSize(dtype));
+    }
+    return uint64_t(dims[0]) * uint64_t(strides[0]);
+}
+
+bool TensorDescriptor::packed() const {
+    int64_t s = elemSize(dtype);
+    for (int i = rank() - 1; i >= 0; --i) {
+        if (strides[size_t(i)] != s) {
+            return false;
+        }
+        s *= dims[size_t(i)];
+    }
+    return true;
+}
+
+namespace {
+
+std::vector<int64_t> packedStrides(int32_t dtype, const std::vector<int64_t> &dims) {
+    // tensor/tensor_arm.cpp:82-92
+    std::vector<int64_t> strides(dims.size());
+    if (dims.empty()) {
+        return strides;
+    }
+    strides.back() = elemSize(dtype);
+    for (size_t i = dims.size() - 1; i > 0; --i) {
+        strides[i - 1] = strides[i] * dims[i];
+    }
+    return strides;
+}
+
+std::unique_ptr<TensorDescriptor> fromDesc(const mlel_tensor_desc &desc) {
+    if (desc.rank <= 0 || desc.rank > kMaxRank) {
+        throw std::runtime_error("Tensor dimension count not supported: " + std::to_string(desc.rank));
+    }
+    if (elemSize(desc.dtype) == 0) {
+        throw UnsupportedError("Unsupported tensor buffer format: " + std::to_string(desc.dtype));
+    }
+    auto t = std::make_unique<TensorDescriptor>();
+    t->dtype = desc.dtype;
+    t->dims.assign(desc.dims, desc.dims + desc.rank);
+    for (auto d : t->dims) {
+        if (d <= 0) {
+            throw std::runtime_error("Tensor dimensions must be greater than zero");
+        }
+    }
+    if (desc.strides[0] == 0) {
+        t->strides = packedStrides(desc.dtype, t->dims);
+    } else {
+        t->strides.assign(desc.strides, desc.strides + desc.rank);
+        if (t->strides[0] < 0) {
+            throw std::runtime_error("Strides must be greater than zero."); // graph/tensor.cpp:194-196
+        }
+    }
+    // Element counts are 32-bit in the reference's dispatch (graph/compute_graph_op.cpp:554).
+    if (t->numel() >= (int64_t(1) << 32)) {
+        throw UnsupportedError("Tensors with 2^32 or more elements are not supported");
+    }
+    return t;
+}
+
+bool isIntegerType(int32_t dt) { return dt >= MLEL_BOOL && dt <= MLEL_U32; }
+
+} // namespace
+
+int32_t GraphPipeline::addTensor(std::unique_ptr<TensorDescriptor> t) {
+    t->id = int32_t(tensors_.size());
+    tensors_.push_back(std::move(t));
+    return tensors_.back()->id;
+}
+
+void GraphPipeline::requireMutable() const {
+    if (finalized_) {
+        throw std::runtime_error("pipeline is immutable once a session exists");
+    }
+}
+
+int32_t GraphPipeline::makeConstTensor(uint32_t id, const mlel_tensor_desc &desc, const void *data) {
+    requireMutable();
+    auto t = fromDesc(desc);
+    t->cls = TensorClass::Constant;
+    if (data == nullptr) {
+        throw std::runtime_error("constant tensor without data");
+    }
+    const auto *bytes = static_cast<const uint8_t *>(data);
+    t->hostData.assign(bytes, bytes + t->sizeBytes()); // constants are copied at create time
+    const int32_t tid = addTensor(std::move(t));
+    constTensorMap_[id] = tid;
+    return tid;
+}
+
+int32_t GraphPipeline::getConstTensor(uint32_t id) const { return constTensorMap_.at(id); }
+
+int32_t GraphPipeline::makeConstCompositeTensor(int32_t dtype, const std::vector<int64_t> &dims, const void *data) {
+    requireMutable();
+    mlel_tensor_desc desc{};
+    desc.dtype = dtype;
+    desc.rank = int32_t(dims.size());
+    for (size_t i = 0; i < dims.size(); ++i) {
+        desc.dims[i] = dims[i];
+    }
+    auto t = fromDesc(desc);
+    t->cls = TensorClass::Constant;
+    const auto *bytes = static_cast<const uint8_t *>(data);
+    t->hostData.assign(bytes, bytes + t->sizeBytes());
+    return addTensor(std::move(t));
+}
+
+int32_t GraphPipeline::makeDescriptorSetBinding(uint32_t set, uint32_t binding, uint32_t arrayIndex,
+                                                const mlel_tensor_desc &desc) {
+    requireMutable();
+    auto t = fromDesc(desc);
+    t->cls = TensorClass::External;
+    t->set = set;
+    t->binding = binding;
+    t->arrayIndex = arrayIndex;
+    const int32_t tid = addTensor(std::move(t));
+    externalMap_[std::make_tuple(set, binding, arrayIndex)] = tid;
+    return tid;
+}
+
+int32_t GraphPipeline::getTensor(uint32_t set, uint32_t binding, uint32_t arrayIndex) const {
+    return externalMap_.at(std::make_tuple(set, binding, arrayIndex));
+}
+
+int32_t GraphPipeline::makeTensor(int32_t dtype, const std::vector<int64_t> &dims,
+                                  const std::vector<int64_t> &strides) {
+    requireMutable();
+    mlel_tensor_desc desc{};
+    desc.dtype = dtype;
+    desc.rank = int32_t(dims.size());
+    for (size_t i = 0; i < dims.size(); ++i) {
+        desc.dims[i] = dims[i];
+        desc.strides[i] = strides.empty() ? 0 : strides[i];
+    }
+    auto t = fromDesc(desc);
+    t->cls = TensorClass::Session;
+    t->sessionOrder = int32_t(sessionTensors_.size());
+    const int32_t tid = addTensor(std::move(t));
+    sessionTensors_.push_back(tid);
+    return tid;
+}
+
+void GraphPipeline::makeInput(int32_t t) {
+    requireMutable();
+    tensor(t).isGraphInput = true;
+    inputs_.push_back(t);
+}
+
+void GraphPipeline::makeOutput(int32_t t) {
+    requireMutable();
+    tensor(t).isGraphOutput = true;
+    outputs_.push_back(t);
+}
+
+OpDesc &GraphPipeline::pushOp(OpKind kind, const std::string &name, std::vector<int32_t> in,
+                              std::vector<int32_t> out) {
+    requireMutable();
+    for (auto t : in) {
+        (void)tensor(t);
+    }
+    for (auto t : out) {
+        if (tensor(t).cls == TensorClass::Constant) {
+            throw std::runtime_error(name + ": a constant tensor cannot be an operator output");
+        }
+    }
+    OpDesc op;
+    op.kind = kind;
+    op.name = name;
+    op.in = std::move(in);
+    op.out = std::move(out);
+    ops_.push_back(std::move(op));
+    return ops_.back();
+}
+
+namespace {
+void need(bool cond, const std::string &what) {
+    if (!cond) {
+        throw UnsupportedError(what);
+    }
+}
+} // namespace
+
+void GraphPipeline::makeConv2D(int32_t input, int32_t output, int32_t weights, int32_t biases,
+                               const std::vector<int32_t> &pad, const std::vector<int32_t> &stride,
+                               const std::vector<int32_t> &dilation, int8_t inputZeroPoint, int8_t weightZeroPoint,
+                               uint32_t accType, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output), &w = tensor(weights), &b = tensor(biases);
+    need(in.rank() == 4 && out.rank() == 4 && w.rank() == 4 && b.rank() == 1, debugName + ": rank mismatch");
+    need(pad.size() == 4 && stride.size() == 2 && dilation.size() == 2, debugName + ": attribute size mismatch");
+    // accType codes: 1 int32, 2 fp16, 3 fp32, 4 int64 (graph/compute_graph_op.cpp:39-67)
+    need(accType == 1 || accType == 4, debugName + ": only integer accumulators are built (accType 1 or 4)");
+    need((in.dtype == MLEL_I8 && out.dtype == MLEL_I32) || (in.dtype == MLEL_I16 && out.dtype == MLEL_I64),
+         debugName + ": supported types are int8->int32 and int16->int64");
+    need(w.dtype == MLEL_I8 && b.dtype == out.dtype, debugName + ": weights must be int8, bias of the output type");
+    auto &op = pushOp(OP_CONV2D, debugName, {input, weights, biases}, {output});
+    for (int k = 0; k < 4; ++k) {
+        op.i[k] = pad[size_t(k)];
+    }
+    op.i[4] = stride[0], op.i[5] = stride[1], op.i[6] = dilation[0], op.i[7] = dilation[1];
+    op.i[8] = inputZeroPoint, op.i[9] = weightZeroPoint, op.i[10] = int32_t(accType);
+}
+
+void GraphPipeline::makeDepthwiseConv2D(int32_t input, int32_t output, int32_t weights, int32_t biases,
+                                        const std::vector<int32_t> &pad, const std::vector<int32_t> &stride,
+                                        const std::vector<int32_t> &dilation, int8_t inputZeroPoint,
+                                        int8_t weightZeroPoint, uint32_t accType, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output), &w = tensor(weights), &b = tensor(biases);
+    need(in.rank() == 4 && out.rank() == 4 && w.rank() == 4 && b.rank() == 1, debugName + ": rank mismatch");
+    need(pad.size() == 4 && stride.size() == 2 && dilation.size() == 2, debugName + ": attribute size mismatch");
+    need(accType == 1 || accType == 4, debugName + ": only integer accumulators are built (accType 1 or 4)");
+    need((in.dtype == MLEL_I8 && out.dtype == MLEL_I32) || (in.dtype == MLEL_I16 && out.dtype == MLEL_I64),
+         debugName + ": supported types are int8->int32 and int16->int64");
+    need(w.dtype == MLEL_I8 && b.dtype == out.dtype, debugName + ": weights must be int8, bias of the output type");
+    auto &op = pushOp(OP_DEPTHWISE_CONV2D, debugName, {input, weights, biases}, {output});
+    for (int k = 0; k < 4; ++k) {
+        op.i[k] = pad[size_t(k)];
+    }
+    op.i[4] = stride[0], op.i[5] = stride[1], op.i[6] = dilation[0], op.i[7] = dilation[1];
+    op.i[8] = inputZeroPoint, op.i[9] = weightZeroPoint, op.i[10] = int32_t(accType);
+}
+
+void GraphPipeline::makeMatmul(int32_t input1, int32_t input2, int32_t output, int32_t zp1, int32_t zp2,
+                               const std::string &debugName) {
+    const auto &a = tensor(input1), &b = tensor(input2), &out = tensor(output);
+    need(a.rank() == 3 && b.rank() == 3 && out.rank() == 3, debugName + ": rank mismatch");
+    need(a.dtype == b.dtype, debugName + ": input types differ");
+    need((a.dtype == MLEL_I8 && out.dtype == MLEL_I32) || (a.dtype == MLEL_I16 && out.dtype == MLEL_I64),
+         debugName + ": supported types are int8->int32 and int16->int64");
+    auto &op = pushOp(OP_MATMUL, debugName, {input1, input2}, {output});
+    op.i[0] = zp1, op.i[1] = zp2;
+}
+
+void GraphPipeline::makeRescale(int32_t input, int32_t output, int32_t inputZeroPoint, int32_t outputZeroPoint,
+                                int32_t multiplier, int32_t shift, bool scale32, bool doubleRound, bool perChannel,
+                                bool inputUnsigned, bool outputUnsigned, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output), &m = tensor(multiplier), &s = tensor(shift);
+    // The reference's unsigned variants mix signed and unsigned operands in clamp(); their result
+    // depends on GLSL overload resolution and no reference test pins it.
+    need(!inputUnsigned && !outputUnsigned, debugName + ": unsigned RESCALE variants are not built");
+    need(in.dtype == MLEL_I8 || in.dtype == MLEL_I16 || in.dtype == MLEL_I32, debugName + ": input type");
+    need(out.dtype == MLEL_I8 || out.dtype == MLEL_I16 || out.dtype == MLEL_I32, debugName + ": output type");
+    need((m.dtype == MLEL_I32 || m.dtype == MLEL_I16) && s.dtype == MLEL_I8, debugName + ": multiplier/shift type");
+    need(m.rank() == 1 && s.rank() == 1, debugName + ": multiplier/shift must be rank 1");
+    auto &op = pushOp(OP_RESCALE, debugName, {input, multiplier, shift}, {output});
+    op.i[0] = inputZeroPoint, op.i[1] = outputZeroPoint, op.i[2] = scale32, op.i[3] = doubleRound;
+    op.i[4] = perChannel, op.i[5] = inputUnsigned, op.i[6] = outputUnsigned;
+}
+
+void GraphPipeline::makeAvgPool2D(int32_t input, int32_t output, const std::vector<int32_t> &kernel,
+                                  const std::vector<int32_t> &stride, const std::vector<int32_t> &pad,
+                                  uint32_t accType, int8_t inputZeroPoint, int8_t outputZeroPoint,
+                                  const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.rank() == 4 && out.rank() == 4, debugName + ": rank mismatch");
+    need(kernel.size() == 2 && stride.size() == 2 && pad.size() == 4, debugName + ": attribute size mismatch");
+    need(accType == 1 && (in.dtype == MLEL_I8 || in.dtype == MLEL_I16) && in.dtype == out.dtype,
+         debugName + ": only int8/int16 with an int32 accumulator is built");
+    auto &op = pushOp(OP_AVG_POOL2D, debugName, {input}, {output});
+    op.i[0] = kernel[0], op.i[1] = kernel[1], op.i[2] = stride[0], op.i[3] = stride[1];
+    for (int k = 0; k < 4; ++k) {
+        op.i[4 + k] = pad[size_t(k)];
+    }
+    op.i[8] = inputZeroPoint, op.i[9] = outputZeroPoint, op.i[10] = int32_t(accType);
+}
+
+void GraphPipeline::makeMaxPool2D(int32_t input, int32_t output, const std::vector<int32_t> &kernel,
+                                  const std::vector<int32_t> &stride, const std::vector<int32_t> &pad,
+                                  uint32_t nanMode, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.rank() == 4 && out.rank() == 4, debugName + ": rank mismatch");
+    need(kernel.size() == 2 && stride.size() == 2 && pad.size() == 4, debugName + ": attribute size mismatch");
+    need((in.dtype == MLEL_I8 || in.dtype == MLEL_I16 || in.dtype == MLEL_I32) && in.dtype == out.dtype,
+         debugName + ": only integer types are built");
+    auto &op = pushOp(OP_MAX_POOL2D, debugName, {input}, {output});
+    op.i[0] = kernel[0], op.i[1] = kernel[1], op.i[2] = stride[0], op.i[3] = stride[1];
+    for (int k = 0; k < 4; ++k) {
+        op.i[4 + k] = pad[size_t(k)];
+    }
+    op.i[8] = int32_t(nanMode);
+}
+
+void GraphPipeline::makeTable(int32_t input, int32_t output, int32_t table, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output), &t = tensor(table);
+    need((in.dtype == MLEL_I8 && out.dtype == MLEL_I8) || (in.dtype == MLEL_I16 && out.dtype == MLEL_I32),
+         debugName + ": supported types are int8->int8 and int16->int32");
+    need(t.dtype == in.dtype && t.rank() == 1, debugName + ": table must be rank 1 of the input type");
+    pushOp(OP_TABLE, debugName, {input, table}, {output});
+}
+
+void GraphPipeline::makeTranspose(int32_t input, int32_t output, const std::vector<uint32_t> &perms,
+                                  const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.rank() == out.rank() && int(perms.size()) == in.rank(), debugName + ": rank mismatch");
+    need(elemSize(in.dtype) == elemSize(out.dtype), debugName + ": element size mismatch");
+    for (auto p : perms) {
+        need(int(p) < in.rank(), debugName + ": permutation out of range");
+    }
+    auto &op = pushOp(OP_TRANSPOSE, debugName, {input}, {output});
+    for (size_t k = 0; k < perms.size(); ++k) {
+        op.i[k] = int32_t(perms[k]);
+    }
+}
+
+void GraphPipeline::makeConcat(const std::vector<int32_t> &inputs, int32_t output, uint32_t axis,
+                               const std::string &debugName) {
+    uint32_t offset = 0;
+    for (auto input : inputs) {
+        const auto &in = tensor(input);
+        need(in.rank() == tensor(output).rank() && int(axis) < in.rank(), debugName + ": rank/axis mismatch");
+        need(elemSize(in.dtype) == elemSize(tensor(output).dtype), debugName + ": element size mismatch");
+        auto &op = pushOp(OP_CONCAT, debugName, {input}, {output});
+        op.i[0] = int32_t(axis), op.i[1] = int32_t(offset);
+        offset += uint32_t(in.dims[axis]);
+    }
+}
+
+void GraphPipeline::makeClamp(int32_t input, int32_t output, double min, double max, uint32_t nanMode,
+                              const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need((in.dtype == MLEL_I8 || in.dtype == MLEL_I16 || in.dtype == MLEL_I32) && in.dtype == out.dtype,
+         debugName + ": only integer types are built");
+    auto &op = pushOp(OP_CLAMP, debugName, {input}, {output});
+    op.d[0] = min, op.d[1] = max, op.i[0] = int32_t(nanMode);
+}
+
+void GraphPipeline::makeBinary(BinaryOp opk, int32_t input1, int32_t input2, int32_t output, uint32_t nanMode,
+                               const std::string &debugName) {
+    const auto &a = tensor(input1), &b = tensor(input2), &out = tensor(output);
+    need(a.dtype == b.dtype, debugName + ": input types differ");
+    need(a.rank() == b.rank() && a.rank() == out.rank(), debugName + ": rank mismatch");
+    const bool f32ok = a.dtype == MLEL_F32 && (opk == BIN_ADD || opk == BIN_SUB || opk == BIN_MAXIMUM ||
+                                               opk == BIN_MINIMUM || opk >= BIN_EQUAL);
+    need((isIntegerType(a.dtype) && a.dtype < MLEL_U8) || f32ok, debugName + ": input type not built");
+    if (a.dtype == MLEL_F32 && (opk == BIN_MAXIMUM || opk == BIN_MINIMUM)) {
+        need(nanMode != 2, debugName + ": NaN-ignore mode is not built");
+    }
+    auto &op = pushOp(OP_BINARY, debugName, {input1, input2}, {output});
+    op.sub = opk;
+    op.i[0] = int32_t(nanMode);
+}
+
+void GraphPipeline::makeUnary(UnaryOp opk, int32_t input, int32_t output, const std::string &debugName) {
+    const auto &in = tensor(input);
+    need(isIntegerType(in.dtype) && in.dtype < MLEL_U8, debugName + ": only integer types are built");
+    auto &op = pushOp(OP_UNARY, debugName, {input}, {output});
+    op.sub = opk;
+}
+
+void GraphPipeline::makeMul(int32_t input1, int32_t input2, int32_t output, uint32_t shift,
+                            const std::string &debugName) {
+    const auto &a = tensor(input1), &b = tensor(input2), &out = tensor(output);
+    need(a.dtype == b.dtype && a.rank() == b.rank() && a.rank() == out.rank(), debugName + ": operand mismatch");
+    need((a.dtype == MLEL_F32 && out.dtype == MLEL_F32) ||
+             ((a.dtype == MLEL_I8 || a.dtype == MLEL_I16 || a.dtype == MLEL_I32) && out.dtype == MLEL_I32),
+         debugName + ": supported types are int8/int16/int32->int32 and fp32");
+    auto &op = pushOp(OP_MUL, debugName, {input1, input2}, {output});
+    op.i[0] = int32_t(shift);
+}
+
+void GraphPipeline::makeReduce(ReduceOp opk, int32_t input, int32_t output, uint32_t axis, uint32_t nanMode,
+                               const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.rank() == out.rank() && int(axis) < in.rank(), debugName + ": rank/axis mismatch");
+    need(isIntegerType(in.dtype) && in.dtype < MLEL_U8 && in.dtype == out.dtype,
+         debugName + ": only integer types are built");
+    auto &op = pushOp(OP_REDUCE, debugName, {input}, {output});
+    op.sub = opk;
+    op.i[0] = int32_t(axis);
+    op.i[1] = 1; // integers force NaN mode PROPAGATE (graph/compute_graph_op.cpp:1674-1682)
+    (void)nanMode;
+}
+
+void GraphPipeline::makeCast(int32_t input, int32_t output, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    const auto ok = [](int32_t dt) { return (isIntegerType(dt) && dt < MLEL_U8) || dt == MLEL_F32; };
+    need(ok(in.dtype) && ok(out.dtype), debugName + ": type not built");
+    need(in.rank() == out.rank(), debugName + ": rank mismatch");
+    pushOp(OP_CAST, debugName, {input}, {output});
+}
+
+void GraphPipeline::makeReshape(int32_t input, int32_t output, const std::string &debugName) {
+    need(elemSize(tensor(input).dtype) == elemSize(tensor(output).dtype), debugName + ": element size mismatch");
+    pushOp(OP_RESHAPE, debugName, {input}, {output});
+}
+
+void GraphPipeline::makeSlice(int32_t input, int32_t output, const std::vector<uint32_t> &start,
+                              const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.rank() == out.rank() && int(start.size()) == in.rank(), debugName + ": rank mismatch");
+    need(elemSize(in.dtype) == elemSize(out.dtype), debugName + ": element size mismatch");
+    auto &op = pushOp(OP_SLICE, debugName, {input}, {output});
+    for (size_t k = 0; k < start.size(); ++k) {
+        op.i[k] = int32_t(start[k]);
+    }
+}
+
+void GraphPipeline::makePad(int32_t input, int32_t output, int32_t padding, double padConst, int32_t padConstInt,
+                            const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output), &p = tensor(padding);
+    need(in.rank() == out.rank() && in.dtype == out.dtype, debugName + ": operand mismatch");
+    need(p.dtype == MLEL_I32 && p.rank() == 1, debugName + ": padding must be a rank-1 int32 tensor");
+    need((isIntegerType(in.dtype) && in.dtype < MLEL_U8) || in.dtype == MLEL_F32, debugName + ": type not built");
+    auto &op = pushOp(OP_PAD, debugName, {input, padding}, {output});
+    op.d[0] = padConst;
+    op.i[0] = padConstInt;
+}
+
+void GraphPipeline::makeArithmeticRightShift(int32_t input1, int32_t input2, int32_t output, bool round,
+                                             const std::string &debugName) {
+    const auto &a = tensor(input1), &b = tensor(input2);
+    need(a.dtype == b.dtype && (a.dtype == MLEL_I8 || a.dtype == MLEL_I16 || a.dtype == MLEL_I32),
+         debugName + ": only int8/int16/int32 are built");
+    auto &op = pushOp(OP_ARITHMETIC_RIGHT_SHIFT, debugName, {input1, input2}, {output});
+    op.i[0] = round;
+}
+
+void GraphPipeline::makeNegate(int32_t input, int32_t output, int32_t inputZeroPoint, int32_t outputZeroPoint,
+                               const std::string &debugName) {
+    const auto &in = tensor(input);
+    need(in.dtype == MLEL_I8 || in.dtype == MLEL_I16 || in.dtype == MLEL_I32, debugName + ": only integers built");
+    auto &op = pushOp(OP_NEGATE, debugName, {input}, {output});
+    op.i[0] = inputZeroPoint, op.i[1] = outputZeroPoint;
+}
+
+void GraphPipeline::makeSelect(int32_t input1, int32_t input2, int32_t input3, int32_t output,
+                               const std::string &debugName) {
+    need(elemSize(tensor(input1).dtype) == 1, debugName + ": condition must be an 8-bit tensor");
+    need(tensor(input2).dtype == tensor(input3).dtype, debugName + ": value types differ");
+    pushOp(OP_SELECT, debugName, {input1, input2, input3}, {output});
+}
+
+/*******************************************************************************
+ * Fusion
+ *******************************************************************************/
+
+namespace {
+
+struct UseInfo {
+    std::vector<int> consumers; // op indices reading the tensor
+    int producers{0};
+};
+
+FusedRescale toFusedRescale(const GraphPipeline &p, const OpDesc &r) {
+    FusedRescale f;
+    f.multTensor = r.in[1];
+    f.shiftTensor = r.in[2];
+    f.inDtype = p.tensor(r.in[0]).dtype;
+    f.outDtype = p.tensor(r.out[0]).dtype;
+    f.attr.inZp = r.i[0];
+    f.attr.outZp = r.i[1];
+    f.attr.scale32 = r.i[2];
+    f.attr.doubleRound = r.i[3];
+    f.attr.perChannel = r.i[4];
+    f.lo = f.outDtype == MLEL_I8 ? -128 : (f.outDtype == MLEL_I16 ? -32768 : INT32_MIN);
+    f.hi = f.outDtype == MLEL_I8 ? 127 : (f.outDtype == MLEL_I16 ? 32767 : INT32_MAX);
+    return f;
+}
+
+} // namespace
+
+// Fusion keeps the arithmetic of every absorbed operator unchanged (the same integer steps run
+// back to back in registers), so results stay bit-identical to the one-kernel-per-op list; it only
+// removes the round trips of intermediates through memory.  A tensor may be elided when it lives
+// in session memory, is not a graph output, is written by exactly one operator and read by
+// exactly one.  The fused node runs at the position of its last absorbed operator.
+void GraphPipeline::fuse() {
+    exec_.clear();
+    const int n = int(ops_.size());
+    if (flags_ & MLEL_PIPELINE_NO_FUSION) {
+        for (int i = 0; i < n; ++i) {
+            exec_.push_back(ops_[size_t(i)]);
+            exec_.back().fusedOps = {i};
+        }
+        return;
+    }
+    std::vector<UseInfo> uses(tensors_.size());
+    std::vector<int> producer(tensors_.size(), -1);
+    for (int i = 0; i < n; ++i) {
+        for (auto t : ops_[size_t(i)].in) {
+            uses[size_t(t)].consumers.push_back(i);
+        }
+        for (auto t : ops_[size_t(i)].out) {
+            uses[size_t(t)].producers++;
+            producer[size_t(t)] = i;
+        }
+    }
+    // The single consumer of an elidable tensor, or -1.
+    const auto soleConsumer = [&](int32_t t) -> int {
+        const auto &td = tensor(t);
+        if (td.cls != TensorClass::Session || td.isGraphOutput || td.isGraphInput || !td.packed()) {
+            return -1;
+        }
+        const auto &u = uses[size_t(t)];
+        if (u.producers != 1 || u.consumers.size() != 1) {
+            return -1;
+        }
+        return u.consumers[0];
+    };
+    const auto isConst = [&](int32_t t) { return tensor(t).cls == TensorClass::Constant; };
+
+    std::vector<int> group(size_t(n), -1); // op -> index into fused
+    struct Group {
+        OpDesc node;
+        int last;
+    };
+    std::vector<Group> fused;
+
+    const auto absorb = [&](Group &g, int gi, int opIndex) {
+        group[size_t(opIndex)] = gi;
+        g.node.fusedOps.push_back(opIndex);
+        g.last = std::max(g.last, opIndex);
+    };
+
+    // Tries to extend `cur` (an int8 tensor) through an optional CLAMP; returns the new tail tensor.
+    const auto tryClamp = [&](Group &g, int gi, int32_t cur, FusedRescale &stage) -> int32_t {
+        const int c = soleConsumer(cur);
+        if (c < 0 || group[size_t(c)] >= 0 || ops_[size_t(c)].kind != OP_CLAMP) {
+            return cur;
+        }
+        const OpDesc &cl = ops_[size_t(c)];
+        const auto &td = tensor(cl.out[0]);
+        if (td.dtype != stage.outDtype) {
+            return cur;
+        }
+        const int64_t lo = int64_t(cl.d[0]), hi = int64_t(cl.d[1]);
+        if (lo > hi || lo < stage.lo || hi > stage.hi) {
+            return cur;
+        }
+        stage.lo = int32_t(lo);
+        stage.hi = int32_t(hi);
+        absorb(g, gi, c);
+        return cl.out[0];
+    };
+
+    for (int i = 0; i < n; ++i) {
+        if (group[size_t(i)] >= 0) {
+            continue;
+        }
+        const OpDesc &op = ops_[size_t(i)];
+        const bool contraction = op.kind == OP_CONV2D || op.kind == OP_MATMUL || op.kind == OP_DEPTHWISE_CONV2D;
+        if (contraction && tensor(op.out[0]).dtype == MLEL_I32 && tensor(op.in[0]).dtype == MLEL_I8) {
+            const int r = soleConsumer(op.out[0]);
+            if (r < 0 || group[size_t(r)] >= 0 || ops_[size_t(r)].kind != OP_RESCALE) {
+                continue;
+            }
+            const OpDesc &rs = ops_[size_t(r)];
+            if (rs.in[0] != op.out[0] || tensor(rs.out[0]).dtype != MLEL_I8 || !rs.i[2] || rs.i[5] || rs.i[6] ||
+                !isConst(rs.in[1]) || !isConst(rs.in[2]) || tensor(rs.in[1]).dtype != MLEL_I32) {
+                continue;
+            }
+            if (rs.i[4] && tensor(rs.in[1]).dims[0] != tensor(rs.out[0]).dims.back()) {
+                continue; // a per-channel table shorter than the channel count reads zeros: leave unfused
+            }
+            Group g;
+            g.node = op;
+            g.node.kind = op.kind == OP_CONV2D ? OP_FUSED_CONV2D
+                                               : (op.kind == OP_MATMUL ? OP_FUSED_MATMUL : OP_FUSED_DEPTHWISE);
+            g.node.name = op.name + "+RESCALE";
+            g.node.fusedOps.clear();
+            g.last = i;
+            const int gi = int(fused.size());
+            absorb(g, gi, i);
+            absorb(g, gi, r);
+            g.node.epi.hasMain = true;
+            g.node.epi.main = toFusedRescale(*this, rs);
+            int32_t tail = tryClamp(g, gi, rs.out[0], g.node.epi.main);
+            if (tail != rs.out[0]) {
+                g.node.name += "+CLAMP";
+            }
+            g.node.out = {tail};
+            fused.push_back(std::move(g));
+            continue;
+        }
+        // RESCALE(a) + RESCALE(b) -> ADD -> RESCALE [-> CLAMP]  (quantised residual add)
+        if (op.kind == OP_BINARY && op.sub == BIN_ADD && tensor(op.out[0]).dtype == MLEL_I32) {
+            const int pa = producer[size_t(op.in[0])], pb = producer[size_t(op.in[1])];
+            if (pa < 0 || pb < 0 || pa == pb || group[size_t(pa)] >= 0 || group[size_t(pb)] >= 0) {
+                continue;
+            }
+            const OpDesc &ra = ops_[size_t(pa)], &rb = ops_[size_t(pb)];
+            const auto okIn = [&](const OpDesc &r, int32_t t) {
+                return r.kind == OP_RESCALE && soleConsumer(t) == i && tensor(r.in[0]).dtype == MLEL_I8 &&
+                       tensor(r.in[0]).packed() && r.i[2] && !r.i[5] && !r.i[6] && !r.i[4] && isConst(r.in[1]) &&
+                       isConst(r.in[2]) && tensor(r.in[1]).dtype == MLEL_I32;
+            };
+            if (!okIn(ra, op.in[0]) || !okIn(rb, op.in[1])) {
+                continue;
+            }
+            const auto &da = tensor(ra.in[0]).dims, &db = tensor(rb.in[0]).dims, &dout = tensor(op.out[0]).dims;
+            if (da != dout || db != dout) {
+                continue; // broadcasting adds stay on the generic kernels
+            }
+            const int ro = soleConsumer(op.out[0]);
+            if (ro < 0 || group[size_t(ro)] >= 0 || ops_[size_t(ro)].kind != OP_RESCALE) {
+                continue;
+            }
+            const OpDesc &rs = ops_[size_t(ro)];
+            if (tensor(rs.out[0]).dtype != MLEL_I8 || !rs.i[2] || rs.i[5] || rs.i[6] || rs.i[4] ||
+                !isConst(rs.in[1]) || !isConst(rs.in[2]) || tensor(rs.in[1]).dtype != MLEL_I32 ||
+                !tensor(rs.out[0]).packed()) {
+                continue;
+            }
+            Group g;
+            g.node = op;
+            g.node.kind = OP_FUSED_ADD;
+            g.node.name = "RESCALE+RESCALE+ADD+RESCALE";
+            g.node.in = {ra.in[0], rb.in[0]};
+            g.node.fusedOps.clear();
+            g.last = i;
+            const int gi = int(fused.size());
+            absorb(g, gi, pa);
+            absorb(g, gi, pb);
+            absorb(g, gi, i);
+            absorb(g, gi, ro);
+            g.node.epi.hasResidual = true;
+            g.node.epi.a = toFusedRescale(*this, ra);
+            g.node.epi.b = toFusedRescale(*this, rb);
+            g.node.epi.out = toFusedRescale(*this, rs);
+            int32_t tail = tryClamp(g, gi, rs.out[0], g.node.epi.out);
+            if (tail != rs.out[0]) {
+                g.node.name += "+CLAMP";
+            }
+            g.node.out = {tail};
+            fused.push_back(std::move(g));
+        }
+    }
+    // The two input RESCALEs of a fused add come before the ADD in op order, possibly far before;
+    // moving them to the ADD's position is legal because their inputs are written exactly once.
+    // A fused node is emitted at the position of its last absorbed operator.
+    for (int i = 0; i < n; ++i) {
+        const int gi = group[size_t(i)];
+        if (gi < 0) {
+            exec_.push_back(ops_[size_t(i)]);
+            exec_.back().fusedOps = {i};
+        } else if (fused[size_t(gi)].last == i) {
+            std::sort(fused[size_t(gi)].node.fusedOps.begin(), fused[size_t(gi)].node.fusedOps.end());
+            exec_.push_back(fused[size_t(gi)].node);
+        }
+    }
+}
+
+const std::vector<OpDesc> &GraphPipeline::getExecList() {
+    finalize();
+    return exec_;
+}
+
+void GraphPipeline::finalize() {
+    if (finalized_) {
+        return;
+    }
+    fuse();
+    // Lay constants out in one slab, each on a 256-byte boundary.
+    uint64_t offset = 0;
+    for (auto &t : tensors_) {
+        if (t->cls == TensorClass::Constant) {
+            t->constOffset = offset;
+            offset += (t->sizeBytes() + 255) / 256 * 256;
+        }
+    }
+    constSlabBytes_ = offset;
+    finalized_ = true;
+}
+
+char *GraphPipeline::constantBase() {
+    finalize();
+    if (constSlab_ != nullptr || constSlabBytes_ == 0) {
+        return constSlab_;
+    }
+    if (cudaGetDevice(&constDevice_) != cudaSuccess) {
+        throw std::runtime_error("no CUDA device is available");
+    }
+    void *p = nullptr;
+    if (cudaMalloc(&p, constSlabBytes_) != cudaSuccess) {
+        throw std::runtime_error("out of device memory for graph constants");
+    }
+    constSlab_ = static_cast<char *>(p);
+    std::vector<uint8_t> staging(constSlabBytes_, 0);
+    for (auto &t : tensors_) {
+        if (t->cls == TensorClass::Constant) {
+            std::memcpy(staging.data() + t->constOffset, t->hostData.data(), t->hostData.size());
+        }
+    }
+    if (cudaMemcpy(constSlab_, staging.data(), constSlabBytes_, cudaMemcpyHostToDevice) != cudaSuccess) {
+        throw std::runtime_error("upload of graph constants failed");
+    }
+    return constSlab_;
+}
+
+GraphPipeline::~GraphPipeline() {
+    if (constSlab_ != nullptr) {
+        cudaFree(constSlab_);
+    }
+}
+
+/*******************************************************************************
+ * Interval planner
+ *******************************************************************************/
+
+namespace {
+
+struct ActiveAllocation {
+    uint32_t last;
+    uint64_t offset;
+    uint64_t size;
+    uint64_t order;
+};
+// The allocation that ends first (then the oldest) is on top.
+struct EndsLater {
+    bool operator()(const ActiveAllocation &l, const ActiveAllocation &r) const {
+        return l.last != r.last ? l.last > r.last : l.order > r.order;
+    }
+};
+struct FreeBlock {
+    uint64_t offset;
+    uint64_t size;
+    uint64_t order;
+};
+struct SmallestFirst {
+    bool operator()(const FreeBlock &l, const FreeBlock &r) const {
+        return l.size != r.size ? l.size < r.size : l.order < r.order;
+    }
+};
+uint64_t roundUp(uint64_t v, uint64_t a) { return a == 0 ? v : (v + a - 1) / a * a; }
+
+} // namespace
+
+// Same policy as the reference's details::allocateIntervals (graph/interval_memory_planner.cpp:
+// 170-216): sort by (first use, larger first, creation order); release allocations whose last use
+// precedes the interval's first use into a free list; take the smallest free block that fits and
+// split off the remainder (blocks are never merged); otherwise grow the arena.  Tensors no
+// operator touches get their own storage at the end.
+AllocationPlan allocateIntervals(std::vector<LiveInterval> intervals, const std::vector<UnseenAllocation> &unseen,
+                                 uint64_t alignment) {
+    std::stable_sort(intervals.begin(), intervals.end(), [](const LiveInterval &l, const LiveInterval &r) {
+        if (l.first != r.first) {
+            return l.first < r.first;
+        }
+        if (l.size != r.size) {
+            return l.size > r.size;
+        }
+        return l.order < r.order;
+    });
+    AllocationPlan plan;
+    std::priority_queue<ActiveAllocation, std::vector<ActiveAllocation>, EndsLater> active;
+    std::multiset<FreeBlock, SmallestFirst> freeBlocks;
+    uint64_t freeOrder = 0;
+    for (const auto &iv : intervals) {
+        while (!active.empty() && active.top().last < iv.first) {
+            freeBlocks.insert({active.top().offset, active.top().size, freeOrder++});
+            active.pop();
+        }
+        uint64_t offset = UINT64_MAX;
+        auto it = freeBlocks.lower_bound(FreeBlock{0, iv.size, 0});
+        if (it != freeBlocks.end()) {
+            offset = it->offset;
+            if (it->size > iv.size) {
+                freeBlocks.insert({it->offset + iv.size, it->size - iv.size, it->order});
+            }
+            freeBlocks.erase(it);
+        } else {
+            offset = roundUp(plan.memorySize, alignment);
+            plan.memorySize = offset + iv.size;
+        }
+        plan.offsets[iv.id] = offset;
+        active.push({iv.last, offset, iv.size, iv.order});
+    }
+    for (const auto &u : unseen) {
+        const uint64_t offset = roundUp(plan.memorySize, alignment);
+        plan.offsets[u.id] = offset;
+        plan.memorySize = offset + u.size;
+    }
+    plan.memorySize = roundUp(plan.memorySize, alignment);
+    return plan;
+}
+
+} // namespace mlel

@@ -1,0 +1,210 @@
+// Device-side helpers shared by the TOSA kernels: typed element access with the tensor
+// layer's out-of-range rules and the RESCALE arithmetic.
+//
+// Access rules follow tensor/shaders/tensor.glsl:24-86 of the reference: coordinates are
+// unsigned; a read with any coordinate >= shape yields 0; a write out of range is dropped.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../ops.hpp"
+
+namespace mlel {
+
+constexpr int kNumSMs = 148; // B200
+constexpr int kThreads = 256;
+
+inline int gridFor(int64_t work, int perBlock = kThreads, int maxBlocksPerSM = 8) {
+    int64_t blocks = (work + perBlock - 1) / perBlock;
+    const int64_t cap = int64_t(kNumSMs) * maxBlocksPerSM;
+    if (blocks > cap) {
+        blocks = cap;
+    }
+    return blocks < 1 ? 1 : int(blocks);
+}
+
+__host__ __device__ inline int dtypeSize(int32_t dtype) {
+    switch (dtype) {
+    case MLEL_BOOL:
+    case MLEL_I8:
+    case MLEL_U8:
+        return 1;
+    case MLEL_I16:
+    case MLEL_U16:
+    case MLEL_F16:
+    case MLEL_BF16:
+        return 2;
+    case MLEL_I32:
+    case MLEL_U32:
+    case MLEL_F32:
+        return 4;
+    case MLEL_I64:
+        return 8;
+    default:
+        return 0;
+    }
+}
+
+// Row-major unravel of a linear element offset (last dimension fastest).
+__device__ inline void unravel(const TView &t, uint32_t off, uint32_t *idx) {
+#pragma unroll
+    for (int i = kMaxRank - 1; i >= 0; --i) {
+        if (i < t.rank) {
+            idx[i] = off % t.dims[i];
+            off /= t.dims[i];
+        }
+    }
+}
+
+// Byte offset of a coordinate, or -1 when any coordinate is out of range.
+__device__ inline int64_t offsetOf(const TView &t, const uint32_t *c) {
+    int64_t off = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxRank; ++i) {
+        if (i < t.rank) {
+            if (c[i] >= t.dims[i]) {
+                return -1;
+            }
+            off += int64_t(c[i]) * t.strides[i];
+        }
+    }
+    return off;
+}
+
+__device__ inline int64_t loadIntAt(const TView &t, int64_t off) {
+    const char *p = t.ptr + off;
+    switch (t.dtype) {
+    case MLEL_BOOL:
+    case MLEL_I8:
+        return *reinterpret_cast<const int8_t *>(p);
+    case MLEL_U8:
+        return *reinterpret_cast<const uint8_t *>(p);
+    case MLEL_I16:
+        return *reinterpret_cast<const int16_t *>(p);
+    case MLEL_U16:
+    case MLEL_F16:
+    case MLEL_BF16:
+        return *reinterpret_cast<const uint16_t *>(p);
+    case MLEL_I32:
+        return *reinterpret_cast<const int32_t *>(p);
+    case MLEL_U32:
+    case MLEL_F32:
+        return *reinterpret_cast<const uint32_t *>(p);
+    default:
+        return *reinterpret_cast<const int64_t *>(p);
+    }
+}
+
+__device__ inline int64_t loadInt(const TView &t, const uint32_t *c) {
+    const int64_t off = offsetOf(t, c);
+    return off < 0 ? 0 : loadIntAt(t, off);
+}
+
+// Narrowing store with the constructor of the tensor's own type (wraps).
+__device__ inline void storeIntAt(const TView &t, int64_t off, int64_t v) {
+    char *p = t.ptr + off;
+    switch (dtypeSize(t.dtype)) {
+    case 1:
+        *reinterpret_cast<int8_t *>(p) = int8_t(uint8_t(uint64_t(v)));
+        break;
+    case 2:
+        *reinterpret_cast<int16_t *>(p) = int16_t(uint16_t(uint64_t(v)));
+        break;
+    case 4:
+        *reinterpret_cast<int32_t *>(p) = int32_t(uint32_t(uint64_t(v)));
+        break;
+    default:
+        *reinterpret_cast<int64_t *>(p) = v;
+        break;
+    }
+}
+
+__device__ inline void storeInt(const TView &t, const uint32_t *c, int64_t v) {
+    const int64_t off = offsetOf(t, c);
+    if (off >= 0) {
+        storeIntAt(t, off, v);
+    }
+}
+
+__host__ __device__ inline int64_t wrapTo(int32_t dtype, int64_t v) {
+    switch (dtype) {
+    case MLEL_BOOL:
+        return v != 0 ? 1 : 0;
+    case MLEL_I8:
+        return int8_t(uint8_t(uint64_t(v)));
+    case MLEL_U8:
+        return uint8_t(uint64_t(v));
+    case MLEL_I16:
+        return int16_t(uint16_t(uint64_t(v)));
+    case MLEL_U16:
+        return uint16_t(uint64_t(v));
+    case MLEL_I32:
+        return int32_t(uint32_t(uint64_t(v)));
+    case MLEL_U32:
+        return uint32_t(uint64_t(v));
+    default:
+        return v;
+    }
+}
+
+__host__ __device__ inline int64_t typeLowest(int32_t dtype) {
+    switch (dtype) {
+    case MLEL_I8:
+        return -128;
+    case MLEL_I16:
+        return -32768;
+    case MLEL_I32:
+        return -2147483647ll - 1;
+    case MLEL_I64:
+        return int64_t(0x8000000000000000ull);
+    default:
+        return 0;
+    }
+}
+
+__host__ __device__ inline int64_t typeMax(int32_t dtype) {
+    switch (dtype) {
+    case MLEL_BOOL:
+        return 1;
+    case MLEL_I8:
+        return 127;
+    case MLEL_U8:
+        return 255;
+    case MLEL_I16:
+        return 32767;
+    case MLEL_U16:
+        return 65535;
+    case MLEL_I32:
+        return 2147483647ll;
+    case MLEL_U32:
+        return 4294967295ll;
+    default:
+        return int64_t(0x7fffffffffffffffull);
+    }
+}
+
+// TOSA RESCALE scaling step as the reference computes it (rescale.comp:27-46): 64-bit
+// product, rounding term 1 << (shift-1) (0 for shift 0), +-(1<<30) when double rounding
+// and shift > 31, arithmetic shift, truncation to 32 bits.
+__host__ __device__ inline int32_t applyScale(int64_t value, int32_t multiplier, int32_t shift, bool doubleRound) {
+    int64_t round = shift > 0 ? int64_t(1ull << ((shift - 1) & 63)) : 0;
+    if (doubleRound && shift > 31) {
+        round += value >= 0 ? (int64_t(1) << 30) : -(int64_t(1) << 30);
+    }
+    const uint64_t prod = uint64_t(value) * uint64_t(int64_t(multiplier));
+    const int64_t sum = int64_t(prod + uint64_t(round));
+    return int32_t(uint32_t(uint64_t(sum >> (shift & 63))));
+}
+
+// One full RESCALE of a 32-bit-or-narrower value to a type with range [lo, hi]:
+// subtract the input zero point, scale, add the output zero point (32-bit wrap), clamp.
+__host__ __device__ inline int32_t rescaleValue(int64_t in, int32_t inZp, int32_t mult, int32_t shift,
+                                                bool doubleRound, int32_t outZp, int32_t lo, int32_t hi) {
+    int32_t r = applyScale(in - int64_t(inZp), mult, shift, doubleRound);
+    r = int32_t(uint32_t(r) + uint32_t(outZp));
+    return r < lo ? lo : (r > hi ? hi : r);
+}
+
+} // namespace mlel

@@ -1,0 +1,199 @@
+// Fused contraction + RESCALE (+ CLAMP, + residual tail) kernels in their simplest form: one
+// thread per output element.  They define the fused operators' results for every shape and are
+// what the tensor-core kernels are checked against and fall back to for shapes those do not take
+// (odd channel counts, non-zero weight zero point, explicit strides).
+//
+// Arithmetic: conv2d.comp:59-112 / depthwise_conv2d.comp:47-75 / matmul.comp:42-69 followed per
+// element by rescale.comp:27-72 and clamp.comp:24-53.
+#include "device_common.cuh"
+#include "kernels.hpp"
+
+namespace mlel {
+
+namespace {
+
+#define GRID_STRIDE(e, total)                                                                                          \
+    for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < (total); e += int64_t(gridDim.x) * blockDim.x)
+
+__device__ inline int32_t stage(const DevRescale &r, int64_t v, uint32_t c) {
+    const uint32_t ci = r.perChannel ? c : 0u;
+    return rescaleValue(v, r.inZp, r.mult[ci], int32_t(r.shift[ci]), r.doubleRound != 0, r.outZp, r.lo, r.hi);
+}
+
+// acc is the int32 contraction result (bias included); c the channel (last output coordinate);
+// flat the packed element offset of the output.
+__device__ inline int32_t epilogue(const DevEpilogue &e, int32_t acc, uint32_t c, int64_t flat) {
+    int32_t y = stage(e.main, int64_t(acc), c);
+    if (e.hasResidual) {
+        const int32_t ta = stage(e.a, int64_t(y), c);
+        const int32_t tb = stage(e.b, int64_t(e.shortcut[flat]), c);
+        const int32_t sum = int32_t(uint32_t(ta) + uint32_t(tb));
+        y = stage(e.out, int64_t(sum), c);
+    }
+    return y;
+}
+
+__host__ __device__ inline int64_t numelOf(const TView &t) {
+    int64_t n = 1;
+    for (int i = 0; i < t.rank; ++i) {
+        n *= t.dims[i];
+    }
+    return n;
+}
+
+__global__ void fusedConvKernel(TView in, TView w, TView bias, TView out, ConvAttr a, DevEpilogue epi) {
+    const int64_t total = numelOf(out);
+    const uint32_t KH = w.dims[1], KW = w.dims[2], IC = in.dims[3], H = in.dims[1], W = in.dims[2];
+    GRID_STRIDE(e, total) {
+        uint32_t idx[kMaxRank];
+        unravel(out, uint32_t(e), idx);
+        const uint32_t n = idx[0], oy = idx[1], ox = idx[2], oc = idx[3];
+        const uint32_t iy = oy * uint32_t(a.stride[0]) - uint32_t(a.pad[0]);
+        const uint32_t ix = ox * uint32_t(a.stride[1]) - uint32_t(a.pad[2]);
+        uint32_t acc = 0;
+        for (uint32_t ky = 0; ky < KH; ++ky) {
+            for (uint32_t kx = 0; kx < KW; ++kx) {
+                const uint32_t y = iy + ky * uint32_t(a.dilation[0]);
+                const uint32_t x = ix + kx * uint32_t(a.dilation[1]);
+                if (y < H && x < W) {
+                    const uint32_t ci0[4] = {n, y, x, 0};
+                    const uint32_t cw0[4] = {oc, ky, kx, 0};
+                    const int64_t io = offsetOf(in, ci0), wo = offsetOf(w, cw0);
+                    for (uint32_t ic = 0; ic < IC; ++ic) {
+                        const int32_t v = int32_t(loadIntAt(in, io + int64_t(ic) * in.strides[3])) - a.inZp;
+                        const int32_t wt = ((wo < 0 || ic >= w.dims[3])
+                                                ? 0
+                                                : int32_t(loadIntAt(w, wo + int64_t(ic) * w.strides[3]))) -
+                                           a.wZp;
+                        acc += uint32_t(v) * uint32_t(wt);
+                    }
+                }
+            }
+        }
+        const uint32_t cb[1] = {bias.dims[0] == 1 ? 0u : oc};
+        acc += uint32_t(int32_t(loadInt(bias, cb)));
+        storeInt(out, idx, epilogue(epi, int32_t(acc), oc, e));
+    }
+}
+
+__global__ void fusedDepthwiseKernel(TView in, TView w, TView bias, TView out, ConvAttr a, DevEpilogue epi) {
+    const int64_t total = numelOf(out);
+    const uint32_t KH = w.dims[0], KW = w.dims[1], M = w.dims[3], H = in.dims[1], W = in.dims[2];
+    GRID_STRIDE(e, total) {
+        uint32_t idx[kMaxRank];
+        unravel(out, uint32_t(e), idx);
+        const uint32_t n = idx[0], oy = idx[1], ox = idx[2], ocm = idx[3];
+        const uint32_t c = ocm / M, m = ocm % M;
+        const uint32_t iy = oy * uint32_t(a.stride[0]) - uint32_t(a.pad[0]);
+        const uint32_t ix = ox * uint32_t(a.stride[1]) - uint32_t(a.pad[2]);
+        uint32_t acc = 0;
+        for (uint32_t ky = 0; ky < KH; ++ky) {
+            for (uint32_t kx = 0; kx < KW; ++kx) {
+                const uint32_t y = iy + ky * uint32_t(a.dilation[0]);
+                const uint32_t x = ix + kx * uint32_t(a.dilation[1]);
+                if (y < H && x < W) {
+                    const uint32_t ci[4] = {n, y, x, c};
+                    const uint32_t cw[4] = {ky, kx, c, m};
+                    const int32_t v = int32_t(loadInt(in, ci)) - a.inZp;
+                    const int32_t wt = int32_t(loadInt(w, cw)) - a.wZp;
+                    acc += uint32_t(v) * uint32_t(wt);
+                }
+            }
+        }
+        const uint32_t cb[1] = {bias.dims[0] == 1 ? 0u : ocm};
+        acc += uint32_t(int32_t(loadInt(bias, cb)));
+        storeInt(out, idx, epilogue(epi, int32_t(acc), ocm, e));
+    }
+}
+
+__global__ void fusedMatmulKernel(TView a, TView b, TView out, int32_t zpA, int32_t zpB, DevEpilogue epi) {
+    const int64_t total = numelOf(out);
+    const uint32_t K = a.dims[2];
+    GRID_STRIDE(e, total) {
+        uint32_t idx[kMaxRank];
+        unravel(out, uint32_t(e), idx);
+        const uint32_t ca[3] = {idx[0], idx[1], 0};
+        const uint32_t cb[3] = {idx[0], 0, idx[2]};
+        const int64_t ao = offsetOf(a, ca), bo = offsetOf(b, cb);
+        uint32_t acc = 0;
+        for (uint32_t c = 0; c < K; ++c) {
+            const int32_t v1 = (ao < 0 ? 0 : int32_t(loadIntAt(a, ao + int64_t(c) * a.strides[2]))) - zpA;
+            const int32_t v2 =
+                ((bo < 0 || c >= b.dims[1]) ? 0 : int32_t(loadIntAt(b, bo + int64_t(c) * b.strides[1]))) - zpB;
+            acc += uint32_t(v1) * uint32_t(v2);
+        }
+        storeInt(out, idx, epilogue(epi, int32_t(acc), idx[2], e));
+    }
+}
+
+// 16 int8 elements per thread, 16-byte loads and stores; n is padded work in 16-element groups.
+__global__ void fusedAddKernel(const int8_t *__restrict__ x, const int8_t *__restrict__ y, int8_t *__restrict__ out,
+                               int64_t n, int64_t groups, DevEpilogue epi) {
+    const int32_t ma = epi.a.mult[0], mb = epi.b.mult[0], mo = epi.out.mult[0];
+    const int32_t sa = epi.a.shift[0], sb = epi.b.shift[0], so = epi.out.shift[0];
+    const auto one = [&](int8_t vx, int8_t vy) -> int8_t {
+        const int32_t ta = rescaleValue(vx, epi.a.inZp, ma, sa, epi.a.doubleRound != 0, epi.a.outZp, epi.a.lo, epi.a.hi);
+        const int32_t tb = rescaleValue(vy, epi.b.inZp, mb, sb, epi.b.doubleRound != 0, epi.b.outZp, epi.b.lo, epi.b.hi);
+        const int32_t sum = int32_t(uint32_t(ta) + uint32_t(tb));
+        return int8_t(rescaleValue(sum, epi.out.inZp, mo, so, epi.out.doubleRound != 0, epi.out.outZp, epi.out.lo,
+                                   epi.out.hi));
+    };
+    GRID_STRIDE(g, groups) {
+        const int4 vx = reinterpret_cast<const int4 *>(x)[g];
+        const int4 vy = reinterpret_cast<const int4 *>(y)[g];
+        int4 vo;
+        const int8_t *px = reinterpret_cast<const int8_t *>(&vx);
+        const int8_t *py = reinterpret_cast<const int8_t *>(&vy);
+        int8_t *po = reinterpret_cast<int8_t *>(&vo);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            po[k] = one(px[k], py[k]);
+        }
+        reinterpret_cast<int4 *>(out)[g] = vo;
+    }
+    // elements past the last full group (all of them when the pointers are not 16-byte aligned)
+    const int64_t rest = n - groups * 16;
+    GRID_STRIDE(t, rest) {
+        const int64_t k = groups * 16 + t;
+        out[k] = one(x[k], y[k]);
+    }
+}
+
+int finish(const char *what) {
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        setLastError(std::string(what) + ": " + cudaGetErrorString(err));
+        return MLEL_ERROR_DEVICE;
+    }
+    return MLEL_SUCCESS;
+}
+
+} // namespace
+
+int fusedConv2dGeneric(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                       const DevEpilogue &epi, cudaStream_t s) {
+    fusedConvKernel<<<gridFor(numelOf(out)), kThreads, 0, s>>>(in, w, bias, out, a, epi);
+    return finish("CONV2D+RESCALE");
+}
+
+int fusedDepthwiseGeneric(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                          const DevEpilogue &epi, cudaStream_t s) {
+    fusedDepthwiseKernel<<<gridFor(numelOf(out)), kThreads, 0, s>>>(in, w, bias, out, a, epi);
+    return finish("DEPTHWISE_CONV2D+RESCALE");
+}
+
+int fusedMatmulGeneric(const TView &a, const TView &b, const TView &out, int32_t zpA, int32_t zpB,
+                       const DevEpilogue &epi, cudaStream_t s) {
+    fusedMatmulKernel<<<gridFor(numelOf(out)), kThreads, 0, s>>>(a, b, out, zpA, zpB, epi);
+    return finish("MATMUL+RESCALE");
+}
+
+int fusedAdd(const int8_t *x, const int8_t *y, int8_t *out, int64_t n, const DevEpilogue &epi, cudaStream_t s) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) |
+                           reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    const int64_t groups = aligned ? n / 16 : 0;
+    fusedAddKernel<<<gridFor(aligned ? groups + 16 : n), kThreads, 0, s>>>(x, y, out, n, groups, epi);
+    return finish("RESCALE+ADD+RESCALE");
+}
+
+} // namespace mlel

@@ -1,0 +1,71 @@
+// Launchers of the CUDA kernels, grouped by file.  All return 0 or a negative mlel_status.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../ops.hpp"
+
+namespace mlel {
+
+struct MoveAttr {
+    int32_t kind;
+    uint32_t v[kMaxRank]; // perms / (axis, offset) / start
+    int64_t padBits;
+};
+
+// Device form of a fused RESCALE (+CLAMP) stage: rescale.comp:27-72 applied in registers.
+struct DevRescale {
+    const int32_t *mult; // [C] or [1]
+    const int8_t *shift; // [C] or [1]
+    int32_t inZp;        // narrowed to the stage's input type
+    int32_t outZp;       // narrowed to the stage's output type
+    int32_t lo, hi;      // output range (type range intersected with a following CLAMP)
+    int32_t perChannel;
+    int32_t doubleRound; // scale32 && double_round
+};
+
+struct DevEpilogue {
+    int32_t hasMain;
+    DevRescale main;
+    int32_t hasResidual;
+    const int8_t *shortcut; // packed, same shape as the output
+    DevRescale a, b, out;   // a: main path, b: shortcut, out: after the ADD
+};
+
+// fused_generic.cu: one-thread-per-output fused kernels (always-correct path of the fused kinds)
+int fusedConv2dGeneric(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                       const DevEpilogue &epi, cudaStream_t s);
+int fusedDepthwiseGeneric(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                          const DevEpilogue &epi, cudaStream_t s);
+int fusedMatmulGeneric(const TView &a, const TView &b, const TView &out, int32_t zpA, int32_t zpB,
+                       const DevEpilogue &epi, cudaStream_t s);
+// out[i] = clamp(rescale_out(rescale_a(x[i]) + rescale_b(y[i]))), all tensors packed int8 of n elements
+int fusedAdd(const int8_t *x, const int8_t *y, int8_t *out, int64_t n, const DevEpilogue &epi, cudaStream_t s);
+
+// generic_ops.cu
+int genericConv2d(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                  cudaStream_t s);
+int genericDepthwise(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                     cudaStream_t s);
+int genericMatmul(const TView &a, const TView &b, const TView &out, int32_t zpA, int32_t zpB, cudaStream_t s);
+int genericRescale(const TView &in, const TView &out, const TView &mult, const TView &shift, const RescaleAttr &a,
+                   cudaStream_t s);
+int genericAvgPool(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s);
+int genericMaxPool(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s);
+int genericTable(const TView &in, const TView &out, const TView &table, cudaStream_t s);
+int genericTranspose(const TView &in, const TView &out, const uint32_t *perms, cudaStream_t s);
+int genericConcat(const TView &in, const TView &out, uint32_t axis, uint32_t offset, cudaStream_t s);
+int genericReshape(const TView &in, const TView &out, cudaStream_t s);
+int genericSlice(const TView &in, const TView &out, const uint32_t *start, cudaStream_t s);
+int genericPad(const TView &in, const TView &out, const TView &padding, int64_t padBits, cudaStream_t s);
+int genericClamp(const TView &in, const TView &out, double minV, double maxV, cudaStream_t s);
+int genericBinary(int32_t op, const TView &a, const TView &b, const TView &out, cudaStream_t s);
+int genericMul(const TView &a, const TView &b, const TView &out, uint32_t shift, cudaStream_t s);
+int genericReduce(int32_t op, const TView &in, const TView &out, uint32_t axis, cudaStream_t s);
+int genericCast(const TView &in, const TView &out, cudaStream_t s);
+int genericArShift(const TView &a, const TView &b, const TView &out, int32_t round, cudaStream_t s);
+int genericNegate(const TView &in, const TView &out, int32_t inZp, int32_t outZp, cudaStream_t s);
+int genericSelect(const TView &c, const TView &a, const TView &b, const TView &out, cudaStream_t s);
+int genericUnary(int32_t op, const TView &in, const TView &out, cudaStream_t s);
+
+} // namespace mlel

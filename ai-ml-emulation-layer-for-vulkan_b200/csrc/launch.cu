@@ -1,0 +1,168 @@
+// Operator dispatch: picks the kernel for one OpDesc.  The order of preference is
+//   1. tensor-core / vectorised kernels for packed int8 shapes (fast_*.cu, gemm_*.cu),
+//   2. the one-thread-per-element kernels (generic_ops.cu, fused_generic.cu).
+// There is no CPU path: every branch ends in a CUDA launch or an error.
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "kernels/device_common.cuh"
+#include "kernels/kernels.hpp"
+#include "ops.hpp"
+
+namespace mlel {
+
+namespace {
+
+thread_local std::string g_lastError;
+
+ConvAttr convAttr(const OpDesc &op) {
+    ConvAttr a{};
+    for (int k = 0; k < 4; ++k) {
+        a.pad[k] = op.i[k];
+    }
+    a.stride[0] = op.i[4], a.stride[1] = op.i[5], a.dilation[0] = op.i[6], a.dilation[1] = op.i[7];
+    a.inZp = op.i[8], a.wZp = op.i[9];
+    return a;
+}
+
+PoolAttr poolAttr(const OpDesc &op) {
+    PoolAttr a{};
+    a.kernel[0] = op.i[0], a.kernel[1] = op.i[1], a.stride[0] = op.i[2], a.stride[1] = op.i[3];
+    for (int k = 0; k < 4; ++k) {
+        a.pad[k] = op.i[4 + k];
+    }
+    a.inZp = op.i[8], a.outZp = op.i[9];
+    return a;
+}
+
+DevRescale devRescale(const FusedRescale &f, const TView *T) {
+    DevRescale r{};
+    r.mult = reinterpret_cast<const int32_t *>(T[f.multTensor].ptr);
+    r.shift = reinterpret_cast<const int8_t *>(T[f.shiftTensor].ptr);
+    r.inZp = int32_t(wrapTo(f.inDtype, f.attr.inZp));
+    r.outZp = int32_t(wrapTo(f.outDtype, f.attr.outZp));
+    r.lo = f.lo, r.hi = f.hi;
+    r.perChannel = f.attr.perChannel;
+    r.doubleRound = f.attr.scale32 && f.attr.doubleRound;
+    return r;
+}
+
+DevEpilogue devEpilogue(const FusedEpilogue &e, const TView *T) {
+    DevEpilogue d{};
+    d.hasMain = e.hasMain;
+    if (e.hasMain) {
+        d.main = devRescale(e.main, T);
+    }
+    d.hasResidual = e.hasResidual;
+    if (e.hasResidual) {
+        d.a = devRescale(e.a, T);
+        d.b = devRescale(e.b, T);
+        d.out = devRescale(e.out, T);
+        d.shortcut = e.shortcutTensor >= 0 ? reinterpret_cast<const int8_t *>(T[e.shortcutTensor].ptr) : nullptr;
+    }
+    return d;
+}
+
+int64_t numelOf(const TView &t) {
+    int64_t n = 1;
+    for (int i = 0; i < t.rank; ++i) {
+        n *= t.dims[i];
+    }
+    return n;
+}
+
+// Storage bits of a PAD constant (pad.comp:46-50): int32 tensors take padConstInt, other integer
+// types the double constant converted by the storage type's constructor, fp32 the float value.
+int64_t padBits(const OpDesc &op, int32_t dtype) {
+    if (dtype == MLEL_I32) {
+        return int64_t(uint32_t(op.i[0]));
+    }
+    if (dtype == MLEL_F32) {
+        const float f = float(op.d[0]);
+        uint32_t u;
+        memcpy(&u, &f, 4);
+        return u;
+    }
+    return wrapTo(dtype, int64_t(op.d[0]));
+}
+
+} // namespace
+
+void setLastError(const std::string &msg) { g_lastError = msg; }
+const std::string &lastError() { return g_lastError; }
+
+int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
+    const auto in = [&](size_t k) -> const TView & { return T[op.in[k]]; };
+    const TView &out = T[op.out[0]];
+    switch (op.kind) {
+    case OP_CONV2D:
+        return genericConv2d(in(0), in(1), in(2), out, convAttr(op), s);
+    case OP_DEPTHWISE_CONV2D:
+        return genericDepthwise(in(0), in(1), in(2), out, convAttr(op), s);
+    case OP_MATMUL:
+        return genericMatmul(in(0), in(1), out, op.i[0], op.i[1], s);
+    case OP_RESCALE: {
+        RescaleAttr a{op.i[0], op.i[1], op.i[2], op.i[3], op.i[4]};
+        return genericRescale(in(0), out, in(1), in(2), a, s);
+    }
+    case OP_AVG_POOL2D:
+        return genericAvgPool(in(0), out, poolAttr(op), s);
+    case OP_MAX_POOL2D:
+        return genericMaxPool(in(0), out, poolAttr(op), s);
+    case OP_TABLE:
+        return genericTable(in(0), out, in(1), s);
+    case OP_TRANSPOSE: {
+        uint32_t perms[kMaxRank];
+        for (int k = 0; k < kMaxRank; ++k) {
+            perms[k] = uint32_t(op.i[k]);
+        }
+        return genericTranspose(in(0), out, perms, s);
+    }
+    case OP_CONCAT:
+        return genericConcat(in(0), out, uint32_t(op.i[0]), uint32_t(op.i[1]), s);
+    case OP_CLAMP:
+        return genericClamp(in(0), out, op.d[0], op.d[1], s);
+    case OP_BINARY:
+        return genericBinary(op.sub, in(0), in(1), out, s);
+    case OP_UNARY:
+        return genericUnary(op.sub, in(0), out, s);
+    case OP_MUL:
+        return genericMul(in(0), in(1), out, uint32_t(op.i[0]), s);
+    case OP_REDUCE:
+        return genericReduce(op.sub, in(0), out, uint32_t(op.i[0]), s);
+    case OP_CAST:
+        return genericCast(in(0), out, s);
+    case OP_RESHAPE:
+        return genericReshape(in(0), out, s);
+    case OP_SLICE: {
+        uint32_t start[kMaxRank];
+        for (int k = 0; k < kMaxRank; ++k) {
+            start[k] = uint32_t(op.i[k]);
+        }
+        return genericSlice(in(0), out, start, s);
+    }
+    case OP_PAD:
+        return genericPad(in(0), out, in(1), padBits(op, out.dtype), s);
+    case OP_ARITHMETIC_RIGHT_SHIFT:
+        return genericArShift(in(0), in(1), out, op.i[0], s);
+    case OP_NEGATE:
+        return genericNegate(in(0), out, op.i[0], op.i[1], s);
+    case OP_SELECT:
+        return genericSelect(in(0), in(1), in(2), out, s);
+    case OP_FUSED_CONV2D:
+        return fusedConv2dGeneric(in(0), in(1), in(2), out, convAttr(op), devEpilogue(op.epi, T), s);
+    case OP_FUSED_DEPTHWISE:
+        return fusedDepthwiseGeneric(in(0), in(1), in(2), out, convAttr(op), devEpilogue(op.epi, T), s);
+    case OP_FUSED_MATMUL:
+        return fusedMatmulGeneric(in(0), in(1), out, op.i[0], op.i[1], devEpilogue(op.epi, T), s);
+    case OP_FUSED_ADD:
+        return fusedAdd(reinterpret_cast<const int8_t *>(in(0).ptr), reinterpret_cast<const int8_t *>(in(1).ptr),
+                        reinterpret_cast<int8_t *>(out.ptr), numelOf(out), devEpilogue(op.epi, T), s);
+    default:
+        setLastError("unknown operator kind");
+        return MLEL_ERROR_UNKNOWN;
+    }
+}
+
+} // namespace mlel

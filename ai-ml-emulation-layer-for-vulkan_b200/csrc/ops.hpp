@@ -1,0 +1,152 @@
+// Operator descriptors shared by the graph layer (host) and the kernel launchers.
+//
+// One OpDesc is what one GraphPipeline::make<Op> call of the reference records
+// (graph/compute_graph_op.hpp:1249-1483): the operator kind, its attributes (the reference's
+// push constants / specialisation constants) and its tensor operands.
+#pragma once
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/mlel_b200.h"
+
+struct CUstream_st;
+using cudaStream_t = CUstream_st *;
+
+namespace mlel {
+
+constexpr int kMaxRank = MLEL_MAX_RANK;
+
+// Device-visible view of a tensor: address, element type, shape and byte strides.
+struct TView {
+    char *ptr;
+    int32_t dtype;
+    int32_t rank;
+    uint32_t dims[kMaxRank];
+    int64_t strides[kMaxRank];
+};
+
+enum OpKind : int32_t {
+    OP_CONV2D = 0,
+    OP_DEPTHWISE_CONV2D,
+    OP_MATMUL,
+    OP_RESCALE,
+    OP_AVG_POOL2D,
+    OP_MAX_POOL2D,
+    OP_TABLE,
+    OP_TRANSPOSE,
+    OP_CONCAT,
+    OP_CLAMP,
+    OP_BINARY,
+    OP_UNARY,
+    OP_MUL,
+    OP_REDUCE,
+    OP_CAST,
+    OP_RESHAPE,
+    OP_SLICE,
+    OP_PAD,
+    OP_ARITHMETIC_RIGHT_SHIFT,
+    OP_NEGATE,
+    OP_SELECT,
+    // Produced only by the fusion pass:
+    OP_FUSED_CONV2D,     // CONV2D -> RESCALE [-> CLAMP] [-> residual RESCALE/ADD/RESCALE [-> CLAMP]]
+    OP_FUSED_DEPTHWISE,  // DEPTHWISE_CONV2D -> RESCALE [-> CLAMP]
+    OP_FUSED_MATMUL,     // MATMUL -> RESCALE [-> CLAMP]
+    OP_FUSED_ADD,        // RESCALE(a), RESCALE(b) -> ADD -> RESCALE [-> CLAMP]
+    OP_KIND_COUNT
+};
+
+enum BinaryOp : int32_t {
+    BIN_ADD = 0,
+    BIN_SUB,
+    BIN_BITWISE_AND,
+    BIN_BITWISE_OR,
+    BIN_BITWISE_XOR,
+    BIN_LOGICAL_AND,
+    BIN_LOGICAL_OR,
+    BIN_LOGICAL_XOR,
+    BIN_LOGICAL_LEFT_SHIFT,
+    BIN_LOGICAL_RIGHT_SHIFT,
+    BIN_INTDIV,
+    BIN_MAXIMUM,
+    BIN_MINIMUM,
+    BIN_EQUAL,
+    BIN_GREATER,
+    BIN_GREATER_EQUAL,
+    BIN_COUNT
+};
+
+enum UnaryOp : int32_t { UN_ABS = 0, UN_BITWISE_NOT, UN_CLZ, UN_LOGICAL_NOT, UN_COUNT };
+enum ReduceOp : int32_t { RED_SUM = 0, RED_MAX, RED_MIN, RED_PRODUCT, RED_ALL, RED_ANY, RED_COUNT };
+
+// CONV2D / DEPTHWISE_CONV2D attributes (the push constants of conv2d.comp:26-33).
+struct ConvAttr {
+    int32_t pad[4];      // top, bottom, left, right
+    int32_t stride[2];   // y, x
+    int32_t dilation[2]; // y, x
+    int32_t inZp;
+    int32_t wZp;
+};
+
+// RESCALE attributes (rescale.comp:11-19).
+struct RescaleAttr {
+    int32_t inZp;
+    int32_t outZp;
+    int32_t scale32;
+    int32_t doubleRound;
+    int32_t perChannel;
+};
+
+// AVG_POOL2D / MAX_POOL2D attributes (avgpool2d.comp:14-20).
+struct PoolAttr {
+    int32_t kernel[2];
+    int32_t stride[2];
+    int32_t pad[4];
+    int32_t inZp;
+    int32_t outZp;
+};
+
+// One RESCALE (optionally followed by a CLAMP) folded into another kernel.  Host form: the
+// multiplier/shift are tensor ids; the session turns them into device pointers.
+struct FusedRescale {
+    int32_t multTensor{-1};
+    int32_t shiftTensor{-1};
+    int32_t inDtype{MLEL_I32};
+    int32_t outDtype{MLEL_I8};
+    RescaleAttr attr{};
+    int32_t lo{-128}, hi{127}; // output range after the optional CLAMP
+};
+
+// What the fusion pass attaches to a contraction:
+//   y   = clamp(rescale_main(acc))                                   -- CONV/MATMUL -> RESCALE [-> CLAMP]
+//   out = clamp(rescale_out(rescale_a(y) + rescale_b(shortcut)))     -- optional residual tail
+struct FusedEpilogue {
+    bool hasMain{false};
+    FusedRescale main;
+    bool hasResidual{false};
+    bool mainIsFirst{true}; // ADD(main, shortcut) or ADD(shortcut, main)
+    int32_t shortcutTensor{-1};
+    FusedRescale a, b, out;
+};
+
+struct OpDesc {
+    OpKind kind{OP_CAST};
+    int32_t sub{0};          // BinaryOp / UnaryOp / ReduceOp
+    int32_t i[24]{};         // integer attributes (layout per kind: see graph_pipeline.cpp)
+    double d[2]{};           // CLAMP bounds / PAD constant
+    std::string name;        // debug name ("CONV2D", ...), as logged by the reference
+    std::vector<int32_t> in; // tensor ids: data inputs, then attribute tensors
+    std::vector<int32_t> out;
+    FusedEpilogue epi;              // fused kinds only
+    std::vector<int32_t> fusedOps;  // indices of the logical ops an exec node stands for
+};
+
+// Launches one operator.  `tensors` is indexed by tensor id (op.in / op.out / op.epi hold ids).
+// Returns 0 or a negative mlel_status and sets the thread's last-error message.
+int launchOp(const OpDesc &op, const TView *tensors, cudaStream_t stream);
+
+void setLastError(const std::string &msg);
+int elemSize(int32_t dtype);
+
+} // namespace mlel

@@ -1,0 +1,259 @@
+/*
+ * C ABI of the B200 (sm_100a) implementation of the ML Emulation Layer's TOSA data-graph
+ * execution path.
+ *
+ * The reference reaches this path through Vulkan entry points of VkLayer_Graph
+ * (graph/graph_layer.cpp) and, below them, through the C++ class GraphPipeline
+ * (graph/compute_graph_op.hpp:1204-1549).  Vulkan handles have no meaning on a CUDA-only
+ * machine, so this ABI keeps the same objects and call order with plain pointers:
+ *
+ *   VkPipeline (data graph)          -> mlel_pipeline*
+ *   VkDataGraphPipelineSessionARM    -> mlel_session*
+ *   VkTensorDescriptionARM           -> mlel_tensor_desc
+ *   VkDeviceMemory + offset          -> device pointer (+ offset)
+ *   VkCommandBuffer / queue order    -> cudaStream_t (passed as void*)
+ *
+ * Every function returns MLEL_SUCCESS (0) or a negative mlel_status; mlel_last_error()
+ * gives the message of the last failure on the calling thread.  No exception crosses the
+ * ABI.  A pipeline is immutable once a session exists; a session must be used from one
+ * stream at a time.  All device work runs on the CUDA device that is current when the
+ * pipeline's first session is created.
+ */
+#ifndef MLEL_B200_H
+#define MLEL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLEL_MAX_RANK 6 /* graph/shaders/graph_op/common.comp:11 */
+
+typedef enum mlel_status {
+    MLEL_SUCCESS = 0,
+    MLEL_ERROR_UNKNOWN = -13,            /* value of VK_ERROR_UNKNOWN: malformed input */
+    MLEL_ERROR_FEATURE_NOT_PRESENT = -8, /* value of VK_ERROR_FEATURE_NOT_PRESENT: op/type not supported */
+    MLEL_INCOMPLETE = 5,                 /* value of VK_INCOMPLETE: caller's array too short */
+    MLEL_ERROR_OUT_OF_DEVICE_MEMORY = -2,
+    MLEL_ERROR_DEVICE = -4               /* a CUDA call failed (value of VK_ERROR_DEVICE_LOST) */
+} mlel_status;
+
+/* Element types.  Integer tensor formats are always signed in the graph layer
+ * (graph/graph_ext_inst_context.cpp:355-402). */
+typedef enum mlel_dtype {
+    MLEL_BOOL = 0,
+    MLEL_I8 = 1,
+    MLEL_I16 = 2,
+    MLEL_I32 = 3,
+    MLEL_I64 = 4,
+    MLEL_U8 = 5,
+    MLEL_U16 = 6,
+    MLEL_U32 = 7,
+    MLEL_F16 = 8,
+    MLEL_BF16 = 9,
+    MLEL_F32 = 10
+} mlel_dtype;
+
+/* Replaces VkTensorDescriptionARM.  strides are in bytes; strides[0] == 0 means packed
+ * row-major (tensor/tensor_arm.cpp:82-92). */
+typedef struct mlel_tensor_desc {
+    int32_t dtype;
+    int32_t rank;
+    int64_t dims[MLEL_MAX_RANK];
+    int64_t strides[MLEL_MAX_RANK];
+} mlel_tensor_desc;
+
+/* A tensor operand of a direct kernel call: a descriptor plus a device address. */
+typedef struct mlel_tensor {
+    void *data;
+    mlel_tensor_desc desc;
+} mlel_tensor;
+
+typedef struct mlel_pipeline mlel_pipeline;
+typedef struct mlel_session mlel_session;
+typedef int32_t mlel_tensor_id; /* index of a tensor descriptor inside its pipeline */
+
+const char *mlel_last_error(void);
+int mlel_elem_size(int32_t dtype);
+
+/* ---- pipeline construction: replaces vkCreateDataGraphPipelinesARM, graph/graph_layer.cpp:815-964 ---- */
+
+/* flags for mlel_pipeline_create */
+#define MLEL_PIPELINE_NO_FUSION 1u /* run one kernel per TOSA op, exactly the reference's op list */
+
+int mlel_pipeline_create(uint32_t flags, mlel_pipeline **out);
+void mlel_pipeline_destroy(mlel_pipeline *pipeline); /* vkDestroyPipeline, graph_layer.cpp:1280-1295 */
+
+/* GraphPipeline::makeDescriptorSetBinding, graph/compute_graph_op.cpp:2441-2450 */
+int mlel_pipeline_bind_external(mlel_pipeline *p, uint32_t set, uint32_t binding, uint32_t array_index,
+                                const mlel_tensor_desc *desc, mlel_tensor_id *out);
+/* GraphPipeline::getTensor(set, binding, arrayIndex), compute_graph_op.cpp:2452-2455 */
+int mlel_pipeline_get_external(mlel_pipeline *p, uint32_t set, uint32_t binding, uint32_t array_index,
+                               mlel_tensor_id *out);
+/* GraphPipeline::makeConstTensor (data is copied), compute_graph_op.cpp:2398-2407 */
+int mlel_pipeline_add_constant(mlel_pipeline *p, uint32_t id, const mlel_tensor_desc *desc, const void *host_data,
+                               mlel_tensor_id *out);
+/* GraphPipeline::getConstTensor, compute_graph_op.cpp:2409-2411 */
+int mlel_pipeline_get_constant(mlel_pipeline *p, uint32_t id, mlel_tensor_id *out);
+/* GraphPipeline::makeConstCompositeTensor, compute_graph_op.cpp:2413-2425 */
+int mlel_pipeline_make_composite_constant(mlel_pipeline *p, const mlel_tensor_desc *desc, const void *host_data,
+                                          mlel_tensor_id *out);
+/* GraphPipeline::makeTensor (session memory), compute_graph_op.cpp:2457-2469 */
+int mlel_pipeline_make_tensor(mlel_pipeline *p, const mlel_tensor_desc *desc, mlel_tensor_id *out);
+/* GraphPipeline::makeInput / makeOutput, compute_graph_op.cpp:2513-2521 */
+int mlel_pipeline_mark_input(mlel_pipeline *p, mlel_tensor_id tensor);
+int mlel_pipeline_mark_output(mlel_pipeline *p, mlel_tensor_id tensor);
+
+/* Lowers a SPIR-V module in assembly text form (the form of the reference's tests/shader
+ * fixtures) through the TOSA.001000.1 registry.  External bindings and graph constants must
+ * have been registered first, as vkCreateDataGraphPipelinesARM does (graph_layer.cpp:874-901)
+ * before it runs the graph pass (graph/graph_pass_ext_inst.cpp:25-82). */
+int mlel_pipeline_lower_spvasm(mlel_pipeline *p, const char *text);
+
+/* Registry queries: graph/graph_ext_inst_registry.cpp:36-59, graph/graph_tosa_1_0_ext_inst.cpp:41-108 */
+int mlel_ext_inst_set_registered(const char *import_name);
+int mlel_tosa_op_count(void);
+const char *mlel_tosa_op_name(int index);
+int mlel_tosa_op_supported(const char *op_name);
+
+/* Introspection of the lowered graph (the reference logs the same at Info severity). */
+int mlel_pipeline_op_count(const mlel_pipeline *p);
+const char *mlel_pipeline_op_name(const mlel_pipeline *p, int index);
+int mlel_pipeline_exec_count(mlel_pipeline *p);               /* kernels per dispatch after fusion */
+const char *mlel_pipeline_exec_name(mlel_pipeline *p, int index);
+int mlel_pipeline_tensor_desc(const mlel_pipeline *p, mlel_tensor_id tensor, mlel_tensor_desc *out);
+
+/* ---- TOSA operators: one call per GraphPipeline::make<Op>, graph/compute_graph_op.hpp:1249-1483.
+ * Argument order and meaning are the reference's; tensors are ids of this pipeline. ---- */
+int mlel_make_conv2d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, mlel_tensor_id weights,
+                     mlel_tensor_id biases, const int32_t pad[4], const int32_t stride[2], const int32_t dilation[2],
+                     int8_t input_zp, int8_t weight_zp, uint32_t acc_type, const char *debug_name);
+int mlel_make_depthwise_conv2d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, mlel_tensor_id weights,
+                               mlel_tensor_id biases, const int32_t pad[4], const int32_t stride[2],
+                               const int32_t dilation[2], int8_t input_zp, int8_t weight_zp, uint32_t acc_type,
+                               const char *debug_name);
+int mlel_make_matmul(mlel_pipeline *p, mlel_tensor_id input1, mlel_tensor_id input2, mlel_tensor_id output,
+                     int32_t input1_zp, int32_t input2_zp, const char *debug_name);
+int mlel_make_rescale(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, int32_t input_zp,
+                      int32_t output_zp, mlel_tensor_id multiplier, mlel_tensor_id shift, int scale32,
+                      int double_round, int per_channel, int input_unsigned, int output_unsigned,
+                      const char *debug_name);
+int mlel_make_avg_pool2d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const int32_t kernel[2],
+                         const int32_t stride[2], const int32_t pad[4], uint32_t acc_type, int8_t input_zp,
+                         int8_t output_zp, const char *debug_name);
+int mlel_make_max_pool2d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const int32_t kernel[2],
+                         const int32_t stride[2], const int32_t pad[4], uint32_t nan_mode, const char *debug_name);
+int mlel_make_table(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, mlel_tensor_id table,
+                    const char *debug_name);
+int mlel_make_transpose(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const uint32_t *perms,
+                        uint32_t perm_count, const char *debug_name);
+int mlel_make_concat(mlel_pipeline *p, const mlel_tensor_id *inputs, uint32_t input_count, mlel_tensor_id output,
+                     uint32_t axis, const char *debug_name);
+int mlel_make_clamp(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, double min_value,
+                    double max_value, uint32_t nan_mode, const char *debug_name);
+/* makeAdd, makeSub, makeBitwise*, makeLogical*, makeIntdiv, makeMaximum, makeMinimum, makeEqual,
+ * makeGreater, makeGreaterEqual: `op_name` is the TOSA name ("ADD", "LOGICAL_LEFT_SHIFT", ...). */
+int mlel_make_binary(mlel_pipeline *p, const char *op_name, mlel_tensor_id input1, mlel_tensor_id input2,
+                     mlel_tensor_id output, uint32_t nan_mode, const char *debug_name);
+/* makeAbs, makeBitwiseNot, makeClz, makeLogicalNot (integer unary operators) */
+int mlel_make_unary(mlel_pipeline *p, const char *op_name, mlel_tensor_id input, mlel_tensor_id output,
+                    const char *debug_name);
+int mlel_make_mul(mlel_pipeline *p, mlel_tensor_id input1, mlel_tensor_id input2, mlel_tensor_id output,
+                  uint32_t shift, const char *debug_name);
+/* makeReduceSum/Max/Min/Product/All/Any: `op_name` is "REDUCE_SUM", ... */
+int mlel_make_reduce(mlel_pipeline *p, const char *op_name, mlel_tensor_id input, mlel_tensor_id output,
+                     uint32_t axis, uint32_t nan_mode, const char *debug_name);
+int mlel_make_cast(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const char *debug_name);
+int mlel_make_reshape(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const char *debug_name);
+int mlel_make_slice(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const uint32_t *start,
+                    uint32_t start_count, const char *debug_name);
+int mlel_make_pad(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, mlel_tensor_id padding,
+                  double pad_const, int32_t pad_const_int, const char *debug_name);
+int mlel_make_arithmetic_right_shift(mlel_pipeline *p, mlel_tensor_id input1, mlel_tensor_id input2,
+                                     mlel_tensor_id output, int round, const char *debug_name);
+int mlel_make_negate(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, int32_t input_zp,
+                     int32_t output_zp, const char *debug_name);
+int mlel_make_select(mlel_pipeline *p, mlel_tensor_id input1, mlel_tensor_id input2, mlel_tensor_id input3,
+                     mlel_tensor_id output, const char *debug_name);
+
+/* ---- interval memory planner: details::allocateIntervals, graph/interval_memory_planner.cpp:170-216 ---- */
+typedef struct mlel_live_interval {
+    uint64_t id;
+    uint32_t first;
+    uint32_t last;
+    uint64_t size;
+    uint64_t order;
+} mlel_live_interval;
+typedef struct mlel_unseen_allocation {
+    uint64_t id;
+    uint64_t size;
+} mlel_unseen_allocation;
+/* offsets_out[i] receives the offset of intervals[i]; unseen_offsets_out[j] that of unseen[j]. */
+int mlel_allocate_intervals(const mlel_live_interval *intervals, size_t interval_count,
+                            const mlel_unseen_allocation *unseen, size_t unseen_count, uint64_t alignment,
+                            uint64_t *offsets_out, uint64_t *unseen_offsets_out, uint64_t *memory_size_out);
+
+/* ---- session: graph/graph_layer.cpp:215-298, 1297-1420, 1844-1917 ---- */
+/* vkCreateDataGraphPipelineSessionARM: plans session memory with the interval planner. */
+int mlel_session_create(mlel_pipeline *p, mlel_session **out);
+void mlel_session_destroy(mlel_session *s);
+/* vkGetDataGraphPipelineSessionMemoryRequirementsARM */
+int mlel_session_memory_requirements(const mlel_session *s, uint64_t *size, uint64_t *alignment);
+/* Planned offset of one session tensor inside the bound memory (for inspection and tests). */
+int mlel_session_tensor_offset(const mlel_session *s, mlel_tensor_id tensor, uint64_t *offset);
+/* vkBindDataGraphPipelineSessionMemoryARM: `memory` is a device pointer owned by the caller. */
+int mlel_session_bind_memory(mlel_session *s, void *memory, uint64_t offset);
+/* Descriptor-set update of one application tensor (vkUpdateDescriptorSets + vkCmdBindDescriptorSets). */
+int mlel_session_set_external(mlel_session *s, uint32_t set, uint32_t binding, uint32_t array_index,
+                              void *device_ptr);
+/* vkCmdDispatchDataGraphARM + queue submission: enqueues every kernel of the graph on `stream`. */
+int mlel_session_dispatch(mlel_session *s, void *cuda_stream);
+/* Same, replayed from a CUDA graph captured on first use (bindings must not change afterwards). */
+int mlel_session_dispatch_graph(mlel_session *s, void *cuda_stream);
+/* Number of kernels one dispatch launches. */
+int mlel_session_launch_count(const mlel_session *s);
+/* Host-buffer convenience used for end-to-end timing: copies `n_in` host inputs to their bound
+ * device tensors, dispatches, copies `n_out` outputs back, and synchronises the stream. */
+typedef struct mlel_host_io {
+    uint32_t set, binding, array_index;
+    void *host_ptr;
+    uint64_t bytes;
+} mlel_host_io;
+int mlel_session_run_host(mlel_session *s, const mlel_host_io *inputs, uint32_t n_in, const mlel_host_io *outputs,
+                          uint32_t n_out, void *cuda_stream);
+
+/* ---- direct kernel entry points: one per reference shader, graph/shaders/graph_op/tosa/<op>.comp.
+ * Operands are device tensors; work is enqueued on `cuda_stream`. ---- */
+int mlel_cuda_conv2d(const mlel_tensor *input, const mlel_tensor *weights, const mlel_tensor *biases,
+                     const mlel_tensor *output, const int32_t pad[4], const int32_t stride[2],
+                     const int32_t dilation[2], int32_t input_zp, int32_t weight_zp, void *cuda_stream);
+int mlel_cuda_depthwise_conv2d(const mlel_tensor *input, const mlel_tensor *weights, const mlel_tensor *biases,
+                               const mlel_tensor *output, const int32_t pad[4], const int32_t stride[2],
+                               const int32_t dilation[2], int32_t input_zp, int32_t weight_zp, void *cuda_stream);
+int mlel_cuda_matmul(const mlel_tensor *a, const mlel_tensor *b, const mlel_tensor *output, int32_t a_zp,
+                     int32_t b_zp, void *cuda_stream);
+int mlel_cuda_rescale(const mlel_tensor *input, const mlel_tensor *output, const mlel_tensor *multiplier,
+                      const mlel_tensor *shift, int32_t input_zp, int32_t output_zp, int scale32, int double_round,
+                      int per_channel, void *cuda_stream);
+
+/* Fused int8 contraction + RESCALE (+ CLAMP): what the fusion pass substitutes for
+ * MATMUL -> RESCALE [-> CLAMP] (matmul.comp + rescale.comp + clamp.comp in one kernel).
+ * a: [N,H,C] int8, b: [N,C,W] int8, out: [N,H,W] int8. clamp_min > clamp_max disables CLAMP. */
+int mlel_cuda_matmul_rescale(const mlel_tensor *a, const mlel_tensor *b, const mlel_tensor *output, int32_t a_zp,
+                             int32_t b_zp, const mlel_tensor *multiplier, const mlel_tensor *shift,
+                             int32_t rescale_in_zp, int32_t output_zp, int double_round, int per_channel,
+                             int32_t clamp_min, int32_t clamp_max, void *cuda_stream);
+/* CONV2D -> RESCALE [-> CLAMP] in one kernel (conv2d.comp + rescale.comp + clamp.comp). */
+int mlel_cuda_conv2d_rescale(const mlel_tensor *input, const mlel_tensor *weights, const mlel_tensor *biases,
+                             const mlel_tensor *output, const int32_t pad[4], const int32_t stride[2],
+                             const int32_t dilation[2], int32_t input_zp, int32_t weight_zp,
+                             const mlel_tensor *multiplier, const mlel_tensor *shift, int32_t rescale_in_zp,
+                             int32_t output_zp, int double_round, int per_channel, int32_t clamp_min,
+                             int32_t clamp_max, void *cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLEL_B200_H */

@@ -1,0 +1,31 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from __graft_entry__ import load_package  # noqa: E402
+
+REFERENCE_ROOT = "/root/reference"  # present only in the authoring container; never needed on a GPU box
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def mlel():
+    """The package, with its CUDA library loaded (fails loudly when the library is not built)."""
+    pkg = load_package()
+    pkg.lib()
+    return pkg
+
+
+@pytest.fixture(scope="session")
+def reference_root():
+    if not os.path.isdir(REFERENCE_ROOT):
+        pytest.skip("reference checkout not present")
+    return REFERENCE_ROOT
