@@ -106,7 +106,7 @@ def make_desc(dtype: int, dims: Sequence[int], strides: Sequence[int] | None = N
     d = TensorDesc()
     d.dtype = int(dtype)
     d.rank = len(dims)
-    for i, v in enumerate(dims):
+    for i, v in enumerate(dims[:MAX_RANK]):  # a rank above MAX_RANK is rejected by the library
         d.dims[i] = int(v)
     if strides is not None:
         for i, v in enumerate(strides):
@@ -359,6 +359,13 @@ class Session:
 
     def dispatch_graph(self, stream: int = 0) -> None:
         check(lib().mlel_session_dispatch_graph(self._h, ctypes.c_void_p(stream)))
+
+    def dispatch_profiled(self, stream: int = 0) -> list[float]:
+        """Per-kernel device milliseconds of one dispatch (synchronises the stream)."""
+        n = self.launch_count()
+        ms = (ctypes.c_float * max(1, n))()
+        check(lib().mlel_session_dispatch_profiled(self._h, ctypes.c_void_p(stream), ms, n))
+        return [ms[i] for i in range(n)]
 
     def launch_count(self) -> int:
         return lib().mlel_session_launch_count(self._h)

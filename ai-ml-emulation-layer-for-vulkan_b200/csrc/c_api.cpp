@@ -497,6 +497,11 @@ int mlel_session_dispatch_graph(mlel_session *s, void *cuda_stream) {
     return guarded([&] { return s->impl.dispatchGraph(static_cast<cudaStream_t>(cuda_stream)); });
 }
 
+int mlel_session_dispatch_profiled(mlel_session *s, void *cuda_stream, float *ms_out, uint32_t capacity) {
+    return guarded(
+        [&] { return s->impl.dispatchProfiled(static_cast<cudaStream_t>(cuda_stream), ms_out, capacity); });
+}
+
 int mlel_session_launch_count(const mlel_session *s) {
     int n = -1;
     guarded([&] {

@@ -98,8 +98,11 @@ void Session::bindMemory(void *memory, uint64_t offset) {
 
 void Session::setExternal(uint32_t set, uint32_t binding, uint32_t arrayIndex, void *devicePtr) {
     (void)pipeline_->getTensor(set, binding, arrayIndex); // throws std::out_of_range when unknown
-    external_[std::make_tuple(set, binding, arrayIndex)] = static_cast<char *>(devicePtr);
-    resolved_ = false;
+    char *&slot = external_[std::make_tuple(set, binding, arrayIndex)];
+    if (slot != static_cast<char *>(devicePtr)) {
+        slot = static_cast<char *>(devicePtr);
+        resolved_ = false;
+    }
 }
 
 int Session::resolve() {
@@ -186,6 +189,39 @@ int Session::dispatch(cudaStream_t stream) {
         }
     }
     return MLEL_SUCCESS;
+}
+
+int Session::dispatchProfiled(cudaStream_t stream, float *msOut, uint32_t capacity) {
+    const int rc = resolve();
+    if (rc != MLEL_SUCCESS) {
+        return rc;
+    }
+    const auto &exec = pipeline_->getExecList();
+    if (capacity < exec.size()) {
+        setLastError("dispatch_profiled: output array too short");
+        return MLEL_INCOMPLETE;
+    }
+    std::vector<cudaEvent_t> events(exec.size() + 1);
+    for (auto &e : events) {
+        cudaEventCreate(&e);
+    }
+    int result = MLEL_SUCCESS;
+    cudaEventRecord(events[0], stream);
+    for (size_t k = 0; k < exec.size() && result == MLEL_SUCCESS; ++k) {
+        result = launchOp(exec[k], views_.data(), stream);
+        cudaEventRecord(events[k + 1], stream);
+    }
+    if (cudaStreamSynchronize(stream) != cudaSuccess && result == MLEL_SUCCESS) {
+        setLastError("dispatch_profiled: stream synchronisation failed");
+        result = MLEL_ERROR_DEVICE;
+    }
+    for (size_t k = 0; k < exec.size() && result == MLEL_SUCCESS; ++k) {
+        cudaEventElapsedTime(&msOut[k], events[k], events[k + 1]);
+    }
+    for (auto &e : events) {
+        cudaEventDestroy(e);
+    }
+    return result;
 }
 
 int Session::dispatchGraph(cudaStream_t stream) {

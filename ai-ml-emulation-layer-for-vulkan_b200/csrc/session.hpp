@@ -29,6 +29,7 @@ class Session {
 
     int dispatch(cudaStream_t stream);
     int dispatchGraph(cudaStream_t stream);
+    int dispatchProfiled(cudaStream_t stream, float *msOut, uint32_t capacity);
     int launchCount() const { return int(pipeline_->getExecList().size()); }
     int runHost(const mlel_host_io *inputs, uint32_t nIn, const mlel_host_io *outputs, uint32_t nOut,
                 cudaStream_t stream);

@@ -212,6 +212,11 @@ int mlel_session_set_external(mlel_session *s, uint32_t set, uint32_t binding, u
 int mlel_session_dispatch(mlel_session *s, void *cuda_stream);
 /* Same, replayed from a CUDA graph captured on first use (bindings must not change afterwards). */
 int mlel_session_dispatch_graph(mlel_session *s, void *cuda_stream);
+/* Dispatch with a CUDA event pair around every launched kernel, the counterpart of the reference's
+ * per-operator timestamp profiling (VMEL_GRAPH_PROFILING, graph/graph_profiler.cpp:157-191).
+ * Synchronises the stream; ms_out[i] receives the device time of kernel i (see
+ * mlel_pipeline_exec_name); `capacity` must be at least mlel_session_launch_count(). */
+int mlel_session_dispatch_profiled(mlel_session *s, void *cuda_stream, float *ms_out, uint32_t capacity);
 /* Number of kernels one dispatch launches. */
 int mlel_session_launch_count(const mlel_session *s);
 /* Host-buffer convenience used for end-to-end timing: copies `n_in` host inputs to their bound

@@ -9,6 +9,8 @@ if ROOT not in sys.path:
 
 from __graft_entry__ import load_package  # noqa: E402
 
+load_package()  # registers the package as module "mlel_b200" so that tests can import its submodules
+
 REFERENCE_ROOT = "/root/reference"  # present only in the authoring container; never needed on a GPU box
 
 

@@ -1,0 +1,58 @@
+"""The C-ABI library loads on a machine without a GPU and exports every function that
+include/mlel_b200.h declares (no compute is called here)."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "mlel_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mlel_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(mlel):
+    lib = mlel.lib()
+    names = declared_functions()
+    assert len(names) > 50
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_registry(mlel):
+    names = mlel.tosa_op_names()
+    assert len(names) == 66  # graph/graph_tosa_1_0_ext_inst.cpp:41-108
+    assert mlel.ext_inst_set_registered("TOSA.001000.1")
+    assert not mlel.ext_inst_set_registered("TOSA.000080.2")
+    for op in ("CONV2D", "DEPTHWISE_CONV2D", "MATMUL", "RESCALE", "AVG_POOL2D", "MAX_POOL2D", "TABLE", "TRANSPOSE",
+               "CONCAT", "CLAMP", "ADD", "SUB", "MUL", "REDUCE_SUM", "REDUCE_MAX", "CAST", "RESHAPE", "SLICE", "PAD"):
+        assert op in names and mlel.tosa_op_supported(op)
+    assert not mlel.tosa_op_supported("FFT2D")
+
+
+def test_errors_are_status_codes_not_exceptions(mlel):
+    p = mlel.Pipeline()
+    a = p.bind_external(0, 0, mlel.I8, (1, 4, 4, 4))
+    import pytest
+    with pytest.raises(mlel.MlelError) as e:  # fp16 accumulate is not built: FEATURE_NOT_PRESENT
+        w = p.composite_constant(__import__("numpy").zeros((4, 1, 1, 4), "int8"))
+        b = p.composite_constant(__import__("numpy").zeros((4,), "int32"))
+        o = p.make_tensor(mlel.I32, (1, 4, 4, 4))
+        p.conv2d(a, o, w, b, [0] * 4, [1, 1], [1, 1], 0, 0, acc_type=2)
+    assert e.value.status == -8
+    with pytest.raises(mlel.MlelError) as e:
+        p.lower_spvasm("this is not spir-v")
+    assert e.value.status == -13
+    with pytest.raises(mlel.MlelError):
+        p.get_external(3, 3)
+    with pytest.raises(mlel.MlelError):
+        p.bind_external(0, 9, mlel.I8, (1, 2, 3, 4, 5, 6, 7))  # rank > 6
+
+
+def test_library_has_no_oracle_dependency():
+    import subprocess
+    out = subprocess.run(["ldd", os.path.join(ROOT, "ai-ml-emulation-layer-for-vulkan_b200", "libmlel_b200.so")],
+                         capture_output=True, text=True).stdout
+    assert "oracle" not in out

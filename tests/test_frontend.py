@@ -1,0 +1,140 @@
+"""SPIR-V text front end and TOSA registry (host logic, no GPU).
+
+Where the reference checkout is present its own fixtures (tests/shader/*.spvasm) are lowered
+unmodified and the resulting operator lists are checked; the same structures are also covered by
+graphs emitted by GraphBuilder, which travel with the repository."""
+import os
+
+import numpy as np
+import pytest
+
+from mlel_b200.graph_builder import GraphBuilder
+from mlel_b200.model_graphs import mobilenet_v2_graph, resnet50_graph
+
+
+def lower(mlel, text, externals, constants=(), flags=0):
+    p = mlel.Pipeline(flags)
+    for (s, b, idx, dtype, dims) in externals:
+        p.bind_external(s, b, dtype, dims, array_index=idx)
+    for cid, arr in constants:
+        p.add_constant(cid, arr)
+    p.lower_spvasm(text)
+    return p
+
+
+def fixture(reference_root, name):
+    return open(os.path.join(reference_root, "tests", "shader", name)).read()
+
+
+def test_reference_conv2d_fixture(mlel, reference_root):
+    p = lower(mlel, fixture(reference_root, "conv2d.spvasm"),
+              [(0, 0, 0, mlel.I8, (1, 8, 8, 3)), (0, 1, 0, mlel.I8, (3, 2, 2, 3)), (0, 2, 0, mlel.I32, (3,)),
+               (0, 3, 0, mlel.I32, (1, 4, 4, 3))])
+    assert p.op_names() == ["CONV2D"]
+    s = mlel.Session(p)
+    assert s.memory_requirements()[0] == 0  # no intermediate tensors
+
+
+def test_reference_maxpool_fixture_uses_array_element(mlel, reference_root):
+    # graph input 0 is element 1 of a tensor array bound at (0, 0) (tests/shader/maxpool.spvasm:33-41)
+    p = lower(mlel, fixture(reference_root, "maxpool.spvasm"),
+              [(0, 0, 0, mlel.I8, (1, 16, 16, 3)), (0, 0, 1, mlel.I8, (1, 16, 16, 3)),
+               (0, 1, 0, mlel.I8, (1, 8, 8, 3))])
+    assert p.op_names() == ["MAX_POOL2D"]
+
+
+def test_reference_two_layer_maxpool_plans_one_intermediate(mlel, reference_root):
+    p = lower(mlel, fixture(reference_root, "twolayer-maxpool.spvasm"),
+              [(0, 0, 0, mlel.I8, (1, 16, 16, 3)), (0, 1, 0, mlel.I8, (1, 4, 4, 3))])
+    assert p.op_names() == ["MAX_POOL2D", "MAX_POOL2D"]
+    size, align = mlel.Session(p).memory_requirements()
+    assert align == 256 and size == 256  # [1,8,8,3] int8 = 192 bytes, rounded up to the alignment
+
+
+def test_reference_graph_constant_fixture(mlel, reference_root):
+    consts = [(0, np.array([2], np.int32)), (1, np.array([0], np.int8)), (2, np.array([3], np.int32)),
+              (3, np.array([0], np.int8)), (4, np.array([4], np.int32)), (5, np.array([0], np.int8))]
+    ext = [(0, 0, 0, mlel.I8, (5,)), (0, 1, 0, mlel.I8, (5,)), (0, 2, 0, mlel.I8, (5,))]
+    p = lower(mlel, fixture(reference_root, "graph-constant-arm.spvasm"), ext, consts, mlel.PIPELINE_NO_FUSION)
+    assert p.op_names() == ["RESCALE", "RESCALE", "ADD", "RESCALE"]
+    assert p.exec_names() == ["RESCALE", "RESCALE", "ADD", "RESCALE"]
+    fused = lower(mlel, fixture(reference_root, "graph-constant-arm.spvasm"), ext, consts)
+    assert fused.exec_names() == ["RESCALE+RESCALE+ADD+RESCALE"]
+
+
+def test_reference_misc_fixtures(mlel, reference_root):
+    p = lower(mlel, fixture(reference_root, "inlined-higher-rank-constant.spvasm"),
+              [(0, 0, 0, mlel.I8, (1, 3, 3, 1)), (0, 1, 0, mlel.I8, (1, 3, 3, 1))])
+    assert p.op_names() == ["CONV2D", "CAST"]
+    p = lower(mlel, fixture(reference_root, "concat_interval.spvasm"),
+              [(0, 0, 0, mlel.F32, (3, 3)), (0, 1, 0, mlel.F32, (3, 3)), (0, 2, 0, mlel.F32, (3, 1)),
+               (0, 3, 0, mlel.F32, (12,))])
+    assert p.op_names() == ["ADD", "CONCAT", "CONCAT", "RESHAPE"]  # one CONCAT pass per input
+    p = lower(mlel, fixture(reference_root, "nop-outputs.spvasm"),
+              [(0, 0, 0, mlel.I8, (1, 8, 8, 3)), (0, 1, 0, mlel.I8, (1, 2, 2, 2)), (0, 2, 0, mlel.I8, (1, 8, 8, 3)),
+               (0, 3, 0, mlel.I8, (1, 8, 8, 3))], [(0, np.arange(192, dtype=np.int8).reshape(1, 8, 8, 3))])
+    assert sorted(p.op_names()) == ["CAST", "CAST", "SLICE"]  # pass-through outputs become CAST
+    p = lower(mlel, fixture(reference_root, "arshift_specbool.spvasm"),
+              [(0, 0, 0, mlel.I8, (4,)), (0, 1, 0, mlel.I8, (4,)), (0, 2, 0, mlel.I8, (4,))])
+    assert p.op_names() == ["ARITHMETIC_RIGHT_SHIFT"]
+    p = lower(mlel, fixture(reference_root, "conv2_acc_int64.spvasm"),
+              [(0, 0, 0, mlel.I16, (1, 2, 2, 4)), (0, 1, 0, mlel.I8, (4, 1, 1, 4)), (0, 2, 0, mlel.I64, (4,)),
+               (0, 3, 0, mlel.I64, (1, 2, 2, 4))])
+    assert p.op_names() == ["CONV2D"]
+
+
+def test_unbuilt_operator_is_feature_not_present(mlel, reference_root):
+    with pytest.raises(mlel.MlelError) as e:
+        lower(mlel, fixture(reference_root, "sin.spvasm"),
+              [(0, 0, 0, mlel.F32, (1, 16, 16, 16)), (0, 1, 0, mlel.F32, (1, 16, 16, 16))])
+    assert e.value.status == -8
+
+
+def test_unregistered_instruction_set_is_rejected(mlel):
+    g = GraphBuilder()
+    x = g.input(np.int8, (4,))
+    g.output(g.unary("ABS", x))
+    text = g.spvasm().replace("TOSA.001000.1", "TOSA.000080.2")
+    with pytest.raises(mlel.MlelError) as e:
+        lower(mlel, text, [(0, 0, 0, mlel.I8, (4,)), (0, 1, 0, mlel.I8, (4,))])
+    assert "Unsupported extension" in str(e.value)
+
+
+def test_emitted_resnet_lowers_and_fuses(mlel):
+    g, _ = resnet50_graph(seed=0, n=2, image=64, width=16, blocks=(2, 1, 1, 1), classes=10)
+    ext = [(v.binding[0], v.binding[1], 0, mlel.NP_TO_DTYPE[v.dtype], v.shape) for v in g.inputs]
+    ext += [(s, b, 0, mlel.NP_TO_DTYPE[v.dtype], v.shape) for v, s, b in g.outputs]
+    consts = list(g.constants.items())
+    p = lower(mlel, g.spvasm(), ext, consts, mlel.PIPELINE_NO_FUSION)
+    assert p.op_names() == [op.name for op in g.ops]
+    assert p.exec_names() == p.op_names()
+    unfused_mem = mlel.Session(p).memory_requirements()[0]
+    pf = lower(mlel, g.spvasm(), ext, consts)
+    names = pf.exec_names()
+    assert names.count("CONV2D+RESCALE+CLAMP") + names.count("CONV2D+RESCALE") == sum(o.name == "CONV2D" for o in g.ops)
+    assert "RESCALE" not in names and "ADD" not in names and "CLAMP" not in names
+    assert names[-1] == "MATMUL+RESCALE"
+    assert 0 < mlel.Session(pf).memory_requirements()[0] < unfused_mem
+
+
+def test_graph_outputs_are_never_elided(mlel):
+    g = GraphBuilder()
+    a = g.input(np.int8, (1, 4, 4, 8))
+    w = g.constant(np.ones((8, 1, 1, 8), np.int8))
+    b = g.constant(np.zeros((8,), np.int32))
+    acc = g.conv2d(a, w, b, [0] * 4, [1, 1], [1, 1], 0, 0)
+    y = g.rescale(acc, [1 << 30], [35], 0, 0, np.int8)
+    g.output(y)
+    g.output(acc)  # the int32 accumulator is itself an output: the pair must not be fused
+    ext = [(0, 0, 0, mlel.I8, a.shape), (0, 1, 0, mlel.I8, y.shape), (0, 2, 0, mlel.I32, acc.shape)]
+    p = lower(mlel, g.spvasm(), ext, list(g.constants.items()))
+    assert p.exec_names() == ["CONV2D", "RESCALE"]
+
+
+def test_mobilenet_lowers(mlel):
+    g, _ = mobilenet_v2_graph(seed=0, n=1, image=32, width_div=4, classes=10)
+    ext = [(v.binding[0], v.binding[1], 0, mlel.NP_TO_DTYPE[v.dtype], v.shape) for v in g.inputs]
+    ext += [(s, b, 0, mlel.NP_TO_DTYPE[v.dtype], v.shape) for v, s, b in g.outputs]
+    p = lower(mlel, g.spvasm(), ext, list(g.constants.items()))
+    names = p.exec_names()
+    assert sum(n.startswith("DEPTHWISE_CONV2D+RESCALE") for n in names) == 17

@@ -1,0 +1,283 @@
+"""GPU parity, operator by operator: every CUDA kernel behind the C ABI against the CPU oracle on
+seeded inputs, bit-exact.  Each case is a one- or two-operator graph that enters through the
+SPIR-V text front end, is dispatched by a session, and is run twice: with the fusion pass on
+(default) and off (one kernel per TOSA operator, the reference's op list)."""
+import numpy as np
+import pytest
+
+from mlel_b200.graph_builder import GraphBuilder
+from tests.graph_eval import evaluate
+
+pytestmark = pytest.mark.gpu
+
+
+def rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+def check(mlel, g, inputs, modes=(0, 1)):
+    from mlel_b200.runtime import GraphRunner
+    want = evaluate(g, inputs)
+    for flags in modes:
+        runner = GraphRunner(g, flags=flags)
+        got = runner.run(inputs)
+        for k, (a, b) in enumerate(zip(got, want)):
+            assert a.dtype == b.dtype and a.shape == b.shape
+            if not np.array_equal(a, b):
+                bad = np.argwhere(a != b)
+                raise AssertionError(f"flags={flags} output {k}: {len(bad)} of {a.size} differ, first at "
+                                     f"{bad[0].tolist()}: got {a[tuple(bad[0])]} want {b[tuple(bad[0])]}; "
+                                     f"kernels={runner.pipeline.exec_names()}")
+
+
+CONV_CASES = [
+    # n, h, w, ic, oc, k, pad, stride, dil, in_zp, w_zp
+    (1, 8, 8, 3, 5, 3, 1, 1, 1, -3, 0),
+    (2, 9, 7, 4, 8, 3, 1, 2, 1, 7, 0),
+    (1, 12, 12, 6, 7, 3, 2, 1, 2, -128, 5),
+    (1, 10, 11, 5, 3, 1, 0, 1, 1, 127, -7),
+    (2, 15, 15, 3, 9, 7, 3, 2, 1, -3, 0),
+    (1, 14, 14, 16, 32, 3, 1, 1, 1, -20, 0),
+    (2, 7, 7, 64, 64, 1, 0, 1, 1, -20, 0),
+    (1, 56, 56, 64, 64, 3, 1, 1, 1, -3, 0),   # configuration 0
+    (3, 28, 28, 32, 48, 3, 1, 2, 1, 11, 0),
+    (1, 5, 5, 128, 256, 1, 0, 2, 1, -7, 0),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+@pytest.mark.parametrize("with_rescale", [False, True])
+def test_conv2d(mlel, case, with_rescale):
+    n, h, w, ic, oc, k, pad, stride, dil, in_zp, w_zp = case
+    r = rng(hash(case) & 0xFFFF)
+    g = GraphBuilder()
+    x = g.input(np.int8, (n, h, w, ic))
+    wt = g.constant(r.integers(-128, 128, (oc, k, k, ic), dtype=np.int8))
+    b = g.constant(r.integers(-(1 << 14), 1 << 14, (oc,), dtype=np.int32))
+    y = g.conv2d(x, wt, b, [pad] * 4, [stride] * 2, [dil] * 2, in_zp, w_zp)
+    if with_rescale:
+        mult = r.integers(1 << 30, (1 << 31) - 1, (oc,), dtype=np.int64).astype(np.int32)
+        shift = r.integers(36, 46, (oc,), dtype=np.int8)
+        y = g.rescale(y, mult, shift, 0, 5, np.int8, True, True, True)
+        y = g.clamp(y, -20, 100)
+    g.output(y)
+    check(mlel, g, [r.integers(-128, 128, (n, h, w, ic), dtype=np.int8)])
+
+
+def test_conv2d_asymmetric_padding_and_stride(mlel):
+    r = rng(1)
+    g = GraphBuilder()
+    x = g.input(np.int8, (1, 9, 10, 8))
+    wt = g.constant(r.integers(-128, 128, (16, 2, 3, 8), dtype=np.int8))
+    b = g.constant(r.integers(-100, 100, (1,), dtype=np.int32))  # one-element bias broadcasts
+    y = g.conv2d(x, wt, b, [0, 1, 2, 0], [1, 2], [1, 1], 9, 0)
+    y = g.rescale(y, [1 << 30], [38], 0, -1, np.int8, True, False, False)
+    g.output(y)
+    check(mlel, g, [r.integers(-128, 128, (1, 9, 10, 8), dtype=np.int8)])
+
+
+def test_conv2d_int16_int64(mlel):
+    r = rng(2)
+    g = GraphBuilder()
+    x = g.input(np.int16, (1, 5, 5, 4))
+    wt = g.constant(r.integers(-128, 128, (6, 3, 3, 4), dtype=np.int8))
+    b = g.constant(r.integers(-1000, 1000, (6,), dtype=np.int64))
+    g.output(g.conv2d(x, wt, b, [1] * 4, [1, 1], [1, 1], 0, 0, acc_type=4))
+    check(mlel, g, [r.integers(-32768, 32768, (1, 5, 5, 4), dtype=np.int16)])
+
+
+@pytest.mark.parametrize("case", [
+    (1, 8, 8, 4, 1, 3, 1, 1, 1, -3, 0), (2, 9, 9, 5, 2, 3, 1, 2, 1, 4, 2), (1, 16, 16, 32, 1, 3, 1, 1, 1, -128, 0),
+    (1, 7, 6, 3, 3, 2, 0, 1, 2, -128, -1), (2, 14, 14, 96, 1, 3, 1, 2, 1, -128, 0),
+])
+@pytest.mark.parametrize("with_rescale", [False, True])
+def test_depthwise_conv2d(mlel, case, with_rescale):
+    n, h, w, c, m, k, pad, stride, dil, in_zp, w_zp = case
+    r = rng(hash(case) & 0xFFFF)
+    g = GraphBuilder()
+    x = g.input(np.int8, (n, h, w, c))
+    wt = g.constant(r.integers(-128, 128, (k, k, c, m), dtype=np.int8))
+    b = g.constant(r.integers(-(1 << 14), 1 << 14, (c * m,), dtype=np.int32))
+    y = g.depthwise_conv2d(x, wt, b, [pad] * 4, [stride] * 2, [dil] * 2, in_zp, w_zp)
+    if with_rescale:
+        mult = r.integers(1 << 30, (1 << 31) - 1, (c * m,), dtype=np.int64).astype(np.int32)
+        shift = r.integers(34, 40, (c * m,), dtype=np.int8)
+        y = g.clamp(g.rescale(y, mult, shift, 0, -128, np.int8, True, True, True), -128, 64)
+    g.output(y)
+    check(mlel, g, [r.integers(-128, 128, (n, h, w, c), dtype=np.int8)])
+
+
+@pytest.mark.parametrize("shape", [(1, 4, 8, 4), (3, 5, 7, 9), (2, 16, 33, 16), (1, 1, 1, 1), (2, 128, 64, 128),
+                                   (1, 130, 200, 72), (4, 64, 1024, 64)])
+@pytest.mark.parametrize("zps", [(0, 0), (-7, 0), (5, -3)])
+@pytest.mark.parametrize("with_rescale", [False, True])
+def test_matmul(mlel, shape, zps, with_rescale):
+    n, h, c, w = shape
+    r = rng(3)
+    g = GraphBuilder()
+    a = g.input(np.int8, (n, h, c))
+    b = g.input(np.int8, (n, c, w))
+    y = g.matmul(a, b, *zps)
+    if with_rescale:
+        y = g.rescale(y, [int(r.integers(1 << 30, 1 << 31))], [38], 0, 0, np.int8, True, False, False)
+    g.output(y)
+    check(mlel, g, [r.integers(-128, 128, (n, h, c), dtype=np.int8), r.integers(-128, 128, (n, c, w), dtype=np.int8)])
+
+
+def test_matmul_constant_weights_per_channel(mlel):
+    r = rng(4)
+    g = GraphBuilder()
+    a = g.input(np.int8, (1, 6, 96))
+    b = g.constant(r.integers(-128, 128, (1, 96, 40), dtype=np.int8))
+    y = g.matmul(a, b, -20, 0)
+    mult = r.integers(1 << 30, (1 << 31) - 1, (40,), dtype=np.int64).astype(np.int32)
+    y = g.rescale(y, mult, np.full(40, 39, np.int8), 0, 3, np.int8, True, True, True)
+    g.output(y)
+    check(mlel, g, [r.integers(-128, 128, (1, 6, 96), dtype=np.int8)])
+
+
+@pytest.mark.parametrize("shift", [0, 1, 2, 30, 31, 32, 33, 40, 62])
+@pytest.mark.parametrize("double_round", [False, True])
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_rescale_i32_to_i8(mlel, shift, double_round, per_channel):
+    r = rng(shift * 4 + double_round * 2 + per_channel)
+    c = 6
+    data = r.integers(-(1 << 31), 1 << 31, (3, 5, c), dtype=np.int64).astype(np.int32)
+    data[0, 0, :] = [0, 1, -1, 2**31 - 1, -(2**31), 12345]
+    n = c if per_channel else 1
+    mult = r.integers(1 << 30, (1 << 31) - 1, (n,), dtype=np.int64).astype(np.int32)
+    sh = np.full((n,), shift, np.int8)
+    if per_channel and shift >= 2:
+        sh[1::2] -= 1
+    g = GraphBuilder()
+    x = g.input(np.int32, data.shape)
+    g.output(g.rescale(x, mult, sh, 0, 5, np.int8, True, double_round, per_channel))
+    check(mlel, g, [data], modes=(0,))
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype,in_zp,out_zp", [
+    (np.int8, np.int32, -7, 0), (np.int8, np.int8, 3, -128), (np.int16, np.int8, 100, 7),
+    (np.int32, np.int16, 0, -5), (np.int8, np.int16, -128, 32767), (np.int32, np.int32, 11, -11),
+])
+def test_rescale_types(mlel, in_dtype, out_dtype, in_zp, out_zp):
+    r = rng(9)
+    info = np.iinfo(in_dtype)
+    data = r.integers(info.min, int(info.max) + 1, (4, 7), dtype=np.int64).astype(in_dtype)
+    g = GraphBuilder()
+    x = g.input(in_dtype, data.shape)
+    g.output(g.rescale(x, [int(r.integers(1 << 30, (1 << 31) - 1))], [23], in_zp, out_zp, out_dtype, True, True))
+    check(mlel, g, [data], modes=(0,))
+
+
+def test_residual_add_pattern(mlel):
+    r = rng(10)
+    for shape in [(2, 7, 7, 24), (1, 3, 5, 7), (1, 1, 1, 1), (4, 14, 14, 256)]:
+        g = GraphBuilder()
+        a = g.input(np.int8, shape)
+        b = g.input(np.int8, shape)
+        ta = g.rescale(a, [int(r.integers(1 << 30, 1 << 31))], [23], -7, 0, np.int32)
+        tb = g.rescale(b, [int(r.integers(1 << 30, 1 << 31))], [23], 3, 0, np.int32)
+        y = g.rescale(g.add(ta, tb), [int(r.integers(1 << 30, 1 << 31))], [40], 0, -20, np.int8, True, True)
+        g.output(g.clamp(y, -20, 127))
+        check(mlel, g, [r.integers(-128, 128, shape, dtype=np.int8), r.integers(-128, 128, shape, dtype=np.int8)])
+
+
+@pytest.mark.parametrize("case", [
+    ((1, 7, 7, 5), (7, 7), (7, 7), (0, 0, 0, 0), -20, -20), ((2, 8, 9, 3), (3, 3), (2, 2), (1, 1, 1, 1), 0, 0),
+    ((1, 6, 6, 4), (2, 3), (1, 2), (0, 1, 1, 1), 5, -3), ((4, 7, 7, 2048), (7, 7), (7, 7), (0, 0, 0, 0), -20, -20),
+])
+def test_avg_pool2d(mlel, case):
+    shape, k, s, p, in_zp, out_zp = case
+    g = GraphBuilder()
+    x = g.input(np.int8, shape)
+    g.output(g.avg_pool2d(x, k, s, p, in_zp, out_zp))
+    check(mlel, g, [rng(2).integers(-128, 128, shape, dtype=np.int8)], modes=(0,))
+
+
+@pytest.mark.parametrize("case", [
+    ((1, 16, 16, 3), (2, 2), (2, 2), (0, 0, 0, 0)), ((2, 9, 9, 5), (3, 3), (2, 2), (1, 1, 1, 1)),
+    ((1, 7, 5, 2), (3, 2), (1, 1), (1, 0, 0, 1)), ((2, 56, 56, 64), (3, 3), (2, 2), (1, 1, 1, 1)),
+])
+def test_max_pool2d(mlel, case):
+    shape, k, s, p = case
+    g = GraphBuilder()
+    x = g.input(np.int8, shape)
+    g.output(g.max_pool2d(x, k, s, p))
+    check(mlel, g, [rng(6).integers(-128, 128, shape, dtype=np.int8)], modes=(0,))
+
+
+def test_table(mlel):
+    r = rng(7)
+    g = GraphBuilder()
+    x = g.input(np.int8, (3, 50, 16))
+    g.output(g.table(x, r.integers(-128, 128, (256,), dtype=np.int8)))
+    check(mlel, g, [r.integers(-128, 128, (3, 50, 16), dtype=np.int8)], modes=(0,))
+    g = GraphBuilder()
+    x = g.input(np.int16, (3, 50))
+    g.output(g.table(x, r.integers(-32768, 32768, (513,), dtype=np.int16)))
+    data = r.integers(-32768, 32768, (3, 50), dtype=np.int16)
+    data[0, :4] = [-32768, 32767, 0, -1]
+    check(mlel, g, [data], modes=(0,))
+
+
+@pytest.mark.parametrize("shape,perms", [((2, 3, 4), (2, 0, 1)), ((4, 12, 6, 8), (0, 2, 1, 3)), ((5, 7), (1, 0)),
+                                         ((2, 3, 4, 5, 6, 2), (5, 3, 1, 0, 2, 4)), ((2, 384, 12, 64), (0, 2, 1, 3))])
+@pytest.mark.parametrize("dtype", [np.int8, np.int32])
+def test_transpose(mlel, shape, perms, dtype):
+    g = GraphBuilder()
+    x = g.input(dtype, shape)
+    g.output(g.transpose(x, perms))
+    check(mlel, g, [rng(8).integers(-128, 128, shape).astype(dtype)], modes=(0,))
+
+
+def test_data_movement(mlel):
+    r = rng(11)
+    g = GraphBuilder()
+    a = g.input(np.int8, (2, 3, 4, 5))
+    b = g.input(np.int8, (2, 2, 4, 5))
+    c = g.concat([a, b, a], 1)
+    d = g.reshape(c, (2, 8, 20))
+    e = g.slice(d, (0, 1, 3), (2, 5, 9))
+    f = g.pad(e, [0, 1, 2, 0, 1, 1], -9)
+    g.output(f)
+    g.output(g.cast(f, np.int32))
+    check(mlel, g, [r.integers(-128, 128, (2, 3, 4, 5), dtype=np.int8), r.integers(-128, 128, (2, 2, 4, 5), dtype=np.int8)],
+          modes=(0,))
+
+
+def test_elementwise_integer(mlel):
+    r = rng(12)
+    g = GraphBuilder()
+    a = g.input(np.int32, (3, 4, 5))
+    b = g.input(np.int32, (3, 1, 5))   # broadcast along axis 1
+    for name in ("ADD", "SUB", "BITWISE_AND", "BITWISE_OR", "BITWISE_XOR", "MAXIMUM", "MINIMUM", "EQUAL", "GREATER",
+                 "GREATER_EQUAL", "LOGICAL_LEFT_SHIFT", "LOGICAL_RIGHT_SHIFT", "INTDIV"):
+        g.output(g.binary(name, a, b))
+    g.output(g.mul(a, b, 0))
+    g.output(g.mul(a, b, 5))
+    g.output(g.clamp(a, -1000, 5000))
+    g.output(g.negate(a, 3, -4))
+    for name in ("ABS", "BITWISE_NOT", "CLZ"):
+        g.output(g.unary(name, a))
+    g.output(g.reduce("REDUCE_SUM", a, 1))
+    g.output(g.reduce("REDUCE_MAX", a, 2))
+    g.output(g.reduce("REDUCE_MIN", a, 0))
+    da = r.integers(-(1 << 31), 1 << 31, (3, 4, 5), dtype=np.int64).astype(np.int32)
+    db = r.integers(-40, 40, (3, 1, 5), dtype=np.int64).astype(np.int32)
+    db[0, 0, 0] = 0
+    check(mlel, g, [da, db], modes=(0,))
+
+
+def test_elementwise_int8_and_shifts(mlel):
+    r = rng(13)
+    g = GraphBuilder()
+    a = g.input(np.int8, (4, 33))
+    s = g.input(np.int8, (4, 33))
+    g.output(g.add(a, s))
+    g.output(g.arithmetic_right_shift(a, s, True))
+    g.output(g.arithmetic_right_shift(a, s, False))
+    g.output(g.reduce("REDUCE_SUM", a, 1))
+    c = g.binary("GREATER", a, s)
+    g.output(g.select(c, a, s))
+    g.output(g.unary("LOGICAL_NOT", c))
+    check(mlel, g, [r.integers(-128, 128, (4, 33), dtype=np.int8), r.integers(0, 8, (4, 33), dtype=np.int8)], modes=(0,))
