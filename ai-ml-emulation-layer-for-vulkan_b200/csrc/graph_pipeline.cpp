@@ -707,6 +707,161 @@ void GraphPipeline::fuse() {
     }
 }
 
+int32_t GraphPipeline::addDerivedConstant(int32_t dtype, const std::vector<int64_t> &dims, const void *data) {
+    auto t = std::make_unique<TensorDescriptor>();
+    t->dtype = dtype;
+    t->dims = dims;
+    t->strides = packedStrides(dtype, dims);
+    t->cls = TensorClass::Constant;
+    const auto *bytes = static_cast<const uint8_t *>(data);
+    t->hostData.assign(bytes, bytes + t->sizeBytes());
+    return addTensor(std::move(t));
+}
+
+// Decides, per launched node, whether the tcgen05 kernel can take it, and tabulates what that kernel
+// needs beyond the graph's own tensors.  Everything here is derived once from constant data.
+//
+// CONV2D (plain or fused): int8 NHWC input, packed; constant int8 OHWI weights with zero point 0;
+// constant int32 bias; IC and OC multiples of 16; K = KH*KW*IC <= 65536 so that the raw int32 sum of
+// products cannot overflow.  The correction table holds, per border class of an output pixel,
+//     corr[class][oc] = bias[oc] - inputZeroPoint * sum over the taps that are in range of w[oc, tap, :]
+// which turns the tensor core's sum(x * w) over zero-filled taps into the reference's
+// sum over in-range taps of (x - zp) * w + bias   (conv2d.comp:59-112), modulo 2^32.
+//
+// MATMUL (plain or fused) with a constant second input [Nb, C, W] and zero point 0 on it: the input
+// is transposed once to K-major [Nb][W][C]; corr[b][w] = -zeroPoint1 * sum_c B[b, c, w].
+void GraphPipeline::prepareTensorCore() {
+    for (auto &op : exec_) {
+        const bool conv = op.kind == OP_CONV2D || op.kind == OP_FUSED_CONV2D;
+        const bool mm = op.kind == OP_MATMUL || op.kind == OP_FUSED_MATMUL;
+        if (!conv && !mm) {
+            continue;
+        }
+        const TensorDescriptor &in = tensor(op.in[0]);
+        const TensorDescriptor &out = tensor(op.out[0]);
+        const bool fusedOut = op.kind == OP_FUSED_CONV2D || op.kind == OP_FUSED_MATMUL;
+        if (in.dtype != MLEL_I8 || !in.packed() || !out.packed() || out.dtype != (fusedOut ? MLEL_I8 : MLEL_I32)) {
+            continue;
+        }
+        if (conv) {
+            const TensorDescriptor &w = tensor(op.in[1]);
+            const TensorDescriptor &b = tensor(op.in[2]);
+            if (w.cls != TensorClass::Constant || b.cls != TensorClass::Constant || !w.packed() || !b.packed() ||
+                w.dtype != MLEL_I8 || b.dtype != MLEL_I32 || op.i[9] != 0) {
+                continue;
+            }
+            const int64_t OC = w.dims[0], KH = w.dims[1], KW = w.dims[2], IC = w.dims[3];
+            const int64_t H = in.dims[1], W = in.dims[2], OH = out.dims[1], OW = out.dims[2];
+            if (in.dims[3] != IC || out.dims[3] != OC || IC % 16 != 0 || OC % 16 != 0 || KH * KW * IC > 65536 ||
+                (b.dims[0] != OC && b.dims[0] != 1) || out.numel() >= (int64_t(1) << 31) ||
+                in.numel() >= (int64_t(1) << 31)) {
+                continue;
+            }
+            const int padTop = op.i[0], padLeft = op.i[2], sy = op.i[4], sx = op.i[5], dy = op.i[6], dx = op.i[7];
+            if (sy <= 0 || sx <= 0 || dy <= 0 || dx <= 0) {
+                continue;
+            }
+            // Border classes: the set of in-range taps along each axis.
+            const auto classify = [](int64_t outDim, int64_t inDim, int64_t k, int stride, int pad, int dil,
+                                     std::vector<uint8_t> &cls, std::vector<std::vector<bool>> &masks) {
+                cls.resize(size_t(outDim));
+                std::map<std::vector<bool>, int> ids;
+                for (int64_t o = 0; o < outDim; ++o) {
+                    std::vector<bool> mask(size_t(k), false);
+                    for (int64_t t = 0; t < k; ++t) {
+                        const int64_t i = o * stride - pad + t * dil;
+                        mask[size_t(t)] = i >= 0 && i < inDim;
+                    }
+                    auto it = ids.find(mask);
+                    if (it == ids.end()) {
+                        it = ids.emplace(mask, int(masks.size())).first;
+                        masks.push_back(mask);
+                    }
+                    if (it->second > 255) {
+                        return false;
+                    }
+                    cls[size_t(o)] = uint8_t(it->second);
+                }
+                return true;
+            };
+            std::vector<uint8_t> rowCls, colCls;
+            std::vector<std::vector<bool>> rowMasks, colMasks;
+            if (!classify(OH, H, KH, sy, padTop, dy, rowCls, rowMasks) ||
+                !classify(OW, W, KW, sx, padLeft, dx, colCls, colMasks)) {
+                continue;
+            }
+            if (rowMasks.size() * colMasks.size() * size_t(OC) > (size_t(1) << 22)) {
+                continue;
+            }
+            const auto *wd = reinterpret_cast<const int8_t *>(w.hostData.data());
+            const auto *bd = reinterpret_cast<const int32_t *>(b.hostData.data());
+            std::vector<int64_t> wsum(size_t(KH * KW * OC), 0); // [ky][kx][oc]
+            for (int64_t oc = 0; oc < OC; ++oc) {
+                for (int64_t t = 0; t < KH * KW; ++t) {
+                    int64_t acc = 0;
+                    const int8_t *row = wd + (oc * KH * KW + t) * IC;
+                    for (int64_t ic = 0; ic < IC; ++ic) {
+                        acc += row[ic];
+                    }
+                    wsum[size_t(t * OC + oc)] = acc;
+                }
+            }
+            const int64_t zx = op.i[8];
+            std::vector<int32_t> corr(rowMasks.size() * colMasks.size() * size_t(OC));
+            for (size_t rc = 0; rc < rowMasks.size(); ++rc) {
+                for (size_t cc = 0; cc < colMasks.size(); ++cc) {
+                    for (int64_t oc = 0; oc < OC; ++oc) {
+                        int64_t sum = 0;
+                        for (int64_t ky = 0; ky < KH; ++ky) {
+                            for (int64_t kx = 0; kx < KW; ++kx) {
+                                if (rowMasks[rc][size_t(ky)] && colMasks[cc][size_t(kx)]) {
+                                    sum += wsum[size_t((ky * KW + kx) * OC + oc)];
+                                }
+                            }
+                        }
+                        const int64_t v = int64_t(bd[b.dims[0] == 1 ? 0 : oc]) - zx * sum;
+                        corr[(rc * colMasks.size() + cc) * size_t(OC) + size_t(oc)] = int32_t(uint32_t(uint64_t(v)));
+                    }
+                }
+            }
+            op.aux[0] = addDerivedConstant(MLEL_I32, {int64_t(corr.size())}, corr.data());
+            op.aux[1] = addDerivedConstant(MLEL_U8, {OH}, rowCls.data());
+            op.aux[2] = addDerivedConstant(MLEL_U8, {OW}, colCls.data());
+            op.auxi[0] = int32_t(colMasks.size());
+            op.auxi[1] = int32_t(rowMasks.size() * colMasks.size());
+            op.tc = 1;
+        } else {
+            const TensorDescriptor &b = tensor(op.in[1]);
+            if (b.cls != TensorClass::Constant || !b.packed() || b.dtype != MLEL_I8 || op.i[1] != 0) {
+                continue;
+            }
+            const int64_t Nb = b.dims[0], C = b.dims[1], W = b.dims[2];
+            if (in.dims[0] != Nb || in.dims[2] != C || C % 16 != 0 || C > 65536 ||
+                out.numel() >= (int64_t(1) << 31) || in.numel() >= (int64_t(1) << 31)) {
+                continue;
+            }
+            const auto *bdata = reinterpret_cast<const int8_t *>(b.hostData.data());
+            std::vector<int8_t> bt(size_t(Nb * W * C));
+            std::vector<int32_t> corr(size_t(Nb * W));
+            const int64_t za = op.i[0];
+            for (int64_t n = 0; n < Nb; ++n) {
+                for (int64_t w = 0; w < W; ++w) {
+                    int64_t sum = 0;
+                    for (int64_t c = 0; c < C; ++c) {
+                        const int8_t v = bdata[(n * C + c) * W + w];
+                        bt[size_t((n * W + w) * C + c)] = v;
+                        sum += v;
+                    }
+                    corr[size_t(n * W + w)] = int32_t(uint32_t(uint64_t(-za * sum)));
+                }
+            }
+            op.aux[0] = addDerivedConstant(MLEL_I32, {Nb * W}, corr.data());
+            op.aux[3] = addDerivedConstant(MLEL_I8, {Nb, W, C}, bt.data());
+            op.tc = 1;
+        }
+    }
+}
+
 const std::vector<OpDesc> &GraphPipeline::getExecList() {
     finalize();
     return exec_;
@@ -717,6 +872,9 @@ void GraphPipeline::finalize() {
         return;
     }
     fuse();
+    if (!(flags_ & MLEL_PIPELINE_NO_TENSOR_CORE)) {
+        prepareTensorCore();
+    }
     // Lay constants out in one slab, each on a 256-byte boundary.
     uint64_t offset = 0;
     for (auto &t : tensors_) {

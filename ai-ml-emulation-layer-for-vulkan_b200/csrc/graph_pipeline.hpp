@@ -124,6 +124,8 @@ class GraphPipeline {
     OpDesc &pushOp(OpKind kind, const std::string &name, std::vector<int32_t> in, std::vector<int32_t> out);
     void requireMutable() const;
     void fuse();
+    void prepareTensorCore();
+    int32_t addDerivedConstant(int32_t dtype, const std::vector<int64_t> &dims, const void *data);
 
     uint32_t flags_;
     bool finalized_{false};

@@ -1,0 +1,469 @@
+// int8 x int8 -> int32 contraction on the 5th-generation tensor cores (tcgen05.mma kind::i8, TMEM
+// accumulator) with the TOSA epilogue fused in.  One kernel serves CONV2D (implicit GEMM), 1x1
+// CONV2D and MATMUL:
+//
+//   D[m, n] = sum_k A[m, k] * B[n, k]         m: output pixel (or matmul row), n: output channel
+//
+//   A operand  - TMA tile loads when A is a plain row-major matrix (1x1 stride-1 convolution, MATMUL);
+//              - otherwise gathered by four producer warps with 16-byte cp.async (im2col on the fly:
+//                any kernel size, stride, dilation and padding; out-of-range taps are zero-filled)
+//   B operand  - TMA tile loads of the K-major weight matrix [N][K] (OHWI weights are exactly that), or
+//                of an N-major [K][N] matrix (MATMUL's second input) with an MN-major descriptor
+//   pipeline   - 128-byte K blocks, SWIZZLE_128B shared-memory tiles, NSTAGE-deep mbarrier ring;
+//                warp 4 issues TMA, warp 5 issues tcgen05.mma, warps 0-3 gather A and run the epilogue
+//   epilogue   - tcgen05.ld of the int32 accumulator, zero-point/bias correction, then either a raw
+//                int32 store or RESCALE (+CLAMP, + residual RESCALE/ADD/RESCALE) to int8
+//
+// Exactness.  The tensor core sums raw products A*B in int32 (no overflow is possible for K <= 65536).
+// The reference computes sum over in-range taps of (x - zx) * w  (conv2d.comp:59-96).  With zero-filled
+// out-of-range taps this equals  sum(x * w) - zx * sum over in-range taps of w, and the second term only
+// depends on the output channel and on which taps are in range, i.e. on a small "border class" of the
+// output pixel.  The host tabulates corr[class][n] = bias[n] - zx * sum_valid_taps(w[n]) once per
+// pipeline; the epilogue adds it (mod 2^32, like the reference's int32 arithmetic).
+//
+// Every wait on an mbarrier is bounded: after about two seconds a waiter records an error code in
+// g_tcgen05Error and leaves its loop, all roles fall through to the common exit, and TMEM is freed.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+
+#include "device_common.cuh"
+#include "gemm_i8_tcgen05.hpp"
+
+namespace mlel {
+
+__device__ int g_tcgen05Error = 0;
+
+namespace {
+
+constexpr int BM = 128;          // rows per CTA tile (UMMA M)
+constexpr int BK = 128;          // bytes (= int8 elements) of K per pipeline stage
+constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit operands
+constexpr int kNumThreads = 192; // warps 0-3: A gather + epilogue, warp 4: TMA, warp 5: MMA + TMEM
+constexpr long long kWaitLimitCycles = 4000000000ll;
+
+__device__ __forceinline__ uint32_t smemAddr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbarInit(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbarArriveExpectTx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smemAddr(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and records `code`) when the barrier did not complete in time.
+__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int code) {
+    if (mbarTryWait(bar, parity)) {
+        return true;
+    }
+    const long long start = clock64();
+    while (!mbarTryWait(bar, parity)) {
+        if (clock64() - start > kWaitLimitCycles) {
+            atomicCAS(&g_tcgen05Error, 0, code);
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tmaLoad2d(const CUtensorMap *map, void *dst, uint64_t *bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(bar)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tmaLoad3d(const CUtensorMap *map, void *dst, uint64_t *bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor for a SWIZZLE_128B tile whose 8-row groups are 1024 bytes apart.
+// bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+// [46,48) descriptor version (1 on sm_100), [61,64) layout type (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t smemDesc(uint32_t addr, uint32_t lboBytes, uint32_t sboBytes) {
+    uint64_t d = 0;
+    d |= uint64_t((addr >> 4) & 0x3FFF);
+    d |= uint64_t((lboBytes >> 4) & 0x3FFF) << 16;
+    d |= uint64_t((sboBytes >> 4) & 0x3FFF) << 32;
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(2) << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::i8: D = s32 (c_format 2), A and B signed 8-bit (format 1),
+// bit 15/16 = A/B major (0 = K-major, 1 = MN-major), [17,23) N >> 3, [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t instrDesc(int n, bool bMnMajor) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(bMnMajor) << 16) | (uint32_t(n >> 3) << 17) |
+           (uint32_t(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(accumulate), "r"(0u)
+                 : "memory");
+}
+__device__ __forceinline__ void ummaCommit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct __align__(8) PipeBarriers {
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t accumReady;
+    uint32_t tmemBase;
+    uint32_t pad;
+};
+
+__device__ __forceinline__ int32_t fusedStage(const DevRescale &r, int64_t v, uint32_t c) {
+    const uint32_t ci = r.perChannel ? c : 0u;
+    return rescaleValue(v, r.inZp, __ldg(r.mult + ci), int32_t(__ldg(r.shift + ci)), r.doubleRound != 0, r.outZp, r.lo,
+                        r.hi);
+}
+
+// A_TMA: A comes through tmapA; otherwise it is gathered from the NHWC input described by p.
+// B_MN : B is an N-contiguous [K][N] matrix (MN-major operand), otherwise a K-contiguous [N][K] matrix.
+template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
+__global__ void __launch_bounds__(kNumThreads)
+gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const GemmI8Params p) {
+    extern __shared__ uint8_t rawSmem[];
+    // SWIZZLE_128B tiles must start on 1024-byte boundaries.
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
+    constexpr int kTileA = BM * BK;
+    constexpr int kTileB = BN * BK;
+    uint8_t *tilesA = smem;
+    uint8_t *tilesB = smem + NSTAGE * kTileA;
+    PipeBarriers *bars = reinterpret_cast<PipeBarriers *>(smem + NSTAGE * (kTileA + kTileB));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM;
+    const int n0 = blockIdx.y * BN;
+    const int batch = blockIdx.z;
+    const int numKb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbarInit(&bars->full[s], A_TMA ? 1u : 1u + 128u);
+            mbarInit(&bars->empty[s], 1u);
+        }
+        mbarInit(&bars->accumReady, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&bars->tmemBase)),
+                     "r"(uint32_t(BN))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmemBase = bars->tmemBase;
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (int kb = 0; kb < numKb; ++kb) {
+                const int s = kb % NSTAGE;
+                const uint32_t phase = uint32_t(kb / NSTAGE) & 1u;
+                if (!mbarWait(&bars->empty[s], phase ^ 1u, 1)) {
+                    break;
+                }
+                mbarArriveExpectTx(&bars->full[s], uint32_t((A_TMA ? kTileA : 0) + kTileB));
+                if (A_TMA) {
+                    tmaLoad3d(&tmapA, tilesA + s * kTileA, &bars->full[s], kb * BK, m0, batch);
+                }
+                if (B_MN) {
+                    tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], n0, kb * BK, batch);
+                } else {
+                    tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], kb * BK, n0, p.batchedB ? batch : 0);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instrDesc(BN, B_MN);
+            bool ok = true;
+            for (int kb = 0; kb < numKb && ok; ++kb) {
+                const int s = kb % NSTAGE;
+                const uint32_t phase = uint32_t(kb / NSTAGE) & 1u;
+                ok = mbarWait(&bars->full[s], phase, 2);
+                if (!ok) {
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t aAddr = smemAddr(tilesA + s * kTileA);
+                const uint32_t bAddr = smemAddr(tilesB + s * kTileB);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // K-major: step 32 bytes inside the 128-byte swizzle row; MN-major: step 32 K-rows of 128 bytes
+                    const uint64_t da = smemDesc(aAddr + k * UMMA_K, 16, 1024);
+                    const uint64_t db = B_MN ? smemDesc(bAddr + k * UMMA_K * 128, BK * 128, 1024)
+                                             : smemDesc(bAddr + k * UMMA_K, 16, 1024);
+                    umma(tmemBase, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                }
+                ummaCommit(&bars->empty[s]); // frees the stage once these MMAs have read it
+            }
+            ummaCommit(&bars->accumReady);
+        }
+    } else {
+        // ---------------- warps 0-3: A gather (when not TMA), then epilogue ----------------
+        const int row = warp * 32 + lane; // row of the tile == TMEM lane
+        const int64_t m = int64_t(m0) + row;
+        if (!A_TMA) {
+            const bool rowValid = m < p.M;
+            int n = 0, oy = 0, ox = 0;
+            if (rowValid) {
+                n = int(m / (int64_t(p.OH) * p.OW));
+                const int rem = int(m - int64_t(n) * p.OH * p.OW);
+                oy = rem / p.OW;
+                ox = rem - oy * p.OW;
+            }
+            const int iy0 = oy * p.strideY - p.padTop;
+            const int ix0 = ox * p.strideX - p.padLeft;
+            const int8_t *base = p.in + int64_t(n) * p.H * p.W * p.IC;
+            int c = 0, kx = 0, ky = 0; // position of the next 16-byte chunk inside K = (ky, kx, c)
+            const uint32_t swz = uint32_t(row & 7);
+            for (int kb = 0; kb < numKb; ++kb) {
+                const int s = kb % NSTAGE;
+                const uint32_t phase = uint32_t(kb / NSTAGE) & 1u;
+                if (!mbarWait(&bars->empty[s], phase ^ 1u, 3)) {
+                    break;
+                }
+                const uint32_t dstRow = smemAddr(tilesA + s * kTileA) + uint32_t(row) * 128u;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int y = iy0 + ky * p.dilY;
+                    const int x = ix0 + kx * p.dilX;
+                    const bool valid = rowValid && ky < p.KH && y >= 0 && y < p.H && x >= 0 && x < p.W;
+                    const int8_t *src = valid ? base + (int64_t(y) * p.W + x) * p.IC + c : p.in;
+                    const uint32_t dst = dstRow + ((uint32_t(j) ^ swz) << 4);
+                    const uint32_t bytes = valid ? 16u : 0u; // 0 source bytes => the 16 bytes are zero-filled
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+                                 : "memory");
+                    c += 16;
+                    if (c >= p.IC) {
+                        c = 0;
+                        if (++kx == p.KW) {
+                            kx = 0;
+                            ++ky;
+                        }
+                    }
+                }
+                // The stage's barrier completes when these copies have landed and every producer arrived.
+                asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s])) : "memory");
+                mbarArrive(&bars->full[s]);
+            }
+        }
+
+        // ---------------- epilogue ----------------
+        if (mbarWait(&bars->accumReady, 0u, 4)) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool rowValid = m < p.M;
+            // zero-point / bias correction row of this pixel's border class
+            const int32_t *corr = p.corr;
+            if (corr != nullptr) {
+                int cls = 0;
+                if (p.rowClass != nullptr && rowValid) {
+                    const int rem = int(m % (int64_t(p.OH) * p.OW));
+                    cls = int(p.rowClass[rem / p.OW]) * p.numColClasses + int(p.colClass[rem % p.OW]);
+                }
+                corr += (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0) + int64_t(cls) * p.N;
+            }
+            const int64_t outRow = (int64_t(batch) * p.M + m) * p.ldOut;
+#pragma unroll 1
+            for (int cb = 0; cb < BN / 32; ++cb) {
+                uint32_t acc[32];
+                tmemLoad32(tmemBase + (uint32_t(warp * 32) << 16) + uint32_t(cb * 32), acc);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col0 = n0 + cb * 32;
+                if (!rowValid || col0 >= p.N) {
+                    continue;
+                }
+                const int ncols = min(32, p.N - col0);
+                if (p.out32 != nullptr) {
+                    int32_t *dst = p.out32 + outRow + col0;
+                    for (int j = 0; j < ncols; ++j) {
+                        dst[j] = int32_t(acc[j] + (corr ? uint32_t(__ldg(corr + col0 + j)) : 0u));
+                    }
+                    continue;
+                }
+                alignas(16) int8_t packed[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const uint32_t col = uint32_t(col0 + j);
+                    int32_t y = 0;
+                    if (j < ncols) {
+                        const int32_t v = int32_t(acc[j] + (corr ? uint32_t(__ldg(corr + col)) : 0u));
+                        y = fusedStage(p.epi.main, int64_t(v), col);
+                        if (p.epi.hasResidual) {
+                            const int32_t ta = fusedStage(p.epi.a, int64_t(y), col);
+                            const int32_t tb = fusedStage(p.epi.b, int64_t(p.epi.shortcut[outRow + col]), col);
+                            y = fusedStage(p.epi.out, int64_t(int32_t(uint32_t(ta) + uint32_t(tb))), col);
+                        }
+                    }
+                    packed[j] = int8_t(y);
+                }
+                int8_t *dst = p.out8 + outRow + col0;
+                if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                    reinterpret_cast<int4 *>(dst)[0] = reinterpret_cast<const int4 *>(packed)[0];
+                    reinterpret_cast<int4 *>(dst)[1] = reinterpret_cast<const int4 *>(packed)[1];
+                } else {
+                    for (int j = 0; j < ncols; ++j) {
+                        dst[j] = packed[j];
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(uint32_t(BN)) : "memory");
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        }
+    });
+    return fn;
+}
+
+// 3-D uint8 tensor map {d0 (contiguous), d1, d2} with a {b0, b1, 1} box and 128-byte swizzle.
+bool makeMap(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1,
+             uint64_t stride2, uint32_t b0, uint32_t b1) {
+    EncodeTiledFn fn = encodeTiled();
+    if (fn == nullptr) {
+        setLastError("cuTensorMapEncodeTiled is not available from the driver");
+        return false;
+    }
+    const cuuint64_t dims[3] = {d0, d1, d2};
+    const cuuint64_t strides[2] = {stride1, stride2}; // bytes, for dims 1 and 2
+    const cuuint32_t box[3] = {b0, b1, 1};
+    const cuuint32_t elemStrides[3] = {1, 1, 1};
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box,
+                           elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        setLastError("cuTensorMapEncodeTiled failed with code " + std::to_string(int(rc)));
+        return false;
+    }
+    return true;
+}
+
+template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
+int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, int batches, cudaStream_t s) {
+    constexpr size_t smemBytes = size_t(NSTAGE) * (BM * BK + BN * BK) + sizeof(PipeBarriers) + 1024;
+    auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_TMA, B_MN>;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smemBytes)) != cudaSuccess) {
+            setLastError("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+            return MLEL_ERROR_DEVICE;
+        }
+        configured = true;
+    }
+    const dim3 grid(unsigned((p.M + BM - 1) / BM), unsigned((p.N + BN - 1) / BN), unsigned(batches));
+    kernel<<<grid, kNumThreads, smemBytes, s>>>(mapA, mapB, p);
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        setLastError(std::string("tcgen05 int8 GEMM launch: ") + cudaGetErrorString(err));
+        return MLEL_ERROR_DEVICE;
+    }
+    return MLEL_SUCCESS;
+}
+
+} // namespace
+
+int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
+    GemmI8Params p = q.params;
+    CUtensorMap mapA{}, mapB{};
+    const bool aTma = q.aMatrix != nullptr;
+    if (aTma) {
+        // A: [batches][M][K], K contiguous
+        if (!makeMap(&mapA, q.aMatrix, uint64_t(p.K), uint64_t(p.M), uint64_t(q.batches), uint64_t(q.aRowBytes),
+                     uint64_t(q.aBatchBytes), BK, BM)) {
+            return MLEL_ERROR_DEVICE;
+        }
+    }
+    const int bn = (!q.bMnMajor && p.N <= 64) ? 64 : 128;
+    if (q.bMnMajor) {
+        // B: [batches][K][N], N contiguous
+        if (!makeMap(&mapB, q.bMatrix, uint64_t(p.N), uint64_t(p.K), uint64_t(q.batches), uint64_t(q.bRowBytes),
+                     uint64_t(q.bBatchBytes), 128, BK)) {
+            return MLEL_ERROR_DEVICE;
+        }
+    } else {
+        // B: [batchesB][N][K], K contiguous
+        if (!makeMap(&mapB, q.bMatrix, uint64_t(p.K), uint64_t(p.N), uint64_t(p.batchedB ? q.batches : 1),
+                     uint64_t(q.bRowBytes), uint64_t(q.bBatchBytes ? q.bBatchBytes : q.bRowBytes * uint64_t(p.N)),
+                     BK, uint32_t(bn))) {
+            return MLEL_ERROR_DEVICE;
+        }
+    }
+    if (q.bMnMajor) {
+        return aTma ? launchVariant<128, 3, true, true>(mapA, mapB, p, q.batches, s)
+                    : launchVariant<128, 3, false, true>(mapA, mapB, p, q.batches, s);
+    }
+    if (bn == 64) {
+        return aTma ? launchVariant<64, 4, true, false>(mapA, mapB, p, q.batches, s)
+                    : launchVariant<64, 4, false, false>(mapA, mapB, p, q.batches, s);
+    }
+    return aTma ? launchVariant<128, 3, true, false>(mapA, mapB, p, q.batches, s)
+                : launchVariant<128, 3, false, false>(mapA, mapB, p, q.batches, s);
+}
+
+int tcgen05ErrorFlag() {
+    int v = 0;
+    cudaMemcpyFromSymbol(&v, g_tcgen05Error, sizeof(int));
+    return v;
+}
+
+} // namespace mlel

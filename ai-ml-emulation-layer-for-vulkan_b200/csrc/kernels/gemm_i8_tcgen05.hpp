@@ -1,0 +1,51 @@
+// Interface of the tcgen05 int8 contraction kernel (gemm_i8_tcgen05.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "kernels.hpp"
+
+namespace mlel {
+
+// Device-side parameters (passed by value to the kernel).
+struct GemmI8Params {
+    int32_t M, N, K;     // per batch: rows, columns (output channels), contraction length in bytes
+    int32_t ldOut;       // elements between consecutive output rows
+    int32_t batchedB;    // K-major B only: B has one matrix per batch (else one shared matrix)
+    // implicit-GEMM geometry (used only when A is gathered): NHWC input, window, output grid
+    const int8_t *in;
+    int32_t H, W, IC, OH, OW, KH, KW;
+    int32_t strideY, strideX, padTop, padLeft, dilY, dilX;
+    // correction term added to the raw accumulator: corr[(batch,) class, n]
+    const int32_t *corr;
+    const uint8_t *rowClass; // [OH] border class of an output row, or null (single class)
+    const uint8_t *colClass; // [OW]
+    int32_t numColClasses, numClasses, batchedCorr;
+    // outputs: exactly one of out32 / out8 is set
+    int32_t *out32;
+    int8_t *out8;
+    DevEpilogue epi;
+};
+
+struct GemmI8Problem {
+    GemmI8Params params;
+    int32_t batches;
+    // A as a matrix [batches][M][K] (K contiguous) for TMA; null => gather from params.in
+    const void *aMatrix;
+    uint64_t aRowBytes, aBatchBytes;
+    // B: K-major [batchesB][N][K] or (bMnMajor) N-major [batches][K][N]
+    const void *bMatrix;
+    uint64_t bRowBytes, bBatchBytes;
+    bool bMnMajor;
+};
+
+// Enqueues the kernel.  Preconditions (checked by the caller): K % 16 == 0, K <= 65536, operands
+// 16-byte aligned with row pitches that are multiples of 16 bytes.
+int gemmI8Launch(const GemmI8Problem &problem, cudaStream_t stream);
+
+// Value of the device-side error word written by a bounded wait that ran out (0 = none).
+int tcgen05ErrorFlag();
+
+} // namespace mlel

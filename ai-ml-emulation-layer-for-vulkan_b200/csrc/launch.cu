@@ -7,6 +7,7 @@
 #include <string>
 
 #include "kernels/device_common.cuh"
+#include "kernels/gemm_i8_tcgen05.hpp"
 #include "kernels/kernels.hpp"
 #include "ops.hpp"
 
@@ -87,6 +88,78 @@ int64_t padBits(const OpDesc &op, int32_t dtype) {
     return wrapTo(dtype, int64_t(op.d[0]));
 }
 
+// CONV2D / fused CONV2D on the tensor cores (the node was prepared by GraphPipeline::prepareTensorCore).
+int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
+    const TView &in = T[op.in[0]], &w = T[op.in[1]], &out = T[op.out[0]];
+    GemmI8Problem q{};
+    GemmI8Params &p = q.params;
+    const int64_t OH = out.dims[1], OW = out.dims[2];
+    p.M = int32_t(int64_t(out.dims[0]) * OH * OW);
+    p.N = int32_t(out.dims[3]);
+    p.K = int32_t(w.dims[1] * w.dims[2] * w.dims[3]);
+    p.ldOut = p.N;
+    p.in = reinterpret_cast<const int8_t *>(in.ptr);
+    p.H = int32_t(in.dims[1]), p.W = int32_t(in.dims[2]), p.IC = int32_t(in.dims[3]);
+    p.OH = int32_t(OH), p.OW = int32_t(OW), p.KH = int32_t(w.dims[1]), p.KW = int32_t(w.dims[2]);
+    p.padTop = op.i[0], p.padLeft = op.i[2], p.strideY = op.i[4], p.strideX = op.i[5], p.dilY = op.i[6], p.dilX = op.i[7];
+    p.corr = reinterpret_cast<const int32_t *>(T[op.aux[0]].ptr);
+    p.rowClass = reinterpret_cast<const uint8_t *>(T[op.aux[1]].ptr);
+    p.colClass = reinterpret_cast<const uint8_t *>(T[op.aux[2]].ptr);
+    p.numColClasses = op.auxi[0];
+    p.numClasses = op.auxi[1];
+    if (op.kind == OP_FUSED_CONV2D) {
+        p.out8 = reinterpret_cast<int8_t *>(out.ptr);
+        p.epi = devEpilogue(op.epi, T);
+    } else {
+        p.out32 = reinterpret_cast<int32_t *>(out.ptr);
+    }
+    q.batches = 1;
+    // A 1x1, stride-1, unpadded convolution reads the input as a plain [pixels][IC] matrix.
+    const bool plain = p.KH == 1 && p.KW == 1 && p.strideY == 1 && p.strideX == 1 && op.i[0] == 0 && op.i[1] == 0 &&
+                       op.i[2] == 0 && op.i[3] == 0 && (reinterpret_cast<uintptr_t>(in.ptr) & 15u) == 0;
+    if (plain) {
+        q.aMatrix = in.ptr;
+        q.aRowBytes = uint64_t(p.IC);
+        q.aBatchBytes = uint64_t(p.IC) * uint64_t(p.M);
+    }
+    q.bMatrix = w.ptr;
+    q.bRowBytes = uint64_t(p.K);
+    q.bBatchBytes = 0;
+    q.bMnMajor = false;
+    return gemmI8Launch(q, s);
+}
+
+// MATMUL / fused MATMUL with a constant, pre-transposed second input.
+int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
+    const TView &a = T[op.in[0]], &bt = T[op.aux[3]], &out = T[op.out[0]];
+    GemmI8Problem q{};
+    GemmI8Params &p = q.params;
+    p.M = int32_t(a.dims[1]);
+    p.N = int32_t(bt.dims[1]);
+    p.K = int32_t(a.dims[2]);
+    p.ldOut = p.N;
+    p.batchedB = 1;
+    p.corr = reinterpret_cast<const int32_t *>(T[op.aux[0]].ptr);
+    p.numClasses = 1;
+    p.numColClasses = 1;
+    p.batchedCorr = 1;
+    if (op.kind == OP_FUSED_MATMUL) {
+        p.out8 = reinterpret_cast<int8_t *>(out.ptr);
+        p.epi = devEpilogue(op.epi, T);
+    } else {
+        p.out32 = reinterpret_cast<int32_t *>(out.ptr);
+    }
+    q.batches = int32_t(a.dims[0]);
+    q.aMatrix = a.ptr;
+    q.aRowBytes = uint64_t(p.K);
+    q.aBatchBytes = uint64_t(p.K) * uint64_t(p.M);
+    q.bMatrix = bt.ptr;
+    q.bRowBytes = uint64_t(p.K);
+    q.bBatchBytes = uint64_t(p.K) * uint64_t(p.N);
+    q.bMnMajor = false;
+    return gemmI8Launch(q, s);
+}
+
 } // namespace
 
 void setLastError(const std::string &msg) { g_lastError = msg; }
@@ -95,6 +168,16 @@ const std::string &lastError() { return g_lastError; }
 int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
     const auto in = [&](size_t k) -> const TView & { return T[op.in[k]]; };
     const TView &out = T[op.out[0]];
+    if (op.tc) {
+        // Addresses are only known here: pointers that are not 16-byte aligned go to the generic kernels.
+        const bool aligned = ((reinterpret_cast<uintptr_t>(in(0).ptr) | reinterpret_cast<uintptr_t>(out.ptr)) & 15u) == 0;
+        if (aligned && (op.kind == OP_CONV2D || op.kind == OP_FUSED_CONV2D)) {
+            return launchConvTensorCore(op, T, s);
+        }
+        if (aligned && (op.kind == OP_MATMUL || op.kind == OP_FUSED_MATMUL)) {
+            return launchMatmulTensorCore(op, T, s);
+        }
+    }
     switch (op.kind) {
     case OP_CONV2D:
         return genericConv2d(in(0), in(1), in(2), out, convAttr(op), s);

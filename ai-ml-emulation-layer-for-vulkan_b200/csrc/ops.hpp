@@ -140,6 +140,14 @@ struct OpDesc {
     std::vector<int32_t> out;
     FusedEpilogue epi;              // fused kinds only
     std::vector<int32_t> fusedOps;  // indices of the logical ops an exec node stands for
+    // Tensor-core path (set by GraphPipeline::prepareTensorCore when the node qualifies):
+    //   CONV2D kinds: aux[0] correction table int32 [classes][OC], aux[1] row classes u8 [OH],
+    //                 aux[2] column classes u8 [OW]; auxi[0] = number of column classes, auxi[1] = classes
+    //   MATMUL kinds with a constant second input: aux[0] correction int32 [batches][W],
+    //                 aux[3] the second input transposed to [batches][W][C]
+    int32_t tc{0};
+    int32_t aux[4]{-1, -1, -1, -1};
+    int32_t auxi[4]{0, 0, 0, 0};
 };
 
 // Launches one operator.  `tensors` is indexed by tensor id (op.in / op.out / op.epi hold ids).

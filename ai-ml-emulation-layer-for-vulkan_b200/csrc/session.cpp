@@ -128,6 +128,7 @@ int Session::resolve() {
             used.insert(f->shiftTensor);
         }
         used.insert(op.epi.shortcutTensor);
+        used.insert(std::begin(op.aux), std::end(op.aux));
     }
     used.erase(-1);
     for (int32_t t = 0; t < n; ++t) {

@@ -25,6 +25,11 @@ def _rng(seed: int) -> np.random.Generator:
     return np.random.Generator(np.random.PCG64(seed))
 
 
+def _data_rng(seed: int) -> np.random.Generator:
+    """Input data come from their own stream so that the weights do not depend on the batch size."""
+    return np.random.Generator(np.random.PCG64(seed + 7919))
+
+
 def _calibrated_shift(k_elems: int) -> int:
     """A shift that keeps a random int8 x int8 contraction of length k inside the int8 range.
 
@@ -127,7 +132,7 @@ def resnet50_graph(seed: int = 0, n: int = 64, image: int = 224, width: int = 64
     g = GraphBuilder("resnet50")
     net = _Net(g, rng)
     x = g.input(np.int8, (n, image, image, 3))
-    data = rng.integers(-128, 128, (n, image, image, 3), dtype=np.int8)
+    data = _data_rng(seed).integers(-128, 128, (n, image, image, 3), dtype=np.int8)
     zp = -20  # zero point of every post-ReLU activation; ReLU = CLAMP(zp, 127)
     relu = (zp, 127)
     y = net.conv(x, -3, width, 7, 2, 3, zp, relu)
@@ -169,7 +174,7 @@ def mobilenet_v2_graph(seed: int = 0, n: int = 32, image: int = 224, width_div: 
     g = GraphBuilder("mobilenet_v2")
     net = _Net(g, rng, calibrated=False)
     x = g.input(np.int8, (n, image, image, 3))
-    data = rng.integers(-128, 128, (n, image, image, 3), dtype=np.int8)
+    data = _data_rng(seed).integers(-128, 128, (n, image, image, 3), dtype=np.int8)
     zp, q6 = -128, 64  # activation zero point and the quantised value of 6.0
     relu6 = (zp, q6)
 

@@ -81,7 +81,8 @@ int mlel_elem_size(int32_t dtype);
 /* ---- pipeline construction: replaces vkCreateDataGraphPipelinesARM, graph/graph_layer.cpp:815-964 ---- */
 
 /* flags for mlel_pipeline_create */
-#define MLEL_PIPELINE_NO_FUSION 1u /* run one kernel per TOSA op, exactly the reference's op list */
+#define MLEL_PIPELINE_NO_FUSION 1u      /* run one kernel per TOSA op, exactly the reference's op list */
+#define MLEL_PIPELINE_NO_TENSOR_CORE 2u /* keep contractions on the one-thread-per-output kernels */
 
 int mlel_pipeline_create(uint32_t flags, mlel_pipeline **out);
 void mlel_pipeline_destroy(mlel_pipeline *pipeline); /* vkDestroyPipeline, graph_layer.cpp:1280-1295 */
