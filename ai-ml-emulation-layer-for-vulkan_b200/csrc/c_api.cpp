@@ -7,6 +7,7 @@
 
 #include "graph_pipeline.hpp"
 #include "kernels/device_common.cuh"
+#include "kernels/gemm_i8_tcgen05.hpp"
 #include "kernels/kernels.hpp"
 #include "session.hpp"
 
@@ -90,6 +91,10 @@ extern "C" {
 
 const char *mlel_last_error(void) { return lastError().c_str(); }
 int mlel_elem_size(int32_t dtype) { return elemSize(dtype); }
+int mlel_device_error(void) {
+    cudaDeviceSynchronize();
+    return tcgen05ErrorFlag();
+}
 
 int mlel_pipeline_create(uint32_t flags, mlel_pipeline **out) {
     return guarded([&] {

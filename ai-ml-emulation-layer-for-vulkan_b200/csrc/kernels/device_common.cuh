@@ -207,4 +207,58 @@ __host__ __device__ inline int32_t rescaleValue(int64_t in, int32_t inZp, int32_
     return r < lo ? lo : (r > hi ? hi : r);
 }
 
+// ---- RESCALE in 32-bit-friendly form ---------------------------------------------------------------
+// applyScale needs (v - zpIn) * mult + round in 64 bits, an arithmetic shift and a truncation to
+// 32 bits.  With the input zero point folded into the rounding constant,
+//     (v - zpIn) * mult + round  ==  v * mult + (round - zpIn * mult)      (mod 2^64)
+// the whole step is one 32x32+64 multiply-add, one funnel shift and one shift.  The double-round
+// variant adds +-2^30 by the sign of (v - zpIn), i.e. picks one of two constants by v >= zpIn.
+// The low 32 bits of a 64-bit value shifted right by s are bits [s, s+32): for s <= 32 a funnel
+// shift of the two halves, for s > 32 the high half shifted arithmetically by s - 32.
+struct FastRescale {
+    int32_t mult;
+    int32_t zpIn;        // narrowed input zero point (threshold of the double-round sign test)
+    uint32_t rpLo, rpHi; // rounding constant for v >= zpIn
+    uint32_t rnLo, rnHi; // rounding constant for v <  zpIn
+    int32_t s1, s2;      // min(shift, 32), max(shift - 32, 0)
+};
+
+__host__ __device__ inline FastRescale makeFastRescale(int32_t mult, int32_t shift, int32_t zpIn, bool doubleRound) {
+    FastRescale f;
+    shift = shift < 0 ? 0 : (shift > 62 ? 62 : shift); // other shifts are undefined in the reference shader
+    uint64_t rp = shift > 0 ? (1ull << (shift - 1)) : 0ull;
+    uint64_t rn = rp;
+    if (doubleRound && shift > 31) {
+        rp += 1ull << 30;
+        rn -= 1ull << 30;
+    }
+    const uint64_t fold = uint64_t(0) - uint64_t(int64_t(zpIn)) * uint64_t(int64_t(mult));
+    rp += fold;
+    rn += fold;
+    f.mult = mult;
+    f.zpIn = zpIn;
+    f.rpLo = uint32_t(rp), f.rpHi = uint32_t(rp >> 32);
+    f.rnLo = uint32_t(rn), f.rnHi = uint32_t(rn >> 32);
+    f.s1 = shift < 32 ? shift : 32;
+    f.s2 = shift > 32 ? shift - 32 : 0;
+    return f;
+}
+
+// int32(((int64(v) - zpIn) * mult + round) >> shift), bit-identical to applyScale.
+__device__ __forceinline__ int32_t fastScale(int32_t v, int32_t mult, int32_t zpIn, uint32_t rpLo, uint32_t rpHi,
+                                             uint32_t rnLo, uint32_t rnHi, int32_t s1, int32_t s2) {
+    const bool nonNeg = v >= zpIn;
+    const uint64_t round = (uint64_t(nonNeg ? rpHi : rnHi) << 32) | uint64_t(nonNeg ? rpLo : rnLo);
+    uint64_t sum;
+    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(sum) : "r"(v), "r"(mult), "l"(round));
+    const uint32_t t = __funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), uint32_t(s1));
+    return int32_t(t) >> s2;
+}
+
+__device__ __forceinline__ int32_t fastRescale(const FastRescale &f, int32_t v, int32_t outZp, int32_t lo, int32_t hi) {
+    int32_t r = fastScale(v, f.mult, f.zpIn, f.rpLo, f.rpHi, f.rnLo, f.rnHi, f.s1, f.s2);
+    r = int32_t(uint32_t(r) + uint32_t(outZp));
+    return min(max(r, lo), hi);
+}
+
 } // namespace mlel

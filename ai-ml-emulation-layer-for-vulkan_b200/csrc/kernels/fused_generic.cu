@@ -129,14 +129,14 @@ __global__ void fusedMatmulKernel(TView a, TView b, TView out, int32_t zpA, int3
 // 16 int8 elements per thread, 16-byte loads and stores; n is padded work in 16-element groups.
 __global__ void fusedAddKernel(const int8_t *__restrict__ x, const int8_t *__restrict__ y, int8_t *__restrict__ out,
                                int64_t n, int64_t groups, DevEpilogue epi) {
-    const int32_t ma = epi.a.mult[0], mb = epi.b.mult[0], mo = epi.out.mult[0];
-    const int32_t sa = epi.a.shift[0], sb = epi.b.shift[0], so = epi.out.shift[0];
+    const FastRescale fa = makeFastRescale(epi.a.mult[0], epi.a.shift[0], epi.a.inZp, epi.a.doubleRound != 0);
+    const FastRescale fb = makeFastRescale(epi.b.mult[0], epi.b.shift[0], epi.b.inZp, epi.b.doubleRound != 0);
+    const FastRescale fo = makeFastRescale(epi.out.mult[0], epi.out.shift[0], epi.out.inZp, epi.out.doubleRound != 0);
     const auto one = [&](int8_t vx, int8_t vy) -> int8_t {
-        const int32_t ta = rescaleValue(vx, epi.a.inZp, ma, sa, epi.a.doubleRound != 0, epi.a.outZp, epi.a.lo, epi.a.hi);
-        const int32_t tb = rescaleValue(vy, epi.b.inZp, mb, sb, epi.b.doubleRound != 0, epi.b.outZp, epi.b.lo, epi.b.hi);
+        const int32_t ta = fastRescale(fa, vx, epi.a.outZp, epi.a.lo, epi.a.hi);
+        const int32_t tb = fastRescale(fb, vy, epi.b.outZp, epi.b.lo, epi.b.hi);
         const int32_t sum = int32_t(uint32_t(ta) + uint32_t(tb));
-        return int8_t(rescaleValue(sum, epi.out.inZp, mo, so, epi.out.doubleRound != 0, epi.out.outZp, epi.out.lo,
-                                   epi.out.hi));
+        return int8_t(fastRescale(fo, sum, epi.out.outZp, epi.out.lo, epi.out.hi));
     };
     GRID_STRIDE(g, groups) {
         const int4 vx = reinterpret_cast<const int4 *>(x)[g];

@@ -144,11 +144,12 @@ struct __align__(8) PipeBarriers {
     uint32_t pad;
 };
 
-__device__ __forceinline__ int32_t fusedStage(const DevRescale &r, int64_t v, uint32_t c) {
-    const uint32_t ci = r.perChannel ? c : 0u;
-    return rescaleValue(v, r.inZp, __ldg(r.mult + ci), int32_t(__ldg(r.shift + ci)), r.doubleRound != 0, r.outZp, r.lo,
-                        r.hi);
-}
+// Constants of the main RESCALE stage for one output column (see FastRescale).
+struct __align__(16) ColConst {
+    int32_t mult;
+    uint32_t rpLo, rpHi, rnLo, rnHi;
+    int32_t s1, s2, pad;
+};
 
 // A_TMA: A comes through tmapA; otherwise it is gathered from the NHWC input described by p.
 // B_MN : B is an N-contiguous [K][N] matrix (MN-major operand), otherwise a K-contiguous [N][K] matrix.
@@ -162,7 +163,8 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     constexpr int kTileB = BN * BK;
     uint8_t *tilesA = smem;
     uint8_t *tilesB = smem + NSTAGE * kTileA;
-    PipeBarriers *bars = reinterpret_cast<PipeBarriers *>(smem + NSTAGE * (kTileA + kTileB));
+    ColConst *colTab = reinterpret_cast<ColConst *>(smem + NSTAGE * (kTileA + kTileB));
+    PipeBarriers *bars = reinterpret_cast<PipeBarriers *>(smem + NSTAGE * (kTileA + kTileB) + BN * sizeof(ColConst));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -170,6 +172,18 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     const int n0 = blockIdx.y * BN;
     const int batch = blockIdx.z;
     const int numKb = (p.K + BK - 1) / BK;
+
+    // Per-column constants of the main RESCALE stage, shared by the 128 rows of the tile.
+    if (p.out8 != nullptr && threadIdx.x < BN) {
+        const int col = n0 + int(threadIdx.x);
+        const int ci = (p.epi.main.perChannel && col < p.N) ? col : 0;
+        const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
+                                              p.epi.main.inZp, p.epi.main.doubleRound != 0);
+        ColConst c;
+        c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi, c.rnLo = f.rnLo, c.rnHi = f.rnHi, c.s1 = f.s1, c.s2 = f.s2;
+        c.pad = 0;
+        colTab[threadIdx.x] = c;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -302,6 +316,16 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                 corr += (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0) + int64_t(cls) * p.N;
             }
             const int64_t outRow = (int64_t(batch) * p.M + m) * p.ldOut;
+            // Per-tensor stages of the residual tail: uniform constants, kept in registers.
+            FastRescale fa{}, fb{}, fo{};
+            if (p.epi.hasResidual) {
+                fa = makeFastRescale(__ldg(p.epi.a.mult), int32_t(__ldg(p.epi.a.shift)), p.epi.a.inZp, p.epi.a.doubleRound != 0);
+                fb = makeFastRescale(__ldg(p.epi.b.mult), int32_t(__ldg(p.epi.b.shift)), p.epi.b.inZp, p.epi.b.doubleRound != 0);
+                fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
+                                     p.epi.out.doubleRound != 0);
+            }
+            const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp, loMain = p.epi.main.lo,
+                          hiMain = p.epi.main.hi;
 #pragma unroll 1
             for (int cb = 0; cb < BN / 32; ++cb) {
                 uint32_t acc[32];
@@ -312,36 +336,84 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                     continue;
                 }
                 const int ncols = min(32, p.N - col0);
+                // + zero-point / bias correction (32-bit wrap, like the reference's int32 accumulator)
+                if (corr != nullptr) {
+                    if (ncols == 32) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const int4 c4 = __ldg(reinterpret_cast<const int4 *>(corr + col0) + q);
+                            acc[4 * q + 0] += uint32_t(c4.x), acc[4 * q + 1] += uint32_t(c4.y);
+                            acc[4 * q + 2] += uint32_t(c4.z), acc[4 * q + 3] += uint32_t(c4.w);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            acc[j] += j < ncols ? uint32_t(__ldg(corr + col0 + j)) : 0u;
+                        }
+                    }
+                }
                 if (p.out32 != nullptr) {
                     int32_t *dst = p.out32 + outRow + col0;
-                    for (int j = 0; j < ncols; ++j) {
-                        dst[j] = int32_t(acc[j] + (corr ? uint32_t(__ldg(corr + col0 + j)) : 0u));
+                    if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            reinterpret_cast<int4 *>(dst)[q] =
+                                make_int4(int(acc[4 * q]), int(acc[4 * q + 1]), int(acc[4 * q + 2]), int(acc[4 * q + 3]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (j < ncols) {
+                                dst[j] = int32_t(acc[j]);
+                            }
+                        }
                     }
                     continue;
                 }
-                alignas(16) int8_t packed[32];
+                int8_t *dst = p.out8 + outRow + col0;
+                const bool vec = ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+                uint32_t sc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; // 32 shortcut bytes of this row
+                if (p.epi.hasResidual) {
+                    const int8_t *scp = p.epi.shortcut + outRow + col0;
+                    if (vec) {
+                        const int4 s0 = __ldg(reinterpret_cast<const int4 *>(scp));
+                        const int4 s1 = __ldg(reinterpret_cast<const int4 *>(scp) + 1);
+                        sc[0] = uint32_t(s0.x), sc[1] = uint32_t(s0.y), sc[2] = uint32_t(s0.z), sc[3] = uint32_t(s0.w);
+                        sc[4] = uint32_t(s1.x), sc[5] = uint32_t(s1.y), sc[6] = uint32_t(s1.z), sc[7] = uint32_t(s1.w);
+                    } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const uint32_t col = uint32_t(col0 + j);
-                    int32_t y = 0;
-                    if (j < ncols) {
-                        const int32_t v = int32_t(acc[j] + (corr ? uint32_t(__ldg(corr + col)) : 0u));
-                        y = fusedStage(p.epi.main, int64_t(v), col);
-                        if (p.epi.hasResidual) {
-                            const int32_t ta = fusedStage(p.epi.a, int64_t(y), col);
-                            const int32_t tb = fusedStage(p.epi.b, int64_t(p.epi.shortcut[outRow + col]), col);
-                            y = fusedStage(p.epi.out, int64_t(int32_t(uint32_t(ta) + uint32_t(tb))), col);
+                        for (int j = 0; j < 32; ++j) {
+                            if (j < ncols) {
+                                sc[j >> 2] |= uint32_t(uint8_t(scp[j])) << (8 * (j & 3));
+                            }
                         }
                     }
-                    packed[j] = int8_t(y);
                 }
-                int8_t *dst = p.out8 + outRow + col0;
-                if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                    reinterpret_cast<int4 *>(dst)[0] = reinterpret_cast<const int4 *>(packed)[0];
-                    reinterpret_cast<int4 *>(dst)[1] = reinterpret_cast<const int4 *>(packed)[1];
+                uint32_t packed[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const ColConst c = colTab[cb * 32 + j];
+                    int32_t y = fastScale(int32_t(acc[j]), c.mult, zpMain, c.rpLo, c.rpHi, c.rnLo, c.rnHi, c.s1, c.s2);
+                    y = int32_t(uint32_t(y) + uint32_t(outZpMain));
+                    y = min(max(y, loMain), hiMain);
+                    if (p.epi.hasResidual) {
+                        const int32_t ta = fastRescale(fa, y, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
+                        const int32_t sv = int32_t(int8_t(sc[j >> 2] >> (8 * (j & 3))));
+                        const int32_t tb = fastRescale(fb, sv, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
+                        y = fastRescale(fo, int32_t(uint32_t(ta) + uint32_t(tb)), p.epi.out.outZp, p.epi.out.lo,
+                                        p.epi.out.hi);
+                    }
+                    packed[j >> 2] |= uint32_t(uint8_t(y)) << (8 * (j & 3));
+                }
+                if (vec) {
+                    reinterpret_cast<int4 *>(dst)[0] = make_int4(int(packed[0]), int(packed[1]), int(packed[2]), int(packed[3]));
+                    reinterpret_cast<int4 *>(dst)[1] = make_int4(int(packed[4]), int(packed[5]), int(packed[6]), int(packed[7]));
                 } else {
-                    for (int j = 0; j < ncols; ++j) {
-                        dst[j] = packed[j];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (j < ncols) {
+                            dst[j] = int8_t(packed[j >> 2] >> (8 * (j & 3)));
+                        }
                     }
                 }
             }
@@ -400,7 +472,7 @@ bool makeMap(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint6
 
 template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
 int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, int batches, cudaStream_t s) {
-    constexpr size_t smemBytes = size_t(NSTAGE) * (BM * BK + BN * BK) + sizeof(PipeBarriers) + 1024;
+    constexpr size_t smemBytes = size_t(NSTAGE) * (BM * BK + BN * BK) + BN * sizeof(ColConst) + sizeof(PipeBarriers) + 1024;
     auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_TMA, B_MN>;
     static bool configured = false;
     if (!configured) {

@@ -77,6 +77,9 @@ typedef int32_t mlel_tensor_id; /* index of a tensor descriptor inside its pipel
 
 const char *mlel_last_error(void);
 int mlel_elem_size(int32_t dtype);
+/* Device-side error word of the current device: 0, or the code a kernel recorded when one of its
+ * bounded waits ran out (the kernel then returns instead of hanging).  Synchronises the device. */
+int mlel_device_error(void);
 
 /* ---- pipeline construction: replaces vkCreateDataGraphPipelinesARM, graph/graph_layer.cpp:815-964 ---- */
 

@@ -31,3 +31,11 @@ def reference_root():
     if not os.path.isdir(REFERENCE_ROOT):
         pytest.skip("reference checkout not present")
     return REFERENCE_ROOT
+
+
+@pytest.fixture(autouse=True)
+def _no_device_side_timeouts(request):
+    """After every GPU test: no kernel may have given up on a bounded wait."""
+    yield
+    if request.node.get_closest_marker("gpu") is not None:
+        assert load_package().lib().mlel_device_error() == 0, "a kernel recorded a timed-out wait"
