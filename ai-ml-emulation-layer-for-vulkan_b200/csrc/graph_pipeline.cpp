@@ -718,6 +718,19 @@ int32_t GraphPipeline::addDerivedConstant(int32_t dtype, const std::vector<int64
     return addTensor(std::move(t));
 }
 
+// Session-memory scratch of one launched node (planned like any other intermediate tensor).
+int32_t GraphPipeline::addScratchTensor(int32_t dtype, const std::vector<int64_t> &dims) {
+    auto t = std::make_unique<TensorDescriptor>();
+    t->dtype = dtype;
+    t->dims = dims;
+    t->strides = packedStrides(dtype, dims);
+    t->cls = TensorClass::Session;
+    t->sessionOrder = int32_t(sessionTensors_.size());
+    const int32_t tid = addTensor(std::move(t));
+    sessionTensors_.push_back(tid);
+    return tid;
+}
+
 // Decides, per launched node, whether the tcgen05 kernel can take it, and tabulates what that kernel
 // needs beyond the graph's own tensors.  Everything here is derived once from constant data.
 //
@@ -752,15 +765,24 @@ void GraphPipeline::prepareTensorCore() {
             }
             const int64_t OC = w.dims[0], KH = w.dims[1], KW = w.dims[2], IC = w.dims[3];
             const int64_t H = in.dims[1], W = in.dims[2], OH = out.dims[1], OW = out.dims[2];
-            if (in.dims[3] != IC || out.dims[3] != OC || IC % 16 != 0 || OC % 16 != 0 || KH * KW * IC > 65536 ||
-                (b.dims[0] != OC && b.dims[0] != 1) || out.numel() >= (int64_t(1) << 31) ||
-                in.numel() >= (int64_t(1) << 31)) {
-                continue;
-            }
             const int padTop = op.i[0], padLeft = op.i[2], sy = op.i[4], sx = op.i[5], dy = op.i[6], dx = op.i[7];
             if (sy <= 0 || sx <= 0 || dy <= 0 || dx <= 0) {
                 continue;
             }
+            // Channel counts that are not multiples of 16 (an RGB stem) cannot be gathered in 16-byte pieces:
+            // such a convolution first materialises its im2col matrix [pixels][kPad] in session memory and
+            // then runs as a plain matrix product against zero-padded weights (tc == 2).
+            const bool viaIm2col = IC % 16 != 0;
+            const int64_t kPad = (KH * KW * IC + 15) / 16 * 16;
+            if (viaIm2col && (dx != 0 && false)) {
+                continue;
+            }
+            if (in.dims[3] != IC || out.dims[3] != OC || OC % 16 != 0 || KH * KW * IC > 65536 ||
+                (b.dims[0] != OC && b.dims[0] != 1) || out.numel() >= (int64_t(1) << 31) ||
+                in.numel() >= (int64_t(1) << 31)) {
+                continue;
+            }
+
             // Border classes: the set of in-range taps along each axis.
             const auto classify = [](int64_t outDim, int64_t inDim, int64_t k, int stride, int pad, int dil,
                                      std::vector<uint8_t> &cls, std::vector<std::vector<bool>> &masks) {
@@ -830,6 +852,21 @@ void GraphPipeline::prepareTensorCore() {
             op.auxi[0] = int32_t(colMasks.size());
             op.auxi[1] = int32_t(rowMasks.size() * colMasks.size());
             op.tc = 1;
+            if (viaIm2col) {
+                const int64_t M = out.dims[0] * OH * OW, K = KH * KW * IC;
+                if (M * kPad >= (int64_t(1) << 32)) {
+                    op.tc = 0;
+                    continue;
+                }
+                std::vector<int8_t> wPad(size_t(OC * kPad), 0);
+                for (int64_t oc = 0; oc < OC; ++oc) {
+                    std::memcpy(&wPad[size_t(oc * kPad)], wd + oc * K, size_t(K));
+                }
+                op.aux[3] = addDerivedConstant(MLEL_I8, {OC, kPad}, wPad.data());
+                op.scratch = addScratchTensor(MLEL_I8, {M, kPad});
+                op.auxi[2] = int32_t(kPad);
+                op.tc = 2;
+            }
         } else {
             const TensorDescriptor &b = tensor(op.in[1]);
             if (b.cls != TensorClass::Constant || !b.packed() || b.dtype != MLEL_I8 || op.i[1] != 0) {

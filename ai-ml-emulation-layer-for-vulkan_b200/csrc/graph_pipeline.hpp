@@ -126,6 +126,7 @@ class GraphPipeline {
     void fuse();
     void prepareTensorCore();
     int32_t addDerivedConstant(int32_t dtype, const std::vector<int64_t> &dims, const void *data);
+    int32_t addScratchTensor(int32_t dtype, const std::vector<int64_t> &dims);
 
     uint32_t flags_;
     bool finalized_{false};

@@ -1,16 +1,21 @@
 // int8 x int8 -> int32 contraction on the 5th-generation tensor cores (tcgen05.mma kind::i8, TMEM
-// accumulator) with the TOSA epilogue fused in.  One kernel serves CONV2D (implicit GEMM), 1x1
-// CONV2D and MATMUL:
+// accumulator) with the TOSA epilogue fused in.  One persistent kernel serves CONV2D (implicit GEMM),
+// 1x1 CONV2D and MATMUL:
 //
 //   D[m, n] = sum_k A[m, k] * B[n, k]         m: output pixel (or matmul row), n: output channel
 //
-//   A operand  - TMA tile loads when A is a plain row-major matrix (1x1 stride-1 convolution, MATMUL);
+//   A operand  - TMA tile loads when A is a plain row-major matrix (1x1 stride-1 convolution, MATMUL,
+//                a materialised im2col matrix);
 //              - otherwise gathered by four producer warps with 16-byte cp.async (im2col on the fly:
 //                any kernel size, stride, dilation and padding; out-of-range taps are zero-filled)
 //   B operand  - TMA tile loads of the K-major weight matrix [N][K] (OHWI weights are exactly that), or
 //                of an N-major [K][N] matrix (MATMUL's second input) with an MN-major descriptor
-//   pipeline   - 128-byte K blocks, SWIZZLE_128B shared-memory tiles, NSTAGE-deep mbarrier ring;
-//                warp 4 issues TMA, warp 5 issues tcgen05.mma, warps 0-3 gather A and run the epilogue
+//   schedule   - one CTA per SM walks the output tiles (n fastest, so concurrently running CTAs share
+//                their A rows in L2); 128-byte K blocks in SWIZZLE_128B shared-memory tiles form an
+//                mbarrier ring that runs on across tiles; two TMEM accumulators alternate so that the
+//                epilogue of tile i overlaps the main loop of tile i+1
+//   warps      - 0-7 epilogue (two per TMEM lane quarter, each half of the columns), 8 TMA producer,
+//                9 MMA issuer and TMEM owner, 10-13 A gather (implicit-GEMM variants only)
 //   epilogue   - tcgen05.ld of the int32 accumulator, zero-point/bias correction, then either a raw
 //                int32 store or RESCALE (+CLAMP, + residual RESCALE/ADD/RESCALE) to int8
 //
@@ -38,10 +43,15 @@ __device__ int g_tcgen05Error = 0;
 
 namespace {
 
-constexpr int BM = 128;          // rows per CTA tile (UMMA M)
-constexpr int BK = 128;          // bytes (= int8 elements) of K per pipeline stage
-constexpr int UMMA_K = 32;       // K per tcgen05.mma for 8-bit operands
-constexpr int kNumThreads = 192; // warps 0-3: A gather + epilogue, warp 4: TMA, warp 5: MMA + TMEM
+constexpr int BM = 128;    // rows per tile (UMMA M)
+constexpr int BK = 128;    // bytes (= int8 elements) of K per pipeline stage
+constexpr int UMMA_K = 32; // K per tcgen05.mma for 8-bit operands
+constexpr int kEpilogueWarps = 8;
+constexpr int kTmaWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kGatherWarp0 = 10;
+constexpr int kThreadsTma = 320;    // warps 0-9
+constexpr int kThreadsGather = 448; // warps 0-13
 constexpr long long kWaitLimitCycles = 4000000000ll;
 
 __device__ __forceinline__ uint32_t smemAddr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -80,11 +90,6 @@ __device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int cod
     return true;
 }
 
-__device__ __forceinline__ void tmaLoad2d(const CUtensorMap *map, void *dst, uint64_t *bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(bar)), "r"(c0), "r"(c1)
-                 : "memory");
-}
 __device__ __forceinline__ void tmaLoad3d(const CUtensorMap *map, void *dst, uint64_t *bar, int c0, int c1, int c2) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -135,11 +140,16 @@ __device__ __forceinline__ void tmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+// Barrier among the epilogue warps only (named barrier 1).
+__device__ __forceinline__ void epilogueSync() {
+    asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+}
 
 struct __align__(8) PipeBarriers {
     uint64_t full[8];
     uint64_t empty[8];
-    uint64_t accumReady;
+    uint64_t accFull[2];
+    uint64_t accEmpty[2];
     uint32_t tmemBase;
     uint32_t pad;
 };
@@ -151,10 +161,14 @@ struct __align__(16) ColConst {
     int32_t s1, s2, pad;
 };
 
+struct TileCoord {
+    int m0, n0, batch;
+};
+
 // A_TMA: A comes through tmapA; otherwise it is gathered from the NHWC input described by p.
 // B_MN : B is an N-contiguous [K][N] matrix (MN-major operand), otherwise a K-contiguous [N][K] matrix.
 template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
-__global__ void __launch_bounds__(kNumThreads)
+__global__ void __launch_bounds__(A_TMA ? kThreadsTma : kThreadsGather, 1)
 gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const GemmI8Params p) {
     extern __shared__ uint8_t rawSmem[];
     // SWIZZLE_128B tiles must start on 1024-byte boundaries.
@@ -168,34 +182,33 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM;
-    const int n0 = blockIdx.y * BN;
-    const int batch = blockIdx.z;
     const int numKb = (p.K + BK - 1) / BK;
-
-    // Per-column constants of the main RESCALE stage, shared by the 128 rows of the tile.
-    if (p.out8 != nullptr && threadIdx.x < BN) {
-        const int col = n0 + int(threadIdx.x);
-        const int ci = (p.epi.main.perChannel && col < p.N) ? col : 0;
-        const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
-                                              p.epi.main.inZp, p.epi.main.doubleRound != 0);
-        ColConst c;
-        c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi, c.rnLo = f.rnLo, c.rnHi = f.rnHi, c.s1 = f.s1, c.s2 = f.s2;
-        c.pad = 0;
-        colTab[threadIdx.x] = c;
-    }
+    const int mTiles = (p.M + BM - 1) / BM;
+    const int nTiles = (p.N + BN - 1) / BN;
+    const int64_t numTiles = int64_t(mTiles) * nTiles * p.batches;
+    const auto tileOf = [&](int64_t t) {
+        TileCoord c;
+        c.n0 = int(t % nTiles) * BN;
+        t /= nTiles;
+        c.m0 = int(t % mTiles) * BM;
+        c.batch = int(t / mTiles);
+        return c;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
             mbarInit(&bars->full[s], A_TMA ? 1u : 1u + 128u);
             mbarInit(&bars->empty[s], 1u);
         }
-        mbarInit(&bars->accumReady, 1u);
+        for (int b = 0; b < 2; ++b) {
+            mbarInit(&bars->accFull[b], 1u);
+            mbarInit(&bars->accEmpty[b], uint32_t(kEpilogueWarps));
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&bars->tmemBase)),
-                     "r"(uint32_t(BN))
+                     "r"(uint32_t(2 * BN))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -204,106 +217,167 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmemBase = bars->tmemBase;
 
-    if (warp == 4) {
+    if (warp == kTmaWarp) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < numKb; ++kb) {
-                const int s = kb % NSTAGE;
-                const uint32_t phase = uint32_t(kb / NSTAGE) & 1u;
-                if (!mbarWait(&bars->empty[s], phase ^ 1u, 1)) {
-                    break;
-                }
-                mbarArriveExpectTx(&bars->full[s], uint32_t((A_TMA ? kTileA : 0) + kTileB));
-                if (A_TMA) {
-                    tmaLoad3d(&tmapA, tilesA + s * kTileA, &bars->full[s], kb * BK, m0, batch);
-                }
-                if (B_MN) {
-                    tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], n0, kb * BK, batch);
-                } else {
-                    tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], kb * BK, n0, p.batchedB ? batch : 0);
+            uint32_t it = 0; // K blocks issued so far: the ring runs on across tiles
+            bool ok = true;
+            for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+                const TileCoord tc = tileOf(t);
+                for (int kb = 0; kb < numKb; ++kb, ++it) {
+                    const int s = int(it % NSTAGE);
+                    const uint32_t phase = (it / NSTAGE) & 1u;
+                    ok = mbarWait(&bars->empty[s], phase ^ 1u, 1);
+                    if (!ok) {
+                        break;
+                    }
+                    mbarArriveExpectTx(&bars->full[s], uint32_t((A_TMA ? kTileA : 0) + kTileB));
+                    if (A_TMA) {
+                        tmaLoad3d(&tmapA, tilesA + s * kTileA, &bars->full[s], kb * BK, tc.m0, tc.batch);
+                    }
+                    if (B_MN) {
+                        tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], tc.n0, kb * BK, tc.batch);
+                    } else {
+                        tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], kb * BK, tc.n0, p.batchedB ? tc.batch : 0);
+                    }
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = instrDesc(BN, B_MN);
+            uint32_t it = 0, tileCount = 0;
             bool ok = true;
-            for (int kb = 0; kb < numKb && ok; ++kb) {
-                const int s = kb % NSTAGE;
-                const uint32_t phase = uint32_t(kb / NSTAGE) & 1u;
-                ok = mbarWait(&bars->full[s], phase, 2);
+            for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileCount) {
+                const uint32_t buf = tileCount & 1u;
+                // wait until the epilogue has drained this accumulator (passes at once for the first two tiles)
+                ok = mbarWait(&bars->accEmpty[buf], ((tileCount >> 1) & 1u) ^ 1u, 5);
                 if (!ok) {
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t aAddr = smemAddr(tilesA + s * kTileA);
-                const uint32_t bAddr = smemAddr(tilesB + s * kTileB);
+                const uint32_t tmemD = tmemBase + buf * uint32_t(BN);
+                for (int kb = 0; kb < numKb; ++kb, ++it) {
+                    const int s = int(it % NSTAGE);
+                    const uint32_t phase = (it / NSTAGE) & 1u;
+                    ok = mbarWait(&bars->full[s], phase, 2);
+                    if (!ok) {
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t aAddr = smemAddr(tilesA + s * kTileA);
+                    const uint32_t bAddr = smemAddr(tilesB + s * kTileB);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // K-major: step 32 bytes inside the 128-byte swizzle row; MN-major: step 32 K-rows of 128 bytes
-                    const uint64_t da = smemDesc(aAddr + k * UMMA_K, 16, 1024);
-                    const uint64_t db = B_MN ? smemDesc(bAddr + k * UMMA_K * 128, BK * 128, 1024)
-                                             : smemDesc(bAddr + k * UMMA_K, 16, 1024);
-                    umma(tmemBase, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major: step 32 bytes inside the 128-byte swizzle row; MN-major: step 32 K-rows of 128 bytes
+                        const uint64_t da = smemDesc(aAddr + k * UMMA_K, 16, 1024);
+                        const uint64_t db = B_MN ? smemDesc(bAddr + k * UMMA_K * 128, BK * 128, 1024)
+                                                 : smemDesc(bAddr + k * UMMA_K, 16, 1024);
+                        umma(tmemD, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ummaCommit(&bars->empty[s]); // frees the stage once these MMAs have read it
                 }
-                ummaCommit(&bars->empty[s]); // frees the stage once these MMAs have read it
+                if (ok) {
+                    ummaCommit(&bars->accFull[buf]);
+                }
             }
-            ummaCommit(&bars->accumReady);
         }
-    } else {
-        // ---------------- warps 0-3: A gather (when not TMA), then epilogue ----------------
-        const int row = warp * 32 + lane; // row of the tile == TMEM lane
-        const int64_t m = int64_t(m0) + row;
+    } else if (warp >= kGatherWarp0) {
+        // ---------------- A gather (implicit GEMM): one tile row per thread ----------------
         if (!A_TMA) {
-            const bool rowValid = m < p.M;
-            int n = 0, oy = 0, ox = 0;
-            if (rowValid) {
-                n = int(m / (int64_t(p.OH) * p.OW));
-                const int rem = int(m - int64_t(n) * p.OH * p.OW);
-                oy = rem / p.OW;
-                ox = rem - oy * p.OW;
-            }
-            const int iy0 = oy * p.strideY - p.padTop;
-            const int ix0 = ox * p.strideX - p.padLeft;
-            const int8_t *base = p.in + int64_t(n) * p.H * p.W * p.IC;
-            int c = 0, kx = 0, ky = 0; // position of the next 16-byte chunk inside K = (ky, kx, c)
+            const int row = (warp - kGatherWarp0) * 32 + lane;
             const uint32_t swz = uint32_t(row & 7);
-            for (int kb = 0; kb < numKb; ++kb) {
-                const int s = kb % NSTAGE;
-                const uint32_t phase = uint32_t(kb / NSTAGE) & 1u;
-                if (!mbarWait(&bars->empty[s], phase ^ 1u, 3)) {
-                    break;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+                const TileCoord tc = tileOf(t);
+                const int64_t m = int64_t(tc.m0) + row;
+                const bool rowValid = m < p.M;
+                int n = 0, oy = 0, ox = 0;
+                if (rowValid) {
+                    n = int(m / (int64_t(p.OH) * p.OW));
+                    const int rem = int(m - int64_t(n) * p.OH * p.OW);
+                    oy = rem / p.OW;
+                    ox = rem - oy * p.OW;
                 }
-                const uint32_t dstRow = smemAddr(tilesA + s * kTileA) + uint32_t(row) * 128u;
+                const int iy0 = oy * p.strideY - p.padTop;
+                const int ix0 = ox * p.strideX - p.padLeft;
+                const int8_t *base = p.in + int64_t(n) * p.H * p.W * p.IC;
+                int c = 0, kx = 0, ky = 0; // position of the next 16-byte chunk inside K = (ky, kx, c)
+                for (int kb = 0; kb < numKb; ++kb, ++it) {
+                    const int s = int(it % NSTAGE);
+                    const uint32_t phase = (it / NSTAGE) & 1u;
+                    ok = mbarWait(&bars->empty[s], phase ^ 1u, 3);
+                    if (!ok) {
+                        break;
+                    }
+                    const uint32_t dstRow = smemAddr(tilesA + s * kTileA) + uint32_t(row) * 128u;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int y = iy0 + ky * p.dilY;
-                    const int x = ix0 + kx * p.dilX;
-                    const bool valid = rowValid && ky < p.KH && y >= 0 && y < p.H && x >= 0 && x < p.W;
-                    const int8_t *src = valid ? base + (int64_t(y) * p.W + x) * p.IC + c : p.in;
-                    const uint32_t dst = dstRow + ((uint32_t(j) ^ swz) << 4);
-                    const uint32_t bytes = valid ? 16u : 0u; // 0 source bytes => the 16 bytes are zero-filled
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
-                                 : "memory");
-                    c += 16;
-                    if (c >= p.IC) {
-                        c = 0;
-                        if (++kx == p.KW) {
-                            kx = 0;
-                            ++ky;
+                    for (int j = 0; j < 8; ++j) {
+                        const int y = iy0 + ky * p.dilY;
+                        const int x = ix0 + kx * p.dilX;
+                        const bool valid = rowValid && ky < p.KH && y >= 0 && y < p.H && x >= 0 && x < p.W;
+                        const int8_t *src = valid ? base + (int64_t(y) * p.W + x) * p.IC + c : p.in;
+                        const uint32_t dst = dstRow + ((uint32_t(j) ^ swz) << 4);
+                        const uint32_t bytes = valid ? 16u : 0u; // 0 source bytes => the 16 bytes are zero-filled
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+                                     : "memory");
+                        c += 16;
+                        if (c >= p.IC) {
+                            c = 0;
+                            if (++kx == p.KW) {
+                                kx = 0;
+                                ++ky;
+                            }
                         }
                     }
+                    // The stage's barrier completes when these copies have landed and every producer arrived.
+                    asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s]))
+                                 : "memory");
+                    mbarArrive(&bars->full[s]);
                 }
-                // The stage's barrier completes when these copies have landed and every producer arrived.
-                asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s])) : "memory");
-                mbarArrive(&bars->full[s]);
             }
         }
-
-        // ---------------- epilogue ----------------
-        if (mbarWait(&bars->accumReady, 0u, 4)) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    } else {
+        // ---------------- epilogue: warps 0-7 ----------------
+        const int quarter = warp & 3;           // TMEM lanes [32 * quarter, 32 * quarter + 32)
+        const int half = warp >> 2;             // which half of the tile's columns
+        constexpr int kChunks = BN / 64;        // 32-column chunks per warp
+        const int row = quarter * 32 + lane;
+        // Per-tensor stages of the residual tail: uniform constants, kept in registers.
+        FastRescale fa{}, fb{}, fo{};
+        if (p.out8 != nullptr && p.epi.hasResidual) {
+            fa = makeFastRescale(__ldg(p.epi.a.mult), int32_t(__ldg(p.epi.a.shift)), p.epi.a.inZp, p.epi.a.doubleRound != 0);
+            fb = makeFastRescale(__ldg(p.epi.b.mult), int32_t(__ldg(p.epi.b.shift)), p.epi.b.inZp, p.epi.b.doubleRound != 0);
+            fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
+                                 p.epi.out.doubleRound != 0);
+        }
+        const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp, loMain = p.epi.main.lo,
+                      hiMain = p.epi.main.hi;
+        uint32_t tileCount = 0;
+        int tabN0 = -1; // column origin the shared constants table was built for
+        bool ok = true;
+        for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileCount) {
+            const TileCoord tc = tileOf(t);
+            const uint32_t buf = tileCount & 1u;
+            // Per-column constants of the main RESCALE stage, shared by the 128 rows of the tile.
+            if (p.out8 != nullptr && tc.n0 != tabN0) {
+                epilogueSync(); // everyone is done with the previous table
+                if (threadIdx.x < BN) {
+                    const int col = tc.n0 + int(threadIdx.x);
+                    const int ci = (p.epi.main.perChannel && col < p.N) ? col : 0;
+                    const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
+                                                          zpMain, p.epi.main.doubleRound != 0);
+                    ColConst c;
+                    c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi, c.rnLo = f.rnLo, c.rnHi = f.rnHi;
+                    c.s1 = f.s1, c.s2 = f.s2, c.pad = 0;
+                    colTab[threadIdx.x] = c;
+                }
+                epilogueSync();
+                tabN0 = tc.n0;
+            }
+            const int64_t m = int64_t(tc.m0) + row;
             const bool rowValid = m < p.M;
             // zero-point / bias correction row of this pixel's border class
             const int32_t *corr = p.corr;
@@ -311,27 +385,32 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                 int cls = 0;
                 if (p.rowClass != nullptr && rowValid) {
                     const int rem = int(m % (int64_t(p.OH) * p.OW));
-                    cls = int(p.rowClass[rem / p.OW]) * p.numColClasses + int(p.colClass[rem % p.OW]);
+                    cls = int(__ldg(p.rowClass + rem / p.OW)) * p.numColClasses + int(__ldg(p.colClass + rem % p.OW));
                 }
-                corr += (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0) + int64_t(cls) * p.N;
+                corr += (p.batchedCorr ? int64_t(tc.batch) * p.numClasses * p.N : 0) + int64_t(cls) * p.N;
             }
-            const int64_t outRow = (int64_t(batch) * p.M + m) * p.ldOut;
-            // Per-tensor stages of the residual tail: uniform constants, kept in registers.
-            FastRescale fa{}, fb{}, fo{};
-            if (p.epi.hasResidual) {
-                fa = makeFastRescale(__ldg(p.epi.a.mult), int32_t(__ldg(p.epi.a.shift)), p.epi.a.inZp, p.epi.a.doubleRound != 0);
-                fb = makeFastRescale(__ldg(p.epi.b.mult), int32_t(__ldg(p.epi.b.shift)), p.epi.b.inZp, p.epi.b.doubleRound != 0);
-                fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
-                                     p.epi.out.doubleRound != 0);
+            const int64_t outRow = (int64_t(tc.batch) * p.M + m) * p.ldOut;
+
+            ok = mbarWait(&bars->accFull[buf], (tileCount >> 1) & 1u, 4);
+            if (!ok) {
+                break;
             }
-            const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp, loMain = p.epi.main.lo,
-                          hiMain = p.epi.main.hi;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr = tmemBase + buf * uint32_t(BN) + (uint32_t(quarter * 32) << 16);
 #pragma unroll 1
-            for (int cb = 0; cb < BN / 32; ++cb) {
+            for (int ch = 0; ch < kChunks; ++ch) {
+                const int cb = half * kChunks + ch;
                 uint32_t acc[32];
-                tmemLoad32(tmemBase + (uint32_t(warp * 32) << 16) + uint32_t(cb * 32), acc);
+                tmemLoad32(taddr + uint32_t(cb * 32), acc);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int col0 = n0 + cb * 32;
+                if (ch == kChunks - 1) {
+                    // this warp's part of the accumulator is in registers: hand the buffer back to the MMA warp
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    if (lane == 0) {
+                        mbarArrive(&bars->accEmpty[buf]);
+                    }
+                }
+                const int col0 = tc.n0 + cb * 32;
                 if (!rowValid || col0 >= p.N) {
                     continue;
                 }
@@ -422,9 +501,10 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(uint32_t(BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(uint32_t(2 * BN))
+                     : "memory");
     }
 }
 
@@ -470,9 +550,22 @@ bool makeMap(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint6
     return true;
 }
 
+int smCount() {
+    static int count = 0;
+    if (count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0) {
+            count = kNumSMs;
+        }
+    }
+    return count;
+}
+
 template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
-int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, int batches, cudaStream_t s) {
-    constexpr size_t smemBytes = size_t(NSTAGE) * (BM * BK + BN * BK) + BN * sizeof(ColConst) + sizeof(PipeBarriers) + 1024;
+int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, cudaStream_t s) {
+    constexpr size_t smemBytes =
+        size_t(NSTAGE) * (BM * BK + BN * BK) + BN * sizeof(ColConst) + sizeof(PipeBarriers) + 1024;
     auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_TMA, B_MN>;
     static bool configured = false;
     if (!configured) {
@@ -482,8 +575,9 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8
         }
         configured = true;
     }
-    const dim3 grid(unsigned((p.M + BM - 1) / BM), unsigned((p.N + BN - 1) / BN), unsigned(batches));
-    kernel<<<grid, kNumThreads, smemBytes, s>>>(mapA, mapB, p);
+    const int64_t tiles = int64_t((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batches;
+    const int grid = int(tiles < smCount() ? tiles : smCount()); // persistent: one CTA per SM
+    kernel<<<grid, A_TMA ? kThreadsTma : kThreadsGather, smemBytes, s>>>(mapA, mapB, p);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
         setLastError(std::string("tcgen05 int8 GEMM launch: ") + cudaGetErrorString(err));
@@ -496,6 +590,7 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8
 
 int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
     GemmI8Params p = q.params;
+    p.batches = q.batches;
     CUtensorMap mapA{}, mapB{};
     const bool aTma = q.aMatrix != nullptr;
     if (aTma) {
@@ -521,15 +616,15 @@ int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
         }
     }
     if (q.bMnMajor) {
-        return aTma ? launchVariant<128, 3, true, true>(mapA, mapB, p, q.batches, s)
-                    : launchVariant<128, 3, false, true>(mapA, mapB, p, q.batches, s);
+        return aTma ? launchVariant<128, 6, true, true>(mapA, mapB, p, s)
+                    : launchVariant<128, 6, false, true>(mapA, mapB, p, s);
     }
     if (bn == 64) {
-        return aTma ? launchVariant<64, 4, true, false>(mapA, mapB, p, q.batches, s)
-                    : launchVariant<64, 4, false, false>(mapA, mapB, p, q.batches, s);
+        return aTma ? launchVariant<64, 8, true, false>(mapA, mapB, p, s)
+                    : launchVariant<64, 8, false, false>(mapA, mapB, p, s);
     }
-    return aTma ? launchVariant<128, 3, true, false>(mapA, mapB, p, q.batches, s)
-                : launchVariant<128, 3, false, false>(mapA, mapB, p, q.batches, s);
+    return aTma ? launchVariant<128, 6, true, false>(mapA, mapB, p, s)
+                : launchVariant<128, 6, false, false>(mapA, mapB, p, s);
 }
 
 int tcgen05ErrorFlag() {

@@ -13,6 +13,7 @@ namespace mlel {
 struct GemmI8Params {
     int32_t M, N, K;     // per batch: rows, columns (output channels), contraction length in bytes
     int32_t ldOut;       // elements between consecutive output rows
+    int32_t batches;     // number of independent [M,K]x[K,N] problems (filled in by gemmI8Launch)
     int32_t batchedB;    // K-major B only: B has one matrix per batch (else one shared matrix)
     // implicit-GEMM geometry (used only when A is gathered): NHWC input, window, output grid
     const int8_t *in;

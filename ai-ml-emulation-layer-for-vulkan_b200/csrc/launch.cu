@@ -114,6 +114,24 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
         p.out32 = reinterpret_cast<int32_t *>(out.ptr);
     }
     q.batches = 1;
+    if (op.tc == 2) {
+        // Channel count not a multiple of 16: materialise the im2col matrix, then a plain matrix product.
+        const int kPad = op.auxi[2];
+        int8_t *scratch = reinterpret_cast<int8_t *>(T[op.scratch].ptr);
+        const int rc = im2colSmallIc(p.in, scratch, p.M, p.H, p.W, p.IC, p.OH, p.OW, p.KH, p.KW, convAttr(op), p.K, kPad, s);
+        if (rc != MLEL_SUCCESS) {
+            return rc;
+        }
+        p.K = kPad;
+        q.aMatrix = scratch;
+        q.aRowBytes = uint64_t(kPad);
+        q.aBatchBytes = uint64_t(kPad) * uint64_t(p.M);
+        q.bMatrix = T[op.aux[3]].ptr;
+        q.bRowBytes = uint64_t(kPad);
+        q.bBatchBytes = 0;
+        q.bMnMajor = false;
+        return gemmI8Launch(q, s);
+    }
     // A 1x1, stride-1, unpadded convolution reads the input as a plain [pixels][IC] matrix.
     const bool plain = p.KH == 1 && p.KW == 1 && p.strideY == 1 && p.strideX == 1 && op.i[0] == 0 && op.i[1] == 0 &&
                        op.i[2] == 0 && op.i[3] == 0 && (reinterpret_cast<uintptr_t>(in.ptr) & 15u) == 0;
@@ -192,6 +210,9 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
     case OP_AVG_POOL2D:
         return genericAvgPool(in(0), out, poolAttr(op), s);
     case OP_MAX_POOL2D:
+        if (maxPoolI8Eligible(in(0), out)) {
+            return maxPoolI8(in(0), out, poolAttr(op), s);
+        }
         return genericMaxPool(in(0), out, poolAttr(op), s);
     case OP_TABLE:
         return genericTable(in(0), out, in(1), s);

@@ -145,7 +145,10 @@ struct OpDesc {
     //                 aux[2] column classes u8 [OW]; auxi[0] = number of column classes, auxi[1] = classes
     //   MATMUL kinds with a constant second input: aux[0] correction int32 [batches][W],
     //                 aux[3] the second input transposed to [batches][W][C]
+    //   CONV2D kinds with tc == 2 (channel count not a multiple of 16): aux[3] weights zero-padded to
+    //                 [OC][kPad], scratch = session tensor [pixels][kPad] for the im2col matrix, auxi[2] = kPad
     int32_t tc{0};
+    int32_t scratch{-1};
     int32_t aux[4]{-1, -1, -1, -1};
     int32_t auxi[4]{0, 0, 0, 0};
 };

@@ -56,6 +56,7 @@ void Session::plan() {
             touch(t, index);
         }
         touch(op.epi.shortcutTensor, index);
+        touch(op.scratch, index);
         ++index;
     }
     for (auto t : pipeline_->graphOutputs()) {
@@ -129,6 +130,7 @@ int Session::resolve() {
         }
         used.insert(op.epi.shortcutTensor);
         used.insert(std::begin(op.aux), std::end(op.aux));
+        used.insert(op.scratch);
     }
     used.erase(-1);
     for (int32_t t = 0; t < n; ++t) {
