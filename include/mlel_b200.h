@@ -262,6 +262,20 @@ int mlel_cuda_conv2d_rescale(const mlel_tensor *input, const mlel_tensor *weight
                              int32_t output_zp, int double_round, int per_channel, int32_t clamp_min,
                              int32_t clamp_max, void *cuda_stream);
 
+/* CONV2D (int8 input, int8 OHWI weights with zero point 0, int32 bias, int32 output; same result as
+ * mlel_cuda_conv2d) for callers that must not allocate device memory, such as a layer's dispatch hook
+ * or code that runs inside another runtime's fixed memory budget.  It has no counterpart in the
+ * reference.  All working memory is a 32 MiB array built into the library, so the call makes no
+ * cudaMalloc/cudaFree and uses no allocating library routine; problems that need more
+ * (pixels * kPad + OC * kPad + 4 * OC bytes, kPad = KH*KW*IC rounded up to 16) are rejected with
+ * MLEL_ERROR_UNKNOWN.  The array is shared by every call on the device: calls whose GPU work may overlap
+ * must be serialised by the caller.  The first call on a device resolves the array's address and should
+ * be made outside stream capture. */
+int mlel_cuda_conv2d_static_scratch(const mlel_tensor *input, const mlel_tensor *weights, const mlel_tensor *biases,
+                                    const mlel_tensor *output, const int32_t pad[4], const int32_t stride[2],
+                                    const int32_t dilation[2], int32_t input_zp, int32_t weight_zp,
+                                    void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
