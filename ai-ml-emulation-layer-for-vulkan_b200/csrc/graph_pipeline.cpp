@@ -774,9 +774,6 @@ void GraphPipeline::prepareTensorCore() {
             // then runs as a plain matrix product against zero-padded weights (tc == 2).
             const bool viaIm2col = IC % 16 != 0;
             const int64_t kPad = (KH * KW * IC + 15) / 16 * 16;
-            if (viaIm2col && (dx != 0 && false)) {
-                continue;
-            }
             if (in.dims[3] != IC || out.dims[3] != OC || OC % 16 != 0 || KH * KW * IC > 65536 ||
                 (b.dims[0] != OC && b.dims[0] != 1) || out.numel() >= (int64_t(1) << 31) ||
                 in.numel() >= (int64_t(1) << 31)) {
@@ -851,6 +848,20 @@ void GraphPipeline::prepareTensorCore() {
             op.aux[2] = addDerivedConstant(MLEL_U8, {OW}, colCls.data());
             op.auxi[0] = int32_t(colMasks.size());
             op.auxi[1] = int32_t(rowMasks.size() * colMasks.size());
+            {
+                // the most common class (normally "every tap in range"): its correction row is what the
+                // kernel stages in shared memory
+                std::vector<int64_t> rowCount(rowMasks.size(), 0), colCount(colMasks.size(), 0);
+                for (auto c : rowCls) {
+                    rowCount[c]++;
+                }
+                for (auto c : colCls) {
+                    colCount[c]++;
+                }
+                const size_t rBest = size_t(std::max_element(rowCount.begin(), rowCount.end()) - rowCount.begin());
+                const size_t cBest = size_t(std::max_element(colCount.begin(), colCount.end()) - colCount.begin());
+                op.auxi[3] = int32_t(rBest * colMasks.size() + cBest);
+            }
             op.tc = 1;
             if (viaIm2col) {
                 const int64_t M = out.dims[0] * OH * OW, K = KH * KW * IC;

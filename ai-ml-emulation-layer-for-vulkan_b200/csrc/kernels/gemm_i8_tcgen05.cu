@@ -158,12 +158,270 @@ struct __align__(8) PipeBarriers {
 struct __align__(16) ColConst {
     int32_t mult;
     uint32_t rpLo, rpHi, rnLo, rnHi;
-    int32_t s1, s2, pad;
+    int32_t s1, s2;
+    int32_t corr0; // correction of the most common border class for this column
 };
 
 struct TileCoord {
     int m0, n0, batch;
 };
+
+__device__ __forceinline__ void tmemLoad16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// Saturates four int32 values to int8 and packs them, e0 in the lowest byte.
+__device__ __forceinline__ uint32_t packSat4(int32_t e0, int32_t e1, int32_t e2, int32_t e3) {
+    uint32_t hi, d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(e3), "r"(e2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(e1), "r"(e0), "r"(hi));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t replicate4(int32_t v) { return uint32_t(uint8_t(v)) * 0x01010101u; }
+
+// The epilogue of the persistent kernel (warps 0-7).  Each warp owns 32 TMEM lanes (tile rows) and half of
+// the tile's columns, which it walks in 16-column steps: one tcgen05.ld, 16 RESCALEs, one 16-byte store.
+template <int BN, int NSTAGE, bool RESIDUAL>
+__device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers *bars, ColConst *colTab,
+                                             uint32_t tmemBase, int warp, int lane, int64_t numTiles, int mTiles,
+                                             int nTiles) {
+    const int quarter = warp & 3; // TMEM lanes [32 * quarter, 32 * quarter + 32)
+    const int half = warp >> 2;   // which half of the tile's columns
+    constexpr int kColsPerWarp = BN / 2;
+    constexpr int kSteps = kColsPerWarp / 16;
+    const int row = quarter * 32 + lane;
+    FastRescale fa{}, fb{}, fo{};
+    if (RESIDUAL) {
+        fa = makeFastRescale(__ldg(p.epi.a.mult), int32_t(__ldg(p.epi.a.shift)), p.epi.a.inZp, p.epi.a.doubleRound != 0);
+        fb = makeFastRescale(__ldg(p.epi.b.mult), int32_t(__ldg(p.epi.b.shift)), p.epi.b.inZp, p.epi.b.doubleRound != 0);
+        fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
+                             p.epi.out.doubleRound != 0);
+    }
+    const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp;
+    const uint32_t lo4 = replicate4(RESIDUAL ? p.epi.out.lo : p.epi.main.lo);
+    const uint32_t hi4 = replicate4(RESIDUAL ? p.epi.out.hi : p.epi.main.hi);
+    const int32_t loMain = p.epi.main.lo, hiMain = p.epi.main.hi;
+    uint32_t tileCount = 0;
+    int tabN0 = -1, tabBatch = -1; // what the shared constants table was built for
+    for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
+        int64_t tt = t;
+        const int n0 = int(tt % nTiles) * BN;
+        tt /= nTiles;
+        const int m0 = int(tt % mTiles) * BM;
+        const int batch = int(tt / mTiles);
+        const uint32_t buf = tileCount & 1u;
+        const int32_t *corrBatch = p.corr + (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0);
+        // Per-column constants shared by the 128 rows of the tile: the main RESCALE stage and the correction
+        // of the most common border class.
+        if (n0 != tabN0 || (p.batchedCorr && batch != tabBatch)) {
+            epilogueSync(); // everyone is done with the previous table
+            if (threadIdx.x < BN) {
+                const int col = n0 + int(threadIdx.x);
+                const int ci = (p.epi.main.perChannel && col < p.N) ? col : 0;
+                const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
+                                                      zpMain, p.epi.main.doubleRound != 0);
+                ColConst c;
+                c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi, c.rnLo = f.rnLo, c.rnHi = f.rnHi;
+                c.s1 = f.s1, c.s2 = f.s2;
+                c.corr0 = col < p.N ? __ldg(corrBatch + int64_t(p.baseClass) * p.N + col) : 0;
+                colTab[threadIdx.x] = c;
+            }
+            epilogueSync();
+            tabN0 = n0;
+            tabBatch = batch;
+        }
+        const int64_t m = int64_t(m0) + row;
+        const bool rowValid = m < p.M;
+        int cls = p.baseClass;
+        if (p.rowClass != nullptr && rowValid) {
+            const int rem = int(m % (int64_t(p.OH) * p.OW));
+            cls = int(__ldg(p.rowClass + rem / p.OW)) * p.numColClasses + int(__ldg(p.colClass + rem % p.OW));
+        }
+        const int64_t outRow = (int64_t(batch) * p.M + m) * p.ldOut;
+
+        if (!mbarWait(&bars->accFull[buf], (tileCount >> 1) & 1u, 4)) {
+            break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmemBase + buf * uint32_t(BN) + (uint32_t(quarter * 32) << 16);
+#pragma unroll 1
+        for (int st = 0; st < kSteps; ++st) {
+            const int cl = half * kColsPerWarp + st * 16; // column inside the tile
+            uint32_t acc[16];
+            tmemLoad16(taddr + uint32_t(cl), acc);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (st == kSteps - 1) {
+                // this warp's part of the accumulator is in registers: hand the buffer back to the MMA warp
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                if (lane == 0) {
+                    mbarArrive(&bars->accEmpty[buf]);
+                }
+            }
+            const int col0 = n0 + cl;
+            if (!rowValid || col0 >= p.N) {
+                continue;
+            }
+            const int ncols = min(16, p.N - col0);
+            int8_t *dst = p.out8 + outRow + col0;
+            const bool vec = ncols == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+            if (cls != p.baseClass) {
+                // a pixel whose window crosses the border: swap the table's correction for its own class's
+                const int32_t *own = corrBatch + int64_t(cls) * p.N + col0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (j < ncols) {
+                        acc[j] += uint32_t(__ldg(own + j)) - uint32_t(colTab[cl + j].corr0);
+                    }
+                }
+            }
+            uint32_t sc[4] = {0, 0, 0, 0}; // 16 shortcut bytes of this row
+            if (RESIDUAL) {
+                const int8_t *scp = p.epi.shortcut + outRow + col0;
+                if (vec) {
+                    const int4 s0 = __ldg(reinterpret_cast<const int4 *>(scp));
+                    sc[0] = uint32_t(s0.x), sc[1] = uint32_t(s0.y), sc[2] = uint32_t(s0.z), sc[3] = uint32_t(s0.w);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j < ncols) {
+                            sc[j >> 2] |= uint32_t(uint8_t(scp[j])) << (8 * (j & 3));
+                        }
+                    }
+                }
+            }
+            uint32_t packed[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                int32_t y[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = 4 * q + e;
+                    const ColConst c = colTab[cl + j];
+                    const int32_t v = int32_t(acc[j] + uint32_t(c.corr0));
+                    int32_t r = fastScale(v, c.mult, zpMain, c.rpLo, c.rpHi, c.rnLo, c.rnHi, c.s1, c.s2);
+                    r = int32_t(uint32_t(r) + uint32_t(outZpMain));
+                    if (RESIDUAL) {
+                        r = min(max(r, loMain), hiMain);
+                        const int32_t ta = fastRescale(fa, r, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
+                        const int32_t sv = int32_t(int8_t(sc[q] >> (8 * e)));
+                        const int32_t tb = fastRescale(fb, sv, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
+                        const int32_t sum = int32_t(uint32_t(ta) + uint32_t(tb));
+                        r = fastScale(sum, fo.mult, fo.zpIn, fo.rpLo, fo.rpHi, fo.rnLo, fo.rnHi, fo.s1, fo.s2);
+                        r = int32_t(uint32_t(r) + uint32_t(p.epi.out.outZp));
+                    }
+                    y[e] = r;
+                }
+                // saturate to int8, then the (narrower) RESCALE/CLAMP range on the four packed bytes
+                packed[q] = __vmins4(__vmaxs4(packSat4(y[0], y[1], y[2], y[3]), lo4), hi4);
+            }
+            if (vec) {
+                *reinterpret_cast<int4 *>(dst) = make_int4(int(packed[0]), int(packed[1]), int(packed[2]), int(packed[3]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (j < ncols) {
+                        dst[j] = int8_t(packed[j >> 2] >> (8 * (j & 3)));
+                    }
+                }
+            }
+        }
+    }
+}
+
+// int32 output: accumulator + correction, no RESCALE.
+template <int BN, int NSTAGE>
+__device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarriers *bars, uint32_t tmemBase, int warp,
+                                              int lane, int64_t numTiles, int mTiles, int nTiles) {
+    const int quarter = warp & 3;
+    const int half = warp >> 2;
+    constexpr int kColsPerWarp = BN / 2;
+    constexpr int kSteps = kColsPerWarp / 16;
+    const int row = quarter * 32 + lane;
+    uint32_t tileCount = 0;
+    for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
+        int64_t tt = t;
+        const int n0 = int(tt % nTiles) * BN;
+        tt /= nTiles;
+        const int m0 = int(tt % mTiles) * BM;
+        const int batch = int(tt / mTiles);
+        const uint32_t buf = tileCount & 1u;
+        const int64_t m = int64_t(m0) + row;
+        const bool rowValid = m < p.M;
+        const int32_t *corr = p.corr;
+        if (corr != nullptr) {
+            int cls = 0;
+            if (p.rowClass != nullptr && rowValid) {
+                const int rem = int(m % (int64_t(p.OH) * p.OW));
+                cls = int(__ldg(p.rowClass + rem / p.OW)) * p.numColClasses + int(__ldg(p.colClass + rem % p.OW));
+            }
+            corr += (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0) + int64_t(cls) * p.N;
+        }
+        const int64_t outRow = (int64_t(batch) * p.M + m) * p.ldOut;
+        if (!mbarWait(&bars->accFull[buf], (tileCount >> 1) & 1u, 4)) {
+            break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmemBase + buf * uint32_t(BN) + (uint32_t(quarter * 32) << 16);
+#pragma unroll 1
+        for (int st = 0; st < kSteps; ++st) {
+            const int cl = half * kColsPerWarp + st * 16;
+            uint32_t acc[16];
+            tmemLoad16(taddr + uint32_t(cl), acc);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (st == kSteps - 1) {
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                if (lane == 0) {
+                    mbarArrive(&bars->accEmpty[buf]);
+                }
+            }
+            const int col0 = n0 + cl;
+            if (!rowValid || col0 >= p.N) {
+                continue;
+            }
+            const int ncols = min(16, p.N - col0);
+            int32_t *dst = p.out32 + outRow + col0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (corr != nullptr && j < ncols) {
+                    acc[j] += uint32_t(__ldg(corr + col0 + j));
+                }
+            }
+            if (ncols == 16 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    reinterpret_cast<int4 *>(dst)[q] =
+                        make_int4(int(acc[4 * q]), int(acc[4 * q + 1]), int(acc[4 * q + 2]), int(acc[4 * q + 3]));
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (j < ncols) {
+                        dst[j] = int32_t(acc[j]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <int BN, int NSTAGE>
+__device__ __forceinline__ void epilogueWarps(const GemmI8Params &p, PipeBarriers *bars, ColConst *colTab,
+                                              uint32_t tmemBase, int warp, int lane, int64_t numTiles, int mTiles,
+                                              int nTiles) {
+    if (p.out32 != nullptr) {
+        epilogueInt32<BN, NSTAGE>(p, bars, tmemBase, warp, lane, numTiles, mTiles, nTiles);
+    } else if (p.epi.hasResidual) {
+        epilogueInt8<BN, NSTAGE, true>(p, bars, colTab, tmemBase, warp, lane, numTiles, mTiles, nTiles);
+    } else {
+        epilogueInt8<BN, NSTAGE, false>(p, bars, colTab, tmemBase, warp, lane, numTiles, mTiles, nTiles);
+    }
+}
 
 // A_TMA: A comes through tmapA; otherwise it is gathered from the NHWC input described by p.
 // B_MN : B is an N-contiguous [K][N] matrix (MN-major operand), otherwise a K-contiguous [N][K] matrix.
@@ -341,162 +599,7 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
         }
     } else {
         // ---------------- epilogue: warps 0-7 ----------------
-        const int quarter = warp & 3;           // TMEM lanes [32 * quarter, 32 * quarter + 32)
-        const int half = warp >> 2;             // which half of the tile's columns
-        constexpr int kChunks = BN / 64;        // 32-column chunks per warp
-        const int row = quarter * 32 + lane;
-        // Per-tensor stages of the residual tail: uniform constants, kept in registers.
-        FastRescale fa{}, fb{}, fo{};
-        if (p.out8 != nullptr && p.epi.hasResidual) {
-            fa = makeFastRescale(__ldg(p.epi.a.mult), int32_t(__ldg(p.epi.a.shift)), p.epi.a.inZp, p.epi.a.doubleRound != 0);
-            fb = makeFastRescale(__ldg(p.epi.b.mult), int32_t(__ldg(p.epi.b.shift)), p.epi.b.inZp, p.epi.b.doubleRound != 0);
-            fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
-                                 p.epi.out.doubleRound != 0);
-        }
-        const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp, loMain = p.epi.main.lo,
-                      hiMain = p.epi.main.hi;
-        uint32_t tileCount = 0;
-        int tabN0 = -1; // column origin the shared constants table was built for
-        bool ok = true;
-        for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileCount) {
-            const TileCoord tc = tileOf(t);
-            const uint32_t buf = tileCount & 1u;
-            // Per-column constants of the main RESCALE stage, shared by the 128 rows of the tile.
-            if (p.out8 != nullptr && tc.n0 != tabN0) {
-                epilogueSync(); // everyone is done with the previous table
-                if (threadIdx.x < BN) {
-                    const int col = tc.n0 + int(threadIdx.x);
-                    const int ci = (p.epi.main.perChannel && col < p.N) ? col : 0;
-                    const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
-                                                          zpMain, p.epi.main.doubleRound != 0);
-                    ColConst c;
-                    c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi, c.rnLo = f.rnLo, c.rnHi = f.rnHi;
-                    c.s1 = f.s1, c.s2 = f.s2, c.pad = 0;
-                    colTab[threadIdx.x] = c;
-                }
-                epilogueSync();
-                tabN0 = tc.n0;
-            }
-            const int64_t m = int64_t(tc.m0) + row;
-            const bool rowValid = m < p.M;
-            // zero-point / bias correction row of this pixel's border class
-            const int32_t *corr = p.corr;
-            if (corr != nullptr) {
-                int cls = 0;
-                if (p.rowClass != nullptr && rowValid) {
-                    const int rem = int(m % (int64_t(p.OH) * p.OW));
-                    cls = int(__ldg(p.rowClass + rem / p.OW)) * p.numColClasses + int(__ldg(p.colClass + rem % p.OW));
-                }
-                corr += (p.batchedCorr ? int64_t(tc.batch) * p.numClasses * p.N : 0) + int64_t(cls) * p.N;
-            }
-            const int64_t outRow = (int64_t(tc.batch) * p.M + m) * p.ldOut;
-
-            ok = mbarWait(&bars->accFull[buf], (tileCount >> 1) & 1u, 4);
-            if (!ok) {
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t taddr = tmemBase + buf * uint32_t(BN) + (uint32_t(quarter * 32) << 16);
-#pragma unroll 1
-            for (int ch = 0; ch < kChunks; ++ch) {
-                const int cb = half * kChunks + ch;
-                uint32_t acc[32];
-                tmemLoad32(taddr + uint32_t(cb * 32), acc);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (ch == kChunks - 1) {
-                    // this warp's part of the accumulator is in registers: hand the buffer back to the MMA warp
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    if (lane == 0) {
-                        mbarArrive(&bars->accEmpty[buf]);
-                    }
-                }
-                const int col0 = tc.n0 + cb * 32;
-                if (!rowValid || col0 >= p.N) {
-                    continue;
-                }
-                const int ncols = min(32, p.N - col0);
-                // + zero-point / bias correction (32-bit wrap, like the reference's int32 accumulator)
-                if (corr != nullptr) {
-                    if (ncols == 32) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const int4 c4 = __ldg(reinterpret_cast<const int4 *>(corr + col0) + q);
-                            acc[4 * q + 0] += uint32_t(c4.x), acc[4 * q + 1] += uint32_t(c4.y);
-                            acc[4 * q + 2] += uint32_t(c4.z), acc[4 * q + 3] += uint32_t(c4.w);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            acc[j] += j < ncols ? uint32_t(__ldg(corr + col0 + j)) : 0u;
-                        }
-                    }
-                }
-                if (p.out32 != nullptr) {
-                    int32_t *dst = p.out32 + outRow + col0;
-                    if (ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            reinterpret_cast<int4 *>(dst)[q] =
-                                make_int4(int(acc[4 * q]), int(acc[4 * q + 1]), int(acc[4 * q + 2]), int(acc[4 * q + 3]));
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < ncols) {
-                                dst[j] = int32_t(acc[j]);
-                            }
-                        }
-                    }
-                    continue;
-                }
-                int8_t *dst = p.out8 + outRow + col0;
-                const bool vec = ncols == 32 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
-                uint32_t sc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; // 32 shortcut bytes of this row
-                if (p.epi.hasResidual) {
-                    const int8_t *scp = p.epi.shortcut + outRow + col0;
-                    if (vec) {
-                        const int4 s0 = __ldg(reinterpret_cast<const int4 *>(scp));
-                        const int4 s1 = __ldg(reinterpret_cast<const int4 *>(scp) + 1);
-                        sc[0] = uint32_t(s0.x), sc[1] = uint32_t(s0.y), sc[2] = uint32_t(s0.z), sc[3] = uint32_t(s0.w);
-                        sc[4] = uint32_t(s1.x), sc[5] = uint32_t(s1.y), sc[6] = uint32_t(s1.z), sc[7] = uint32_t(s1.w);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (j < ncols) {
-                                sc[j >> 2] |= uint32_t(uint8_t(scp[j])) << (8 * (j & 3));
-                            }
-                        }
-                    }
-                }
-                uint32_t packed[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const ColConst c = colTab[cb * 32 + j];
-                    int32_t y = fastScale(int32_t(acc[j]), c.mult, zpMain, c.rpLo, c.rpHi, c.rnLo, c.rnHi, c.s1, c.s2);
-                    y = int32_t(uint32_t(y) + uint32_t(outZpMain));
-                    y = min(max(y, loMain), hiMain);
-                    if (p.epi.hasResidual) {
-                        const int32_t ta = fastRescale(fa, y, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
-                        const int32_t sv = int32_t(int8_t(sc[j >> 2] >> (8 * (j & 3))));
-                        const int32_t tb = fastRescale(fb, sv, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
-                        y = fastRescale(fo, int32_t(uint32_t(ta) + uint32_t(tb)), p.epi.out.outZp, p.epi.out.lo,
-                                        p.epi.out.hi);
-                    }
-                    packed[j >> 2] |= uint32_t(uint8_t(y)) << (8 * (j & 3));
-                }
-                if (vec) {
-                    reinterpret_cast<int4 *>(dst)[0] = make_int4(int(packed[0]), int(packed[1]), int(packed[2]), int(packed[3]));
-                    reinterpret_cast<int4 *>(dst)[1] = make_int4(int(packed[4]), int(packed[5]), int(packed[6]), int(packed[7]));
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (j < ncols) {
-                            dst[j] = int8_t(packed[j >> 2] >> (8 * (j & 3)));
-                        }
-                    }
-                }
-            }
-        }
+        epilogueWarps<BN, NSTAGE>(p, bars, colTab, tmemBase, warp, lane, numTiles, mTiles, nTiles);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

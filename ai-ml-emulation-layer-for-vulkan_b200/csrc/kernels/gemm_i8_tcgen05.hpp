@@ -24,6 +24,7 @@ struct GemmI8Params {
     const uint8_t *rowClass; // [OH] border class of an output row, or null (single class)
     const uint8_t *colClass; // [OW]
     int32_t numColClasses, numClasses, batchedCorr;
+    int32_t baseClass;       // the most common class: its correction row is staged in shared memory
     // outputs: exactly one of out32 / out8 is set
     int32_t *out32;
     int8_t *out8;

@@ -107,6 +107,7 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     p.colClass = reinterpret_cast<const uint8_t *>(T[op.aux[2]].ptr);
     p.numColClasses = op.auxi[0];
     p.numClasses = op.auxi[1];
+    p.baseClass = op.auxi[3];
     if (op.kind == OP_FUSED_CONV2D) {
         p.out8 = reinterpret_cast<int8_t *>(out.ptr);
         p.epi = devEpilogue(op.epi, T);
