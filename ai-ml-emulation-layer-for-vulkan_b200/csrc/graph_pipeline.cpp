@@ -692,6 +692,50 @@ void GraphPipeline::fuse() {
             fused.push_back(std::move(g));
         }
     }
+    // Residual tail into the producing convolution: when one operand of a fused add is the (otherwise
+    // unused) output of a fused CONV2D, the add and its three RESCALEs run in that convolution's epilogue
+    // on the value still in registers; the other operand (the shortcut) is read there.  The merged node
+    // runs where the add would have run, so the shortcut is complete by then.
+    std::vector<bool> dead(fused.size(), false);
+    for (size_t ga = 0; ga < fused.size(); ++ga) {
+        Group &add = fused[ga];
+        if (add.node.kind != OP_FUSED_ADD) {
+            continue;
+        }
+        for (int side = 0; side < 2; ++side) {
+            const int32_t mainT = add.node.in[size_t(side)], shortT = add.node.in[size_t(1 - side)];
+            const int prod = producer[size_t(mainT)];
+            if (prod < 0 || group[size_t(prod)] < 0) {
+                continue;
+            }
+            const size_t gc = size_t(group[size_t(prod)]);
+            Group &conv = fused[gc];
+            if (dead[gc] || conv.node.kind != OP_FUSED_CONV2D || conv.node.epi.hasResidual ||
+                conv.node.out[0] != mainT || mainT == shortT) {
+                continue;
+            }
+            // the convolution's own output must feed nothing but this add's RESCALE
+            const int consumer = soleConsumer(mainT);
+            if (consumer < 0 || group[size_t(consumer)] != int(ga) || !tensor(shortT).packed() ||
+                tensor(shortT).dims != tensor(mainT).dims) {
+                continue;
+            }
+            conv.node.epi.hasResidual = true;
+            conv.node.epi.a = side == 0 ? add.node.epi.a : add.node.epi.b;
+            conv.node.epi.b = side == 0 ? add.node.epi.b : add.node.epi.a;
+            conv.node.epi.out = add.node.epi.out;
+            conv.node.epi.shortcutTensor = shortT;
+            conv.node.out = add.node.out;
+            conv.node.name += add.node.name.find("+CLAMP") != std::string::npos ? "+ADD+RESCALE+CLAMP" : "+ADD+RESCALE";
+            for (int opIndex : add.node.fusedOps) {
+                group[size_t(opIndex)] = int(gc);
+                conv.node.fusedOps.push_back(opIndex);
+            }
+            conv.last = std::max(conv.last, add.last);
+            dead[ga] = true;
+            break;
+        }
+    }
     // The two input RESCALEs of a fused add come before the ADD in op order, possibly far before;
     // moving them to the ADD's position is legal because their inputs are written exactly once.
     // A fused node is emitted at the position of its last absorbed operator.

@@ -32,6 +32,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 
 #include "device_common.cuh"
@@ -725,6 +726,15 @@ int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
     if (bn == 64) {
         return aTma ? launchVariant<64, 8, true, false>(mapA, mapB, p, s)
                     : launchVariant<64, 8, false, false>(mapA, mapB, p, s);
+    }
+    static const char *dbg = getenv("MLEL_DBG_STAGES");
+    if (dbg != nullptr && dbg[0] == '2') {
+        return aTma ? launchVariant<128, 2, true, false>(mapA, mapB, p, s)
+                    : launchVariant<128, 2, false, false>(mapA, mapB, p, s);
+    }
+    if (dbg != nullptr && dbg[0] == '4') {
+        return aTma ? launchVariant<128, 4, true, false>(mapA, mapB, p, s)
+                    : launchVariant<128, 4, false, false>(mapA, mapB, p, s);
     }
     return aTma ? launchVariant<128, 6, true, false>(mapA, mapB, p, s)
                 : launchVariant<128, 6, false, false>(mapA, mapB, p, s);

@@ -111,7 +111,9 @@ def test_emitted_resnet_lowers_and_fuses(mlel):
     unfused_mem = mlel.Session(p).memory_requirements()[0]
     pf = lower(mlel, g.spvasm(), ext, consts)
     names = pf.exec_names()
-    assert names.count("CONV2D+RESCALE+CLAMP") + names.count("CONV2D+RESCALE") == sum(o.name == "CONV2D" for o in g.ops)
+    assert sum(n.startswith("CONV2D+RESCALE") for n in names) == sum(o.name == "CONV2D" for o in g.ops)
+    # every residual add runs in the epilogue of the convolution that produces its main operand
+    assert sum("+ADD+RESCALE" in n for n in names) == sum(o.name == "ADD" for o in g.ops)
     assert "RESCALE" not in names and "ADD" not in names and "CLAMP" not in names
     assert names[-1] == "MATMUL+RESCALE"
     assert 0 < mlel.Session(pf).memory_requirements()[0] < unfused_mem
