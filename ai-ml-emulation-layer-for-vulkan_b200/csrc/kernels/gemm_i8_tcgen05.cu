@@ -47,12 +47,12 @@ namespace {
 constexpr int BM = 128;    // rows per tile (UMMA M)
 constexpr int BK = 128;    // bytes (= int8 elements) of K per pipeline stage
 constexpr int UMMA_K = 32; // K per tcgen05.mma for 8-bit operands
-constexpr int kEpilogueWarps = 8;
-constexpr int kTmaWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kGatherWarp0 = 10;
-constexpr int kThreadsTma = 320;    // warps 0-9
-constexpr int kThreadsGather = 448; // warps 0-13
+constexpr int kEpilogueWarps = 16;
+constexpr int kTmaWarp = kEpilogueWarps;
+constexpr int kMmaWarp = kEpilogueWarps + 1;
+constexpr int kGatherWarp0 = kEpilogueWarps + 2;
+constexpr int kThreadsTma = (kEpilogueWarps + 2) * 32;
+constexpr int kThreadsGather = (kEpilogueWarps + 6) * 32;
 constexpr long long kWaitLimitCycles = 4000000000ll;
 
 __device__ __forceinline__ uint32_t smemAddr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -76,13 +76,16 @@ __device__ __forceinline__ bool mbarTryWait(uint64_t *bar, uint32_t parity) {
                  : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false (and records `code`) when the barrier did not complete in time.
-__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int code) {
+// Bounded wait: returns false (and records `code`) when the barrier did not complete in time.  Between
+// polls the waiter sleeps `sleepNs` so that a waiting role does not take issue slots from the warps that
+// share its scheduler (the epilogue warps do the arithmetic).
+__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int code, unsigned sleepNs = 32) {
     if (mbarTryWait(bar, parity)) {
         return true;
     }
     const long long start = clock64();
     while (!mbarTryWait(bar, parity)) {
+        __nanosleep(sleepNs);
         if (clock64() - start > kWaitLimitCycles) {
             atomicCAS(&g_tcgen05Error, 0, code);
             return false;
@@ -156,11 +159,12 @@ struct __align__(8) PipeBarriers {
 };
 
 // Constants of the main RESCALE stage for one output column (see FastRescale).
+// One 16-byte shared-memory read per element: the rounding constant for negative inputs is the positive
+// one minus 2^31 (double rounding) or the same (single rounding), so it is derived, not stored.
 struct __align__(16) ColConst {
     int32_t mult;
-    uint32_t rpLo, rpHi, rnLo, rnHi;
-    int32_t s1, s2;
-    int32_t corr0; // correction of the most common border class for this column
+    uint32_t rpLo, rpHi; // rounding constant for v >= zpIn (input zero point folded in)
+    int32_t corr0;       // correction of the most common border class for this column
 };
 
 struct TileCoord {
@@ -176,15 +180,12 @@ __device__ __forceinline__ void tmemLoad16(uint32_t taddr, uint32_t (&r)[16]) {
                  : "memory");
 }
 
-// Saturates four int32 values to int8 and packs them, e0 in the lowest byte.
-__device__ __forceinline__ uint32_t packSat4(int32_t e0, int32_t e1, int32_t e2, int32_t e3) {
-    uint32_t hi, d;
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(e3), "r"(e2), "r"(0));
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(e1), "r"(e0), "r"(hi));
-    return d;
+// Packs the low bytes of four int32 values, e0 in the lowest byte (values are already clamped to int8).
+__device__ __forceinline__ uint32_t pack4(int32_t e0, int32_t e1, int32_t e2, int32_t e3) {
+    const uint32_t lo = __byte_perm(uint32_t(e0), uint32_t(e1), 0x0040);
+    const uint32_t hi = __byte_perm(uint32_t(e2), uint32_t(e3), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
 }
-
-__device__ __forceinline__ uint32_t replicate4(int32_t v) { return uint32_t(uint8_t(v)) * 0x01010101u; }
 
 // The epilogue of the persistent kernel (warps 0-7).  Each warp owns 32 TMEM lanes (tile rows) and half of
 // the tile's columns, which it walks in 16-column steps: one tcgen05.ld, 16 RESCALEs, one 16-byte store.
@@ -194,7 +195,7 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                                              int nTiles) {
     const int quarter = warp & 3; // TMEM lanes [32 * quarter, 32 * quarter + 32)
     const int half = warp >> 2;   // which half of the tile's columns
-    constexpr int kColsPerWarp = BN / 2;
+    constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
     constexpr int kSteps = kColsPerWarp / 16;
     const int row = quarter * 32 + lane;
     FastRescale fa{}, fb{}, fo{};
@@ -205,8 +206,7 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                              p.epi.out.doubleRound != 0);
     }
     const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp;
-    const uint32_t lo4 = replicate4(RESIDUAL ? p.epi.out.lo : p.epi.main.lo);
-    const uint32_t hi4 = replicate4(RESIDUAL ? p.epi.out.hi : p.epi.main.hi);
+    uint32_t *shiftTab = reinterpret_cast<uint32_t *>(colTab + BN);
     const int32_t loMain = p.epi.main.lo, hiMain = p.epi.main.hi;
     uint32_t tileCount = 0;
     int tabN0 = -1, tabBatch = -1; // what the shared constants table was built for
@@ -228,10 +228,13 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                 const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
                                                       zpMain, p.epi.main.doubleRound != 0);
                 ColConst c;
-                c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi, c.rnLo = f.rnLo, c.rnHi = f.rnHi;
-                c.s1 = f.s1, c.s2 = f.s2;
+                c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi;
                 c.corr0 = col < p.N ? __ldg(corrBatch + int64_t(p.baseClass) * p.N + col) : 0;
                 colTab[threadIdx.x] = c;
+                // bits 0-5: min(shift, 32); bits 8-12: max(shift - 32, 0); bit 31: the two rounding
+                // constants differ (double rounding with shift > 31)
+                const bool twoRounds = f.rpLo != f.rnLo || f.rpHi != f.rnHi;
+                shiftTab[threadIdx.x] = uint32_t(f.s1) | (uint32_t(f.s2) << 8) | (twoRounds ? 0x80000000u : 0u);
             }
             epilogueSync();
             tabN0 = n0;
@@ -304,22 +307,28 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                 for (int e = 0; e < 4; ++e) {
                     const int j = 4 * q + e;
                     const ColConst c = colTab[cl + j];
+                    const uint32_t sh = shiftTab[cl + j];
                     const int32_t v = int32_t(acc[j] + uint32_t(c.corr0));
-                    int32_t r = fastScale(v, c.mult, zpMain, c.rpLo, c.rpHi, c.rnLo, c.rnHi, c.s1, c.s2);
+                    uint64_t round = (uint64_t(c.rpHi) << 32) | uint64_t(c.rpLo);
+                    if (v < zpMain) {
+                        round -= uint64_t(sh >> 31) << 31; // double rounding: -2^30 instead of +2^30
+                    }
+                    uint64_t sum;
+                    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(sum) : "r"(v), "r"(c.mult), "l"(round));
+                    const uint32_t tq = __funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), sh & 63u);
+                    int32_t r = int32_t(tq) >> ((sh >> 8) & 31u);
                     r = int32_t(uint32_t(r) + uint32_t(outZpMain));
+                    r = min(max(r, loMain), hiMain);
                     if (RESIDUAL) {
-                        r = min(max(r, loMain), hiMain);
                         const int32_t ta = fastRescale(fa, r, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
                         const int32_t sv = int32_t(int8_t(sc[q] >> (8 * e)));
                         const int32_t tb = fastRescale(fb, sv, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
-                        const int32_t sum = int32_t(uint32_t(ta) + uint32_t(tb));
-                        r = fastScale(sum, fo.mult, fo.zpIn, fo.rpLo, fo.rpHi, fo.rnLo, fo.rnHi, fo.s1, fo.s2);
-                        r = int32_t(uint32_t(r) + uint32_t(p.epi.out.outZp));
+                        r = fastRescale(fo, int32_t(uint32_t(ta) + uint32_t(tb)), p.epi.out.outZp, p.epi.out.lo,
+                                        p.epi.out.hi);
                     }
                     y[e] = r;
                 }
-                // saturate to int8, then the (narrower) RESCALE/CLAMP range on the four packed bytes
-                packed[q] = __vmins4(__vmaxs4(packSat4(y[0], y[1], y[2], y[3]), lo4), hi4);
+                packed[q] = pack4(y[0], y[1], y[2], y[3]);
             }
             if (vec) {
                 *reinterpret_cast<int4 *>(dst) = make_int4(int(packed[0]), int(packed[1]), int(packed[2]), int(packed[3]));
@@ -341,7 +350,7 @@ __device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarrier
                                               int lane, int64_t numTiles, int mTiles, int nTiles) {
     const int quarter = warp & 3;
     const int half = warp >> 2;
-    constexpr int kColsPerWarp = BN / 2;
+    constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
     constexpr int kSteps = kColsPerWarp / 16;
     const int row = quarter * 32 + lane;
     uint32_t tileCount = 0;
@@ -437,7 +446,7 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     uint8_t *tilesA = smem;
     uint8_t *tilesB = smem + NSTAGE * kTileA;
     ColConst *colTab = reinterpret_cast<ColConst *>(smem + NSTAGE * (kTileA + kTileB));
-    PipeBarriers *bars = reinterpret_cast<PipeBarriers *>(smem + NSTAGE * (kTileA + kTileB) + BN * sizeof(ColConst));
+    PipeBarriers *bars = reinterpret_cast<PipeBarriers *>(smem + NSTAGE * (kTileA + kTileB) + BN * (sizeof(ColConst) + 4));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -669,7 +678,7 @@ int smCount() {
 template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
 int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes =
-        size_t(NSTAGE) * (BM * BK + BN * BK) + BN * sizeof(ColConst) + sizeof(PipeBarriers) + 1024;
+        size_t(NSTAGE) * (BM * BK + BN * BK) + BN * (sizeof(ColConst) + 4) + sizeof(PipeBarriers) + 1024;
     auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_TMA, B_MN>;
     static bool configured = false;
     if (!configured) {
