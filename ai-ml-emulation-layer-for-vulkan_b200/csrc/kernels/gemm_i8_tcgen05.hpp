@@ -47,6 +47,12 @@ struct GemmI8Problem {
 // 16-byte aligned with row pitches that are multiples of 16 bytes.
 int gemmI8Launch(const GemmI8Problem &problem, cudaStream_t stream);
 
+// Channel-major variant (gemm_i8_ocmajor.cu) for fused int8 convolutions with more than 64 output channels:
+// same problem description, weights as the tensor-core A operand.  `Applies` tells whether it can take q.
+bool gemmI8OcMajorApplies(const GemmI8Problem &problem);
+int gemmI8OcMajorLaunch(const GemmI8Problem &problem, cudaStream_t stream);
+int ocMajorErrorWord();
+
 // Value of the device-side error word written by a bounded wait that ran out (0 = none).
 int tcgen05ErrorFlag();
 

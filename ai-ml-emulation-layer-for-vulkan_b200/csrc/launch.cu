@@ -108,6 +108,10 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     p.numColClasses = op.auxi[0];
     p.numClasses = op.auxi[1];
     p.baseClass = op.auxi[3];
+    if (p.numClasses <= 1) {
+        p.rowClass = p.colClass = nullptr; // no window crosses the border: one correction row serves every pixel
+        p.baseClass = 0;
+    }
     if (op.kind == OP_FUSED_CONV2D) {
         p.out8 = reinterpret_cast<int8_t *>(out.ptr);
         p.epi = devEpilogue(op.epi, T);
@@ -145,7 +149,7 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     q.bRowBytes = uint64_t(p.K);
     q.bBatchBytes = 0;
     q.bMnMajor = false;
-    return gemmI8Launch(q, s);
+    return gemmI8OcMajorApplies(q) ? gemmI8OcMajorLaunch(q, s) : gemmI8Launch(q, s);
 }
 
 // MATMUL / fused MATMUL with a constant, pre-transposed second input.

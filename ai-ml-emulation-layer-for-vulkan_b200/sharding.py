@@ -1,0 +1,67 @@
+"""Batch sharding of a data-graph dispatch over ranks (one process per GPU).
+
+A TOSA data graph of the kind this library runs treats the images of a batch independently: every
+operator on the path is per-pixel, per-window or per-row of one image, so a batch of B images can be
+cut into contiguous shards, each rank dispatches its own shard through its own pipeline and session,
+and no tensor crosses ranks while the graph runs.  The only exchange is the all-gather of the graph's
+outputs (the logits) at the end, and only when the caller wants the whole batch on every rank.
+
+The reference has no multi-device path (one VkDevice per graph pipeline, graph/graph_layer.cpp:853-1003);
+this module is the host-side logic a data-parallel host needs on top of the C ABI.  It uses
+``torch.distributed`` with whatever backend the process group was created with (NCCL on GPUs, gloo in the
+CPU tests).
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def shard_range(total: int, world: int, rank: int) -> Tuple[int, int]:
+    """``(first, count)`` of the contiguous shard of ``total`` items owned by ``rank``.
+
+    Shards differ by at most one item; the first ``total % world`` ranks hold the larger ones.  Ranks past
+    the end of a batch smaller than the world get an empty shard.
+    """
+    if world <= 0 or not 0 <= rank < world or total < 0:
+        raise ValueError(f"bad shard request: total={total} world={world} rank={rank}")
+    base, extra = divmod(total, world)
+    first = rank * base + min(rank, extra)
+    return first, base + (1 if rank < extra else 0)
+
+
+def shard_arrays(arrays: Sequence[np.ndarray], world: int, rank: int) -> List[np.ndarray]:
+    """The rank's slice along axis 0 (the batch axis) of every graph input."""
+    out = []
+    for a in arrays:
+        first, count = shard_range(a.shape[0], world, rank)
+        out.append(np.ascontiguousarray(a[first:first + count]))
+    return out
+
+
+def all_gather_batch(local: torch.Tensor, total: int, group=None) -> torch.Tensor:
+    """Concatenates every rank's output shard along axis 0 and returns the whole batch on every rank.
+
+    ``local`` is this rank's ``[count, ...]`` output, ``total`` the batch size that ``shard_range`` cut.
+    Shards of equal size go through one ``all_gather_into_tensor``; uneven shards are padded to the largest
+    one for the exchange and trimmed afterwards.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    first, count = shard_range(total, world, rank)
+    if local.shape[0] != count:
+        raise ValueError(f"rank {rank} holds {local.shape[0]} items, its shard of {total} has {count}")
+    biggest = shard_range(total, world, 0)[1]
+    tail = tuple(local.shape[1:])
+    if total % world == 0:
+        out = torch.empty((total,) + tail, dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+        return out
+    padded = torch.zeros((biggest,) + tail, dtype=local.dtype, device=local.device)
+    padded[:count] = local
+    pieces = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(pieces, padded, group=group)
+    return torch.cat([pieces[r][:shard_range(total, world, r)[1]] for r in range(world)], dim=0)

@@ -42,6 +42,13 @@ CONV_CASES = [
     (1, 56, 56, 64, 64, 3, 1, 1, 1, -3, 0),   # configuration 0
     (3, 28, 28, 32, 48, 3, 1, 2, 1, 11, 0),
     (1, 5, 5, 128, 256, 1, 0, 2, 1, -7, 0),
+    # more than 64 output channels: channel count not a multiple of the 128-channel tile, pixel counts that
+    # end inside a tile, border classes, and layers large enough for the 256-pixel tiles
+    (1, 20, 20, 32, 200, 3, 1, 1, 1, -5, 0),
+    (2, 30, 30, 64, 136, 3, 1, 1, 1, 9, 0),
+    (4, 17, 17, 128, 130, 1, 0, 1, 1, -11, 0),
+    (8, 56, 56, 32, 128, 1, 0, 1, 1, 6, 0),
+    (8, 40, 40, 16, 192, 3, 1, 1, 1, 3, 0),
 ]
 
 
