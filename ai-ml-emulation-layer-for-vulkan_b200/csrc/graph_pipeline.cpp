@@ -813,12 +813,21 @@ void GraphPipeline::prepareTensorCore() {
             if (sy <= 0 || sx <= 0 || dy <= 0 || dx <= 0) {
                 continue;
             }
-            // Channel counts that are not multiples of 16 (an RGB stem) cannot be gathered in 16-byte pieces:
-            // such a convolution first materialises its im2col matrix [pixels][kPad] in session memory and
-            // then runs as a plain matrix product against zero-padded weights (tc == 2).
-            const bool viaIm2col = IC % 16 != 0;
-            const int64_t kPad = (KH * KW * IC + 15) / 16 * 16;
-            if (in.dims[3] != IC || out.dims[3] != OC || OC % 16 != 0 || KH * KW * IC > 65536 ||
+            // Channel counts that are not multiples of 16 (an RGB stem) cannot be gathered in 16-byte pieces
+            // from the tensor itself.  Such a convolution (tc == 2) first copies its input into session memory
+            // with the channels zero-padded to 4, 8 or a multiple of 16 and the padding border materialised as
+            // zeros, and then gathers from the copy, where every tap is in range, by a table of byte offsets.
+            // Where the window's rows are contiguous and suitably aligned in the copy (unit x dilation, x stride
+            // times padded channels a multiple of 8 bytes) one piece is 8 or 16 bytes of a window row, and each
+            // window row is padded to whole pieces in the K order (with zero weights); otherwise one piece is
+            // one tap (or 16 bytes of one).
+            const bool padChannels = IC % 16 != 0;
+            const int64_t ICp = !padChannels ? IC : (IC <= 4 ? 4 : (IC <= 8 ? 8 : (IC + 15) / 16 * 16));
+            const bool rowRuns = padChannels && dx == 1 && ICp < 16 && (sx * ICp) % 8 == 0;
+            const int64_t piece = !padChannels ? 16 : (rowRuns ? ((sx * ICp) % 16 == 0 ? 16 : 8) : std::min<int64_t>(ICp, 16));
+            const int64_t runBytes = rowRuns ? (KW * ICp + piece - 1) / piece * piece : KW * ICp; // K bytes per window row
+            const int64_t kPad = (KH * runBytes + 15) / 16 * 16;
+            if (in.dims[3] != IC || out.dims[3] != OC || OC % 16 != 0 || kPad > 65536 ||
                 (b.dims[0] != OC && b.dims[0] != 1) || out.numel() >= (int64_t(1) << 31) ||
                 in.numel() >= (int64_t(1) << 31)) {
                 continue;
@@ -907,19 +916,39 @@ void GraphPipeline::prepareTensorCore() {
                 op.auxi[3] = int32_t(rBest * colMasks.size() + cBest);
             }
             op.tc = 1;
-            if (viaIm2col) {
-                const int64_t M = out.dims[0] * OH * OW, K = KH * KW * IC;
-                if (M * kPad >= (int64_t(1) << 32)) {
+            if (padChannels) {
+                // geometry of the padded copy: rows and columns that any window can touch
+                const int64_t Hp = std::max<int64_t>(H + padTop, (OH - 1) * sy + (KH - 1) * dy + 1);
+                const int64_t xReach = rowRuns ? runBytes / ICp : (KW - 1) * dx + 1;
+                const int64_t Wp = std::max<int64_t>(W + padLeft, (OW - 1) * sx + xReach);
+                const int64_t numChunks = (kPad + 127) / 128 * 128 / piece;
+                if (in.dims[0] * Hp * Wp * ICp >= (int64_t(1) << 31) || numChunks > 1024) {
                     op.tc = 0;
                     continue;
                 }
                 std::vector<int8_t> wPad(size_t(OC * kPad), 0);
                 for (int64_t oc = 0; oc < OC; ++oc) {
-                    std::memcpy(&wPad[size_t(oc * kPad)], wd + oc * K, size_t(K));
+                    for (int64_t ky = 0; ky < KH; ++ky) {
+                        for (int64_t kx = 0; kx < KW; ++kx) {
+                            std::memcpy(&wPad[size_t(oc * kPad + ky * runBytes + kx * ICp)],
+                                        wd + ((oc * KH + ky) * KW + kx) * IC, size_t(IC));
+                        }
+                    }
+                }
+                std::vector<int32_t> table(size_t(numChunks), 0); // pieces past the window read offset 0 (weights 0)
+                for (int64_t q = 0; q < numChunks; ++q) {
+                    const int64_t k = q * piece;
+                    if (k >= KH * runBytes) {
+                        continue;
+                    }
+                    const int64_t ky = k / runBytes, r = k % runBytes;
+                    const int64_t xBytes = rowRuns ? r : (r / ICp) * dx * ICp + r % ICp;
+                    table[size_t(q)] = int32_t(ky * dy * Wp * ICp + xBytes);
                 }
                 op.aux[3] = addDerivedConstant(MLEL_I8, {OC, kPad}, wPad.data());
-                op.scratch = addScratchTensor(MLEL_I8, {M, kPad});
-                op.auxi[2] = int32_t(kPad);
+                op.aux[4] = addDerivedConstant(MLEL_I32, {numChunks}, table.data());
+                op.scratch = addScratchTensor(MLEL_I8, {in.dims[0], Hp, Wp, ICp});
+                op.auxi[2] = int32_t(piece);
                 op.tc = 2;
             }
         } else {

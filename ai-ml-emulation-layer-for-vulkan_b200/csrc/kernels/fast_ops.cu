@@ -7,51 +7,31 @@ namespace mlel {
 
 namespace {
 
-// ---- im2col for convolutions whose channel count is not a multiple of 16 (e.g. an RGB stem) ---------
-// Writes A'[m][k], m = output pixel, k = (ky, kx, ic) flattened and zero-padded to kPad (a multiple of
-// 16), out-of-range taps as zeros (the tensor-core kernel's border-class correction assumes exactly
-// that).  One warp owns one pixel at a time: lane l produces the 32-bit words l, l+32, ... of the row,
-// so a row is written with coalesced 128-byte stores while the byte gathers hit L1.
-__global__ void im2colSmallIcKernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int64_t M, int H, int W,
-                                    int IC, int OH, int OW, int KH, int KW, int strideY, int strideX, int padTop,
-                                    int padLeft, int dilY, int dilX, int K, int kPad) {
-    const int lane = threadIdx.x & 31;
-    const int64_t warpId = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const int64_t numWarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
-    const int words = kPad >> 2;
-    for (int w0 = 0; w0 < words; w0 += 32) {
-        const int w = w0 + lane;
-        // tap decomposition of this lane's four bytes: fixed for every pixel
-        int dy[4], dx[4], ci[4];
-        bool inK[4];
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const int k = 4 * w + b;
-            inK[b] = w < words && k < K;
-            const int tap = inK[b] ? k / IC : 0;
-            ci[b] = inK[b] ? k - tap * IC : 0;
-            const int ky = tap / KW;
-            dy[b] = ky * dilY;
-            dx[b] = (tap - ky * KW) * dilX;
-        }
-        for (int64_t m = warpId; m < M; m += numWarps) {
-            const int n = int(m / (int64_t(OH) * OW));
-            const int rem = int(m - int64_t(n) * OH * OW);
-            const int oy = rem / OW, ox = rem - oy * OW;
-            const int iy0 = oy * strideY - padTop, ix0 = ox * strideX - padLeft;
-            const int8_t *base = in + int64_t(n) * H * W * IC;
-            uint32_t word = 0;
+// ---- padded copy for convolutions whose channel count is not a multiple of 16 (an RGB stem) ---------
+// Copies an NHWC int8 tensor [N][H][W][C] into [N][Hp][Wp][Cp] (Cp >= C a multiple of 4) at row offset
+// padTop and column offset padLeft; the new channels and the border are zero.  One thread per 32-bit word
+// of the copy: byte reads hit L1, writes are coalesced.
+__global__ void padImageKernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int64_t words, int H, int W, int C,
+                               int Hp, int Wp, int Cp, int padTop, int padLeft) {
+    const int wordsPerPixel = Cp >> 2;
+    for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < words; e += int64_t(gridDim.x) * blockDim.x) {
+        int64_t pix = e / wordsPerPixel;
+        const int c0 = int(e - pix * wordsPerPixel) * 4;
+        const int x = int(pix % Wp) - padLeft;
+        pix /= Wp;
+        const int y = int(pix % Hp) - padTop;
+        const int64_t n = pix / Hp;
+        uint32_t word = 0;
+        if (y >= 0 && y < H && x >= 0 && x < W) {
+            const int8_t *src = in + ((n * H + y) * W + x) * C;
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const int y = iy0 + dy[b], x = ix0 + dx[b];
-                if (inK[b] && y >= 0 && y < H && x >= 0 && x < W) {
-                    word |= uint32_t(uint8_t(__ldg(base + (int64_t(y) * W + x) * IC + ci[b]))) << (8 * b);
+                if (c0 + b < C) {
+                    word |= uint32_t(uint8_t(__ldg(src + c0 + b))) << (8 * b);
                 }
             }
-            if (w < words) {
-                reinterpret_cast<uint32_t *>(out + m * kPad)[w] = word;
-            }
         }
+        reinterpret_cast<uint32_t *>(out)[e] = word;
     }
 }
 
@@ -102,14 +82,11 @@ int finish(const char *what) {
 
 } // namespace
 
-int im2colSmallIc(const int8_t *in, int8_t *out, int64_t M, int H, int W, int IC, int OH, int OW, int KH, int KW,
-                  const ConvAttr &a, int K, int kPad, cudaStream_t s) {
-    const int64_t warps = M < int64_t(kNumSMs) * 64 ? M : int64_t(kNumSMs) * 64;
-    const int blocks = int((warps * 32 + kThreads - 1) / kThreads);
-    im2colSmallIcKernel<<<blocks < 1 ? 1 : blocks, kThreads, 0, s>>>(in, out, M, H, W, IC, OH, OW, KH, KW, a.stride[0],
-                                                                      a.stride[1], a.pad[0], a.pad[2], a.dilation[0],
-                                                                      a.dilation[1], K, kPad);
-    return finish("im2col");
+int padImageI8(const int8_t *in, int8_t *out, int N, int H, int W, int C, int Hp, int Wp, int Cp, int padTop, int padLeft,
+               cudaStream_t s) {
+    const int64_t words = int64_t(N) * Hp * Wp * (Cp >> 2);
+    padImageKernel<<<gridFor(words, kThreads, 8), kThreads, 0, s>>>(in, out, words, H, W, C, Hp, Wp, Cp, padTop, padLeft);
+    return finish("padded copy");
 }
 
 bool maxPoolI8Eligible(const TView &in, const TView &out) {

@@ -62,6 +62,8 @@ struct __align__(16) ColConst {
     int32_t corr0;       // correction of the most common border class for this column
 };
 
+constexpr int kMaxGatherPieces = 1024; // entries of the shared-memory copy of GemmI8Params::gatherTable
+
 struct TileCoord {
     int m0, n0, batch;
 };
@@ -319,6 +321,30 @@ __device__ __forceinline__ void epilogueWarps(const GemmI8Params &p, PipeBarrier
     }
 }
 
+// Table gather of one 128-byte K block of one tile row: BK / G pieces of G bytes, piece j from origin + tab[j],
+// written to its place in the SWIZZLE_128B row at dstRow (swz = row & 7).
+template <int G>
+__device__ __forceinline__ void gatherPieces(const int8_t *origin, const int32_t *tab, uint32_t dstRow, uint32_t swz) {
+#pragma unroll
+    for (int j4 = 0; j4 < BK / G; j4 += 4) {
+        const int4 off = *reinterpret_cast<const int4 *>(tab + j4);
+        const int offs[4] = {off.x, off.y, off.z, off.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int o = (j4 + e) * G; // byte position inside the K block
+            const uint32_t dst = dstRow + ((uint32_t(o >> 4) ^ swz) << 4) + uint32_t(o & 15);
+            const int8_t *src = origin + offs[e];
+            if (G == 4) {
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+            } else if (G == 8) {
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+            } else {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
+        }
+    }
+}
+
 // A_TMA: A comes through tmapA; otherwise it is gathered from the NHWC input described by p.
 // B_MN : B is an N-contiguous [K][N] matrix (MN-major operand), otherwise a K-contiguous [N][K] matrix.
 template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
@@ -333,6 +359,9 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     uint8_t *tilesB = smem + NSTAGE * kTileA;
     ColConst *colTab = reinterpret_cast<ColConst *>(smem + NSTAGE * (kTileA + kTileB));
     PipeBarriers *bars = reinterpret_cast<PipeBarriers *>(smem + NSTAGE * (kTileA + kTileB) + BN * (sizeof(ColConst) + 4));
+    // gather variants only: the table of piece offsets (at most kMaxGatherPieces entries), 16-byte aligned
+    int32_t *gatherTab = reinterpret_cast<int32_t *>(
+        (reinterpret_cast<uintptr_t>(bars) + sizeof(PipeBarriers) + 15) & ~uintptr_t(15));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -359,6 +388,12 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
             mbarInit(&bars->accEmpty[b], uint32_t(kEpilogueWarps));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (!A_TMA && p.gatherTable != nullptr && warp >= kGatherWarp0) {
+        const int pieces = ((p.K + BK - 1) / BK) * (BK / p.chunkBytes);
+        for (int i = int(threadIdx.x) - kGatherWarp0 * 32; i < pieces && i < kMaxGatherPieces; i += 128) {
+            gatherTab[i] = __ldg(p.gatherTable + i);
+        }
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&bars->tmemBase)),
@@ -467,6 +502,22 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                         break;
                     }
                     const uint32_t dstRow = smemAddr(tilesA + s * kTileA) + uint32_t(row) * 128u;
+                    if (p.gatherTable != nullptr) {
+                        // every tap is in range (zero-padded copy): pieces at tabulated offsets from the origin
+                        const int8_t *origin =
+                            rowValid ? base + (int64_t(oy * p.strideY) * p.W + ox * p.strideX) * p.IC : p.in;
+                        if (p.chunkBytes == 4) {
+                            gatherPieces<4>(origin, gatherTab + kb * (BK / 4), dstRow, swz);
+                        } else if (p.chunkBytes == 8) {
+                            gatherPieces<8>(origin, gatherTab + kb * (BK / 8), dstRow, swz);
+                        } else {
+                            gatherPieces<16>(origin, gatherTab + kb * (BK / 16), dstRow, swz);
+                        }
+                        asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s]))
+                                     : "memory");
+                        mbarArrive(&bars->full[s]);
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int y = iy0 + ky * p.dilY;
@@ -512,7 +563,8 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
 template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
 int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes =
-        size_t(NSTAGE) * (BM * BK + BN * BK) + BN * (sizeof(ColConst) + 4) + sizeof(PipeBarriers) + 1024;
+        size_t(NSTAGE) * (BM * BK + BN * BK) + BN * (sizeof(ColConst) + 4) + sizeof(PipeBarriers) + 1024 +
+        (A_TMA ? 0 : kMaxGatherPieces * sizeof(int32_t) + 16);
     auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_TMA, B_MN>;
     static bool configured = false;
     if (!configured) {

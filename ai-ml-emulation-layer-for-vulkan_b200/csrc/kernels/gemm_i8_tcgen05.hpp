@@ -19,6 +19,11 @@ struct GemmI8Params {
     const int8_t *in;
     int32_t H, W, IC, OH, OW, KH, KW;
     int32_t strideY, strideX, padTop, padLeft, dilY, dilX;
+    // Table gather (a convolution over a zero-padded copy of its input, where every tap is in range): piece q
+    // of a pixel's K row is chunkBytes (4, 8 or 16) bytes at gatherTable[q] from the window origin
+    // in + ((n * H + oy * strideY) * W + ox * strideX) * IC.  Null => gather 16-byte pieces with bounds checks.
+    const int32_t *gatherTable;
+    int32_t chunkBytes;
     // correction term added to the raw accumulator: corr[(batch,) class, n]
     const int32_t *corr;
     const uint8_t *rowClass; // [OH] border class of an output row, or null (single class)

@@ -43,8 +43,8 @@ int fusedMatmulGeneric(const TView &a, const TView &b, const TView &out, int32_t
 int fusedAdd(const int8_t *x, const int8_t *y, int8_t *out, int64_t n, const DevEpilogue &epi, cudaStream_t s);
 
 // fast_ops.cu: vectorised kernels for packed int8 NHWC tensors
-int im2colSmallIc(const int8_t *in, int8_t *out, int64_t M, int H, int W, int IC, int OH, int OW, int KH, int KW,
-                  const ConvAttr &a, int K, int kPad, cudaStream_t s);
+int padImageI8(const int8_t *in, int8_t *out, int N, int H, int W, int C, int Hp, int Wp, int Cp, int padTop, int padLeft,
+               cudaStream_t s);
 bool maxPoolI8Eligible(const TView &in, const TView &out);
 int maxPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s);
 

@@ -120,19 +120,22 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     }
     q.batches = 1;
     if (op.tc == 2) {
-        // Channel count not a multiple of 16: materialise the im2col matrix, then a plain matrix product.
-        const int kPad = op.auxi[2];
-        int8_t *scratch = reinterpret_cast<int8_t *>(T[op.scratch].ptr);
-        const int rc = im2colSmallIc(p.in, scratch, p.M, p.H, p.W, p.IC, p.OH, p.OW, p.KH, p.KW, convAttr(op), p.K, kPad, s);
+        // Channel count not a multiple of 16: gather, by a table of offsets, from a copy of the input with
+        // zero-padded channels and borders.
+        const TView &copy = T[op.scratch];
+        const int rc = padImageI8(p.in, reinterpret_cast<int8_t *>(copy.ptr), int(in.dims[0]), p.H, p.W, p.IC,
+                                  int(copy.dims[1]), int(copy.dims[2]), int(copy.dims[3]), p.padTop, p.padLeft, s);
         if (rc != MLEL_SUCCESS) {
             return rc;
         }
-        p.K = kPad;
-        q.aMatrix = scratch;
-        q.aRowBytes = uint64_t(kPad);
-        q.aBatchBytes = uint64_t(kPad) * uint64_t(p.M);
+        p.in = reinterpret_cast<const int8_t *>(copy.ptr);
+        p.H = int32_t(copy.dims[1]), p.W = int32_t(copy.dims[2]), p.IC = int32_t(copy.dims[3]);
+        p.padTop = p.padLeft = 0;
+        p.K = int32_t(T[op.aux[3]].dims[1]);
+        p.chunkBytes = op.auxi[2];
+        p.gatherTable = reinterpret_cast<const int32_t *>(T[op.aux[4]].ptr);
         q.bMatrix = T[op.aux[3]].ptr;
-        q.bRowBytes = uint64_t(kPad);
+        q.bRowBytes = uint64_t(p.K);
         q.bBatchBytes = 0;
         q.bMnMajor = false;
         return gemmI8Launch(q, s);

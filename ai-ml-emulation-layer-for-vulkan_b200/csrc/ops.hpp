@@ -145,11 +145,13 @@ struct OpDesc {
     //                 aux[2] column classes u8 [OW]; auxi[0] = number of column classes, auxi[1] = classes
     //   MATMUL kinds with a constant second input: aux[0] correction int32 [batches][W],
     //                 aux[3] the second input transposed to [batches][W][C]
-    //   CONV2D kinds with tc == 2 (channel count not a multiple of 16): aux[3] weights zero-padded to
-    //                 [OC][kPad], scratch = session tensor [pixels][kPad] for the im2col matrix, auxi[2] = kPad
+    //   CONV2D kinds with tc == 2 (channel count not a multiple of 16): scratch = session tensor
+    //                 [N][Hp][Wp][ICp], a copy of the input with zero-padded channels and borders;
+    //                 aux[3] weights re-laid to the gather's K order [OC][kPad]; aux[4] int32 byte offset
+    //                 of every gathered piece from a pixel's window origin; auxi[2] = bytes per piece
     int32_t tc{0};
     int32_t scratch{-1};
-    int32_t aux[4]{-1, -1, -1, -1};
+    int32_t aux[5]{-1, -1, -1, -1, -1};
     int32_t auxi[4]{0, 0, 0, 0};
 };
 
