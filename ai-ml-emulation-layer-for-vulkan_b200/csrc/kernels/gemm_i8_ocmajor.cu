@@ -203,7 +203,8 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     int32_t *lutA = reinterpret_cast<int32_t *>(smem + NSTAGE * (kTileW + kTileX));
     int32_t *lutB = lutA + 256;
     uint8_t *clsTab = reinterpret_cast<uint8_t *>(lutB + 256);
-    OcBarriers *bars = reinterpret_cast<OcBarriers *>(clsTab + 2 * BNP);
+    int32_t *tapTab = reinterpret_cast<int32_t *>(clsTab + 2 * BNP);
+    OcBarriers *bars = reinterpret_cast<OcBarriers *>(tapTab + kTapTabEntries);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -236,6 +237,10 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                      "r"(uint32_t(2 * BNP))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    const bool fastGather = !X_TMA && fastGatherApplies(p);
+    if (fastGather && warp >= kGatherWarp0) {
+        fillTapTable(p, tapTab, kGatherWarp0 * 32, 128);
     }
     if (p.epi.hasResidual && threadIdx.x < 256) {
         // the two int8 -> int32 RESCALEs of the residual tail, tabulated over their whole domain
@@ -325,6 +330,28 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
             bool ok = true;
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
                 const OcTile tc = tileOf(t);
+                if (fastGather) {
+                    GatherRow rows[kRows];
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r) {
+                        rows[r] = gatherRowSetup(p, int64_t(tc.m0) + row0 + r * 128);
+                    }
+                    int tap = 0, c0 = 0;
+                    for (int kb = 0; kb < numKb; ++kb, ++it) {
+                        const int s = int(it % NSTAGE);
+                        const uint32_t phase = (it / NSTAGE) & 1u;
+                        ok = mbarWait(&bars->empty[s], phase ^ 1u, 13);
+                        if (!ok) {
+                            break;
+                        }
+                        const uint32_t dstRow = smemAddr(tilesX + s * kTileX) + uint32_t(row0) * 128u;
+                        gatherBlock<kRows>(rows, tapTab, p.KH * p.KW, p.IC, tap, c0, dstRow, swz, p.in);
+                        asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s]))
+                                     : "memory");
+                        mbarArrive(&bars->full[s]);
+                    }
+                    continue;
+                }
                 int iy0[kRows], ix0[kRows];
                 const int8_t *base[kRows];
                 bool rowValid[kRows];
@@ -402,7 +429,8 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
 template <int BNP, int NSTAGE, bool X_TMA>
 int launchOcMajor(const CUtensorMap &mapX, const CUtensorMap &mapW, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes =
-        size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * 256 * sizeof(int32_t) + 2 * BNP + sizeof(OcBarriers) + 1024;
+        size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * 256 * sizeof(int32_t) + 2 * BNP +
+        kTapTabEntries * sizeof(int32_t) + sizeof(OcBarriers) + 1024;
     auto kernel = gemmI8OcMajor<BNP, NSTAGE, X_TMA>;
     static bool configured = false;
     if (!configured) {

@@ -362,6 +362,8 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     // gather variants only: the table of piece offsets (at most kMaxGatherPieces entries), 16-byte aligned
     int32_t *gatherTab = reinterpret_cast<int32_t *>(
         (reinterpret_cast<uintptr_t>(bars) + sizeof(PipeBarriers) + 15) & ~uintptr_t(15));
+    int32_t *tapTab = gatherTab + kMaxGatherPieces; // tap offsets of the segment gather
+    const bool fastGather = !A_TMA && fastGatherApplies(p);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -388,6 +390,9 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
             mbarInit(&bars->accEmpty[b], uint32_t(kEpilogueWarps));
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (fastGather && warp >= kGatherWarp0) {
+        fillTapTable(p, tapTab, kGatherWarp0 * 32, 128);
     }
     if (!A_TMA && p.gatherTable != nullptr && warp >= kGatherWarp0) {
         const int pieces = ((p.K + BK - 1) / BK) * (BK / p.chunkBytes);
@@ -482,6 +487,24 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
                 const TileCoord tc = tileOf(t);
                 const int64_t m = int64_t(tc.m0) + row;
+                if (fastGather) {
+                    const GatherRow rows[1] = {gatherRowSetup(p, m)};
+                    int tap = 0, c0 = 0;
+                    for (int kb = 0; kb < numKb; ++kb, ++it) {
+                        const int s = int(it % NSTAGE);
+                        const uint32_t phase = (it / NSTAGE) & 1u;
+                        ok = mbarWait(&bars->empty[s], phase ^ 1u, 3);
+                        if (!ok) {
+                            break;
+                        }
+                        const uint32_t dstRow = smemAddr(tilesA + s * kTileA) + uint32_t(row) * 128u;
+                        gatherBlock<1>(rows, tapTab, p.KH * p.KW, p.IC, tap, c0, dstRow, swz, p.in);
+                        asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s]))
+                                     : "memory");
+                        mbarArrive(&bars->full[s]);
+                    }
+                    continue;
+                }
                 const bool rowValid = m < p.M;
                 int n = 0, oy = 0, ox = 0;
                 if (rowValid) {
@@ -564,7 +587,7 @@ template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
 int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes =
         size_t(NSTAGE) * (BM * BK + BN * BK) + BN * (sizeof(ColConst) + 4) + sizeof(PipeBarriers) + 1024 +
-        (A_TMA ? 0 : kMaxGatherPieces * sizeof(int32_t) + 16);
+        (A_TMA ? 0 : (kMaxGatherPieces + kTapTabEntries) * sizeof(int32_t) + 16);
     auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_TMA, B_MN>;
     static bool configured = false;
     if (!configured) {

@@ -127,6 +127,106 @@ __device__ __forceinline__ void epilogueSync() {
     asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
 }
 
+// ---- implicit-GEMM gather of one tile row per K block (im2col on the fly) -------------------------------
+// The K axis of a convolution is (ky, kx, channel).  When the channel count is 16, 32, 64 or a multiple of
+// 128, a 128-byte K block splits into equal segments of 16 * SEG contiguous bytes of one tap, and which tap
+// (and which channel offset) a segment covers is the same for every row of the tile.  A row then only
+// needs, once per tile, the address of its window's first tap and a bit mask of its in-range taps; per
+// segment it adds a tabulated tap offset and issues SEG 16-byte copies (zero-filled when the tap is out
+// of range).  This keeps the producer warps at a handful of instructions per K block.
+constexpr int kMaxTaps = 64;       // bits of the in-range mask
+constexpr int kTapTabEntries = 80; // taps plus the run-off of the last K block
+
+struct GatherRow {
+    const int8_t *origin; // address of tap (0, 0), channel 0 of the window; may lie outside the tensor
+    uint64_t mask;        // bit ky * KW + kx: that tap is inside the tensor
+};
+
+template <class Params>
+__device__ __forceinline__ bool fastGatherApplies(const Params &p) {
+    return p.gatherTable == nullptr && p.KH * p.KW <= kMaxTaps &&
+           (p.IC == 16 || p.IC == 32 || p.IC == 64 || p.IC % 128 == 0);
+}
+
+// Byte offset of tap t from tap 0 (0 past the window); filled once per CTA by the producer warps.
+template <class Params>
+__device__ __forceinline__ void fillTapTable(const Params &p, int32_t *tapTab, int firstThread, int numThreads) {
+    for (int t = int(threadIdx.x) - firstThread; t < kTapTabEntries; t += numThreads) {
+        const int ky = t / p.KW, kx = t - ky * p.KW;
+        tapTab[t] = ky < p.KH ? (ky * p.dilY * p.W + kx * p.dilX) * p.IC : 0;
+    }
+}
+
+template <class Params>
+__device__ __forceinline__ GatherRow gatherRowSetup(const Params &p, int64_t m) {
+    GatherRow r;
+    r.origin = p.in;
+    r.mask = 0;
+    if (m < p.M) {
+        const int n = int(m / (int64_t(p.OH) * p.OW));
+        const int rem = int(m - int64_t(n) * p.OH * p.OW);
+        const int oy = rem / p.OW, ox = rem - oy * p.OW;
+        const int iy0 = oy * p.strideY - p.padTop, ix0 = ox * p.strideX - p.padLeft;
+        uint32_t colMask = 0;
+        for (int kx = 0; kx < p.KW; ++kx) {
+            const int x = ix0 + kx * p.dilX;
+            colMask |= (x >= 0 && x < p.W) ? (1u << kx) : 0u;
+        }
+        for (int ky = 0; ky < p.KH; ++ky) {
+            const int y = iy0 + ky * p.dilY;
+            if (y >= 0 && y < p.H) {
+                r.mask |= uint64_t(colMask) << (ky * p.KW);
+            }
+        }
+        const int64_t off = ((int64_t(n) * p.H + iy0) * p.W + ix0) * p.IC;
+        r.origin = reinterpret_cast<const int8_t *>(reinterpret_cast<intptr_t>(p.in) + off);
+    }
+    return r;
+}
+
+// One 128-byte K block for ROWS tile rows (128 rows apart) of one thread.  (t, c0) is the running position
+// on the K axis: tap index and channel offset of the next segment.
+template <int SEG, int ROWS>
+__device__ __forceinline__ void gatherSegments(const GatherRow (&rows)[ROWS], const int32_t *tapTab, int taps, int IC,
+                                               int &t, int &c0, uint32_t dstRow, uint32_t swz, const int8_t *dummy) {
+#pragma unroll
+    for (int sg = 0; sg < 8 / SEG; ++sg) {
+        const bool tapInWindow = t < taps;
+        const int32_t off = tapTab[t] + c0;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            const bool valid = tapInWindow && ((rows[r].mask >> (t & 63)) & 1ull) != 0;
+            const int8_t *src = valid ? rows[r].origin + off : dummy;
+            const uint32_t bytes = valid ? 16u : 0u; // 0 source bytes: the 16 bytes are zero-filled
+#pragma unroll
+            for (int j = 0; j < SEG; ++j) {
+                const uint32_t dst = dstRow + uint32_t(r) * (128u * 128u) + ((uint32_t(sg * SEG + j) ^ swz) << 4);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src + 16 * j), "r"(bytes)
+                             : "memory");
+            }
+        }
+        c0 += SEG * 16;
+        if (c0 >= IC) {
+            c0 = 0;
+            ++t;
+        }
+    }
+}
+
+template <int ROWS>
+__device__ __forceinline__ void gatherBlock(const GatherRow (&rows)[ROWS], const int32_t *tapTab, int taps, int IC, int &t,
+                                            int &c0, uint32_t dstRow, uint32_t swz, const int8_t *dummy) {
+    if (IC >= 128) {
+        gatherSegments<8, ROWS>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
+    } else if (IC == 64) {
+        gatherSegments<4, ROWS>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
+    } else if (IC == 32) {
+        gatherSegments<2, ROWS>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
+    } else {
+        gatherSegments<1, ROWS>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
+    }
+}
+
 
 // ---- host side ----
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

@@ -49,6 +49,14 @@ CONV_CASES = [
     (4, 17, 17, 128, 130, 1, 0, 1, 1, -11, 0),
     (8, 56, 56, 32, 128, 1, 0, 1, 1, 6, 0),
     (8, 40, 40, 16, 192, 3, 1, 1, 1, 3, 0),
+    # gather variants: channel counts whose taps do not split a 128-byte K block evenly (48), dilation, a
+    # 5x5 window with stride 2, and a 7x7 window (49 taps) over 16 channels
+    (1, 9, 9, 48, 32, 3, 1, 1, 1, 4, 0),
+    (1, 9, 9, 48, 144, 3, 1, 1, 1, 4, 0),
+    (1, 13, 13, 32, 80, 3, 2, 1, 2, -9, 0),
+    (2, 15, 15, 16, 16, 5, 2, 2, 1, 1, 0),
+    (1, 20, 20, 16, 96, 7, 3, 2, 1, -2, 0),
+    (2, 11, 11, 256, 128, 3, 1, 1, 1, 12, 0),
 ]
 
 
