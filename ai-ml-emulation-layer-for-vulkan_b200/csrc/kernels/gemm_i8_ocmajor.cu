@@ -5,15 +5,18 @@
 //
 //   A operand  - weight tile, 128 output channels x 128 K bytes, TMA from the OHWI weight matrix [OC][K]
 //   B operand  - BNP (128 or 256) output pixels x 128 K bytes: TMA from a row-major pixel matrix (1x1
-//                stride-1 convolution, materialised im2col), else gathered with 16-byte cp.async
+//                stride-1 convolution), else gathered with 16-byte cp.async (segment gather)
 //   accumulator- TMEM lane = output channel, TMEM column = pixel; two accumulators of BNP columns alternate
+//   C/D tile   - a [BNP pixels][128 channels] byte tile in shared memory, two of them alternating with the
+//                accumulators: TMA brings the shortcut bytes of the residual tail into it, the epilogue
+//                replaces them in place by the results, TMA stores the tile.  Tensor bounds clip both
+//                directions, so the epilogue has no address arithmetic and no validity tests per element.
 //
 // Why a second orientation.  The TOSA RESCALE constants (multiplier, shift, folded rounding term) and the
 // zero-point correction are per output channel.  With the channel on the lane every epilogue thread keeps
 // the constants of its own channel in registers for the whole tile, where the pixel-major kernel reads
-// them from shared memory for every element; the instruction count per output element roughly halves.
-// A 256-pixel tile also moves 48 KB from L2 per 4.2 M multiply-accumulates instead of 32 KB per 2.1 M.
-// Stores are one byte per thread; a warp writes 32 consecutive channels of one pixel (one 32-byte sector).
+// them from shared memory for every element.  A 256-pixel tile also moves 48 KB from L2 per 4.2 M
+// multiply-accumulates instead of 32 KB per 2.1 M.
 //
 // The residual tail (RESCALE of the main value and of the shortcut, ADD, RESCALE) takes its two
 // int8 -> int32 RESCALEs from 256-entry tables computed once per launch with the very function the
@@ -35,11 +38,30 @@ using namespace tc;
 
 constexpr int kOcTile = 128; // output channels per tile (UMMA M)
 
+// Warp roles of this kernel: 0-7 epilogue (two per TMEM lane quarter; few enough warps that a thread may use
+// 128 registers and keep two 16-column accumulator slices in flight), 8 TMA producer, 9 MMA issuer and TMEM
+// owner, 10-11 pixel gather (implicit-GEMM variants only; two warps keep the CTA at 384 threads, so that
+// the epilogue's 168 registers per thread fit).
+constexpr int kOcEpiWarps = 8;
+constexpr int kOcTmaWarp = kOcEpiWarps;
+constexpr int kOcMmaWarp = kOcEpiWarps + 1;
+constexpr int kOcGatherWarp0 = kOcEpiWarps + 2;
+constexpr int kOcThreadsTma = (kOcEpiWarps + 2) * 32;
+constexpr int kOcGatherThreads = 64;
+constexpr int kOcThreadsGather = (kOcEpiWarps + 2) * 32 + kOcGatherThreads;
+
+// Barrier among the epilogue warps only (named barrier 1).
+__device__ __forceinline__ void ocEpilogueSync() {
+    asm volatile("bar.sync 1, %0;" ::"r"(kOcEpiWarps * 32) : "memory");
+}
+
 struct __align__(8) OcBarriers {
     uint64_t full[8];
     uint64_t empty[8];
     uint64_t accFull[2];
     uint64_t accEmpty[2];
+    uint64_t cFull[2];  // the shortcut bytes of a tile have landed in its C/D tile
+    uint64_t cdEmpty[2]; // the store of a C/D tile has finished reading it: the tile may be loaded again
     uint32_t tmemBase;
     uint32_t pad;
 };
@@ -48,25 +70,125 @@ struct OcTile {
     int c0, m0, batch;
 };
 
-template <int BNP, bool RESIDUAL>
-__device__ __forceinline__ void epilogueOcMajor(const GemmI8Params &p, OcBarriers *bars, uint8_t *clsTab,
-                                                const int32_t *lutA, const int32_t *lutB, uint32_t tmemBase, int warp,
-                                                int lane, int64_t numTiles, int pTiles, int cTiles) {
-    const int quarter = warp & 3; // TMEM lanes [32 * quarter, +32): output channels of the tile
-    const int part = warp >> 2;   // which quarter of the tile's pixels
-    constexpr int kColsPerWarp = BNP / (kEpilogueWarps / 4);
-    constexpr int kSteps = kColsPerWarp / 16;
-    FastRescale fo{};
-    if (RESIDUAL) {
-        fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
-                             p.epi.out.doubleRound != 0);
+__device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, const void *src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smemAddr(src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
+// High 32 bits of v * mult + (v >= thr ? rp : rn): product and rounding of a RESCALE whose shift is at least
+// 32, where the result only depends on the high word.  The compare feeds two predicated multiply-adds,
+// which run on the FMA pipe; the integer ALU pipe, which bounds this epilogue, sees one instruction.
+__device__ __forceinline__ int32_t scaleHigh(int32_t v, int32_t mult, int32_t thr, uint64_t rp, uint64_t rn) {
+    uint64_t sum;
+    asm("{\n\t.reg .pred q;\n\t"
+        "setp.ge.s32 q, %1, %3;\n\t"
+        "@q mad.wide.s32 %0, %1, %2, %4;\n\t"
+        "@!q mad.wide.s32 %0, %1, %2, %5;\n\t}"
+        : "=l"(sum)
+        : "r"(v), "r"(mult), "r"(thr), "l"(rp), "l"(rn));
+    return int32_t(uint32_t(sum >> 32));
+}
+
+// The rest of such a RESCALE: remaining shift, output zero point (wrapping add), clamp.
+__device__ __forceinline__ int32_t finishHigh(int32_t high, int32_t s2, int32_t outZp, int32_t lo, int32_t hi) {
+    return min(__viaddmax_s32(high >> s2, outZp, lo), hi);
+}
+
+// Constants of one epilogue thread (one output channel) and of the per-tensor output stage.
+struct EpiConsts {
+    FastRescale fm, fo;
+    uint64_t rpM, rnM, rpO, rnO;
+    int32_t corr0;
+    int32_t outZpMain, loMain, hiMain, outZpOut, loOut, hiOut;
+    bool fast; // every shift involved is at least 32: see scaleHigh
+};
+
+// 16 pixels of one channel: accumulator slice -> bytes in the C/D tile (column `cd`, rows 128 bytes apart).
+// All shortcut bytes are read before the first result is written: the compiler must assume that a byte store
+// may alias any later load, and 16 load-compute-store chains in a row would run one after the other.
+template <bool RESIDUAL, bool FAST>
+__device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], const EpiConsts &k, const int32_t *lutA128,
+                                                 const int32_t *lutB, uint8_t *cd) {
+    constexpr int CH = 8; // pixels per group: enough independent chains, few enough live registers
+#pragma unroll
+    for (int g = 0; g < 16; g += CH) {
+        uint32_t sc[CH];
+        if (RESIDUAL) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+                sc[j] = cd[128 * (g + j)];
+            }
+        }
+        int32_t r[CH];
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            const int32_t v = int32_t(acc[g + j] + uint32_t(k.corr0));
+            if (FAST) {
+                r[j] = finishHigh(scaleHigh(v, k.fm.mult, k.fm.zpIn, k.rpM, k.rnM), k.fm.s2, k.outZpMain, k.loMain, k.hiMain);
+            } else {
+                r[j] = fastRescale(k.fm, v, k.outZpMain, k.loMain, k.hiMain);
+            }
+        }
+        if (RESIDUAL) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+                const int32_t sum = int32_t(uint32_t(lutA128[r[j]]) + uint32_t(lutB[sc[j]]));
+                if (FAST) {
+                    r[j] = finishHigh(scaleHigh(sum, k.fo.mult, k.fo.zpIn, k.rpO, k.rnO), k.fo.s2, k.outZpOut, k.loOut, k.hiOut);
+                } else {
+                    r[j] = fastRescale(k.fo, sum, k.outZpOut, k.loOut, k.hiOut);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            cd[128 * (g + j)] = uint8_t(r[j]);
+        }
     }
-    const int32_t outZpMain = p.epi.main.outZp, loMain = p.epi.main.lo, hiMain = p.epi.main.hi;
-    FastRescale fm{}; // main RESCALE stage of this thread's output channel
-    int32_t corr0 = 0;
+}
+
+template <bool RESIDUAL>
+__device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const EpiConsts &k, const int32_t *lutA128,
+                                             const int32_t *lutB, uint8_t *cd) {
+    if (k.fast) {
+        rescaleSliceImpl<RESIDUAL, true>(acc, k, lutA128, lutB, cd);
+    } else {
+        rescaleSliceImpl<RESIDUAL, false>(acc, k, lutA128, lutB, cd);
+    }
+}
+
+// The epilogue warps.  Warp w owns TMEM lanes 32 * (w & 3) .. +31 (output channels) and half of the tile's
+// pixels, which it walks in slices of 16 pixels; the tcgen05.ld of the next slice is in flight while the
+// current one is rescaled.
+template <int BNP, bool RESIDUAL>
+__device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const GemmI8Params &p, OcBarriers *bars,
+                                                uint8_t *clsTab, const int32_t *lutA, const int32_t *lutB, uint8_t *cdTiles,
+                                                uint32_t tmemBase, int warp, int lane, int64_t numTiles, int pTiles,
+                                                int cTiles) {
+    const int quarter = warp & 3;
+    const int part = warp >> 2;
+    constexpr int kColsPerWarp = BNP / (kOcEpiWarps / 4);
+    constexpr int kSteps = kColsPerWarp / 16;
+    static_assert(kSteps % 2 == 0, "slices are processed in pairs");
+    EpiConsts k{};
+    if (RESIDUAL) {
+        k.fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
+                               p.epi.out.doubleRound != 0);
+        k.rpO = (uint64_t(k.fo.rpHi) << 32) | k.fo.rpLo;
+        k.rnO = (uint64_t(k.fo.rnHi) << 32) | k.fo.rnLo;
+        // These are the same in every thread; passing them through an opaque statement keeps them in ordinary
+        // registers, where the multiply-add can use them directly, instead of being copied in before each use.
+        asm volatile("" : "+l"(k.rpO), "+l"(k.rnO));
+    }
+    k.outZpMain = p.epi.main.outZp, k.loMain = p.epi.main.lo, k.hiMain = p.epi.main.hi;
+    k.outZpOut = p.epi.out.outZp, k.loOut = p.epi.out.lo, k.hiOut = p.epi.out.hi;
+    const int32_t *lutA128 = lutA + 128; // indexed by the signed int8 value of the main stage
     int curC0 = -1, curBatch = -1;
     const bool hasClasses = p.rowClass != nullptr;
     const int baseClass = p.baseClass;
+    const bool storer = warp == 0 && lane == 0; // issues the tile stores and tracks their completion
     uint32_t tileCount = 0;
     for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
         int64_t tt = t;
@@ -75,132 +197,141 @@ __device__ __forceinline__ void epilogueOcMajor(const GemmI8Params &p, OcBarrier
         const int m0 = int(tt % pTiles) * BNP;
         const int batch = int(tt / pTiles);
         const uint32_t buf = tileCount & 1u;
+        const uint32_t par = (tileCount >> 1) & 1u;
         const int oc = c0 + quarter * 32 + lane;
         const bool ocValid = oc < p.N;
         const int32_t *corrBatch = p.corr + (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0);
+        if (storer) {
+            // The previous tile's store has read its C/D tile (and so have all before it): that tile may be
+            // filled again, by the next shortcut load or by the epilogue of the next tile.
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (RESIDUAL && tileCount > 0) {
+                mbarArrive(&bars->cdEmpty[buf ^ 1u]);
+            }
+        }
         if (c0 != curC0 || (p.batchedCorr && batch != curBatch)) {
             const int ci = (p.epi.main.perChannel && ocValid) ? oc : 0;
-            fm = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)), p.epi.main.inZp,
-                                 p.epi.main.doubleRound != 0);
-            corr0 = ocValid ? __ldg(corrBatch + int64_t(p.baseClass) * p.N + oc) : 0;
+            k.fm = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)), p.epi.main.inZp,
+                                   p.epi.main.doubleRound != 0);
+            k.rpM = (uint64_t(k.fm.rpHi) << 32) | k.fm.rpLo;
+            k.rnM = (uint64_t(k.fm.rnHi) << 32) | k.fm.rnLo;
+            k.corr0 = ocValid ? __ldg(corrBatch + int64_t(baseClass) * p.N + oc) : 0;
+            k.fast = __all_sync(0xffffffffu, k.fm.s1 == 32) && (!RESIDUAL || k.fo.s1 == 32);
             curC0 = c0;
             curBatch = batch;
         }
         uint8_t *cls = clsTab + buf * BNP;
-        if (p.rowClass != nullptr) {
+        if (hasClasses) {
             // border class of every pixel of the tile; the table alternates with the accumulator, so a warp that
             // is a tile ahead never overwrites what a slower warp still reads
             if (threadIdx.x < BNP) {
                 const int64_t m = int64_t(m0) + threadIdx.x;
-                int c = p.baseClass;
+                int c = baseClass;
                 if (m < p.M) {
                     const int rem = int(m % (int64_t(p.OH) * p.OW));
                     c = int(__ldg(p.rowClass + rem / p.OW)) * p.numColClasses + int(__ldg(p.colClass + rem % p.OW));
                 }
                 cls[threadIdx.x] = uint8_t(c);
             }
-            epilogueSync();
+            ocEpilogueSync();
         }
-        if (!mbarWait(&bars->accFull[buf], (tileCount >> 1) & 1u, 4)) {
+        if (RESIDUAL && !mbarWait(&bars->cFull[buf], par, 6)) {
+            break;
+        }
+        if (!mbarWait(&bars->accFull[buf], par, 4)) {
             break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t taddr = tmemBase + buf * uint32_t(BNP) + (uint32_t(quarter * 32) << 16);
+        const uint32_t taddr = tmemBase + buf * uint32_t(BNP) + (uint32_t(quarter * 32) << 16) + uint32_t(part * kColsPerWarp);
+        // this thread's column of the C/D tile, at the first pixel of its half
+        uint8_t *cd = cdTiles + buf * (BNP * 128) + (part * kColsPerWarp) * 128 + quarter * 32 + lane;
+        const auto borderFix = [&](uint32_t (&acc)[16], int col) {
+            // pixels of this slice whose window crosses the border take their own class's correction
+            const uint32_t borderMask = __ballot_sync(0xffffffffu, lane < 16 && int(cls[col + (lane & 15)]) != baseClass);
+            if (borderMask != 0 && ocValid) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if ((borderMask >> j) & 1u) {
+                        const int c = int(cls[col + j]);
+                        acc[j] += uint32_t(__ldg(corrBatch + int64_t(c) * p.N + oc)) - uint32_t(k.corr0);
+                    }
+                }
+            }
+            __syncwarp();
+        };
+        uint32_t accA[16], accB[16];
+        if (RESIDUAL) {
+            // the residual tail needs the registers a second slice in flight would take
 #pragma unroll 1
-        for (int st = 0; st < kSteps; ++st) {
-            const int col = part * kColsPerWarp + st * 16; // first pixel of this step inside the tile
-            uint32_t acc[16];
-            tmemLoad16(taddr + uint32_t(col), acc);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (st == kSteps - 1) {
+            for (int st = 0; st < kSteps; ++st) {
+                tmemLoad16(taddr + uint32_t(16 * st), accA);
+                tmemWait16(accA);
+                if (st == kSteps - 1) {
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    if (lane == 0) {
+                        mbarArrive(&bars->accEmpty[buf]);
+                    }
+                }
+                if (hasClasses) {
+                    borderFix(accA, part * kColsPerWarp + 16 * st);
+                }
+                rescaleSlice<RESIDUAL>(accA, k, lutA128, lutB, cd + (16 * st) * 128);
+            }
+        } else {
+        tmemLoad16(taddr, accA);
+#pragma unroll 1
+        for (int st = 0; st < kSteps; st += 2) {
+            tmemWait16(accA);
+            tmemLoad16(taddr + uint32_t(16 * (st + 1)), accB);
+            if (hasClasses) {
+                borderFix(accA, part * kColsPerWarp + 16 * st);
+            }
+            rescaleSlice<RESIDUAL>(accA, k, lutA128, lutB, cd + (16 * st) * 128);
+            tmemWait16(accB);
+            if (st + 2 < kSteps) {
+                tmemLoad16(taddr + uint32_t(16 * (st + 2)), accA);
+            } else {
+                // this warp's part of the accumulator is in registers: hand the buffer back to the MMA warp
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 if (lane == 0) {
                     mbarArrive(&bars->accEmpty[buf]);
                 }
             }
-            const int64_t mBase = int64_t(m0) + col;
-            if (mBase >= p.M) {
-                continue; // the same for the whole warp
-            }
-            const int npix = int(min(int64_t(16), int64_t(p.M) - mBase));
-            // pixels of this step whose window crosses the border (their class differs from the common one)
-            uint32_t borderMask = 0;
             if (hasClasses) {
-                borderMask = __ballot_sync(0xffffffffu, lane < 16 && int(cls[col + (lane & 15)]) != baseClass);
+                borderFix(accB, part * kColsPerWarp + 16 * (st + 1));
             }
-            if (ocValid) {
-                // pixel part of the address: the same for the whole warp; channel part: 32 bits per thread
-                const int64_t off0 = (int64_t(batch) * p.M + mBase) * p.ldOut;
-                int8_t *dstRow = p.out8 + off0;
-                const uint32_t ld = uint32_t(p.ldOut);
-                if (borderMask != 0) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if ((borderMask >> j) & 1u) {
-                            const int c = int(cls[col + j]);
-                            acc[j] += uint32_t(__ldg(corrBatch + int64_t(c) * p.N + oc)) - uint32_t(corr0);
-                        }
-                    }
-                }
-                int32_t sc[16];
-                if (RESIDUAL) {
-                    const int8_t *scRow = p.epi.shortcut + off0;
-                    if (npix == 16) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            sc[j] = int32_t(__ldg(scRow + (uint32_t(j) * ld + uint32_t(oc))));
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            sc[j] = j < npix ? int32_t(__ldg(scRow + (uint32_t(j) * ld + uint32_t(oc)))) : 0;
-                        }
-                    }
-                }
-                int32_t r[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    r[j] = fastRescale(fm, int32_t(acc[j] + uint32_t(corr0)), outZpMain, loMain, hiMain);
-                }
-                if (RESIDUAL) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int32_t ta = lutA[r[j] + 128];
-                        const int32_t tb = lutB[sc[j] + 128];
-                        r[j] = fastRescale(fo, int32_t(uint32_t(ta) + uint32_t(tb)), p.epi.out.outZp, p.epi.out.lo,
-                                           p.epi.out.hi);
-                    }
-                }
-                if (npix == 16) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        dstRow[uint32_t(j) * ld + uint32_t(oc)] = int8_t(r[j]);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (j < npix) {
-                            dstRow[uint32_t(j) * ld + uint32_t(oc)] = int8_t(r[j]);
-                        }
-                    }
-                }
-            }
-            __syncwarp(); // channels past the end skipped the block: converge before the next aligned TMEM load
+            rescaleSlice<RESIDUAL>(accB, k, lutA128, lutB, cd + (16 * (st + 1)) * 128);
         }
+        }
+        // make the tile visible to the TMA unit, then one thread stores it (pixels and channels past the
+        // tensor's end are clipped by the tensor map)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        ocEpilogueSync();
+        if (storer) {
+            tmaStore3d(tmapD, cdTiles + buf * (BNP * 128), c0, m0, 0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+    if (storer) {
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 }
 
 // X_TMA: the pixel operand comes through tmapX; otherwise it is gathered from the NHWC input described by p.
-template <int BNP, int NSTAGE, bool X_TMA>
-__global__ void __launch_bounds__(X_TMA ? kThreadsTma : kThreadsGather, 1)
-gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CUtensorMap tmapW, const GemmI8Params p) {
+// RESIDUAL: the fused residual tail is present (tmapC describes the shortcut tensor).
+template <int BNP, int NSTAGE, bool X_TMA, bool RESIDUAL>
+__global__ void __launch_bounds__(X_TMA ? kOcThreadsTma : kOcThreadsGather, 1)
+gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CUtensorMap tmapW,
+              const __grid_constant__ CUtensorMap tmapC, const __grid_constant__ CUtensorMap tmapD, const GemmI8Params p) {
     extern __shared__ uint8_t rawSmem[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
     constexpr int kTileW = kOcTile * BK;
     constexpr int kTileX = BNP * BK;
+    constexpr int kTileCd = BNP * 128;
     uint8_t *tilesW = smem;
     uint8_t *tilesX = smem + NSTAGE * kTileW;
-    int32_t *lutA = reinterpret_cast<int32_t *>(smem + NSTAGE * (kTileW + kTileX));
+    uint8_t *cdTiles = smem + NSTAGE * (kTileW + kTileX);
+    int32_t *lutA = reinterpret_cast<int32_t *>(cdTiles + 2 * kTileCd);
     int32_t *lutB = lutA + 256;
     uint8_t *clsTab = reinterpret_cast<uint8_t *>(lutB + 256);
     int32_t *tapTab = reinterpret_cast<int32_t *>(clsTab + 2 * BNP);
@@ -223,26 +354,27 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
-            mbarInit(&bars->full[s], X_TMA ? 1u : 1u + 128u);
+            mbarInit(&bars->full[s], X_TMA ? 1u : 1u + uint32_t(kOcGatherThreads));
             mbarInit(&bars->empty[s], 1u);
         }
         for (int b = 0; b < 2; ++b) {
             mbarInit(&bars->accFull[b], 1u);
-            mbarInit(&bars->accEmpty[b], uint32_t(kEpilogueWarps));
+            mbarInit(&bars->accEmpty[b], uint32_t(kOcEpiWarps));
+            mbarInit(&bars->cFull[b], 1u);
+            mbarInit(&bars->cdEmpty[b], 1u);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kMmaWarp) {
+    if (warp == kOcMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&bars->tmemBase)),
                      "r"(uint32_t(2 * BNP))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    const bool fastGather = !X_TMA && fastGatherApplies(p);
-    if (fastGather && warp >= kGatherWarp0) {
-        fillTapTable(p, tapTab, kGatherWarp0 * 32, 128);
+    if (!X_TMA && warp >= kOcGatherWarp0) {
+        fillTapTable(p, tapTab, kOcGatherWarp0 * 32, kOcGatherThreads);
     }
-    if (p.epi.hasResidual && threadIdx.x < 256) {
+    if (RESIDUAL && threadIdx.x < 256) {
         // the two int8 -> int32 RESCALEs of the residual tail, tabulated over their whole domain
         const int32_t v = int32_t(threadIdx.x) - 128;
         const FastRescale fa =
@@ -250,19 +382,20 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         const FastRescale fb =
             makeFastRescale(__ldg(p.epi.b.mult), int32_t(__ldg(p.epi.b.shift)), p.epi.b.inZp, p.epi.b.doubleRound != 0);
         lutA[threadIdx.x] = fastRescale(fa, v, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
-        lutB[threadIdx.x] = fastRescale(fb, v, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
+        // the shortcut table is indexed by the raw byte: entry u belongs to the value int8(u)
+        lutB[uint8_t(v)] = fastRescale(fb, v, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmemBase = bars->tmemBase;
 
-    if (warp == kTmaWarp) {
+    if (warp == kOcTmaWarp) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t it = 0, tileCount = 0;
             bool ok = true;
-            for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
+            for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileCount) {
                 const OcTile tc = tileOf(t);
                 for (int kb = 0; kb < numKb; ++kb, ++it) {
                     const int s = int(it % NSTAGE);
@@ -282,9 +415,18 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                         }
                     }
                 }
+                if (RESIDUAL && ok) {
+                    // the tile's shortcut bytes, once the store that last used this C/D tile has read it
+                    const uint32_t buf = tileCount & 1u;
+                    ok = mbarWait(&bars->cdEmpty[buf], ((tileCount >> 1) & 1u) ^ 1u, 16);
+                    if (ok) {
+                        mbarArriveExpectTx(&bars->cFull[buf], uint32_t(kTileCd));
+                        tmaLoad3d(&tmapC, cdTiles + buf * kTileCd, &bars->cFull[buf], tc.c0, tc.m0, 0);
+                    }
+                }
             }
         }
-    } else if (warp == kMmaWarp) {
+    } else if (warp == kOcMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = instrDesc(BNP, false);
@@ -320,57 +462,22 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                 }
             }
         }
-    } else if (warp >= kGatherWarp0) {
-        // ---------------- pixel gather (implicit GEMM): BNP / 128 tile rows per thread ----------------
+    } else if (warp >= kOcGatherWarp0) {
+        // ---------------- pixel gather (implicit GEMM): BNP / 64 tile rows per thread ----------------
         if (!X_TMA) {
-            constexpr int kRows = BNP / 128;
-            const int row0 = (warp - kGatherWarp0) * 32 + lane;
-            const uint32_t swz = uint32_t(row0 & 7); // rows 128 apart share the swizzle phase
+            constexpr int kRows = BNP / kOcGatherThreads;
+            const int row0 = (warp - kOcGatherWarp0) * 32 + lane;
+            const uint32_t swz = uint32_t(row0 & 7); // rows 64 apart share the swizzle phase
             uint32_t it = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
                 const OcTile tc = tileOf(t);
-                if (fastGather) {
-                    GatherRow rows[kRows];
-#pragma unroll
-                    for (int r = 0; r < kRows; ++r) {
-                        rows[r] = gatherRowSetup(p, int64_t(tc.m0) + row0 + r * 128);
-                    }
-                    int tap = 0, c0 = 0;
-                    for (int kb = 0; kb < numKb; ++kb, ++it) {
-                        const int s = int(it % NSTAGE);
-                        const uint32_t phase = (it / NSTAGE) & 1u;
-                        ok = mbarWait(&bars->empty[s], phase ^ 1u, 13);
-                        if (!ok) {
-                            break;
-                        }
-                        const uint32_t dstRow = smemAddr(tilesX + s * kTileX) + uint32_t(row0) * 128u;
-                        gatherBlock<kRows>(rows, tapTab, p.KH * p.KW, p.IC, tap, c0, dstRow, swz, p.in);
-                        asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s]))
-                                     : "memory");
-                        mbarArrive(&bars->full[s]);
-                    }
-                    continue;
-                }
-                int iy0[kRows], ix0[kRows];
-                const int8_t *base[kRows];
-                bool rowValid[kRows];
+                GatherRow rows[kRows];
 #pragma unroll
                 for (int r = 0; r < kRows; ++r) {
-                    const int64_t m = int64_t(tc.m0) + row0 + r * 128;
-                    rowValid[r] = m < p.M;
-                    int n = 0, oy = 0, ox = 0;
-                    if (rowValid[r]) {
-                        n = int(m / (int64_t(p.OH) * p.OW));
-                        const int rem = int(m - int64_t(n) * p.OH * p.OW);
-                        oy = rem / p.OW;
-                        ox = rem - oy * p.OW;
-                    }
-                    iy0[r] = oy * p.strideY - p.padTop;
-                    ix0[r] = ox * p.strideX - p.padLeft;
-                    base[r] = p.in + int64_t(n) * p.H * p.W * p.IC;
+                    rows[r] = gatherRowSetup(p, int64_t(tc.m0) + row0 + r * kOcGatherThreads);
                 }
-                int c = 0, kx = 0, ky = 0;
+                int tap = 0, c0 = 0;
                 for (int kb = 0; kb < numKb; ++kb, ++it) {
                     const int s = int(it % NSTAGE);
                     const uint32_t phase = (it / NSTAGE) & 1u;
@@ -379,29 +486,8 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                         break;
                     }
                     const uint32_t dstRow = smemAddr(tilesX + s * kTileX) + uint32_t(row0) * 128u;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int dy = ky * p.dilY, dx = kx * p.dilX;
-#pragma unroll
-                        for (int r = 0; r < kRows; ++r) {
-                            const int y = iy0[r] + dy;
-                            const int x = ix0[r] + dx;
-                            const bool valid = rowValid[r] && ky < p.KH && y >= 0 && y < p.H && x >= 0 && x < p.W;
-                            const int8_t *src = valid ? base[r] + (int64_t(y) * p.W + x) * p.IC + c : p.in;
-                            const uint32_t dst = dstRow + uint32_t(r) * (128u * 128u) + ((uint32_t(j) ^ swz) << 4);
-                            const uint32_t bytes = valid ? 16u : 0u;
-                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
-                                         : "memory");
-                        }
-                        c += 16;
-                        if (c >= p.IC) {
-                            c = 0;
-                            if (++kx == p.KW) {
-                                kx = 0;
-                                ++ky;
-                            }
-                        }
-                    }
+                    gatherBlock<kRows, kOcGatherThreads>(rows, tapTab, p.KH * p.KW, p.IC, tap, c0, dstRow, swz, p.in);
+                    // The stage's barrier completes when these copies have landed and every producer arrived.
                     asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s]))
                                  : "memory");
                     mbarArrive(&bars->full[s]);
@@ -410,28 +496,30 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         }
     } else {
         // ---------------- epilogue ----------------
-        if (p.epi.hasResidual) {
-            epilogueOcMajor<BNP, true>(p, bars, clsTab, lutA, lutB, tmemBase, warp, lane, numTiles, pTiles, cTiles);
-        } else {
-            epilogueOcMajor<BNP, false>(p, bars, clsTab, lutA, lutB, tmemBase, warp, lane, numTiles, pTiles, cTiles);
-        }
+        epilogueOcMajor<BNP, RESIDUAL>(&tmapD, p, bars, clsTab, lutA, lutB, cdTiles, tmemBase, warp, lane, numTiles,
+                                       pTiles, cTiles);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == kMmaWarp) {
+    if (warp == kOcMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(uint32_t(2 * BNP))
                      : "memory");
     }
 }
 
-template <int BNP, int NSTAGE, bool X_TMA>
-int launchOcMajor(const CUtensorMap &mapX, const CUtensorMap &mapW, const GemmI8Params &p, cudaStream_t s) {
-    constexpr size_t smemBytes =
-        size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * 256 * sizeof(int32_t) + 2 * BNP +
-        kTapTabEntries * sizeof(int32_t) + sizeof(OcBarriers) + 1024;
-    auto kernel = gemmI8OcMajor<BNP, NSTAGE, X_TMA>;
+struct OcMaps {
+    CUtensorMap x, w, c, d;
+};
+
+template <int BNP, int NSTAGE, bool X_TMA, bool RESIDUAL>
+int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
+    constexpr size_t smemBytes = size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * size_t(BNP) * 128 +
+                                 2 * 256 * sizeof(int32_t) + 2 * BNP + kTapTabEntries * sizeof(int32_t) +
+                                 sizeof(OcBarriers) + 1024;
+    static_assert(smemBytes <= 232448, "shared memory per CTA");
+    auto kernel = gemmI8OcMajor<BNP, NSTAGE, X_TMA, RESIDUAL>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smemBytes)) != cudaSuccess) {
@@ -442,7 +530,7 @@ int launchOcMajor(const CUtensorMap &mapX, const CUtensorMap &mapW, const GemmI8
     }
     const int64_t tiles = int64_t((p.M + BNP - 1) / BNP) * ((p.N + kOcTile - 1) / kOcTile) * p.batches;
     const int grid = int(tiles < smCount() ? tiles : smCount());
-    kernel<<<grid, X_TMA ? kThreadsTma : kThreadsGather, smemBytes, s>>>(mapX, mapW, p);
+    kernel<<<grid, X_TMA ? kOcThreadsTma : kOcThreadsGather, smemBytes, s>>>(maps.x, maps.w, maps.c, maps.d, p);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
         setLastError(std::string("tcgen05 channel-major convolution launch: ") + cudaGetErrorString(err));
@@ -451,15 +539,33 @@ int launchOcMajor(const CUtensorMap &mapX, const CUtensorMap &mapW, const GemmI8
     return MLEL_SUCCESS;
 }
 
+template <int BNP, int NSTAGE>
+int launchOcMajorShape(const OcMaps &maps, const GemmI8Params &p, bool xTma, cudaStream_t s) {
+    if (p.epi.hasResidual) {
+        return xTma ? launchOcMajor<BNP, NSTAGE, true, true>(maps, p, s) : launchOcMajor<BNP, NSTAGE, false, true>(maps, p, s);
+    }
+    return xTma ? launchOcMajor<BNP, NSTAGE, true, false>(maps, p, s) : launchOcMajor<BNP, NSTAGE, false, false>(maps, p, s);
+}
+
 } // namespace
 
 bool gemmI8OcMajorApplies(const GemmI8Problem &q) {
     const GemmI8Params &p = q.params;
-    if (p.out8 == nullptr || !p.epi.hasMain || q.bMnMajor || p.batchedB || p.N <= 64 || p.ldOut >= (1 << 27)) {
+    if (p.out8 == nullptr || !p.epi.hasMain || q.bMnMajor || p.batchedB || q.batches != 1 || p.N <= 64) {
+        return false;
+    }
+    // the output (and the shortcut) move as TMA tiles of 16-byte aligned rows
+    if (p.N % 16 != 0 || p.ldOut % 16 != 0 || (reinterpret_cast<uintptr_t>(p.out8) & 15u) != 0) {
+        return false;
+    }
+    // a gathered pixel operand goes through the segment gather
+    if (q.aMatrix == nullptr && !(p.gatherTable == nullptr && p.KH * p.KW <= kMaxTaps &&
+                                  (p.IC == 16 || p.IC == 32 || p.IC == 64 || p.IC % 128 == 0))) {
         return false;
     }
     // the residual tables are indexed by the int8 value of the main stage
-    return !p.epi.hasResidual || (p.epi.main.lo >= -128 && p.epi.main.hi <= 127);
+    return !p.epi.hasResidual || (p.epi.main.lo >= -128 && p.epi.main.hi <= 127 &&
+                                  (reinterpret_cast<uintptr_t>(p.epi.shortcut) & 15u) == 0);
 }
 
 int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
@@ -472,20 +578,27 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
     const int64_t t128 = int64_t((p.M + 127) / 128) * cTiles * q.batches;
     const int64_t sms = smCount();
     const bool wide = ((t256 + sms - 1) / sms) * 2 <= (t128 + sms - 1) / sms;
-    CUtensorMap mapX{}, mapW{};
+    OcMaps maps{};
     const bool xTma = q.aMatrix != nullptr;
-    if (xTma && !makeMap(&mapX, q.aMatrix, uint64_t(p.K), uint64_t(p.M), uint64_t(q.batches), uint64_t(q.aRowBytes),
+    if (xTma && !makeMap(&maps.x, q.aMatrix, uint64_t(p.K), uint64_t(p.M), uint64_t(q.batches), uint64_t(q.aRowBytes),
                          uint64_t(q.aBatchBytes), BK, 128)) {
         return MLEL_ERROR_DEVICE;
     }
-    if (!makeMap(&mapW, q.bMatrix, uint64_t(p.K), uint64_t(p.N), 1, uint64_t(q.bRowBytes),
+    if (!makeMap(&maps.w, q.bMatrix, uint64_t(p.K), uint64_t(p.N), 1, uint64_t(q.bRowBytes),
                  uint64_t(q.bRowBytes) * uint64_t(p.N), BK, kOcTile)) {
         return MLEL_ERROR_DEVICE;
     }
-    if (wide) {
-        return xTma ? launchOcMajor<256, 4, true>(mapX, mapW, p, s) : launchOcMajor<256, 4, false>(mapX, mapW, p, s);
+    // output and shortcut: [pixels][channels] bytes, unswizzled tiles of 128 channels x (128 or 256) pixels
+    const uint32_t boxPixels = wide ? 256u : 128u;
+    const uint64_t plane = uint64_t(p.ldOut) * uint64_t(p.M);
+    if (!makeMap(&maps.d, p.out8, uint64_t(p.N), uint64_t(p.M), 1, uint64_t(p.ldOut), plane, kOcTile, boxPixels, false)) {
+        return MLEL_ERROR_DEVICE;
     }
-    return xTma ? launchOcMajor<128, 6, true>(mapX, mapW, p, s) : launchOcMajor<128, 6, false>(mapX, mapW, p, s);
+    if (p.epi.hasResidual &&
+        !makeMap(&maps.c, p.epi.shortcut, uint64_t(p.N), uint64_t(p.M), 1, uint64_t(p.ldOut), plane, kOcTile, boxPixels, false)) {
+        return MLEL_ERROR_DEVICE;
+    }
+    return wide ? launchOcMajorShape<256, 3>(maps, p, xTma, s) : launchOcMajorShape<128, 5>(maps, p, xTma, s);
 }
 
 int ocMajorErrorWord() { return tc::readErrorWord(); }

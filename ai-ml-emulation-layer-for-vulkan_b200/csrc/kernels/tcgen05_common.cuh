@@ -122,6 +122,16 @@ __device__ __forceinline__ void tmemLoad16(uint32_t taddr, uint32_t (&r)[16]) {
                  : "memory");
 }
 
+// Waits for this warp's outstanding tcgen05.ld.  The loaded registers pass through the statement so that the
+// compiler cannot schedule a use of them above the wait.
+__device__ __forceinline__ void tmemWait16(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
+
 // Barrier among the epilogue warps only (named barrier 1).
 __device__ __forceinline__ void epilogueSync() {
     asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
@@ -184,9 +194,9 @@ __device__ __forceinline__ GatherRow gatherRowSetup(const Params &p, int64_t m) 
     return r;
 }
 
-// One 128-byte K block for ROWS tile rows (128 rows apart) of one thread.  (t, c0) is the running position
+// One 128-byte K block for ROWS tile rows (ROW_STEP rows apart, a multiple of 8) of one thread.  (t, c0) is the running position
 // on the K axis: tap index and channel offset of the next segment.
-template <int SEG, int ROWS>
+template <int SEG, int ROWS, int ROW_STEP>
 __device__ __forceinline__ void gatherSegments(const GatherRow (&rows)[ROWS], const int32_t *tapTab, int taps, int IC,
                                                int &t, int &c0, uint32_t dstRow, uint32_t swz, const int8_t *dummy) {
 #pragma unroll
@@ -200,7 +210,7 @@ __device__ __forceinline__ void gatherSegments(const GatherRow (&rows)[ROWS], co
             const uint32_t bytes = valid ? 16u : 0u; // 0 source bytes: the 16 bytes are zero-filled
 #pragma unroll
             for (int j = 0; j < SEG; ++j) {
-                const uint32_t dst = dstRow + uint32_t(r) * (128u * 128u) + ((uint32_t(sg * SEG + j) ^ swz) << 4);
+                const uint32_t dst = dstRow + uint32_t(r * ROW_STEP * 128) + ((uint32_t(sg * SEG + j) ^ swz) << 4);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src + 16 * j), "r"(bytes)
                              : "memory");
             }
@@ -213,17 +223,17 @@ __device__ __forceinline__ void gatherSegments(const GatherRow (&rows)[ROWS], co
     }
 }
 
-template <int ROWS>
+template <int ROWS, int ROW_STEP = 128>
 __device__ __forceinline__ void gatherBlock(const GatherRow (&rows)[ROWS], const int32_t *tapTab, int taps, int IC, int &t,
                                             int &c0, uint32_t dstRow, uint32_t swz, const int8_t *dummy) {
     if (IC >= 128) {
-        gatherSegments<8, ROWS>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
+        gatherSegments<8, ROWS, ROW_STEP>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
     } else if (IC == 64) {
-        gatherSegments<4, ROWS>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
+        gatherSegments<4, ROWS, ROW_STEP>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
     } else if (IC == 32) {
-        gatherSegments<2, ROWS>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
+        gatherSegments<2, ROWS, ROW_STEP>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
     } else {
-        gatherSegments<1, ROWS>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
+        gatherSegments<1, ROWS, ROW_STEP>(rows, tapTab, taps, IC, t, c0, dstRow, swz, dummy);
     }
 }
 
@@ -249,7 +259,7 @@ inline EncodeTiledFn encodeTiled() {
 
 // 3-D uint8 tensor map {d0 (contiguous), d1, d2} with a {b0, b1, 1} box and 128-byte swizzle.
 inline bool makeMap(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1,
-             uint64_t stride2, uint32_t b0, uint32_t b1) {
+             uint64_t stride2, uint32_t b0, uint32_t b1, bool swizzle128 = true) {
     EncodeTiledFn fn = encodeTiled();
     if (fn == nullptr) {
         setLastError("cuTensorMapEncodeTiled is not available from the driver");
@@ -260,7 +270,8 @@ inline bool makeMap(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1
     const cuuint32_t box[3] = {b0, b1, 1};
     const cuuint32_t elemStrides[3] = {1, 1, 1};
     const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box,
-                           elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) {
         setLastError("cuTensorMapEncodeTiled failed with code " + std::to_string(int(rc)));
