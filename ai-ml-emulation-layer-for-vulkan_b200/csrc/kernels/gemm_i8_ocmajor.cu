@@ -4,8 +4,10 @@
 //   D[oc, pix] = sum_k W[oc, k] * X[pix, k]
 //
 //   A operand  - weight tile, 128 output channels x 128 K bytes, TMA from the OHWI weight matrix [OC][K]
-//   B operand  - BNP (128 or 256) output pixels x 128 K bytes: TMA from a row-major pixel matrix (1x1
-//                stride-1 convolution), else gathered with 16-byte cp.async (segment gather)
+//   B operand  - BNP (128 or 256) output pixels x 128 K bytes: TMA tiles of a row-major pixel matrix (1x1
+//                stride-1 convolution); TMA in im2col mode when the channel count is a multiple of 128 (one
+//                instruction fetches one tap, 128 channels, of all the tile's windows, zero-filled outside
+//                the image); else gathered with 16-byte cp.async (segment gather)
 //   accumulator- TMEM lane = output channel, TMEM column = pixel; two accumulators of BNP columns alternate
 //   C/D tile   - a [BNP pixels][128 channels] byte tile in shared memory, two of them alternating with the
 //                accumulators: TMA brings the shortcut bytes of the residual tail into it, the epilogue
@@ -54,6 +56,8 @@ constexpr int kOcThreadsGather = (kOcEpiWarps + 2) * 32 + kOcGatherThreads;
 __device__ __forceinline__ void ocEpilogueSync() {
     asm volatile("bar.sync 1, %0;" ::"r"(kOcEpiWarps * 32) : "memory");
 }
+
+constexpr int kXGather = 0, kXTiled = 1, kXIm2col = 2;
 
 struct __align__(8) OcBarriers {
     uint64_t full[8];
@@ -191,11 +195,13 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     const bool storer = warp == 0 && lane == 0; // issues the tile stores and tracks their completion
     uint32_t tileCount = 0;
     for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
+        // pixel tile fastest, then channel tile: a CTA's consecutive tiles mostly share their channels, so the
+        // per-channel constants are reloaded rarely
         int64_t tt = t;
-        const int c0 = int(tt % cTiles) * kOcTile;
-        tt /= cTiles;
         const int m0 = int(tt % pTiles) * BNP;
-        const int batch = int(tt / pTiles);
+        tt /= pTiles;
+        const int c0 = int(tt % cTiles) * kOcTile;
+        const int batch = int(tt / cTiles);
         const uint32_t buf = tileCount & 1u;
         const uint32_t par = (tileCount >> 1) & 1u;
         const int oc = c0 + quarter * 32 + lane;
@@ -317,10 +323,11 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     }
 }
 
-// X_TMA: the pixel operand comes through tmapX; otherwise it is gathered from the NHWC input described by p.
+// X_MODE: how the pixel operand arrives: kXGather = gathered from the NHWC input described by p, kXTiled = tmapX
+// is a plain matrix, kXIm2col = tmapX is an im2col map of the NHWC input.
 // RESIDUAL: the fused residual tail is present (tmapC describes the shortcut tensor).
-template <int BNP, int NSTAGE, bool X_TMA, bool RESIDUAL>
-__global__ void __launch_bounds__(X_TMA ? kOcThreadsTma : kOcThreadsGather, 1)
+template <int BNP, int NSTAGE, int X_MODE, bool RESIDUAL>
+__global__ void __launch_bounds__(X_MODE != kXGather ? kOcThreadsTma : kOcThreadsGather, 1)
 gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CUtensorMap tmapW,
               const __grid_constant__ CUtensorMap tmapC, const __grid_constant__ CUtensorMap tmapD, const GemmI8Params p) {
     extern __shared__ uint8_t rawSmem[];
@@ -337,6 +344,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     int32_t *tapTab = reinterpret_cast<int32_t *>(clsTab + 2 * BNP);
     OcBarriers *bars = reinterpret_cast<OcBarriers *>(tapTab + kTapTabEntries);
 
+    constexpr bool X_TMA = X_MODE != kXGather;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int numKb = (p.K + BK - 1) / BK;
@@ -345,10 +353,10 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     const int64_t numTiles = int64_t(pTiles) * cTiles * p.batches;
     const auto tileOf = [&](int64_t t) {
         OcTile c;
-        c.c0 = int(t % cTiles) * kOcTile;
-        t /= cTiles;
         c.m0 = int(t % pTiles) * BNP;
-        c.batch = int(t / pTiles);
+        t /= pTiles;
+        c.c0 = int(t % cTiles) * kOcTile;
+        c.batch = int(t / cTiles);
         return c;
     };
 
@@ -397,6 +405,15 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
             bool ok = true;
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileCount) {
                 const OcTile tc = tileOf(t);
+                // im2col mode: first tap of the tile's first window, and the running position on the K axis
+                int w0 = 0, h0 = 0, n0 = 0, kx = 0, ky = 0, cb = 0;
+                if (X_MODE == kXIm2col) {
+                    n0 = tc.m0 / (p.OH * p.OW);
+                    const int rem = tc.m0 - n0 * p.OH * p.OW;
+                    const int oy = rem / p.OW;
+                    h0 = oy * p.strideY - p.padTop;
+                    w0 = (rem - oy * p.OW) * p.strideX - p.padLeft;
+                }
                 for (int kb = 0; kb < numKb; ++kb, ++it) {
                     const int s = int(it % NSTAGE);
                     const uint32_t phase = (it / NSTAGE) & 1u;
@@ -406,12 +423,23 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                     }
                     mbarArriveExpectTx(&bars->full[s], uint32_t(kTileW + (X_TMA ? kTileX : 0)));
                     tmaLoad3d(&tmapW, tilesW + s * kTileW, &bars->full[s], kb * BK, tc.c0, 0);
-                    if (X_TMA) {
+                    if (X_MODE == kXTiled) {
                         // boxes hold at most 256 rows of 128 bytes: one copy per 128 pixels
 #pragma unroll
                         for (int h = 0; h < BNP / 128; ++h) {
                             tmaLoad3d(&tmapX, tilesX + s * kTileX + h * 128 * BK, &bars->full[s], kb * BK, tc.m0 + h * 128,
                                       tc.batch);
+                        }
+                    } else if (X_MODE == kXIm2col) {
+                        tmaLoadIm2col4d(&tmapX, tilesX + s * kTileX, &bars->full[s], cb, w0, h0, n0, uint16_t(kx * p.dilX),
+                                        uint16_t(ky * p.dilY));
+                        cb += BK;
+                        if (cb >= p.IC) {
+                            cb = 0;
+                            if (++kx == p.KW) {
+                                kx = 0;
+                                ++ky;
+                            }
                         }
                     }
                 }
@@ -513,13 +541,13 @@ struct OcMaps {
     CUtensorMap x, w, c, d;
 };
 
-template <int BNP, int NSTAGE, bool X_TMA, bool RESIDUAL>
+template <int BNP, int NSTAGE, int X_MODE, bool RESIDUAL>
 int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes = size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * size_t(BNP) * 128 +
                                  2 * 256 * sizeof(int32_t) + 2 * BNP + kTapTabEntries * sizeof(int32_t) +
                                  sizeof(OcBarriers) + 1024;
     static_assert(smemBytes <= 232448, "shared memory per CTA");
-    auto kernel = gemmI8OcMajor<BNP, NSTAGE, X_TMA, RESIDUAL>;
+    auto kernel = gemmI8OcMajor<BNP, NSTAGE, X_MODE, RESIDUAL>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smemBytes)) != cudaSuccess) {
@@ -530,7 +558,7 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     }
     const int64_t tiles = int64_t((p.M + BNP - 1) / BNP) * ((p.N + kOcTile - 1) / kOcTile) * p.batches;
     const int grid = int(tiles < smCount() ? tiles : smCount());
-    kernel<<<grid, X_TMA ? kOcThreadsTma : kOcThreadsGather, smemBytes, s>>>(maps.x, maps.w, maps.c, maps.d, p);
+    kernel<<<grid, X_MODE != kXGather ? kOcThreadsTma : kOcThreadsGather, smemBytes, s>>>(maps.x, maps.w, maps.c, maps.d, p);
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
         setLastError(std::string("tcgen05 channel-major convolution launch: ") + cudaGetErrorString(err));
@@ -539,12 +567,21 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     return MLEL_SUCCESS;
 }
 
+template <int BNP, int NSTAGE, int X_MODE>
+int launchOcMajorMode(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
+    return p.epi.hasResidual ? launchOcMajor<BNP, NSTAGE, X_MODE, true>(maps, p, s)
+                             : launchOcMajor<BNP, NSTAGE, X_MODE, false>(maps, p, s);
+}
+
 template <int BNP, int NSTAGE>
-int launchOcMajorShape(const OcMaps &maps, const GemmI8Params &p, bool xTma, cudaStream_t s) {
-    if (p.epi.hasResidual) {
-        return xTma ? launchOcMajor<BNP, NSTAGE, true, true>(maps, p, s) : launchOcMajor<BNP, NSTAGE, false, true>(maps, p, s);
+int launchOcMajorShape(const OcMaps &maps, const GemmI8Params &p, int xMode, cudaStream_t s) {
+    if (xMode == kXTiled) {
+        return launchOcMajorMode<BNP, NSTAGE, kXTiled>(maps, p, s);
     }
-    return xTma ? launchOcMajor<BNP, NSTAGE, true, false>(maps, p, s) : launchOcMajor<BNP, NSTAGE, false, false>(maps, p, s);
+    if (xMode == kXIm2col) {
+        return launchOcMajorMode<BNP, NSTAGE, kXIm2col>(maps, p, s);
+    }
+    return launchOcMajorMode<BNP, NSTAGE, kXGather>(maps, p, s);
 }
 
 } // namespace
@@ -579,17 +616,24 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
     const int64_t sms = smCount();
     const bool wide = ((t256 + sms - 1) / sms) * 2 <= (t128 + sms - 1) / sms;
     OcMaps maps{};
-    const bool xTma = q.aMatrix != nullptr;
-    if (xTma && !makeMap(&maps.x, q.aMatrix, uint64_t(p.K), uint64_t(p.M), uint64_t(q.batches), uint64_t(q.aRowBytes),
-                         uint64_t(q.aBatchBytes), BK, 128)) {
-        return MLEL_ERROR_DEVICE;
+    const uint32_t boxPixels = wide ? 256u : 128u;
+    int xMode = kXGather;
+    if (q.aMatrix != nullptr) {
+        if (!makeMap(&maps.x, q.aMatrix, uint64_t(p.K), uint64_t(p.M), uint64_t(q.batches), uint64_t(q.aRowBytes),
+                     uint64_t(q.aBatchBytes), BK, 128)) {
+            return MLEL_ERROR_DEVICE;
+        }
+        xMode = kXTiled;
+    } else if (p.gatherTable == nullptr && p.IC % 128 == 0 && (reinterpret_cast<uintptr_t>(p.in) & 15u) == 0 &&
+               makeIm2colMap(&maps.x, p.in, p.M / (p.OH * p.OW), p.H, p.W, p.IC, p.KH, p.KW, p.padTop, p.padLeft, p.OH, p.OW,
+                             p.strideY, p.strideX, p.dilY, p.dilX, boxPixels)) {
+        xMode = kXIm2col;
     }
     if (!makeMap(&maps.w, q.bMatrix, uint64_t(p.K), uint64_t(p.N), 1, uint64_t(q.bRowBytes),
                  uint64_t(q.bRowBytes) * uint64_t(p.N), BK, kOcTile)) {
         return MLEL_ERROR_DEVICE;
     }
     // output and shortcut: [pixels][channels] bytes, unswizzled tiles of 128 channels x (128 or 256) pixels
-    const uint32_t boxPixels = wide ? 256u : 128u;
     const uint64_t plane = uint64_t(p.ldOut) * uint64_t(p.M);
     if (!makeMap(&maps.d, p.out8, uint64_t(p.N), uint64_t(p.M), 1, uint64_t(p.ldOut), plane, kOcTile, boxPixels, false)) {
         return MLEL_ERROR_DEVICE;
@@ -598,7 +642,7 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
         !makeMap(&maps.c, p.epi.shortcut, uint64_t(p.N), uint64_t(p.M), 1, uint64_t(p.ldOut), plane, kOcTile, boxPixels, false)) {
         return MLEL_ERROR_DEVICE;
     }
-    return wide ? launchOcMajorShape<256, 3>(maps, p, xTma, s) : launchOcMajorShape<128, 5>(maps, p, xTma, s);
+    return wide ? launchOcMajorShape<256, 3>(maps, p, xMode, s) : launchOcMajorShape<128, 5>(maps, p, xMode, s);
 }
 
 int ocMajorErrorWord() { return tc::readErrorWord(); }

@@ -58,16 +58,19 @@ __device__ __forceinline__ bool mbarTryWait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: returns false (and records `code`) when the barrier did not complete in time.  Between
-// polls the waiter sleeps `sleepNs` so that a waiting role does not take issue slots from the warps that
-// share its scheduler (the epilogue warps do the arithmetic).
+// polls the waiter sleeps, a little longer each time up to a quarter of a microsecond, so that a waiting role
+// does not take issue slots from the warps that share its scheduler (the epilogue warps do the arithmetic);
+// the clock is read every 16th poll.
 __device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int code, unsigned sleepNs = 32) {
     if (mbarTryWait(bar, parity)) {
         return true;
     }
     const long long start = clock64();
+    unsigned polls = 0;
     while (!mbarTryWait(bar, parity)) {
         __nanosleep(sleepNs);
-        if (clock64() - start > kWaitLimitCycles) {
+        sleepNs = sleepNs < 256u ? sleepNs * 2u : 256u;
+        if ((++polls & 15u) == 0 && clock64() - start > kWaitLimitCycles) {
             atomicCAS(&g_tcgen05Error, 0, code);
             return false;
         }
@@ -80,6 +83,19 @@ __device__ __forceinline__ void tmaLoad3d(const CUtensorMap *map, void *dst, uin
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
+}
+
+// TMA load in im2col mode from an NHWC tensor {C, W, H, N}: pixelsPerColumn consecutive window positions
+// (x fastest, then y, then image; stepping by the convolution stride inside the map's bounding box) starting
+// at the window whose first tap is at input pixel (w, h) of image n; of each window the tap at offset
+// (offW, offH) from the first one is read, channelsPerPixel channels from channel c on.  Positions outside
+// the tensor read zeros.
+__device__ __forceinline__ void tmaLoadIm2col4d(const CUtensorMap *map, void *dst, uint64_t *bar, int c, int w, int h, int n,
+                                                uint16_t offW, uint16_t offH) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(smemAddr(dst)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(offW), "h"(offH)
+                 : "memory");
 }
 
 // Shared-memory matrix descriptor for a SWIZZLE_128B tile whose 8-row groups are 1024 bytes apart.
@@ -278,6 +294,55 @@ inline bool makeMap(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1
         return false;
     }
     return true;
+}
+
+using EncodeIm2colFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t,
+                                    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+inline EncodeIm2colFn encodeIm2col() {
+    static EncodeIm2colFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &sym, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeIm2colFn>(sym);
+        }
+    });
+    return fn;
+}
+
+// Im2col tensor map over an int8 NHWC tensor for a convolution window: 128 channels per pixel (one 128-byte
+// swizzled row per window position), `pixels` window positions per load.  The bounding box of the windows'
+// first taps runs from -pad to the last position a window still fits with its far-side padding.
+// Returns false without setting an error text when the driver refuses the geometry.
+inline bool makeIm2colMap(CUtensorMap *map, const void *base, int N, int H, int W, int C, int KH, int KW, int padTop,
+                          int padLeft, int OH, int OW, int strideY, int strideX, int dilY, int dilX, uint32_t pixels) {
+    EncodeIm2colFn fn = encodeIm2col();
+    if (fn == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[4] = {cuuint64_t(C), cuuint64_t(W), cuuint64_t(H), cuuint64_t(N)};
+    const cuuint64_t strides[3] = {cuuint64_t(C), cuuint64_t(C) * W, cuuint64_t(C) * W * H};
+    // the last window of a row starts at (OW - 1) * stride - pad; relative to the tensor's last pixel W - 1
+    const int lower[2] = {-padLeft, -padTop};
+    const int upper[2] = {(OW - 1) * strideX - padLeft - (W - 1), (OH - 1) * strideY - padTop - (H - 1)};
+    for (int i = 0; i < 2; ++i) {
+        if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) {
+            return false;
+        }
+    }
+    if ((KW - 1) * dilX > 255 || (KH - 1) * dilY > 255 || strideX > 8 || strideY > 8) {
+        return false;
+    }
+    const cuuint32_t elemStrides[4] = {1, cuuint32_t(strideX), cuuint32_t(strideY), 1};
+    const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, lower, upper, 128,
+                           pixels, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
 }
 
 inline int smCount() {

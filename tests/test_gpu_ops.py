@@ -57,6 +57,12 @@ CONV_CASES = [
     (2, 15, 15, 16, 16, 5, 2, 2, 1, 1, 0),
     (1, 20, 20, 16, 96, 7, 3, 2, 1, -2, 0),
     (2, 11, 11, 256, 128, 3, 1, 1, 1, 12, 0),
+    # channel counts that are multiples of 128 with more than 64 output channels (hardware im2col loads):
+    # dilation, stride 2 over an odd size, a 5x5 window, and a tile that spans several images
+    (1, 12, 12, 128, 96, 3, 2, 1, 2, 5, 0),
+    (2, 15, 15, 128, 80, 3, 1, 2, 1, -4, 0),
+    (1, 9, 9, 128, 96, 5, 2, 1, 1, 3, 0),
+    (40, 7, 7, 128, 144, 3, 1, 1, 1, -8, 0),
 ]
 
 
@@ -89,6 +95,21 @@ def test_conv2d_asymmetric_padding_and_stride(mlel):
     y = g.rescale(y, [1 << 30], [38], 0, -1, np.int8, True, False, False)
     g.output(y)
     check(mlel, g, [r.integers(-128, 128, (1, 9, 10, 8), dtype=np.int8)])
+
+
+def test_conv2d_asymmetric_padding_many_channels(mlel):
+    """The same geometry on the 128-channel path (hardware im2col loads): uneven padding, a 2x3 window,
+    different strides per axis, more than 64 output channels, residual-free RESCALE with small shifts."""
+    r = rng(5)
+    g = GraphBuilder()
+    x = g.input(np.int8, (3, 9, 10, 128))
+    wt = g.constant(r.integers(-128, 128, (80, 2, 3, 128), dtype=np.int8))
+    b = g.constant(r.integers(-(1 << 14), 1 << 14, (80,), dtype=np.int32))
+    y = g.conv2d(x, wt, b, [0, 1, 2, 0], [1, 2], [1, 1], 9, 0)
+    mult = r.integers(1 << 30, (1 << 31) - 1, (80,), dtype=np.int64).astype(np.int32)
+    y = g.rescale(y, mult, r.integers(28, 44, (80,), dtype=np.int8), 0, -1, np.int8, True, True, True)
+    g.output(y)
+    check(mlel, g, [r.integers(-128, 128, (3, 9, 10, 128), dtype=np.int8)])
 
 
 def test_conv2d_int16_int64(mlel):
