@@ -397,6 +397,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmemBase = bars->tmemBase;
+    gridDependencySync(); // from here on activations are read and written
 
     if (warp == kOcTmaWarp) {
         // ---------------- TMA producer ----------------
@@ -558,8 +559,8 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     }
     const int64_t tiles = int64_t((p.M + BNP - 1) / BNP) * ((p.N + kOcTile - 1) / kOcTile) * p.batches;
     const int grid = int(tiles < smCount() ? tiles : smCount());
-    kernel<<<grid, X_MODE != kXGather ? kOcThreadsTma : kOcThreadsGather, smemBytes, s>>>(maps.x, maps.w, maps.c, maps.d, p);
-    const cudaError_t err = cudaGetLastError();
+    const cudaError_t err = launchDependent(kernel, grid, X_MODE != kXGather ? kOcThreadsTma : kOcThreadsGather, smemBytes,
+                                            s, maps.x, maps.w, maps.c, maps.d, p);
     if (err != cudaSuccess) {
         setLastError(std::string("tcgen05 channel-major convolution launch: ") + cudaGetErrorString(err));
         return MLEL_ERROR_DEVICE;

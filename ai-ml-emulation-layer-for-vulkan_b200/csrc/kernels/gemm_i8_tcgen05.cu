@@ -410,6 +410,7 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmemBase = bars->tmemBase;
+    gridDependencySync(); // from here on activations are read and written
 
     if (warp == kTmaWarp) {
         // ---------------- TMA producer ----------------
@@ -599,8 +600,7 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8
     }
     const int64_t tiles = int64_t((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batches;
     const int grid = int(tiles < smCount() ? tiles : smCount()); // persistent: one CTA per SM
-    kernel<<<grid, A_TMA ? kThreadsTma : kThreadsGather, smemBytes, s>>>(mapA, mapB, p);
-    const cudaError_t err = cudaGetLastError();
+    const cudaError_t err = launchDependent(kernel, grid, A_TMA ? kThreadsTma : kThreadsGather, smemBytes, s, mapA, mapB, p);
     if (err != cudaSuccess) {
         setLastError(std::string("tcgen05 int8 GEMM launch: ") + cudaGetErrorString(err));
         return MLEL_ERROR_DEVICE;

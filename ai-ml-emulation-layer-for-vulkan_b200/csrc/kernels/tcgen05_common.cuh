@@ -6,8 +6,10 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 #include <string>
+#include <utility>
 
 #include "device_common.cuh"
 
@@ -146,6 +148,17 @@ __device__ __forceinline__ void tmemWait16(uint32_t (&r)[16]) {
                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
                  :
                  : "memory");
+}
+
+// Programmatic dependent launch.  A kernel launched with launchDependent() may start while the kernel before
+// it in the stream is still running (on SMs that kernel has already left): everything up to this call - barrier
+// and TMEM set-up, tables built from graph constants - overlaps the predecessor's tail.  The wait returns when
+// the predecessor has completed and its writes are visible; nothing before it may touch memory that another
+// kernel of the stream writes or reads for writing later.  The trigger lets the successor start as early as
+// it finds room.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void gridDependencySync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // Barrier among the epilogue warps only (named barrier 1).
@@ -343,6 +356,24 @@ inline bool makeIm2colMap(CUtensorMap *map, const void *base, int N, int H, int 
                            pixels, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return rc == CUDA_SUCCESS;
+}
+
+// Launches `kernel` so that it may overlap the end of its predecessor in the stream (see gridDependencySync).
+template <class... Params, class... Args>
+inline cudaError_t launchDependent(void (*kernel)(Params...), int grid, int threads, size_t smemBytes, cudaStream_t stream,
+                                   Args &&...args) {
+    static const bool disabled = getenv("MLEL_NO_DEPENDENT_LAUNCH") != nullptr;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(unsigned(threads));
+    cfg.dynamicSmemBytes = smemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = disabled ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 inline int smCount() {
