@@ -61,7 +61,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu_index), "-lms", "100"], stdout=self.file,
+                                          "-i", str(self.gpu_index), "-lms", "50"], stdout=self.file,
                                          stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -112,29 +112,44 @@ def graph_stats(graph):
     return conv_macs, other_macs
 
 
+class CpuReference:
+    """The CPU oracle (one kernel per operator, all host threads) on a bounded sample of the benchmark
+    workload: the same graph at a batch small enough that one pass takes about `target_seconds`."""
+
+    def __init__(self, target_seconds: float):
+        from __graft_entry__ import load_package
+        load_package()
+        from mlel_b200.model_graphs import resnet50_graph
+        from oracle import oracle
+        from tests.graph_eval import evaluate
+        oracle.build()
+        self.evaluate = evaluate
+        self.cores = os.cpu_count() or 1
+        g, inputs = resnet50_graph(seed=0, n=1, image=IMAGE)
+        evaluate(g, inputs)  # warm-up (page-in, thread pool)
+        t0 = time.perf_counter()
+        evaluate(g, inputs)
+        per_image = time.perf_counter() - t0
+        self.n = int(max(1, min(BATCH_PER_GPU, target_seconds / max(per_image, 1e-6))))
+        self.graph, self.inputs = resnet50_graph(seed=0, n=self.n, image=IMAGE)
+
+    def step(self):
+        """One pass over the sample; returns (images/s, seconds)."""
+        t0 = time.perf_counter()
+        self.evaluate(self.graph, self.inputs)
+        dt = time.perf_counter() - t0
+        return self.n / dt, dt
+
+    def describe(self, value: float, dt: float):
+        return {"value": value, "unit": "images/s", "cores": self.cores, "kind": "port",
+                "sample": f"{self.n} of {BATCH_PER_GPU} images of the same graph per pass, {dt:.2f} s per pass, OpenMP "
+                          f"over {self.cores} host threads"}
+
+
 def cpu_reference_rate(target_seconds: float = 10.0):
-    """images/s of the CPU oracle (one kernel per operator, all host threads) on a bounded sample of the
-    benchmark workload: the same graph at a batch small enough to finish in about target_seconds."""
-    from __graft_entry__ import load_package
-    load_package()
-    from mlel_b200.model_graphs import resnet50_graph
-    from oracle import oracle
-    from tests.graph_eval import evaluate
-    oracle.build()
-    cores = os.cpu_count() or 1
-    g, inputs = resnet50_graph(seed=0, n=2, image=IMAGE)
-    evaluate(g, inputs)  # warm-up (page-in, thread pool)
-    t0 = time.perf_counter()
-    evaluate(g, inputs)
-    per_image = (time.perf_counter() - t0) / 2
-    n = int(max(2, min(BATCH_PER_GPU, target_seconds / max(per_image, 1e-6))))
-    g, inputs = resnet50_graph(seed=0, n=n, image=IMAGE)
-    t0 = time.perf_counter()
-    evaluate(g, inputs)
-    dt = time.perf_counter() - t0
-    return {"value": n / dt, "unit": "images/s", "cores": cores, "kind": "port",
-            "sample": f"{n} of {BATCH_PER_GPU} images of the same graph, one pass, {dt:.2f} s, OpenMP over "
-                      f"{cores} host threads"}
+    ref = CpuReference(target_seconds)
+    value, dt = ref.step()
+    return ref.describe(value, dt)
 
 
 def run_reference_arm(args):
@@ -142,10 +157,13 @@ def run_reference_arm(args):
     if rank != 0:
         return
     steps = max(1, args.steps)
-    results = [cpu_reference_rate(target_seconds=max(2.0, 20.0 / steps)) for _ in range(args.warmup + steps)]
-    timed = results[args.warmup:]
-    value = float(np.mean([r["value"] for r in timed]))
-    base = dict(timed[-1], value=value)
+    # the whole run (warm-up and timed passes) is sized to about two minutes of CPU work
+    ref = CpuReference(target_seconds=max(0.1, 120.0 / (steps + args.warmup)))
+    for _ in range(args.warmup):
+        ref.step()
+    timed = [ref.step() for _ in range(steps)]
+    seconds = sum(dt for _, dt in timed)
+    value = ref.n * steps / seconds
     line = {
         "impl": "reference", "metric": "int8 TOSA ResNet-50 images/s", "value": value, "unit": "images/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": 1e3 * BATCH_PER_GPU / value,
@@ -153,8 +171,9 @@ def run_reference_arm(args):
         "data": "synthetic",
         "config": {"workload": "BASELINE configs[3]: ResNet-50-shaped int8 TOSA graph, 224x224x3, bounded sample per step",
                    "note": "the reference has no CPU path and no Vulkan stack exists on this box; this is the CPU "
-                           "restatement of its shaders (oracle/), one kernel per operator"},
-        "cpu_baseline": base,
+                           "restatement of its shaders (oracle/), one kernel per operator; ms_per_step is scaled to "
+                           "the 64-image step of the GPU arm"},
+        "cpu_baseline": ref.describe(value, seconds / steps),
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -163,7 +182,7 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU (benchmark value: 64)")
