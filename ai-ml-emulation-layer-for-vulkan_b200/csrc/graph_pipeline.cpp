@@ -953,12 +953,25 @@ void GraphPipeline::prepareTensorCore() {
             }
         } else {
             const TensorDescriptor &b = tensor(op.in[1]);
-            if (b.cls != TensorClass::Constant || !b.packed() || b.dtype != MLEL_I8 || op.i[1] != 0) {
+            if (!b.packed() || b.dtype != MLEL_I8 || op.i[1] != 0 || b.dims.size() != 3) {
                 continue;
             }
             const int64_t Nb = b.dims[0], C = b.dims[1], W = b.dims[2];
             if (in.dims[0] != Nb || in.dims[2] != C || C % 16 != 0 || C > 65536 ||
                 out.numel() >= (int64_t(1) << 31) || in.numel() >= (int64_t(1) << 31)) {
+                continue;
+            }
+            if (b.cls != TensorClass::Constant) {
+                // Second input produced at run time (tc == 3): a kernel in front of the product transposes it to
+                // the K-contiguous form the tensor core reads and sums its columns for the zero-point
+                // correction; both land in one scratch tensor: [Nb][W][C] bytes, then [Nb][W] int32.
+                if (W % 16 != 0 || b.numel() >= (int64_t(1) << 31)) {
+                    continue;
+                }
+                const int64_t btBytes = (Nb * W * C + 255) / 256 * 256;
+                op.scratch = addScratchTensor(MLEL_I8, {btBytes + Nb * W * 4});
+                op.auxi[2] = int32_t(btBytes);
+                op.tc = 3;
                 continue;
             }
             const auto *bdata = reinterpret_cast<const int8_t *>(b.hostData.data());

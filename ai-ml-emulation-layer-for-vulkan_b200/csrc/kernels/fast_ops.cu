@@ -35,6 +35,48 @@ __global__ void padImageKernel(const int8_t *__restrict__ in, int8_t *__restrict
     }
 }
 
+// ---- transpose of MATMUL's second input [N][C][W] -> [N][W][C] with column sums ---------------------------
+// A block owns 64 columns (w) of one batch and walks the rows (c) in tiles of 64: 16-byte loads of the
+// tile, byte transposition through shared memory, 16-byte stores; each thread keeps the running sum of the
+// bytes it moved, and four neighbouring lanes combine them into the column sum at the end.
+__global__ void __launch_bounds__(256) transposeColsumKernel(const int8_t *__restrict__ b, int8_t *__restrict__ bt,
+                                                             int32_t *__restrict__ corr, int C, int W, int32_t za) {
+    __shared__ int8_t tile[64][64 + 16]; // [c][w], rows padded to spread the banks of the column reads
+    const int n = blockIdx.y;
+    const int w0 = blockIdx.x * 64;
+    const int t = threadIdx.x;
+    const int8_t *src = b + int64_t(n) * C * W;
+    int8_t *dst = bt + int64_t(n) * W * C;
+    // load role: row (c) t / 4, 16-byte segment (w) t % 4; store role: column (w) t / 4, segment (c) t % 4
+    const int lr = t >> 2, ls = (t & 3) * 16;
+    int32_t sum = 0;
+    for (int c0 = 0; c0 < C; c0 += 64) {
+        int4 v = make_int4(0, 0, 0, 0);
+        if (c0 + lr < C && w0 + ls < W) {
+            v = __ldg(reinterpret_cast<const int4 *>(src + int64_t(c0 + lr) * W + w0 + ls));
+        }
+        *reinterpret_cast<int4 *>(&tile[lr][ls]) = v;
+        __syncthreads();
+        uint32_t words[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int8_t x = tile[ls + i][lr];
+            sum += x;
+            words[i >> 2] |= uint32_t(uint8_t(x)) << (8 * (i & 3));
+        }
+        if (w0 + lr < W && c0 + ls < C) {
+            *reinterpret_cast<int4 *>(dst + int64_t(w0 + lr) * C + c0 + ls) =
+                make_int4(int(words[0]), int(words[1]), int(words[2]), int(words[3]));
+        }
+        __syncthreads();
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if ((t & 3) == 0 && w0 + lr < W) {
+        corr[int64_t(n) * W + w0 + lr] = int32_t(uint32_t(0) - uint32_t(za) * uint32_t(sum));
+    }
+}
+
 // ---- MAX_POOL2D, int8 NHWC, C % 16 == 0 (maxpool2d.comp:23-72) --------------------------------------
 // One thread per (pixel, 16-channel group): 16-byte loads, per-byte signed max, one 16-byte store.
 __global__ void maxPoolI8Kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int64_t total, int H, int W,
@@ -87,6 +129,12 @@ int padImageI8(const int8_t *in, int8_t *out, int N, int H, int W, int C, int Hp
     const int64_t words = int64_t(N) * Hp * Wp * (Cp >> 2);
     padImageKernel<<<gridFor(words, kThreads, 8), kThreads, 0, s>>>(in, out, words, H, W, C, Hp, Wp, Cp, padTop, padLeft);
     return finish("padded copy");
+}
+
+int transposeForMatmul(const int8_t *b, int8_t *bt, int32_t *corr, int batches, int C, int W, int32_t za, cudaStream_t s) {
+    const dim3 grid(unsigned((W + 63) / 64), unsigned(batches));
+    transposeColsumKernel<<<grid, 256, 0, s>>>(b, bt, corr, C, W, za);
+    return finish("MATMUL operand transpose");
 }
 
 bool maxPoolI8Eligible(const TView &in, const TView &out) {

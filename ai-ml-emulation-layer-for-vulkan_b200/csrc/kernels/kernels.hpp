@@ -45,6 +45,8 @@ int fusedAdd(const int8_t *x, const int8_t *y, int8_t *out, int64_t n, const Dev
 // fast_ops.cu: vectorised kernels for packed int8 NHWC tensors
 int padImageI8(const int8_t *in, int8_t *out, int N, int H, int W, int C, int Hp, int Wp, int Cp, int padTop, int padLeft,
                cudaStream_t s);
+// bt[n][w][c] = b[n][c][w]; corr[n][w] = -za * sum_c b[n][c][w] (mod 2^32).  C and W multiples of 16.
+int transposeForMatmul(const int8_t *b, int8_t *bt, int32_t *corr, int batches, int C, int W, int32_t za, cudaStream_t s);
 bool maxPoolI8Eligible(const TView &in, const TView &out);
 int maxPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s);
 

@@ -155,17 +155,33 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     return gemmI8OcMajorApplies(q) ? gemmI8OcMajorLaunch(q, s) : gemmI8Launch(q, s);
 }
 
-// MATMUL / fused MATMUL with a constant, pre-transposed second input.
+// MATMUL / fused MATMUL: second input constant and pre-transposed (tc == 1), or transposed here (tc == 3).
 int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
-    const TView &a = T[op.in[0]], &bt = T[op.aux[3]], &out = T[op.out[0]];
+    const TView &a = T[op.in[0]], &out = T[op.out[0]];
     GemmI8Problem q{};
     GemmI8Params &p = q.params;
     p.M = int32_t(a.dims[1]);
-    p.N = int32_t(bt.dims[1]);
     p.K = int32_t(a.dims[2]);
+    const void *bt = nullptr;
+    if (op.tc == 3) {
+        const TView &b = T[op.in[1]];
+        p.N = int32_t(b.dims[2]);
+        int8_t *scratch = reinterpret_cast<int8_t *>(T[op.scratch].ptr);
+        int32_t *corr = reinterpret_cast<int32_t *>(scratch + op.auxi[2]);
+        const int rc = transposeForMatmul(reinterpret_cast<const int8_t *>(b.ptr), scratch, corr, int(b.dims[0]), p.K, p.N,
+                                          op.i[0], s);
+        if (rc != MLEL_SUCCESS) {
+            return rc;
+        }
+        bt = scratch;
+        p.corr = corr;
+    } else {
+        p.N = int32_t(T[op.aux[3]].dims[1]);
+        bt = T[op.aux[3]].ptr;
+        p.corr = reinterpret_cast<const int32_t *>(T[op.aux[0]].ptr);
+    }
     p.ldOut = p.N;
     p.batchedB = 1;
-    p.corr = reinterpret_cast<const int32_t *>(T[op.aux[0]].ptr);
     p.numClasses = 1;
     p.numColClasses = 1;
     p.batchedCorr = 1;
@@ -179,7 +195,7 @@ int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     q.aMatrix = a.ptr;
     q.aRowBytes = uint64_t(p.K);
     q.aBatchBytes = uint64_t(p.K) * uint64_t(p.M);
-    q.bMatrix = bt.ptr;
+    q.bMatrix = bt;
     q.bRowBytes = uint64_t(p.K);
     q.bBatchBytes = uint64_t(p.K) * uint64_t(p.N);
     q.bMnMajor = false;
@@ -200,7 +216,8 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         if (aligned && (op.kind == OP_CONV2D || op.kind == OP_FUSED_CONV2D)) {
             return launchConvTensorCore(op, T, s);
         }
-        if (aligned && (op.kind == OP_MATMUL || op.kind == OP_FUSED_MATMUL)) {
+        if (aligned && (op.kind == OP_MATMUL || op.kind == OP_FUSED_MATMUL) &&
+            (op.tc != 3 || (reinterpret_cast<uintptr_t>(in(1).ptr) & 15u) == 0)) {
             return launchMatmulTensorCore(op, T, s);
         }
     }

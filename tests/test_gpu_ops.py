@@ -144,7 +144,8 @@ def test_depthwise_conv2d(mlel, case, with_rescale):
 
 
 @pytest.mark.parametrize("shape", [(1, 4, 8, 4), (3, 5, 7, 9), (2, 16, 33, 16), (1, 1, 1, 1), (2, 128, 64, 128),
-                                   (1, 130, 200, 72), (4, 64, 1024, 64)])
+                                   (1, 130, 200, 72), (4, 64, 1024, 64), (3, 100, 48, 80), (2, 70, 32, 272),
+                                   (5, 384, 64, 384)])
 @pytest.mark.parametrize("zps", [(0, 0), (-7, 0), (5, -3)])
 @pytest.mark.parametrize("with_rescale", [False, True])
 def test_matmul(mlel, shape, zps, with_rescale):
