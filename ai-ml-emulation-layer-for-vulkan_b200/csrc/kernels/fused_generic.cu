@@ -106,6 +106,99 @@ __global__ void fusedDepthwiseKernel(TView in, TView w, TView bias, TView out, C
     }
 }
 
+// ---- DEPTHWISE_CONV2D 3x3, packed int8 NHWC, channel multiplier 1 (depthwise_conv2d.comp:31-78) ----------
+// Memory-bound shape of a MobileNet block.  A thread owns four channels (one 32-bit word) of PX consecutive
+// output pixels of one row: the 36 weights of its channels live in registers for all of them, every input
+// word is loaded once per row of the window and serves up to three neighbouring outputs, and each output
+// pixel is one 32-bit store.  Out-of-range taps read the input zero point instead of being skipped, which
+// gives the same sum: (zp - zp) * w = 0.  SX = x stride (1 or 2); the y stride is free; dilation is 1.
+// OUT8: fused RESCALE(+CLAMP) to int8, else the raw int32 result.
+template <int PX, int SX, bool OUT8>
+__global__ void depthwise3x3Kernel(const int8_t *__restrict__ in, const int8_t *__restrict__ w,
+                                   const int32_t *__restrict__ bias, int biasCount, void *__restrict__ out, int N, int H,
+                                   int W, int C, int OH, int OW, ConvAttr a, DevEpilogue epi) {
+    constexpr int COLS = (PX - 1) * SX + 3;
+    const int cw = C >> 2;
+    const int groupsX = (OW + PX - 1) / PX;
+    const int64_t total = int64_t(N) * OH * groupsX * cw;
+    const uint32_t zword = uint32_t(uint8_t(a.inZp)) * 0x01010101u;
+    GRID_STRIDE(e, total) {
+        int64_t t = e;
+        const int c0 = int(t % cw) * 4;
+        t /= cw;
+        const int ox0 = int(t % groupsX) * PX;
+        t /= groupsX;
+        const int oy = int(t % OH);
+        const int n = int(t / OH);
+        int32_t acc[PX][4];
+#pragma unroll
+        for (int px = 0; px < PX; ++px) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[px][k] = 0;
+            }
+        }
+        int32_t wsum[4] = {0, 0, 0, 0};
+        const int x0 = ox0 * SX - a.pad[2];
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+            const int y = oy * a.stride[0] - a.pad[0] + ky;
+            const bool rowOk = y >= 0 && y < H;
+            const int8_t *row = in + ((int64_t(n) * H + (rowOk ? y : 0)) * W) * C + c0;
+            uint32_t cols[COLS];
+#pragma unroll
+            for (int i = 0; i < COLS; ++i) {
+                const int x = x0 + i;
+                cols[i] = (rowOk && x >= 0 && x < W) ? __ldg(reinterpret_cast<const uint32_t *>(row + int64_t(x) * C)) : zword;
+            }
+#pragma unroll
+            for (int kx = 0; kx < 3; ++kx) {
+                const uint32_t wword = __ldg(reinterpret_cast<const uint32_t *>(w + (ky * 3 + kx) * C + c0));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int32_t wt = int32_t(int8_t(wword >> (8 * k))) - a.wZp;
+                    wsum[k] += wt;
+#pragma unroll
+                    for (int px = 0; px < PX; ++px) {
+                        const int32_t x = int32_t(int8_t(cols[px * SX + kx] >> (8 * k)));
+                        acc[px][k] = int32_t(uint32_t(acc[px][k]) + uint32_t(x) * uint32_t(wt));
+                    }
+                }
+            }
+        }
+        int32_t add[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int32_t b = __ldg(bias + (biasCount == 1 ? 0 : c0 + k));
+            add[k] = int32_t(uint32_t(b) - uint32_t(a.inZp) * uint32_t(wsum[k]));
+        }
+#pragma unroll
+        for (int px = 0; px < PX; ++px) {
+            const int ox = ox0 + px;
+            if (ox >= OW) {
+                break;
+            }
+            const int64_t flat = ((int64_t(n) * OH + oy) * OW + ox) * C + c0;
+            if (OUT8) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int32_t v = int32_t(uint32_t(acc[px][k]) + uint32_t(add[k]));
+                    word |= uint32_t(uint8_t(epilogue(epi, v, uint32_t(c0 + k), flat + k))) << (8 * k);
+                }
+                *reinterpret_cast<uint32_t *>(static_cast<int8_t *>(out) + flat) = word;
+            } else {
+                int4 v;
+                v.x = int32_t(uint32_t(acc[px][0]) + uint32_t(add[0]));
+                v.y = int32_t(uint32_t(acc[px][1]) + uint32_t(add[1]));
+                v.z = int32_t(uint32_t(acc[px][2]) + uint32_t(add[2]));
+                v.w = int32_t(uint32_t(acc[px][3]) + uint32_t(add[3]));
+                *reinterpret_cast<int4 *>(static_cast<int32_t *>(out) + flat) = v;
+            }
+        }
+    }
+}
+
 __global__ void fusedMatmulKernel(TView a, TView b, TView out, int32_t zpA, int32_t zpB, DevEpilogue epi) {
     const int64_t total = numelOf(out);
     const uint32_t K = a.dims[2];
@@ -180,6 +273,60 @@ int fusedDepthwiseGeneric(const TView &in, const TView &w, const TView &bias, co
                           const DevEpilogue &epi, cudaStream_t s) {
     fusedDepthwiseKernel<<<gridFor(numelOf(out)), kThreads, 0, s>>>(in, w, bias, out, a, epi);
     return finish("DEPTHWISE_CONV2D+RESCALE");
+}
+
+bool depthwise3x3Eligible(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                          bool fused) {
+    const auto packed = [](const TView &t) {
+        int64_t s = dtypeSize(t.dtype); // strides are in bytes
+        for (int i = t.rank - 1; i >= 0; --i) {
+            if (t.strides[i] != s) {
+                return false;
+            }
+            s *= t.dims[i];
+        }
+        return true;
+    };
+    if (in.dtype != MLEL_I8 || w.dtype != MLEL_I8 || bias.dtype != MLEL_I32 || out.dtype != (fused ? MLEL_I8 : MLEL_I32) ||
+        in.rank != 4 || w.rank != 4 || out.rank != 4 || !packed(in) || !packed(w) || !packed(bias) || !packed(out)) {
+        return false;
+    }
+    const int64_t C = in.dims[3];
+    if (w.dims[0] != 3 || w.dims[1] != 3 || w.dims[2] != C || w.dims[3] != 1 || out.dims[3] != C || C % 4 != 0 ||
+        out.dims[0] != in.dims[0] || (bias.dims[0] != C && bias.dims[0] != 1) || a.dilation[0] != 1 || a.dilation[1] != 1 ||
+        a.stride[0] < 1 || (a.stride[1] != 1 && a.stride[1] != 2) || numelOf(in) >= (int64_t(1) << 31) ||
+        numelOf(out) >= (int64_t(1) << 31)) {
+        return false;
+    }
+    const uintptr_t ptrs = reinterpret_cast<uintptr_t>(in.ptr) | reinterpret_cast<uintptr_t>(w.ptr) |
+                           reinterpret_cast<uintptr_t>(bias.ptr);
+    return (ptrs & 3u) == 0 && (reinterpret_cast<uintptr_t>(out.ptr) & (fused ? 3u : 15u)) == 0;
+}
+
+int depthwise3x3(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                 const DevEpilogue *epi, cudaStream_t s) {
+    constexpr int PX = 4;
+    const int N = int(in.dims[0]), H = int(in.dims[1]), W = int(in.dims[2]), C = int(in.dims[3]);
+    const int OH = int(out.dims[1]), OW = int(out.dims[2]);
+    const int64_t total = int64_t(N) * OH * ((OW + PX - 1) / PX) * (C / 4);
+    const int grid = gridFor(total, 128, 16);
+    const auto *pi = reinterpret_cast<const int8_t *>(in.ptr);
+    const auto *pw = reinterpret_cast<const int8_t *>(w.ptr);
+    const auto *pb = reinterpret_cast<const int32_t *>(bias.ptr);
+    const int nb = int(bias.dims[0]);
+    const DevEpilogue none{};
+    if (epi != nullptr) {
+        if (a.stride[1] == 1) {
+            depthwise3x3Kernel<PX, 1, true><<<grid, 128, 0, s>>>(pi, pw, pb, nb, out.ptr, N, H, W, C, OH, OW, a, *epi);
+        } else {
+            depthwise3x3Kernel<PX, 2, true><<<grid, 128, 0, s>>>(pi, pw, pb, nb, out.ptr, N, H, W, C, OH, OW, a, *epi);
+        }
+    } else if (a.stride[1] == 1) {
+        depthwise3x3Kernel<PX, 1, false><<<grid, 128, 0, s>>>(pi, pw, pb, nb, out.ptr, N, H, W, C, OH, OW, a, none);
+    } else {
+        depthwise3x3Kernel<PX, 2, false><<<grid, 128, 0, s>>>(pi, pw, pb, nb, out.ptr, N, H, W, C, OH, OW, a, none);
+    }
+    return finish("DEPTHWISE_CONV2D 3x3");
 }
 
 int fusedMatmulGeneric(const TView &a, const TView &b, const TView &out, int32_t zpA, int32_t zpB,

@@ -37,6 +37,11 @@ int fusedConv2dGeneric(const TView &in, const TView &w, const TView &bias, const
                        const DevEpilogue &epi, cudaStream_t s);
 int fusedDepthwiseGeneric(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
                           const DevEpilogue &epi, cudaStream_t s);
+// 3x3 depthwise convolution of packed int8 NHWC tensors with channel multiplier 1; epi == nullptr: int32 output
+bool depthwise3x3Eligible(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                          bool fused);
+int depthwise3x3(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                 const DevEpilogue *epi, cudaStream_t s);
 int fusedMatmulGeneric(const TView &a, const TView &b, const TView &out, int32_t zpA, int32_t zpB,
                        const DevEpilogue &epi, cudaStream_t s);
 // out[i] = clamp(rescale_out(rescale_a(x[i]) + rescale_b(y[i]))), all tensors packed int8 of n elements

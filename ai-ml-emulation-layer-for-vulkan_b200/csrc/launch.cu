@@ -225,6 +225,9 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
     case OP_CONV2D:
         return genericConv2d(in(0), in(1), in(2), out, convAttr(op), s);
     case OP_DEPTHWISE_CONV2D:
+        if (depthwise3x3Eligible(in(0), in(1), in(2), out, convAttr(op), false)) {
+            return depthwise3x3(in(0), in(1), in(2), out, convAttr(op), nullptr, s);
+        }
         return genericDepthwise(in(0), in(1), in(2), out, convAttr(op), s);
     case OP_MATMUL:
         return genericMatmul(in(0), in(1), out, op.i[0], op.i[1], s);
@@ -281,8 +284,13 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         return genericSelect(in(0), in(1), in(2), out, s);
     case OP_FUSED_CONV2D:
         return fusedConv2dGeneric(in(0), in(1), in(2), out, convAttr(op), devEpilogue(op.epi, T), s);
-    case OP_FUSED_DEPTHWISE:
-        return fusedDepthwiseGeneric(in(0), in(1), in(2), out, convAttr(op), devEpilogue(op.epi, T), s);
+    case OP_FUSED_DEPTHWISE: {
+        const DevEpilogue epi = devEpilogue(op.epi, T);
+        if (!epi.hasResidual && depthwise3x3Eligible(in(0), in(1), in(2), out, convAttr(op), true)) {
+            return depthwise3x3(in(0), in(1), in(2), out, convAttr(op), &epi, s);
+        }
+        return fusedDepthwiseGeneric(in(0), in(1), in(2), out, convAttr(op), epi, s);
+    }
     case OP_FUSED_MATMUL:
         return fusedMatmulGeneric(in(0), in(1), out, op.i[0], op.i[1], devEpilogue(op.epi, T), s);
     case OP_FUSED_ADD:

@@ -125,6 +125,9 @@ def test_conv2d_int16_int64(mlel):
 @pytest.mark.parametrize("case", [
     (1, 8, 8, 4, 1, 3, 1, 1, 1, -3, 0), (2, 9, 9, 5, 2, 3, 1, 2, 1, 4, 2), (1, 16, 16, 32, 1, 3, 1, 1, 1, -128, 0),
     (1, 7, 6, 3, 3, 2, 0, 1, 2, -128, -1), (2, 14, 14, 96, 1, 3, 1, 2, 1, -128, 0),
+    # the vectorised 3x3 kernel: weight zero point, widths that end inside a 4-pixel group, no padding
+    (1, 10, 10, 8, 1, 3, 1, 1, 1, 5, -3), (1, 11, 13, 12, 1, 3, 1, 2, 1, -7, 2), (2, 9, 9, 16, 1, 3, 0, 1, 1, 3, 0),
+    (3, 28, 28, 144, 1, 3, 1, 1, 1, -128, 0),
 ])
 @pytest.mark.parametrize("with_rescale", [False, True])
 def test_depthwise_conv2d(mlel, case, with_rescale):
