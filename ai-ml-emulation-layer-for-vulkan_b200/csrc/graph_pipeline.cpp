@@ -827,7 +827,7 @@ void GraphPipeline::prepareTensorCore() {
             const int64_t piece = !padChannels ? 16 : (rowRuns ? ((sx * ICp) % 16 == 0 ? 16 : 8) : std::min<int64_t>(ICp, 16));
             const int64_t runBytes = rowRuns ? (KW * ICp + piece - 1) / piece * piece : KW * ICp; // K bytes per window row
             const int64_t kPad = (KH * runBytes + 15) / 16 * 16;
-            if (in.dims[3] != IC || out.dims[3] != OC || OC % 16 != 0 || kPad > 65536 ||
+            if (in.dims[3] != IC || out.dims[3] != OC || kPad > 65536 ||
                 (b.dims[0] != OC && b.dims[0] != 1) || out.numel() >= (int64_t(1) << 31) ||
                 in.numel() >= (int64_t(1) << 31)) {
                 continue;

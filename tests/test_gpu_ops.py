@@ -63,6 +63,11 @@ CONV_CASES = [
     (2, 15, 15, 128, 80, 3, 1, 2, 1, -4, 0),
     (1, 9, 9, 128, 96, 5, 2, 1, 1, 3, 0),
     (40, 7, 7, 128, 144, 3, 1, 1, 1, -8, 0),
+    # output channel counts that are not multiples of 16 (MobileNet's 24-channel projections, a single channel)
+    (2, 14, 14, 96, 24, 1, 0, 1, 1, -5, 0),
+    (1, 10, 10, 32, 40, 3, 1, 1, 1, 4, 0),
+    (1, 6, 6, 16, 1, 1, 0, 1, 1, 0, 0),
+    (2, 9, 9, 128, 72, 3, 1, 1, 1, 7, 0),
 ]
 
 
