@@ -206,6 +206,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         const uint32_t par = (tileCount >> 1) & 1u;
         const int oc = c0 + quarter * 32 + lane;
         const bool ocValid = oc < p.N;
+        const bool warpLive = c0 + quarter * 32 < p.N; // else all 32 channels of this warp are past the end
         const int32_t *corrBatch = p.corr + (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0);
         if (storer) {
             // The previous tile's store has read its C/D tile (and so have all before it): that tile may be
@@ -281,7 +282,9 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 if (hasClasses) {
                     borderFix(accA, part * kColsPerWarp + 16 * st);
                 }
-                rescaleSlice<RESIDUAL>(accA, k, lutA128, lutB, cd + (16 * st) * 128);
+                if (warpLive) {
+                    rescaleSlice<RESIDUAL>(accA, k, lutA128, lutB, cd + (16 * st) * 128);
+                }
             }
         } else {
         tmemLoad16(taddr, accA);
@@ -292,7 +295,9 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             if (hasClasses) {
                 borderFix(accA, part * kColsPerWarp + 16 * st);
             }
-            rescaleSlice<RESIDUAL>(accA, k, lutA128, lutB, cd + (16 * st) * 128);
+            if (warpLive) {
+                rescaleSlice<RESIDUAL>(accA, k, lutA128, lutB, cd + (16 * st) * 128);
+            }
             tmemWait16(accB);
             if (st + 2 < kSteps) {
                 tmemLoad16(taddr + uint32_t(16 * (st + 2)), accA);
@@ -306,7 +311,9 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             if (hasClasses) {
                 borderFix(accB, part * kColsPerWarp + 16 * (st + 1));
             }
-            rescaleSlice<RESIDUAL>(accB, k, lutA128, lutB, cd + (16 * (st + 1)) * 128);
+            if (warpLive) {
+                rescaleSlice<RESIDUAL>(accB, k, lutA128, lutB, cd + (16 * (st + 1)) * 128);
+            }
         }
         }
         // make the tile visible to the TMA unit, then one thread stores it (pixels and channels past the
