@@ -77,6 +77,68 @@ __global__ void __launch_bounds__(256) transposeColsumKernel(const int8_t *__res
     }
 }
 
+// ---- AVG_POOL2D, int8 NHWC, C % 4 == 0 (avgpool2d.comp:27-75) ---------------------------------------------
+// A 256-thread block owns one output pixel and up to 128 channels: 32 lanes hold four channels each (one
+// coalesced 128-byte read per tap), eight slices share the window's taps and add their partial sums in
+// shared memory.  Built for the global pooling at the end of a classifier, where the generic kernel's one
+// thread per output walks 49 dependent loads.
+__global__ void __launch_bounds__(256) avgPoolI8Kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int H, int W,
+                                                       int C, int OH, int OW, PoolAttr a) {
+    __shared__ int32_t part[8][32][4];
+    const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int chunks = (C + 127) / 128;
+    int64_t b = blockIdx.x;
+    const int c0 = int(b % chunks) * 128 + lane * 4;
+    b /= chunks;
+    const int ox = int(b % OW);
+    b /= OW;
+    const int oy = int(b % OH);
+    const int n = int(b / OH);
+    const int iy = oy * a.stride[0] - a.pad[0], ix = ox * a.stride[1] - a.pad[2];
+    const int taps = a.kernel[0] * a.kernel[1];
+    int32_t acc[4] = {0, 0, 0, 0};
+    // in-range taps of the whole window: (rows inside) x (columns inside)
+    const int ny = min(iy + a.kernel[0], H) - max(iy, 0), nx = min(ix + a.kernel[1], W) - max(ix, 0);
+    const int count = (ny > 0 && nx > 0) ? ny * nx : 0;
+    for (int t = slice; t < taps; t += 8) {
+        const int ky = t / a.kernel[1], kx = t - ky * a.kernel[1];
+        const int y = iy + ky, x = ix + kx;
+        if (y >= 0 && y < H && x >= 0 && x < W && c0 < C) {
+            const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(in + ((int64_t(n) * H + y) * W + x) * C + c0));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                acc[k] += int32_t(int8_t(word >> (8 * k))) - a.inZp;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        part[slice][lane][k] = acc[k];
+    }
+    __syncthreads();
+    if (slice == 0 && c0 < C) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int32_t v = 0;
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) {
+                v = int32_t(uint32_t(v) + uint32_t(part[sl][lane][k]));
+            }
+            if (count == 0) {
+                v = 0;
+            } else {
+                const int32_t round = v < 0 ? -(count >> 1) : (count >> 1);
+                v = int32_t(uint32_t(v) + uint32_t(round)) / count; // truncates toward zero
+            }
+            v = int32_t(uint32_t(v) + uint32_t(a.outZp));
+            v = v < -128 ? -128 : (v > 127 ? 127 : v);
+            word |= uint32_t(uint8_t(v)) << (8 * k);
+        }
+        *reinterpret_cast<uint32_t *>(out + ((int64_t(n) * OH + oy) * OW + ox) * C + c0) = word;
+    }
+}
+
 // ---- MAX_POOL2D, int8 NHWC, C % 16 == 0 (maxpool2d.comp:23-72) --------------------------------------
 // One thread per (pixel, 16-channel group): 16-byte loads, per-byte signed max, one 16-byte store.
 __global__ void maxPoolI8Kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int64_t total, int H, int W,
@@ -151,6 +213,22 @@ bool maxPoolI8Eligible(const TView &in, const TView &out) {
     return in.dtype == MLEL_I8 && out.dtype == MLEL_I8 && in.rank == 4 && out.rank == 4 && in.dims[3] % 16 == 0 &&
            in.dims[3] == out.dims[3] && in.dims[0] == out.dims[0] && packed(in) && packed(out) &&
            ((reinterpret_cast<uintptr_t>(in.ptr) | reinterpret_cast<uintptr_t>(out.ptr)) & 15u) == 0;
+}
+
+bool avgPoolI8Eligible(const TView &in, const TView &out, const PoolAttr &a) {
+    // one block per output pixel and 128 channels: worthwhile when the window is large
+    return maxPoolI8Eligible(in, out) && a.kernel[0] > 0 && a.kernel[1] > 0 && a.kernel[0] * a.kernel[1] >= 16 &&
+           a.stride[0] > 0 && a.stride[1] > 0 &&
+           int64_t(out.dims[0]) * out.dims[1] * out.dims[2] * ((out.dims[3] + 127) / 128) < (int64_t(1) << 30);
+}
+
+int avgPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s) {
+    const int C = int(in.dims[3]);
+    const int64_t blocks = int64_t(out.dims[0]) * out.dims[1] * out.dims[2] * ((C + 127) / 128);
+    avgPoolI8Kernel<<<unsigned(blocks), 256, 0, s>>>(reinterpret_cast<const int8_t *>(in.ptr),
+                                                    reinterpret_cast<int8_t *>(out.ptr), int(in.dims[1]), int(in.dims[2]), C,
+                                                    int(out.dims[1]), int(out.dims[2]), a);
+    return finish("AVG_POOL2D");
 }
 
 int maxPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s) {

@@ -53,6 +53,9 @@ int padImageI8(const int8_t *in, int8_t *out, int N, int H, int W, int C, int Hp
 // bt[n][w][c] = b[n][c][w]; corr[n][w] = -za * sum_c b[n][c][w] (mod 2^32).  C and W multiples of 16.
 int transposeForMatmul(const int8_t *b, int8_t *bt, int32_t *corr, int batches, int C, int W, int32_t za, cudaStream_t s);
 bool maxPoolI8Eligible(const TView &in, const TView &out);
+// packed int8 NHWC tensors (same conditions as maxPoolI8Eligible) with a window of at least 16 taps
+bool avgPoolI8Eligible(const TView &in, const TView &out, const PoolAttr &a);
+int avgPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s);
 int maxPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s);
 
 // generic_ops.cu

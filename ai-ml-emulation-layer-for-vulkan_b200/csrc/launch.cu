@@ -236,6 +236,9 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         return genericRescale(in(0), out, in(1), in(2), a, s);
     }
     case OP_AVG_POOL2D:
+        if (avgPoolI8Eligible(in(0), out, poolAttr(op))) {
+            return avgPoolI8(in(0), out, poolAttr(op), s);
+        }
         return genericAvgPool(in(0), out, poolAttr(op), s);
     case OP_MAX_POOL2D:
         if (maxPoolI8Eligible(in(0), out)) {
@@ -265,8 +268,28 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         return genericReduce(op.sub, in(0), out, uint32_t(op.i[0]), s);
     case OP_CAST:
         return genericCast(in(0), out, s);
-    case OP_RESHAPE:
+    case OP_RESHAPE: {
+        // same linear index on both sides: packed tensors of equal size are one device-to-device copy
+        const auto packedBytes = [](const TView &t) -> int64_t {
+            int64_t st = dtypeSize(t.dtype);
+            for (int i = t.rank - 1; i >= 0; --i) {
+                if (t.strides[i] != st) {
+                    return -1;
+                }
+                st *= t.dims[i];
+            }
+            return st;
+        };
+        const int64_t nin = packedBytes(in(0)), nout = packedBytes(out);
+        if (nin > 0 && nin == nout && in(0).dtype == out.dtype) {
+            if (cudaMemcpyAsync(out.ptr, in(0).ptr, size_t(nin), cudaMemcpyDeviceToDevice, s) != cudaSuccess) {
+                setLastError("RESHAPE: device-to-device copy failed");
+                return MLEL_ERROR_DEVICE;
+            }
+            return MLEL_SUCCESS;
+        }
         return genericReshape(in(0), out, s);
+    }
     case OP_SLICE: {
         uint32_t start[kMaxRank];
         for (int k = 0; k < kMaxRank; ++k) {

@@ -230,6 +230,10 @@ def test_residual_add_pattern(mlel):
 @pytest.mark.parametrize("case", [
     ((1, 7, 7, 5), (7, 7), (7, 7), (0, 0, 0, 0), -20, -20), ((2, 8, 9, 3), (3, 3), (2, 2), (1, 1, 1, 1), 0, 0),
     ((1, 6, 6, 4), (2, 3), (1, 2), (0, 1, 1, 1), 5, -3), ((4, 7, 7, 2048), (7, 7), (7, 7), (0, 0, 0, 0), -20, -20),
+    # large windows on 16-channel multiples (block-per-pixel kernel): padded borders with fewer in-range taps,
+    # overlapping windows, a channel count that ends inside a 128-channel chunk, saturating zero points
+    ((2, 11, 13, 16), (5, 5), (2, 2), (2, 2, 2, 2), 7, -5), ((1, 14, 14, 144), (4, 4), (3, 3), (1, 0, 0, 1), -128, 127),
+    ((3, 7, 7, 1280), (7, 7), (7, 7), (0, 0, 0, 0), 0, 0),
 ])
 def test_avg_pool2d(mlel, case):
     shape, k, s, p, in_zp, out_zp = case
