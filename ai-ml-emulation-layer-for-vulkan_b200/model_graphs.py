@@ -210,6 +210,82 @@ def mobilenet_v2_graph(seed: int = 0, n: int = 32, image: int = 224, width_div: 
     return g, [data]
 
 
+def _lut16(fn) -> np.ndarray:
+    """513-entry int16 table for TABLE on int16 inputs: entry i is the function at input (i - 256) * 128."""
+    x = (np.arange(513, dtype=np.float64) - 256.0) * 128.0
+    return np.clip(np.round(fn(x)), -32768, 32767).astype(np.int16)
+
+
+def bert_graph(seed: int = 0, n: int = 32, seq: int = 384, hidden: int = 768, heads: int = 12, ffn: int = 3072,
+               layers: int = 12):
+    """Configuration 4: BERT-base-shaped int8 encoder stack (random int8 weights, zero points 0).
+
+    Per layer: Q/K/V/output/FFN projections as int8 MATMUL + per-channel RESCALE; attention scores as a batched
+    int8 MATMUL of two activations, softmax as REDUCE_MAX, SUB, int16 TABLE (exp), REDUCE_SUM, int16 TABLE
+    (reciprocal) and MUL; the context as a second activation MATMUL; GELU as an int8 TABLE; layer norm as
+    REDUCE_SUM, MUL, SUB and an int16 TABLE (reciprocal square root); residual ADDs on int32 with RESCALE on both
+    sides.  ``n``/``seq``/``hidden``/``heads``/``ffn``/``layers`` shrink the stack for tests."""
+    rng = _rng(seed)
+    g = GraphBuilder("bert")
+    d = hidden // heads
+    rows = n * seq
+    x = g.input(np.int8, (1, rows, hidden))
+    data = _data_rng(seed).integers(-128, 128, (1, rows, hidden), dtype=np.int8)
+    exp_lut = _lut16(lambda v: 32767.0 * np.exp(np.minimum(v, 0.0) / 4096.0))
+    recip_lut = _lut16(lambda v: 32767.0 * 256.0 / (v + 32768.0 + 256.0))
+    rsqrt_lut = _lut16(lambda v: 32767.0 * 16.0 / np.sqrt(v + 32768.0 + 256.0))
+    gelu_lut = np.clip(np.round([0.5 * v * (1.0 + math.erf(v / 32.0 / math.sqrt(2.0))) for v in range(-128, 128)]),
+                       -128, 127).astype(np.int8)
+
+    def project(t, cin, cout, out_zp=0):
+        w = g.constant(rng.integers(-128, 128, (1, cin, cout), dtype=np.int8))
+        mult = rng.integers(1 << 30, (1 << 31) - 1, (cout,), dtype=np.int64).astype(np.int32)
+        shift = np.full((cout,), _calibrated_shift(cin), np.int8)
+        y = g.matmul(t, w, 0, 0)
+        return g.rescale(y, mult, shift, 0, out_zp, np.int8, scale32=True, double_round=True, per_channel=True)
+
+    def to32(t, shift=24):
+        return g.rescale(t, [1 << 30], [shift], 0, 0, np.int32)
+
+    def layer_norm(t32):
+        # t32: int32 [1, rows, hidden] with about 6 fractional bits
+        total = g.reduce("REDUCE_SUM", t32, 2)
+        inv = g.inline(np.asarray([(1 << 20) // hidden], np.int32).reshape(1, 1, 1))
+        mean = g.mul(total, inv, 20)
+        cen = g.sub(t32, mean)
+        var = g.mul(g.reduce("REDUCE_SUM", g.mul(cen, cen, 8), 2), inv, 20)
+        var16 = g.rescale(var, [1 << 30], [34], 0, -32768, np.int16)
+        rs = g.table(var16, rsqrt_lut)
+        normed = g.mul(cen, rs, 12)
+        # cen / rms(cen) arrives with 20 fractional bits (13 from the look-up's scale, 7 from its interpolation)
+        return g.rescale(normed, [1 << 30], [45], 0, 0, np.int8, double_round=True)
+
+    for _ in range(layers):
+        q, k, v = project(x, hidden, hidden), project(x, hidden, hidden), project(x, hidden, hidden)
+        q = g.reshape(g.transpose(g.reshape(q, (n, seq, heads, d)), (0, 2, 1, 3)), (n * heads, seq, d))
+        k = g.reshape(g.transpose(g.reshape(k, (n, seq, heads, d)), (0, 2, 3, 1)), (n * heads, d, seq))
+        v = g.reshape(g.transpose(g.reshape(v, (n, seq, heads, d)), (0, 2, 1, 3)), (n * heads, seq, d))
+        scores = g.matmul(q, k, 0, 0)                                   # int32 [n*heads, seq, seq]
+        diff = g.sub(scores, g.reduce("REDUCE_MAX", scores, 2))         # <= 0
+        diff16 = g.rescale(diff, [1 << 30], [30 + max(1, int(math.log2(d)) - 2)], 0, 0, np.int16)
+        e = g.table(diff16, exp_lut)                                    # int32, 7 extra fractional bits
+        denom = g.reduce("REDUCE_SUM", e, 2)
+        denom16 = g.rescale(denom, [1 << 30], [30 + 7 + max(1, int(math.ceil(math.log2(seq))))], 0, -32768, np.int16)
+        r = g.table(denom16, recip_lut)
+        log_seq = max(1, int(math.ceil(math.log2(seq))))
+        # e * r >> 22 is the probability with 15 + log2(seq) fractional bits; keep 8 of them
+        probs = g.rescale(g.mul(e, r, 22), [1 << 30], [30 + 7 + log_seq], 0, -128, np.int8)
+        ctx = g.matmul(probs, v, -128, 0)
+        ctx = g.rescale(ctx, [int(rng.integers(1 << 30, 1 << 31))], [39], 0, 0, np.int8, double_round=True)
+        ctx = g.reshape(g.transpose(g.reshape(ctx, (n, heads, seq, d)), (0, 2, 1, 3)), (1, rows, hidden))
+        attn = project(ctx, hidden, hidden)
+        x = layer_norm(g.add(to32(attn), to32(x)))
+        h = g.table(project(x, hidden, ffn), gelu_lut)
+        x = layer_norm(g.add(to32(project(h, ffn, hidden)), to32(x)))
+    g.output(x)
+    return g, [data]
+
+
 def macs_of(graph: GraphBuilder) -> int:
     """Algorithmic multiply-accumulates of a graph (padded taps counted, the usual convention)."""
     total = 0

@@ -119,6 +119,21 @@ def test_emitted_resnet_lowers_and_fuses(mlel):
     assert 0 < mlel.Session(pf).memory_requirements()[0] < unfused_mem
 
 
+def test_emitted_bert_lowers_and_fuses(mlel):
+    from mlel_b200.model_graphs import bert_graph
+    g, _ = bert_graph(seed=0, n=2, seq=16, hidden=32, heads=2, ffn=64, layers=2)
+    ext = [(v.binding[0], v.binding[1], 0, mlel.NP_TO_DTYPE[v.dtype], v.shape) for v in g.inputs]
+    ext += [(s, b, 0, mlel.NP_TO_DTYPE[v.dtype], v.shape) for v, s, b in g.outputs]
+    consts = list(g.constants.items())
+    p = lower(mlel, g.spvasm(), ext, consts, mlel.PIPELINE_NO_FUSION)
+    assert p.op_names() == [op.name for op in g.ops]
+    names = lower(mlel, g.spvasm(), ext, consts).exec_names()
+    # every projection and the context product carry their RESCALE; the score product feeds REDUCE_MAX and SUB
+    # as int32 and stays a plain MATMUL
+    assert names.count("MATMUL+RESCALE") == 2 * 7 and names.count("MATMUL") == 2
+    assert names.count("TABLE") == 2 * 5 and names.count("TRANSPOSE") == 2 * 4
+
+
 def test_graph_outputs_are_never_elided(mlel):
     g = GraphBuilder()
     a = g.input(np.int8, (1, 4, 4, 8))

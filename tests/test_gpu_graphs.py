@@ -10,7 +10,8 @@ import numpy as np
 import pytest
 
 from mlel_b200.graph_builder import GraphBuilder
-from mlel_b200.model_graphs import (conv2d_rescale_graph, matmul_rescale_graph, mobilenet_v2_graph, resnet50_graph)
+from mlel_b200.model_graphs import (bert_graph, conv2d_rescale_graph, matmul_rescale_graph, mobilenet_v2_graph,
+                                     resnet50_graph)
 from tests.graph_eval import evaluate
 
 pytestmark = pytest.mark.gpu
@@ -215,6 +216,33 @@ def test_mobilenet_shaped_graph(mlel):
     want = evaluate(g, inputs)[0]
     np.testing.assert_array_equal(run(g, inputs, flags=1)[0], want)
     np.testing.assert_array_equal(run(g, inputs, flags=0, use_cuda_graph=True)[0], want)
+
+
+def test_bert_shaped_graph(mlel):
+    """Configuration 4 at reduced size: projections and both attention products on the tensor cores, the
+    softmax / layer-norm chains (REDUCE_MAX, SUB, int16 TABLE, REDUCE_SUM, MUL), head split and merge
+    (RESHAPE, TRANSPOSE), GELU as an int8 TABLE, rescaled residual ADDs."""
+    g, inputs = bert_graph(seed=1, n=2, seq=48, hidden=64, heads=4, ffn=128, layers=2)
+    want = evaluate(g, inputs)[0]
+    assert want.std() > 5.0 and np.unique(want).size > 50
+    np.testing.assert_array_equal(run(g, inputs, flags=1)[0], want)
+    np.testing.assert_array_equal(run(g, inputs, flags=0)[0], want)
+    np.testing.assert_array_equal(run(g, inputs, flags=0, use_cuda_graph=True)[0], want)
+
+
+def test_bert_intermediate_tensors(mlel):
+    """Every int8 and int16 tensor of one encoder layer is made a graph output, so that a wrong value in the
+    attention or normalisation chains cannot be masked by later saturation."""
+    g, inputs = bert_graph(seed=2, n=1, seq=32, hidden=32, heads=2, ffn=64, layers=1)
+    outputs = [id(v) for v, _, _ in g.outputs]
+    for op in list(g.ops):
+        if op.name in ("RESCALE", "TABLE", "MUL", "REDUCE_SUM") and id(op.out) not in outputs:
+            g.output(op.out)
+    want = evaluate(g, inputs)
+    got = run(g, inputs)
+    assert len(got) > 20
+    for a, b in zip(got, want):
+        np.testing.assert_array_equal(a, b)
 
 
 def test_batch_is_independent(mlel):
