@@ -58,6 +58,17 @@ bool avgPoolI8Eligible(const TView &in, const TView &out, const PoolAttr &a);
 int avgPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s);
 int maxPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s);
 
+// vector_ops.cu: vectorised kernels for packed tensors.  Each returns false when it does not apply (the caller
+// then runs the generic kernel); otherwise *rc is the launch status.
+bool vecRescale(const TView &in, const TView &out, const TView &mult, const TView &shift, const RescaleAttr &a, cudaStream_t s,
+                int *rc);
+bool vecTable(const TView &in, const TView &out, const TView &table, cudaStream_t s, int *rc);
+// op: BIN_ADD or BIN_SUB, or -1 for MUL with `shift`
+bool vecBinaryI32(int32_t op, const TView &a, const TView &b, const TView &out, uint32_t shift, cudaStream_t s, int *rc);
+bool vecClampI8(const TView &in, const TView &out, int64_t lo, int64_t hi, cudaStream_t s, int *rc);
+bool vecRowReduce(int32_t op, const TView &in, const TView &out, uint32_t axis, cudaStream_t s, int *rc);
+bool vecTransposeRows(const TView &in, const TView &out, const uint32_t *perms, cudaStream_t s, int *rc);
+
 // generic_ops.cu
 int genericConv2d(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
                   cudaStream_t s);

@@ -1,0 +1,489 @@
+// Vectorised kernels for the element-wise, table, reduction and data-movement operators on packed
+// tensors.  Each has a generic counterpart in generic_ops.cu that defines the result for every rank, stride
+// and type; these take the common case - contiguous tensors, signed integer types, operands of the same
+// shape or broadcast along the last axis - and only change how the bytes move: four elements per thread
+// with 4-, 8- or 16-byte accesses, no index unravelling, a warp per row for reductions.  The arithmetic is
+// the same functions (device_common.cuh), so the results are the same bits.
+//
+// Every entry point returns false when it does not apply; the caller then runs the generic kernel.
+#include <string>
+
+#include "device_common.cuh"
+#include "kernels.hpp"
+
+namespace mlel {
+
+namespace {
+
+#define GRID_STRIDE(e, total)                                                                                          \
+    for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < (total); e += int64_t(gridDim.x) * blockDim.x)
+
+int finish(const char *what) {
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        setLastError(std::string(what) + ": " + cudaGetErrorString(err));
+        return MLEL_ERROR_DEVICE;
+    }
+    return MLEL_SUCCESS;
+}
+
+// Number of elements of a contiguous (byte strides = packed) tensor, or -1.
+int64_t packedNumel(const TView &t) {
+    int64_t st = dtypeSize(t.dtype), n = 1;
+    for (int i = t.rank - 1; i >= 0; --i) {
+        if (t.strides[i] != st) {
+            return -1;
+        }
+        st *= t.dims[i];
+        n *= t.dims[i];
+    }
+    return n;
+}
+
+bool sameShape(const TView &a, const TView &b) {
+    if (a.rank != b.rank) {
+        return false;
+    }
+    for (int i = 0; i < a.rank; ++i) {
+        if (a.dims[i] != b.dims[i]) {
+            return false;
+        }
+    }
+    return true;
+}
+
+// b has out's shape except for a last axis of 1 (one value per row of out).
+bool rowBroadcast(const TView &b, const TView &out) {
+    if (b.rank != out.rank || out.rank < 1 || b.dims[b.rank - 1] != 1) {
+        return false;
+    }
+    for (int i = 0; i + 1 < out.rank; ++i) {
+        if (b.dims[i] != out.dims[i]) {
+            return false;
+        }
+    }
+    return true;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool signedInt(int32_t dtype) { return dtype == MLEL_I8 || dtype == MLEL_I16 || dtype == MLEL_I32; }
+
+// Four consecutive elements of a signed integer type, widened to int32.
+template <typename T> __device__ __forceinline__ void load4(const T *p, int32_t (&v)[4]);
+template <> __device__ __forceinline__ void load4<int8_t>(const int8_t *p, int32_t (&v)[4]) {
+    const uint32_t w = *reinterpret_cast<const uint32_t *>(p);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        v[k] = int32_t(int8_t(w >> (8 * k)));
+    }
+}
+template <> __device__ __forceinline__ void load4<int16_t>(const int16_t *p, int32_t (&v)[4]) {
+    const uint2 w = *reinterpret_cast<const uint2 *>(p);
+    v[0] = int32_t(int16_t(w.x)), v[1] = int32_t(int16_t(w.x >> 16));
+    v[2] = int32_t(int16_t(w.y)), v[3] = int32_t(int16_t(w.y >> 16));
+}
+template <> __device__ __forceinline__ void load4<int32_t>(const int32_t *p, int32_t (&v)[4]) {
+    const int4 w = *reinterpret_cast<const int4 *>(p);
+    v[0] = w.x, v[1] = w.y, v[2] = w.z, v[3] = w.w;
+}
+// Stores the low bits of four values (the caller has clamped or wants the wrap).
+template <typename T> __device__ __forceinline__ void store4(T *p, const int32_t (&v)[4]);
+template <> __device__ __forceinline__ void store4<int8_t>(int8_t *p, const int32_t (&v)[4]) {
+    *reinterpret_cast<uint32_t *>(p) = uint32_t(uint8_t(v[0])) | (uint32_t(uint8_t(v[1])) << 8) |
+                                       (uint32_t(uint8_t(v[2])) << 16) | (uint32_t(uint8_t(v[3])) << 24);
+}
+template <> __device__ __forceinline__ void store4<int16_t>(int16_t *p, const int32_t (&v)[4]) {
+    *reinterpret_cast<uint2 *>(p) = make_uint2(uint32_t(uint16_t(v[0])) | (uint32_t(uint16_t(v[1])) << 16),
+                                               uint32_t(uint16_t(v[2])) | (uint32_t(uint16_t(v[3])) << 16));
+}
+template <> __device__ __forceinline__ void store4<int32_t>(int32_t *p, const int32_t (&v)[4]) {
+    *reinterpret_cast<int4 *>(p) = make_int4(v[0], v[1], v[2], v[3]);
+}
+
+template <typename T> __host__ __device__ constexpr int32_t lowestOf() {
+    return sizeof(T) == 1 ? -128 : (sizeof(T) == 2 ? -32768 : int32_t(0x80000000u));
+}
+template <typename T> __host__ __device__ constexpr int32_t highestOf() {
+    return sizeof(T) == 1 ? 127 : (sizeof(T) == 2 ? 32767 : 0x7fffffff);
+}
+
+// ---- RESCALE (rescale.comp:27-72) -------------------------------------------------------------------------
+template <typename IN, typename OUT>
+__global__ void rescaleVecKernel(const IN *__restrict__ in, OUT *__restrict__ out, int64_t groups,
+                                 const int32_t *__restrict__ mult, const int8_t *__restrict__ shift, int perChannel, int C,
+                                 int32_t inZp, int32_t outZp, int doubleRound) {
+    FastRescale f = makeFastRescale(__ldg(mult), int32_t(__ldg(shift)), inZp, doubleRound != 0);
+    GRID_STRIDE(g, groups) {
+        int32_t v[4], r[4];
+        load4<IN>(in + 4 * g, v);
+        const int c0 = perChannel ? int((4 * g) % C) : 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (perChannel) {
+                f = makeFastRescale(__ldg(mult + c0 + k), int32_t(__ldg(shift + c0 + k)), inZp, doubleRound != 0);
+            }
+            r[k] = fastRescale(f, v[k], outZp, lowestOf<OUT>(), highestOf<OUT>());
+        }
+        store4<OUT>(out + 4 * g, r);
+    }
+}
+
+template <typename IN, typename OUT>
+void launchRescale(const TView &in, const TView &out, const TView &mult, const TView &shift, const RescaleAttr &a,
+                   int64_t n, cudaStream_t s) {
+    const int C = int(out.dims[out.rank - 1]);
+    rescaleVecKernel<IN, OUT><<<gridFor(n / 4, kThreads, 16), kThreads, 0, s>>>(
+        reinterpret_cast<const IN *>(in.ptr), reinterpret_cast<OUT *>(out.ptr), n / 4,
+        reinterpret_cast<const int32_t *>(mult.ptr), reinterpret_cast<const int8_t *>(shift.ptr), a.perChannel ? 1 : 0, C,
+        int32_t(wrapTo(in.dtype, a.inZp)), int32_t(wrapTo(out.dtype, a.outZp)), (a.scale32 && a.doubleRound) ? 1 : 0);
+}
+
+// ---- TABLE (table.comp:17-52) -------------------------------------------------------------------------------
+__global__ void tableI8Kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int64_t groups,
+                              const int8_t *__restrict__ table) {
+    __shared__ int8_t lut[256];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        lut[i] = table[i];
+    }
+    __syncthreads();
+    GRID_STRIDE(g, groups) {
+        const int4 w = *reinterpret_cast<const int4 *>(in + 16 * g);
+        const uint32_t words[4] = {uint32_t(w.x), uint32_t(w.y), uint32_t(w.z), uint32_t(w.w)};
+        uint32_t res[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t r = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int idx = int(int8_t(words[q] >> (8 * k))) + 128;
+                r |= uint32_t(uint8_t(lut[idx])) << (8 * k);
+            }
+            res[q] = r;
+        }
+        *reinterpret_cast<int4 *>(out + 16 * g) = make_int4(int(res[0]), int(res[1]), int(res[2]), int(res[3]));
+    }
+}
+
+__global__ void tableI16Kernel(const int16_t *__restrict__ in, int32_t *__restrict__ out, int64_t groups,
+                               const int16_t *__restrict__ table) {
+    __shared__ int16_t lut[513];
+    for (int i = threadIdx.x; i < 513; i += blockDim.x) {
+        lut[i] = table[i];
+    }
+    __syncthreads();
+    GRID_STRIDE(g, groups) {
+        int32_t v[4], r[4];
+        load4<int16_t>(in + 4 * g, v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int32_t index = (v[k] + 32768) >> 7;
+            const int32_t fraction = v[k] & 0x7f;
+            const int32_t base = lut[index], next = lut[index + 1];
+            r[k] = int32_t((uint32_t(base) << 7) + uint32_t(next - base) * uint32_t(fraction));
+        }
+        store4<int32_t>(out + 4 * g, r);
+    }
+}
+
+// ---- ADD / SUB / MUL on int32 (elementwise_binary.comp:146-173, mul.comp:24-59) ---------------------------------
+// B_MODE: 0 = same shape, 1 = one value per row of `rowLen` elements, 2 = one value.
+enum { kVecAdd = 0, kVecSub = 1, kVecMul = 2 };
+template <int OP, int B_MODE>
+__global__ void binaryI32Kernel(const int32_t *__restrict__ a, const int32_t *__restrict__ b, int32_t *__restrict__ out,
+                                int64_t groups, int rowLen, uint32_t shift) {
+    GRID_STRIDE(g, groups) {
+        int32_t x[4], y[4], r[4];
+        load4<int32_t>(a + 4 * g, x);
+        if (B_MODE == 0) {
+            load4<int32_t>(b + 4 * g, y);
+        } else {
+            const int32_t v = __ldg(b + (B_MODE == 1 ? (4 * g) / rowLen : 0));
+            y[0] = y[1] = y[2] = y[3] = v;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (OP == kVecAdd) {
+                r[k] = int32_t(uint32_t(x[k]) + uint32_t(y[k]));
+            } else if (OP == kVecSub) {
+                r[k] = int32_t(uint32_t(x[k]) - uint32_t(y[k]));
+            } else {
+                int64_t p = int64_t(x[k]) * int64_t(y[k]);
+                if (shift > 0) {
+                    p = int64_t(uint64_t(p) + (1ull << ((shift - 1) & 63))) >> (shift & 63);
+                }
+                r[k] = int32_t(uint32_t(uint64_t(p)));
+            }
+        }
+        store4<int32_t>(out + 4 * g, r);
+    }
+}
+
+template <int OP>
+void launchBinary(const int32_t *a, const int32_t *b, int32_t *out, int64_t n, int mode, int rowLen, uint32_t shift,
+                  cudaStream_t s) {
+    const int grid = gridFor(n / 4, kThreads, 16);
+    if (mode == 0) {
+        binaryI32Kernel<OP, 0><<<grid, kThreads, 0, s>>>(a, b, out, n / 4, rowLen, shift);
+    } else if (mode == 1) {
+        binaryI32Kernel<OP, 1><<<grid, kThreads, 0, s>>>(a, b, out, n / 4, rowLen, shift);
+    } else {
+        binaryI32Kernel<OP, 2><<<grid, kThreads, 0, s>>>(a, b, out, n / 4, rowLen, shift);
+    }
+}
+
+// ---- CLAMP on int8 (clamp.comp:24-53) -----------------------------------------------------------------------
+__global__ void clampI8Kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int64_t groups, int lo, int hi) {
+    GRID_STRIDE(g, groups) {
+        const int4 w = *reinterpret_cast<const int4 *>(in + 16 * g);
+        const uint32_t words[4] = {uint32_t(w.x), uint32_t(w.y), uint32_t(w.z), uint32_t(w.w)};
+        uint32_t res[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t r = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int v = int(int8_t(words[q] >> (8 * k)));
+                r |= uint32_t(uint8_t(min(max(v, lo), hi))) << (8 * k);
+            }
+            res[q] = r;
+        }
+        *reinterpret_cast<int4 *>(out + 16 * g) = make_int4(int(res[0]), int(res[1]), int(res[2]), int(res[3]));
+    }
+}
+
+// ---- REDUCE_SUM / MAX / MIN along the last axis (reduce.comp:24-70) ------------------------------------------
+// One warp per row: lanes stride through the row four elements at a time, then combine with shuffles.  Integer
+// addition wraps, so the order of the partial sums does not change the result.
+template <typename T, int OP>
+__global__ void rowReduceKernel(const T *__restrict__ in, T *__restrict__ out, int64_t rows, int len) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t row = warp; row < rows; row += warps) {
+        const T *src = in + row * len;
+        int32_t acc = OP == RED_SUM ? 0 : (OP == RED_MAX ? lowestOf<T>() : highestOf<T>());
+        for (int i = lane * 4; i < len; i += 128) {
+            int32_t v[4];
+            load4<T>(src + i, v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (OP == RED_SUM) {
+                    acc = int32_t(uint32_t(acc) + uint32_t(v[k]));
+                } else if (OP == RED_MAX) {
+                    acc = max(acc, v[k]);
+                } else {
+                    acc = min(acc, v[k]);
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const int32_t o = __shfl_xor_sync(0xffffffffu, acc, d);
+            if (OP == RED_SUM) {
+                acc = int32_t(uint32_t(acc) + uint32_t(o));
+            } else if (OP == RED_MAX) {
+                acc = max(acc, o);
+            } else {
+                acc = min(acc, o);
+            }
+        }
+        if (lane == 0) {
+            out[row] = T(acc); // a sum of T keeps T's low bits: the generic kernel wraps to the type after every step
+        }
+    }
+}
+
+template <typename T> void launchRowReduce(int32_t op, const TView &in, const TView &out, int64_t rows, int len, cudaStream_t s) {
+    const int grid = gridFor(rows * 32, kThreads, 16);
+    const T *pi = reinterpret_cast<const T *>(in.ptr);
+    T *po = reinterpret_cast<T *>(out.ptr);
+    if (op == RED_SUM) {
+        rowReduceKernel<T, RED_SUM><<<grid, kThreads, 0, s>>>(pi, po, rows, len);
+    } else if (op == RED_MAX) {
+        rowReduceKernel<T, RED_MAX><<<grid, kThreads, 0, s>>>(pi, po, rows, len);
+    } else {
+        rowReduceKernel<T, RED_MIN><<<grid, kThreads, 0, s>>>(pi, po, rows, len);
+    }
+}
+
+// ---- TRANSPOSE that keeps the last axis (transpose.comp:19-32) -------------------------------------------------
+// Rows of the last axis move as wholes: a thread copies 16 bytes; only the row index is permuted.
+struct RowPermute {
+    uint32_t outDims[kMaxRank]; // output dims without the last axis
+    int64_t inStride[kMaxRank]; // input byte stride of the axis each output axis comes from
+    int rank;                   // number of outer axes
+};
+
+__global__ void transposeRowsKernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int64_t chunks, int chunksPerRow,
+                                    RowPermute p) {
+    GRID_STRIDE(e, chunks) {
+        int64_t row = e / chunksPerRow;
+        const int chunk = int(e - row * chunksPerRow);
+        int64_t src = 0;
+#pragma unroll
+        for (int i = kMaxRank - 1; i >= 0; --i) {
+            if (i < p.rank) {
+                src += int64_t(row % p.outDims[i]) * p.inStride[i];
+                row /= p.outDims[i];
+            }
+        }
+        *reinterpret_cast<int4 *>(out + 16 * e) = *reinterpret_cast<const int4 *>(in + src + 16 * int64_t(chunk));
+    }
+}
+
+} // namespace
+
+bool vecRescale(const TView &in, const TView &out, const TView &mult, const TView &shift, const RescaleAttr &a, cudaStream_t s,
+                int *rc) {
+    const int64_t n = packedNumel(in);
+    if (n <= 0 || n != packedNumel(out) || n % 4 != 0 || !sameShape(in, out) || !signedInt(in.dtype) || !signedInt(out.dtype) ||
+        !aligned16(in.ptr) || !aligned16(out.ptr) || mult.dtype != MLEL_I32 || shift.dtype != MLEL_I8 ||
+        packedNumel(mult) < 1 || packedNumel(shift) < 1 || n >= (int64_t(1) << 40)) {
+        return false;
+    }
+    const int64_t C = out.dims[out.rank - 1];
+    if (a.perChannel && (C % 4 != 0 || packedNumel(mult) != C || packedNumel(shift) != C)) {
+        return false;
+    }
+#define MLEL_RESCALE_CASE(IN_ID, IN_T, OUT_ID, OUT_T)                                                                          \
+    if (in.dtype == IN_ID && out.dtype == OUT_ID) {                                                                            \
+        launchRescale<IN_T, OUT_T>(in, out, mult, shift, a, n, s);                                                             \
+        *rc = finish("RESCALE");                                                                                               \
+        return true;                                                                                                           \
+    }
+    MLEL_RESCALE_CASE(MLEL_I32, int32_t, MLEL_I8, int8_t)
+    MLEL_RESCALE_CASE(MLEL_I32, int32_t, MLEL_I16, int16_t)
+    MLEL_RESCALE_CASE(MLEL_I32, int32_t, MLEL_I32, int32_t)
+    MLEL_RESCALE_CASE(MLEL_I8, int8_t, MLEL_I32, int32_t)
+    MLEL_RESCALE_CASE(MLEL_I8, int8_t, MLEL_I8, int8_t)
+    MLEL_RESCALE_CASE(MLEL_I16, int16_t, MLEL_I32, int32_t)
+    MLEL_RESCALE_CASE(MLEL_I16, int16_t, MLEL_I16, int16_t)
+    MLEL_RESCALE_CASE(MLEL_I16, int16_t, MLEL_I8, int8_t)
+    MLEL_RESCALE_CASE(MLEL_I8, int8_t, MLEL_I16, int16_t)
+#undef MLEL_RESCALE_CASE
+    return false;
+}
+
+bool vecTable(const TView &in, const TView &out, const TView &table, cudaStream_t s, int *rc) {
+    const int64_t n = packedNumel(in);
+    if (n <= 0 || n != packedNumel(out) || !sameShape(in, out) || !aligned16(in.ptr) || !aligned16(out.ptr) ||
+        packedNumel(table) < 0) {
+        return false;
+    }
+    if (in.dtype == MLEL_I8 && out.dtype == MLEL_I8 && table.dtype == MLEL_I8 && packedNumel(table) == 256 && n % 16 == 0) {
+        tableI8Kernel<<<gridFor(n / 16, kThreads, 16), kThreads, 0, s>>>(reinterpret_cast<const int8_t *>(in.ptr),
+                                                                         reinterpret_cast<int8_t *>(out.ptr), n / 16,
+                                                                         reinterpret_cast<const int8_t *>(table.ptr));
+        *rc = finish("TABLE");
+        return true;
+    }
+    if (in.dtype == MLEL_I16 && out.dtype == MLEL_I32 && table.dtype == MLEL_I16 && packedNumel(table) == 513 && n % 4 == 0) {
+        tableI16Kernel<<<gridFor(n / 4, kThreads, 16), kThreads, 0, s>>>(reinterpret_cast<const int16_t *>(in.ptr),
+                                                                        reinterpret_cast<int32_t *>(out.ptr), n / 4,
+                                                                        reinterpret_cast<const int16_t *>(table.ptr));
+        *rc = finish("TABLE");
+        return true;
+    }
+    return false;
+}
+
+// op: BIN_ADD or BIN_SUB of ops.hpp, or -1 for MUL with `shift`.
+bool vecBinaryI32(int32_t op, const TView &a, const TView &b, const TView &out, uint32_t shift, cudaStream_t s, int *rc) {
+    const int64_t n = packedNumel(out);
+    if (n <= 0 || n % 4 != 0 || a.dtype != MLEL_I32 || b.dtype != MLEL_I32 || out.dtype != MLEL_I32 || packedNumel(a) != n ||
+        !sameShape(a, out) || packedNumel(b) < 1 || !aligned16(a.ptr) || !aligned16(out.ptr) || shift > 62) {
+        return false;
+    }
+    const int rowLen = int(out.dims[out.rank - 1]);
+    int mode;
+    if (sameShape(b, out)) {
+        mode = 0;
+        if (!aligned16(b.ptr)) {
+            return false;
+        }
+    } else if (packedNumel(b) == 1 && b.rank == out.rank) {
+        mode = 2;
+    } else if (rowBroadcast(b, out) && rowLen % 4 == 0) {
+        mode = 1;
+    } else {
+        return false;
+    }
+    const auto *pa = reinterpret_cast<const int32_t *>(a.ptr), *pb = reinterpret_cast<const int32_t *>(b.ptr);
+    auto *po = reinterpret_cast<int32_t *>(out.ptr);
+    if (op == BIN_ADD) {
+        launchBinary<kVecAdd>(pa, pb, po, n, mode, rowLen, 0, s);
+    } else if (op == BIN_SUB) {
+        launchBinary<kVecSub>(pa, pb, po, n, mode, rowLen, 0, s);
+    } else if (op == -1) {
+        launchBinary<kVecMul>(pa, pb, po, n, mode, rowLen, shift, s);
+    } else {
+        return false;
+    }
+    *rc = finish("element-wise int32");
+    return true;
+}
+
+bool vecClampI8(const TView &in, const TView &out, int64_t lo, int64_t hi, cudaStream_t s, int *rc) {
+    const int64_t n = packedNumel(in);
+    if (n <= 0 || n % 16 != 0 || n != packedNumel(out) || !sameShape(in, out) || in.dtype != MLEL_I8 || out.dtype != MLEL_I8 ||
+        !aligned16(in.ptr) || !aligned16(out.ptr)) {
+        return false;
+    }
+    clampI8Kernel<<<gridFor(n / 16, kThreads, 16), kThreads, 0, s>>>(reinterpret_cast<const int8_t *>(in.ptr),
+                                                                     reinterpret_cast<int8_t *>(out.ptr), n / 16, int(lo), int(hi));
+    *rc = finish("CLAMP");
+    return true;
+}
+
+bool vecRowReduce(int32_t op, const TView &in, const TView &out, uint32_t axis, cudaStream_t s, int *rc) {
+    const int64_t n = packedNumel(in), rows = packedNumel(out);
+    if (n <= 0 || rows <= 0 || in.rank < 1 || int(axis) != in.rank - 1 || out.rank != in.rank || out.dims[axis] != 1 ||
+        in.dtype != out.dtype || !signedInt(in.dtype) || (op != RED_SUM && op != RED_MAX && op != RED_MIN) ||
+        !aligned16(in.ptr)) {
+        return false;
+    }
+    const int64_t len = in.dims[axis];
+    if (len % 4 != 0 || len > (1 << 30) || rows * len != n || (len * dtypeSize(in.dtype)) % 16 != 0) {
+        return false;
+    }
+    if (in.dtype == MLEL_I32) {
+        launchRowReduce<int32_t>(op, in, out, rows, int(len), s);
+    } else if (in.dtype == MLEL_I16) {
+        launchRowReduce<int16_t>(op, in, out, rows, int(len), s);
+    } else {
+        launchRowReduce<int8_t>(op, in, out, rows, int(len), s);
+    }
+    *rc = finish("REDUCE");
+    return true;
+}
+
+bool vecTransposeRows(const TView &in, const TView &out, const uint32_t *perms, cudaStream_t s, int *rc) {
+    const int64_t n = packedNumel(in);
+    const int rank = out.rank;
+    if (n <= 0 || n != packedNumel(out) || rank < 2 || in.rank != rank || in.dtype != out.dtype ||
+        int(perms[rank - 1]) != rank - 1 || !aligned16(in.ptr) || !aligned16(out.ptr)) {
+        return false;
+    }
+    const int64_t rowBytes = int64_t(out.dims[rank - 1]) * dtypeSize(out.dtype);
+    if (rowBytes % 16 != 0 || rowBytes / 16 > (1 << 24)) {
+        return false;
+    }
+    RowPermute p{};
+    p.rank = rank - 1;
+    for (int i = 0; i < rank - 1; ++i) {
+        if (perms[i] >= uint32_t(rank - 1) || in.dims[perms[i]] != out.dims[i]) {
+            return false;
+        }
+        p.outDims[i] = out.dims[i];
+        p.inStride[i] = in.strides[perms[i]];
+    }
+    const int64_t chunks = n * dtypeSize(out.dtype) / 16;
+    transposeRowsKernel<<<gridFor(chunks, kThreads, 16), kThreads, 0, s>>>(reinterpret_cast<const uint8_t *>(in.ptr),
+                                                                          reinterpret_cast<uint8_t *>(out.ptr), chunks,
+                                                                          int(rowBytes / 16), p);
+    *rc = finish("TRANSPOSE");
+    return true;
+}
+
+} // namespace mlel

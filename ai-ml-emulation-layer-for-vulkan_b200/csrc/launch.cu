@@ -210,6 +210,7 @@ const std::string &lastError() { return g_lastError; }
 int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
     const auto in = [&](size_t k) -> const TView & { return T[op.in[k]]; };
     const TView &out = T[op.out[0]];
+    int rc = MLEL_SUCCESS; // status of a vectorised kernel that took the operator
     if (op.tc) {
         // Addresses are only known here: pointers that are not 16-byte aligned go to the generic kernels.
         const bool aligned = ((reinterpret_cast<uintptr_t>(in(0).ptr) | reinterpret_cast<uintptr_t>(out.ptr)) & 15u) == 0;
@@ -233,6 +234,9 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         return genericMatmul(in(0), in(1), out, op.i[0], op.i[1], s);
     case OP_RESCALE: {
         RescaleAttr a{op.i[0], op.i[1], op.i[2], op.i[3], op.i[4]};
+        if (vecRescale(in(0), out, in(1), in(2), a, s, &rc)) {
+            return rc;
+        }
         return genericRescale(in(0), out, in(1), in(2), a, s);
     }
     case OP_AVG_POOL2D:
@@ -246,25 +250,43 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         }
         return genericMaxPool(in(0), out, poolAttr(op), s);
     case OP_TABLE:
+        if (vecTable(in(0), out, in(1), s, &rc)) {
+            return rc;
+        }
         return genericTable(in(0), out, in(1), s);
     case OP_TRANSPOSE: {
         uint32_t perms[kMaxRank];
         for (int k = 0; k < kMaxRank; ++k) {
             perms[k] = uint32_t(op.i[k]);
         }
+        if (vecTransposeRows(in(0), out, perms, s, &rc)) {
+            return rc;
+        }
         return genericTranspose(in(0), out, perms, s);
     }
     case OP_CONCAT:
         return genericConcat(in(0), out, uint32_t(op.i[0]), uint32_t(op.i[1]), s);
     case OP_CLAMP:
+        if (vecClampI8(in(0), out, wrapTo(out.dtype, int64_t(op.d[0])), wrapTo(out.dtype, int64_t(op.d[1])), s, &rc)) {
+            return rc;
+        }
         return genericClamp(in(0), out, op.d[0], op.d[1], s);
     case OP_BINARY:
+        if ((op.sub == BIN_ADD || op.sub == BIN_SUB) && vecBinaryI32(op.sub, in(0), in(1), out, 0, s, &rc)) {
+            return rc;
+        }
         return genericBinary(op.sub, in(0), in(1), out, s);
     case OP_UNARY:
         return genericUnary(op.sub, in(0), out, s);
     case OP_MUL:
+        if (vecBinaryI32(-1, in(0), in(1), out, uint32_t(op.i[0]), s, &rc)) {
+            return rc;
+        }
         return genericMul(in(0), in(1), out, uint32_t(op.i[0]), s);
     case OP_REDUCE:
+        if (vecRowReduce(op.sub, in(0), out, uint32_t(op.i[0]), s, &rc)) {
+            return rc;
+        }
         return genericReduce(op.sub, in(0), out, uint32_t(op.i[0]), s);
     case OP_CAST:
         return genericCast(in(0), out, s);

@@ -1,0 +1,122 @@
+"""GPU parity of the vectorised element-wise, table, reduction and row-transpose kernels.
+
+The generic kernels take every rank, stride and type; the vectorised ones take packed tensors whose sizes
+allow 4-, 8- or 16-byte accesses.  The shapes here are chosen to land on the vectorised kernels (the
+operator-by-operator tests in test_gpu_ops.py mostly use small odd shapes that do not); values include the
+extremes of each type.  All comparisons are bit-exact against the CPU oracle.
+"""
+import numpy as np
+import pytest
+
+from mlel_b200.graph_builder import GraphBuilder
+from tests.graph_eval import evaluate
+
+pytestmark = pytest.mark.gpu
+
+
+def rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+def full_range(r, dtype, shape):
+    info = np.iinfo(dtype)
+    data = r.integers(info.min, int(info.max) + 1, shape, dtype=np.int64).astype(dtype)
+    flat = data.reshape(-1)
+    extremes = [info.min, info.max, 0, -1]
+    flat[:min(4, flat.size)] = extremes[:min(4, flat.size)]
+    return data
+
+
+def check(g, inputs):
+    from mlel_b200.runtime import GraphRunner
+    want = evaluate(g, inputs)
+    got = GraphRunner(g, flags=1).run(inputs)  # no fusion: every operator runs as its own kernel
+    assert len(got) == len(want)
+    for k, (a, b) in enumerate(zip(got, want)):
+        assert a.dtype == b.dtype and a.shape == b.shape
+        if not np.array_equal(a, b):
+            bad = np.argwhere(a != b)
+            raise AssertionError(f"output {k}: {len(bad)} of {a.size} differ, first at {bad[0].tolist()}: "
+                                 f"got {a[tuple(bad[0])]} want {b[tuple(bad[0])]}")
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [
+    (np.int32, np.int8), (np.int32, np.int16), (np.int32, np.int32), (np.int8, np.int32), (np.int8, np.int8),
+    (np.int16, np.int32), (np.int16, np.int16), (np.int16, np.int8), (np.int8, np.int16),
+])
+@pytest.mark.parametrize("shift,double_round", [(0, False), (23, True), (31, True), (32, True), (45, True), (62, False)])
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_rescale(mlel, in_dtype, out_dtype, shift, double_round, per_channel):
+    r = rng(shift + 7 * per_channel)
+    shape = (3, 40, 64)
+    data = full_range(r, in_dtype, shape)
+    n = shape[-1] if per_channel else 1
+    mult = r.integers(1 << 30, (1 << 31) - 1, (n,), dtype=np.int64).astype(np.int32)
+    sh = np.full((n,), shift, np.int8)
+    if per_channel and shift >= 2:
+        sh[1::2] -= 1
+        mult[::3] = -mult[::3]  # negative multipliers are legal in the shader arithmetic
+    in_zp = int(np.iinfo(in_dtype).max) if in_dtype != np.int32 else -123456789
+    g = GraphBuilder()
+    x = g.input(in_dtype, shape)
+    g.output(g.rescale(x, mult, sh, in_zp, -3, out_dtype, True, double_round, per_channel))
+    check(g, [data])
+
+
+def test_table_int8_and_int16(mlel):
+    r = rng(1)
+    g = GraphBuilder()
+    a = g.input(np.int8, (5, 48, 64))
+    b = g.input(np.int16, (5, 48, 64))
+    g.output(g.table(a, r.integers(-128, 128, (256,), dtype=np.int8)))
+    g.output(g.table(b, r.integers(-32768, 32768, (513,), dtype=np.int16)))
+    check(g, [full_range(r, np.int8, (5, 48, 64)), full_range(r, np.int16, (5, 48, 64))])
+
+
+@pytest.mark.parametrize("b_shape", [(6, 24, 128), (6, 24, 1), (1, 1, 1)])
+def test_add_sub_mul_int32(mlel, b_shape):
+    r = rng(2)
+    shape = (6, 24, 128)
+    g = GraphBuilder()
+    a = g.input(np.int32, shape)
+    b = g.input(np.int32, b_shape)
+    g.output(g.add(a, b))
+    g.output(g.sub(a, b))
+    g.output(g.mul(a, b, 0))
+    g.output(g.mul(a, b, 17))
+    g.output(g.mul(a, b, 62))
+    check(g, [full_range(r, np.int32, shape), full_range(r, np.int32, b_shape)])
+
+
+def test_clamp_int8(mlel):
+    r = rng(3)
+    g = GraphBuilder()
+    x = g.input(np.int8, (4, 28, 28, 32))
+    g.output(g.clamp(x, -20, 127))
+    g.output(g.clamp(x, -128, 6))
+    check(g, [full_range(r, np.int8, (4, 28, 28, 32))])
+
+
+@pytest.mark.parametrize("dtype,length", [(np.int32, 384), (np.int32, 4), (np.int32, 768), (np.int16, 136), (np.int8, 400)])
+def test_reduce_along_the_last_axis(mlel, dtype, length):
+    r = rng(4)
+    shape = (3, 37, length)
+    g = GraphBuilder()
+    x = g.input(dtype, shape)
+    if dtype == np.int32:
+        g.output(g.reduce("REDUCE_SUM", x, 2))  # wraps modulo 2^32 in any order
+    g.output(g.reduce("REDUCE_MAX", x, 2))
+    g.output(g.reduce("REDUCE_MIN", x, 2))
+    check(g, [full_range(r, dtype, shape)])
+
+
+@pytest.mark.parametrize("dtype,shape,perms", [
+    (np.int8, (2, 48, 4, 64), (0, 2, 1, 3)), (np.int32, (3, 5, 7, 8), (2, 0, 1, 3)), (np.int16, (6, 10, 24), (1, 0, 2)),
+    (np.int8, (2, 3, 4, 5, 32), (3, 1, 0, 2, 4)),
+])
+def test_transpose_that_keeps_the_last_axis(mlel, dtype, shape, perms):
+    r = rng(5)
+    g = GraphBuilder()
+    x = g.input(dtype, shape)
+    g.output(g.transpose(x, perms))
+    check(g, [full_range(r, dtype, shape)])
