@@ -177,7 +177,8 @@ class Pipeline:
         check(lib().mlel_pipeline_create(ctypes.c_uint32(flags), ctypes.byref(self._h)))
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        # at interpreter shutdown the module globals may already be gone; the process is ending anyway
+        if getattr(self, "_h", None) and lib is not None:
             lib().mlel_pipeline_destroy(self._h)
             self._h = None
 
@@ -334,7 +335,7 @@ class Session:
         check(lib().mlel_session_create(pipeline._h, ctypes.byref(self._h)))
 
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:
             lib().mlel_session_destroy(self._h)
             self._h = None
 

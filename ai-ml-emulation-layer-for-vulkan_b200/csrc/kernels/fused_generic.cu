@@ -167,10 +167,16 @@ __global__ void depthwise3x3Kernel(const int8_t *__restrict__ in, const int8_t *
             }
         }
         int32_t add[4];
+        FastRescale fr[4]; // the fused RESCALE of this thread's four channels (OUT8 only)
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int32_t b = __ldg(bias + (biasCount == 1 ? 0 : c0 + k));
             add[k] = int32_t(uint32_t(b) - uint32_t(a.inZp) * uint32_t(wsum[k]));
+            if (OUT8) {
+                const int ci = epi.main.perChannel ? c0 + k : 0;
+                fr[k] = makeFastRescale(__ldg(epi.main.mult + ci), int32_t(__ldg(epi.main.shift + ci)), epi.main.inZp,
+                                        epi.main.doubleRound != 0);
+            }
         }
 #pragma unroll
         for (int px = 0; px < PX; ++px) {
@@ -184,7 +190,7 @@ __global__ void depthwise3x3Kernel(const int8_t *__restrict__ in, const int8_t *
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int32_t v = int32_t(uint32_t(acc[px][k]) + uint32_t(add[k]));
-                    word |= uint32_t(uint8_t(epilogue(epi, v, uint32_t(c0 + k), flat + k))) << (8 * k);
+                    word |= uint32_t(uint8_t(fastRescale(fr[k], v, epi.main.outZp, epi.main.lo, epi.main.hi))) << (8 * k);
                 }
                 *reinterpret_cast<uint32_t *>(static_cast<int8_t *>(out) + flat) = word;
             } else {

@@ -68,6 +68,8 @@ bool vecBinaryI32(int32_t op, const TView &a, const TView &b, const TView &out, 
 bool vecClampI8(const TView &in, const TView &out, int64_t lo, int64_t hi, cudaStream_t s, int *rc);
 bool vecRowReduce(int32_t op, const TView &in, const TView &out, uint32_t axis, cudaStream_t s, int *rc);
 bool vecTransposeRows(const TView &in, const TView &out, const uint32_t *perms, cudaStream_t s, int *rc);
+// one-byte elements, the input's last axis becomes the output's second-to-last and another axis its last
+bool vecTransposeLast2Bytes(const TView &in, const TView &out, const uint32_t *perms, cudaStream_t s, int *rc);
 
 // generic_ops.cu
 int genericConv2d(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,

@@ -332,6 +332,50 @@ __global__ void transposeRowsKernel(const uint8_t *__restrict__ in, uint8_t *__r
     }
 }
 
+// ---- TRANSPOSE that swaps the last axis with another one, one-byte elements ------------------------------------
+// out[..., c, r] = in[..., r (axis p), ..., c (last axis)]: per combination of the other axes a 2-D transpose of
+// an R x Ccols byte matrix whose rows are `inRowStride` bytes apart.  64 x 64 tiles through shared memory,
+// 16-byte loads and stores.
+struct BatchPermute {
+    uint32_t outDims[kMaxRank]; // output dims of the outer axes (all but the last two)
+    int64_t inStride[kMaxRank]; // input byte stride of the axis each of them comes from
+    int rank;
+};
+
+__global__ void __launch_bounds__(256) transposeLast2BytesKernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out,
+                                                                 int R, int Ccols, int64_t inRowStride, BatchPermute p) {
+    __shared__ uint8_t tile[64][64 + 16]; // [r][c]
+    int64_t batch = blockIdx.z;
+    int64_t src = 0;
+#pragma unroll
+    for (int i = kMaxRank - 1; i >= 0; --i) {
+        if (i < p.rank) {
+            src += int64_t(batch % p.outDims[i]) * p.inStride[i];
+            batch /= p.outDims[i];
+        }
+    }
+    const uint8_t *mat = in + src;
+    uint8_t *dst = out + int64_t(blockIdx.z) * R * Ccols;
+    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int t = threadIdx.x;
+    const int lr = t >> 2, ls = (t & 3) * 16; // load: row r0 + lr, bytes c0 + ls ..; store: row c0 + lr, bytes r0 + ls ..
+    int4 v = make_int4(0, 0, 0, 0);
+    if (r0 + lr < R && c0 + ls < Ccols) {
+        v = __ldg(reinterpret_cast<const int4 *>(mat + int64_t(r0 + lr) * inRowStride + c0 + ls));
+    }
+    *reinterpret_cast<int4 *>(&tile[lr][ls]) = v;
+    __syncthreads();
+    if (c0 + lr < Ccols && r0 + ls < R) {
+        uint32_t words[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            words[i >> 2] |= uint32_t(tile[ls + i][lr]) << (8 * (i & 3));
+        }
+        *reinterpret_cast<int4 *>(dst + int64_t(c0 + lr) * R + r0 + ls) =
+            make_int4(int(words[0]), int(words[1]), int(words[2]), int(words[3]));
+    }
+}
+
 } // namespace
 
 bool vecRescale(const TView &in, const TView &out, const TView &mult, const TView &shift, const RescaleAttr &a, cudaStream_t s,
@@ -482,6 +526,43 @@ bool vecTransposeRows(const TView &in, const TView &out, const uint32_t *perms, 
     transposeRowsKernel<<<gridFor(chunks, kThreads, 16), kThreads, 0, s>>>(reinterpret_cast<const uint8_t *>(in.ptr),
                                                                           reinterpret_cast<uint8_t *>(out.ptr), chunks,
                                                                           int(rowBytes / 16), p);
+    *rc = finish("TRANSPOSE");
+    return true;
+}
+
+bool vecTransposeLast2Bytes(const TView &in, const TView &out, const uint32_t *perms, cudaStream_t s, int *rc) {
+    const int64_t n = packedNumel(in);
+    const int rank = out.rank;
+    if (n <= 0 || n != packedNumel(out) || rank < 2 || in.rank != rank || in.dtype != out.dtype || dtypeSize(out.dtype) != 1 ||
+        int(perms[rank - 2]) != rank - 1 || int(perms[rank - 1]) == rank - 1 || !aligned16(in.ptr) || !aligned16(out.ptr)) {
+        return false;
+    }
+    const uint32_t pAxis = perms[rank - 1];
+    const int64_t R = in.dims[pAxis], Ccols = in.dims[rank - 1];
+    const int64_t inRowStride = in.strides[pAxis];
+    if (R % 16 != 0 || Ccols % 16 != 0 || inRowStride % 16 != 0 || out.dims[rank - 1] != R || out.dims[rank - 2] != Ccols) {
+        return false;
+    }
+    BatchPermute p{};
+    p.rank = rank - 2;
+    int64_t batches = 1;
+    for (int i = 0; i < rank - 2; ++i) {
+        if (perms[i] >= uint32_t(rank) || perms[i] == pAxis || int(perms[i]) == rank - 1 || in.dims[perms[i]] != out.dims[i]) {
+            return false;
+        }
+        p.outDims[i] = out.dims[i];
+        p.inStride[i] = in.strides[perms[i]];
+        if (p.inStride[i] % 16 != 0) {
+            return false;
+        }
+        batches *= out.dims[i];
+    }
+    if (batches > 65535 || (R + 63) / 64 > 65535) {
+        return false;
+    }
+    const dim3 grid(unsigned((Ccols + 63) / 64), unsigned((R + 63) / 64), unsigned(batches));
+    transposeLast2BytesKernel<<<grid, 256, 0, s>>>(reinterpret_cast<const uint8_t *>(in.ptr), reinterpret_cast<uint8_t *>(out.ptr),
+                                                   int(R), int(Ccols), inRowStride, p);
     *rc = finish("TRANSPOSE");
     return true;
 }

@@ -259,7 +259,7 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         for (int k = 0; k < kMaxRank; ++k) {
             perms[k] = uint32_t(op.i[k]);
         }
-        if (vecTransposeRows(in(0), out, perms, s, &rc)) {
+        if (vecTransposeRows(in(0), out, perms, s, &rc) || vecTransposeLast2Bytes(in(0), out, perms, s, &rc)) {
             return rc;
         }
         return genericTranspose(in(0), out, perms, s);

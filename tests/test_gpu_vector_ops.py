@@ -120,3 +120,15 @@ def test_transpose_that_keeps_the_last_axis(mlel, dtype, shape, perms):
     x = g.input(dtype, shape)
     g.output(g.transpose(x, perms))
     check(g, [full_range(r, dtype, shape)])
+
+
+@pytest.mark.parametrize("shape,perms", [
+    ((2, 48, 4, 64), (0, 2, 3, 1)),   # attention keys: [batch, seq, heads, d] -> [batch, heads, d, seq]
+    ((3, 32, 80), (0, 2, 1)), ((80, 144), (1, 0)), ((2, 16, 3, 5, 32), (3, 0, 2, 4, 1)),
+])
+def test_transpose_that_swaps_the_last_axis_of_bytes(mlel, shape, perms):
+    r = rng(6)
+    g = GraphBuilder()
+    x = g.input(np.int8, shape)
+    g.output(g.transpose(x, perms))
+    check(g, [full_range(r, np.int8, shape)])
