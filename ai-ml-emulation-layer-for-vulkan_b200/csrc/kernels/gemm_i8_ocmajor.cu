@@ -5,9 +5,10 @@
 //
 //   A operand  - weight tile, 128 output channels x 128 K bytes, TMA from the OHWI weight matrix [OC][K]
 //   B operand  - BNP (128 or 256) output pixels x 128 K bytes: TMA tiles of a row-major pixel matrix (1x1
-//                stride-1 convolution); TMA in im2col mode when the channel count is a multiple of 128 (one
-//                instruction fetches one tap, 128 channels, of all the tile's windows, zero-filled outside
-//                the image); else gathered with 16-byte cp.async (segment gather)
+//                stride-1 convolution); TMA in im2col mode for other windows (one instruction fetches one tap,
+//                128 channels, of all the tile's windows, zero-filled outside the image and past the last
+//                channel, so any channel count that is a multiple of 16 works; the weight tile is zero-filled
+//                the same way); gathered with 16-byte cp.async (segment gather) if the driver refuses the map
 //   accumulator- TMEM lane = output channel, TMEM column = pixel; two accumulators of BNP columns alternate
 //   C/D tile   - a [BNP pixels][128 channels] byte tile in shared memory, two of them alternating with the
 //                accumulators: TMA brings the shortcut bytes of the residual tail into it, the epilogue
@@ -354,7 +355,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     constexpr bool X_TMA = X_MODE != kXGather;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int numKb = (p.K + BK - 1) / BK;
+    const int numKb = X_MODE == kXIm2col ? p.KH * p.KW * p.kbPerTap : (p.K + BK - 1) / BK;
     const int pTiles = (p.M + BNP - 1) / BNP;
     const int cTiles = (p.N + kOcTile - 1) / kOcTile;
     const int64_t numTiles = int64_t(pTiles) * cTiles * p.batches;
@@ -430,7 +431,11 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                         break;
                     }
                     mbarArriveExpectTx(&bars->full[s], uint32_t(kTileW + (X_TMA ? kTileX : 0)));
-                    tmaLoad3d(&tmapW, tilesW + s * kTileW, &bars->full[s], kb * BK, tc.c0, 0);
+                    if (X_MODE == kXIm2col) {
+                        tmaLoad3d(&tmapW, tilesW + s * kTileW, &bars->full[s], cb, ky * p.KW + kx, tc.c0);
+                    } else {
+                        tmaLoad3d(&tmapW, tilesW + s * kTileW, &bars->full[s], kb * BK, tc.c0, 0);
+                    }
                     if (X_MODE == kXTiled) {
                         // boxes hold at most 256 rows of 128 bytes: one copy per 128 pixels
 #pragma unroll
@@ -632,13 +637,16 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
             return MLEL_ERROR_DEVICE;
         }
         xMode = kXTiled;
-    } else if (p.gatherTable == nullptr && p.IC % 128 == 0 && (reinterpret_cast<uintptr_t>(p.in) & 15u) == 0 &&
+    } else if (p.gatherTable == nullptr && p.IC % 16 == 0 && (reinterpret_cast<uintptr_t>(p.in) & 15u) == 0 &&
+               (reinterpret_cast<uintptr_t>(q.bMatrix) & 15u) == 0 &&
                makeIm2colMap(&maps.x, p.in, p.M / (p.OH * p.OW), p.H, p.W, p.IC, p.KH, p.KW, p.padTop, p.padLeft, p.OH, p.OW,
-                             p.strideY, p.strideX, p.dilY, p.dilX, boxPixels)) {
+                             p.strideY, p.strideX, p.dilY, p.dilX, boxPixels) &&
+               makeWeightTapMap(&maps.w, q.bMatrix, p.IC, p.KH * p.KW, p.N, kOcTile)) {
         xMode = kXIm2col;
+        p.kbPerTap = (p.IC + 127) / 128;
     }
-    if (!makeMap(&maps.w, q.bMatrix, uint64_t(p.K), uint64_t(p.N), 1, uint64_t(q.bRowBytes),
-                 uint64_t(q.bRowBytes) * uint64_t(p.N), BK, kOcTile)) {
+    if (xMode != kXIm2col && !makeMap(&maps.w, q.bMatrix, uint64_t(p.K), uint64_t(p.N), 1, uint64_t(q.bRowBytes),
+                                      uint64_t(q.bRowBytes) * uint64_t(p.N), BK, kOcTile)) {
         return MLEL_ERROR_DEVICE;
     }
     // output and shortcut: [pixels][channels] bytes, unswizzled tiles of 128 channels x (128 or 256) pixels

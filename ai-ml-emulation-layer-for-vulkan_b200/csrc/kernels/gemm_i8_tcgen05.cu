@@ -62,6 +62,7 @@ struct __align__(16) ColConst {
     int32_t corr0;       // correction of the most common border class for this column
 };
 
+constexpr int kAGather = 0, kATiled = 1, kAIm2col = 2;
 constexpr int kMaxGatherPieces = 1024; // entries of the shared-memory copy of GemmI8Params::gatherTable
 
 struct TileCoord {
@@ -345,11 +346,13 @@ __device__ __forceinline__ void gatherPieces(const int8_t *origin, const int32_t
     }
 }
 
-// A_TMA: A comes through tmapA; otherwise it is gathered from the NHWC input described by p.
+// A_MODE: how the A (pixel) operand arrives: kAGather = gathered from the NHWC input described by p, kATiled =
+// tmapA is a plain matrix, kAIm2col = tmapA is an im2col map of the NHWC input and tmapB a {IC, taps, OC} map.
 // B_MN : B is an N-contiguous [K][N] matrix (MN-major operand), otherwise a K-contiguous [N][K] matrix.
-template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
-__global__ void __launch_bounds__(A_TMA ? kThreadsTma : kThreadsGather, 1)
+template <int BN, int NSTAGE, int A_MODE, bool B_MN>
+__global__ void __launch_bounds__(A_MODE != kAGather ? kThreadsTma : kThreadsGather, 1)
 gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const GemmI8Params p) {
+    constexpr bool A_TMA = A_MODE != kAGather;
     extern __shared__ uint8_t rawSmem[];
     // SWIZZLE_128B tiles must start on 1024-byte boundaries.
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(rawSmem) + 1023) & ~uintptr_t(1023));
@@ -367,7 +370,7 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int numKb = (p.K + BK - 1) / BK;
+    const int numKb = A_MODE == kAIm2col ? p.KH * p.KW * p.kbPerTap : (p.K + BK - 1) / BK;
     const int mTiles = (p.M + BM - 1) / BM;
     const int nTiles = (p.N + BN - 1) / BN;
     const int64_t numTiles = int64_t(mTiles) * nTiles * p.batches;
@@ -419,6 +422,15 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
             bool ok = true;
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
                 const TileCoord tc = tileOf(t);
+                // im2col mode: first tap of the tile's first window, and the running position on the K axis
+                int w0 = 0, h0 = 0, n0 = 0, kx = 0, ky = 0, cb = 0;
+                if (A_MODE == kAIm2col) {
+                    n0 = tc.m0 / (p.OH * p.OW);
+                    const int rem = tc.m0 - n0 * p.OH * p.OW;
+                    const int oy = rem / p.OW;
+                    h0 = oy * p.strideY - p.padTop;
+                    w0 = (rem - oy * p.OW) * p.strideX - p.padLeft;
+                }
                 for (int kb = 0; kb < numKb; ++kb, ++it) {
                     const int s = int(it % NSTAGE);
                     const uint32_t phase = (it / NSTAGE) & 1u;
@@ -427,10 +439,22 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                         break;
                     }
                     mbarArriveExpectTx(&bars->full[s], uint32_t((A_TMA ? kTileA : 0) + kTileB));
-                    if (A_TMA) {
+                    if (A_MODE == kATiled) {
                         tmaLoad3d(&tmapA, tilesA + s * kTileA, &bars->full[s], kb * BK, tc.m0, tc.batch);
                     }
-                    if (B_MN) {
+                    if (A_MODE == kAIm2col) {
+                        tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], cb, ky * p.KW + kx, tc.n0);
+                        tmaLoadIm2col4d(&tmapA, tilesA + s * kTileA, &bars->full[s], cb, w0, h0, n0, uint16_t(kx * p.dilX),
+                                        uint16_t(ky * p.dilY));
+                        cb += BK;
+                        if (cb >= p.IC) {
+                            cb = 0;
+                            if (++kx == p.KW) {
+                                kx = 0;
+                                ++ky;
+                            }
+                        }
+                    } else if (B_MN) {
                         tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], tc.n0, kb * BK, tc.batch);
                     } else {
                         tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], kb * BK, tc.n0, p.batchedB ? tc.batch : 0);
@@ -584,12 +608,12 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
 
 // ---- host side --------------------------------------------------------------------------------------------
 
-template <int BN, int NSTAGE, bool A_TMA, bool B_MN>
+template <int BN, int NSTAGE, int A_MODE, bool B_MN>
 int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes =
         size_t(NSTAGE) * (BM * BK + BN * BK) + BN * (sizeof(ColConst) + 4) + sizeof(PipeBarriers) + 1024 +
-        (A_TMA ? 0 : (kMaxGatherPieces + kTapTabEntries) * sizeof(int32_t) + 16);
-    auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_TMA, B_MN>;
+        (A_MODE != kAGather ? 0 : (kMaxGatherPieces + kTapTabEntries) * sizeof(int32_t) + 16);
+    auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_MODE, B_MN>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smemBytes)) != cudaSuccess) {
@@ -600,7 +624,7 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8
     }
     const int64_t tiles = int64_t((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batches;
     const int grid = int(tiles < smCount() ? tiles : smCount()); // persistent: one CTA per SM
-    const cudaError_t err = launchDependent(kernel, grid, A_TMA ? kThreadsTma : kThreadsGather, smemBytes, s, mapA, mapB, p);
+    const cudaError_t err = launchDependent(kernel, grid, A_MODE != kAGather ? kThreadsTma : kThreadsGather, smemBytes, s, mapA, mapB, p);
     if (err != cudaSuccess) {
         setLastError(std::string("tcgen05 int8 GEMM launch: ") + cudaGetErrorString(err));
         return MLEL_ERROR_DEVICE;
@@ -614,16 +638,27 @@ int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
     GemmI8Params p = q.params;
     p.batches = q.batches;
     CUtensorMap mapA{}, mapB{};
-    const bool aTma = q.aMatrix != nullptr;
-    if (aTma) {
+    const int bn = (!q.bMnMajor && p.N <= 64) ? 64 : 128;
+    int aMode = kAGather;
+    if (q.aMatrix != nullptr) {
         // A: [batches][M][K], K contiguous
         if (!makeMap(&mapA, q.aMatrix, uint64_t(p.K), uint64_t(p.M), uint64_t(q.batches), uint64_t(q.aRowBytes),
                      uint64_t(q.aBatchBytes), BK, BM)) {
             return MLEL_ERROR_DEVICE;
         }
+        aMode = kATiled;
+    } else if (p.gatherTable == nullptr && !q.bMnMajor && !p.batchedB && q.batches == 1 && p.IC % 16 == 0 && p.KH > 0 &&
+               ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(q.bMatrix)) & 15u) == 0 &&
+               makeIm2colMap(&mapA, p.in, p.M / (p.OH * p.OW), p.H, p.W, p.IC, p.KH, p.KW, p.padTop, p.padLeft, p.OH, p.OW,
+                             p.strideY, p.strideX, p.dilY, p.dilX, BM) &&
+               makeWeightTapMap(&mapB, q.bMatrix, p.IC, p.KH * p.KW, p.N, uint32_t(bn))) {
+        // a window over a multiple of 16 channels: hardware im2col loads, zero-filled past the last channel
+        aMode = kAIm2col;
+        p.kbPerTap = (p.IC + 127) / 128;
     }
-    const int bn = (!q.bMnMajor && p.N <= 64) ? 64 : 128;
-    if (q.bMnMajor) {
+    if (aMode == kAIm2col) {
+        // tmapB is the {IC, taps, OC} weight map made above
+    } else if (q.bMnMajor) {
         // B: [batches][K][N], N contiguous
         if (!makeMap(&mapB, q.bMatrix, uint64_t(p.N), uint64_t(p.K), uint64_t(q.batches), uint64_t(q.bRowBytes),
                      uint64_t(q.bBatchBytes), 128, BK)) {
@@ -638,15 +673,17 @@ int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
         }
     }
     if (q.bMnMajor) {
-        return aTma ? launchVariant<128, 6, true, true>(mapA, mapB, p, s)
-                    : launchVariant<128, 6, false, true>(mapA, mapB, p, s);
+        return aMode == kATiled ? launchVariant<128, 6, kATiled, true>(mapA, mapB, p, s)
+                                : launchVariant<128, 6, kAGather, true>(mapA, mapB, p, s);
     }
     if (bn == 64) {
-        return aTma ? launchVariant<64, 8, true, false>(mapA, mapB, p, s)
-                    : launchVariant<64, 8, false, false>(mapA, mapB, p, s);
+        return aMode == kATiled    ? launchVariant<64, 8, kATiled, false>(mapA, mapB, p, s)
+               : aMode == kAIm2col ? launchVariant<64, 8, kAIm2col, false>(mapA, mapB, p, s)
+                                   : launchVariant<64, 8, kAGather, false>(mapA, mapB, p, s);
     }
-    return aTma ? launchVariant<128, 6, true, false>(mapA, mapB, p, s)
-                : launchVariant<128, 6, false, false>(mapA, mapB, p, s);
+    return aMode == kATiled    ? launchVariant<128, 6, kATiled, false>(mapA, mapB, p, s)
+           : aMode == kAIm2col ? launchVariant<128, 6, kAIm2col, false>(mapA, mapB, p, s)
+                               : launchVariant<128, 6, kAGather, false>(mapA, mapB, p, s);
 }
 
 int tcgen05ErrorFlag() {

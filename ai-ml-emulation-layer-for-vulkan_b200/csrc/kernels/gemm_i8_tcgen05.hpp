@@ -24,6 +24,8 @@ struct GemmI8Params {
     // in + ((n * H + oy * strideY) * W + ox * strideX) * IC.  Null => gather 16-byte pieces with bounds checks.
     const int32_t *gatherTable;
     int32_t chunkBytes;
+    // im2col TMA mode (set by the launchers): K blocks per tap = ceil(IC / 128), each zero-filled past IC; 0 = off
+    int32_t kbPerTap;
     // correction term added to the raw accumulator: corr[(batch,) class, n]
     const int32_t *corr;
     const uint8_t *rowClass; // [OH] border class of an output row, or null (single class)

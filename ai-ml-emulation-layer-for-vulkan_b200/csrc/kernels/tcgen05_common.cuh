@@ -309,6 +309,23 @@ inline bool makeMap(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1
     return true;
 }
 
+// Weights [OC][taps][IC] (OHWI) as a 3-D map {IC, taps, OC} with a {128, 1, rows} box: one load brings 128
+// channels of one tap for `rows` output channels, zero-filled past IC.  Pairs with the im2col map below, whose
+// loads are padded the same way, so that any channel count that is a multiple of 16 works.
+inline bool makeWeightTapMap(CUtensorMap *map, const void *base, int IC, int taps, int OC, uint32_t rows) {
+    EncodeTiledFn fn = encodeTiled();
+    if (fn == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[3] = {cuuint64_t(IC), cuuint64_t(taps), cuuint64_t(OC)};
+    const cuuint64_t strides[2] = {cuuint64_t(IC), cuuint64_t(IC) * taps};
+    const cuuint32_t box[3] = {128, 1, rows};
+    const cuuint32_t elemStrides[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, elemStrides,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 using EncodeIm2colFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                     const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t,
                                     const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
