@@ -1,4 +1,4 @@
-"""Batch sharding of a data-graph dispatch over ranks (one process per GPU).
+"""Sharding of a data-graph dispatch over ranks (one process per GPU): by batch, and by output channel.
 
 A TOSA data graph of the kind this library runs treats the images of a batch independently: every
 operator on the path is per-pixel, per-window or per-row of one image, so a batch of B images can be
@@ -65,3 +65,53 @@ def all_gather_batch(local: torch.Tensor, total: int, group=None) -> torch.Tenso
     pieces = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(pieces, padded, group=group)
     return torch.cat([pieces[r][:shard_range(total, world, r)[1]] for r in range(world)], dim=0)
+
+
+# ---- output-channel sharding of one large MATMUL ---------------------------------------------------------------
+#
+# A single-batch (or few-batch) MATMUL  out[n, h, w] = sum_c A[n, h, c] * B[n, c, w]  with its RESCALE can be cut
+# along w: every rank keeps all of A, takes a block of B's columns and the matching slice of the per-channel
+# RESCALE parameters, and computes  out[:, :, w0:w1]  with the fused epilogue.  The contraction axis is never
+# split, so no reduction crosses ranks and the integer results are the same bits as on one GPU; the only exchange
+# is the all-gather of the column blocks.
+
+def shard_columns(total: int, world: int, rank: int, align: int = 16) -> Tuple[int, int]:
+    """``(first, count)`` of the block of ``total`` output columns owned by ``rank``.
+
+    Blocks are multiples of ``align`` columns (the tensor-core path moves 16-byte pieces of a row) except that
+    the last non-empty block takes the remainder; ranks past the end get an empty block."""
+    if world <= 0 or not 0 <= rank < world or total < 0 or align <= 0:
+        raise ValueError(f"bad shard request: total={total} world={world} rank={rank} align={align}")
+    units = -(-total // align)  # blocks of `align` columns, the last one possibly short
+    first_unit, count_units = shard_range(units, world, rank)
+    first = min(first_unit * align, total)
+    last = min((first_unit + count_units) * align, total)
+    return first, last - first
+
+
+def shard_matmul_operands(b: np.ndarray, per_channel: Sequence[np.ndarray], world: int, rank: int,
+                          align: int = 16) -> Tuple[np.ndarray, List[np.ndarray]]:
+    """The rank's column block of ``b`` ``[N, C, W]`` and the same slice of every per-channel parameter vector
+    (RESCALE multipliers and shifts of length ``W``; vectors of length 1 are per-tensor and pass unchanged)."""
+    first, count = shard_columns(b.shape[2], world, rank, align)
+    params = [np.ascontiguousarray(p if p.shape[0] == 1 else p[first:first + count]) for p in per_channel]
+    return np.ascontiguousarray(b[:, :, first:first + count]), params
+
+
+def all_gather_columns(local: torch.Tensor, total: int, align: int = 16, group=None) -> torch.Tensor:
+    """Joins every rank's ``[N, H, count]`` block along the last axis into ``[N, H, total]`` on every rank.
+
+    The column axis is the contiguous one, so the blocks are exchanged as whole tensors (padded to the widest
+    block) and interleaved locally."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    first, count = shard_columns(total, world, rank, align)
+    if local.shape[-1] != count:
+        raise ValueError(f"rank {rank} holds {local.shape[-1]} columns, its block of {total} has {count}")
+    widest = max(shard_columns(total, world, r, align)[1] for r in range(world))
+    padded = torch.zeros(tuple(local.shape[:-1]) + (widest,), dtype=local.dtype, device=local.device)
+    padded[..., :count] = local
+    pieces = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(pieces, padded, group=group)
+    return torch.cat([pieces[r][..., :shard_columns(total, world, r, align)[1]] for r in range(world)], dim=-1)
+
