@@ -83,17 +83,32 @@ __device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, const void *s
 }
 
 // High 32 bits of v * mult + (v >= thr ? rp : rn): product and rounding of a RESCALE whose shift is at least
-// 32, where the result only depends on the high word.  The compare feeds two predicated multiply-adds,
-// which run on the FMA pipe; the integer ALU pipe, which bounds this epilogue, sees one instruction.
+// 32, where the result only depends on the high word.  The rounding constant is selected first (two selects),
+// so that the 64-bit addition rides on the multiply-add; adding it afterwards costs two instructions per
+// candidate constant.
 __device__ __forceinline__ int32_t scaleHigh(int32_t v, int32_t mult, int32_t thr, uint64_t rp, uint64_t rn) {
+    const bool nonNeg = v >= thr;
+    const uint32_t lo = nonNeg ? uint32_t(rp) : uint32_t(rn);
+    const uint32_t hi = nonNeg ? uint32_t(rp >> 32) : uint32_t(rn >> 32);
     uint64_t sum;
-    asm("{\n\t.reg .pred q;\n\t"
-        "setp.ge.s32 q, %1, %3;\n\t"
-        "@q mad.wide.s32 %0, %1, %2, %4;\n\t"
-        "@!q mad.wide.s32 %0, %1, %2, %5;\n\t}"
-        : "=l"(sum)
-        : "r"(v), "r"(mult), "r"(thr), "l"(rp), "l"(rn));
+    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(sum) : "r"(v), "r"(mult), "l"((uint64_t(hi) << 32) | lo));
     return int32_t(uint32_t(sum >> 32));
+}
+
+// Shared-memory accesses by 32-bit shared address (a pointer into dynamic shared memory that has been passed
+// through a few functions is otherwise accessed with generic 64-bit loads and stores).
+__device__ __forceinline__ uint32_t ldsU8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int32_t ldsS32(uint32_t addr) {
+    int32_t v;
+    asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void stsU8(uint32_t addr, int32_t v) {
+    asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
 // The rest of such a RESCALE: remaining shift, output zero point (wrapping add), clamp.
@@ -114,8 +129,8 @@ struct EpiConsts {
 // All shortcut bytes are read before the first result is written: the compiler must assume that a byte store
 // may alias any later load, and 16 load-compute-store chains in a row would run one after the other.
 template <bool RESIDUAL, bool FAST>
-__device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], const EpiConsts &k, const int32_t *lutA128,
-                                                 const int32_t *lutB, uint8_t *cd) {
+__device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t lutA128,
+                                                 uint32_t lutB, uint32_t cd) {
     constexpr int CH = 8; // pixels per group: enough independent chains, few enough live registers
 #pragma unroll
     for (int g = 0; g < 16; g += CH) {
@@ -123,7 +138,7 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
         if (RESIDUAL) {
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-                sc[j] = cd[128 * (g + j)];
+                sc[j] = ldsU8(cd + 128 * (g + j));
             }
         }
         int32_t r[CH];
@@ -139,7 +154,7 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
         if (RESIDUAL) {
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-                const int32_t sum = int32_t(uint32_t(lutA128[r[j]]) + uint32_t(lutB[sc[j]]));
+                const int32_t sum = int32_t(uint32_t(ldsS32(lutA128 + uint32_t(r[j] * 4))) + uint32_t(ldsS32(lutB + sc[j] * 4u)));
                 if (FAST) {
                     r[j] = finishHigh(scaleHigh(sum, k.fo.mult, k.fo.zpIn, k.rpO, k.rnO), k.fo.s2, k.outZpOut, k.loOut, k.hiOut);
                 } else {
@@ -149,14 +164,16 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
         }
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
-            cd[128 * (g + j)] = uint8_t(r[j]);
+            stsU8(cd + 128 * (g + j), r[j]);
         }
     }
 }
 
+// cd: shared address of this thread's column of the C/D tile at the slice's first pixel; lutA128 / lutB: shared
+// addresses of the residual tables (the first one at the entry of value 0).
 template <bool RESIDUAL>
-__device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const EpiConsts &k, const int32_t *lutA128,
-                                             const int32_t *lutB, uint8_t *cd) {
+__device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t lutA128,
+                                             uint32_t lutB, uint32_t cd) {
     if (k.fast) {
         rescaleSliceImpl<RESIDUAL, true>(acc, k, lutA128, lutB, cd);
     } else {
@@ -189,7 +206,8 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     }
     k.outZpMain = p.epi.main.outZp, k.loMain = p.epi.main.lo, k.hiMain = p.epi.main.hi;
     k.outZpOut = p.epi.out.outZp, k.loOut = p.epi.out.lo, k.hiOut = p.epi.out.hi;
-    const int32_t *lutA128 = lutA + 128; // indexed by the signed int8 value of the main stage
+    const uint32_t lutA128 = smemAddr(lutA + 128); // indexed by the signed int8 value of the main stage
+    const uint32_t lutBAddr = smemAddr(lutB);
     int curC0 = -1, curBatch = -1;
     const bool hasClasses = p.rowClass != nullptr;
     const int baseClass = p.baseClass;
@@ -252,7 +270,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmemBase + buf * uint32_t(BNP) + (uint32_t(quarter * 32) << 16) + uint32_t(part * kColsPerWarp);
         // this thread's column of the C/D tile, at the first pixel of its half
-        uint8_t *cd = cdTiles + buf * (BNP * 128) + (part * kColsPerWarp) * 128 + quarter * 32 + lane;
+        const uint32_t cd = smemAddr(cdTiles + buf * (BNP * 128) + (part * kColsPerWarp) * 128 + quarter * 32 + lane);
         const auto borderFix = [&](uint32_t (&acc)[16], int col) {
             // pixels of this slice whose window crosses the border take their own class's correction
             const uint32_t borderMask = __ballot_sync(0xffffffffu, lane < 16 && int(cls[col + (lane & 15)]) != baseClass);
@@ -284,7 +302,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                     borderFix(accA, part * kColsPerWarp + 16 * st);
                 }
                 if (warpLive) {
-                    rescaleSlice<RESIDUAL>(accA, k, lutA128, lutB, cd + (16 * st) * 128);
+                    rescaleSlice<RESIDUAL>(accA, k, lutA128, lutBAddr, cd + uint32_t((16 * st) * 128));
                 }
             }
         } else {
@@ -297,7 +315,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 borderFix(accA, part * kColsPerWarp + 16 * st);
             }
             if (warpLive) {
-                rescaleSlice<RESIDUAL>(accA, k, lutA128, lutB, cd + (16 * st) * 128);
+                rescaleSlice<RESIDUAL>(accA, k, lutA128, lutBAddr, cd + uint32_t((16 * st) * 128));
             }
             tmemWait16(accB);
             if (st + 2 < kSteps) {
@@ -313,7 +331,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 borderFix(accB, part * kColsPerWarp + 16 * (st + 1));
             }
             if (warpLive) {
-                rescaleSlice<RESIDUAL>(accB, k, lutA128, lutB, cd + (16 * (st + 1)) * 128);
+                rescaleSlice<RESIDUAL>(accB, k, lutA128, lutBAddr, cd + uint32_t((16 * (st + 1)) * 128));
             }
         }
         }
