@@ -59,22 +59,34 @@ __device__ __forceinline__ bool mbarTryWait(uint64_t *bar, uint32_t parity) {
                  : "memory");
     return ok != 0;
 }
-// Bounded wait: returns false (and records `code`) when the barrier did not complete in time.  Between
-// polls the waiter sleeps, a little longer each time up to a quarter of a microsecond, so that a waiting role
-// does not take issue slots from the warps that share its scheduler (the epilogue warps do the arithmetic);
-// the clock is read every 16th poll.
-__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int code, unsigned sleepNs = 32) {
+// The same with a suspend-time hint: the thread may stay suspended in hardware for up to `hintNs`
+// nanoseconds waiting for the phase to complete, instead of coming back to poll.
+__device__ __forceinline__ bool mbarTryWaitHint(uint64_t *bar, uint32_t parity, uint32_t hintNs) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smemAddr(bar)), "r"(parity), "r"(hintNs)
+                 : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false (and records `code`) when the barrier did not complete in time.  A waiter that
+// does not get through at once suspends in hardware between checks, so that a waiting role does not take issue
+// slots from the warps that share its scheduler (the epilogue warps do the arithmetic); the clock is read every
+// 64th check.
+__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int code) {
     if (mbarTryWait(bar, parity)) {
         return true;
     }
     const long long start = clock64();
     unsigned polls = 0;
-    while (!mbarTryWait(bar, parity)) {
-        __nanosleep(sleepNs);
-        sleepNs = sleepNs < 256u ? sleepNs * 2u : 256u;
-        if ((++polls & 15u) == 0 && clock64() - start > kWaitLimitCycles) {
-            atomicCAS(&g_tcgen05Error, 0, code);
-            return false;
+    while (!mbarTryWaitHint(bar, parity, 1000u)) {
+        if ((++polls & 63u) == 0) {
+            if (clock64() - start > kWaitLimitCycles) {
+                atomicCAS(&g_tcgen05Error, 0, code);
+                return false;
+            }
         }
     }
     return true;
