@@ -53,14 +53,19 @@ struct __align__(8) PipeBarriers {
     uint32_t pad;
 };
 
-// Constants of the main RESCALE stage for one output column (see FastRescale).
-// One 16-byte shared-memory read per element: the rounding constant for negative inputs is the positive
-// one minus 2^31 (double rounding) or the same (single rounding), so it is derived, not stored.
+// Constants of the main RESCALE stage for one output column (see FastRescale): two 16-byte shared-memory reads
+// per element, by shared address.
 struct __align__(16) ColConst {
     int32_t mult;
-    uint32_t rpLo, rpHi; // rounding constant for v >= zpIn (input zero point folded in)
     int32_t corr0;       // correction of the most common border class for this column
+    uint32_t rpLo, rpHi; // rounding constant for v >= zpIn (input zero point folded in)
+    uint32_t rnLo, rnHi; // rounding constant for v <  zpIn
+    int32_t s1, s2;      // min(shift, 32), max(shift - 32, 0)
 };
+
+__device__ __forceinline__ void ldsV4(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
 
 constexpr int kAGather = 0, kATiled = 1, kAIm2col = 2;
 constexpr int kMaxGatherPieces = 1024; // entries of the shared-memory copy of GemmI8Params::gatherTable
@@ -95,7 +100,7 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                              p.epi.out.doubleRound != 0);
     }
     const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp;
-    uint32_t *shiftTab = reinterpret_cast<uint32_t *>(colTab + BN);
+    const uint32_t tabAddr = smemAddr(colTab);
     const int32_t loMain = p.epi.main.lo, hiMain = p.epi.main.hi;
     uint32_t tileCount = 0;
     int tabN0 = -1, tabBatch = -1; // what the shared constants table was built for
@@ -117,13 +122,9 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                 const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
                                                       zpMain, p.epi.main.doubleRound != 0);
                 ColConst c;
-                c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi;
+                c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi, c.rnLo = f.rnLo, c.rnHi = f.rnHi, c.s1 = f.s1, c.s2 = f.s2;
                 c.corr0 = col < p.N ? __ldg(corrBatch + int64_t(p.baseClass) * p.N + col) : 0;
                 colTab[threadIdx.x] = c;
-                // bits 0-5: min(shift, 32); bits 8-12: max(shift - 32, 0); bit 31: the two rounding
-                // constants differ (double rounding with shift > 31)
-                const bool twoRounds = f.rpLo != f.rnLo || f.rpHi != f.rnHi;
-                shiftTab[threadIdx.x] = uint32_t(f.s1) | (uint32_t(f.s2) << 8) | (twoRounds ? 0x80000000u : 0u);
             }
             epilogueSync();
             tabN0 = n0;
@@ -195,19 +196,17 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = 4 * q + e;
-                    const ColConst c = colTab[cl + j];
-                    const uint32_t sh = shiftTab[cl + j];
-                    const int32_t v = int32_t(acc[j] + uint32_t(c.corr0));
-                    uint64_t round = (uint64_t(c.rpHi) << 32) | uint64_t(c.rpLo);
-                    if (v < zpMain) {
-                        round -= uint64_t(sh >> 31) << 31; // double rounding: -2^30 instead of +2^30
-                    }
+                    uint32_t mult, corr0, rpLo, rpHi, rnLo, rnHi, s1, s2;
+                    ldsV4(tabAddr + uint32_t(cl + j) * 32u, mult, corr0, rpLo, rpHi);
+                    ldsV4(tabAddr + uint32_t(cl + j) * 32u + 16u, rnLo, rnHi, s1, s2);
+                    const int32_t v = int32_t(acc[j] + corr0);
+                    // the rounding constant is selected first, so that the 64-bit addition rides on the multiply-add
+                    const bool nonNeg = v >= zpMain;
+                    const uint64_t round = (uint64_t(nonNeg ? rpHi : rnHi) << 32) | uint64_t(nonNeg ? rpLo : rnLo);
                     uint64_t sum;
-                    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(sum) : "r"(v), "r"(c.mult), "l"(round));
-                    const uint32_t tq = __funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), sh & 63u);
-                    int32_t r = int32_t(tq) >> ((sh >> 8) & 31u);
-                    r = int32_t(uint32_t(r) + uint32_t(outZpMain));
-                    r = min(max(r, loMain), hiMain);
+                    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(sum) : "r"(v), "r"(int32_t(mult)), "l"(round));
+                    const uint32_t tq = __funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), s1);
+                    int32_t r = min(__viaddmax_s32(int32_t(tq) >> s2, outZpMain, loMain), hiMain);
                     if (RESIDUAL) {
                         const int32_t ta = fastRescale(fa, r, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
                         const int32_t sv = int32_t(int8_t(sc[q] >> (8 * e)));
@@ -361,7 +360,7 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     uint8_t *tilesA = smem;
     uint8_t *tilesB = smem + NSTAGE * kTileA;
     ColConst *colTab = reinterpret_cast<ColConst *>(smem + NSTAGE * (kTileA + kTileB));
-    PipeBarriers *bars = reinterpret_cast<PipeBarriers *>(smem + NSTAGE * (kTileA + kTileB) + BN * (sizeof(ColConst) + 4));
+    PipeBarriers *bars = reinterpret_cast<PipeBarriers *>(smem + NSTAGE * (kTileA + kTileB) + BN * sizeof(ColConst));
     // gather variants only: the table of piece offsets (at most kMaxGatherPieces entries), 16-byte aligned
     int32_t *gatherTab = reinterpret_cast<int32_t *>(
         (reinterpret_cast<uintptr_t>(bars) + sizeof(PipeBarriers) + 15) & ~uintptr_t(15));
@@ -611,7 +610,7 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
 template <int BN, int NSTAGE, int A_MODE, bool B_MN>
 int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes =
-        size_t(NSTAGE) * (BM * BK + BN * BK) + BN * (sizeof(ColConst) + 4) + sizeof(PipeBarriers) + 1024 +
+        size_t(NSTAGE) * (BM * BK + BN * BK) + BN * sizeof(ColConst) + sizeof(PipeBarriers) + 1024 +
         (A_MODE != kAGather ? 0 : (kMaxGatherPieces + kTapTabEntries) * sizeof(int32_t) + 16);
     auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_MODE, B_MN>;
     static bool configured = false;
