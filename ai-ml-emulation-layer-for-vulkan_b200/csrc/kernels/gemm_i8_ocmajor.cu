@@ -82,16 +82,14 @@ __device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, const void *s
                  : "memory");
 }
 
-// High 32 bits of v * mult + (v >= thr ? rp : rn): product and rounding of a RESCALE whose shift is at least
-// 32, where the result only depends on the high word.  The rounding constant is selected first (two selects),
-// so that the 64-bit addition rides on the multiply-add; adding it afterwards costs two instructions per
-// candidate constant.
-__device__ __forceinline__ int32_t scaleHigh(int32_t v, int32_t mult, int32_t thr, uint64_t rp, uint64_t rn) {
-    const bool nonNeg = v >= thr;
-    const uint32_t lo = nonNeg ? uint32_t(rp) : uint32_t(rn);
-    const uint32_t hi = nonNeg ? uint32_t(rp >> 32) : uint32_t(rn >> 32);
-    uint64_t sum;
-    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(sum) : "r"(v), "r"(mult), "l"((uint64_t(hi) << 32) | lo));
+// High 32 bits of v * mult + (v >= thr ? rn + bump : rn): product and rounding of a RESCALE whose shift is at
+// least 32, where the result only depends on the high word.  The two rounding constants of double rounding
+// differ by 2^31 (bump; 0 without double rounding), which fits the third input of the 64-bit addition that
+// follows the multiply, so the choice costs one compare and one select.
+__device__ __forceinline__ int32_t scaleHigh(int32_t v, int32_t mult, int32_t thr, uint64_t rn, uint32_t bump) {
+    const uint64_t prod = uint64_t(int64_t(v) * int64_t(mult));
+    const uint32_t extra = v >= thr ? bump : 0u;
+    const uint64_t sum = prod + rn + uint64_t(extra);
     return int32_t(uint32_t(sum >> 32));
 }
 
@@ -119,7 +117,8 @@ __device__ __forceinline__ int32_t finishHigh(int32_t high, int32_t s2, int32_t 
 // Constants of one epilogue thread (one output channel) and of the per-tensor output stage.
 struct EpiConsts {
     FastRescale fm, fo;
-    uint64_t rpM, rnM, rpO, rnO;
+    uint64_t rnM, rnO;      // rounding constants for inputs below the zero point
+    uint32_t bumpM, bumpO;  // what the constants for inputs at or above it add: 2^31 with double rounding, else 0
     int32_t corr0;
     int32_t outZpMain, loMain, hiMain, outZpOut, loOut, hiOut;
     bool fast; // every shift involved is at least 32: see scaleHigh
@@ -146,7 +145,7 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
         for (int j = 0; j < CH; ++j) {
             const int32_t v = int32_t(acc[g + j] + uint32_t(k.corr0));
             if (FAST) {
-                r[j] = finishHigh(scaleHigh(v, k.fm.mult, k.fm.zpIn, k.rpM, k.rnM), k.fm.s2, k.outZpMain, k.loMain, k.hiMain);
+                r[j] = finishHigh(scaleHigh(v, k.fm.mult, k.fm.zpIn, k.rnM, k.bumpM), k.fm.s2, k.outZpMain, k.loMain, k.hiMain);
             } else {
                 r[j] = fastRescale(k.fm, v, k.outZpMain, k.loMain, k.hiMain);
             }
@@ -156,7 +155,7 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
             for (int j = 0; j < CH; ++j) {
                 const int32_t sum = int32_t(uint32_t(ldsS32(lutA128 + uint32_t(r[j] * 4))) + uint32_t(ldsS32(lutB + sc[j] * 4u)));
                 if (FAST) {
-                    r[j] = finishHigh(scaleHigh(sum, k.fo.mult, k.fo.zpIn, k.rpO, k.rnO), k.fo.s2, k.outZpOut, k.loOut, k.hiOut);
+                    r[j] = finishHigh(scaleHigh(sum, k.fo.mult, k.fo.zpIn, k.rnO, k.bumpO), k.fo.s2, k.outZpOut, k.loOut, k.hiOut);
                 } else {
                     r[j] = fastRescale(k.fo, sum, k.outZpOut, k.loOut, k.hiOut);
                 }
@@ -198,11 +197,8 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     if (RESIDUAL) {
         k.fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
                                p.epi.out.doubleRound != 0);
-        k.rpO = (uint64_t(k.fo.rpHi) << 32) | k.fo.rpLo;
         k.rnO = (uint64_t(k.fo.rnHi) << 32) | k.fo.rnLo;
-        // These are the same in every thread; passing them through an opaque statement keeps them in ordinary
-        // registers, where the multiply-add can use them directly, instead of being copied in before each use.
-        asm volatile("" : "+l"(k.rpO), "+l"(k.rnO));
+        k.bumpO = uint32_t(((uint64_t(k.fo.rpHi) << 32) | k.fo.rpLo) - k.rnO);
     }
     k.outZpMain = p.epi.main.outZp, k.loMain = p.epi.main.lo, k.hiMain = p.epi.main.hi;
     k.outZpOut = p.epi.out.outZp, k.loOut = p.epi.out.lo, k.hiOut = p.epi.out.hi;
@@ -239,8 +235,8 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             const int ci = (p.epi.main.perChannel && ocValid) ? oc : 0;
             k.fm = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)), p.epi.main.inZp,
                                    p.epi.main.doubleRound != 0);
-            k.rpM = (uint64_t(k.fm.rpHi) << 32) | k.fm.rpLo;
             k.rnM = (uint64_t(k.fm.rnHi) << 32) | k.fm.rnLo;
+            k.bumpM = uint32_t(((uint64_t(k.fm.rpHi) << 32) | k.fm.rpLo) - k.rnM);
             k.corr0 = ocValid ? __ldg(corrBatch + int64_t(baseClass) * p.N + oc) : 0;
             k.fast = __all_sync(0xffffffffu, k.fm.s1 == 32) && (!RESIDUAL || k.fo.s1 == 32);
             curC0 = c0;
