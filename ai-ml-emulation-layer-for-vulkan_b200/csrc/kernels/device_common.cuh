@@ -244,13 +244,14 @@ __host__ __device__ inline FastRescale makeFastRescale(int32_t mult, int32_t shi
     return f;
 }
 
-// int32(((int64(v) - zpIn) * mult + round) >> shift), bit-identical to applyScale.
+// int32(((int64(v) - zpIn) * mult + round) >> shift), bit-identical to applyScale.  The two rounding constants
+// differ by 0 or 2^31, so the choice between them is the third input of the 64-bit addition that follows the
+// multiply (one compare and one select) rather than a select of both halves of the constant.
 __device__ __forceinline__ int32_t fastScale(int32_t v, int32_t mult, int32_t zpIn, uint32_t rpLo, uint32_t rpHi,
                                              uint32_t rnLo, uint32_t rnHi, int32_t s1, int32_t s2) {
-    const bool nonNeg = v >= zpIn;
-    const uint64_t round = (uint64_t(nonNeg ? rpHi : rnHi) << 32) | uint64_t(nonNeg ? rpLo : rnLo);
-    uint64_t sum;
-    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(sum) : "r"(v), "r"(mult), "l"(round));
+    const uint64_t rn = (uint64_t(rnHi) << 32) | uint64_t(rnLo);
+    const uint32_t bump = rpLo - rnLo; // (rp - rn) mod 2^32: 0 or 2^31
+    const uint64_t sum = uint64_t(int64_t(v) * int64_t(mult)) + rn + uint64_t(v >= zpIn ? bump : 0u);
     const uint32_t t = __funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), uint32_t(s1));
     return int32_t(t) >> s2;
 }
