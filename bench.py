@@ -117,14 +117,21 @@ class CpuReference:
     workload: the same graph at a batch small enough that one pass takes about `target_seconds`."""
 
     def __init__(self, target_seconds: float):
+        # torchrun gives every worker OMP_NUM_THREADS=1; the CPU arm is meant to use all host threads
+        self.cores = os.cpu_count() or 1
+        os.environ["OMP_NUM_THREADS"] = str(self.cores)
         from __graft_entry__ import load_package
         load_package()
         from mlel_b200.model_graphs import resnet50_graph
         from oracle import oracle
         from tests.graph_eval import evaluate
         oracle.build()
+        try:  # in case the OpenMP runtime was initialised before the variable changed
+            import ctypes
+            ctypes.CDLL("libgomp.so.1").omp_set_num_threads(self.cores)
+        except OSError:
+            pass
         self.evaluate = evaluate
-        self.cores = os.cpu_count() or 1
         g, inputs = resnet50_graph(seed=0, n=1, image=IMAGE)
         evaluate(g, inputs)  # warm-up (page-in, thread pool)
         t0 = time.perf_counter()
