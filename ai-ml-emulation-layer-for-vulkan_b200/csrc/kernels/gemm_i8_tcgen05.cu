@@ -4,20 +4,28 @@
 //
 //   D[m, n] = sum_k A[m, k] * B[n, k]         m: output pixel (or matmul row), n: output channel
 //
-//   A operand  - TMA tile loads when A is a plain row-major matrix (1x1 stride-1 convolution, MATMUL,
-//                a materialised im2col matrix);
-//              - otherwise gathered by four producer warps with 16-byte cp.async (im2col on the fly:
-//                any kernel size, stride, dilation and padding; out-of-range taps are zero-filled)
-//   B operand  - TMA tile loads of the K-major weight matrix [N][K] (OHWI weights are exactly that), or
-//                of an N-major [K][N] matrix (MATMUL's second input) with an MN-major descriptor
+//   A operand  - TMA tile loads when A is a plain row-major matrix (1x1 stride-1 convolution, MATMUL);
+//              - TMA im2col loads for a convolution window over a multiple of 16 channels: one instruction
+//                fetches one tap, 128 channels (zero-filled past the last one), of the tile's 128 windows;
+//              - otherwise gathered by four producer warps with cp.async: 16-byte pieces with bounds
+//                checks (any kernel size, stride, dilation and padding; out-of-range taps zero-filled), or
+//                4/8/16-byte pieces at tabulated offsets from a zero-padded copy of the input (channel
+//                counts that are not multiples of 16, e.g. an RGB stem)
+//   B operand  - TMA tile loads of the K-major weight matrix [N][K] (OHWI weights are exactly that; in im2col
+//                mode through a {IC, taps, OC} map that pads each tap like the A loads), or of an N-major
+//                [K][N] matrix with an MN-major descriptor
 //   schedule   - one CTA per SM walks the output tiles (n fastest, so concurrently running CTAs share
 //                their A rows in L2); 128-byte K blocks in SWIZZLE_128B shared-memory tiles form an
 //                mbarrier ring that runs on across tiles; two TMEM accumulators alternate so that the
 //                epilogue of tile i overlaps the main loop of tile i+1
-//   warps      - 0-7 epilogue (two per TMEM lane quarter, each half of the columns), 8 TMA producer,
-//                9 MMA issuer and TMEM owner, 10-13 A gather (implicit-GEMM variants only)
+//   warps      - 0-15 epilogue (four per TMEM lane quarter, each a quarter of the columns), 16 TMA
+//                producer, 17 MMA issuer and TMEM owner, 18-21 A gather (gathered variants only)
 //   epilogue   - tcgen05.ld of the int32 accumulator, zero-point/bias correction, then either a raw
-//                int32 store or RESCALE (+CLAMP, + residual RESCALE/ADD/RESCALE) to int8
+//                int32 store or RESCALE (+CLAMP, + residual RESCALE/ADD/RESCALE) to int8, with the
+//                per-column constants read from shared memory
+//
+// Fused int8 convolutions with more than 64 output channels run on the channel-major companion kernel
+// (gemm_i8_ocmajor.cu) instead, whose epilogue keeps the per-channel constants in registers.
 //
 // Exactness.  The tensor core sums raw products A*B in int32 (no overflow is possible for K <= 65536).
 // The reference computes sum over in-range taps of (x - zx) * w  (conv2d.comp:59-96).  With zero-filled
@@ -81,8 +89,8 @@ __device__ __forceinline__ uint32_t pack4(int32_t e0, int32_t e1, int32_t e2, in
     return __byte_perm(lo, hi, 0x5410);
 }
 
-// The epilogue of the persistent kernel (warps 0-7).  Each warp owns 32 TMEM lanes (tile rows) and half of
-// the tile's columns, which it walks in 16-column steps: one tcgen05.ld, 16 RESCALEs, one 16-byte store.
+// The epilogue of the persistent kernel (warps 0-15).  Each warp owns 32 TMEM lanes (tile rows) and a quarter
+// of the tile's columns, which it walks in 16-column steps: one tcgen05.ld, 16 RESCALEs, one 16-byte store.
 template <int BN, int NSTAGE, bool RESIDUAL>
 __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers *bars, ColConst *colTab,
                                              uint32_t tmemBase, int warp, int lane, int64_t numTiles, int mTiles,
@@ -592,7 +600,7 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
             }
         }
     } else {
-        // ---------------- epilogue: warps 0-7 ----------------
+        // ---------------- epilogue: warps 0-15 ----------------
         epilogueWarps<BN, NSTAGE>(p, bars, colTab, tmemBase, warp, lane, numTiles, mTiles, nTiles);
     }
 
