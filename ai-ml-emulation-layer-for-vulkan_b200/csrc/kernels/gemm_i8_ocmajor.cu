@@ -367,6 +367,8 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     OcBarriers *bars = reinterpret_cast<OcBarriers *>(tapTab + kTapTabEntries);
 
     constexpr bool X_TMA = X_MODE != kXGather;
+    constexpr uint32_t kTmemCols = 2 * BNP <= 256 ? 256u : 512u; // two accumulators; allocations are powers of two
+    constexpr int kXBoxRows = BNP % 128 == 0 ? 128 : 64;         // rows of one tiled load of the pixel operand
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int numKb = X_MODE == kXIm2col ? p.KH * p.KW * p.kbPerTap : (p.K + BK - 1) / BK;
@@ -397,7 +399,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     }
     if (warp == kOcMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(&bars->tmemBase)),
-                     "r"(uint32_t(2 * BNP))
+                     "r"(kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -451,11 +453,11 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                         tmaLoad3d(&tmapW, tilesW + s * kTileW, &bars->full[s], kb * BK, tc.c0, 0);
                     }
                     if (X_MODE == kXTiled) {
-                        // boxes hold at most 256 rows of 128 bytes: one copy per 128 pixels
+                        // one copy per kXBoxRows pixels (the map's box)
 #pragma unroll
-                        for (int h = 0; h < BNP / 128; ++h) {
-                            tmaLoad3d(&tmapX, tilesX + s * kTileX + h * 128 * BK, &bars->full[s], kb * BK, tc.m0 + h * 128,
-                                      tc.batch);
+                        for (int h = 0; h < BNP / kXBoxRows; ++h) {
+                            tmaLoad3d(&tmapX, tilesX + s * kTileX + h * kXBoxRows * BK, &bars->full[s], kb * BK,
+                                      tc.m0 + h * kXBoxRows, tc.batch);
                         }
                     } else if (X_MODE == kXIm2col) {
                         tmaLoadIm2col4d(&tmapX, tilesX + s * kTileX, &bars->full[s], cb, w0, h0, n0, uint16_t(kx * p.dilX),
@@ -559,7 +561,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     __syncthreads();
     if (warp == kOcMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(uint32_t(2 * BNP))
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmemBase), "r"(kTmemCols)
                      : "memory");
     }
 }
@@ -635,19 +637,26 @@ bool gemmI8OcMajorApplies(const GemmI8Problem &q) {
 int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
     GemmI8Params p = q.params;
     p.batches = q.batches;
-    // 256-pixel tiles halve the operand traffic per multiply-accumulate; 128-pixel tiles fill the last wave
-    // better on small layers.  Pick by the number of waves times the work of one tile.
+    // Wider pixel tiles move less operand data per multiply-accumulate; narrower ones fill the last wave of CTAs
+    // better.  Pick the width (128, 192 or 256 pixels) with the least waves x work per tile; ties go to the wider.
     const int64_t cTiles = (p.N + kOcTile - 1) / kOcTile;
-    const int64_t t256 = int64_t((p.M + 255) / 256) * cTiles * q.batches;
-    const int64_t t128 = int64_t((p.M + 127) / 128) * cTiles * q.batches;
     const int64_t sms = smCount();
-    const bool wide = ((t256 + sms - 1) / sms) * 2 <= (t128 + sms - 1) / sms;
+    int width = 256;
+    int64_t best = -1;
+    for (const int w : {256, 192, 128}) {
+        const int64_t tiles = int64_t((p.M + w - 1) / w) * cTiles * q.batches;
+        const int64_t cost = ((tiles + sms - 1) / sms) * w;
+        if (best < 0 || cost < best) {
+            best = cost;
+            width = w;
+        }
+    }
     OcMaps maps{};
-    const uint32_t boxPixels = wide ? 256u : 128u;
+    const uint32_t boxPixels = uint32_t(width);
     int xMode = kXGather;
     if (q.aMatrix != nullptr) {
         if (!makeMap(&maps.x, q.aMatrix, uint64_t(p.K), uint64_t(p.M), uint64_t(q.batches), uint64_t(q.aRowBytes),
-                     uint64_t(q.aBatchBytes), BK, 128)) {
+                     uint64_t(q.aBatchBytes), BK, width % 128 == 0 ? 128 : 64)) {
             return MLEL_ERROR_DEVICE;
         }
         xMode = kXTiled;
@@ -672,7 +681,10 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
         !makeMap(&maps.c, p.epi.shortcut, uint64_t(p.N), uint64_t(p.M), 1, uint64_t(p.ldOut), plane, kOcTile, boxPixels, false)) {
         return MLEL_ERROR_DEVICE;
     }
-    return wide ? launchOcMajorShape<256, 3>(maps, p, xMode, s) : launchOcMajorShape<128, 5>(maps, p, xMode, s);
+    if (width == 256) {
+        return launchOcMajorShape<256, 3>(maps, p, xMode, s);
+    }
+    return width == 192 ? launchOcMajorShape<192, 3>(maps, p, xMode, s) : launchOcMajorShape<128, 5>(maps, p, xMode, s);
 }
 
 int ocMajorErrorWord() { return tc::readErrorWord(); }
