@@ -66,11 +66,21 @@ struct __align__(8) PipeBarriers {
 struct __align__(16) ColConst {
     int32_t mult;
     int32_t corr0;       // correction of the most common border class for this column
-    uint32_t rpLo, rpHi; // rounding constant for v >= zpIn (input zero point folded in)
-    uint32_t rnLo, rnHi; // rounding constant for v <  zpIn
-    int32_t s1, s2;      // min(shift, 32), max(shift - 32, 0)
+    uint32_t rnLo, rnHi; // rounding constant for v < zpIn (input zero point folded in)
+    int32_t s2;          // max(shift - 32, 0)
+    uint32_t bump;       // what the constant for v >= zpIn adds: 2^31 with double rounding and shift > 31, else 0
+    int32_t s1;          // min(shift, 32)
+    int32_t pad;
 };
 
+__device__ __forceinline__ void ldsV2(uint32_t addr, uint32_t &a, uint32_t &b) {
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr));
+}
+__device__ __forceinline__ int32_t ldsS32(uint32_t addr) {
+    int32_t v;
+    asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void ldsV4(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
 }
@@ -109,6 +119,8 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
     }
     const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp;
     const uint32_t tabAddr = smemAddr(colTab);
+    volatile uint32_t *fastFlag = &bars->pad; // 1: every column of the table has a shift of at least 32
+    bool fast = false;
     const int32_t loMain = p.epi.main.lo, hiMain = p.epi.main.hi;
     uint32_t tileCount = 0;
     int tabN0 = -1, tabBatch = -1; // what the shared constants table was built for
@@ -124,17 +136,26 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
         // of the most common border class.
         if (n0 != tabN0 || (p.batchedCorr && batch != tabBatch)) {
             epilogueSync(); // everyone is done with the previous table
+            if (threadIdx.x == 0) {
+                *fastFlag = 1;
+            }
+            epilogueSync();
             if (threadIdx.x < BN) {
                 const int col = n0 + int(threadIdx.x);
                 const int ci = (p.epi.main.perChannel && col < p.N) ? col : 0;
                 const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
                                                       zpMain, p.epi.main.doubleRound != 0);
                 ColConst c;
-                c.mult = f.mult, c.rpLo = f.rpLo, c.rpHi = f.rpHi, c.rnLo = f.rnLo, c.rnHi = f.rnHi, c.s1 = f.s1, c.s2 = f.s2;
+                c.mult = f.mult, c.rnLo = f.rnLo, c.rnHi = f.rnHi, c.s1 = f.s1, c.s2 = f.s2, c.pad = 0;
+                c.bump = f.rpLo - f.rnLo; // (rp - rn) mod 2^32: 0 or 2^31
+                if (f.s1 != 32) {
+                    *fastFlag = 0; // a shift below 32 in this tile: the low word of the product matters
+                }
                 c.corr0 = col < p.N ? __ldg(corrBatch + int64_t(p.baseClass) * p.N + col) : 0;
                 colTab[threadIdx.x] = c;
             }
             epilogueSync();
+            fast = *fastFlag != 0;
             tabN0 = n0;
             tabBatch = batch;
         }
@@ -204,17 +225,21 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = 4 * q + e;
-                    uint32_t mult, corr0, rpLo, rpHi, rnLo, rnHi, s1, s2;
-                    ldsV4(tabAddr + uint32_t(cl + j) * 32u, mult, corr0, rpLo, rpHi);
-                    ldsV4(tabAddr + uint32_t(cl + j) * 32u + 16u, rnLo, rnHi, s1, s2);
+                    uint32_t mult, corr0, rnLo, rnHi, s2, bump;
+                    ldsV4(tabAddr + uint32_t(cl + j) * 32u, mult, corr0, rnLo, rnHi);
+                    ldsV2(tabAddr + uint32_t(cl + j) * 32u + 16u, s2, bump);
                     const int32_t v = int32_t(acc[j] + corr0);
-                    // the rounding constant is selected first, so that the 64-bit addition rides on the multiply-add
-                    const bool nonNeg = v >= zpMain;
-                    const uint64_t round = (uint64_t(nonNeg ? rpHi : rnHi) << 32) | uint64_t(nonNeg ? rpLo : rnLo);
-                    uint64_t sum;
-                    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(sum) : "r"(v), "r"(int32_t(mult)), "l"(round));
-                    const uint32_t tq = __funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), s1);
-                    int32_t r = min(__viaddmax_s32(int32_t(tq) >> s2, outZpMain, loMain), hiMain);
+                    // the double-rounding choice is the third input of the 64-bit addition after the multiply
+                    const uint64_t sum = uint64_t(int64_t(v) * int64_t(int32_t(mult))) + ((uint64_t(rnHi) << 32) | rnLo) +
+                                         uint64_t(v >= zpMain ? bump : 0u);
+                    int32_t q32;
+                    if (fast) {
+                        q32 = int32_t(uint32_t(sum >> 32)); // shifts of 32 and more only see the high word
+                    } else {
+                        const uint32_t s1 = uint32_t(ldsS32(tabAddr + uint32_t(cl + j) * 32u + 24u));
+                        q32 = int32_t(__funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), s1));
+                    }
+                    int32_t r = min(__viaddmax_s32(q32 >> s2, outZpMain, loMain), hiMain);
                     if (RESIDUAL) {
                         const int32_t ta = fastRescale(fa, r, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
                         const int32_t sv = int32_t(int8_t(sc[q] >> (8 * e)));
