@@ -684,7 +684,7 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
     if (width == 256) {
         return launchOcMajorShape<256, 3>(maps, p, xMode, s);
     }
-    return width == 192 ? launchOcMajorShape<192, 3>(maps, p, xMode, s) : launchOcMajorShape<128, 5>(maps, p, xMode, s);
+    return width == 192 ? launchOcMajorShape<192, 4>(maps, p, xMode, s) : launchOcMajorShape<128, 5>(maps, p, xMode, s);
 }
 
 int ocMajorErrorWord() { return tc::readErrorWord(); }
