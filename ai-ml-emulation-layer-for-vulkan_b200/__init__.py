@@ -22,6 +22,9 @@ LIB_PATH = os.path.join(_HERE, "libmlel_b200.so")
 BOOL, I8, I16, I32, I64, U8, U16, U32, F16, BF16, F32 = range(11)
 MAX_RANK = 6
 PIPELINE_NO_FUSION = 1
+INCOMPLETE = 5
+PROPERTY_CREATION_LOG = 0
+PROPERTY_PROFILING = 0x7FFFFFFE
 
 NP_TO_DTYPE = {
     np.dtype(np.bool_): BOOL,
@@ -76,6 +79,11 @@ class UnseenAllocation(ctypes.Structure):
     _fields_ = [("id", ctypes.c_uint64), ("size", ctypes.c_uint64)]
 
 
+class PlannedTensor(ctypes.Structure):
+    _fields_ = [("tensor", ctypes.c_int32), ("seen", ctypes.c_uint32), ("offset", ctypes.c_uint64),
+                ("size", ctypes.c_uint64), ("first", ctypes.c_uint32), ("last", ctypes.c_uint32)]
+
+
 _lib = None
 
 
@@ -92,6 +100,7 @@ def lib() -> ctypes.CDLL:
         _lib.mlel_tosa_op_name.restype = ctypes.c_char_p
         _lib.mlel_pipeline_op_name.restype = ctypes.c_char_p
         _lib.mlel_pipeline_exec_name.restype = ctypes.c_char_p
+        _lib.mlel_session_planner_name.restype = ctypes.c_char_p
         _lib.mlel_pipeline_destroy.restype = None
         _lib.mlel_session_destroy.restype = None
     return _lib
@@ -181,6 +190,33 @@ class Pipeline:
         if getattr(self, "_h", None) and lib is not None:
             lib().mlel_pipeline_destroy(self._h)
             self._h = None
+
+    # ---- properties (vkGetDataGraphPipelineAvailablePropertiesARM / vkGetDataGraphPipelinePropertiesARM) ----
+    def available_properties(self) -> list[int]:
+        n = ctypes.c_uint32()
+        check(lib().mlel_pipeline_available_properties(self._h, ctypes.byref(n), None))
+        ids = (ctypes.c_uint32 * max(1, n.value))()
+        check(lib().mlel_pipeline_available_properties(self._h, ctypes.byref(n), ids))
+        return [ids[i] for i in range(n.value)]
+
+    def text_property(self, prop: int) -> str:
+        """Two-call query of a text property; the profiling property waits for the recorded dispatches."""
+        size, is_text = ctypes.c_size_t(), ctypes.c_int()
+        check(lib().mlel_pipeline_get_property(self._h, ctypes.c_uint32(prop), None, ctypes.byref(size),
+                                               ctypes.byref(is_text)))
+        buf = ctypes.create_string_buffer(size.value)
+        check(lib().mlel_pipeline_get_property(self._h, ctypes.c_uint32(prop), buf, ctypes.byref(size),
+                                               ctypes.byref(is_text)))
+        assert is_text.value == 1
+        return buf.raw[:size.value - 1].decode()
+
+    def profile(self) -> dict:
+        """The profiling document (graph/graph_profiler.cpp:563-620) as a dictionary."""
+        import json
+        return json.loads(self.text_property(PROPERTY_PROFILING))
+
+    def clear_profile(self) -> None:
+        check(lib().mlel_pipeline_clear_profile(self._h))
 
     # ---- tensors ----
     def bind_external(self, set_: int, binding: int, dtype: int, dims, array_index: int = 0, strides=None) -> int:
@@ -343,6 +379,17 @@ class Session:
         size, align = ctypes.c_uint64(), ctypes.c_uint64()
         check(lib().mlel_session_memory_requirements(self._h, ctypes.byref(size), ctypes.byref(align)))
         return size.value, align.value
+
+    def planner_name(self) -> str:
+        return lib().mlel_session_planner_name(self._h).decode()
+
+    def plan(self) -> list[PlannedTensor]:
+        """Placement and live range of every session tensor, in session-tensor order."""
+        n = ctypes.c_uint32()
+        check(lib().mlel_session_plan(self._h, ctypes.byref(n), None))
+        out = (PlannedTensor * max(1, n.value))()
+        check(lib().mlel_session_plan(self._h, ctypes.byref(n), out))
+        return [out[i] for i in range(n.value)]
 
     def tensor_offset(self, tensor: int) -> int:
         off = ctypes.c_uint64()

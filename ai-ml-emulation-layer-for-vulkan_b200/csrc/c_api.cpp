@@ -1,8 +1,10 @@
 // extern "C" boundary (declared in include/mlel_b200.h).  Exceptions of the C++ graph layer are
 // turned into status codes here; the reference lets std::runtime_error escape its Vulkan entry
 // points (graph/graph_layer.cpp:815-964), which a C ABI must not do.
+#include <algorithm>
 #include <cstring>
 #include <memory>
+#include <string>
 #include <unordered_map>
 
 #include "graph_pipeline.hpp"
@@ -505,6 +507,91 @@ int mlel_session_dispatch_graph(mlel_session *s, void *cuda_stream) {
 int mlel_session_dispatch_profiled(mlel_session *s, void *cuda_stream, float *ms_out, uint32_t capacity) {
     return guarded(
         [&] { return s->impl.dispatchProfiled(static_cast<cudaStream_t>(cuda_stream), ms_out, capacity); });
+}
+
+const char *mlel_session_planner_name(const mlel_session *s) { return plannerName(s->impl.planner()); }
+
+int mlel_session_plan(const mlel_session *s, uint32_t *count, mlel_planned_tensor *out) {
+    return guarded([&]() -> int {
+        const auto &planned = s->impl.plannedTensors();
+        if (out == nullptr) {
+            *count = uint32_t(planned.size());
+            return MLEL_SUCCESS;
+        }
+        const size_t n = std::min<size_t>(*count, planned.size());
+        for (size_t k = 0; k < n; ++k) {
+            const auto &p = planned[k];
+            out[k] = {p.tensor, p.seen ? 1u : 0u, p.offset, p.size, p.first, p.last};
+        }
+        const bool cut = *count < planned.size();
+        *count = uint32_t(n);
+        return int(cut ? MLEL_INCOMPLETE : MLEL_SUCCESS);
+    });
+}
+
+/* ---- pipeline properties ---- */
+
+namespace {
+constexpr const char *kCreationLog = "Graph pipeline created"; // graph/graph_layer.cpp:51
+
+// writeTextProperty, graph/graph_layer.cpp:1427-1448
+int writeTextProperty(const std::string &text, void *data, size_t *dataSize, int *isText) {
+    if (isText != nullptr) {
+        *isText = 1;
+    }
+    const size_t required = text.size() + 1;
+    if (data == nullptr) {
+        *dataSize = required;
+        return MLEL_SUCCESS;
+    }
+    const size_t n = std::min(*dataSize, required);
+    std::memcpy(data, text.c_str(), n); // c_str() holds the terminating zero as its last byte
+    *dataSize = n;
+    return n < required ? MLEL_INCOMPLETE : MLEL_SUCCESS;
+}
+} // namespace
+
+int mlel_pipeline_available_properties(const mlel_pipeline *p, uint32_t *count, uint32_t *properties) {
+    return guarded([&]() -> int {
+        std::vector<uint32_t> all{MLEL_PIPELINE_PROPERTY_CREATION_LOG};
+        if (p->impl->profiler() != nullptr) {
+            all.push_back(MLEL_PIPELINE_PROPERTY_PROFILING);
+        }
+        if (properties == nullptr) {
+            *count = uint32_t(all.size());
+            return MLEL_SUCCESS;
+        }
+        const size_t n = std::min<size_t>(*count, all.size());
+        std::copy(all.begin(), all.begin() + long(n), properties);
+        const bool cut = *count < all.size();
+        *count = uint32_t(n);
+        return int(cut ? MLEL_INCOMPLETE : MLEL_SUCCESS);
+    });
+}
+
+int mlel_pipeline_get_property(mlel_pipeline *p, uint32_t property, void *data, size_t *data_size, int *is_text) {
+    return guarded([&]() -> int {
+        if (data_size == nullptr) {
+            throw std::runtime_error("get_property: data_size must not be null");
+        }
+        if (property == MLEL_PIPELINE_PROPERTY_CREATION_LOG) {
+            return writeTextProperty(kCreationLog, data, data_size, is_text);
+        }
+        if (property == MLEL_PIPELINE_PROPERTY_PROFILING && p->impl->profiler() != nullptr) {
+            return writeTextProperty(p->impl->profiler()->makeJson(), data, data_size, is_text);
+        }
+        setLastError("unknown pipeline property");
+        return MLEL_ERROR_UNKNOWN;
+    });
+}
+
+int mlel_pipeline_clear_profile(mlel_pipeline *p) {
+    return guarded([&] {
+        if (p->impl->profiler() != nullptr) {
+            p->impl->profiler()->clear();
+        }
+        return MLEL_SUCCESS;
+    });
 }
 
 int mlel_session_launch_count(const mlel_session *s) {

@@ -1046,7 +1046,14 @@ char *GraphPipeline::constantBase() {
     return constSlab_;
 }
 
+GraphPipeline::GraphPipeline(uint32_t flags) : flags_(flags) {
+    if (GraphProfiler::isEnabled()) {
+        profiler_ = std::make_unique<GraphProfiler>();
+    }
+}
+
 GraphPipeline::~GraphPipeline() {
+    profiler_.reset(); // its events go before the constants
     if (constSlab_ != nullptr) {
         cudaFree(constSlab_);
     }

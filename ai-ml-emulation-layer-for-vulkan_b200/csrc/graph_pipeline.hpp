@@ -13,6 +13,7 @@
 #include <tuple>
 #include <vector>
 
+#include "graph_profiler.hpp"
 #include "ops.hpp"
 
 namespace mlel {
@@ -47,7 +48,13 @@ class UnsupportedError : public std::runtime_error {
 
 class GraphPipeline {
   public:
-    explicit GraphPipeline(uint32_t flags) : flags_(flags) {}
+    explicit GraphPipeline(uint32_t flags);
+    GraphPipeline(const GraphPipeline &) = delete;
+    GraphPipeline &operator=(const GraphPipeline &) = delete;
+
+    // Present when VMEL_GRAPH_PROFILING was truthy at creation (graph/graph_layer.cpp:318-322); every
+    // dispatch of a session of this pipeline is then timed operator by operator.
+    GraphProfiler *profiler() { return profiler_.get(); }
 
     // --- tensors (names follow the reference) ---
     int32_t makeConstTensor(uint32_t id, const mlel_tensor_desc &desc, const void *data);
@@ -129,6 +136,7 @@ class GraphPipeline {
     int32_t addScratchTensor(int32_t dtype, const std::vector<int64_t> &dims);
 
     uint32_t flags_;
+    std::unique_ptr<GraphProfiler> profiler_;
     bool finalized_{false};
     std::vector<std::unique_ptr<TensorDescriptor>> tensors_;
     std::vector<int32_t> sessionTensors_;

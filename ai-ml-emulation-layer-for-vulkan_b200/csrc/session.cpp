@@ -1,7 +1,9 @@
 #include "session.hpp"
 
 #include <algorithm>
+#include <cstdlib>
 #include <set>
+#include <string>
 
 namespace mlel {
 
@@ -63,24 +65,143 @@ void Session::plan() {
         touch(t, index);
     }
 
-    std::vector<LiveInterval> intervals;
-    std::vector<UnseenAllocation> unseen;
+    // One record per session tensor that needs storage, in session-tensor order.
+    planned_.clear();
     for (size_t order = 0; order < sessionTensors.size(); ++order) {
         const int32_t t = sessionTensors[order];
         const uint64_t size = roundUp(pipeline_->tensor(t).sizeBytes(), kSessionAlignment);
         const auto it = ranges.find(t);
         if (it != ranges.end()) {
-            intervals.push_back({uint64_t(order), it->second.first, it->second.second, size, uint64_t(order)});
+            planned_.push_back({t, 0, size, it->second.first, it->second.second, true});
         } else if (pipeline_->flags() & MLEL_PIPELINE_NO_FUSION) {
-            unseen.push_back({uint64_t(order), size});
+            planned_.push_back({t, 0, size, 0, 0, false});
         }
         // With fusion on, a tensor nothing touches was elided and needs no storage.
     }
+    planner_ = plannerFromEnvironment();
+    switch (planner_) {
+    case PlannerKind::Linear:
+        planLinear();
+        break;
+    case PlannerKind::BestFit:
+        planBestFit();
+        break;
+    case PlannerKind::Interval:
+        planInterval();
+        break;
+    }
+    offsets_.clear();
+    for (const auto &p : planned_) {
+        offsets_[p.tensor] = p.offset;
+    }
+}
+
+// The session's planner is chosen by VMEL_MEMORY_PLANNER exactly as the reference chooses it
+// (graph/graph_layer.cpp:282-297): "Linear", "BestFit", anything else (or unset) = interval.
+PlannerKind plannerFromEnvironment() {
+    const char *name = std::getenv("VMEL_MEMORY_PLANNER");
+    if (name != nullptr && std::string(name) == "Linear") {
+        return PlannerKind::Linear;
+    }
+    if (name != nullptr && std::string(name) == "BestFit") {
+        return PlannerKind::BestFit;
+    }
+    return PlannerKind::Interval;
+}
+
+const char *plannerName(PlannerKind kind) {
+    switch (kind) {
+    case PlannerKind::Linear:
+        return "Linear";
+    case PlannerKind::BestFit:
+        return "BestFit";
+    case PlannerKind::Interval:
+        break;
+    }
+    return "Interval";
+}
+
+void Session::planInterval() {
+    std::vector<LiveInterval> intervals;
+    std::vector<UnseenAllocation> unseen;
+    for (size_t k = 0; k < planned_.size(); ++k) {
+        const auto &p = planned_[k];
+        if (p.seen) {
+            intervals.push_back({uint64_t(k), p.first, p.last, p.size, uint64_t(k)});
+        } else {
+            unseen.push_back({uint64_t(k), p.size});
+        }
+    }
     const AllocationPlan plan = allocateIntervals(std::move(intervals), unseen, kSessionAlignment);
     memorySize_ = plan.memorySize;
-    for (const auto &[order, offset] : plan.offsets) {
-        offsets_[sessionTensors[size_t(order)]] = offset;
+    for (const auto &[k, offset] : plan.offsets) {
+        planned_[size_t(k)].offset = offset;
     }
+}
+
+// Every tensor gets storage of its own, one after the other (LinearMemoryPlanner,
+// graph/memory_planner.cpp:52-98).  Sizes are already multiples of the alignment.
+void Session::planLinear() {
+    uint64_t offset = 0;
+    for (auto &p : planned_) {
+        p.offset = offset;
+        offset += p.size;
+    }
+    memorySize_ = offset;
+}
+
+// Best fit (BestFitMemoryPlanner, graph/memory_planner.cpp:239-263, 284-310, 352-381): tensors are
+// taken largest first; each looks, among the already placed tensors that are at least as large and
+// that it may share memory with, for the smallest one whose slot holds only tensors it may share
+// with, and moves in at that slot's address; if there is none it opens a new slot at the end.
+// Two tensors may share memory when their live ranges over the launched operator list do not
+// intersect -- the relation the reference derives by passing tensor references along the graph's
+// edges (memory_planner.cpp:154-237) stated on the linear execution order that a stream gives.
+// A tensor no operator touches never shares.
+void Session::planBestFit() {
+    std::vector<size_t> order(planned_.size());
+    for (size_t k = 0; k < order.size(); ++k) {
+        order[k] = k;
+    }
+    std::stable_sort(order.begin(), order.end(),
+                     [&](size_t a, size_t b) { return planned_[a].size > planned_[b].size; });
+    const auto mayShare = [&](size_t a, size_t b) {
+        const auto &x = planned_[a];
+        const auto &y = planned_[b];
+        return x.seen && y.seen && (x.last < y.first || y.last < x.first);
+    };
+    std::vector<int> slotOf(planned_.size(), -1);
+    std::vector<std::vector<size_t>> slots; // occupants of each slot; all share the slot's address
+    std::vector<size_t> placed;             // tensors placed so far, smallest first (stable)
+    uint64_t end = 0;
+    for (const size_t k : order) {
+        int chosen = -1;
+        for (const size_t alt : placed) {
+            if (planned_[alt].size < planned_[k].size || !mayShare(k, alt)) {
+                continue;
+            }
+            const auto &occupants = slots[size_t(slotOf[alt])];
+            if (std::all_of(occupants.begin(), occupants.end(), [&](size_t o) { return mayShare(k, o); })) {
+                chosen = slotOf[alt];
+                planned_[k].offset = planned_[alt].offset;
+                break;
+            }
+        }
+        if (chosen < 0) {
+            chosen = int(slots.size());
+            slots.emplace_back();
+            planned_[k].offset = end;
+            end += planned_[k].size;
+        }
+        slotOf[k] = chosen;
+        slots[size_t(chosen)].push_back(k);
+        // keep `placed` sorted by size ascending; among equal sizes earlier placements come first
+        const auto pos = std::upper_bound(placed.begin(), placed.end(), k, [&](size_t a, size_t b) {
+            return planned_[a].size < planned_[b].size;
+        });
+        placed.insert(pos, k);
+    }
+    memorySize_ = end;
 }
 
 bool Session::tensorOffset(int32_t tensor, uint64_t *offset) const {
@@ -185,7 +306,22 @@ int Session::dispatch(cudaStream_t stream) {
     // Operators run in creation order on one stream: the stream order is the full
     // write-to-read barrier the reference records between consecutive dispatches
     // (graph/compute_graph_op.cpp:251-299).
-    for (const auto &op : pipeline_->getExecList()) {
+    const auto &exec = pipeline_->getExecList();
+    GraphProfiler *profiler = pipeline_->profiler();
+    if (profiler != nullptr) {
+        // The reference wraps every operator's dispatch in a pair of timestamp writes when profiling is on
+        // (graph/graph_profiler.cpp:157-191); one event after each kernel closes it and opens the next.
+        const size_t token = profiler->beginDispatch(stream, exec.size());
+        for (size_t k = 0; k < exec.size(); ++k) {
+            const int r = launchOp(exec[k], views_.data(), stream);
+            if (r != MLEL_SUCCESS) {
+                return r;
+            }
+            profiler->afterOperator(token, uint32_t(k), exec[k].name, stream);
+        }
+        return MLEL_SUCCESS;
+    }
+    for (const auto &op : exec) {
         const int r = launchOp(op, views_.data(), stream);
         if (r != MLEL_SUCCESS) {
             return r;
@@ -228,6 +364,9 @@ int Session::dispatchProfiled(cudaStream_t stream, float *msOut, uint32_t capaci
 }
 
 int Session::dispatchGraph(cudaStream_t stream) {
+    if (pipeline_->profiler() != nullptr) {
+        return dispatch(stream); // timestamps go between the kernels, which a replayed graph has no place for
+    }
     int rc = resolve();
     if (rc != MLEL_SUCCESS) {
         return rc;

@@ -15,6 +15,22 @@
 
 namespace mlel {
 
+// The three session memory planners of the reference (graph/graph_layer.cpp:282-297).
+enum class PlannerKind { Interval, Linear, BestFit };
+PlannerKind plannerFromEnvironment(); // reads VMEL_MEMORY_PLANNER
+const char *plannerName(PlannerKind kind);
+
+// Placement of one session tensor: where it lies in the session memory and over which launches
+// (index 0 = graph inputs, 1..n = launched operators, n + 1 = graph outputs) it is alive.
+struct PlannedTensor {
+    int32_t tensor;
+    uint64_t offset;
+    uint64_t size;
+    uint32_t first;
+    uint32_t last;
+    bool seen; // false: no launched operator touches it (only kept when fusion is off)
+};
+
 class Session {
   public:
     explicit Session(GraphPipeline *pipeline);
@@ -23,6 +39,8 @@ class Session {
     uint64_t memorySize() const { return memorySize_; }
     uint64_t alignment() const { return kSessionAlignment; }
     bool tensorOffset(int32_t tensor, uint64_t *offset) const;
+    PlannerKind planner() const { return planner_; }
+    const std::vector<PlannedTensor> &plannedTensors() const { return planned_; }
 
     void bindMemory(void *memory, uint64_t offset);
     void setExternal(uint32_t set, uint32_t binding, uint32_t arrayIndex, void *devicePtr);
@@ -36,10 +54,15 @@ class Session {
 
   private:
     void plan();
+    void planInterval();
+    void planLinear();
+    void planBestFit();
     int resolve(); // fills views_ with device addresses; fails if something is unbound
 
     GraphPipeline *pipeline_;
     uint64_t memorySize_{0};
+    PlannerKind planner_{PlannerKind::Interval};
+    std::vector<PlannedTensor> planned_;
     std::map<int32_t, uint64_t> offsets_; // session tensor id -> offset
     char *memory_{nullptr};
     std::map<std::tuple<uint32_t, uint32_t, uint32_t>, char *> external_;

@@ -12,22 +12,29 @@ from . import NP_TO_DTYPE, Pipeline, Session
 from .graph_builder import GraphBuilder
 
 
+def make_pipeline(graph: GraphBuilder, flags: int = 0):
+    """Registers the graph's resources and constants and lowers its SPIR-V assembly; needs no device.
+    Returns ``(pipeline, input_keys, output_keys)`` with keys ``(set, binding, value)``."""
+    pipeline = Pipeline(flags)
+    in_keys, out_keys = [], []
+    for v in graph.inputs:
+        s, b = v.binding
+        pipeline.bind_external(s, b, NP_TO_DTYPE[v.dtype], v.shape)
+        in_keys.append((s, b, v))
+    for v, s, b in graph.outputs:
+        pipeline.bind_external(s, b, NP_TO_DTYPE[v.dtype], v.shape)
+        out_keys.append((s, b, v))
+    for cid, data in graph.constants.items():
+        pipeline.add_constant(cid, data)
+    pipeline.lower_spvasm(graph.spvasm())
+    return pipeline, in_keys, out_keys
+
+
 class GraphRunner:
     def __init__(self, graph: GraphBuilder, flags: int = 0, device: str | torch.device = "cuda"):
         self.graph = graph
         self.device = torch.device(device)
-        self.pipeline = Pipeline(flags)
-        self._in_keys, self._out_keys = [], []
-        for v in graph.inputs:
-            s, b = v.binding
-            self.pipeline.bind_external(s, b, NP_TO_DTYPE[v.dtype], v.shape)
-            self._in_keys.append((s, b, v))
-        for v, s, b in graph.outputs:
-            self.pipeline.bind_external(s, b, NP_TO_DTYPE[v.dtype], v.shape)
-            self._out_keys.append((s, b, v))
-        for cid, data in graph.constants.items():
-            self.pipeline.add_constant(cid, data)
-        self.pipeline.lower_spvasm(graph.spvasm())
+        self.pipeline, self._in_keys, self._out_keys = make_pipeline(graph, flags)
         self.session = Session(self.pipeline)
         size, align = self.session.memory_requirements()
         self.memory_size = size

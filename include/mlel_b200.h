@@ -221,6 +221,42 @@ int mlel_session_dispatch_graph(mlel_session *s, void *cuda_stream);
  * Synchronises the stream; ms_out[i] receives the device time of kernel i (see
  * mlel_pipeline_exec_name); `capacity` must be at least mlel_session_launch_count(). */
 int mlel_session_dispatch_profiled(mlel_session *s, void *cuda_stream, float *ms_out, uint32_t capacity);
+/* ---- session memory planners: graph/graph_layer.cpp:282-297, graph/memory_planner.cpp ----
+ * The environment variable VMEL_MEMORY_PLANNER, read when a session is created, selects "Linear"
+ * (every tensor its own storage, memory_planner.cpp:52-98), "BestFit" (largest first into the
+ * best-fitting reusable slot, memory_planner.cpp:239-381) or, by default, the interval planner. */
+typedef struct mlel_planned_tensor {
+    mlel_tensor_id tensor;
+    uint32_t seen;   /* 0: no launched kernel touches it (kept only when fusion is off) */
+    uint64_t offset; /* inside the bound session memory */
+    uint64_t size;   /* rounded up to the session alignment */
+    uint32_t first;  /* live range over {0 = graph inputs, 1..n = launched kernels, n + 1 = outputs} */
+    uint32_t last;
+} mlel_planned_tensor;
+/* "Interval", "Linear" or "BestFit": the planner this session was planned with. */
+const char *mlel_session_planner_name(const mlel_session *s);
+/* Two-call enumeration: with `out` NULL *count receives the number of planned tensors; otherwise up to
+ * *count records are written, *count receives the number written, MLEL_INCOMPLETE if there were more. */
+int mlel_session_plan(const mlel_session *s, uint32_t *count, mlel_planned_tensor *out);
+
+/* ---- pipeline properties: vkGetDataGraphPipelineAvailablePropertiesARM and
+ * vkGetDataGraphPipelinePropertiesARM, graph/graph_layer.cpp:1427-1524 ----
+ * The profiling property exists only for pipelines created while VMEL_GRAPH_PROFILING was truthy
+ * (graph/graph_profiler.cpp:29-38, 107).  Every dispatch of such a pipeline's sessions is then timed kernel
+ * by kernel with CUDA events, and the property returns the reference's JSON document
+ * (graph/graph_profiler.cpp:563-620: "timestamp_period_ns", "samples", "by_operator") after waiting for the
+ * recorded dispatches; ticks are nanoseconds since the pipeline's first profiled dispatch. */
+#define MLEL_PIPELINE_PROPERTY_CREATION_LOG 0u     /* VK_DATA_GRAPH_PIPELINE_PROPERTY_CREATION_LOG_ARM */
+#define MLEL_PIPELINE_PROPERTY_PROFILING 0x7ffffffeu /* the layer-private property, graph_layer.cpp:108-114 */
+/* Two-call enumeration as above. */
+int mlel_pipeline_available_properties(const mlel_pipeline *p, uint32_t *count, uint32_t *properties);
+/* With `data` NULL *data_size receives the size needed (text plus its terminating zero).  Otherwise at most
+ * *data_size bytes are written and *data_size receives the number written; MLEL_INCOMPLETE if the text was
+ * cut short.  *is_text is set to 1.  Unknown property, or profiling not enabled: MLEL_ERROR_UNKNOWN. */
+int mlel_pipeline_get_property(mlel_pipeline *p, uint32_t property, void *data, size_t *data_size, int *is_text);
+/* Forgets the samples taken so far (the reference drops them with their command buffers). */
+int mlel_pipeline_clear_profile(mlel_pipeline *p);
+
 /* Number of kernels one dispatch launches. */
 int mlel_session_launch_count(const mlel_session *s);
 /* Host-buffer convenience used for end-to-end timing: copies `n_in` host inputs to their bound
