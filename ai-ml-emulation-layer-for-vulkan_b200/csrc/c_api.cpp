@@ -423,6 +423,74 @@ int mlel_make_select(mlel_pipeline *p, mlel_tensor_id input1, mlel_tensor_id inp
     });
 }
 
+int mlel_make_argmax(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, uint32_t axis, uint32_t nan_mode,
+                     const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeArgmax(input, output, axis, nan_mode, nameOr(debug_name, "ARGMAX"));
+        return MLEL_SUCCESS;
+    });
+}
+
+int mlel_make_gather(mlel_pipeline *p, mlel_tensor_id values, mlel_tensor_id indices, mlel_tensor_id output,
+                     const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeGather(values, indices, output, nameOr(debug_name, "GATHER"));
+        return MLEL_SUCCESS;
+    });
+}
+
+int mlel_make_scatter(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id values, mlel_tensor_id indices,
+                      mlel_tensor_id output, const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeScatter(input, values, indices, output, nameOr(debug_name, "SCATTER"));
+        return MLEL_SUCCESS;
+    });
+}
+
+int mlel_make_reverse(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, uint32_t axis,
+                      const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeReverse(input, output, axis, nameOr(debug_name, "REVERSE"));
+        return MLEL_SUCCESS;
+    });
+}
+
+int mlel_make_tile(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeTile(input, output, nameOr(debug_name, "TILE"));
+        return MLEL_SUCCESS;
+    });
+}
+
+int mlel_make_resize(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const int32_t scale[4],
+                     const int32_t offset[2], const int32_t border[2], uint32_t mode, const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeResize(input, output, vec(scale, 4), vec(offset, 2), vec(border, 2), mode,
+                            nameOr(debug_name, "RESIZE"));
+        return MLEL_SUCCESS;
+    });
+}
+
+int mlel_make_transpose_conv2d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, mlel_tensor_id weights,
+                               mlel_tensor_id biases, const int32_t out_pad[4], const int32_t stride[2],
+                               int8_t input_zp, int8_t weight_zp, uint32_t acc_type, const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeTransposeConv2D(input, output, weights, biases, vec(out_pad, 4), vec(stride, 2), input_zp,
+                                     weight_zp, acc_type, nameOr(debug_name, "TRANSPOSE_CONV2D"));
+        return MLEL_SUCCESS;
+    });
+}
+
+int mlel_make_conv3d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, mlel_tensor_id weights,
+                     mlel_tensor_id biases, const int32_t pad[6], const int32_t stride[3], const int32_t dilation[3],
+                     int8_t input_zp, int8_t weight_zp, uint32_t acc_type, const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeConv3D(input, output, weights, biases, vec(pad, 6), vec(stride, 3), vec(dilation, 3), input_zp,
+                            weight_zp, acc_type, nameOr(debug_name, "CONV3D"));
+        return MLEL_SUCCESS;
+    });
+}
+
 /* ---- planner ---- */
 
 int mlel_allocate_intervals(const mlel_live_interval *intervals, size_t interval_count,

@@ -22,6 +22,15 @@
 //   ARITHMETIC_RIGHT_SHIFT    i[0] round
 //   NEGATE                    i[0] inputZeroPoint i[1] outputZeroPoint
 //   SELECT                    in = {condition, input2, input3}
+//   ARGMAX                    i[0] axis i[1] nanMode
+//   GATHER                    in = {values, indices}
+//   SCATTER                   in = {values_in, indices, input}
+//   REVERSE                   i[0] axis
+//   RESIZE                    i[0..3] scale (y_n, y_d, x_n, x_d) i[4..5] offset i[6..7] border i[8] mode
+//   TRANSPOSE_CONV2D          i[0..3] out_pad i[4..5] stride i[8] inputZeroPoint i[9] weightZeroPoint i[10] accType
+//                             in = {input, weights, biases}
+//   CONV3D                    i[0..5] pad i[6..8] stride i[9..11] dilation i[12] inputZeroPoint
+//                             i[13] weightZeroPoint i[14] accType      in = {input, weights, biases}
 #include "graph_pipeline.hpp"
 
 #include <cuda_runtime.h>
@@ -495,6 +504,114 @@ void GraphPipeline::makeSelect(int32_t input1, int32_t input2, int32_t input3, i
     need(elemSize(tensor(input1).dtype) == 1, debugName + ": condition must be an 8-bit tensor");
     need(tensor(input2).dtype == tensor(input3).dtype, debugName + ": value types differ");
     pushOp(OP_SELECT, debugName, {input1, input2, input3}, {output});
+}
+
+void GraphPipeline::makeArgmax(int32_t input, int32_t output, uint32_t axis, uint32_t nanMode,
+                               const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.dtype == MLEL_I8 || in.dtype == MLEL_I16 || in.dtype == MLEL_I32, debugName + ": only integers built");
+    need(out.dtype == MLEL_I32, debugName + ": the output holds int32 indices");
+    need(int(axis) < in.rank() && out.rank() == in.rank() - 1, debugName + ": axis or rank mismatch");
+    auto &op = pushOp(OP_ARGMAX, debugName, {input}, {output});
+    op.i[0] = int32_t(axis), op.i[1] = int32_t(nanMode);
+}
+
+void GraphPipeline::makeGather(int32_t values, int32_t indices, int32_t output, const std::string &debugName) {
+    const auto &v = tensor(values), &ix = tensor(indices), &out = tensor(output);
+    need(v.rank() == 3 && ix.rank() == 2 && out.rank() == 3, debugName + ": rank mismatch");
+    need(ix.dtype == MLEL_I32, debugName + ": indices must be int32");
+    need(elemSize(v.dtype) == elemSize(out.dtype), debugName + ": element size mismatch");
+    pushOp(OP_GATHER, debugName, {values, indices}, {output});
+}
+
+void GraphPipeline::makeScatter(int32_t input, int32_t values, int32_t indices, int32_t output,
+                                const std::string &debugName) {
+    const auto &in = tensor(input), &v = tensor(values), &ix = tensor(indices), &out = tensor(output);
+    need(in.rank() == 3 && v.rank() == 3 && ix.rank() == 2 && out.rank() == 3, debugName + ": rank mismatch");
+    need(ix.dtype == MLEL_I32, debugName + ": indices must be int32");
+    need(elemSize(v.dtype) == elemSize(out.dtype) && elemSize(in.dtype) == elemSize(out.dtype),
+         debugName + ": element size mismatch");
+    pushOp(OP_SCATTER, debugName, {values, indices, input}, {output});
+}
+
+void GraphPipeline::makeReverse(int32_t input, int32_t output, uint32_t axis, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.rank() == out.rank() && int(axis) < in.rank(), debugName + ": axis or rank mismatch");
+    need(elemSize(in.dtype) == elemSize(out.dtype), debugName + ": element size mismatch");
+    auto &op = pushOp(OP_REVERSE, debugName, {input}, {output});
+    op.i[0] = int32_t(axis);
+}
+
+void GraphPipeline::makeTile(int32_t input, int32_t output, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.rank() == out.rank(), debugName + ": rank mismatch");
+    need(elemSize(in.dtype) == elemSize(out.dtype), debugName + ": element size mismatch");
+    for (int k = 0; k < in.rank(); ++k) {
+        need(in.dims[size_t(k)] > 0, debugName + ": empty input dimension");
+    }
+    pushOp(OP_TILE, debugName, {input}, {output});
+}
+
+void GraphPipeline::makeResize(int32_t input, int32_t output, const std::vector<int32_t> &scale,
+                               const std::vector<int32_t> &offset, const std::vector<int32_t> &border, uint32_t mode,
+                               const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output);
+    need(in.rank() == 4 && out.rank() == 4, debugName + ": rank mismatch");
+    need(scale.size() == 4 && offset.size() == 2 && border.size() == 2, debugName + ": attribute size mismatch");
+    need(mode == 1 || mode == 2, debugName + ": mode must be NEAREST (1) or BILINEAR (2)");
+    need(scale[0] > 0 && scale[2] > 0, debugName + ": scale numerators must be positive");
+    // integer variants of the operator: int8 -> int8 / int32, int16 -> int16 / int64 (48-bit)
+    const bool ok = (in.dtype == MLEL_I8 && (out.dtype == MLEL_I8 || out.dtype == MLEL_I32)) ||
+                    (in.dtype == MLEL_I16 && (out.dtype == MLEL_I16 || out.dtype == MLEL_I64));
+    need(ok, debugName + ": only the integer variants are built");
+    auto &op = pushOp(OP_RESIZE, debugName, {input}, {output});
+    for (int k = 0; k < 4; ++k) {
+        op.i[k] = scale[size_t(k)];
+    }
+    op.i[4] = offset[0], op.i[5] = offset[1], op.i[6] = border[0], op.i[7] = border[1], op.i[8] = int32_t(mode);
+}
+
+void GraphPipeline::makeTransposeConv2D(int32_t input, int32_t output, int32_t weights, int32_t biases,
+                                        const std::vector<int32_t> &outPad, const std::vector<int32_t> &stride,
+                                        int8_t inputZeroPoint, int8_t weightZeroPoint, uint32_t accType,
+                                        const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output), &w = tensor(weights), &b = tensor(biases);
+    need(in.rank() == 4 && out.rank() == 4 && w.rank() == 4 && b.rank() == 1, debugName + ": rank mismatch");
+    need(outPad.size() == 4 && stride.size() == 2, debugName + ": attribute size mismatch");
+    need(stride[0] > 0 && stride[1] > 0, debugName + ": strides must be positive");
+    need(accType == 1 || accType == 4, debugName + ": only integer accumulators are built (accType 1 or 4)");
+    need((in.dtype == MLEL_I8 && out.dtype == MLEL_I32) || (in.dtype == MLEL_I16 && out.dtype == MLEL_I64),
+         debugName + ": supported types are int8->int32 and int16->int64");
+    need(w.dtype == MLEL_I8 && b.dtype == out.dtype, debugName + ": weights must be int8, bias of the output type");
+    auto &op = pushOp(OP_TRANSPOSE_CONV2D, debugName, {input, weights, biases}, {output});
+    for (int k = 0; k < 4; ++k) {
+        op.i[k] = outPad[size_t(k)];
+    }
+    op.i[4] = stride[0], op.i[5] = stride[1], op.i[6] = 1, op.i[7] = 1;
+    op.i[8] = inputZeroPoint, op.i[9] = weightZeroPoint, op.i[10] = int32_t(accType);
+}
+
+void GraphPipeline::makeConv3D(int32_t input, int32_t output, int32_t weights, int32_t biases,
+                               const std::vector<int32_t> &pad, const std::vector<int32_t> &stride,
+                               const std::vector<int32_t> &dilation, int8_t inputZeroPoint, int8_t weightZeroPoint,
+                               uint32_t accType, const std::string &debugName) {
+    const auto &in = tensor(input), &out = tensor(output), &w = tensor(weights), &b = tensor(biases);
+    need(in.rank() == 5 && out.rank() == 5 && w.rank() == 5 && b.rank() == 1, debugName + ": rank mismatch");
+    need(pad.size() == 6 && stride.size() == 3 && dilation.size() == 3, debugName + ": attribute size mismatch");
+    need(dilation[0] > 0 && dilation[1] > 0 && dilation[2] > 0, debugName + ": dilations must be positive");
+    need(accType == 1 || accType == 4, debugName + ": only integer accumulators are built (accType 1 or 4)");
+    need((in.dtype == MLEL_I8 && out.dtype == MLEL_I32) || (in.dtype == MLEL_I16 && out.dtype == MLEL_I64),
+         debugName + ": supported types are int8->int32 and int16->int64");
+    need(w.dtype == MLEL_I8 && b.dtype == out.dtype, debugName + ": weights must be int8, bias of the output type");
+    auto &op = pushOp(OP_CONV3D, debugName, {input, weights, biases}, {output});
+    for (int k = 0; k < 6; ++k) {
+        op.i[k] = pad[size_t(k)];
+    }
+    for (int k = 0; k < 3; ++k) {
+        op.i[6 + k] = stride[size_t(k)];
+        op.i[9 + k] = dilation[size_t(k)];
+    }
+    op.i[12] = inputZeroPoint, op.i[13] = weightZeroPoint, op.i[14] = int32_t(accType);
 }
 
 /*******************************************************************************

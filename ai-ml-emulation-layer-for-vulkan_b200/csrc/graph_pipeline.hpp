@@ -108,6 +108,21 @@ class GraphPipeline {
     void makeNegate(int32_t input, int32_t output, int32_t inputZeroPoint, int32_t outputZeroPoint,
                     const std::string &debugName);
     void makeSelect(int32_t input1, int32_t input2, int32_t input3, int32_t output, const std::string &debugName);
+    void makeArgmax(int32_t input, int32_t output, uint32_t axis, uint32_t nanMode, const std::string &debugName);
+    void makeGather(int32_t values, int32_t indices, int32_t output, const std::string &debugName);
+    void makeScatter(int32_t input, int32_t values, int32_t indices, int32_t output, const std::string &debugName);
+    void makeReverse(int32_t input, int32_t output, uint32_t axis, const std::string &debugName);
+    void makeTile(int32_t input, int32_t output, const std::string &debugName);
+    void makeResize(int32_t input, int32_t output, const std::vector<int32_t> &scale,
+                    const std::vector<int32_t> &offset, const std::vector<int32_t> &border, uint32_t mode,
+                    const std::string &debugName);
+    void makeTransposeConv2D(int32_t input, int32_t output, int32_t weights, int32_t biases,
+                             const std::vector<int32_t> &outPad, const std::vector<int32_t> &stride,
+                             int8_t inputZeroPoint, int8_t weightZeroPoint, uint32_t accType,
+                             const std::string &debugName);
+    void makeConv3D(int32_t input, int32_t output, int32_t weights, int32_t biases, const std::vector<int32_t> &pad,
+                    const std::vector<int32_t> &stride, const std::vector<int32_t> &dilation, int8_t inputZeroPoint,
+                    int8_t weightZeroPoint, uint32_t accType, const std::string &debugName);
 
     // --- access ---
     const std::vector<OpDesc> &getPipelines() const { return ops_; }   // logical op list

@@ -97,4 +97,15 @@ int genericNegate(const TView &in, const TView &out, int32_t inZp, int32_t outZp
 int genericSelect(const TView &c, const TView &a, const TView &b, const TView &out, cudaStream_t s);
 int genericUnary(int32_t op, const TView &in, const TView &out, cudaStream_t s);
 
+// index_ops.cu: ARGMAX, GATHER, SCATTER, REVERSE, TILE, integer RESIZE, TRANSPOSE_CONV2D, CONV3D
+int indexArgmax(const TView &in, const TView &out, uint32_t axis, cudaStream_t s);
+int indexGather(const TView &values, const TView &indices, const TView &out, cudaStream_t s);
+int indexScatter(const TView &valuesIn, const TView &indices, const TView &input, const TView &out, cudaStream_t s);
+int indexReverse(const TView &in, const TView &out, uint32_t axis, cudaStream_t s);
+int indexTile(const TView &in, const TView &out, cudaStream_t s);
+int resizeInteger(const TView &in, const TView &out, const ResizeAttr &a, cudaStream_t s);
+int transposeConv2d(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
+                    cudaStream_t s);
+int conv3d(const TView &in, const TView &w, const TView &bias, const TView &out, const Conv3dAttr &a, cudaStream_t s);
+
 } // namespace mlel

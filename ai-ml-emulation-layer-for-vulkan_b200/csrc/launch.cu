@@ -327,6 +327,38 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         return genericNegate(in(0), out, op.i[0], op.i[1], s);
     case OP_SELECT:
         return genericSelect(in(0), in(1), in(2), out, s);
+    case OP_ARGMAX:
+        return indexArgmax(in(0), out, uint32_t(op.i[0]), s);
+    case OP_GATHER:
+        return indexGather(in(0), in(1), out, s);
+    case OP_SCATTER:
+        return indexScatter(in(0), in(1), in(2), out, s);
+    case OP_REVERSE:
+        return indexReverse(in(0), out, uint32_t(op.i[0]), s);
+    case OP_TILE:
+        return indexTile(in(0), out, s);
+    case OP_RESIZE: {
+        ResizeAttr a{};
+        for (int k = 0; k < 4; ++k) {
+            a.scale[k] = op.i[k];
+        }
+        a.offset[0] = op.i[4], a.offset[1] = op.i[5], a.border[0] = op.i[6], a.border[1] = op.i[7], a.mode = op.i[8];
+        return resizeInteger(in(0), out, a, s);
+    }
+    case OP_TRANSPOSE_CONV2D:
+        return transposeConv2d(in(0), in(1), in(2), out, convAttr(op), s);
+    case OP_CONV3D: {
+        Conv3dAttr a{};
+        for (int k = 0; k < 6; ++k) {
+            a.pad[k] = op.i[k];
+        }
+        for (int k = 0; k < 3; ++k) {
+            a.stride[k] = op.i[6 + k];
+            a.dilation[k] = op.i[9 + k];
+        }
+        a.inZp = op.i[12], a.wZp = op.i[13];
+        return conv3d(in(0), in(1), in(2), out, a, s);
+    }
     case OP_FUSED_CONV2D:
         return fusedConv2dGeneric(in(0), in(1), in(2), out, convAttr(op), devEpilogue(op.epi, T), s);
     case OP_FUSED_DEPTHWISE: {

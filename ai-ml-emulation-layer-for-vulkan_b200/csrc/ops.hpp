@@ -49,6 +49,14 @@ enum OpKind : int32_t {
     OP_ARITHMETIC_RIGHT_SHIFT,
     OP_NEGATE,
     OP_SELECT,
+    OP_ARGMAX,
+    OP_GATHER,
+    OP_SCATTER,
+    OP_REVERSE,
+    OP_TILE,
+    OP_RESIZE,
+    OP_TRANSPOSE_CONV2D,
+    OP_CONV3D,
     // Produced only by the fusion pass:
     OP_FUSED_CONV2D,     // CONV2D -> RESCALE [-> CLAMP] [-> residual RESCALE/ADD/RESCALE [-> CLAMP]]
     OP_FUSED_DEPTHWISE,  // DEPTHWISE_CONV2D -> RESCALE [-> CLAMP]
@@ -87,6 +95,23 @@ struct ConvAttr {
     int32_t dilation[2]; // y, x
     int32_t inZp;
     int32_t wZp;
+};
+
+// CONV3D attributes (the push constants of conv3d.comp:17-23).
+struct Conv3dAttr {
+    int32_t pad[6];      // front, back, top, bottom, left, right
+    int32_t stride[3];   // d, y, x
+    int32_t dilation[3]; // d, y, x
+    int32_t inZp;
+    int32_t wZp;
+};
+
+// RESIZE attributes (resize.comp:16-39).
+struct ResizeAttr {
+    int32_t scale[4];  // y numerator, y denominator, x numerator, x denominator
+    int32_t offset[2]; // y, x
+    int32_t border[2]; // y, x
+    int32_t mode;      // 1 = NEAREST, 2 = BILINEAR
 };
 
 // RESCALE attributes (rescale.comp:11-19).

@@ -99,15 +99,15 @@ struct TosaEntry {
     bool built;
 };
 const TosaEntry kTosaOps[] = {
-    {"ABS", true},          {"ADD", true},           {"ARGMAX", false},
+    {"ABS", true},          {"ADD", true},           {"ARGMAX", true},
     {"ARITHMETIC_RIGHT_SHIFT", true},                {"AVG_POOL2D", true},
     {"BITWISE_AND", true},  {"BITWISE_NOT", true},   {"BITWISE_OR", true},
     {"BITWISE_XOR", true},  {"CAST", true},          {"CEIL", false},
     {"CLAMP", true},        {"CLZ", true},           {"CONCAT", true},
-    {"CONV2D", true},       {"CONV3D", false},       {"COS", false},
+    {"CONV2D", true},       {"CONV3D", true},       {"COS", false},
     {"DEPTHWISE_CONV2D", true},                      {"EQUAL", true},
     {"ERF", false},         {"EXP", false},          {"FFT2D", false},
-    {"FLOOR", false},       {"GATHER", false},       {"GREATER", true},
+    {"FLOOR", false},       {"GATHER", true},       {"GREATER", true},
     {"GREATER_EQUAL", true},                         {"INTDIV", true},
     {"LOG", false},         {"LOGICAL_AND", true},   {"LOGICAL_LEFT_SHIFT", true},
     {"LOGICAL_NOT", true},  {"LOGICAL_OR", true},    {"LOGICAL_RIGHT_SHIFT", true},
@@ -117,11 +117,11 @@ const TosaEntry kTosaOps[] = {
     {"RECIPROCAL", false},  {"REDUCE_ALL", true},    {"REDUCE_ANY", true},
     {"REDUCE_MAX", true},   {"REDUCE_MIN", true},    {"REDUCE_PRODUCT", true},
     {"REDUCE_SUM", true},   {"RESCALE", true},       {"RESHAPE", true},
-    {"RESIZE", false},      {"REVERSE", false},      {"RFFT2D", false},
-    {"RSQRT", false},       {"SCATTER", false},      {"SELECT", true},
+    {"RESIZE", true},      {"REVERSE", true},      {"RFFT2D", false},
+    {"RSQRT", false},       {"SCATTER", true},      {"SELECT", true},
     {"SIGMOID", false},     {"SIN", false},          {"SLICE", true},
     {"SUB", true},          {"TABLE", true},         {"TANH", false},
-    {"TILE", false},        {"TRANSPOSE", true},     {"TRANSPOSE_CONV2D", false},
+    {"TILE", true},        {"TRANSPOSE", true},     {"TRANSPOSE_CONV2D", true},
 };
 
 const std::unordered_map<std::string, BinaryOp> kBinaryOps = {
@@ -738,6 +738,42 @@ class Lowering {
         } else if (name == "SELECT") {
             argc(3);
             p.makeSelect(getTensor(a[0]), getTensor(a[1]), getTensor(a[2]), result(), name);
+        } else if (name == "ARGMAX") {
+            argc(3); // axis nanMode input
+            p.makeArgmax(getTensor(a[2]), result(), constScalar(a[0]).as<uint32_t>(),
+                         constScalar(a[1]).as<uint32_t>(), name);
+        } else if (name == "GATHER") {
+            argc(2); // values indices
+            p.makeGather(getTensor(a[0]), getTensor(a[1]), result(), name);
+        } else if (name == "SCATTER") {
+            argc(3); // valuesIn indices input
+            p.makeScatter(getTensor(a[2]), getTensor(a[0]), getTensor(a[1]), result(), name);
+        } else if (name == "REVERSE") {
+            argc(2); // axis input
+            p.makeReverse(getTensor(a[1]), result(), constScalar(a[0]).as<uint32_t>(), name);
+        } else if (name == "TILE") {
+            argc(2); // input multiples (decoded; the output tensor's shape is what is used)
+            (void)constVector<uint32_t>(a[1]);
+            p.makeTile(getTensor(a[0]), result(), name);
+        } else if (name == "RESIZE") {
+            argc(5); // mode input scale offset border
+            p.makeResize(getTensor(a[1]), result(), constVector<int32_t>(a[2]), constVector<int32_t>(a[3]),
+                         constVector<int32_t>(a[4]), constScalar(a[0]).as<uint32_t>(), name);
+        } else if (name == "TRANSPOSE_CONV2D") {
+            // outPad stride accType localBound input weight bias inputZeroPoint weightZeroPoint
+            argc(9);
+            (void)boolConstant(a[3]);
+            p.makeTransposeConv2D(getTensor(a[4]), result(), getTensor(a[5]), getTensor(a[6]),
+                                  constVector<int32_t>(a[0]), constVector<int32_t>(a[1]),
+                                  constVector<int8_t>(a[7]).at(0), constVector<int8_t>(a[8]).at(0),
+                                  constScalar(a[2]).as<uint32_t>(), name);
+        } else if (name == "CONV3D") {
+            // pad stride dilation accType localBound input weight bias inputZeroPoint weightZeroPoint
+            argc(10);
+            (void)boolConstant(a[4]);
+            p.makeConv3D(getTensor(a[5]), result(), getTensor(a[6]), getTensor(a[7]), constVector<int32_t>(a[0]),
+                         constVector<int32_t>(a[1]), constVector<int32_t>(a[2]), constVector<int8_t>(a[8]).at(0),
+                         constVector<int8_t>(a[9]).at(0), constScalar(a[3]).as<uint32_t>(), name);
         } else {
             bool known = false;
             for (const auto &e : kTosaOps) {

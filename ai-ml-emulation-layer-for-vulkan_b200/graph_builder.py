@@ -318,6 +318,66 @@ class GraphBuilder:
         shape = tuple(max(p, q, r) for p, q, r in zip(cond.shape, a.shape, b.shape))
         return self._emit("SELECT", [cond.name, a.name, b.name], [cond, a, b], {}, a.dtype, shape)
 
+    def argmax(self, x, axis, nan_mode=NAN_PROPAGATE):
+        shape = x.shape[:axis] + x.shape[axis + 1:]
+        return self._emit("ARGMAX", [self._u32(axis)[1:], self._u32(nan_mode)[1:], x.name], [x], dict(axis=axis),
+                          np.int32, shape)
+
+    def gather(self, values, indices):
+        shape = (values.shape[0], indices.shape[1], values.shape[2])
+        return self._emit("GATHER", [values.name, indices.name], [values, indices], {}, values.dtype, shape)
+
+    def scatter(self, values_in, indices, input_):
+        return self._emit("SCATTER", [values_in.name, indices.name, input_.name], [values_in, indices, input_], {},
+                          values_in.dtype, values_in.shape)
+
+    def reverse(self, x, axis):
+        return self._emit("REVERSE", [self._u32(axis)[1:], x.name], [x], dict(axis=axis), x.dtype, x.shape)
+
+    def tile(self, x, multiples):
+        m = self.inline(np.asarray(multiples, np.int32))
+        shape = tuple(d * int(k) for d, k in zip(x.shape, multiples))
+        return self._emit("TILE", [x.name, m.name], [x], dict(multiples=list(multiples)), x.dtype, shape)
+
+    def resize(self, x, scale, offset, border, mode, out_dtype):
+        """``scale`` = (y_n, y_d, x_n, x_d); ``mode`` 1 = NEAREST, 2 = BILINEAR.  Output size as in TOSA:
+        ``(in - 1) * n - offset + border) // d + 1`` per axis."""
+        n, h, w, c = x.shape
+        oh = ((h - 1) * scale[0] - offset[0] + border[0]) // scale[1] + 1
+        ow = ((w - 1) * scale[2] - offset[1] + border[1]) // scale[3] + 1
+        ops = [self._u32(mode)[1:], x.name, self.inline(np.asarray(scale, np.int32)).name,
+               self.inline(np.asarray(offset, np.int32)).name, self.inline(np.asarray(border, np.int32)).name]
+        return self._emit("RESIZE", ops, [x], dict(scale=list(scale), offset=list(offset), border=list(border),
+                                                   mode=mode), out_dtype, (n, oh, ow, c))
+
+    def transpose_conv2d(self, x, w, bias, out_pad, stride, in_zp, w_zp, acc_type=ACC_INT32):
+        n, h, wd, _ = x.shape
+        oc, kh, kw, _ = w.shape
+        oh = (h - 1) * stride[0] + out_pad[0] + out_pad[1] + kh
+        ow = (wd - 1) * stride[1] + out_pad[2] + out_pad[3] + kw
+        acc = np.int64 if acc_type == ACC_INT64 else np.int32
+        ops = [self.inline(np.asarray(out_pad, np.int32)).name, self.inline(np.asarray(stride, np.int32)).name,
+               self._u32(acc_type)[1:], self._bool(False)[1:], x.name, w.name, bias.name,
+               self.inline(np.asarray([in_zp], np.int8)).name, self.inline(np.asarray([w_zp], np.int8)).name]
+        return self._emit("TRANSPOSE_CONV2D", ops, [x, w, bias],
+                          dict(out_pad=list(out_pad), stride=list(stride), in_zp=in_zp, w_zp=w_zp), acc,
+                          (n, oh, ow, oc))
+
+    def conv3d(self, x, w, bias, pad, stride, dilation, in_zp, w_zp, acc_type=ACC_INT32):
+        n, d, h, wd, _ = x.shape
+        oc, kd, kh, kw, _ = w.shape
+        od = (d + pad[0] + pad[1] - (kd - 1) * dilation[0] - 1) // stride[0] + 1
+        oh = (h + pad[2] + pad[3] - (kh - 1) * dilation[1] - 1) // stride[1] + 1
+        ow = (wd + pad[4] + pad[5] - (kw - 1) * dilation[2] - 1) // stride[2] + 1
+        acc = np.int64 if acc_type == ACC_INT64 else np.int32
+        ops = [self.inline(np.asarray(pad, np.int32)).name, self.inline(np.asarray(stride, np.int32)).name,
+               self.inline(np.asarray(dilation, np.int32)).name, self._u32(acc_type)[1:], self._bool(False)[1:],
+               x.name, w.name, bias.name, self.inline(np.asarray([in_zp], np.int8)).name,
+               self.inline(np.asarray([w_zp], np.int8)).name]
+        return self._emit("CONV3D", ops, [x, w, bias],
+                          dict(pad=list(pad), stride=list(stride), dilation=list(dilation), in_zp=in_zp, w_zp=w_zp),
+                          acc, (n, od, oh, ow, oc))
+
     # ------------------------------------------------------------------ emission
     def spvasm(self) -> str:
         head = [

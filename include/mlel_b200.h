@@ -181,6 +181,29 @@ int mlel_make_negate(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id outp
                      int32_t output_zp, const char *debug_name);
 int mlel_make_select(mlel_pipeline *p, mlel_tensor_id input1, mlel_tensor_id input2, mlel_tensor_id input3,
                      mlel_tensor_id output, const char *debug_name);
+/* makeArgmax: the output has the input's shape without `axis` and holds int32 indices. */
+int mlel_make_argmax(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, uint32_t axis, uint32_t nan_mode,
+                     const char *debug_name);
+/* makeGather: values [N,K,C], indices int32 [N,W] -> output [N,W,C]. */
+int mlel_make_gather(mlel_pipeline *p, mlel_tensor_id values, mlel_tensor_id indices, mlel_tensor_id output,
+                     const char *debug_name);
+/* makeScatter: input [N,W,C] written into a copy of values [N,K,C] at rows indices [N,W] -> output [N,K,C]. */
+int mlel_make_scatter(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id values, mlel_tensor_id indices,
+                      mlel_tensor_id output, const char *debug_name);
+int mlel_make_reverse(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, uint32_t axis,
+                      const char *debug_name);
+/* makeTile: the multiples are implied by the output's shape. */
+int mlel_make_tile(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const char *debug_name);
+/* makeResize: scale = {y_n, y_d, x_n, x_d}; mode 1 = NEAREST, 2 = BILINEAR (integer variants). */
+int mlel_make_resize(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, const int32_t scale[4],
+                     const int32_t offset[2], const int32_t border[2], uint32_t mode, const char *debug_name);
+int mlel_make_transpose_conv2d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, mlel_tensor_id weights,
+                               mlel_tensor_id biases, const int32_t out_pad[4], const int32_t stride[2],
+                               int8_t input_zp, int8_t weight_zp, uint32_t acc_type, const char *debug_name);
+/* makeConv3D: pad = {front, back, top, bottom, left, right}; stride and dilation = {d, y, x}. */
+int mlel_make_conv3d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, mlel_tensor_id weights,
+                     mlel_tensor_id biases, const int32_t pad[6], const int32_t stride[3], const int32_t dilation[3],
+                     int8_t input_zp, int8_t weight_zp, uint32_t acc_type, const char *debug_name);
 
 /* ---- interval memory planner: details::allocateIntervals, graph/interval_memory_planner.cpp:170-216 ---- */
 typedef struct mlel_live_interval {

@@ -15,11 +15,12 @@
 // integer division truncates toward zero, narrowing constructors wrap.
 //
 // Parity pins: the golden vectors of the reference's own tests (tests/vulkan.cpp) for CONV2D,
-// int64-accumulate CONV2D, RESCALE+ADD, MAX_POOL2D, CONCAT, SLICE, MAXIMUM are replayed against
-// this file by tests/test_oracle_golden.py.  MATMUL, DEPTHWISE_CONV2D, AVG_POOL2D, TABLE,
-// TRANSPOSE, CLAMP, MUL, REDUCE_*, per-channel and double-round RESCALE have no golden in the
-// reference: for those this file is "parity unpinned" and is cross-checked against an
-// independent numpy restatement (oracle/np_ref.py).
+// int64-accumulate CONV2D, CONV3D, RESCALE+ADD, MAX_POOL2D, CONCAT, SLICE, MAXIMUM are replayed
+// against this file by tests/test_oracle_golden.py.  MATMUL, DEPTHWISE_CONV2D, AVG_POOL2D, TABLE,
+// TRANSPOSE, CLAMP, MUL, REDUCE_*, per-channel and double-round RESCALE, ARGMAX, GATHER, SCATTER,
+// REVERSE, TILE, RESIZE and TRANSPOSE_CONV2D have no golden in the reference: for those this file
+// is "parity unpinned" and is cross-checked against an independent numpy restatement
+// (oracle/np_ref.py).
 
 #include <algorithm>
 #include <cmath>
@@ -1128,6 +1129,328 @@ int orc_unary(const orc_tensor *in, const orc_tensor *out, int op) {
             break;
         }
         wrInt(*out, idx, r);
+    }
+    return 0;
+}
+
+
+} // extern "C"
+
+namespace {
+
+// Raw bits of one element (any type); a coordinate out of range reads as zero (tensor.glsl:26-50).
+int64_t rdBits(const orc_tensor &t, const uint32_t *c) {
+    switch (elemSize(t.dtype)) {
+    case 1:
+        return rd<uint8_t>(t, c);
+    case 2:
+        return rd<uint16_t>(t, c);
+    case 4:
+        return rd<uint32_t>(t, c);
+    default:
+        return rd<int64_t>(t, c);
+    }
+}
+
+void wrBits(const orc_tensor &t, const uint32_t *c, int64_t bits) {
+    switch (elemSize(t.dtype)) {
+    case 1:
+        wr<uint8_t>(t, c, uint8_t(bits));
+        break;
+    case 2:
+        wr<uint16_t>(t, c, uint16_t(bits));
+        break;
+    case 4:
+        wr<uint32_t>(t, c, uint32_t(bits));
+        break;
+    default:
+        wr<int64_t>(t, c, bits);
+        break;
+    }
+}
+
+// resize.comp:43-51
+int32_t idivFloor(int32_t n, int32_t d) {
+    int32_t r = n / d;
+    if (r * d > n) {
+        --r;
+    }
+    return r;
+}
+
+// resize.comp:53-134 for the integer types: ACC (= the output's own type) holds the products, which wrap.
+template <typename ACC>
+void resizeImpl(const orc_tensor &in, const orc_tensor &out, const int32_t *scale, const int32_t *offset, int32_t mode) {
+    using U = std::make_unsigned_t<ACC>;
+    const int64_t total = numel(out);
+    const uint32_t H = uint32_t(in.dims[1]), W = uint32_t(in.dims[2]);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank];
+        unravel(out, uint32_t(e), idx);
+        const uint32_t n = idx[0], oy = idx[1], ox = idx[2], c = idx[3];
+        const int16_t unitY = int16_t(scale[0]), unitX = int16_t(scale[2]);
+        const int32_t y = int32_t(oy * uint32_t(scale[1]) + uint32_t(offset[0]));
+        const int16_t iy = int16_t(idivFloor(y, scale[0]));
+        const int16_t ry = int16_t(uint32_t(y) - uint32_t(int32_t(iy)) * uint32_t(scale[0]));
+        const int32_t x = int32_t(ox * uint32_t(scale[3]) + uint32_t(offset[1]));
+        const int16_t ix = int16_t(idivFloor(x, scale[2]));
+        const int16_t rx = int16_t(uint32_t(x) - uint32_t(int32_t(ix)) * uint32_t(scale[2]));
+        const int16_t dy = ry, dx = rx;
+        // GLSL: max(int16_t, int) -> int; min(int, uint) -> uint (the signed operand converts)
+        const int16_t iy0 = int16_t(std::max(int32_t(iy), 0));
+        const int16_t iy1 = int16_t(std::min(uint32_t(int32_t(iy) + 1), H - 1));
+        const int16_t ix0 = int16_t(std::max(int32_t(ix), 0));
+        const int16_t ix1 = int16_t(std::min(uint32_t(int32_t(ix) + 1), W - 1));
+        const auto at = [&](int16_t yy, int16_t xx) {
+            const uint32_t ci[4] = {n, uint32_t(int32_t(yy)), uint32_t(int32_t(xx)), c};
+            return U(ACC(rdInt(in, ci)));
+        };
+        const auto mul3 = [](U a, U b, U cc) { return U(uint64_t(U(uint64_t(a) * uint64_t(b))) * uint64_t(cc)); };
+        ACC acc = 0;
+        if (mode == 2) {
+            const U wy0 = U(ACC(int16_t(unitY - dy))), wy1 = U(ACC(dy));
+            const U wx0 = U(ACC(int16_t(unitX - dx))), wx1 = U(ACC(dx));
+            U sum = mul3(at(iy0, ix0), wy0, wx0);
+            sum = U(sum + mul3(at(iy0, ix1), wy0, wx1));
+            sum = U(sum + mul3(at(iy1, ix0), wy1, wx0));
+            sum = U(sum + mul3(at(iy1, ix1), wy1, wx1));
+            acc = ACC(sum);
+        } else if (mode == 1) {
+            const int16_t py = (2 * int32_t(dy) >= scale[0]) ? iy1 : iy0;
+            const int16_t px = (2 * int32_t(dx) >= scale[2]) ? ix1 : ix0;
+            acc = ACC(at(py, px));
+        }
+        wrInt(out, idx, int64_t(acc));
+    }
+}
+
+// transpose_conv2d.comp:29-70
+template <typename ACC>
+void transposeConv2dImpl(const orc_tensor &in, const orc_tensor &w, const orc_tensor &bias, const orc_tensor &out,
+                         const int32_t *pad, const int32_t *stride, int32_t inZp, int32_t wZp) {
+    const int64_t total = numel(out);
+    const uint32_t KH = uint32_t(w.dims[1]), KW = uint32_t(w.dims[2]), IC = uint32_t(in.dims[3]);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank];
+        unravel(out, uint32_t(e), idx);
+        const uint32_t n = idx[0], oy = idx[1], ox = idx[2], oc = idx[3];
+        const uint32_t cb[1] = {bias.dims[0] == 1 ? 0u : oc};
+        ACC acc = ACC(rdInt(bias, cb));
+        for (uint32_t ky = 0; ky < KH; ++ky) {
+            for (uint32_t kx = 0; kx < KW; ++kx) {
+                int32_t iy = int32_t(oy) - pad[0] - int32_t(ky);
+                int32_t ix = int32_t(ox) - pad[2] - int32_t(kx);
+                if ((iy % stride[0]) == 0 && (ix % stride[1]) == 0) {
+                    iy /= stride[0];
+                    ix /= stride[1];
+                    if (iy >= 0 && ix >= 0 && int64_t(iy) < in.dims[1] && int64_t(ix) < in.dims[2]) {
+                        for (uint32_t ic = 0; ic < IC; ++ic) {
+                            const uint32_t ci[4] = {n, uint32_t(iy), uint32_t(ix), ic};
+                            const uint32_t cw[4] = {oc, ky, kx, ic};
+                            const ACC v = Wrap<ACC>::sub(ACC(rdInt(in, ci)), ACC(inZp));
+                            const ACC wt = Wrap<ACC>::sub(ACC(rdInt(w, cw)), ACC(wZp));
+                            acc = Wrap<ACC>::add(acc, Wrap<ACC>::mul(v, wt));
+                        }
+                    }
+                }
+            }
+        }
+        wrInt(out, idx, int64_t(acc));
+    }
+}
+
+// conv3d.comp:33-104, with the shader's own start/stop logic for the taps
+template <typename ACC>
+void conv3dImpl(const orc_tensor &in, const orc_tensor &w, const orc_tensor &bias, const orc_tensor &out,
+                const int32_t *pad, const int32_t *stride, const int32_t *dil, int32_t inZp, int32_t wZp) {
+    const int64_t total = numel(out);
+    const int KD = int(w.dims[1]), KH = int(w.dims[2]), KW = int(w.dims[3]), IC = int(w.dims[4]);
+    const int ID = int(in.dims[1]), IH = int(in.dims[2]), IW = int(in.dims[3]);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank];
+        unravel(out, uint32_t(e), idx);
+        const uint32_t n = idx[0], oc = idx[4];
+        const int id = int(idx[1]) * stride[0] - pad[0];
+        const int iy = int(idx[2]) * stride[1] - pad[2];
+        const int ix = int(idx[3]) * stride[2] - pad[4];
+        int dStart = id, kdStart = 0;
+        if (dStart < 0) {
+            kdStart = (-dStart + dil[0] - 1) / dil[0];
+            dStart = id + kdStart * dil[0];
+        }
+        int yStart = iy, kyStart = 0;
+        if (yStart < 0) {
+            kyStart = (-yStart + dil[1] - 1) / dil[1];
+            yStart = iy + kyStart * dil[1];
+        }
+        int xStart = ix, kxStart = 0;
+        if (xStart < 0) {
+            kxStart = (-xStart + dil[2] - 1) / dil[2];
+            xStart = ix + kxStart * dil[2];
+        }
+        ACC acc = 0;
+        for (int d = dStart, kd = kdStart; kd < KD && d < ID; ++kd, d += dil[0]) {
+            for (int y = yStart, ky = kyStart; ky < KH && y < IH; ++ky, y += dil[1]) {
+                for (int x = xStart, kx = kxStart; kx < KW && x < IW; ++kx, x += dil[2]) {
+                    for (int ic = 0; ic < IC; ++ic) {
+                        const uint32_t ci[5] = {n, uint32_t(d), uint32_t(y), uint32_t(x), uint32_t(ic)};
+                        const uint32_t cw[5] = {oc, uint32_t(kd), uint32_t(ky), uint32_t(kx), uint32_t(ic)};
+                        const ACC v = Wrap<ACC>::sub(ACC(rdInt(in, ci)), ACC(inZp));
+                        const ACC wt = Wrap<ACC>::sub(ACC(rdInt(w, cw)), ACC(wZp));
+                        acc = Wrap<ACC>::add(acc, Wrap<ACC>::mul(v, wt));
+                    }
+                }
+            }
+        }
+        const uint32_t cb[1] = {bias.dims[0] == 1 ? 0u : oc};
+        acc = Wrap<ACC>::add(ACC(rdInt(bias, cb)), acc);
+        wrInt(out, idx, int64_t(acc));
+    }
+}
+
+} // namespace
+
+extern "C" {
+
+// graph/shaders/graph_op/tosa/argmax.comp:26-66, integer inputs
+int orc_argmax(const orc_tensor *in, const orc_tensor *out, uint32_t axis) {
+    const int64_t total = numel(*out);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank] = {0, 0, 0, 0, 0, 0}, src[kMaxRank] = {0, 0, 0, 0, 0, 0};
+        unravel(*out, uint32_t(e), idx);
+        for (uint32_t i = 0; i < axis; ++i) {
+            src[i] = idx[i];
+        }
+        for (uint32_t i = axis; i < uint32_t(out->rank); ++i) {
+            src[i + 1] = idx[i];
+        }
+        int64_t maxValue = typeLowest(in->dtype);
+        int32_t maxIndex = 0;
+        for (int32_t i = 0; i < int32_t(in->dims[axis]); ++i) {
+            src[axis] = uint32_t(i);
+            const int64_t v = rdInt(*in, src);
+            if (v > maxValue) {
+                maxValue = v;
+                maxIndex = i;
+            }
+        }
+        wrInt(*out, idx, maxIndex);
+    }
+    return 0;
+}
+
+// graph/shaders/graph_op/tosa/gather.comp:14-25
+int orc_gather(const orc_tensor *values, const orc_tensor *indices, const orc_tensor *out) {
+    const int64_t total = numel(*out);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank];
+        unravel(*out, uint32_t(e), idx);
+        const uint32_t ci[2] = {idx[0], idx[1]};
+        const uint32_t k = uint32_t(rdInt(*indices, ci));
+        const uint32_t cv[3] = {idx[0], k, idx[2]};
+        wrBits(*out, idx, rdBits(*values, cv));
+    }
+    return 0;
+}
+
+// graph/shaders/graph_op/tosa/scatter.comp:15-34
+int orc_scatter(const orc_tensor *valuesIn, const orc_tensor *indices, const orc_tensor *input,
+                const orc_tensor *out) {
+    const int64_t total = numel(*out);
+    const uint32_t W = uint32_t(indices->dims[1]);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank];
+        unravel(*out, uint32_t(e), idx);
+        int64_t bits = rdBits(*valuesIn, idx);
+        for (uint32_t w = 0; w < W; ++w) {
+            const uint32_t ci[2] = {idx[0], w};
+            if (uint32_t(rdInt(*indices, ci)) == idx[1]) {
+                const uint32_t cs[3] = {idx[0], w, idx[2]};
+                bits = rdBits(*input, cs);
+                break;
+            }
+        }
+        wrBits(*out, idx, bits);
+    }
+    return 0;
+}
+
+// graph/shaders/graph_op/tosa/reverse.comp:19-30
+int orc_reverse(const orc_tensor *in, const orc_tensor *out, uint32_t axis) {
+    const int64_t total = numel(*out);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank];
+        unravel(*out, uint32_t(e), idx);
+        const int64_t bits = rdBits(*in, idx);
+        idx[axis] = uint32_t(out->dims[axis]) - 1 - idx[axis];
+        wrBits(*out, idx, bits);
+    }
+    return 0;
+}
+
+// graph/shaders/graph_op/tosa/tile.comp:15-30
+int orc_tile(const orc_tensor *in, const orc_tensor *out) {
+    const int64_t total = numel(*out);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank], src[kMaxRank];
+        unravel(*out, uint32_t(e), idx);
+        for (int i = 0; i < out->rank; ++i) {
+            src[i] = idx[i] % uint32_t(in->dims[i]);
+        }
+        wrBits(*out, idx, rdBits(*in, src));
+    }
+    return 0;
+}
+
+// graph/shaders/graph_op/tosa/resize.comp; scale = {y_n, y_d, x_n, x_d}, mode 1 NEAREST / 2 BILINEAR
+int orc_resize(const orc_tensor *in, const orc_tensor *out, const int32_t *scale, const int32_t *offset,
+               int32_t mode) {
+    switch (out->dtype) {
+    case ORC_I8:
+        resizeImpl<int8_t>(*in, *out, scale, offset, mode);
+        return 0;
+    case ORC_I16:
+        resizeImpl<int16_t>(*in, *out, scale, offset, mode);
+        return 0;
+    case ORC_I32:
+        resizeImpl<int32_t>(*in, *out, scale, offset, mode);
+        return 0;
+    case ORC_I64:
+        resizeImpl<int64_t>(*in, *out, scale, offset, mode);
+        return 0;
+    default:
+        return -1;
+    }
+}
+
+int orc_transpose_conv2d(const orc_tensor *in, const orc_tensor *w, const orc_tensor *bias, const orc_tensor *out,
+                         const int32_t *pad, const int32_t *stride, int32_t inZp, int32_t wZp) {
+    if (out->dtype == ORC_I32) {
+        transposeConv2dImpl<int32_t>(*in, *w, *bias, *out, pad, stride, inZp, wZp);
+    } else if (out->dtype == ORC_I64) {
+        transposeConv2dImpl<int64_t>(*in, *w, *bias, *out, pad, stride, inZp, wZp);
+    } else {
+        return -1;
+    }
+    return 0;
+}
+
+int orc_conv3d(const orc_tensor *in, const orc_tensor *w, const orc_tensor *bias, const orc_tensor *out,
+               const int32_t *pad, const int32_t *stride, const int32_t *dil, int32_t inZp, int32_t wZp) {
+    if (out->dtype == ORC_I32) {
+        conv3dImpl<int32_t>(*in, *w, *bias, *out, pad, stride, dil, inZp, wZp);
+    } else if (out->dtype == ORC_I64) {
+        conv3dImpl<int64_t>(*in, *w, *bias, *out, pad, stride, dil, inZp, wZp);
+    } else {
+        return -1;
     }
     return 0;
 }

@@ -154,3 +154,91 @@ def mul(a, b, shift):
     if shift > 0:
         r = (r + (1 << (shift - 1))) >> shift
     return _wrap32(r)
+
+
+# ---- index-driven operators, TRANSPOSE_CONV2D, CONV3D, integer RESIZE: written from the TOSA definitions of
+# the operators (scatter-style accumulation for the transposed convolution, explicit zero padding for CONV3D,
+# Python integers for RESIZE), i.e. not shaped like the shaders the C++ oracle follows.
+
+def argmax(x, axis):
+    return np.argmax(x, axis=axis).astype(np.int32)  # numpy returns the first maximum as well
+
+
+def gather(values, indices):
+    n = np.arange(values.shape[0])[:, None]
+    return values[n, indices, :]
+
+
+def scatter(values_in, indices, input_):
+    out = values_in.copy()
+    for n in range(indices.shape[0]):
+        for w in reversed(range(indices.shape[1])):  # the first occurrence of an index must win
+            out[n, indices[n, w]] = input_[n, w]
+    return out
+
+
+def transpose_conv2d(x, w, bias, out_pad, stride, in_zp, w_zp, acc=np.int32):
+    n, h, wd, ic = x.shape
+    oc, kh, kw, _ = w.shape
+    oh = (h - 1) * stride[0] + out_pad[0] + out_pad[1] + kh
+    ow = (wd - 1) * stride[1] + out_pad[2] + out_pad[3] + kw
+    out = np.zeros((n, oh, ow, oc), dtype=object)
+    out[...] = np.broadcast_to(np.asarray(bias, dtype=object), (oc,)) if bias.shape[0] == oc else int(bias[0])
+    xs = x.astype(object) - in_zp
+    ws = w.astype(object) - w_zp
+    for iy in range(h):
+        for ix in range(wd):
+            for ky in range(kh):
+                for kx in range(kw):
+                    oy = iy * stride[0] + out_pad[0] + ky
+                    ox = ix * stride[1] + out_pad[2] + kx
+                    if 0 <= oy < oh and 0 <= ox < ow:
+                        out[:, oy, ox, :] += xs[:, iy, ix, :] @ ws[:, ky, kx, :].T
+    bits = 64 if acc == np.int64 else 32
+    wrap = np.vectorize(lambda v: ((int(v) + (1 << (bits - 1))) % (1 << bits)) - (1 << (bits - 1)), otypes=[object])
+    return wrap(out).astype(acc)
+
+
+def conv3d(x, w, bias, pad, stride, dil, in_zp, w_zp):
+    n, d, h, wd, ic = x.shape
+    oc, kd, kh, kw, _ = w.shape
+    xp = np.full((n, d + pad[0] + pad[1], h + pad[2] + pad[3], wd + pad[4] + pad[5], ic), in_zp, np.int64)
+    xp[:, pad[0]:pad[0] + d, pad[2]:pad[2] + h, pad[4]:pad[4] + wd, :] = x
+    xp -= in_zp
+    ws = w.astype(np.int64) - w_zp
+    od = (xp.shape[1] - (kd - 1) * dil[0] - 1) // stride[0] + 1
+    oh = (xp.shape[2] - (kh - 1) * dil[1] - 1) // stride[1] + 1
+    ow = (xp.shape[3] - (kw - 1) * dil[2] - 1) // stride[2] + 1
+    out = np.zeros((n, od, oh, ow, oc), np.int64)
+    for a in range(kd):
+        for b in range(kh):
+            for c in range(kw):
+                win = xp[:, a * dil[0]:a * dil[0] + (od - 1) * stride[0] + 1:stride[0],
+                         b * dil[1]:b * dil[1] + (oh - 1) * stride[1] + 1:stride[1],
+                         c * dil[2]:c * dil[2] + (ow - 1) * stride[2] + 1:stride[2], :]
+                out += np.einsum("ndhwi,oi->ndhwo", win, ws[:, a, b, c, :])
+    out += bias.astype(np.int64)
+    return out.astype(np.int32) if x.dtype == np.int8 else out
+
+
+def resize(x, scale, offset, border, mode, out_dtype):
+    n, h, w, c = x.shape
+    yn, yd, xn, xd = scale
+    oh = ((h - 1) * yn - offset[0] + border[0]) // yd + 1
+    ow = ((w - 1) * xn - offset[1] + border[1]) // xd + 1
+    out = np.zeros((n, oh, ow, c), out_dtype)
+    for oy in range(oh):
+        y = oy * yd + offset[0]
+        iy, ry = y // yn, y % yn  # Python's floor division and non-negative remainder
+        y0, y1 = max(iy, 0), min(iy + 1, h - 1)
+        for ox in range(ow):
+            xx = ox * xd + offset[1]
+            ix, rx = xx // xn, xx % xn
+            x0, x1 = max(ix, 0), min(ix + 1, w - 1)
+            if mode == 1:
+                out[:, oy, ox, :] = x[:, y1 if 2 * ry >= yn else y0, x1 if 2 * rx >= xn else x0, :]
+            else:
+                v = (x[:, y0, x0, :].astype(np.int64) * (yn - ry) * (xn - rx) + x[:, y0, x1, :].astype(np.int64) * (yn - ry) * rx +
+                     x[:, y1, x0, :].astype(np.int64) * ry * (xn - rx) + x[:, y1, x1, :].astype(np.int64) * ry * rx)
+                out[:, oy, ox, :] = v.astype(out_dtype)
+    return out

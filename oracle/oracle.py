@@ -279,3 +279,58 @@ def unary(op, x):
     out = np.zeros(x.shape, x.dtype)
     _check(lib().orc_unary(ctypes.byref(_t(x)), ctypes.byref(_t(out)), UNARY_OPS[op]))
     return out
+
+
+def argmax(x, axis):
+    out = np.zeros(x.shape[:axis] + x.shape[axis + 1:], np.int32)
+    _check(lib().orc_argmax(ctypes.byref(_t(x)), ctypes.byref(_t(out)), ctypes.c_uint32(axis)))
+    return out
+
+
+def gather(values, indices):
+    out = np.zeros((values.shape[0], indices.shape[1], values.shape[2]), values.dtype)
+    _check(lib().orc_gather(ctypes.byref(_t(values)), ctypes.byref(_t(indices)), ctypes.byref(_t(out))))
+    return out
+
+
+def scatter(values_in, indices, input_):
+    out = np.zeros(values_in.shape, values_in.dtype)
+    _check(lib().orc_scatter(ctypes.byref(_t(values_in)), ctypes.byref(_t(indices)), ctypes.byref(_t(input_)),
+                             ctypes.byref(_t(out))))
+    return out
+
+
+def reverse(x, axis):
+    out = np.zeros(x.shape, x.dtype)
+    _check(lib().orc_reverse(ctypes.byref(_t(x)), ctypes.byref(_t(out)), ctypes.c_uint32(axis)))
+    return out
+
+
+def tile(x, multiples):
+    out = np.zeros(tuple(d * m for d, m in zip(x.shape, multiples)), x.dtype)
+    _check(lib().orc_tile(ctypes.byref(_t(x)), ctypes.byref(_t(out))))
+    return out
+
+
+def resize(x, out_shape, out_dtype, scale, offset, border, mode):
+    """``scale`` = (y_n, y_d, x_n, x_d); ``mode`` 1 = NEAREST, 2 = BILINEAR.  ``border`` only enters the output
+    shape, which the caller supplies."""
+    out = np.zeros(out_shape, out_dtype)
+    _check(lib().orc_resize(ctypes.byref(_t(x)), ctypes.byref(_t(out)), _i32(scale), _i32(offset),
+                            ctypes.c_int32(mode)))
+    return out
+
+
+def transpose_conv2d(x, w, bias, out_shape, out_pad, stride, in_zp, w_zp):
+    out = np.zeros(out_shape, np.int64 if x.dtype == np.int16 else np.int32)
+    _check(lib().orc_transpose_conv2d(ctypes.byref(_t(x)), ctypes.byref(_t(w)), ctypes.byref(_t(bias)),
+                                      ctypes.byref(_t(out)), _i32(out_pad), _i32(stride), ctypes.c_int32(in_zp),
+                                      ctypes.c_int32(w_zp)))
+    return out
+
+
+def conv3d(x, w, bias, out_shape, pad, stride, dil, in_zp, w_zp):
+    out = np.zeros(out_shape, np.int64 if x.dtype == np.int16 else np.int32)
+    _check(lib().orc_conv3d(ctypes.byref(_t(x)), ctypes.byref(_t(w)), ctypes.byref(_t(bias)), ctypes.byref(_t(out)),
+                            _i32(pad), _i32(stride), _i32(dil), ctypes.c_int32(in_zp), ctypes.c_int32(w_zp)))
+    return out

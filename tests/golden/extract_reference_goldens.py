@@ -29,6 +29,13 @@ CASES = {
     "GraphConstantARM": ("ref", "int8", [5]),
     "HigherRankConstant": ("ref", "int8", [1, 3, 3, 1]),
     "Maximum": ("ref", "int32", [1, 2, 2, 2]),
+    "Conv3DLargeStridePadRegression": ("expectedValues", "int32", [1, 3, 2, 2, 3]),
+}
+
+# further arrays of a case that its inputs are built from: fixture name -> (gtest case, array, type, shape)
+EXTRA = {
+    "Conv3DLargeStridePadRegression.relevantWeights": ("Conv3DLargeStridePadRegression", "relevantWeights", "int8",
+                                                       [96]),
 }
 
 _WIDTH = {"int8": 8, "int32": 32, "int64": 64}
@@ -82,6 +89,14 @@ def main(ref_root: str) -> None:
             "dtype": dtype,
             "shape": shape if shape is not None else [len(values)],
             "values": values,
+        }
+    for name, (case, var, dtype, shape) in EXTRA.items():
+        body, line = _case_body(text, case)
+        goldens[name] = {
+            "source": "tests/vulkan.cpp:%d" % line,
+            "dtype": dtype,
+            "shape": shape,
+            "values": _numbers(_array_literal(body, var), dtype),
         }
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_goldens.json")
     with open(dst, "w", encoding="utf-8") as f:

@@ -69,6 +69,24 @@ def evaluate(graph, inputs, keep_all=False):
             r = oracle.negate(i[0], a["in_zp"], a["out_zp"])
         elif n == "SELECT":
             r = oracle.select(i[0], i[1], i[2])
+        elif n == "ARGMAX":
+            r = oracle.argmax(i[0], a["axis"])
+        elif n == "GATHER":
+            r = oracle.gather(i[0], i[1])
+        elif n == "SCATTER":
+            r = oracle.scatter(i[0], i[1], i[2])
+        elif n == "REVERSE":
+            r = oracle.reverse(i[0], a["axis"])
+        elif n == "TILE":
+            r = oracle.tile(i[0], a["multiples"])
+        elif n == "RESIZE":
+            r = oracle.resize(i[0], op.out.shape, op.out.dtype, a["scale"], a["offset"], a["border"], a["mode"])
+        elif n == "TRANSPOSE_CONV2D":
+            r = oracle.transpose_conv2d(i[0], i[1], i[2], op.out.shape, a["out_pad"], a["stride"], a["in_zp"],
+                                        a["w_zp"])
+        elif n == "CONV3D":
+            r = oracle.conv3d(i[0], i[1], i[2], op.out.shape, a["pad"], a["stride"], a["dilation"], a["in_zp"],
+                              a["w_zp"])
         else:
             raise NotImplementedError(n)
         assert tuple(r.shape) == tuple(op.out.shape), (n, r.shape, op.out.shape)

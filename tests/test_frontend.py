@@ -83,6 +83,14 @@ def test_reference_misc_fixtures(mlel, reference_root):
     assert p.op_names() == ["CONV2D"]
 
 
+def test_reference_conv3d_fixture(mlel, reference_root):
+    # tests/shader/conv3d_large_stride.spvasm: rank-5 tensors, six pads, OpConstantNull bias and zero point
+    w = np.zeros((3, 2, 2, 8192, 4), np.int8)
+    p = lower(mlel, fixture(reference_root, "conv3d_large_stride.spvasm"),
+              [(0, 0, 0, mlel.I8, (1, 3, 2, 2, 4)), (0, 1, 0, mlel.I32, (1, 3, 2, 2, 3))], [(0, w)])
+    assert p.op_names() == ["CONV3D"]
+
+
 def test_unbuilt_operator_is_feature_not_present(mlel, reference_root):
     with pytest.raises(mlel.MlelError) as e:
         lower(mlel, fixture(reference_root, "sin.spvasm"),

@@ -192,3 +192,104 @@ def test_mul_and_elementwise():
                                   np.pad(a, ((0, 0), (1, 2), (2, 0)), constant_values=-5))
     sh = r.integers(0, 8, a.shape, dtype=np.int8)
     np.testing.assert_array_equal(oracle.arithmetic_right_shift(a, sh, False), a >> sh)
+
+
+# ---- index-driven operators, TRANSPOSE_CONV2D, CONV3D, RESIZE ------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [np.int8, np.int16, np.int32])
+@pytest.mark.parametrize("axis", [0, 1, 2])
+def test_argmax(dtype, axis):
+    r = rng(axis)
+    info = np.iinfo(dtype)
+    x = r.integers(info.min, int(info.max) + 1, (5, 6, 7), dtype=np.int64).astype(dtype)
+    x[0, 0, :] = info.min  # all-lowest row: index 0
+    x[1, :, 1] = 5         # ties: the first one
+    np.testing.assert_array_equal(oracle.argmax(x, axis), np_ref.argmax(x, axis))
+
+
+@pytest.mark.parametrize("dtype", [np.int8, np.int16, np.int32, np.float32])
+def test_gather_scatter_reverse_tile(dtype):
+    r = rng(11)
+    values = r.integers(-100, 100, (3, 9, 5)).astype(dtype)
+    indices = np.stack([r.permutation(9)[:6] for _ in range(3)]).astype(np.int32)
+    np.testing.assert_array_equal(oracle.gather(values, indices), np_ref.gather(values, indices))
+    inp = r.integers(-100, 100, (3, 6, 5)).astype(dtype)
+    np.testing.assert_array_equal(oracle.scatter(values, indices, inp), np_ref.scatter(values, indices, inp))
+    dup = indices.copy()
+    dup[:, 3] = dup[:, 1]  # a repeated index: the first occurrence wins (scatter.comp:26-31)
+    np.testing.assert_array_equal(oracle.scatter(values, dup, inp), np_ref.scatter(values, dup, inp))
+    for axis in range(3):
+        np.testing.assert_array_equal(oracle.reverse(values, axis), np.flip(values, axis))
+    np.testing.assert_array_equal(oracle.tile(values, (2, 1, 3)), np.tile(values, (2, 1, 3)))
+
+
+def test_gather_out_of_range_index_reads_zero():
+    values = np.arange(1, 1 + 2 * 4 * 3, dtype=np.int8).reshape(2, 4, 3)
+    indices = np.array([[0, 4, 3], [7, 1, -1]], np.int32)  # 4, 7 and -1 (as unsigned) are out of range
+    out = oracle.gather(values, indices)
+    assert (out[0, 1] == 0).all() and (out[1, 0] == 0).all() and (out[1, 2] == 0).all()
+    np.testing.assert_array_equal(out[0, 0], values[0, 0])
+    np.testing.assert_array_equal(out[1, 1], values[1, 1])
+
+
+TCONV_CASES = [
+    # n, h, w, ic, oc, kh, kw, out_pad, stride, in_zp, w_zp
+    (1, 4, 5, 3, 4, 3, 3, (0, 0, 0, 0), (1, 1), -3, 0),
+    (2, 3, 3, 5, 2, 2, 3, (0, 0, 0, 0), (2, 2), 7, 1),
+    (1, 5, 4, 2, 3, 3, 2, (-1, 0, 0, -1), (2, 3), -128, -4),
+    (1, 2, 2, 1, 1, 1, 1, (1, 2, 0, 1), (3, 2), 0, 0),
+]
+
+
+@pytest.mark.parametrize("case", TCONV_CASES)
+def test_transpose_conv2d(case):
+    n, h, w, ic, oc, kh, kw, out_pad, stride, in_zp, w_zp = case
+    r = rng(sum(case[:7]))
+    x = r.integers(-128, 128, (n, h, w, ic), dtype=np.int8)
+    wt = r.integers(-128, 128, (oc, kh, kw, ic), dtype=np.int8)
+    bias = r.integers(-1000, 1000, (oc,), dtype=np.int32)
+    want = np_ref.transpose_conv2d(x, wt, bias, out_pad, stride, in_zp, w_zp)
+    got = oracle.transpose_conv2d(x, wt, bias, want.shape, list(out_pad), list(stride), in_zp, w_zp)
+    np.testing.assert_array_equal(got, want)
+
+
+CONV3D_CASES = [
+    # n, d, h, w, ic, oc, kd, kh, kw, pad, stride, dil, in_zp, w_zp
+    (1, 4, 5, 6, 3, 4, 2, 3, 3, (1, 0, 1, 1, 1, 1), (1, 1, 1), (1, 1, 1), -3, 0),
+    (2, 5, 5, 5, 2, 3, 3, 3, 3, (1, 1, 1, 1, 1, 1), (2, 2, 2), (1, 1, 1), 9, 2),
+    (1, 6, 7, 5, 4, 2, 2, 2, 2, (2, 2, 0, 3, 1, 0), (1, 2, 1), (2, 3, 2), -128, -5),
+]
+
+
+@pytest.mark.parametrize("case", CONV3D_CASES)
+def test_conv3d(case):
+    n, d, h, w, ic, oc, kd, kh, kw, pad, stride, dil, in_zp, w_zp = case
+    r = rng(sum(case[:9]))
+    x = r.integers(-128, 128, (n, d, h, w, ic), dtype=np.int8)
+    wt = r.integers(-128, 128, (oc, kd, kh, kw, ic), dtype=np.int8)
+    bias = r.integers(-1000, 1000, (oc,), dtype=np.int32)
+    want = np_ref.conv3d(x, wt, bias, pad, stride, dil, in_zp, w_zp)
+    got = oracle.conv3d(x, wt, bias, want.shape, list(pad), list(stride), list(dil), in_zp, w_zp)
+    np.testing.assert_array_equal(got, want)
+
+
+RESIZE_CASES = [
+    # scale (y_n, y_d, x_n, x_d), offset, border
+    ((2, 1, 2, 1), (0, 0), (0, 0)),
+    ((4, 2, 4, 2), (-1, -1), (1, 1)),      # half-pixel centres, 2x up
+    ((3, 2, 5, 3), (1, -2), (0, 2)),
+    ((1, 2, 1, 3), (0, 0), (0, 0)),        # down-scaling
+    ((16, 1, 16, 1), (-8, 7), (15, -7)),
+]
+
+
+@pytest.mark.parametrize("scale,offset,border", RESIZE_CASES)
+@pytest.mark.parametrize("in_dtype,out_dtype,mode", [(np.int8, np.int8, 1), (np.int8, np.int32, 2),
+                                                     (np.int16, np.int16, 1), (np.int16, np.int64, 2)])
+def test_resize(scale, offset, border, in_dtype, out_dtype, mode):
+    r = rng(scale[0] + mode)
+    info = np.iinfo(in_dtype)
+    x = r.integers(info.min, int(info.max) + 1, (2, 7, 9, 3), dtype=np.int64).astype(in_dtype)
+    want = np_ref.resize(x, scale, offset, border, mode, out_dtype)
+    got = oracle.resize(x, want.shape, out_dtype, scale, offset, border, mode)
+    np.testing.assert_array_equal(got, want)

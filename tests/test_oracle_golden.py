@@ -133,3 +133,21 @@ def test_maximum():
     a = np.arange(8, dtype=np.int32).reshape(1, 2, 2, 2)
     b = (np.arange(8, dtype=np.int64) * 4 - 16).astype(np.int32).reshape(1, 2, 2, 2)
     np.testing.assert_array_equal(oracle.binary("MAXIMUM", a, b), gold("Maximum"))
+
+
+def test_conv3d_large_stride_and_pad():
+    # tests/vulkan.cpp:1211-1293 + tests/shader/conv3d_large_stride.spvasm: input [1,3,2,2,4] all -128 with zero
+    # point 9; weights [3,2,2,8192,4] zero except the last two taps of the 8192-wide kernel, which hold
+    # `relevantWeights` in blocks of 8 per (oc, kd, kh); pad (1,0, 1,0, 8190,8192), stride (1,1,8192).
+    rel = gold("Conv3DLargeStridePadRegression.relevantWeights")
+    w = np.zeros((3, 2, 2, 8192, 4), np.int8)
+    for oc in range(3):
+        for kd in range(2):
+            for kh in range(2):
+                base = ((oc * 2 + kd) * 2 + kh) * 8
+                w[oc, kd, kh, 8190, :] = rel[base:base + 4]
+                w[oc, kd, kh, 8191, :] = rel[base + 4:base + 8]
+    x = np.full((1, 3, 2, 2, 4), -128, np.int8)
+    bias = np.zeros((1,), np.int32)
+    out = oracle.conv3d(x, w, bias, (1, 3, 2, 2, 3), [1, 0, 1, 0, 8190, 8192], [1, 1, 8192], [1, 1, 1], 9, 0)
+    np.testing.assert_array_equal(out, gold("Conv3DLargeStridePadRegression"))
