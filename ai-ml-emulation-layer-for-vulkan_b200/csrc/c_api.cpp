@@ -65,6 +65,7 @@ TView viewOf(const mlel_tensor &t) {
 
 const std::unordered_map<std::string, BinaryOp> kBinary = {
     {"ADD", BIN_ADD},
+    {"POW", BIN_POW},
     {"SUB", BIN_SUB},
     {"BITWISE_AND", BIN_BITWISE_AND},
     {"BITWISE_OR", BIN_BITWISE_OR},
@@ -82,7 +83,10 @@ const std::unordered_map<std::string, BinaryOp> kBinary = {
     {"GREATER_EQUAL", BIN_GREATER_EQUAL},
 };
 const std::unordered_map<std::string, UnaryOp> kUnary = {
-    {"ABS", UN_ABS}, {"BITWISE_NOT", UN_BITWISE_NOT}, {"CLZ", UN_CLZ}, {"LOGICAL_NOT", UN_LOGICAL_NOT}};
+    {"ABS", UN_ABS},     {"BITWISE_NOT", UN_BITWISE_NOT}, {"CLZ", UN_CLZ},         {"LOGICAL_NOT", UN_LOGICAL_NOT},
+    {"CEIL", UN_CEIL},   {"COS", UN_COS},                 {"ERF", UN_ERF},         {"EXP", UN_EXP},
+    {"FLOOR", UN_FLOOR}, {"LOG", UN_LOG},                 {"RECIPROCAL", UN_RECIPROCAL},
+    {"RSQRT", UN_RSQRT}, {"SIGMOID", UN_SIGMOID},         {"SIN", UN_SIN},         {"TANH", UN_TANH}};
 const std::unordered_map<std::string, ReduceOp> kReduce = {
     {"REDUCE_SUM", RED_SUM},         {"REDUCE_MAX", RED_MAX}, {"REDUCE_MIN", RED_MIN},
     {"REDUCE_PRODUCT", RED_PRODUCT}, {"REDUCE_ALL", RED_ALL}, {"REDUCE_ANY", RED_ANY}};

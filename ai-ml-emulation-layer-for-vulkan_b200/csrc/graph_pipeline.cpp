@@ -407,7 +407,7 @@ void GraphPipeline::makeBinary(BinaryOp opk, int32_t input1, int32_t input2, int
     need(a.rank() == b.rank() && a.rank() == out.rank(), debugName + ": rank mismatch");
     const bool f32ok = a.dtype == MLEL_F32 && (opk == BIN_ADD || opk == BIN_SUB || opk == BIN_MAXIMUM ||
                                                opk == BIN_MINIMUM || opk >= BIN_EQUAL);
-    need((isIntegerType(a.dtype) && a.dtype < MLEL_U8) || f32ok, debugName + ": input type not built");
+    need((isIntegerType(a.dtype) && a.dtype < MLEL_U8 && opk != BIN_POW) || f32ok, debugName + ": input type not built");
     if (a.dtype == MLEL_F32 && (opk == BIN_MAXIMUM || opk == BIN_MINIMUM)) {
         need(nanMode != 2, debugName + ": NaN-ignore mode is not built");
     }
@@ -417,8 +417,15 @@ void GraphPipeline::makeBinary(BinaryOp opk, int32_t input1, int32_t input2, int
 }
 
 void GraphPipeline::makeUnary(UnaryOp opk, int32_t input, int32_t output, const std::string &debugName) {
-    const auto &in = tensor(input);
-    need(isIntegerType(in.dtype) && in.dtype < MLEL_U8, debugName + ": only integer types are built");
+    const auto &in = tensor(input), &out = tensor(output);
+    if (opk >= UN_CEIL) {
+        need(in.dtype == MLEL_F32 && out.dtype == MLEL_F32, debugName + ": only fp32 is built");
+    } else if (in.dtype == MLEL_F32) {
+        need(opk == UN_ABS && out.dtype == MLEL_F32, debugName + ": not a floating-point operator");
+    } else {
+        need(isIntegerType(in.dtype) && in.dtype < MLEL_U8, debugName + ": input type not built");
+    }
+    need(in.rank() == out.rank(), debugName + ": rank mismatch");
     auto &op = pushOp(OP_UNARY, debugName, {input}, {output});
     op.sub = opk;
 }

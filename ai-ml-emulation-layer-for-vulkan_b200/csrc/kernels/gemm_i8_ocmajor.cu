@@ -30,6 +30,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "gemm_i8_tcgen05.hpp"
 #include "tcgen05_common.cuh"
@@ -41,21 +42,17 @@ using namespace tc;
 
 constexpr int kOcTile = 128; // output channels per tile (UMMA M)
 
-// Warp roles of this kernel: 0-7 epilogue (two per TMEM lane quarter; few enough warps that a thread may use
-// 128 registers and keep two 16-column accumulator slices in flight), 8 TMA producer, 9 MMA issuer and TMEM
-// owner, 10-11 pixel gather (implicit-GEMM variants only; two warps keep the CTA at 384 threads, so that
-// the epilogue's 168 registers per thread fit).
-constexpr int kOcEpiWarps = 8;
-constexpr int kOcTmaWarp = kOcEpiWarps;
-constexpr int kOcMmaWarp = kOcEpiWarps + 1;
-constexpr int kOcGatherWarp0 = kOcEpiWarps + 2;
-constexpr int kOcThreadsTma = (kOcEpiWarps + 2) * 32;
+// Warp roles of this kernel, EW = number of epilogue warps (8 or 12): 0..EW-1 epilogue (EW / 4 per TMEM lane
+// quarter, each with its own share of the tile's pixels), EW TMA producer, EW + 1 MMA issuer and TMEM owner,
+// EW + 2 and EW + 3 pixel gather (implicit-GEMM variants only).  The register file bounds the count: the
+// epilogue needs about 128 registers per thread, which a CTA of up to 512 threads (EW = 12 with both gather
+// warps) still gets; with 16 epilogue warps it spilled.
 constexpr int kOcGatherThreads = 64;
-constexpr int kOcThreadsGather = (kOcEpiWarps + 2) * 32 + kOcGatherThreads;
+constexpr int ocThreads(int ew, bool gather) { return (ew + 2) * 32 + (gather ? kOcGatherThreads : 0); }
 
 // Barrier among the epilogue warps only (named barrier 1).
-__device__ __forceinline__ void ocEpilogueSync() {
-    asm volatile("bar.sync 1, %0;" ::"r"(kOcEpiWarps * 32) : "memory");
+template <int EW> __device__ __forceinline__ void ocEpilogueSync() {
+    asm volatile("bar.sync 1, %0;" ::"r"(EW * 32) : "memory");
 }
 
 constexpr int kXGather = 0, kXTiled = 1, kXIm2col = 2;
@@ -183,16 +180,18 @@ __device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const Ep
 // The epilogue warps.  Warp w owns TMEM lanes 32 * (w & 3) .. +31 (output channels) and half of the tile's
 // pixels, which it walks in slices of 16 pixels; the tcgen05.ld of the next slice is in flight while the
 // current one is rescaled.
-template <int BNP, bool RESIDUAL>
+template <int BNP, int EW, bool RESIDUAL>
 __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const GemmI8Params &p, OcBarriers *bars,
                                                 uint8_t *clsTab, const int32_t *lutA, const int32_t *lutB, uint8_t *cdTiles,
                                                 uint32_t tmemBase, int warp, int lane, int64_t numTiles, int pTiles,
                                                 int cTiles) {
     const int quarter = warp & 3;
     const int part = warp >> 2;
-    constexpr int kColsPerWarp = BNP / (kOcEpiWarps / 4);
+    constexpr int kColsPerWarp = BNP / (EW / 4);
     constexpr int kSteps = kColsPerWarp / 16;
+    static_assert(EW % 4 == 0 && kColsPerWarp * (EW / 4) == BNP && kColsPerWarp % 16 == 0, "pixel shares of the warps");
     static_assert(kSteps % 2 == 0, "slices are processed in pairs");
+    static_assert(EW * 32 >= BNP, "one thread per pixel fills the class table");
     EpiConsts k{};
     if (RESIDUAL) {
         k.fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
@@ -255,7 +254,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 }
                 cls[threadIdx.x] = uint8_t(c);
             }
-            ocEpilogueSync();
+            ocEpilogueSync<EW>();
         }
         if (RESIDUAL && !mbarWait(&bars->cFull[buf], par, 6)) {
             break;
@@ -334,7 +333,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         // make the tile visible to the TMA unit, then one thread stores it (pixels and channels past the
         // tensor's end are clipped by the tensor map)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        ocEpilogueSync();
+        ocEpilogueSync<EW>();
         if (storer) {
             tmaStore3d(tmapD, cdTiles + buf * (BNP * 128), c0, m0, 0);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -348,8 +347,8 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
 // X_MODE: how the pixel operand arrives: kXGather = gathered from the NHWC input described by p, kXTiled = tmapX
 // is a plain matrix, kXIm2col = tmapX is an im2col map of the NHWC input.
 // RESIDUAL: the fused residual tail is present (tmapC describes the shortcut tensor).
-template <int BNP, int NSTAGE, int X_MODE, bool RESIDUAL>
-__global__ void __launch_bounds__(X_MODE != kXGather ? kOcThreadsTma : kOcThreadsGather, 1)
+template <int BNP, int NSTAGE, int EW, int X_MODE, bool RESIDUAL>
+__global__ void __launch_bounds__(ocThreads(EW, X_MODE == kXGather), 1)
 gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CUtensorMap tmapW,
               const __grid_constant__ CUtensorMap tmapC, const __grid_constant__ CUtensorMap tmapD, const GemmI8Params p) {
     extern __shared__ uint8_t rawSmem[];
@@ -367,6 +366,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     OcBarriers *bars = reinterpret_cast<OcBarriers *>(tapTab + kTapTabEntries);
 
     constexpr bool X_TMA = X_MODE != kXGather;
+    constexpr int kOcTmaWarp = EW, kOcMmaWarp = EW + 1, kOcGatherWarp0 = EW + 2;
     constexpr uint32_t kTmemCols = 2 * BNP <= 256 ? 256u : 512u; // two accumulators; allocations are powers of two
     constexpr int kXBoxRows = BNP % 128 == 0 ? 128 : 64;         // rows of one tiled load of the pixel operand
     const int warp = threadIdx.x >> 5;
@@ -391,7 +391,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         }
         for (int b = 0; b < 2; ++b) {
             mbarInit(&bars->accFull[b], 1u);
-            mbarInit(&bars->accEmpty[b], uint32_t(kOcEpiWarps));
+            mbarInit(&bars->accEmpty[b], uint32_t(EW));
             mbarInit(&bars->cFull[b], 1u);
             mbarInit(&bars->cdEmpty[b], 1u);
         }
@@ -553,7 +553,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         }
     } else {
         // ---------------- epilogue ----------------
-        epilogueOcMajor<BNP, RESIDUAL>(&tmapD, p, bars, clsTab, lutA, lutB, cdTiles, tmemBase, warp, lane, numTiles,
+        epilogueOcMajor<BNP, EW, RESIDUAL>(&tmapD, p, bars, clsTab, lutA, lutB, cdTiles, tmemBase, warp, lane, numTiles,
                                        pTiles, cTiles);
     }
 
@@ -570,13 +570,13 @@ struct OcMaps {
     CUtensorMap x, w, c, d;
 };
 
-template <int BNP, int NSTAGE, int X_MODE, bool RESIDUAL>
+template <int BNP, int NSTAGE, int EW, int X_MODE, bool RESIDUAL>
 int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes = size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * size_t(BNP) * 128 +
                                  2 * 256 * sizeof(int32_t) + 2 * BNP + kTapTabEntries * sizeof(int32_t) +
                                  sizeof(OcBarriers) + 1024;
     static_assert(smemBytes <= 232448, "shared memory per CTA");
-    auto kernel = gemmI8OcMajor<BNP, NSTAGE, X_MODE, RESIDUAL>;
+    auto kernel = gemmI8OcMajor<BNP, NSTAGE, EW, X_MODE, RESIDUAL>;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smemBytes)) != cudaSuccess) {
@@ -587,8 +587,8 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     }
     const int64_t tiles = int64_t((p.M + BNP - 1) / BNP) * ((p.N + kOcTile - 1) / kOcTile) * p.batches;
     const int grid = int(tiles < smCount() ? tiles : smCount());
-    const cudaError_t err = launchDependent(kernel, grid, X_MODE != kXGather ? kOcThreadsTma : kOcThreadsGather, smemBytes,
-                                            s, maps.x, maps.w, maps.c, maps.d, p);
+    const cudaError_t err = launchDependent(kernel, grid, ocThreads(EW, X_MODE == kXGather), smemBytes, s, maps.x, maps.w,
+                                            maps.c, maps.d, p);
     if (err != cudaSuccess) {
         setLastError(std::string("tcgen05 channel-major convolution launch: ") + cudaGetErrorString(err));
         return MLEL_ERROR_DEVICE;
@@ -596,21 +596,21 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     return MLEL_SUCCESS;
 }
 
-template <int BNP, int NSTAGE, int X_MODE>
+template <int BNP, int NSTAGE, int EW, int X_MODE>
 int launchOcMajorMode(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
-    return p.epi.hasResidual ? launchOcMajor<BNP, NSTAGE, X_MODE, true>(maps, p, s)
-                             : launchOcMajor<BNP, NSTAGE, X_MODE, false>(maps, p, s);
+    return p.epi.hasResidual ? launchOcMajor<BNP, NSTAGE, EW, X_MODE, true>(maps, p, s)
+                             : launchOcMajor<BNP, NSTAGE, EW, X_MODE, false>(maps, p, s);
 }
 
-template <int BNP, int NSTAGE>
+template <int BNP, int NSTAGE, int EW>
 int launchOcMajorShape(const OcMaps &maps, const GemmI8Params &p, int xMode, cudaStream_t s) {
     if (xMode == kXTiled) {
-        return launchOcMajorMode<BNP, NSTAGE, kXTiled>(maps, p, s);
+        return launchOcMajorMode<BNP, NSTAGE, EW, kXTiled>(maps, p, s);
     }
     if (xMode == kXIm2col) {
-        return launchOcMajorMode<BNP, NSTAGE, kXIm2col>(maps, p, s);
+        return launchOcMajorMode<BNP, NSTAGE, EW, kXIm2col>(maps, p, s);
     }
-    return launchOcMajorMode<BNP, NSTAGE, kXGather>(maps, p, s);
+    return launchOcMajorMode<BNP, NSTAGE, EW, kXGather>(maps, p, s);
 }
 
 } // namespace
@@ -651,6 +651,13 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
             width = w;
         }
     }
+    static const int forced = [] {
+        const char *e = std::getenv("MLEL_OC_TILE_PIXELS");
+        return e != nullptr ? std::atoi(e) : 0;
+    }();
+    if (forced == 128 || forced == 192 || forced == 256) {
+        width = forced;
+    }
     OcMaps maps{};
     const uint32_t boxPixels = uint32_t(width);
     int xMode = kXGather;
@@ -682,9 +689,10 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
         return MLEL_ERROR_DEVICE;
     }
     if (width == 256) {
-        return launchOcMajorShape<256, 3>(maps, p, xMode, s);
+        return launchOcMajorShape<256, 3, 8>(maps, p, xMode, s);
     }
-    return width == 192 ? launchOcMajorShape<192, 4>(maps, p, xMode, s) : launchOcMajorShape<128, 5>(maps, p, xMode, s);
+    return width == 192 ? launchOcMajorShape<192, 4, 12>(maps, p, xMode, s)
+                        : launchOcMajorShape<128, 5, 8>(maps, p, xMode, s);
 }
 
 int ocMajorErrorWord() { return tc::readErrorWord(); }

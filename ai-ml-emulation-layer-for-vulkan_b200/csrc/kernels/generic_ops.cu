@@ -388,6 +388,18 @@ __global__ void binaryGeneric(TView a, TView b, TView out, int32_t op) {
             case BIN_GREATER_EQUAL:
                 ri = x >= y, isBool = true;
                 break;
+            case BIN_POW:
+                // elementwise_binary.comp:71-89: a negative base takes an integral exponent only
+                if (x >= 0.0f) {
+                    r = powf(x, y);
+                } else if (fmodf(y, 2.0f) == 0.0f) {
+                    r = powf(-x, y);
+                } else if (fmodf(y, 1.0f) == 0.0f) {
+                    r = -powf(-x, y);
+                } else {
+                    r = nanf("");
+                }
+                break;
             default:
                 break;
             }
@@ -648,6 +660,92 @@ __global__ void unaryGeneric(TView in, TView out, int32_t op) {
     }
 }
 
+// ---- fp32 unary: elementwise_unary.comp:204-223 with the expressions of graph/compute_graph_op.cpp:2527-2945.
+// A NaN input passes through unchanged; LOG of a negative number is NaN (log_guarded, :161-163); TANH is +-1
+// beyond |x| = 10 and a four-term series below 0.2 (tanh_clamped, :139-159); SIN uses the odd series through
+// x^11 below 1e-3 (sin_hybrid, :166-192).  The transcendental functions themselves are CUDA's single-precision
+// ones (at most 2 ulp from the exact result, where the reference inherits its Vulkan device's precision).
+__device__ inline float unaryF32(int32_t op, float x) {
+    if (isnan(x)) {
+        return x;
+    }
+    switch (op) {
+    case UN_ABS:
+        return fabsf(x);
+    case UN_CEIL:
+        return ceilf(x);
+    case UN_FLOOR:
+        return floorf(x);
+    case UN_COS:
+        return cosf(x);
+    case UN_ERF:
+        return erff(x);
+    case UN_EXP:
+        return expf(x);
+    case UN_LOG:
+        return x < 0.0f ? nanf("") : logf(x);
+    case UN_RECIPROCAL:
+        return __fdiv_rn(1.0f, x);
+    case UN_RSQRT:
+        return rsqrtf(x);
+    case UN_SIGMOID:
+        return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x)));
+    case UN_SIN: {
+        if (fabsf(x) < 1.0e-3f) {
+            const float x2 = __fmul_rn(x, x);
+            float p = __fadd_rn(__fmul_rn(__fadd_rn(__fmul_rn(-1.0f / 39916800.0f, x2), 1.0f / 362880.0f), x2),
+                                -1.0f / 5040.0f);
+            p = __fadd_rn(__fmul_rn(p, x2), 1.0f / 120.0f);
+            p = __fadd_rn(__fmul_rn(p, x2), -1.0f / 6.0f);
+            p = __fadd_rn(__fmul_rn(p, x2), 1.0f);
+            return __fmul_rn(x, p);
+        }
+        return sinf(x);
+    }
+    case UN_TANH: {
+        if (x > 10.0f) {
+            return 1.0f;
+        }
+        if (x < -10.0f) {
+            return -1.0f;
+        }
+        if (fabsf(x) < 0.2f) {
+            const float x2 = __fmul_rn(x, x);
+            const float t = __fsub_rn(2.0f / 15.0f, __fmul_rn(17.0f / 315.0f, x2));
+            const float u = __fsub_rn(1.0f / 3.0f, __fmul_rn(x2, t));
+            return __fmul_rn(x, __fsub_rn(1.0f, __fmul_rn(x2, u)));
+        }
+        return tanhf(x);
+    }
+    default:
+        return x;
+    }
+}
+
+__global__ void unaryF32Generic(TView in, TView out, int32_t op) {
+    const int64_t total = numelOf(out);
+    GRID_STRIDE(e, total) {
+        uint32_t idx[kMaxRank];
+        unravel(out, uint32_t(e), idx);
+        const int64_t off = offsetOf(out, idx);
+        if (off >= 0) {
+            *reinterpret_cast<float *>(out.ptr + off) = unaryF32(op, loadF32(in, idx));
+        }
+    }
+}
+
+// Packed tensors: four elements per thread.
+__global__ void unaryF32Packed(const float4 *__restrict__ in, float4 *__restrict__ out, int64_t quads, int32_t op) {
+    GRID_STRIDE(e, quads) {
+        float4 v = in[e];
+        v.x = unaryF32(op, v.x);
+        v.y = unaryF32(op, v.y);
+        v.z = unaryF32(op, v.z);
+        v.w = unaryF32(op, v.w);
+        out[e] = v;
+    }
+}
+
 int finish(const char *what) {
     const cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) {
@@ -795,6 +893,27 @@ int genericSelect(const TView &c, const TView &a, const TView &b, const TView &o
 }
 
 int genericUnary(int32_t op, const TView &in, const TView &out, cudaStream_t s) {
+    if (in.dtype == MLEL_F32) {
+        const auto packed = [](const TView &t) {
+            int64_t st = 4;
+            for (int i = t.rank - 1; i >= 0; --i) {
+                if (t.strides[i] != st) {
+                    return false;
+                }
+                st *= t.dims[i];
+            }
+            return true;
+        };
+        const int64_t n = numelOf(out);
+        const bool same = in.rank == out.rank && numelOf(in) == n;
+        if (same && n % 4 == 0 && packed(in) && packed(out) && ((uintptr_t(in.ptr) | uintptr_t(out.ptr)) & 15u) == 0) {
+            unaryF32Packed<<<gridFor(n / 4), kThreads, 0, s>>>(reinterpret_cast<const float4 *>(in.ptr),
+                                                               reinterpret_cast<float4 *>(out.ptr), n / 4, op);
+        } else {
+            LAUNCH_1D(unaryF32Generic, n, s, in, out, op);
+        }
+        return finish("elementwise unary");
+    }
     LAUNCH_1D(unaryGeneric, numelOf(out), s, in, out, op);
     return finish("elementwise unary");
 }

@@ -82,10 +82,29 @@ enum BinaryOp : int32_t {
     BIN_EQUAL,
     BIN_GREATER,
     BIN_GREATER_EQUAL,
+    BIN_POW, // fp32 only
     BIN_COUNT
 };
 
-enum UnaryOp : int32_t { UN_ABS = 0, UN_BITWISE_NOT, UN_CLZ, UN_LOGICAL_NOT, UN_COUNT };
+enum UnaryOp : int32_t {
+    UN_ABS = 0,
+    UN_BITWISE_NOT,
+    UN_CLZ,
+    UN_LOGICAL_NOT,
+    // fp32 only from here on
+    UN_CEIL,
+    UN_COS,
+    UN_ERF,
+    UN_EXP,
+    UN_FLOOR,
+    UN_LOG,
+    UN_RECIPROCAL,
+    UN_RSQRT,
+    UN_SIGMOID,
+    UN_SIN,
+    UN_TANH,
+    UN_COUNT
+};
 enum ReduceOp : int32_t { RED_SUM = 0, RED_MAX, RED_MIN, RED_PRODUCT, RED_ALL, RED_ANY, RED_COUNT };
 
 // CONV2D / DEPTHWISE_CONV2D attributes (the push constants of conv2d.comp:26-33).

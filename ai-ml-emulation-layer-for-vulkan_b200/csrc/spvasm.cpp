@@ -102,25 +102,25 @@ const TosaEntry kTosaOps[] = {
     {"ABS", true},          {"ADD", true},           {"ARGMAX", true},
     {"ARITHMETIC_RIGHT_SHIFT", true},                {"AVG_POOL2D", true},
     {"BITWISE_AND", true},  {"BITWISE_NOT", true},   {"BITWISE_OR", true},
-    {"BITWISE_XOR", true},  {"CAST", true},          {"CEIL", false},
+    {"BITWISE_XOR", true},  {"CAST", true},          {"CEIL", true},
     {"CLAMP", true},        {"CLZ", true},           {"CONCAT", true},
-    {"CONV2D", true},       {"CONV3D", true},       {"COS", false},
+    {"CONV2D", true},       {"CONV3D", true},       {"COS", true},
     {"DEPTHWISE_CONV2D", true},                      {"EQUAL", true},
-    {"ERF", false},         {"EXP", false},          {"FFT2D", false},
-    {"FLOOR", false},       {"GATHER", true},       {"GREATER", true},
+    {"ERF", true},         {"EXP", true},          {"FFT2D", false},
+    {"FLOOR", true},       {"GATHER", true},       {"GREATER", true},
     {"GREATER_EQUAL", true},                         {"INTDIV", true},
-    {"LOG", false},         {"LOGICAL_AND", true},   {"LOGICAL_LEFT_SHIFT", true},
+    {"LOG", true},         {"LOGICAL_AND", true},   {"LOGICAL_LEFT_SHIFT", true},
     {"LOGICAL_NOT", true},  {"LOGICAL_OR", true},    {"LOGICAL_RIGHT_SHIFT", true},
     {"LOGICAL_XOR", true},  {"MATMUL", true},        {"MAX_POOL2D", true},
     {"MAXIMUM", true},      {"MINIMUM", true},       {"MUL", true},
-    {"NEGATE", true},       {"PAD", true},           {"POW", false},
-    {"RECIPROCAL", false},  {"REDUCE_ALL", true},    {"REDUCE_ANY", true},
+    {"NEGATE", true},       {"PAD", true},           {"POW", true},
+    {"RECIPROCAL", true},  {"REDUCE_ALL", true},    {"REDUCE_ANY", true},
     {"REDUCE_MAX", true},   {"REDUCE_MIN", true},    {"REDUCE_PRODUCT", true},
     {"REDUCE_SUM", true},   {"RESCALE", true},       {"RESHAPE", true},
     {"RESIZE", true},      {"REVERSE", true},      {"RFFT2D", false},
-    {"RSQRT", false},       {"SCATTER", true},      {"SELECT", true},
-    {"SIGMOID", false},     {"SIN", false},          {"SLICE", true},
-    {"SUB", true},          {"TABLE", true},         {"TANH", false},
+    {"RSQRT", true},       {"SCATTER", true},      {"SELECT", true},
+    {"SIGMOID", true},     {"SIN", true},          {"SLICE", true},
+    {"SUB", true},          {"TABLE", true},         {"TANH", true},
     {"TILE", true},        {"TRANSPOSE", true},     {"TRANSPOSE_CONV2D", true},
 };
 
@@ -141,12 +141,24 @@ const std::unordered_map<std::string, BinaryOp> kBinaryOps = {
     {"EQUAL", BIN_EQUAL},
     {"GREATER", BIN_GREATER},
     {"GREATER_EQUAL", BIN_GREATER_EQUAL},
+    {"POW", BIN_POW},
 };
 const std::unordered_map<std::string, UnaryOp> kUnaryOps = {
     {"ABS", UN_ABS},
     {"BITWISE_NOT", UN_BITWISE_NOT},
     {"CLZ", UN_CLZ},
     {"LOGICAL_NOT", UN_LOGICAL_NOT},
+    {"CEIL", UN_CEIL},
+    {"COS", UN_COS},
+    {"ERF", UN_ERF},
+    {"EXP", UN_EXP},
+    {"FLOOR", UN_FLOOR},
+    {"LOG", UN_LOG},
+    {"RECIPROCAL", UN_RECIPROCAL},
+    {"RSQRT", UN_RSQRT},
+    {"SIGMOID", UN_SIGMOID},
+    {"SIN", UN_SIN},
+    {"TANH", UN_TANH},
 };
 const std::unordered_map<std::string, ReduceOp> kReduceOps = {
     {"REDUCE_SUM", RED_SUM},         {"REDUCE_MAX", RED_MAX}, {"REDUCE_MIN", RED_MIN},

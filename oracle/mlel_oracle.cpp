@@ -774,6 +774,7 @@ enum orc_binary_op {
     ORC_EQUAL = 13,
     ORC_GREATER = 14,
     ORC_GREATER_EQUAL = 15,
+    ORC_POW = 16,
 };
 
 namespace {
@@ -824,6 +825,17 @@ int orc_binary(const orc_tensor *a, const orc_tensor *b, const orc_tensor *out, 
                 break;
             case ORC_GREATER_EQUAL:
                 ri = x >= y, isBool = true;
+                break;
+            case ORC_POW: // elementwise_binary.comp:71-89; the power itself in double, rounded once
+                if (x >= 0.0f) {
+                    r = float(std::pow(double(x), double(y)));
+                } else if (std::fmod(y, 2.0f) == 0.0f) {
+                    r = float(std::pow(double(-x), double(y)));
+                } else if (std::fmod(y, 1.0f) == 0.0f) {
+                    r = float(-std::pow(double(-x), double(y)));
+                } else {
+                    r = std::numeric_limits<float>::quiet_NaN();
+                }
                 break;
             default:
                 break;
@@ -1451,6 +1463,87 @@ int orc_conv3d(const orc_tensor *in, const orc_tensor *w, const orc_tensor *bias
         conv3dImpl<int64_t>(*in, *w, *bias, *out, pad, stride, dil, inZp, wZp);
     } else {
         return -1;
+    }
+    return 0;
+}
+
+
+enum orc_unary_f32_op {
+    ORC_F_ABS = 0,
+    ORC_F_CEIL = 4,
+    ORC_F_COS = 5,
+    ORC_F_ERF = 6,
+    ORC_F_EXP = 7,
+    ORC_F_FLOOR = 8,
+    ORC_F_LOG = 9,
+    ORC_F_RECIPROCAL = 10,
+    ORC_F_RSQRT = 11,
+    ORC_F_SIGMOID = 12,
+    ORC_F_SIN = 13,
+    ORC_F_TANH = 14,
+};
+
+// graph/shaders/graph_op/tosa/elementwise_unary.comp:204-223 for fp32 tensors, with the operator expressions of
+// graph/compute_graph_op.cpp:2527-2945.  The reference evaluates the transcendental functions with its Vulkan
+// device's single-precision builtins, whose last bits differ between devices; this restatement evaluates them
+// in double precision and rounds once, i.e. it gives the value every conforming implementation approximates.
+// The shader's special cases are kept: NaN passes through, LOG of a negative number is NaN, TANH saturates
+// beyond |x| = 10.  Comparisons against this function use a tolerance stated in the tests.
+int orc_unary_f32(const orc_tensor *in, const orc_tensor *out, int op) {
+    if (in->dtype != ORC_F32 || out->dtype != ORC_F32) {
+        return -1;
+    }
+    const int64_t total = numel(*out);
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank];
+        unravel(*out, uint32_t(e), idx);
+        const float xf = rd<float>(*in, idx);
+        const double x = double(xf);
+        float r = xf;
+        if (!std::isnan(xf)) {
+            switch (op) {
+            case ORC_F_ABS:
+                r = std::fabs(xf);
+                break;
+            case ORC_F_CEIL:
+                r = std::ceil(xf);
+                break;
+            case ORC_F_FLOOR:
+                r = std::floor(xf);
+                break;
+            case ORC_F_COS:
+                r = float(std::cos(x));
+                break;
+            case ORC_F_ERF:
+                r = float(std::erf(x));
+                break;
+            case ORC_F_EXP:
+                r = float(std::exp(x));
+                break;
+            case ORC_F_LOG:
+                r = xf < 0.0f ? std::numeric_limits<float>::quiet_NaN() : float(std::log(x));
+                break;
+            case ORC_F_RECIPROCAL:
+                r = 1.0f / xf;
+                break;
+            case ORC_F_RSQRT:
+                r = float(1.0 / std::sqrt(x));
+                break;
+            case ORC_F_SIGMOID:
+                r = float(1.0 / (1.0 + std::exp(-x)));
+                break;
+            case ORC_F_SIN:
+                r = float(std::sin(x));
+                break;
+            case ORC_F_TANH:
+                r = xf > 10.0f ? 1.0f : (xf < -10.0f ? -1.0f : float(std::tanh(x)));
+                break;
+            default:
+                break;
+            }
+        }
+        wr<float>(*out, idx, r);
     }
     return 0;
 }

@@ -35,11 +35,13 @@ _NP2DT = {
 BINARY_OPS = {
     "ADD": 0, "SUB": 1, "BITWISE_AND": 2, "BITWISE_OR": 3, "BITWISE_XOR": 4, "LOGICAL_AND": 5,
     "LOGICAL_OR": 6, "LOGICAL_XOR": 7, "LOGICAL_LEFT_SHIFT": 8, "LOGICAL_RIGHT_SHIFT": 9,
-    "INTDIV": 10, "MAXIMUM": 11, "MINIMUM": 12, "EQUAL": 13, "GREATER": 14, "GREATER_EQUAL": 15,
+    "INTDIV": 10, "MAXIMUM": 11, "MINIMUM": 12, "EQUAL": 13, "GREATER": 14, "GREATER_EQUAL": 15, "POW": 16,
 }
 REDUCE_OPS = {"REDUCE_SUM": 0, "REDUCE_MAX": 1, "REDUCE_MIN": 2, "REDUCE_PRODUCT": 3, "REDUCE_ALL": 4,
               "REDUCE_ANY": 5}
-UNARY_OPS = {"ABS": 0, "BITWISE_NOT": 1, "CLZ": 2, "LOGICAL_NOT": 3}
+UNARY_OPS = {"ABS": 0, "BITWISE_NOT": 1, "CLZ": 2, "LOGICAL_NOT": 3, "CEIL": 4, "COS": 5, "ERF": 6, "EXP": 7,
+             "FLOOR": 8, "LOG": 9, "RECIPROCAL": 10, "RSQRT": 11, "SIGMOID": 12, "SIN": 13, "TANH": 14}
+FLOAT_UNARY_OPS = frozenset(UNARY_OPS) - {"BITWISE_NOT", "CLZ", "LOGICAL_NOT"}
 
 
 class _Tensor(ctypes.Structure):
@@ -277,6 +279,10 @@ def select(cond, a, b):
 
 def unary(op, x):
     out = np.zeros(x.shape, x.dtype)
+    if x.dtype == np.float32:
+        assert op in FLOAT_UNARY_OPS
+        _check(lib().orc_unary_f32(ctypes.byref(_t(x)), ctypes.byref(_t(out)), UNARY_OPS[op]))
+        return out
     _check(lib().orc_unary(ctypes.byref(_t(x)), ctypes.byref(_t(out)), UNARY_OPS[op]))
     return out
 

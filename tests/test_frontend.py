@@ -91,11 +91,17 @@ def test_reference_conv3d_fixture(mlel, reference_root):
     assert p.op_names() == ["CONV3D"]
 
 
+def test_reference_sin_fixture(mlel, reference_root):
+    p = lower(mlel, fixture(reference_root, "sin.spvasm"), [(0, 0, 0, mlel.F32, (1,)), (0, 1, 0, mlel.F32, (1,))])
+    assert p.op_names() == ["SIN"]
+
+
 def test_unbuilt_operator_is_feature_not_present(mlel, reference_root):
     with pytest.raises(mlel.MlelError) as e:
-        lower(mlel, fixture(reference_root, "sin.spvasm"),
-              [(0, 0, 0, mlel.F32, (1, 16, 16, 16)), (0, 1, 0, mlel.F32, (1, 16, 16, 16))])
+        lower(mlel, fixture(reference_root, "fft2d.spvasm"),
+              [(0, b, 0, mlel.F32, (1, 4, 4096)) for b in range(4)])
     assert e.value.status == -8
+    assert "FFT2D" in str(e.value)
 
 
 def test_unregistered_instruction_set_is_rejected(mlel):

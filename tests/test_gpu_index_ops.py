@@ -181,3 +181,83 @@ def test_golden_conv3d_large_stride_and_pad(mlel):
     from mlel_b200.runtime import GraphRunner
     got = GraphRunner(g).run([np.full((1, 3, 2, 2, 4), -128, np.int8)])[0]
     np.testing.assert_array_equal(got, gold("Conv3DLargeStridePadRegression"))
+
+
+# ---- fp32 unary operators and POW ------------------------------------------------------------------------------
+# The reference evaluates these with its Vulkan device's single-precision builtins and pins one value only (SIN,
+# to 7.7e-8 absolute).  The oracle evaluates in double precision and rounds once; the CUDA single-precision
+# functions are documented to stay within 2 ulp of that (4 ulp for POW), which is the tolerance used here.
+# CEIL, FLOOR, ABS and RECIPROCAL are exact.
+
+def ulp_distance(a, b):
+    ia = a.view(np.int32).astype(np.int64)
+    ib = b.view(np.int32).astype(np.int64)
+    ia = np.where(ia < 0, -(ia & 0x7FFFFFFF), ia)  # sign-magnitude -> a monotone integer line
+    ib = np.where(ib < 0, -(ib & 0x7FFFFFFF), ib)
+    return np.abs(ia - ib)
+
+
+def check_float(got, want, ulps, what):
+    assert got.dtype == np.float32 and got.shape == want.shape
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got), nan), what
+    inf = np.isinf(want)
+    assert np.array_equal(got[inf], want[inf]), what
+    ok = ~(nan | inf)
+    # results that round to a denormal may be flushed; compare those absolutely
+    tiny = ok & (np.abs(want) < 1e-37)
+    assert np.all(np.abs(got[tiny] - want[tiny]) < 1e-37), what
+    rest = ok & ~tiny
+    dist = ulp_distance(got[rest], want[rest])
+    assert dist.size == 0 or dist.max() <= ulps, f"{what}: {dist.max()} ulp"
+
+
+FLOAT_UNARY = [
+    # operator, input range, ulps allowed
+    ("ABS", (-100, 100), 0), ("CEIL", (-100, 100), 0), ("FLOOR", (-100, 100), 0), ("RECIPROCAL", (-100, 100), 0),
+    ("COS", (-20, 20), 2), ("SIN", (-20, 20), 2), ("EXP", (-80, 80), 2), ("LOG", (-1, 1000), 2),
+    ("RSQRT", (0, 1000), 2), ("SIGMOID", (-30, 30), 3), ("TANH", (-12, 12), 2), ("ERF", (-5, 5), 2),
+]
+
+
+@pytest.mark.parametrize("name,span,ulps", FLOAT_UNARY)
+@pytest.mark.parametrize("shape", [(4, 33, 64), (3, 5, 7)])  # packed, four at a time / generic indexing
+def test_float_unary(mlel, name, span, ulps, shape):
+    from mlel_b200.runtime import GraphRunner
+    r = rng(len(name))
+    data = r.uniform(span[0], span[1], shape).astype(np.float32)
+    flat = data.reshape(-1)
+    special = [0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 1e-4, -1e-4, 0.15, -0.15, 10.5, -10.5, 1e-30, 0.5, 4.5]
+    flat[:len(special)] = special
+    g = GraphBuilder()
+    x = g.input(np.float32, shape)
+    g.output(g.unary(name, x))
+    want = evaluate(g, [data])[0]
+    got = GraphRunner(g).run([data])[0]
+    check_float(got, want, ulps, name)
+
+
+def test_sin_known_answer_through_the_front_end(mlel):
+    # the reference's own pin: tests/vulkan.cpp:1795-1841
+    from mlel_b200.runtime import GraphRunner
+    g = GraphBuilder()
+    x = g.input(np.float32, (1,))
+    g.output(g.unary("SIN", x))
+    got = GraphRunner(g).run([np.array([0.000111731846], np.float32)])[0]
+    assert abs(float(got[0]) - 0.00011173184588586903) <= 7.715463482888105e-08
+
+
+def test_pow(mlel):
+    from mlel_b200.runtime import GraphRunner
+    r = rng(77)
+    base = r.uniform(-8, 8, (6, 40, 32)).astype(np.float32)
+    expo = r.uniform(-4, 4, (6, 40, 32)).astype(np.float32)
+    expo[:, ::2, :] = np.round(expo[:, ::2, :])  # integral exponents: negative bases are defined
+    base[0, 0, :4] = [0.0, -0.0, 2.0, -2.0]
+    expo[0, 0, :4] = [0.0, 3.0, 0.5, 0.5]
+    g = GraphBuilder()
+    a, b = g.input(np.float32, base.shape), g.input(np.float32, expo.shape)
+    g.output(g.binary("POW", a, b))
+    want = evaluate(g, [base, expo])[0]
+    got = GraphRunner(g).run([base, expo])[0]
+    check_float(got, want, 4, "POW")

@@ -151,3 +151,10 @@ def test_conv3d_large_stride_and_pad():
     bias = np.zeros((1,), np.int32)
     out = oracle.conv3d(x, w, bias, (1, 3, 2, 2, 3), [1, 0, 1, 0, 8190, 8192], [1, 1, 8192], [1, 1, 1], 9, 0)
     np.testing.assert_array_equal(out, gold("Conv3DLargeStridePadRegression"))
+
+
+def test_sin_known_answer():
+    # tests/vulkan.cpp:1795-1841: sin(0.000111731846f) must lie within 7.715463482888105e-08 of 0.00011173184588586903
+    out = oracle.unary("SIN", np.array([0.000111731846], np.float32))
+    assert out.dtype == np.float32
+    assert abs(float(out[0]) - 0.00011173184588586903) <= 7.715463482888105e-08
