@@ -427,6 +427,22 @@ int mlel_make_select(mlel_pipeline *p, mlel_tensor_id input1, mlel_tensor_id inp
     });
 }
 
+int mlel_make_fft2d(mlel_pipeline *p, mlel_tensor_id input_real, mlel_tensor_id input_imag, mlel_tensor_id output_real,
+                    mlel_tensor_id output_imag, int inverse, const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeFft2D(input_real, input_imag, output_real, output_imag, inverse != 0, nameOr(debug_name, "FFT2D"));
+        return MLEL_SUCCESS;
+    });
+}
+
+int mlel_make_rfft2d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output_real, mlel_tensor_id output_imag,
+                     const char *debug_name) {
+    return guarded([&] {
+        p->impl->makeRfft2D(input, output_real, output_imag, nameOr(debug_name, "RFFT2D"));
+        return MLEL_SUCCESS;
+    });
+}
+
 int mlel_make_argmax(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, uint32_t axis, uint32_t nan_mode,
                      const char *debug_name) {
     return guarded([&] {

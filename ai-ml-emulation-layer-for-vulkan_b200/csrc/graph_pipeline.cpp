@@ -23,6 +23,8 @@
 //   NEGATE                    i[0] inputZeroPoint i[1] outputZeroPoint
 //   SELECT                    in = {condition, input2, input3}
 //   ARGMAX                    i[0] axis i[1] nanMode
+//   FFT2D                     i[0] inverse     in = {real, imag}  out = {real, imag}
+//   RFFT2D                    in = {input}     out = {real, imag}
 //   GATHER                    in = {values, indices}
 //   SCATTER                   in = {values_in, indices, input}
 //   REVERSE                   i[0] axis
@@ -32,6 +34,8 @@
 //   CONV3D                    i[0..5] pad i[6..8] stride i[9..11] dilation i[12] inputZeroPoint
 //                             i[13] weightZeroPoint i[14] accType      in = {input, weights, biases}
 #include "graph_pipeline.hpp"
+#include "kernels/device_common.cuh"
+#include "kernels/gemm_i8_tcgen05.hpp"
 
 #include <cuda_runtime.h>
 
@@ -513,6 +517,26 @@ void GraphPipeline::makeSelect(int32_t input1, int32_t input2, int32_t input3, i
     pushOp(OP_SELECT, debugName, {input1, input2, input3}, {output});
 }
 
+void GraphPipeline::makeFft2D(int32_t inputReal, int32_t inputImag, int32_t outputReal, int32_t outputImag,
+                              bool inverse, const std::string &debugName) {
+    const auto &re = tensor(inputReal), &im = tensor(inputImag), &ore = tensor(outputReal), &oim = tensor(outputImag);
+    need(re.dtype == MLEL_F32 && im.dtype == MLEL_F32 && ore.dtype == MLEL_F32 && oim.dtype == MLEL_F32,
+         debugName + ": only fp32 is built");
+    need(re.rank() == 3 && im.dims == re.dims && ore.dims == re.dims && oim.dims == re.dims,
+         debugName + ": all four tensors must have the same [N, H, W] shape");
+    auto &op = pushOp(OP_FFT2D, debugName, {inputReal, inputImag}, {outputReal, outputImag});
+    op.i[0] = inverse;
+}
+
+void GraphPipeline::makeRfft2D(int32_t input, int32_t outputReal, int32_t outputImag, const std::string &debugName) {
+    const auto &in = tensor(input), &ore = tensor(outputReal), &oim = tensor(outputImag);
+    need(in.dtype == MLEL_F32 && ore.dtype == MLEL_F32 && oim.dtype == MLEL_F32, debugName + ": only fp32 is built");
+    need(in.rank() == 3 && ore.rank() == 3 && oim.dims == ore.dims && ore.dims[0] == in.dims[0] &&
+             ore.dims[1] == in.dims[1] && ore.dims[2] == in.dims[2] / 2 + 1,
+         debugName + ": outputs must have the shape [N, H, W / 2 + 1]");
+    pushOp(OP_RFFT2D, debugName, {input}, {outputReal, outputImag});
+}
+
 void GraphPipeline::makeArgmax(int32_t input, int32_t output, uint32_t axis, uint32_t nanMode,
                                const std::string &debugName) {
     const auto &in = tensor(input), &out = tensor(output);
@@ -911,6 +935,56 @@ int32_t GraphPipeline::addScratchTensor(int32_t dtype, const std::vector<int64_t
 //
 // MATMUL (plain or fused) with a constant second input [Nb, C, W] and zero point 0 on it: the input
 // is transposed once to K-major [Nb][W][C]; corr[b][w] = -zeroPoint1 * sum_c B[b, c, w].
+// The residual tail of a fused convolution maps (main-stage int8 value m, shortcut int8 value s) to one output
+// byte: RESCALE_out(RESCALE_a(m) + RESCALE_b(s)) with the clamps of each stage.  All three RESCALEs are
+// per-tensor with constant parameters, so the whole map is 256 x 256 bytes, computed here once with the
+// reference's own arithmetic (rescale.comp:27-72 via rescaleValue) and looked up by the kernel's epilogue.
+void GraphPipeline::buildResidualTable(OpDesc &op) {
+    struct Stage {
+        int32_t mult, shift, inZp, outZp, lo, hi;
+        bool doubleRound;
+    };
+    const auto stageOf = [&](const FusedRescale &f, Stage &st) {
+        if (f.multTensor < 0 || f.shiftTensor < 0 || f.attr.perChannel) {
+            return false;
+        }
+        const TensorDescriptor &m = tensor(f.multTensor), &sh = tensor(f.shiftTensor);
+        if (m.cls != TensorClass::Constant || sh.cls != TensorClass::Constant || m.dtype != MLEL_I32 ||
+            elemSize(sh.dtype) != 1 || m.hostData.size() < 4 || sh.hostData.empty() || !f.attr.scale32) {
+            return false;
+        }
+        std::memcpy(&st.mult, m.hostData.data(), 4);
+        const int32_t shift = int32_t(int8_t(sh.hostData[0]));
+        st.shift = shift < 0 ? 0 : (shift > 62 ? 62 : shift);
+        st.inZp = int32_t(wrapTo(f.inDtype, f.attr.inZp));
+        st.outZp = int32_t(wrapTo(f.outDtype, f.attr.outZp));
+        st.lo = f.lo, st.hi = f.hi;
+        st.doubleRound = f.attr.doubleRound != 0;
+        return true;
+    };
+    Stage a{}, b{}, o{};
+    if (!stageOf(op.epi.a, a) || !stageOf(op.epi.b, b) || !stageOf(op.epi.out, o)) {
+        return;
+    }
+    const auto run = [](const Stage &st, int64_t v) {
+        return rescaleValue(v, st.inZp, st.mult, st.shift, st.doubleRound, st.outZp, st.lo, st.hi);
+    };
+    int32_t fromMain[256], fromShortcut[256];
+    for (int v = -128; v < 128; ++v) {
+        fromMain[v + 128] = run(a, v);
+        fromShortcut[uint8_t(int8_t(v))] = run(b, v);
+    }
+    constexpr int kRow = GemmI8Params::kResidualRowBytes; // rows are padded: see gemm_i8_ocmajor.cu
+    std::vector<uint8_t> table(size_t(256 * kRow), 0);
+    for (int m = 0; m < 256; ++m) {
+        for (int sc = 0; sc < 256; ++sc) {
+            const int32_t sum = int32_t(uint32_t(fromMain[m]) + uint32_t(fromShortcut[sc]));
+            table[size_t(m * kRow + sc)] = uint8_t(run(o, sum));
+        }
+    }
+    op.aux[3] = addDerivedConstant(MLEL_U8, {int64_t(table.size())}, table.data());
+}
+
 void GraphPipeline::prepareTensorCore() {
     for (auto &op : exec_) {
         const bool conv = op.kind == OP_CONV2D || op.kind == OP_FUSED_CONV2D;
@@ -1040,6 +1114,9 @@ void GraphPipeline::prepareTensorCore() {
                 op.auxi[3] = int32_t(rBest * colMasks.size() + cBest);
             }
             op.tc = 1;
+            if (!padChannels && op.kind == OP_FUSED_CONV2D && op.epi.hasResidual) {
+                buildResidualTable(op);
+            }
             if (padChannels) {
                 // geometry of the padded copy: rows and columns that any window can touch
                 const int64_t Hp = std::max<int64_t>(H + padTop, (OH - 1) * sy + (KH - 1) * dy + 1);

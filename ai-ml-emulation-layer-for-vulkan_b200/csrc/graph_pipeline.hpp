@@ -108,6 +108,9 @@ class GraphPipeline {
     void makeNegate(int32_t input, int32_t output, int32_t inputZeroPoint, int32_t outputZeroPoint,
                     const std::string &debugName);
     void makeSelect(int32_t input1, int32_t input2, int32_t input3, int32_t output, const std::string &debugName);
+    void makeFft2D(int32_t inputReal, int32_t inputImag, int32_t outputReal, int32_t outputImag, bool inverse,
+                   const std::string &debugName);
+    void makeRfft2D(int32_t input, int32_t outputReal, int32_t outputImag, const std::string &debugName);
     void makeArgmax(int32_t input, int32_t output, uint32_t axis, uint32_t nanMode, const std::string &debugName);
     void makeGather(int32_t values, int32_t indices, int32_t output, const std::string &debugName);
     void makeScatter(int32_t input, int32_t values, int32_t indices, int32_t output, const std::string &debugName);
@@ -147,6 +150,7 @@ class GraphPipeline {
     void requireMutable() const;
     void fuse();
     void prepareTensorCore();
+    void buildResidualTable(OpDesc &op);
     int32_t addDerivedConstant(int32_t dtype, const std::vector<int64_t> &dims, const void *data);
     int32_t addScratchTensor(int32_t dtype, const std::vector<int64_t> &dims);
 

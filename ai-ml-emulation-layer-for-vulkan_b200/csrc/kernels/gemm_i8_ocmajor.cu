@@ -48,6 +48,13 @@ constexpr int kOcTile = 128; // output channels per tile (UMMA M)
 // epilogue needs about 128 registers per thread, which a CTA of up to 512 threads (EW = 12 with both gather
 // warps) still gets; with 16 epilogue warps it spilled.
 constexpr int kOcGatherThreads = 64;
+// The residual table: 256 rows (main-stage value) of 256 bytes (shortcut byte), rows 260 bytes apart.  With rows
+// of 256 bytes the shared-memory bank of an entry would depend on the shortcut byte alone, and the lanes of a
+// warp -- whose shortcut values are often equal (activations clamped by a ReLU) while their main-stage values
+// differ -- would all hit one bank; the extra word per row spreads them over the banks.
+constexpr int kResidualRowBytes = GemmI8Params::kResidualRowBytes;
+constexpr int kResidualTableBytes = 256 * kResidualRowBytes;
+static_assert(kResidualTableBytes % 16 == 0, "bulk copies move multiples of 16 bytes");
 constexpr int ocThreads(int ew, bool gather) { return (ew + 2) * 32 + (gather ? kOcGatherThreads : 0); }
 
 // Barrier among the epilogue warps only (named barrier 1).
@@ -58,12 +65,13 @@ template <int EW> __device__ __forceinline__ void ocEpilogueSync() {
 constexpr int kXGather = 0, kXTiled = 1, kXIm2col = 2;
 
 struct __align__(8) OcBarriers {
-    uint64_t full[8];
-    uint64_t empty[8];
+    uint64_t full[6];
+    uint64_t empty[6];
     uint64_t accFull[2];
     uint64_t accEmpty[2];
     uint64_t cFull[2];  // the shortcut bytes of a tile have landed in its C/D tile
     uint64_t cdEmpty[2]; // the store of a C/D tile has finished reading it: the tile may be loaded again
+    uint64_t tabFull;    // the residual table has landed in shared memory
     uint32_t tmemBase;
     uint32_t pad;
 };
@@ -71,6 +79,15 @@ struct __align__(8) OcBarriers {
 struct OcTile {
     int c0, m0, batch;
 };
+
+// Plain (untiled) bulk copy global -> shared, completing on an mbarrier; both addresses and the size are
+// multiples of 16 bytes.
+__device__ __forceinline__ void bulkLoad(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smemAddr(dst)),
+                 "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smemAddr(bar))
+                 : "memory");
+}
 
 __device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, const void *src, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
@@ -97,11 +114,6 @@ __device__ __forceinline__ uint32_t ldsU8(uint32_t addr) {
     asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ int32_t ldsS32(uint32_t addr) {
-    int32_t v;
-    asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
 __device__ __forceinline__ void stsU8(uint32_t addr, int32_t v) {
     asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
@@ -113,20 +125,20 @@ __device__ __forceinline__ int32_t finishHigh(int32_t high, int32_t s2, int32_t 
 
 // Constants of one epilogue thread (one output channel) and of the per-tensor output stage.
 struct EpiConsts {
-    FastRescale fm, fo;
-    uint64_t rnM, rnO;      // rounding constants for inputs below the zero point
-    uint32_t bumpM, bumpO;  // what the constants for inputs at or above it add: 2^31 with double rounding, else 0
+    FastRescale fm;
+    uint64_t rnM;    // rounding constant for inputs below the zero point
+    uint32_t bumpM;  // what the constant for inputs at or above it adds: 2^31 with double rounding, else 0
     int32_t corr0;
-    int32_t outZpMain, loMain, hiMain, outZpOut, loOut, hiOut;
-    bool fast; // every shift involved is at least 32: see scaleHigh
+    int32_t outZpMain, loMain, hiMain;
+    bool fast; // the shift is at least 32: see scaleHigh
 };
 
 // 16 pixels of one channel: accumulator slice -> bytes in the C/D tile (column `cd`, rows 128 bytes apart).
 // All shortcut bytes are read before the first result is written: the compiler must assume that a byte store
 // may alias any later load, and 16 load-compute-store chains in a row would run one after the other.
 template <bool RESIDUAL, bool FAST>
-__device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t lutA128,
-                                                 uint32_t lutB, uint32_t cd) {
+__device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t tab128,
+                                                 uint32_t cd) {
     constexpr int CH = 8; // pixels per group: enough independent chains, few enough live registers
 #pragma unroll
     for (int g = 0; g < 16; g += CH) {
@@ -148,14 +160,11 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
             }
         }
         if (RESIDUAL) {
+            // the whole tail -- both input RESCALEs, the ADD, the output RESCALE and its clamp -- is one byte
+            // of the table, addressed by the main stage's value and the shortcut byte
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-                const int32_t sum = int32_t(uint32_t(ldsS32(lutA128 + uint32_t(r[j] * 4))) + uint32_t(ldsS32(lutB + sc[j] * 4u)));
-                if (FAST) {
-                    r[j] = finishHigh(scaleHigh(sum, k.fo.mult, k.fo.zpIn, k.rnO, k.bumpO), k.fo.s2, k.outZpOut, k.loOut, k.hiOut);
-                } else {
-                    r[j] = fastRescale(k.fo, sum, k.outZpOut, k.loOut, k.hiOut);
-                }
+                r[j] = int32_t(ldsU8(tab128 + sc[j] + uint32_t(r[j] * kResidualRowBytes)));
             }
         }
 #pragma unroll
@@ -165,15 +174,14 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
     }
 }
 
-// cd: shared address of this thread's column of the C/D tile at the slice's first pixel; lutA128 / lutB: shared
-// addresses of the residual tables (the first one at the entry of value 0).
+// cd: shared address of this thread's column of the C/D tile at the slice's first pixel; tab128: shared address
+// of the residual table's row for main-stage value 0.
 template <bool RESIDUAL>
-__device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t lutA128,
-                                             uint32_t lutB, uint32_t cd) {
+__device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t tab128, uint32_t cd) {
     if (k.fast) {
-        rescaleSliceImpl<RESIDUAL, true>(acc, k, lutA128, lutB, cd);
+        rescaleSliceImpl<RESIDUAL, true>(acc, k, tab128, cd);
     } else {
-        rescaleSliceImpl<RESIDUAL, false>(acc, k, lutA128, lutB, cd);
+        rescaleSliceImpl<RESIDUAL, false>(acc, k, tab128, cd);
     }
 }
 
@@ -182,7 +190,7 @@ __device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const Ep
 // current one is rescaled.
 template <int BNP, int EW, bool RESIDUAL>
 __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const GemmI8Params &p, OcBarriers *bars,
-                                                uint8_t *clsTab, const int32_t *lutA, const int32_t *lutB, uint8_t *cdTiles,
+                                                uint8_t *clsTab, const uint8_t *resTab, uint8_t *cdTiles,
                                                 uint32_t tmemBase, int warp, int lane, int64_t numTiles, int pTiles,
                                                 int cTiles) {
     const int quarter = warp & 3;
@@ -193,16 +201,9 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     static_assert(kSteps % 2 == 0, "slices are processed in pairs");
     static_assert(EW * 32 >= BNP, "one thread per pixel fills the class table");
     EpiConsts k{};
-    if (RESIDUAL) {
-        k.fo = makeFastRescale(__ldg(p.epi.out.mult), int32_t(__ldg(p.epi.out.shift)), p.epi.out.inZp,
-                               p.epi.out.doubleRound != 0);
-        k.rnO = (uint64_t(k.fo.rnHi) << 32) | k.fo.rnLo;
-        k.bumpO = uint32_t(((uint64_t(k.fo.rpHi) << 32) | k.fo.rpLo) - k.rnO);
-    }
     k.outZpMain = p.epi.main.outZp, k.loMain = p.epi.main.lo, k.hiMain = p.epi.main.hi;
-    k.outZpOut = p.epi.out.outZp, k.loOut = p.epi.out.lo, k.hiOut = p.epi.out.hi;
-    const uint32_t lutA128 = smemAddr(lutA + 128); // indexed by the signed int8 value of the main stage
-    const uint32_t lutBAddr = smemAddr(lutB);
+    const uint32_t tab128 = smemAddr(resTab) + 128u * uint32_t(kResidualRowBytes); // row of main-stage value 0
+    bool tableReady = !RESIDUAL;
     int curC0 = -1, curBatch = -1;
     const bool hasClasses = p.rowClass != nullptr;
     const int baseClass = p.baseClass;
@@ -237,7 +238,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             k.rnM = (uint64_t(k.fm.rnHi) << 32) | k.fm.rnLo;
             k.bumpM = uint32_t(((uint64_t(k.fm.rpHi) << 32) | k.fm.rpLo) - k.rnM);
             k.corr0 = ocValid ? __ldg(corrBatch + int64_t(baseClass) * p.N + oc) : 0;
-            k.fast = __all_sync(0xffffffffu, k.fm.s1 == 32) && (!RESIDUAL || k.fo.s1 == 32);
+            k.fast = __all_sync(0xffffffffu, k.fm.s1 == 32);
             curC0 = c0;
             curBatch = batch;
         }
@@ -255,6 +256,12 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 cls[threadIdx.x] = uint8_t(c);
             }
             ocEpilogueSync<EW>();
+        }
+        if (!tableReady) {
+            if (!mbarWait(&bars->tabFull, 0u, 7)) {
+                break;
+            }
+            tableReady = true;
         }
         if (RESIDUAL && !mbarWait(&bars->cFull[buf], par, 6)) {
             break;
@@ -281,8 +288,10 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             __syncwarp();
         };
         uint32_t accA[16], accB[16];
-        if (RESIDUAL) {
-            // the residual tail needs the registers a second slice in flight would take
+        // With 12 epilogue warps a thread has 128 registers, which the residual variant's shortcut bytes and a
+        // second accumulator slice in flight do not both fit into.
+        constexpr bool kOneSliceAtATime = RESIDUAL && EW > 8;
+        if (kOneSliceAtATime) {
 #pragma unroll 1
             for (int st = 0; st < kSteps; ++st) {
                 tmemLoad16(taddr + uint32_t(16 * st), accA);
@@ -297,7 +306,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                     borderFix(accA, part * kColsPerWarp + 16 * st);
                 }
                 if (warpLive) {
-                    rescaleSlice<RESIDUAL>(accA, k, lutA128, lutBAddr, cd + uint32_t((16 * st) * 128));
+                    rescaleSlice<RESIDUAL>(accA, k, tab128, cd + uint32_t((16 * st) * 128));
                 }
             }
         } else {
@@ -310,7 +319,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 borderFix(accA, part * kColsPerWarp + 16 * st);
             }
             if (warpLive) {
-                rescaleSlice<RESIDUAL>(accA, k, lutA128, lutBAddr, cd + uint32_t((16 * st) * 128));
+                rescaleSlice<RESIDUAL>(accA, k, tab128, cd + uint32_t((16 * st) * 128));
             }
             tmemWait16(accB);
             if (st + 2 < kSteps) {
@@ -326,7 +335,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 borderFix(accB, part * kColsPerWarp + 16 * (st + 1));
             }
             if (warpLive) {
-                rescaleSlice<RESIDUAL>(accB, k, lutA128, lutBAddr, cd + uint32_t((16 * (st + 1)) * 128));
+                rescaleSlice<RESIDUAL>(accB, k, tab128, cd + uint32_t((16 * (st + 1)) * 128));
             }
         }
         }
@@ -359,13 +368,13 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     uint8_t *tilesW = smem;
     uint8_t *tilesX = smem + NSTAGE * kTileW;
     uint8_t *cdTiles = smem + NSTAGE * (kTileW + kTileX);
-    int32_t *lutA = reinterpret_cast<int32_t *>(cdTiles + 2 * kTileCd);
-    int32_t *lutB = lutA + 256;
-    uint8_t *clsTab = reinterpret_cast<uint8_t *>(lutB + 256);
+    uint8_t *resTab = cdTiles + 2 * kTileCd; // the residual tail as a table (RESIDUAL only)
+    uint8_t *clsTab = resTab + (RESIDUAL ? kResidualTableBytes : 0);
     int32_t *tapTab = reinterpret_cast<int32_t *>(clsTab + 2 * BNP);
     OcBarriers *bars = reinterpret_cast<OcBarriers *>(tapTab + kTapTabEntries);
 
     constexpr bool X_TMA = X_MODE != kXGather;
+    static_assert(NSTAGE <= 6, "OcBarriers holds six stages");
     constexpr int kOcTmaWarp = EW, kOcMmaWarp = EW + 1, kOcGatherWarp0 = EW + 2;
     constexpr uint32_t kTmemCols = 2 * BNP <= 256 ? 256u : 512u; // two accumulators; allocations are powers of two
     constexpr int kXBoxRows = BNP % 128 == 0 ? 128 : 64;         // rows of one tiled load of the pixel operand
@@ -395,6 +404,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
             mbarInit(&bars->cFull[b], 1u);
             mbarInit(&bars->cdEmpty[b], 1u);
         }
+        mbarInit(&bars->tabFull, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == kOcMmaWarp) {
@@ -406,21 +416,16 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     if (!X_TMA && warp >= kOcGatherWarp0) {
         fillTapTable(p, tapTab, kOcGatherWarp0 * 32, kOcGatherThreads);
     }
-    if (RESIDUAL && threadIdx.x < 256) {
-        // the two int8 -> int32 RESCALEs of the residual tail, tabulated over their whole domain
-        const int32_t v = int32_t(threadIdx.x) - 128;
-        const FastRescale fa =
-            makeFastRescale(__ldg(p.epi.a.mult), int32_t(__ldg(p.epi.a.shift)), p.epi.a.inZp, p.epi.a.doubleRound != 0);
-        const FastRescale fb =
-            makeFastRescale(__ldg(p.epi.b.mult), int32_t(__ldg(p.epi.b.shift)), p.epi.b.inZp, p.epi.b.doubleRound != 0);
-        lutA[threadIdx.x] = fastRescale(fa, v, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
-        // the shortcut table is indexed by the raw byte: entry u belongs to the value int8(u)
-        lutB[uint8_t(v)] = fastRescale(fb, v, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmemBase = bars->tmemBase;
+    if (RESIDUAL && warp == kOcTmaWarp && lane == 0) {
+        // the table is a constant of the pipeline, not an activation: it may be fetched before the previous
+        // kernel of the stream has finished
+        mbarArriveExpectTx(&bars->tabFull, uint32_t(kResidualTableBytes));
+        bulkLoad(resTab, p.residualTable, uint32_t(kResidualTableBytes), &bars->tabFull);
+    }
     gridDependencySync(); // from here on activations are read and written
 
     if (warp == kOcTmaWarp) {
@@ -553,8 +558,8 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         }
     } else {
         // ---------------- epilogue ----------------
-        epilogueOcMajor<BNP, EW, RESIDUAL>(&tmapD, p, bars, clsTab, lutA, lutB, cdTiles, tmemBase, warp, lane, numTiles,
-                                       pTiles, cTiles);
+        epilogueOcMajor<BNP, EW, RESIDUAL>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase, warp, lane, numTiles, pTiles,
+                                           cTiles);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -573,8 +578,8 @@ struct OcMaps {
 template <int BNP, int NSTAGE, int EW, int X_MODE, bool RESIDUAL>
 int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     constexpr size_t smemBytes = size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * size_t(BNP) * 128 +
-                                 2 * 256 * sizeof(int32_t) + 2 * BNP + kTapTabEntries * sizeof(int32_t) +
-                                 sizeof(OcBarriers) + 1024;
+                                 (RESIDUAL ? size_t(kResidualTableBytes) : 0) + 2 * BNP +
+                                 kTapTabEntries * sizeof(int32_t) + sizeof(OcBarriers) + 1024;
     static_assert(smemBytes <= 232448, "shared memory per CTA");
     auto kernel = gemmI8OcMajor<BNP, NSTAGE, EW, X_MODE, RESIDUAL>;
     static bool configured = false;
@@ -596,9 +601,12 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
     return MLEL_SUCCESS;
 }
 
+// The residual table takes 64 KB of shared memory: the variants with a residual tail run with fewer stages
+// (they are 1x1 convolutions of one to four K blocks, and the pipeline runs across tile boundaries).
 template <int BNP, int NSTAGE, int EW, int X_MODE>
 int launchOcMajorMode(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
-    return p.epi.hasResidual ? launchOcMajor<BNP, NSTAGE, EW, X_MODE, true>(maps, p, s)
+    constexpr int kStagesResidual = BNP == 128 ? 4 : 2;
+    return p.epi.hasResidual ? launchOcMajor<BNP, kStagesResidual, EW, X_MODE, true>(maps, p, s)
                              : launchOcMajor<BNP, NSTAGE, EW, X_MODE, false>(maps, p, s);
 }
 
@@ -629,9 +637,10 @@ bool gemmI8OcMajorApplies(const GemmI8Problem &q) {
                                   (p.IC == 16 || p.IC == 32 || p.IC == 64 || p.IC % 128 == 0))) {
         return false;
     }
-    // the residual tables are indexed by the int8 value of the main stage
-    return !p.epi.hasResidual || (p.epi.main.lo >= -128 && p.epi.main.hi <= 127 &&
-                                  (reinterpret_cast<uintptr_t>(p.epi.shortcut) & 15u) == 0);
+    // the residual table is indexed by the int8 value of the main stage and the shortcut byte
+    return !p.epi.hasResidual ||
+           (p.residualTable != nullptr && (reinterpret_cast<uintptr_t>(p.residualTable) & 15u) == 0 &&
+            p.epi.main.lo >= -128 && p.epi.main.hi <= 127 && (reinterpret_cast<uintptr_t>(p.epi.shortcut) & 15u) == 0);
 }
 
 int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {

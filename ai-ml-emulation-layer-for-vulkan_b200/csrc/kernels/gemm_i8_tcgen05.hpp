@@ -36,6 +36,12 @@ struct GemmI8Params {
     int32_t *out32;
     int8_t *out8;
     DevEpilogue epi;
+    // Fused residual tail as one table: residualTable[(m + 128) * kResidualRowBytes + s] is the output byte for
+    // main-stage value m (int8) and raw shortcut byte s, i.e. RESCALE_out(RESCALE_a(m) + RESCALE_b(int8(s)))
+    // with its clamp.  256 rows of kResidualRowBytes bytes (the last four of a row unused), 16-byte aligned, or
+    // null when the node has none.
+    static constexpr int kResidualRowBytes = 260;
+    const uint8_t *residualTable;
 };
 
 struct GemmI8Problem {

@@ -1,5 +1,5 @@
 // Index-driven and less common TOSA operators: ARGMAX, GATHER, SCATTER, REVERSE, TILE, RESIZE (integer
-// modes), TRANSPOSE_CONV2D and CONV3D.  As in generic_ops.cu one thread produces one output element, the
+// modes), TRANSPOSE_CONV2D, CONV3D, FFT2D and RFFT2D.  As in generic_ops.cu one thread produces one output element, the
 // work split of the reference's 1-D compute shaders, with any rank, stride and integer element type the
 // reference accepts; element moves copy raw bits, so they carry float types too.
 //
@@ -255,6 +255,54 @@ template <typename ACC> __global__ void conv3dKernel(TView in, TView w, TView bi
     }
 }
 
+// ---- FFT2D: fft2d.comp:17-55, RFFT2D: rfft2d.comp:12-71 ------------------------------------------------------
+// Both shaders evaluate the defining double sum directly, one output element per invocation; so does this
+// kernel.  The angle of a term is 2*pi*(iy*oy/H + ix*ox/W); its numerator is reduced modulo H*W in integers (as
+// rfft2d.comp:44-49 does) so that sine and cosine are taken of an angle in [0, 2*pi) at full precision, and the
+// sums are kept in double (fft2d.comp accumulates in DOUBLE; rfft2d.comp compensates its float sum).  RFFT2D
+// writes an exact zero for the imaginary part of the four self-conjugate bins (rfft2d.comp:33-38).
+// imag.ptr == nullptr: real input, outputs hold W / 2 + 1 columns.
+__global__ void fft2dKernel(TView real, TView imag, TView outReal, TView outImag, int32_t inverse) {
+    const int64_t total = numelOf(outReal);
+    const uint32_t H = real.dims[1], W = real.dims[2];
+    const bool realOnly = imag.ptr == nullptr;
+    GRID_STRIDE(e, total) {
+        uint32_t idx[kMaxRank] = {0, 0, 0, 0, 0, 0};
+        unravel(outReal, uint32_t(e), idx);
+        const uint32_t n = idx[0], oy = idx[1], ox = idx[2];
+        const bool skipImag = realOnly && (oy == 0 || oy == H / 2) && (ox == 0 || ox == W / 2);
+        double sumRe = 0.0, sumIm = 0.0;
+        for (uint32_t iy = 0; iy < H; ++iy) {
+            const uint64_t rowTerm = uint64_t((uint64_t(iy) * oy) % H) * W;
+            for (uint32_t ix = 0; ix < W; ++ix) {
+                const uint32_t ci[3] = {n, iy, ix};
+                const int64_t ro = offsetOf(real, ci);
+                const double re = ro < 0 ? 0.0 : double(*reinterpret_cast<const float *>(real.ptr + ro));
+                double im = 0.0;
+                if (!realOnly) {
+                    const int64_t io = offsetOf(imag, ci);
+                    im = io < 0 ? 0.0 : double(*reinterpret_cast<const float *>(imag.ptr + io));
+                }
+                const uint64_t num = (rowTerm + uint64_t((uint64_t(ix) * ox) % W) * H) % (uint64_t(H) * W);
+                double sn, cs;
+                sincospi(2.0 * double(num) / double(uint64_t(H) * W), &sn, &cs);
+                if (inverse) {
+                    sn = -sn;
+                }
+                sumRe += re * cs + im * sn;
+                sumIm += im * cs - re * sn;
+            }
+        }
+        const int64_t orOff = offsetOf(outReal, idx), oiOff = offsetOf(outImag, idx);
+        if (orOff >= 0) {
+            *reinterpret_cast<float *>(outReal.ptr + orOff) = float(sumRe);
+        }
+        if (oiOff >= 0) {
+            *reinterpret_cast<float *>(outImag.ptr + oiOff) = skipImag ? 0.0f : float(sumIm);
+        }
+    }
+}
+
 } // namespace
 
 #define LAUNCH_1D(kernel, total, stream, ...) kernel<<<gridFor(total), kThreads, 0, stream>>>(__VA_ARGS__)
@@ -318,6 +366,22 @@ int transposeConv2d(const TView &in, const TView &w, const TView &bias, const TV
         return MLEL_ERROR_FEATURE_NOT_PRESENT;
     }
     return finish("TRANSPOSE_CONV2D");
+}
+
+int fft2d(const TView *real, const TView *imag, const TView &outReal, const TView &outImag, bool inverse,
+          cudaStream_t s) {
+    if (uint64_t(real->dims[1]) * real->dims[2] >= (uint64_t(1) << 31)) {
+        setLastError("FFT2D: more than 2^31 points per image");
+        return MLEL_ERROR_FEATURE_NOT_PRESENT;
+    }
+    TView none{};
+    // one output element per thread, each a sum over the whole image: small blocks spread the work over all SMs
+    const int64_t total = numelOf(outReal);
+    const int threads = 64;
+    const int64_t blocks = (total + threads - 1) / threads;
+    fft2dKernel<<<unsigned(blocks < 1 ? 1 : (blocks > 148 * 64 ? 148 * 64 : blocks)), threads, 0, s>>>(
+        *real, imag != nullptr ? *imag : none, outReal, outImag, inverse ? 1 : 0);
+    return finish(imag != nullptr ? "FFT2D" : "RFFT2D");
 }
 
 int conv3d(const TView &in, const TView &w, const TView &bias, const TView &out, const Conv3dAttr &a, cudaStream_t s) {

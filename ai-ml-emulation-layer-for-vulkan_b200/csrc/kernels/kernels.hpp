@@ -106,6 +106,9 @@ int indexTile(const TView &in, const TView &out, cudaStream_t s);
 int resizeInteger(const TView &in, const TView &out, const ResizeAttr &a, cudaStream_t s);
 int transposeConv2d(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
                     cudaStream_t s);
+// FFT2D (imag != nullptr) and RFFT2D (imag == nullptr, outputs hold W / 2 + 1 columns): direct sums in double
+int fft2d(const TView *real, const TView *imag, const TView &outReal, const TView &outImag, bool inverse,
+          cudaStream_t s);
 int conv3d(const TView &in, const TView &w, const TView &bias, const TView &out, const Conv3dAttr &a, cudaStream_t s);
 
 } // namespace mlel

@@ -115,6 +115,9 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     if (op.kind == OP_FUSED_CONV2D) {
         p.out8 = reinterpret_cast<int8_t *>(out.ptr);
         p.epi = devEpilogue(op.epi, T);
+        if (op.epi.hasResidual && op.tc == 1 && op.aux[3] >= 0) {
+            p.residualTable = reinterpret_cast<const uint8_t *>(T[op.aux[3]].ptr);
+        }
     } else {
         p.out32 = reinterpret_cast<int32_t *>(out.ptr);
     }
@@ -327,6 +330,10 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         return genericNegate(in(0), out, op.i[0], op.i[1], s);
     case OP_SELECT:
         return genericSelect(in(0), in(1), in(2), out, s);
+    case OP_FFT2D:
+        return fft2d(&in(0), &in(1), out, T[op.out[1]], op.i[0] != 0, s);
+    case OP_RFFT2D:
+        return fft2d(&in(0), nullptr, out, T[op.out[1]], false, s);
     case OP_ARGMAX:
         return indexArgmax(in(0), out, uint32_t(op.i[0]), s);
     case OP_GATHER:

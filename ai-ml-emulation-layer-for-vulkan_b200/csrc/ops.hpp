@@ -57,6 +57,8 @@ enum OpKind : int32_t {
     OP_RESIZE,
     OP_TRANSPOSE_CONV2D,
     OP_CONV3D,
+    OP_FFT2D,  // in = {real, imag}, out = {real, imag}
+    OP_RFFT2D, // in = {real},       out = {real, imag}
     // Produced only by the fusion pass:
     OP_FUSED_CONV2D,     // CONV2D -> RESCALE [-> CLAMP] [-> residual RESCALE/ADD/RESCALE [-> CLAMP]]
     OP_FUSED_DEPTHWISE,  // DEPTHWISE_CONV2D -> RESCALE [-> CLAMP]
@@ -187,6 +189,7 @@ struct OpDesc {
     // Tensor-core path (set by GraphPipeline::prepareTensorCore when the node qualifies):
     //   CONV2D kinds: aux[0] correction table int32 [classes][OC], aux[1] row classes u8 [OH],
     //                 aux[2] column classes u8 [OW]; auxi[0] = number of column classes, auxi[1] = classes
+    //                 with a fused residual tail and tc == 1: aux[3] = the tail as a table of 256 x 256 bytes
     //   MATMUL kinds with a constant second input: aux[0] correction int32 [batches][W],
     //                 aux[3] the second input transposed to [batches][W][C]
     //   CONV2D kinds with tc == 2 (channel count not a multiple of 16): scratch = session tensor

@@ -106,7 +106,7 @@ const TosaEntry kTosaOps[] = {
     {"CLAMP", true},        {"CLZ", true},           {"CONCAT", true},
     {"CONV2D", true},       {"CONV3D", true},       {"COS", true},
     {"DEPTHWISE_CONV2D", true},                      {"EQUAL", true},
-    {"ERF", true},         {"EXP", true},          {"FFT2D", false},
+    {"ERF", true},         {"EXP", true},          {"FFT2D", true},
     {"FLOOR", true},       {"GATHER", true},       {"GREATER", true},
     {"GREATER_EQUAL", true},                         {"INTDIV", true},
     {"LOG", true},         {"LOGICAL_AND", true},   {"LOGICAL_LEFT_SHIFT", true},
@@ -117,7 +117,7 @@ const TosaEntry kTosaOps[] = {
     {"RECIPROCAL", true},  {"REDUCE_ALL", true},    {"REDUCE_ANY", true},
     {"REDUCE_MAX", true},   {"REDUCE_MIN", true},    {"REDUCE_PRODUCT", true},
     {"REDUCE_SUM", true},   {"RESCALE", true},       {"RESHAPE", true},
-    {"RESIZE", true},      {"REVERSE", true},      {"RFFT2D", false},
+    {"RESIZE", true},      {"REVERSE", true},      {"RFFT2D", true},
     {"RSQRT", true},       {"SCATTER", true},      {"SELECT", true},
     {"SIGMOID", true},     {"SIN", true},          {"SLICE", true},
     {"SUB", true},          {"TABLE", true},         {"TANH", true},
@@ -503,7 +503,13 @@ class Lowering {
         } else if (isCompositeOp(inst.op) || isReplicateOp(inst.op) || inst.op == "OpConstantNull") {
             t = makeCompositeTensor(id);
         } else if (inst.op == "OpExtInst") {
-            const Inst &tt = tensorType(idOf(inst.operands.at(0)));
+            // a two-result instruction (FFT2D, RFFT2D) returns a struct: member `arrayIndex` is this tensor's type
+            const Inst &resultType = def(idOf(inst.operands.at(0)));
+            const bool isStruct = resultType.op == "OpTypeStruct";
+            if (isStruct && arrayIndex >= resultType.operands.size()) {
+                fail("result %" + id + " has no member " + std::to_string(arrayIndex));
+            }
+            const Inst &tt = tensorType(isStruct ? idOf(resultType.operands.at(arrayIndex)) : idOf(inst.operands.at(0)));
             const auto dims = tensorShape(tt);
             if (dims.empty()) {
                 fail("intermediate tensor %" + id + " has an unshaped type");
@@ -750,6 +756,15 @@ class Lowering {
         } else if (name == "SELECT") {
             argc(3);
             p.makeSelect(getTensor(a[0]), getTensor(a[1]), getTensor(a[2]), result(), name);
+        } else if (name == "FFT2D") {
+            argc(4); // inverse localBound inputReal inputImag
+            (void)boolConstant(a[1]);
+            p.makeFft2D(getTensor(a[2]), getTensor(a[3]), getTensor(inst.result, 0), getTensor(inst.result, 1),
+                        boolConstant(a[0]), name);
+        } else if (name == "RFFT2D") {
+            argc(2); // localBound input
+            (void)boolConstant(a[0]);
+            p.makeRfft2D(getTensor(a[1]), getTensor(inst.result, 0), getTensor(inst.result, 1), name);
         } else if (name == "ARGMAX") {
             argc(3); // axis nanMode input
             p.makeArgmax(getTensor(a[2]), result(), constScalar(a[0]).as<uint32_t>(),

@@ -47,6 +47,7 @@ class OpRecord:
     attrs: dict
     out: Value
     operands: list = field(default_factory=list)  # emitted operand ids in TOSA order
+    more_outs: list = field(default_factory=list)  # further results of a multi-result instruction (FFT2D, RFFT2D)
 
 
 class GraphBuilder:
@@ -378,6 +379,22 @@ class GraphBuilder:
                           dict(pad=list(pad), stride=list(stride), dilation=list(dilation), in_zp=in_zp, w_zp=w_zp),
                           acc, (n, od, oh, ow, oc))
 
+    def _emit2(self, name, operands, inputs, attrs, out_dtype, out_shape):
+        """An instruction with two results of one type, returned as a struct and taken apart by
+        OpCompositeExtract."""
+        first = self._emit(name, operands, inputs, attrs, out_dtype, out_shape)
+        second = Value(self._fresh("v"), np.dtype(out_dtype), tuple(int(d) for d in out_shape), "op")
+        self.ops[-1].more_outs.append(second)
+        return first, second
+
+    def fft2d(self, real, imag, inverse):
+        ops = [self._bool(inverse)[1:], self._bool(False)[1:], real.name, imag.name]
+        return self._emit2("FFT2D", ops, [real, imag], dict(inverse=bool(inverse)), np.float32, real.shape)
+
+    def rfft2d(self, x):
+        shape = x.shape[:2] + (x.shape[2] // 2 + 1,)
+        return self._emit2("RFFT2D", [self._bool(False)[1:], x.name], [x], {}, np.float32, shape)
+
     # ------------------------------------------------------------------ emission
     def spvasm(self) -> str:
         head = [
@@ -413,6 +430,14 @@ class GraphBuilder:
         for op in self.ops:
             t = self._tensor_type(op.out.dtype, op.out.shape)
             args = " ".join("%" + o for o in op.operands)
+            if op.more_outs:
+                outs = [op.out] + op.more_outs
+                types = [self._tensor_type(v.dtype, v.shape) for v in outs]
+                st = self._decl("struct_" + "_".join(x[1:] for x in types), "OpTypeStruct " + " ".join(types))
+                body.append(f"%{op.out.name}_all = OpExtInst {st} %tosa {op.name} {args}")
+                for k, (v, vt) in enumerate(zip(outs, types)):
+                    body.append(f"%{v.name} = OpCompositeExtract {vt} %{op.out.name}_all {k}")
+                continue
             body.append(f"%{op.out.name} = OpExtInst {t} %tosa {op.name} {args}")
         for k, (v, _, _) in enumerate(self.outputs):
             body.append(f"OpGraphSetOutputARM %{v.name} {self._u32(k)}")

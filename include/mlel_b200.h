@@ -181,6 +181,12 @@ int mlel_make_negate(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id outp
                      int32_t output_zp, const char *debug_name);
 int mlel_make_select(mlel_pipeline *p, mlel_tensor_id input1, mlel_tensor_id input2, mlel_tensor_id input3,
                      mlel_tensor_id output, const char *debug_name);
+/* makeFft2D / makeRfft2D: fp32 tensors [N, H, W]; RFFT2D's outputs are [N, H, W / 2 + 1].  The inverse transform
+ * is not scaled (fft2d.comp). */
+int mlel_make_fft2d(mlel_pipeline *p, mlel_tensor_id input_real, mlel_tensor_id input_imag, mlel_tensor_id output_real,
+                    mlel_tensor_id output_imag, int inverse, const char *debug_name);
+int mlel_make_rfft2d(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output_real, mlel_tensor_id output_imag,
+                     const char *debug_name);
 /* makeArgmax: the output has the input's shape without `axis` and holds int32 indices. */
 int mlel_make_argmax(mlel_pipeline *p, mlel_tensor_id input, mlel_tensor_id output, uint32_t axis, uint32_t nan_mode,
                      const char *debug_name);

@@ -1548,4 +1548,39 @@ int orc_unary_f32(const orc_tensor *in, const orc_tensor *out, int op) {
     return 0;
 }
 
+
+// graph/shaders/graph_op/tosa/fft2d.comp:17-55 (imag != null) and rfft2d.comp:12-71 (imag == null, outputs of
+// W / 2 + 1 columns): the defining double sum, evaluated in double precision with the angle's numerator reduced
+// modulo H*W and rounded to float once.  The shaders compute the same sums with their device's single-precision
+// sine and cosine; comparisons against this function use a tolerance stated in the tests.
+int orc_fft2d(const orc_tensor *real, const orc_tensor *imag, const orc_tensor *outReal, const orc_tensor *outImag,
+              int inverse) {
+    const int64_t total = numel(*outReal);
+    const uint32_t H = uint32_t(real->dims[1]), W = uint32_t(real->dims[2]);
+    const double kPi = 3.14159265358979323846;
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < total; ++e) {
+        uint32_t idx[kMaxRank];
+        unravel(*outReal, uint32_t(e), idx);
+        const uint32_t n = idx[0], oy = idx[1], ox = idx[2];
+        const bool skipImag = imag == nullptr && (oy == 0 || oy == H / 2) && (ox == 0 || ox == W / 2);
+        long double sumRe = 0.0L, sumIm = 0.0L;
+        for (uint32_t iy = 0; iy < H; ++iy) {
+            for (uint32_t ix = 0; ix < W; ++ix) {
+                const uint32_t ci[3] = {n, iy, ix};
+                const double re = rd<float>(*real, ci);
+                const double im = imag != nullptr ? double(rd<float>(*imag, ci)) : 0.0;
+                const uint64_t num = ((uint64_t(iy) * oy % H) * W + (uint64_t(ix) * ox % W) * H) % (uint64_t(H) * W);
+                const double angle = 2.0 * kPi * double(num) / double(uint64_t(H) * W);
+                const double cs = std::cos(angle), sn = inverse ? -std::sin(angle) : std::sin(angle);
+                sumRe += re * cs + im * sn;
+                sumIm += im * cs - re * sn;
+            }
+        }
+        wr<float>(*outReal, idx, float(sumRe));
+        wr<float>(*outImag, idx, skipImag ? 0.0f : float(sumIm));
+    }
+    return 0;
+}
+
 } // extern "C"

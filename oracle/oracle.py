@@ -340,3 +340,17 @@ def conv3d(x, w, bias, out_shape, pad, stride, dil, in_zp, w_zp):
     _check(lib().orc_conv3d(ctypes.byref(_t(x)), ctypes.byref(_t(w)), ctypes.byref(_t(bias)), ctypes.byref(_t(out)),
                             _i32(pad), _i32(stride), _i32(dil), ctypes.c_int32(in_zp), ctypes.c_int32(w_zp)))
     return out
+
+
+def fft2d(real, imag, inverse):
+    out_re, out_im = np.zeros(real.shape, np.float32), np.zeros(real.shape, np.float32)
+    _check(lib().orc_fft2d(ctypes.byref(_t(real)), ctypes.byref(_t(imag)), ctypes.byref(_t(out_re)),
+                           ctypes.byref(_t(out_im)), int(bool(inverse))))
+    return out_re, out_im
+
+
+def rfft2d(x):
+    shape = x.shape[:2] + (x.shape[2] // 2 + 1,)
+    out_re, out_im = np.zeros(shape, np.float32), np.zeros(shape, np.float32)
+    _check(lib().orc_fft2d(ctypes.byref(_t(x)), None, ctypes.byref(_t(out_re)), ctypes.byref(_t(out_im)), 0))
+    return out_re, out_im

@@ -69,6 +69,9 @@ def evaluate(graph, inputs, keep_all=False):
             r = oracle.negate(i[0], a["in_zp"], a["out_zp"])
         elif n == "SELECT":
             r = oracle.select(i[0], i[1], i[2])
+        elif n in ("FFT2D", "RFFT2D"):
+            r, second = oracle.fft2d(i[0], i[1], a["inverse"]) if n == "FFT2D" else oracle.rfft2d(i[0])
+            env[op.more_outs[0].name] = second
         elif n == "ARGMAX":
             r = oracle.argmax(i[0], a["axis"])
         elif n == "GATHER":

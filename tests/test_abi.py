@@ -29,7 +29,8 @@ def test_registry(mlel):
     for op in ("CONV2D", "DEPTHWISE_CONV2D", "MATMUL", "RESCALE", "AVG_POOL2D", "MAX_POOL2D", "TABLE", "TRANSPOSE",
                "CONCAT", "CLAMP", "ADD", "SUB", "MUL", "REDUCE_SUM", "REDUCE_MAX", "CAST", "RESHAPE", "SLICE", "PAD"):
         assert op in names and mlel.tosa_op_supported(op)
-    assert not mlel.tosa_op_supported("FFT2D")
+    assert all(mlel.tosa_op_supported(op) for op in names)
+    assert not mlel.tosa_op_supported("NOT_A_TOSA_OPERATOR")
 
 
 def test_errors_are_status_codes_not_exceptions(mlel):

@@ -96,12 +96,27 @@ def test_reference_sin_fixture(mlel, reference_root):
     assert p.op_names() == ["SIN"]
 
 
-def test_unbuilt_operator_is_feature_not_present(mlel, reference_root):
+def test_reference_fft2d_fixture(mlel, reference_root):
+    # tests/shader/fft2d.spvasm: a two-result instruction (OpTypeStruct result, OpCompositeExtract per output)
+    p = lower(mlel, fixture(reference_root, "fft2d.spvasm"), [(0, b, 0, mlel.F32, (1, 4, 4096)) for b in range(4)])
+    assert p.op_names() == ["FFT2D"]
+
+
+def test_every_tosa_operator_is_registered_and_built(mlel):
+    names = mlel.tosa_op_names()
+    assert len(names) == 66  # graph/graph_tosa_1_0_ext_inst.cpp:41-108
+    assert all(mlel.tosa_op_supported(n) for n in names)
+
+
+def test_unbuilt_variant_is_feature_not_present(mlel):
+    # every operator is lowered, but not for every element type: a transcendental of an integer tensor is refused
+    g = GraphBuilder()
+    x = g.input(np.int8, (4,))
+    g.output(g.unary("SIN", x))
     with pytest.raises(mlel.MlelError) as e:
-        lower(mlel, fixture(reference_root, "fft2d.spvasm"),
-              [(0, b, 0, mlel.F32, (1, 4, 4096)) for b in range(4)])
+        lower(mlel, g.spvasm(), [(0, 0, 0, mlel.I8, (4,)), (0, 1, 0, mlel.I8, (4,))])
     assert e.value.status == -8
-    assert "FFT2D" in str(e.value)
+    assert "SIN" in str(e.value)
 
 
 def test_unregistered_instruction_set_is_rejected(mlel):

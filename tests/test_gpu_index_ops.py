@@ -261,3 +261,34 @@ def test_pow(mlel):
     want = evaluate(g, [base, expo])[0]
     got = GraphRunner(g).run([base, expo])[0]
     check_float(got, want, 4, "POW")
+
+
+# ---- FFT2D / RFFT2D: direct sums in double on both sides; what differs is the sine/cosine (sincospi of the reduced
+# fraction on the device, cos/sin of the reduced angle in the oracle), far below the float rounding of the result.
+# Tolerance: 2e-6 * sqrt(H * W) absolute for unit-variance inputs (the results have standard deviation sqrt(H * W)).
+
+@pytest.mark.parametrize("shape", [(2, 8, 16), (1, 4, 256), (3, 5, 12)])
+def test_fft2d_and_rfft2d(mlel, shape):
+    from mlel_b200.runtime import GraphRunner
+    r = rng(shape[2])
+    re = r.standard_normal(shape).astype(np.float32)
+    im = r.standard_normal(shape).astype(np.float32)
+    g = GraphBuilder()
+    a, b = g.input(np.float32, shape), g.input(np.float32, shape)
+    f_re, f_im = g.fft2d(a, b, False)
+    i_re, i_im = g.fft2d(f_re, f_im, True)  # an intermediate pair: both results live in session memory
+    r_re, r_im = g.rfft2d(a)
+    for v in (f_re, f_im, i_re, i_im, r_re, r_im):
+        g.output(v)
+    want = evaluate(g, [re, im])
+    got = GraphRunner(g).run([re, im])
+    points = shape[1] * shape[2]
+    tol = [np.sqrt(points)] * 2 + [float(points)] * 2 + [np.sqrt(points)] * 2
+    for k, (x, y, t) in enumerate(zip(got, want, tol)):
+        assert x.dtype == np.float32 and x.shape == y.shape
+        assert np.abs(x - y).max() <= 2e-6 * t, (k, np.abs(x - y).max())
+    # forward then unscaled inverse returns the input times H * W
+    assert np.abs(got[2] / points - re).max() < 1e-5 and np.abs(got[3] / points - im).max() < 1e-5
+    for oy in {0, shape[1] // 2}:
+        for ox in {0, shape[2] // 2}:
+            assert (got[5][:, oy, ox] == 0).all()

@@ -293,3 +293,22 @@ def test_resize(scale, offset, border, in_dtype, out_dtype, mode):
     want = np_ref.resize(x, scale, offset, border, mode, out_dtype)
     got = oracle.resize(x, want.shape, out_dtype, scale, offset, border, mode)
     np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 16), (1, 4, 64), (3, 1, 8), (1, 6, 10)])
+def test_fft2d_and_rfft2d_against_numpy(shape):
+    r = rng(shape[2])
+    re = r.standard_normal(shape).astype(np.float32)
+    im = r.standard_normal(shape).astype(np.float32)
+    z = re.astype(np.float64) + 1j * im.astype(np.float64)
+    scale = np.sqrt(shape[1] * shape[2])
+    for inverse, want in ((False, np.fft.fft2(z)), (True, np.fft.ifft2(z) * shape[1] * shape[2])):
+        got_re, got_im = oracle.fft2d(re, im, inverse)
+        assert np.abs(got_re - want.real).max() < 1e-6 * scale and np.abs(got_im - want.imag).max() < 1e-6 * scale
+    want = np.fft.rfft2(re.astype(np.float64))
+    got_re, got_im = oracle.rfft2d(re)
+    assert got_re.shape == want.shape
+    assert np.abs(got_re - want.real).max() < 1e-6 * scale and np.abs(got_im - want.imag).max() < 1e-6 * scale
+    for oy in {0, shape[1] // 2}:       # the self-conjugate bins are written as exact zeros (rfft2d.comp:33-38)
+        for ox in {0, shape[2] // 2}:
+            assert (got_im[:, oy, ox] == 0).all()
