@@ -11,7 +11,8 @@ from __graft_entry__ import load_package  # noqa: E402
 
 load_package()  # registers the package as module "mlel_b200" so that tests can import its submodules
 
-REFERENCE_ROOT = "/root/reference"  # present only in the authoring container; never needed on a GPU box
+# checkout of the reference project: present only where the fixtures were authored, never needed on a GPU box
+REFERENCE_ROOT = os.environ.get("MLEL_REFERENCE_ROOT", "/root/reference")
 
 
 def pytest_configure(config):

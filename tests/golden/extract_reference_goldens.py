@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checked out:
 
-    python tests/golden/extract_reference_goldens.py /root/reference
+    python tests/golden/extract_reference_goldens.py <path of the reference checkout>
 
 It reads ``tests/vulkan.cpp`` as text, finds the expected-output array literal of each listed
 gtest case and writes ``tests/golden/reference_goldens.json``.  Only numbers are taken; the
@@ -105,4 +105,4 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MLEL_REFERENCE_ROOT", "/root/reference"))
