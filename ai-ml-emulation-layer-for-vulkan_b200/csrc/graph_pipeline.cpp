@@ -1094,6 +1094,16 @@ void GraphPipeline::prepareTensorCore() {
                     }
                 }
             }
+            {
+                // With corrections this small, accumulator + correction - zero point cannot leave int32 (the raw sum
+                // of at most 65536 products is at most 2^30 in size): the epilogue may then fold the three terms into
+                // one 32-bit addition without changing the reference's 64-bit arithmetic.
+                bool small = true;
+                for (const int32_t c : corr) {
+                    small = small && c >= -((1 << 30) - 256) && c <= (1 << 30) - 256;
+                }
+                op.auxi[4] = small ? 1 : 0;
+            }
             op.aux[0] = addDerivedConstant(MLEL_I32, {int64_t(corr.size())}, corr.data());
             op.aux[1] = addDerivedConstant(MLEL_U8, {OH}, rowCls.data());
             op.aux[2] = addDerivedConstant(MLEL_U8, {OW}, colCls.data());

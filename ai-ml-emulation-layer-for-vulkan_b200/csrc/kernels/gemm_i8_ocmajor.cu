@@ -96,13 +96,13 @@ __device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, const void *s
                  : "memory");
 }
 
-// High 32 bits of v * mult + (v >= thr ? rn + bump : rn): product and rounding of a RESCALE whose shift is at
-// least 32, where the result only depends on the high word.  The two rounding constants of double rounding
-// differ by 2^31 (bump; 0 without double rounding), which fits the third input of the 64-bit addition that
-// follows the multiply, so the choice costs one compare and one select.
-__device__ __forceinline__ int32_t scaleHigh(int32_t v, int32_t mult, int32_t thr, uint64_t rn, uint32_t bump) {
-    const uint64_t prod = uint64_t(int64_t(v) * int64_t(mult));
-    const uint32_t extra = v >= thr ? bump : 0u;
+// High 32 bits of x * mult + round(x), x = value - input zero point: product and rounding of a RESCALE whose shift
+// is at least 32, where the result only depends on the high word.  Double rounding adds 2^30 for x >= 0 and
+// subtracts it for x < 0: that is rn = 2^(shift-1) - 2^30 plus 2^31 when the sign bit of x is clear, one logic
+// operation on x (bumpMask = 2^31, or 0 without double rounding) feeding the third input of the 64-bit addition.
+__device__ __forceinline__ int32_t scaleHigh(int32_t x, int32_t mult, uint64_t rn, uint32_t bumpMask) {
+    const uint64_t prod = uint64_t(int64_t(x) * int64_t(mult));
+    const uint32_t extra = ~uint32_t(x) & bumpMask;
     const uint64_t sum = prod + rn + uint64_t(extra);
     return int32_t(uint32_t(sum >> 32));
 }
@@ -126,11 +126,12 @@ __device__ __forceinline__ int32_t finishHigh(int32_t high, int32_t s2, int32_t 
 // Constants of one epilogue thread (one output channel) and of the per-tensor output stage.
 struct EpiConsts {
     FastRescale fm;
-    uint64_t rnM;    // rounding constant for inputs below the zero point
-    uint32_t bumpM;  // what the constant for inputs at or above it adds: 2^31 with double rounding, else 0
-    int32_t corr0;
+    uint64_t rnM;    // scaleHigh: rounding constant without the zero-point fold, for x < 0
+    uint32_t bumpM;  // scaleHigh: 2^31 with double rounding, else 0
+    int32_t corr0;   // correction of the most common border class
+    int32_t corrX;   // corr0 - input zero point: accumulator + corrX is x of scaleHigh
     int32_t outZpMain, loMain, hiMain;
-    bool fast; // the shift is at least 32: see scaleHigh
+    bool fast; // the shift is at least 32 and the corrections are small: see scaleHigh
 };
 
 // 16 pixels of one channel: accumulator slice -> bytes in the C/D tile (column `cd`, rows 128 bytes apart).
@@ -152,10 +153,11 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
         int32_t r[CH];
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
-            const int32_t v = int32_t(acc[g + j] + uint32_t(k.corr0));
             if (FAST) {
-                r[j] = finishHigh(scaleHigh(v, k.fm.mult, k.fm.zpIn, k.rnM, k.bumpM), k.fm.s2, k.outZpMain, k.loMain, k.hiMain);
+                const int32_t x = int32_t(acc[g + j] + uint32_t(k.corrX));
+                r[j] = finishHigh(scaleHigh(x, k.fm.mult, k.rnM, k.bumpM), k.fm.s2, k.outZpMain, k.loMain, k.hiMain);
             } else {
+                const int32_t v = int32_t(acc[g + j] + uint32_t(k.corr0));
                 r[j] = fastRescale(k.fm, v, k.outZpMain, k.loMain, k.hiMain);
             }
         }
@@ -235,10 +237,14 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             const int ci = (p.epi.main.perChannel && ocValid) ? oc : 0;
             k.fm = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)), p.epi.main.inZp,
                                    p.epi.main.doubleRound != 0);
-            k.rnM = (uint64_t(k.fm.rnHi) << 32) | k.fm.rnLo;
-            k.bumpM = uint32_t(((uint64_t(k.fm.rpHi) << 32) | k.fm.rpLo) - k.rnM);
             k.corr0 = ocValid ? __ldg(corrBatch + int64_t(baseClass) * p.N + oc) : 0;
-            k.fast = __all_sync(0xffffffffu, k.fm.s1 == 32);
+            k.corrX = int32_t(uint32_t(k.corr0) - uint32_t(k.fm.zpIn));
+            // shift >= 32 here whenever the constants below are used
+            const bool twoRounds = p.epi.main.doubleRound != 0;
+            const int shiftM = k.fm.s1 + k.fm.s2;
+            k.rnM = (uint64_t(1) << ((shiftM > 0 ? shiftM : 1) - 1)) - (twoRounds ? (uint64_t(1) << 30) : 0);
+            k.bumpM = twoRounds ? 0x80000000u : 0u;
+            k.fast = __all_sync(0xffffffffu, k.fm.s1 == 32) && p.corrSmall != 0;
             curC0 = c0;
             curBatch = batch;
         }

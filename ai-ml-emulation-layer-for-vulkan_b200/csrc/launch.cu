@@ -108,6 +108,7 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     p.numColClasses = op.auxi[0];
     p.numClasses = op.auxi[1];
     p.baseClass = op.auxi[3];
+    p.corrSmall = op.auxi[4];
     if (p.numClasses <= 1) {
         p.rowClass = p.colClass = nullptr; // no window crosses the border: one correction row serves every pixel
         p.baseClass = 0;

@@ -188,7 +188,8 @@ struct OpDesc {
     std::vector<int32_t> fusedOps;  // indices of the logical ops an exec node stands for
     // Tensor-core path (set by GraphPipeline::prepareTensorCore when the node qualifies):
     //   CONV2D kinds: aux[0] correction table int32 [classes][OC], aux[1] row classes u8 [OH],
-    //                 aux[2] column classes u8 [OW]; auxi[0] = number of column classes, auxi[1] = classes
+    //                 aux[2] column classes u8 [OW]; auxi[0] = number of column classes, auxi[1] = classes,
+    //                 auxi[3] = the most common class, auxi[4] = 1 when every correction is below 2^30 - 256 in size
     //                 with a fused residual tail and tc == 1: aux[3] = the tail as a table of 256 x 256 bytes
     //   MATMUL kinds with a constant second input: aux[0] correction int32 [batches][W],
     //                 aux[3] the second input transposed to [batches][W][C]
@@ -199,7 +200,7 @@ struct OpDesc {
     int32_t tc{0};
     int32_t scratch{-1};
     int32_t aux[5]{-1, -1, -1, -1, -1};
-    int32_t auxi[4]{0, 0, 0, 0};
+    int32_t auxi[5]{0, 0, 0, 0, 0};
 };
 
 // Launches one operator.  `tensors` is indexed by tensor id (op.in / op.out / op.epi hold ids).

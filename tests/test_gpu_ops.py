@@ -117,6 +117,32 @@ def test_conv2d_asymmetric_padding_many_channels(mlel):
     check(mlel, g, [r.integers(-128, 128, (3, 9, 10, 128), dtype=np.int8)])
 
 
+@pytest.mark.parametrize("double_round", [False, True])
+@pytest.mark.parametrize("bias_bits", [12, 29, 31])
+def test_conv2d_channel_major_bias_range_and_rounding(mlel, bias_bits, double_round):
+    """The channel-major kernel's short RESCALE form applies when accumulator + correction cannot leave int32;
+    biases of 2^31 make the convolution's int32 output wrap (conv2d.comp adds the bias in 32 bits) and take the
+    general form.  Both rounding modes, shifts from 32 up, a negative zero point, with and without a border."""
+    r = rng(bias_bits + double_round)
+    lim = (1 << bias_bits) - 1
+    for k, pad in ((1, 0), (3, 1)):
+        g = GraphBuilder()
+        x = g.input(np.int8, (2, 14, 14, 128))
+        wt = g.constant(r.integers(-128, 128, (160, k, k, 128), dtype=np.int8))
+        bias = r.integers(-lim - 1, lim + 1, (160,), dtype=np.int64).astype(np.int32)
+        bias[:4] = [lim, -lim - 1, 0, -1]
+        y = g.conv2d(x, wt, g.constant(bias), [pad] * 4, [1, 1], [1, 1], -128, 0)
+        mult = r.integers(1 << 30, (1 << 31) - 1, (160,), dtype=np.int64).astype(np.int32)
+        mult[5:8] = -mult[5:8]
+        shift = r.integers(32, 48, (160,), dtype=np.int8)
+        shift[:3] = [32, 33, 62]
+        g.output(g.rescale(y, mult, shift, 0, -9, np.int8, True, double_round, True))
+        data = r.integers(-128, 128, (2, 14, 14, 128), dtype=np.int8)
+        data[0, :2] = -128
+        data[1, :2] = 127
+        check(mlel, g, [data])
+
+
 def test_conv2d_int16_int64(mlel):
     r = rng(2)
     g = GraphBuilder()
