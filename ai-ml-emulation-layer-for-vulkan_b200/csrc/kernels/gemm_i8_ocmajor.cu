@@ -155,10 +155,17 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
         for (int j = 0; j < CH; ++j) {
             if (FAST) {
                 const int32_t x = int32_t(acc[g + j] + uint32_t(k.corrX));
-                r[j] = finishHigh(scaleHigh(x, k.fm.mult, k.rnM, k.bumpM), k.fm.s2, k.outZpMain, k.loMain, k.hiMain);
+                const int32_t high = scaleHigh(x, k.fm.mult, k.rnM, k.bumpM);
+                if (RESIDUAL) {
+                    // the value is only used as a row number of the residual table: clamp(q + zp, lo, hi) - lo is one
+                    // add-min-relu, and the table's base address takes the - lo
+                    r[j] = __viaddmin_s32_relu(high >> k.fm.s2, k.outZpMain - k.loMain, k.hiMain - k.loMain);
+                } else {
+                    r[j] = finishHigh(high, k.fm.s2, k.outZpMain, k.loMain, k.hiMain);
+                }
             } else {
                 const int32_t v = int32_t(acc[g + j] + uint32_t(k.corr0));
-                r[j] = fastRescale(k.fm, v, k.outZpMain, k.loMain, k.hiMain);
+                r[j] = fastRescale(k.fm, v, k.outZpMain, k.loMain, k.hiMain) - (RESIDUAL ? k.loMain : 0);
             }
         }
         if (RESIDUAL) {
@@ -177,7 +184,7 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
 }
 
 // cd: shared address of this thread's column of the C/D tile at the slice's first pixel; tab128: shared address
-// of the residual table's row for main-stage value 0.
+// of the residual table's row for the lowest main-stage value.
 template <bool RESIDUAL>
 __device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t tab128, uint32_t cd) {
     if (k.fast) {
@@ -204,7 +211,8 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     static_assert(EW * 32 >= BNP, "one thread per pixel fills the class table");
     EpiConsts k{};
     k.outZpMain = p.epi.main.outZp, k.loMain = p.epi.main.lo, k.hiMain = p.epi.main.hi;
-    const uint32_t tab128 = smemAddr(resTab) + 128u * uint32_t(kResidualRowBytes); // row of main-stage value 0
+    // row of the lowest main-stage value: the element loop counts rows from there
+    const uint32_t tab128 = smemAddr(resTab) + uint32_t((128 + p.epi.main.lo) * kResidualRowBytes);
     bool tableReady = !RESIDUAL;
     int curC0 = -1, curBatch = -1;
     const bool hasClasses = p.rowClass != nullptr;
