@@ -16,13 +16,26 @@ Session::Session(GraphPipeline *pipeline) : pipeline_(pipeline) {
     plan();
 }
 
-Session::~Session() {
-    if (graphExec_ != nullptr) {
-        cudaGraphExecDestroy(graphExec_);
+Session::~Session() { dropGraphs(); }
+
+void Session::dropGraphs() {
+    for (auto &entry : graphs_) {
+        if (entry.second.exec != nullptr) {
+            cudaGraphExecDestroy(entry.second.exec);
+        }
+        if (entry.second.graph != nullptr) {
+            cudaGraphDestroy(entry.second.graph);
+        }
     }
-    if (graph_ != nullptr) {
-        cudaGraphDestroy(graph_);
+    graphs_.clear();
+}
+
+std::vector<const void *> Session::bindingKey() const {
+    std::vector<const void *> key{memory_};
+    for (const auto &entry : external_) {
+        key.push_back(entry.second);
     }
+    return key;
 }
 
 // Live range of a session tensor = [first, last] execution index over {inputs node = 0,
@@ -231,12 +244,6 @@ int Session::resolve() {
     if (resolved_) {
         return MLEL_SUCCESS;
     }
-    if (graphExec_ != nullptr) { // bindings changed: the captured graph holds stale addresses
-        cudaGraphExecDestroy(graphExec_);
-        cudaGraphDestroy(graph_);
-        graphExec_ = nullptr;
-        graph_ = nullptr;
-    }
     const int32_t n = pipeline_->tensorCount();
     views_.assign(size_t(n), TView{});
     char *constBase = pipeline_->constantBase();
@@ -371,7 +378,15 @@ int Session::dispatchGraph(cudaStream_t stream) {
     if (rc != MLEL_SUCCESS) {
         return rc;
     }
-    if (graphExec_ == nullptr) {
+    // A captured graph holds the addresses that were bound when it was taken: one graph per set of bindings.
+    constexpr size_t kMaxCapturedGraphs = 64;
+    const std::vector<const void *> key = bindingKey();
+    auto found = graphs_.find(key);
+    if (found == graphs_.end()) {
+        if (graphs_.size() >= kMaxCapturedGraphs) {
+            dropGraphs();
+        }
+        CapturedGraph captured;
         cudaStream_t capture = nullptr;
         if (cudaStreamCreateWithFlags(&capture, cudaStreamNonBlocking) != cudaSuccess) {
             setLastError("cudaStreamCreate failed");
@@ -380,21 +395,28 @@ int Session::dispatchGraph(cudaStream_t stream) {
         cudaError_t err = cudaStreamBeginCapture(capture, cudaStreamCaptureModeThreadLocal);
         if (err == cudaSuccess) {
             rc = dispatch(capture);
-            err = cudaStreamEndCapture(capture, &graph_);
+            err = cudaStreamEndCapture(capture, &captured.graph);
         }
         if (err == cudaSuccess && rc == MLEL_SUCCESS) {
-            err = cudaGraphInstantiate(&graphExec_, graph_, 0);
+            err = cudaGraphInstantiate(&captured.exec, captured.graph, 0);
         }
         cudaStreamDestroy(capture);
-        if (rc != MLEL_SUCCESS) {
-            return rc;
-        }
-        if (err != cudaSuccess) {
+        if (rc != MLEL_SUCCESS || err != cudaSuccess) {
+            if (captured.exec != nullptr) {
+                cudaGraphExecDestroy(captured.exec);
+            }
+            if (captured.graph != nullptr) {
+                cudaGraphDestroy(captured.graph);
+            }
+            if (rc != MLEL_SUCCESS) {
+                return rc;
+            }
             setLastError(std::string("CUDA graph capture failed: ") + cudaGetErrorString(err));
             return MLEL_ERROR_DEVICE;
         }
+        found = graphs_.emplace(key, captured).first;
     }
-    if (cudaGraphLaunch(graphExec_, stream) != cudaSuccess) {
+    if (cudaGraphLaunch(found->second.exec, stream) != cudaSuccess) {
         setLastError("cudaGraphLaunch failed");
         return MLEL_ERROR_DEVICE;
     }

@@ -68,8 +68,15 @@ class Session {
     std::map<std::tuple<uint32_t, uint32_t, uint32_t>, char *> external_;
     std::vector<TView> views_;
     bool resolved_{false};
-    cudaGraphExec_t graphExec_{nullptr};
-    cudaGraph_t graph_{nullptr};
+    // Captured dispatches, one per set of bound addresses (session memory, then every external tensor in key
+    // order): a host that alternates between a few input buffers replays a graph for each of them.
+    struct CapturedGraph {
+        cudaGraph_t graph{nullptr};
+        cudaGraphExec_t exec{nullptr};
+    };
+    std::map<std::vector<const void *>, CapturedGraph> graphs_;
+    std::vector<const void *> bindingKey() const;
+    void dropGraphs();
 };
 
 const std::string &lastError();

@@ -194,6 +194,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU (benchmark value: 64)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="enqueue every kernel of every step instead of replaying one captured CUDA graph per bound buffer")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -233,10 +235,14 @@ def main():
     host_out = torch.empty(out_bytes, dtype=torch.uint8).pin_memory()
     stream = torch.cuda.current_stream(device)
 
+    # mlel_session_dispatch_graph keeps one captured CUDA graph per set of bound addresses, so rotating over the
+    # ring (or over the two staging buffers of the end-to-end path) replays graphs after the first round.
+    dispatch = session.dispatch if args.no_graph else session.dispatch_graph
+
     def step_resident(i):
         # inputs already in HBM: rebinding an external tensor is a descriptor update, not a copy
         session.set_external(0, 0, dev_ring[i % RING].data_ptr())
-        session.dispatch(stream.cuda_stream)
+        dispatch(stream.cuda_stream)
         if world > 1:
             all_gather_batch(out_dev.view(n, -1), world * n)
 
@@ -266,7 +272,7 @@ def main():
             ready[b].record(copy_stream)
         stream.wait_event(ready[b])
         session.set_external(0, 0, stage_in[b].data_ptr())
-        session.dispatch(stream.cuda_stream)
+        dispatch(stream.cuda_stream)
         free[b].record(stream)
         host_out.copy_(out_dev, non_blocking=True)
         if world > 1:
@@ -297,6 +303,8 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for i in range(RING):  # untimed: every buffer of the ring has its graph before the clock starts
+        step_resident(i)
     total_ms = timed(step_resident, W, K)
     clocks = sampler.stop() if rank == 0 else None
     e2e_steps = max(3, K // 2)
@@ -355,12 +363,14 @@ def main():
             "cache": "inputs rotate over a ring of %d device buffers (%.0f MB) larger than the 126 MB L2" %
                      (RING, RING * in_bytes / 1e6),
             "parallelism": "batch-sharded, one rank per GPU, NCCL all-gather of the logits" if world > 1 else "single GPU",
+            "dispatch": "per-kernel launches" if args.no_graph else "CUDA-graph replay, one captured graph per bound input buffer",
         },
         "clocks": clocks,
         "gpu_launches": launches_per_dispatch * K * world,
         "e2e": {"value": world * n * e2e_steps / (e2e_ms / 1e3), "unit": "images/s",
                 "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
-                "path": "set_external + dispatch per step; host->device copy of the next batch on a second stream",
+                "path": "set_external + %s per step; host->device copy of the next batch on a second stream" %
+                        ("dispatch" if args.no_graph else "dispatch_graph (one captured CUDA graph per staging buffer)"),
                 "single_call_run_host": world * n * e2e_steps / (run_host_ms / 1e3)},
         "roofline": {
             "kernel": "fused CONV2D+RESCALE[+CLAMP] (%d launches per dispatch)" % n_conv,

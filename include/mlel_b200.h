@@ -243,7 +243,8 @@ int mlel_session_set_external(mlel_session *s, uint32_t set, uint32_t binding, u
                               void *device_ptr);
 /* vkCmdDispatchDataGraphARM + queue submission: enqueues every kernel of the graph on `stream`. */
 int mlel_session_dispatch(mlel_session *s, void *cuda_stream);
-/* Same, replayed from a CUDA graph captured on first use (bindings must not change afterwards). */
+/* Same, replayed from a CUDA graph captured on first use.  One graph is kept per set of bound addresses (up to
+ * 64 sets), so a host that alternates between a few input and output buffers replays a graph for each. */
 int mlel_session_dispatch_graph(mlel_session *s, void *cuda_stream);
 /* Dispatch with a CUDA event pair around every launched kernel, the counterpart of the reference's
  * per-operator timestamp profiling (VMEL_GRAPH_PROFILING, graph/graph_profiler.cpp:157-191).

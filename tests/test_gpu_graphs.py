@@ -349,3 +349,29 @@ def test_direct_kernel_entry_points(mlel):
                                             ctypes.byref(tm), ctypes.byref(ts), 0, 3, 1, 0, 1, 0, stream))
     torch.cuda.synchronize()
     np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
+def test_graph_replay_follows_rebinding(mlel):
+    """mlel_session_dispatch_graph keeps one captured graph per set of bound addresses: a host that alternates
+    between input (and output) buffers gets, from every replay, the result for the buffers bound at that moment."""
+    import torch
+    from mlel_b200.runtime import GraphRunner
+    g, inputs = resnet50_graph(seed=4, n=2, image=32, width=16, blocks=(1, 1, 1, 1), classes=16)
+    r = GraphRunner(g)
+    rng = np.random.Generator(np.random.PCG64(9))
+    batches = [rng.integers(-128, 128, inputs[0].shape, dtype=np.int8) for _ in range(3)]
+    want = [evaluate(g, [b])[0] for b in batches]
+    assert not np.array_equal(want[0], want[1])
+    dev_in = [torch.from_numpy(b.reshape(-1).view(np.uint8)).cuda() for b in batches]
+    dev_out = [torch.zeros_like(r.outputs[0]) for _ in range(2)]
+    (s_in, b_in, _), (s_out, b_out, v_out) = r._in_keys[0], r._out_keys[0]
+    stream = torch.cuda.current_stream().cuda_stream
+    for step in range(9):  # every buffer pair comes round again after its graph was captured
+        i, o = step % 3, step % 2
+        r.session.set_external(s_in, b_in, dev_in[i].data_ptr())
+        r.session.set_external(s_out, b_out, dev_out[o].data_ptr())
+        dev_out[o].zero_()
+        r.session.dispatch_graph(stream)
+        torch.cuda.synchronize()
+        got = dev_out[o].cpu().numpy().view(v_out.dtype).reshape(v_out.shape)
+        np.testing.assert_array_equal(got, want[i])
