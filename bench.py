@@ -303,8 +303,9 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    for i in range(RING):  # untimed: every buffer of the ring has its graph before the clock starts
-        step_resident(i)
+    if not args.no_graph:
+        for i in range(RING):  # untimed: every buffer of the ring has its graph before the clock starts
+            step_resident(i)
     total_ms = timed(step_resident, W, K)
     clocks = sampler.stop() if rank == 0 else None
     e2e_steps = max(3, K // 2)
