@@ -253,6 +253,37 @@ def test_residual_add_pattern(mlel):
         check(mlel, g, [r.integers(-128, 128, shape, dtype=np.int8), r.integers(-128, 128, shape, dtype=np.int8)])
 
 
+@pytest.mark.parametrize("oc", [32, 160])            # pixel-major kernel / channel-major kernel with the residual table
+@pytest.mark.parametrize("main_first", [True, False])  # ADD(main, shortcut) and ADD(shortcut, main)
+@pytest.mark.parametrize("main_clamp", [False, True])  # a CLAMP between the convolution's RESCALE and the add
+def test_conv_with_fused_residual_tail(mlel, oc, main_first, main_clamp):
+    """CONV2D -> RESCALE [-> CLAMP] -> RESCALE, RESCALE(shortcut) -> ADD -> RESCALE -> CLAMP is one kernel; all
+    three tail RESCALEs with their own zero points, multipliers and rounding modes, shortcut bytes over the whole
+    int8 range, against the one-kernel-per-operator oracle."""
+    from mlel_b200.runtime import GraphRunner
+    r = rng(oc + 2 * main_first + main_clamp)
+    g = GraphBuilder()
+    x = g.input(np.int8, (3, 14, 14, 64))
+    sc = g.input(np.int8, (3, 14, 14, oc))
+    wt = g.constant(r.integers(-128, 128, (oc, 1, 1, 64), dtype=np.int8))
+    b = g.constant(r.integers(-(1 << 14), 1 << 14, (oc,), dtype=np.int32))
+    y = g.conv2d(x, wt, b, [0] * 4, [1, 1], [1, 1], -20, 0)
+    mult = r.integers(1 << 30, (1 << 31) - 1, (oc,), dtype=np.int64).astype(np.int32)
+    y = g.rescale(y, mult, r.integers(34, 40, (oc,), dtype=np.int8), 0, -7, np.int8, True, True, True)
+    if main_clamp:
+        y = g.clamp(y, -100, 90)
+    ta = g.rescale(y, [int(r.integers(1 << 30, 1 << 31))], [22], -7, 11, np.int32, True, False)
+    tb = g.rescale(sc, [int(r.integers(1 << 30, 1 << 31))], [24], 3, -5, np.int32, True, True)
+    s = g.add(ta, tb) if main_first else g.add(tb, ta)
+    out = g.rescale(s, [int(r.integers(1 << 30, 1 << 31))], [39], 2, -20, np.int8, True, True)
+    g.output(g.clamp(out, -20, 127))
+    assert GraphRunner(g).pipeline.exec_names() == ["CONV2D+RESCALE" + ("+CLAMP" if main_clamp else "") +
+                                                     "+ADD+RESCALE+CLAMP"]
+    shortcut = r.integers(-128, 128, (3, 14, 14, oc), dtype=np.int8)
+    shortcut[0, 0, :, :] = -20  # many equal shortcut bytes in one warp (what a ReLU leaves behind)
+    check(mlel, g, [r.integers(-128, 128, (3, 14, 14, 64), dtype=np.int8), shortcut])
+
+
 @pytest.mark.parametrize("case", [
     ((1, 7, 7, 5), (7, 7), (7, 7), (0, 0, 0, 0), -20, -20), ((2, 8, 9, 3), (3, 3), (2, 2), (1, 1, 1, 1), 0, 0),
     ((1, 6, 6, 4), (2, 3), (1, 2), (0, 1, 1, 1), 5, -3), ((4, 7, 7, 2048), (7, 7), (7, 7), (0, 0, 0, 0), -20, -20),
