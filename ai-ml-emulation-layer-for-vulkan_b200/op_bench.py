@@ -7,6 +7,7 @@ against the measured copy bandwidth of the machine (``MEASURED_PEAKS.json`` besi
 6538 GB/s).
 
 Run from the repository root:  python ai-ml-emulation-layer-for-vulkan_b200/op_bench.py
+One tensor-core convolution alone:  op_bench.py --conv|--residual IMAGES SIZE IN_CHANNELS OUT_CHANNELS [KERNEL]
 """
 import json
 import os
@@ -113,5 +114,39 @@ def main():
           f"(transpose and product)  {'+'.join(r.pipeline.exec_names())}")
 
 
+def one_convolution(n, hw, ic, oc, k, residual):
+    """One fused int8 convolution of ``n`` images of ``hw`` x ``hw`` x ``ic`` (1x1 or 3x3, per-channel
+    double-round RESCALE), optionally with the fused residual tail, timed alone: the probe behind the per-layer
+    figures of the design notes and the single-layer profiles."""
+    from mlel_b200.model_graphs import _Net, _rng
+    rng = _rng(0)
+    g = GraphBuilder("one_convolution")
+    net = _Net(g, rng)
+    x = g.input(np.int8, (n, hw, hw, ic))
+    inputs = [rng.integers(-128, 128, (n, hw, hw, ic), dtype=np.int8)]
+    if residual:
+        sc = g.input(np.int8, (n, hw, hw, oc))
+        t = net.conv(x, -20, oc, k, 1, k // 2, -7, None)
+        g.output(net.residual_add(t, -7, sc, -20, -20, (-20, 127)))
+        inputs.append(rng.integers(-128, 128, (n, hw, hw, oc), dtype=np.int8))
+    else:
+        g.output(net.conv(x, -20, oc, k, 1, k // 2, -20, (-20, 127)))
+    r = GraphRunner(g)
+    r.set_inputs(inputs)
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        r.session.dispatch(s)
+    torch.cuda.synchronize()
+    ms = min(sum(r.session.dispatch_profiled(s)) for _ in range(5))
+    ops = 2.0 * n * hw * hw * oc * k * k * ic
+    print(f"{'+'.join(r.pipeline.exec_names())}: {ms * 1e3:.1f} us, {ops / ms / 1e9:.0f} TOP/s, "
+          f"{n * hw * hw * oc / ms / 1e6:.0f} G outputs/s")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] in ("--conv", "--residual"):
+        # op_bench.py --conv|--residual IMAGES SIZE IN_CHANNELS OUT_CHANNELS [KERNEL]
+        a = [int(v) for v in sys.argv[2:]]
+        one_convolution(a[0], a[1], a[2], a[3], a[4] if len(a) > 4 else 1, sys.argv[1] == "--residual")
+    else:
+        main()
