@@ -157,6 +157,14 @@ def ext_inst_set_registered(name: str) -> bool:
     return bool(lib().mlel_ext_inst_set_registered(name.encode()))
 
 
+def measure_int8_mma_peak(batches: int, stream: int = 0) -> float:
+    """What the int8 tensor pipe sustains, in TOP/s: ``batches`` batches of 64 back-to-back ``tcgen05.mma
+    kind::i8`` instructions on every SM (about 5 microseconds per batch)."""
+    ms, ops = ctypes.c_float(), ctypes.c_double()
+    check(lib().mlel_measure_int8_mma_peak(int(batches), ctypes.c_void_p(stream), ctypes.byref(ms), ctypes.byref(ops)))
+    return ops.value / (ms.value * 1e-3) / 1e12
+
+
 def allocate_intervals(intervals, unseen, alignment):
     """details::allocateIntervals of the reference (graph/interval_memory_planner.cpp:170-216).
 

@@ -682,6 +682,10 @@ int mlel_pipeline_clear_profile(mlel_pipeline *p) {
     });
 }
 
+int mlel_measure_int8_mma_peak(int batches, void *cuda_stream, float *ms, double *ops) {
+    return guarded([&] { return int8MmaPeak(batches, static_cast<cudaStream_t>(cuda_stream), ms, ops); });
+}
+
 int mlel_session_launch_count(const mlel_session *s) {
     int n = -1;
     guarded([&] {

@@ -111,4 +111,8 @@ int fft2d(const TView *real, const TView *imag, const TView &outReal, const TVie
           cudaStream_t s);
 int conv3d(const TView &in, const TView &w, const TView &bias, const TView &out, const Conv3dAttr &a, cudaStream_t s);
 
+// int8_mma_peak.cu: back-to-back tcgen05.mma kind::i8 on shared-memory operands, every SM: device time and the
+// int8 operations it stands for
+int int8MmaPeak(int batches, cudaStream_t stream, float *msOut, double *opsOut);
+
 } // namespace mlel

@@ -287,6 +287,13 @@ int mlel_pipeline_get_property(mlel_pipeline *p, uint32_t property, void *data, 
 /* Forgets the samples taken so far (the reference drops them with their command buffers). */
 int mlel_pipeline_clear_profile(mlel_pipeline *p);
 
+/* ---- measurement helper (no counterpart in the reference) ----
+ * Runs tcgen05.mma kind::i8 (M 128, N 256, K 32) back to back on every SM, on operands that stay in shared
+ * memory: `batches` batches of 64 instructions per SM.  *ms receives the device time, *ops the number of int8
+ * operations (two per multiply-accumulate) it stands for: ops / ms is what the int8 tensor pipe sustains, the
+ * denominator of tensor-bound roofline fractions.  Synchronises the stream. */
+int mlel_measure_int8_mma_peak(int batches, void *cuda_stream, float *ms, double *ops);
+
 /* Number of kernels one dispatch launches. */
 int mlel_session_launch_count(const mlel_session *s);
 /* Host-buffer convenience used for end-to-end timing: copies `n_in` host inputs to their bound

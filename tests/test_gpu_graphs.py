@@ -375,3 +375,10 @@ def test_graph_replay_follows_rebinding(mlel):
         torch.cuda.synchronize()
         got = dev_out[o].cpu().numpy().view(v_out.dtype).reshape(v_out.shape)
         np.testing.assert_array_equal(got, want[i])
+
+
+def test_int8_mma_peak_loop(mlel):
+    """The measurement helper behind the roofline denominator: back-to-back tcgen05.mma kind::i8 on every SM.
+    A B200's nominal dense int8 rate is 4.5 POP/s; a short burst must land within a factor of two of it."""
+    tops = max(mlel.measure_int8_mma_peak(500) for _ in range(3))
+    assert 2000.0 < tops < 6000.0, tops
