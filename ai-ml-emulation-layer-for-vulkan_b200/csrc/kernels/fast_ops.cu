@@ -169,9 +169,53 @@ __global__ void __launch_bounds__(256) avgPoolI8Kernel(const int8_t *__restrict_
 
 // ---- MAX_POOL2D, int8 NHWC, C % 16 == 0 (maxpool2d.comp:23-72) --------------------------------------
 // One thread per (pixel, 16-channel group): 16-byte loads, per-byte signed max, one 16-byte store.
+//
+// There is no four-lane byte maximum in hardware, but there is a three-input one on two 16-bit lanes.  A word of
+// four int8 is therefore split into its even and its odd bytes, each moved to the HIGH byte of a 16-bit lane with
+// a zero below it: the signed order of the lanes is the signed order of the bytes.  One byte permute per half and
+// one three-input maximum per half and pair of taps replace the emulated byte maximum.
+__device__ __forceinline__ uint32_t evenBytesHigh(uint32_t v) { return __byte_perm(v, 0u, 0x2404); }
+__device__ __forceinline__ uint32_t oddBytesHigh(uint32_t v) { return __byte_perm(v, 0u, 0x3414); }
+__device__ __forceinline__ uint32_t max3Lanes(uint32_t a, uint32_t b, uint32_t c) { return __vimax3_s16x2(a, b, c); }
+
+struct PoolAcc {
+    uint32_t even[4], odd[4];
+    __device__ __forceinline__ PoolAcc() {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            even[i] = odd[i] = 0x80008000u; // int8 lowest in both lanes
+        }
+    }
+    __device__ __forceinline__ void take(const int4 &p, const int4 &q) {
+        const uint32_t a[4] = {uint32_t(p.x), uint32_t(p.y), uint32_t(p.z), uint32_t(p.w)};
+        const uint32_t b[4] = {uint32_t(q.x), uint32_t(q.y), uint32_t(q.z), uint32_t(q.w)};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            even[i] = max3Lanes(even[i], evenBytesHigh(a[i]), evenBytesHigh(b[i]));
+            odd[i] = max3Lanes(odd[i], oddBytesHigh(a[i]), oddBytesHigh(b[i]));
+        }
+    }
+    __device__ __forceinline__ void take(const PoolAcc &o) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            even[i] = max3Lanes(even[i], o.even[i], o.even[i]);
+            odd[i] = max3Lanes(odd[i], o.odd[i], o.odd[i]);
+        }
+    }
+    __device__ __forceinline__ int4 packed() const {
+        // byte 0 and 2 from the high bytes of `even`, byte 1 and 3 from the high bytes of `odd`
+        return make_int4(int(__byte_perm(even[0], odd[0], 0x7351)), int(__byte_perm(even[1], odd[1], 0x7351)),
+                         int(__byte_perm(even[2], odd[2], 0x7351)), int(__byte_perm(even[3], odd[3], 0x7351)));
+    }
+};
+
+// KH, KW > 0: the window is known at compile time, all its loads are issued before the first maximum.
+// KH == 0: any window, two taps at a time.
+template <int KH, int KW>
 __global__ void maxPoolI8Kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int64_t total, int H, int W,
                                 int C, int OH, int OW, PoolAttr a) {
     const int groups = C >> 4;
+    const int4 lowest = make_int4(int(0x80808080u), int(0x80808080u), int(0x80808080u), int(0x80808080u));
     for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += int64_t(gridDim.x) * blockDim.x) {
         const int g = int(e % groups);
         int64_t pix = e / groups;
@@ -180,26 +224,75 @@ __global__ void maxPoolI8Kernel(const int8_t *__restrict__ in, int8_t *__restric
         const int oy = int(pix % OH);
         const int n = int(pix / OH);
         const int iy0 = oy * max(a.stride[0], 1) - a.pad[0], ix0 = ox * max(a.stride[1], 1) - a.pad[2];
-        uint32_t acc[4] = {0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u}; // int8 lowest
-        for (int ky = 0; ky < a.kernel[0]; ++ky) {
-            const int y = iy0 + ky;
-            if (y < 0 || y >= H) {
-                continue;
+        const int4 *image = reinterpret_cast<const int4 *>(in + int64_t(n) * H * W * C) + g;
+        const auto tap = [&](int y, int x) {
+            return (unsigned(y) < unsigned(H) && unsigned(x) < unsigned(W)) ? __ldg(image + (int64_t(y) * W + x) * groups)
+                                                                            : lowest;
+        };
+        PoolAcc acc;
+        if constexpr (KH > 0) {
+            constexpr int kTaps = KH * KW;
+            int4 v[kTaps + 1];
+#pragma unroll
+            for (int t = 0; t < kTaps; ++t) {
+                v[t] = tap(iy0 + t / KW, ix0 + t % KW);
             }
-            for (int kx = 0; kx < a.kernel[1]; ++kx) {
-                const int x = ix0 + kx;
-                if (x < 0 || x >= W) {
-                    continue;
-                }
-                const int4 v = __ldg(reinterpret_cast<const int4 *>(in + ((int64_t(n) * H + y) * W + x) * C) + g);
-                acc[0] = __vmaxs4(acc[0], uint32_t(v.x));
-                acc[1] = __vmaxs4(acc[1], uint32_t(v.y));
-                acc[2] = __vmaxs4(acc[2], uint32_t(v.z));
-                acc[3] = __vmaxs4(acc[3], uint32_t(v.w));
+            v[kTaps] = lowest;
+#pragma unroll
+            for (int t = 0; t < kTaps; t += 2) {
+                acc.take(v[t], v[t + 1]);
+            }
+        } else {
+            const int taps = a.kernel[0] * a.kernel[1];
+            for (int t = 0; t < taps; t += 2) {
+                const int4 p = tap(iy0 + t / a.kernel[1], ix0 + t % a.kernel[1]);
+                const int4 q = t + 1 < taps ? tap(iy0 + (t + 1) / a.kernel[1], ix0 + (t + 1) % a.kernel[1]) : lowest;
+                acc.take(p, q);
             }
         }
-        reinterpret_cast<int4 *>(out + ((int64_t(n) * OH + oy) * OW + ox) * C)[g] =
-            make_int4(int(acc[0]), int(acc[1]), int(acc[2]), int(acc[3]));
+        reinterpret_cast<int4 *>(out + ((int64_t(n) * OH + oy) * OW + ox) * C)[g] = acc.packed();
+    }
+}
+
+// The 3x3 window with stride 2 (the stem pool of the residual networks): one thread makes two horizontally
+// adjacent outputs, whose windows share a column, from 15 loads instead of 18.  OW must be even.
+__global__ void maxPool3x3s2PairKernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, int64_t total, int H,
+                                       int W, int C, int OH, int OW, int padTop, int padLeft) {
+    const int groups = C >> 4, pairs = OW >> 1;
+    const int4 lowest = make_int4(int(0x80808080u), int(0x80808080u), int(0x80808080u), int(0x80808080u));
+    for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += int64_t(gridDim.x) * blockDim.x) {
+        const int g = int(e % groups);
+        int64_t pix = e / groups;
+        const int ox = int(pix % pairs) * 2;
+        pix /= pairs;
+        const int oy = int(pix % OH);
+        const int n = int(pix / OH);
+        const int iy0 = oy * 2 - padTop, ix0 = ox * 2 - padLeft;
+        const int4 *image = reinterpret_cast<const int4 *>(in + int64_t(n) * H * W * C) + g;
+        int4 v[3][5];
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+#pragma unroll
+            for (int kx = 0; kx < 5; ++kx) {
+                const int y = iy0 + ky, x = ix0 + kx;
+                v[ky][kx] = (unsigned(y) < unsigned(H) && unsigned(x) < unsigned(W))
+                                ? __ldg(image + (int64_t(y) * W + x) * groups)
+                                : lowest;
+            }
+        }
+        PoolAcc left, right, shared;
+        shared.take(v[0][2], v[1][2]);
+        shared.take(v[2][2], lowest);
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+            left.take(v[ky][0], v[ky][1]);
+            right.take(v[ky][3], v[ky][4]);
+        }
+        left.take(shared);
+        right.take(shared);
+        int4 *o = reinterpret_cast<int4 *>(out + ((int64_t(n) * OH + oy) * OW + ox) * C) + g;
+        o[0] = left.packed();
+        o[groups] = right.packed();
     }
 }
 
@@ -266,9 +359,23 @@ int avgPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t
 
 int maxPoolI8(const TView &in, const TView &out, const PoolAttr &a, cudaStream_t s) {
     const int64_t total = int64_t(out.dims[0]) * out.dims[1] * out.dims[2] * (out.dims[3] >> 4);
-    maxPoolI8Kernel<<<gridFor(total, kThreads, 16), kThreads, 0, s>>>(
-        reinterpret_cast<const int8_t *>(in.ptr), reinterpret_cast<int8_t *>(out.ptr), total, int(in.dims[1]),
-        int(in.dims[2]), int(in.dims[3]), int(out.dims[1]), int(out.dims[2]), a);
+    const auto launch = [&](auto kernel) {
+        kernel<<<gridFor(total, kThreads, 16), kThreads, 0, s>>>(
+            reinterpret_cast<const int8_t *>(in.ptr), reinterpret_cast<int8_t *>(out.ptr), total, int(in.dims[1]),
+            int(in.dims[2]), int(in.dims[3]), int(out.dims[1]), int(out.dims[2]), a);
+    };
+    if (a.kernel[0] == 3 && a.kernel[1] == 3 && a.stride[0] == 2 && a.stride[1] == 2 && out.dims[2] % 2 == 0) {
+        const int64_t pairs = total / 2;
+        maxPool3x3s2PairKernel<<<gridFor(pairs, kThreads, 16), kThreads, 0, s>>>(
+            reinterpret_cast<const int8_t *>(in.ptr), reinterpret_cast<int8_t *>(out.ptr), pairs, int(in.dims[1]),
+            int(in.dims[2]), int(in.dims[3]), int(out.dims[1]), int(out.dims[2]), a.pad[0], a.pad[2]);
+    } else if (a.kernel[0] == 3 && a.kernel[1] == 3) {
+        launch(maxPoolI8Kernel<3, 3>);
+    } else if (a.kernel[0] == 2 && a.kernel[1] == 2) {
+        launch(maxPoolI8Kernel<2, 2>);
+    } else {
+        launch(maxPoolI8Kernel<0, 0>);
+    }
     return finish("MAX_POOL2D");
 }
 

@@ -303,6 +303,12 @@ def test_avg_pool2d(mlel, case):
 @pytest.mark.parametrize("case", [
     ((1, 16, 16, 3), (2, 2), (2, 2), (0, 0, 0, 0)), ((2, 9, 9, 5), (3, 3), (2, 2), (1, 1, 1, 1)),
     ((1, 7, 5, 2), (3, 2), (1, 1), (1, 0, 0, 1)), ((2, 56, 56, 64), (3, 3), (2, 2), (1, 1, 1, 1)),
+    # the 16-channel-group kernel: its 2x2 variant, and the any-window variant with an even and an odd tap count
+    ((2, 12, 12, 16), (2, 2), (2, 2), (0, 0, 0, 0)), ((1, 9, 10, 32), (3, 2), (1, 2), (1, 0, 0, 1)),
+    ((1, 8, 8, 48), (5, 5), (1, 1), (2, 2, 2, 2)),
+    # 3x3: stride 1, stride 2 with an odd output width (one output per thread), stride 2 without padding (two)
+    ((1, 10, 10, 16), (3, 3), (1, 1), (1, 1, 1, 1)), ((1, 9, 9, 16), (3, 3), (2, 2), (1, 1, 1, 1)),
+    ((2, 9, 13, 32), (3, 3), (2, 2), (0, 0, 0, 0)),
 ])
 def test_max_pool2d(mlel, case):
     shape, k, s, p = case
