@@ -222,11 +222,11 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
         // pixel tile fastest, then channel tile: a CTA's consecutive tiles mostly share their channels, so the
         // per-channel constants are reloaded rarely
-        int64_t tt = t;
-        const int m0 = int(tt % pTiles) * BNP;
-        tt /= pTiles;
-        const int c0 = int(tt % cTiles) * kOcTile;
-        const int batch = int(tt / cTiles);
+        uint32_t tt = uint32_t(t); // the launcher refuses 2^31 tiles and more: 32-bit divisions
+        const int m0 = int(tt % uint32_t(pTiles)) * BNP;
+        tt /= uint32_t(pTiles);
+        const int c0 = int(tt % uint32_t(cTiles)) * kOcTile;
+        const int batch = int(tt / uint32_t(cTiles));
         const uint32_t buf = tileCount & 1u;
         const uint32_t par = (tileCount >> 1) & 1u;
         const int oc = c0 + quarter * 32 + lane;
@@ -264,8 +264,9 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 const int64_t m = int64_t(m0) + threadIdx.x;
                 int c = baseClass;
                 if (m < p.M) {
-                    const int rem = int(m % (int64_t(p.OH) * p.OW));
-                    c = int(__ldg(p.rowClass + rem / p.OW)) * p.numColClasses + int(__ldg(p.colClass + rem % p.OW));
+                    // m < 2^31 and the output plane is smaller: 32-bit divisions (a 64-bit one is a long subroutine)
+                const uint32_t rem = uint32_t(m) % (uint32_t(p.OH) * uint32_t(p.OW));
+                    c = int(__ldg(p.rowClass + rem / uint32_t(p.OW))) * p.numColClasses + int(__ldg(p.colClass + rem % uint32_t(p.OW)));
                 }
                 cls[threadIdx.x] = uint8_t(c);
             }
@@ -398,12 +399,13 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     const int pTiles = (p.M + BNP - 1) / BNP;
     const int cTiles = (p.N + kOcTile - 1) / kOcTile;
     const int64_t numTiles = int64_t(pTiles) * cTiles * p.batches;
-    const auto tileOf = [&](int64_t t) {
+    const auto tileOf = [&](int64_t tile) {
+        uint32_t t = uint32_t(tile); // the launcher refuses 2^31 tiles and more: 32-bit divisions
         OcTile c;
-        c.m0 = int(t % pTiles) * BNP;
-        t /= pTiles;
-        c.c0 = int(t % cTiles) * kOcTile;
-        c.batch = int(t / cTiles);
+        c.m0 = int(t % uint32_t(pTiles)) * BNP;
+        t /= uint32_t(pTiles);
+        c.c0 = int(t % uint32_t(cTiles)) * kOcTile;
+        c.batch = int(t / uint32_t(cTiles));
         return c;
     };
 
@@ -605,6 +607,10 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
         configured = true;
     }
     const int64_t tiles = int64_t((p.M + BNP - 1) / BNP) * ((p.N + kOcTile - 1) / kOcTile) * p.batches;
+    if (tiles >= (int64_t(1) << 31)) {
+        setLastError("channel-major int8 GEMM: too many tiles");
+        return MLEL_ERROR_UNKNOWN;
+    }
     const int grid = int(tiles < smCount() ? tiles : smCount());
     const cudaError_t err = launchDependent(kernel, grid, ocThreads(EW, X_MODE == kXGather), smemBytes, s, maps.x, maps.w,
                                             maps.c, maps.d, p);

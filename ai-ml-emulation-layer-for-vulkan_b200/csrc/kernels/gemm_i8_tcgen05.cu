@@ -61,17 +61,30 @@ struct __align__(8) PipeBarriers {
     uint32_t pad;
 };
 
-// Constants of the main RESCALE stage for one output column (see FastRescale): two 16-byte shared-memory reads
-// per element, by shared address.
+// Constants of the main RESCALE stage for one output column (see FastRescale): two shared-memory reads per
+// element, by shared address.  A table is built in one of two forms.  General: {mult, corr0, rnLo, rnHi} with the
+// rounding constant for v < zpIn (input zero point folded in).  High-word form, when every shift of the table is
+// at least 32 and the corrections are small (see scaleHigh): {mult, corr0 - zpIn, rnM} with the rounding constant
+// without the zero-point fold.
 struct __align__(16) ColConst {
     int32_t mult;
-    int32_t corr0;       // correction of the most common border class for this column
-    uint32_t rnLo, rnHi; // rounding constant for v < zpIn (input zero point folded in)
+    int32_t corr;        // general: correction of the most common border class; high-word form: that minus zpIn
+    uint32_t rnLo, rnHi; // rounding constant (see above)
     int32_t s2;          // max(shift - 32, 0)
     uint32_t bump;       // what the constant for v >= zpIn adds: 2^31 with double rounding and shift > 31, else 0
     int32_t s1;          // min(shift, 32)
-    int32_t pad;
+    int32_t corr0;       // correction of the most common border class (what a border pixel swaps for its own)
 };
+
+// High word of (accumulator + correction - zpIn) * mult + rounding: with x = v - zpIn the double-rounding test
+// v >= zpIn is the sign of x, and bumpMask (2^31 or 0) & ~x adds the 2^31 for x >= 0.  The caller shifts the high
+// word by shift - 32.  Exact while x does not overflow, which the host's bound on the corrections guarantees.
+__device__ __forceinline__ int32_t scaleHigh(int32_t x, int32_t mult, uint64_t rn, uint32_t bumpMask) {
+    const uint64_t prod = uint64_t(int64_t(x) * int64_t(mult));
+    const uint32_t extra = ~uint32_t(x) & bumpMask;
+    const uint64_t sum = prod + rn + uint64_t(extra);
+    return int32_t(uint32_t(sum >> 32));
+}
 
 __device__ __forceinline__ void ldsV2(uint32_t addr, uint32_t &a, uint32_t &b) {
     asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr));
@@ -120,16 +133,17 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
     const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp;
     const uint32_t tabAddr = smemAddr(colTab);
     volatile uint32_t *fastFlag = &bars->pad; // 1: every column of the table has a shift of at least 32
-    bool fast = false;
+    bool fast = false, high = false; // forms of the table: see ColConst
+    const uint32_t bumpMask = p.epi.main.doubleRound != 0 ? 0x80000000u : 0u;
     const int32_t loMain = p.epi.main.lo, hiMain = p.epi.main.hi;
     uint32_t tileCount = 0;
     int tabN0 = -1, tabBatch = -1; // what the shared constants table was built for
     for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
-        int64_t tt = t;
-        const int n0 = int(tt % nTiles) * BN;
-        tt /= nTiles;
-        const int m0 = int(tt % mTiles) * BM;
-        const int batch = int(tt / mTiles);
+        uint32_t tt = uint32_t(t); // the launcher refuses 2^31 tiles and more: 32-bit divisions
+        const int n0 = int(tt % uint32_t(nTiles)) * BN;
+        tt /= uint32_t(nTiles);
+        const int m0 = int(tt % uint32_t(mTiles)) * BM;
+        const int batch = int(tt / uint32_t(mTiles));
         const uint32_t buf = tileCount & 1u;
         const int32_t *corrBatch = p.corr + (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0);
         // Per-column constants shared by the 128 rows of the tile: the main RESCALE stage and the correction
@@ -140,22 +154,36 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                 *fastFlag = 1;
             }
             epilogueSync();
+            FastRescale f{};
+            int32_t corr0 = 0;
             if (threadIdx.x < BN) {
                 const int col = n0 + int(threadIdx.x);
                 const int ci = (p.epi.main.perChannel && col < p.N) ? col : 0;
-                const FastRescale f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)),
-                                                      zpMain, p.epi.main.doubleRound != 0);
-                ColConst c;
-                c.mult = f.mult, c.rnLo = f.rnLo, c.rnHi = f.rnHi, c.s1 = f.s1, c.s2 = f.s2, c.pad = 0;
-                c.bump = f.rpLo - f.rnLo; // (rp - rn) mod 2^32: 0 or 2^31
+                f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)), zpMain,
+                                    p.epi.main.doubleRound != 0);
                 if (f.s1 != 32) {
                     *fastFlag = 0; // a shift below 32 in this tile: the low word of the product matters
                 }
-                c.corr0 = col < p.N ? __ldg(corrBatch + int64_t(p.baseClass) * p.N + col) : 0;
-                colTab[threadIdx.x] = c;
+                corr0 = col < p.N ? __ldg(corrBatch + int64_t(p.baseClass) * p.N + col) : 0;
             }
             epilogueSync();
             fast = *fastFlag != 0;
+            high = fast && p.corrSmall != 0 && !RESIDUAL;
+            if (threadIdx.x < BN) {
+                ColConst c;
+                c.mult = f.mult, c.s1 = f.s1, c.s2 = f.s2, c.corr0 = corr0;
+                c.bump = f.rpLo - f.rnLo; // (rp - rn) mod 2^32: 0 or 2^31
+                if (high) {
+                    const bool twoRounds = p.epi.main.doubleRound != 0;
+                    const uint64_t rn = (uint64_t(1) << (f.s1 + f.s2 - 1)) - (twoRounds ? (uint64_t(1) << 30) : 0);
+                    c.corr = int32_t(uint32_t(corr0) - uint32_t(f.zpIn));
+                    c.rnLo = uint32_t(rn), c.rnHi = uint32_t(rn >> 32);
+                } else {
+                    c.corr = corr0, c.rnLo = f.rnLo, c.rnHi = f.rnHi;
+                }
+                colTab[threadIdx.x] = c;
+            }
+            epilogueSync();
             tabN0 = n0;
             tabBatch = batch;
         }
@@ -163,8 +191,9 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
         const bool rowValid = m < p.M;
         int cls = p.baseClass;
         if (p.rowClass != nullptr && rowValid) {
-            const int rem = int(m % (int64_t(p.OH) * p.OW));
-            cls = int(__ldg(p.rowClass + rem / p.OW)) * p.numColClasses + int(__ldg(p.colClass + rem % p.OW));
+            // m < 2^31 and the output plane is smaller: 32-bit divisions (a 64-bit one is a long subroutine)
+                const uint32_t rem = uint32_t(m) % (uint32_t(p.OH) * uint32_t(p.OW));
+            cls = int(__ldg(p.rowClass + rem / uint32_t(p.OW))) * p.numColClasses + int(__ldg(p.colClass + rem % uint32_t(p.OW)));
         }
         const int64_t outRow = (int64_t(batch) * p.M + m) * p.ldOut;
 
@@ -219,37 +248,55 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                 }
             }
             uint32_t packed[4];
+            if (!RESIDUAL && high) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                int32_t y[4];
+                for (int q = 0; q < 4; ++q) {
+                    int32_t y[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int j = 4 * q + e;
-                    uint32_t mult, corr0, rnLo, rnHi, s2, bump;
-                    ldsV4(tabAddr + uint32_t(cl + j) * 32u, mult, corr0, rnLo, rnHi);
-                    ldsV2(tabAddr + uint32_t(cl + j) * 32u + 16u, s2, bump);
-                    const int32_t v = int32_t(acc[j] + corr0);
-                    // the double-rounding choice is the third input of the 64-bit addition after the multiply
-                    const uint64_t sum = uint64_t(int64_t(v) * int64_t(int32_t(mult))) + ((uint64_t(rnHi) << 32) | rnLo) +
-                                         uint64_t(v >= zpMain ? bump : 0u);
-                    int32_t q32;
-                    if (fast) {
-                        q32 = int32_t(uint32_t(sum >> 32)); // shifts of 32 and more only see the high word
-                    } else {
-                        const uint32_t s1 = uint32_t(ldsS32(tabAddr + uint32_t(cl + j) * 32u + 24u));
-                        q32 = int32_t(__funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), s1));
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = 4 * q + e;
+                        uint32_t mult, corrX, rnLo, rnHi;
+                        ldsV4(tabAddr + uint32_t(cl + j) * 32u, mult, corrX, rnLo, rnHi);
+                        const int32_t s2 = ldsS32(tabAddr + uint32_t(cl + j) * 32u + 16u);
+                        const int32_t h = scaleHigh(int32_t(acc[j] + corrX), int32_t(mult), (uint64_t(rnHi) << 32) | rnLo,
+                                                    bumpMask);
+                        y[e] = min(__viaddmax_s32(h >> s2, outZpMain, loMain), hiMain);
                     }
-                    int32_t r = min(__viaddmax_s32(q32 >> s2, outZpMain, loMain), hiMain);
-                    if (RESIDUAL) {
-                        const int32_t ta = fastRescale(fa, r, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
-                        const int32_t sv = int32_t(int8_t(sc[q] >> (8 * e)));
-                        const int32_t tb = fastRescale(fb, sv, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
-                        r = fastRescale(fo, int32_t(uint32_t(ta) + uint32_t(tb)), p.epi.out.outZp, p.epi.out.lo,
-                                        p.epi.out.hi);
-                    }
-                    y[e] = r;
+                    packed[q] = pack4(y[0], y[1], y[2], y[3]);
                 }
-                packed[q] = pack4(y[0], y[1], y[2], y[3]);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    int32_t y[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = 4 * q + e;
+                        uint32_t mult, corr0, rnLo, rnHi, s2, bump;
+                        ldsV4(tabAddr + uint32_t(cl + j) * 32u, mult, corr0, rnLo, rnHi);
+                        ldsV2(tabAddr + uint32_t(cl + j) * 32u + 16u, s2, bump);
+                        const int32_t v = int32_t(acc[j] + corr0);
+                        // the double-rounding choice is the third input of the 64-bit addition after the multiply
+                        const uint64_t sum = uint64_t(int64_t(v) * int64_t(int32_t(mult))) + ((uint64_t(rnHi) << 32) | rnLo) +
+                                             uint64_t(v >= zpMain ? bump : 0u);
+                        int32_t q32;
+                        if (fast) {
+                            q32 = int32_t(uint32_t(sum >> 32)); // shifts of 32 and more only see the high word
+                        } else {
+                            const uint32_t s1 = uint32_t(ldsS32(tabAddr + uint32_t(cl + j) * 32u + 24u));
+                            q32 = int32_t(__funnelshift_rc(uint32_t(sum), uint32_t(sum >> 32), s1));
+                        }
+                        int32_t r = min(__viaddmax_s32(q32 >> s2, outZpMain, loMain), hiMain);
+                        if (RESIDUAL) {
+                            const int32_t ta = fastRescale(fa, r, p.epi.a.outZp, p.epi.a.lo, p.epi.a.hi);
+                            const int32_t sv = int32_t(int8_t(sc[q] >> (8 * e)));
+                            const int32_t tb = fastRescale(fb, sv, p.epi.b.outZp, p.epi.b.lo, p.epi.b.hi);
+                            r = fastRescale(fo, int32_t(uint32_t(ta) + uint32_t(tb)), p.epi.out.outZp, p.epi.out.lo,
+                                            p.epi.out.hi);
+                        }
+                        y[e] = r;
+                    }
+                    packed[q] = pack4(y[0], y[1], y[2], y[3]);
+                }
             }
             if (vec) {
                 *reinterpret_cast<int4 *>(dst) = make_int4(int(packed[0]), int(packed[1]), int(packed[2]), int(packed[3]));
@@ -276,11 +323,11 @@ __device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarrier
     const int row = quarter * 32 + lane;
     uint32_t tileCount = 0;
     for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
-        int64_t tt = t;
-        const int n0 = int(tt % nTiles) * BN;
-        tt /= nTiles;
-        const int m0 = int(tt % mTiles) * BM;
-        const int batch = int(tt / mTiles);
+        uint32_t tt = uint32_t(t); // the launcher refuses 2^31 tiles and more: 32-bit divisions
+        const int n0 = int(tt % uint32_t(nTiles)) * BN;
+        tt /= uint32_t(nTiles);
+        const int m0 = int(tt % uint32_t(mTiles)) * BM;
+        const int batch = int(tt / uint32_t(mTiles));
         const uint32_t buf = tileCount & 1u;
         const int64_t m = int64_t(m0) + row;
         const bool rowValid = m < p.M;
@@ -288,8 +335,9 @@ __device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarrier
         if (corr != nullptr) {
             int cls = 0;
             if (p.rowClass != nullptr && rowValid) {
-                const int rem = int(m % (int64_t(p.OH) * p.OW));
-                cls = int(__ldg(p.rowClass + rem / p.OW)) * p.numColClasses + int(__ldg(p.colClass + rem % p.OW));
+                // m < 2^31 and the output plane is smaller: 32-bit divisions (a 64-bit one is a long subroutine)
+                const uint32_t rem = uint32_t(m) % (uint32_t(p.OH) * uint32_t(p.OW));
+                cls = int(__ldg(p.rowClass + rem / uint32_t(p.OW))) * p.numColClasses + int(__ldg(p.colClass + rem % uint32_t(p.OW)));
             }
             corr += (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0) + int64_t(cls) * p.N;
         }
@@ -406,12 +454,13 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     const int mTiles = (p.M + BM - 1) / BM;
     const int nTiles = (p.N + BN - 1) / BN;
     const int64_t numTiles = int64_t(mTiles) * nTiles * p.batches;
-    const auto tileOf = [&](int64_t t) {
+    const auto tileOf = [&](int64_t tile) {
+        uint32_t t = uint32_t(tile); // the launcher refuses 2^31 tiles and more: 32-bit divisions
         TileCoord c;
-        c.n0 = int(t % nTiles) * BN;
-        t /= nTiles;
-        c.m0 = int(t % mTiles) * BM;
-        c.batch = int(t / mTiles);
+        c.n0 = int(t % uint32_t(nTiles)) * BN;
+        t /= uint32_t(nTiles);
+        c.m0 = int(t % uint32_t(mTiles)) * BM;
+        c.batch = int(t / uint32_t(mTiles));
         return c;
     };
 
@@ -565,10 +614,11 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                 const bool rowValid = m < p.M;
                 int n = 0, oy = 0, ox = 0;
                 if (rowValid) {
-                    n = int(m / (int64_t(p.OH) * p.OW));
-                    const int rem = int(m - int64_t(n) * p.OH * p.OW);
-                    oy = rem / p.OW;
-                    ox = rem - oy * p.OW;
+                    const uint32_t plane = uint32_t(p.OH) * uint32_t(p.OW); // m < 2^31: 32-bit divisions
+                    n = int(uint32_t(m) / plane);
+                    const uint32_t rem = uint32_t(m) - uint32_t(n) * plane;
+                    oy = int(rem / uint32_t(p.OW));
+                    ox = int(rem) - oy * p.OW;
                 }
                 const int iy0 = oy * p.strideY - p.padTop;
                 const int ix0 = ox * p.strideX - p.padLeft;
@@ -655,6 +705,10 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8
         configured = true;
     }
     const int64_t tiles = int64_t((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batches;
+    if (tiles >= (int64_t(1) << 31)) {
+        setLastError("tcgen05 int8 GEMM: too many tiles");
+        return MLEL_ERROR_UNKNOWN;
+    }
     const int grid = int(tiles < smCount() ? tiles : smCount()); // persistent: one CTA per SM
     const cudaError_t err = launchDependent(kernel, grid, A_MODE != kAGather ? kThreadsTma : kThreadsGather, smemBytes, s, mapA, mapB, p);
     if (err != cudaSuccess) {

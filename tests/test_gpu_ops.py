@@ -37,6 +37,10 @@ CONV_CASES = [
     (1, 12, 12, 6, 7, 3, 2, 1, 2, -128, 5),
     (1, 10, 11, 5, 3, 1, 0, 1, 1, 127, -7),
     (2, 15, 15, 3, 9, 7, 3, 2, 1, -3, 0),
+    # an RGB stem over several tiles and images, odd sizes (windows start every 8 bytes of the padded copy:
+    # even and odd pixels take turns); one and two channels the same way
+    (3, 33, 37, 3, 64, 7, 3, 2, 1, 5, 0),
+    (2, 21, 18, 1, 16, 5, 2, 2, 1, -9, 0),
     (1, 14, 14, 16, 32, 3, 1, 1, 1, -20, 0),
     (2, 7, 7, 64, 64, 1, 0, 1, 1, -20, 0),
     (1, 56, 56, 64, 64, 3, 1, 1, 1, -3, 0),   # configuration 0
