@@ -222,11 +222,11 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
         // pixel tile fastest, then channel tile: a CTA's consecutive tiles mostly share their channels, so the
         // per-channel constants are reloaded rarely
-        uint32_t tt = uint32_t(t); // the launcher refuses 2^31 tiles and more: 32-bit divisions
-        const int m0 = int(tt % uint32_t(pTiles)) * BNP;
-        tt /= uint32_t(pTiles);
-        const int c0 = int(tt % uint32_t(cTiles)) * kOcTile;
-        const int batch = int(tt / uint32_t(cTiles));
+        // the launcher refuses 2^31 tiles and more: divisions by multiply-high (see FastDiv)
+        const uint32_t overP = fastDiv(uint32_t(t), p.divTiles0), overC = fastDiv(overP, p.divTiles1);
+        const int m0 = int(uint32_t(t) - overP * uint32_t(pTiles)) * BNP;
+        const int c0 = int(overP - overC * uint32_t(cTiles)) * kOcTile;
+        const int batch = int(overC);
         const uint32_t buf = tileCount & 1u;
         const uint32_t par = (tileCount >> 1) & 1u;
         const int oc = c0 + quarter * 32 + lane;
@@ -264,9 +264,9 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 const int64_t m = int64_t(m0) + threadIdx.x;
                 int c = baseClass;
                 if (m < p.M) {
-                    // m < 2^31 and the output plane is smaller: 32-bit divisions (a 64-bit one is a long subroutine)
-                const uint32_t rem = uint32_t(m) % (uint32_t(p.OH) * uint32_t(p.OW));
-                    c = int(__ldg(p.rowClass + rem / uint32_t(p.OW))) * p.numColClasses + int(__ldg(p.colClass + rem % uint32_t(p.OW)));
+                    const uint32_t rem = uint32_t(m) - fastDiv(uint32_t(m), p.divPlane) * p.divPlane.d; // pixel inside its image
+                    const uint32_t oy = fastDiv(rem, p.divOW);
+                    c = int(__ldg(p.rowClass + oy)) * p.numColClasses + int(__ldg(p.colClass + (rem - oy * uint32_t(p.OW))));
                 }
                 cls[threadIdx.x] = uint8_t(c);
             }
@@ -400,12 +400,12 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     const int cTiles = (p.N + kOcTile - 1) / kOcTile;
     const int64_t numTiles = int64_t(pTiles) * cTiles * p.batches;
     const auto tileOf = [&](int64_t tile) {
-        uint32_t t = uint32_t(tile); // the launcher refuses 2^31 tiles and more: 32-bit divisions
+        // the launcher refuses 2^31 tiles and more: divisions by multiply-high (see FastDiv)
+        const uint32_t overP = fastDiv(uint32_t(tile), p.divTiles0), overC = fastDiv(overP, p.divTiles1);
         OcTile c;
-        c.m0 = int(t % uint32_t(pTiles)) * BNP;
-        t /= uint32_t(pTiles);
-        c.c0 = int(t % uint32_t(cTiles)) * kOcTile;
-        c.batch = int(t / uint32_t(cTiles));
+        c.m0 = int(uint32_t(tile) - overP * uint32_t(pTiles)) * BNP;
+        c.c0 = int(overP - overC * uint32_t(cTiles)) * kOcTile;
+        c.batch = int(overC);
         return c;
     };
 
@@ -454,9 +454,9 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                 // im2col mode: first tap of the tile's first window, and the running position on the K axis
                 int w0 = 0, h0 = 0, n0 = 0, kx = 0, ky = 0, cb = 0;
                 if (X_MODE == kXIm2col) {
-                    n0 = tc.m0 / (p.OH * p.OW);
+                    n0 = int(fastDiv(uint32_t(tc.m0), p.divPlane));
                     const int rem = tc.m0 - n0 * p.OH * p.OW;
-                    const int oy = rem / p.OW;
+                    const int oy = int(fastDiv(uint32_t(rem), p.divOW));
                     h0 = oy * p.strideY - p.padTop;
                     w0 = (rem - oy * p.OW) * p.strideX - p.padLeft;
                 }
@@ -592,7 +592,10 @@ struct OcMaps {
 };
 
 template <int BNP, int NSTAGE, int EW, int X_MODE, bool RESIDUAL>
-int launchOcMajor(const OcMaps &maps, const GemmI8Params &p, cudaStream_t s) {
+int launchOcMajor(const OcMaps &maps, const GemmI8Params &params, cudaStream_t s) {
+    GemmI8Params p = params;
+    p.divPlane = makeFastDiv(int64_t(p.OH) * p.OW), p.divOW = makeFastDiv(p.OW);
+    p.divTiles0 = makeFastDiv((p.M + BNP - 1) / BNP), p.divTiles1 = makeFastDiv((p.N + kOcTile - 1) / kOcTile);
     constexpr size_t smemBytes = size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * size_t(BNP) * 128 +
                                  (RESIDUAL ? size_t(kResidualTableBytes) : 0) + 2 * BNP +
                                  kTapTabEntries * sizeof(int32_t) + sizeof(OcBarriers) + 1024;

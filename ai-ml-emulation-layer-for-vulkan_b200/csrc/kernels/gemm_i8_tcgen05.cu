@@ -139,11 +139,11 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
     uint32_t tileCount = 0;
     int tabN0 = -1, tabBatch = -1; // what the shared constants table was built for
     for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
-        uint32_t tt = uint32_t(t); // the launcher refuses 2^31 tiles and more: 32-bit divisions
-        const int n0 = int(tt % uint32_t(nTiles)) * BN;
-        tt /= uint32_t(nTiles);
-        const int m0 = int(tt % uint32_t(mTiles)) * BM;
-        const int batch = int(tt / uint32_t(mTiles));
+        // the launcher refuses 2^31 tiles and more: divisions by multiply-high (see FastDiv)
+        const uint32_t overN = fastDiv(uint32_t(t), p.divTiles0), overM = fastDiv(overN, p.divTiles1);
+        const int n0 = int(uint32_t(t) - overN * uint32_t(nTiles)) * BN;
+        const int m0 = int(overN - overM * uint32_t(mTiles)) * BM;
+        const int batch = int(overM);
         const uint32_t buf = tileCount & 1u;
         const int32_t *corrBatch = p.corr + (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0);
         // Per-column constants shared by the 128 rows of the tile: the main RESCALE stage and the correction
@@ -191,9 +191,9 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
         const bool rowValid = m < p.M;
         int cls = p.baseClass;
         if (p.rowClass != nullptr && rowValid) {
-            // m < 2^31 and the output plane is smaller: 32-bit divisions (a 64-bit one is a long subroutine)
-                const uint32_t rem = uint32_t(m) % (uint32_t(p.OH) * uint32_t(p.OW));
-            cls = int(__ldg(p.rowClass + rem / uint32_t(p.OW))) * p.numColClasses + int(__ldg(p.colClass + rem % uint32_t(p.OW)));
+            const uint32_t rem = uint32_t(m) - fastDiv(uint32_t(m), p.divPlane) * p.divPlane.d; // pixel inside its image
+            const uint32_t oy = fastDiv(rem, p.divOW);
+            cls = int(__ldg(p.rowClass + oy)) * p.numColClasses + int(__ldg(p.colClass + (rem - oy * uint32_t(p.OW))));
         }
         const int64_t outRow = (int64_t(batch) * p.M + m) * p.ldOut;
 
@@ -323,11 +323,11 @@ __device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarrier
     const int row = quarter * 32 + lane;
     uint32_t tileCount = 0;
     for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
-        uint32_t tt = uint32_t(t); // the launcher refuses 2^31 tiles and more: 32-bit divisions
-        const int n0 = int(tt % uint32_t(nTiles)) * BN;
-        tt /= uint32_t(nTiles);
-        const int m0 = int(tt % uint32_t(mTiles)) * BM;
-        const int batch = int(tt / uint32_t(mTiles));
+        // the launcher refuses 2^31 tiles and more: divisions by multiply-high (see FastDiv)
+        const uint32_t overN = fastDiv(uint32_t(t), p.divTiles0), overM = fastDiv(overN, p.divTiles1);
+        const int n0 = int(uint32_t(t) - overN * uint32_t(nTiles)) * BN;
+        const int m0 = int(overN - overM * uint32_t(mTiles)) * BM;
+        const int batch = int(overM);
         const uint32_t buf = tileCount & 1u;
         const int64_t m = int64_t(m0) + row;
         const bool rowValid = m < p.M;
@@ -455,12 +455,12 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     const int nTiles = (p.N + BN - 1) / BN;
     const int64_t numTiles = int64_t(mTiles) * nTiles * p.batches;
     const auto tileOf = [&](int64_t tile) {
-        uint32_t t = uint32_t(tile); // the launcher refuses 2^31 tiles and more: 32-bit divisions
+        // the launcher refuses 2^31 tiles and more: divisions by multiply-high (see FastDiv)
+        const uint32_t overN = fastDiv(uint32_t(tile), p.divTiles0), overM = fastDiv(overN, p.divTiles1);
         TileCoord c;
-        c.n0 = int(t % uint32_t(nTiles)) * BN;
-        t /= uint32_t(nTiles);
-        c.m0 = int(t % uint32_t(mTiles)) * BM;
-        c.batch = int(t / uint32_t(mTiles));
+        c.n0 = int(uint32_t(tile) - overN * uint32_t(nTiles)) * BN;
+        c.m0 = int(overN - overM * uint32_t(mTiles)) * BM;
+        c.batch = int(overM);
         return c;
     };
 
@@ -506,9 +506,9 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                 // im2col mode: first tap of the tile's first window, and the running position on the K axis
                 int w0 = 0, h0 = 0, n0 = 0, kx = 0, ky = 0, cb = 0;
                 if (A_MODE == kAIm2col) {
-                    n0 = tc.m0 / (p.OH * p.OW);
+                    n0 = int(fastDiv(uint32_t(tc.m0), p.divPlane));
                     const int rem = tc.m0 - n0 * p.OH * p.OW;
-                    const int oy = rem / p.OW;
+                    const int oy = int(fastDiv(uint32_t(rem), p.divOW));
                     h0 = oy * p.strideY - p.padTop;
                     w0 = (rem - oy * p.OW) * p.strideX - p.padLeft;
                 }
@@ -614,10 +614,9 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                 const bool rowValid = m < p.M;
                 int n = 0, oy = 0, ox = 0;
                 if (rowValid) {
-                    const uint32_t plane = uint32_t(p.OH) * uint32_t(p.OW); // m < 2^31: 32-bit divisions
-                    n = int(uint32_t(m) / plane);
-                    const uint32_t rem = uint32_t(m) - uint32_t(n) * plane;
-                    oy = int(rem / uint32_t(p.OW));
+                    n = int(fastDiv(uint32_t(m), p.divPlane));
+                    const uint32_t rem = uint32_t(m) - uint32_t(n) * p.divPlane.d;
+                    oy = int(fastDiv(rem, p.divOW));
                     ox = int(rem) - oy * p.OW;
                 }
                 const int iy0 = oy * p.strideY - p.padTop;
@@ -691,7 +690,10 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
 // ---- host side --------------------------------------------------------------------------------------------
 
 template <int BN, int NSTAGE, int A_MODE, bool B_MN>
-int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &p, cudaStream_t s) {
+int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &params, cudaStream_t s) {
+    GemmI8Params p = params;
+    p.divPlane = makeFastDiv(int64_t(p.OH) * p.OW), p.divOW = makeFastDiv(p.OW);
+    p.divTiles0 = makeFastDiv((p.N + BN - 1) / BN), p.divTiles1 = makeFastDiv((p.M + BM - 1) / BM);
     constexpr size_t smemBytes =
         size_t(NSTAGE) * (BM * BK + BN * BK) + BN * sizeof(ColConst) + sizeof(PipeBarriers) + 1024 +
         (A_MODE != kAGather ? 0 : (kMaxGatherPieces + kTapTabEntries) * sizeof(int32_t) + 16);

@@ -9,6 +9,28 @@
 
 namespace mlel {
 
+// Division of a number below 2^31 by a constant as a multiply-high and a shift (Granlund and Montgomery): with
+// l = ceil(log2 d), mul = ceil(2^(31 + l) / d) fits 32 bits and n / d = (n * mul) >> (31 + l) for every n < 2^31.
+// The kernels divide tile and pixel indices several times per tile and warp; a hardware-less 32-bit division is
+// some twenty instructions.  mul == 0 stands for d == 1.
+struct FastDiv {
+    uint32_t mul = 0, shift = 0, d = 1;
+};
+inline FastDiv makeFastDiv(int64_t divisor) {
+    FastDiv f;
+    const uint64_t d = divisor > 1 ? uint64_t(divisor) : 1;
+    f.d = uint32_t(d);
+    if (d > 1) {
+        uint32_t l = 0;
+        while ((uint64_t(1) << l) < d) {
+            ++l;
+        }
+        f.mul = uint32_t(((uint64_t(1) << (31 + l)) + d - 1) / d);
+        f.shift = l - 1;
+    }
+    return f;
+}
+
 // Device-side parameters (passed by value to the kernel).
 struct GemmI8Params {
     int32_t M, N, K;     // per batch: rows, columns (output channels), contraction length in bytes
@@ -24,6 +46,9 @@ struct GemmI8Params {
     // in + ((n * H + oy * strideY) * W + ox * strideX) * IC.  Null => gather 16-byte pieces with bounds checks.
     const int32_t *gatherTable;
     int32_t chunkBytes;
+    // filled in by the launchers: divisors OH * OW and OW (pixel index -> image, row, column), and the two inner
+    // extents of the tile index (fastest first)
+    FastDiv divPlane, divOW, divTiles0, divTiles1;
     // im2col TMA mode (set by the launchers): K blocks per tap = ceil(IC / 128), each zero-filled past IC; 0 = off
     int32_t kbPerTap;
     // correction term added to the raw accumulator: corr[(batch,) class, n]

@@ -12,6 +12,7 @@
 #include <utility>
 
 #include "device_common.cuh"
+#include "gemm_i8_tcgen05.hpp"
 
 namespace mlel {
 
@@ -174,6 +175,11 @@ __device__ __forceinline__ void gridDependencySync() {
 }
 
 // Barrier among the epilogue warps only (named barrier 1).
+// n / f.d for n < 2^31 (see FastDiv)
+__device__ __forceinline__ uint32_t fastDiv(uint32_t n, const FastDiv &f) {
+    return f.mul == 0u ? n : __umulhi(n, f.mul) >> f.shift;
+}
+
 __device__ __forceinline__ void epilogueSync() {
     asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
 }
@@ -214,9 +220,9 @@ __device__ __forceinline__ GatherRow gatherRowSetup(const Params &p, int64_t m) 
     r.origin = p.in;
     r.mask = 0;
     if (m < p.M) {
-        const int n = int(m / (int64_t(p.OH) * p.OW));
-        const int rem = int(m - int64_t(n) * p.OH * p.OW);
-        const int oy = rem / p.OW, ox = rem - oy * p.OW;
+        const int n = int(fastDiv(uint32_t(m), p.divPlane));
+        const int rem = int(uint32_t(m) - uint32_t(n) * p.divPlane.d);
+        const int oy = int(fastDiv(uint32_t(rem), p.divOW)), ox = rem - oy * p.OW;
         const int iy0 = oy * p.strideY - p.padTop, ix0 = ox * p.strideX - p.padLeft;
         uint32_t colMask = 0;
         for (int kx = 0; kx < p.KW; ++kx) {
