@@ -128,14 +128,26 @@ __global__ void __launch_bounds__(256) avgPoolI8Kernel(const int8_t *__restrict_
     // in-range taps of the whole window: (rows inside) x (columns inside)
     const int ny = min(iy + a.kernel[0], H) - max(iy, 0), nx = min(ix + a.kernel[1], W) - max(ix, 0);
     const int count = (ny > 0 && nx > 0) ? ny * nx : 0;
-    for (int t = slice; t < taps; t += 8) {
-        const int ky = t / a.kernel[1], kx = t - ky * a.kernel[1];
-        const int y = iy + ky, x = ix + kx;
-        if (y >= 0 && y < H && x >= 0 && x < W && c0 < C) {
-            const uint32_t word = __ldg(reinterpret_cast<const uint32_t *>(in + ((int64_t(n) * H + y) * W + x) * C + c0));
+    // eight taps of this slice at a time: all their loads are issued before the first sum
+    const int8_t *image = in + int64_t(n) * H * W * C + c0;
+    for (int t0 = slice; t0 < taps; t0 += 64) {
+        uint32_t word[8];
+        bool live[8];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                acc[k] += int32_t(int8_t(word >> (8 * k))) - a.inZp;
+        for (int i = 0; i < 8; ++i) {
+            const int t = t0 + 8 * i;
+            const int ky = t / a.kernel[1], kx = t - ky * a.kernel[1];
+            const int y = iy + ky, x = ix + kx;
+            live[i] = t < taps && y >= 0 && y < H && x >= 0 && x < W && c0 < C;
+            word[i] = live[i] ? __ldg(reinterpret_cast<const uint32_t *>(image + (int64_t(y) * W + x) * C)) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (live[i]) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    acc[k] += int32_t(int8_t(word[i] >> (8 * k))) - a.inZp;
+                }
             }
         }
     }

@@ -726,7 +726,10 @@ int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
     GemmI8Params p = q.params;
     p.batches = q.batches;
     CUtensorMap mapA{}, mapB{};
-    const int bn = (!q.bMnMajor && p.N <= 64) ? 64 : 128;
+    // 64-column tiles for narrow outputs, and where 128-column tiles would occupy less than half of the SMs (a
+    // classifier's product of a few rows with a wide weight matrix: twice the CTAs each stream half the weights)
+    const int64_t wideTiles = int64_t((p.M + BM - 1) / BM) * ((p.N + 127) / 128) * q.batches;
+    const int bn = (!q.bMnMajor && (p.N <= 64 || 2 * wideTiles <= smCount())) ? 64 : 128;
     int aMode = kAGather;
     if (q.aMatrix != nullptr) {
         // A: [batches][M][K], K contiguous
