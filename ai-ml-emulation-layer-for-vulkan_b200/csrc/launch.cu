@@ -308,6 +308,9 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
         };
         const int64_t nin = packedBytes(in(0)), nout = packedBytes(out);
         if (nin > 0 && nin == nout && in(0).dtype == out.dtype) {
+            if (in(0).ptr == out.ptr) {
+                return MLEL_SUCCESS; // the session gave both tensors one storage: nothing to move
+            }
             if (cudaMemcpyAsync(out.ptr, in(0).ptr, size_t(nin), cudaMemcpyDeviceToDevice, s) != cudaSuccess) {
                 setLastError("RESHAPE: device-to-device copy failed");
                 return MLEL_ERROR_DEVICE;

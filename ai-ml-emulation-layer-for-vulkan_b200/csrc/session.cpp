@@ -78,6 +78,38 @@ void Session::plan() {
         touch(t, index);
     }
 
+    // With fusion on, a RESHAPE between two packed session tensors of one size moves no bytes: its result shares
+    // its input's storage (the launch skips the copy when both addresses are equal), and the shared storage
+    // lives as long as either tensor.  Chains of such RESHAPEs resolve to the first tensor.
+    std::map<int32_t, int32_t> aliasOf;
+    if (!(pipeline_->flags() & MLEL_PIPELINE_NO_FUSION)) {
+        for (const auto &op : exec) {
+            if (op.kind != OP_RESHAPE || op.in.empty() || op.out.empty()) {
+                continue;
+            }
+            const int32_t src = op.in[0], dst = op.out[0];
+            if (src < 0 || dst < 0 || src == dst) {
+                continue;
+            }
+            const TensorDescriptor &a = pipeline_->tensor(src), &b = pipeline_->tensor(dst);
+            if (a.cls != TensorClass::Session || b.cls != TensorClass::Session || !a.packed() || !b.packed() ||
+                a.dtype != b.dtype || a.sizeBytes() != b.sizeBytes()) {
+                continue;
+            }
+            const auto rootIt = aliasOf.find(src);
+            const int32_t root = rootIt != aliasOf.end() ? rootIt->second : src;
+            if (!ranges.count(root) || !ranges.count(dst)) {
+                continue;
+            }
+            aliasOf[dst] = root;
+            auto &r = ranges[root];
+            const auto d = ranges[dst];
+            r.first = std::min(r.first, d.first);
+            r.second = std::max(r.second, d.second);
+            ranges.erase(dst);
+        }
+    }
+
     // One record per session tensor that needs storage, in session-tensor order.
     planned_.clear();
     for (size_t order = 0; order < sessionTensors.size(); ++order) {
@@ -106,6 +138,12 @@ void Session::plan() {
     offsets_.clear();
     for (const auto &p : planned_) {
         offsets_[p.tensor] = p.offset;
+    }
+    for (const auto &alias : aliasOf) {
+        const auto it = offsets_.find(alias.second);
+        if (it != offsets_.end()) {
+            offsets_[alias.first] = it->second;
+        }
     }
 }
 
