@@ -396,9 +396,9 @@ def main():
             "peak_source": peak_source,
             "conv_ms_per_dispatch": conv_ms,
             # dram__bytes_read.sum + dram__bytes_write.sum per tensor-core launch, from the ncu capture summarised
-            # in profiles/resnet50_n64_launch_list.md (1032 MB over the 54 launches of one 64-image dispatch);
+            # in profiles/resnet50_n64_launch_list.md (1034 MB over the 54 launches of one 64-image dispatch);
             # scaled by the batch, which the activation bytes follow
-            "traffic": 19.1e6 * n / 64.0,
+            "traffic": 19.2e6 * n / 64.0,
             "algorithmic_bytes_per_launch": (1064e6 + 711e6) / 54.0 * n / 64.0,
         },
         "kernel_ms_per_dispatch": {k: round(v, 4) for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1])},
