@@ -41,6 +41,10 @@ CONV_CASES = [
     # even and odd pixels take turns); one and two channels the same way
     (3, 33, 37, 3, 64, 7, 3, 2, 1, 5, 0),
     (2, 21, 18, 1, 16, 5, 2, 2, 1, -9, 0),
+    # rows of whole 32-bit words in the source image: three, two and one channel
+    (2, 20, 16, 3, 16, 7, 3, 2, 1, -7, 0),
+    (1, 12, 12, 2, 8, 3, 1, 1, 1, 4, 0),
+    (3, 9, 16, 1, 8, 3, 1, 2, 1, -1, 0),
     (1, 14, 14, 16, 32, 3, 1, 1, 1, -20, 0),
     (2, 7, 7, 64, 64, 1, 0, 1, 1, -20, 0),
     (1, 56, 56, 64, 64, 3, 1, 1, 1, -3, 0),   # configuration 0
