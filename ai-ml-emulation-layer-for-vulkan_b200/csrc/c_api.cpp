@@ -102,6 +102,31 @@ int mlel_device_error(void) {
     return tcgen05ErrorFlag();
 }
 
+int mlel_set_tuning(const char *key, int value) {
+    return guarded([&] {
+        TensorCoreTuning &t = tensorCoreTuning();
+        const std::string k = key != nullptr ? key : "";
+        const bool width = value == 0 || value == 128 || value == 192 || value == 256;
+        if (k == "pair_kernel") {
+            t.pairKernel = value != 0;
+        } else if (k == "dependent_launch") {
+            t.dependentLaunch = value != 0;
+        } else if (k == "pair_tile_pixels" && width) {
+            t.pairTilePixels = value;
+        } else if (k == "oc_tile_pixels" && width) {
+            t.ocTilePixels = value;
+        } else {
+            setLastError("mlel_set_tuning: unknown key or value: " + k);
+            return int(MLEL_ERROR_UNKNOWN);
+        }
+        return int(MLEL_SUCCESS);
+    });
+}
+
+long long mlel_tensor_core_launches(int kernel) {
+    return kernel >= 0 && kernel < 3 ? g_tensorCoreLaunches[kernel].load(std::memory_order_relaxed) : -1;
+}
+
 int mlel_pipeline_create(uint32_t flags, mlel_pipeline **out) {
     return guarded([&] {
         *out = new mlel_pipeline(flags);

@@ -35,338 +35,13 @@
 #include "gemm_i8_tcgen05.hpp"
 #include "tcgen05_common.cuh"
 
+#include "ocmajor_epilogue.cuh"
+
 namespace mlel {
 namespace {
 
 using namespace tc;
 
-constexpr int kOcTile = 128; // output channels per tile (UMMA M)
-
-// Warp roles of this kernel, EW = number of epilogue warps (8 or 12): 0..EW-1 epilogue (EW / 4 per TMEM lane
-// quarter, each with its own share of the tile's pixels), EW TMA producer, EW + 1 MMA issuer and TMEM owner,
-// EW + 2 and EW + 3 pixel gather (implicit-GEMM variants only).  The register file bounds the count: the
-// epilogue needs about 128 registers per thread, which a CTA of up to 512 threads (EW = 12 with both gather
-// warps) still gets; with 16 epilogue warps it spilled.
-constexpr int kOcGatherThreads = 64;
-// The residual table: 256 rows (main-stage value) of 256 bytes (shortcut byte), rows 260 bytes apart.  With rows
-// of 256 bytes the shared-memory bank of an entry would depend on the shortcut byte alone, and the lanes of a
-// warp -- whose shortcut values are often equal (activations clamped by a ReLU) while their main-stage values
-// differ -- would all hit one bank; the extra word per row spreads them over the banks.
-constexpr int kResidualRowBytes = GemmI8Params::kResidualRowBytes;
-constexpr int kResidualTableBytes = 256 * kResidualRowBytes;
-static_assert(kResidualTableBytes % 16 == 0, "bulk copies move multiples of 16 bytes");
-constexpr int ocThreads(int ew, bool gather) { return (ew + 2) * 32 + (gather ? kOcGatherThreads : 0); }
-
-// Barrier among the epilogue warps only (named barrier 1).
-template <int EW> __device__ __forceinline__ void ocEpilogueSync() {
-    asm volatile("bar.sync 1, %0;" ::"r"(EW * 32) : "memory");
-}
-
-constexpr int kXGather = 0, kXTiled = 1, kXIm2col = 2;
-
-struct __align__(8) OcBarriers {
-    uint64_t full[6];
-    uint64_t empty[6];
-    uint64_t accFull[2];
-    uint64_t accEmpty[2];
-    uint64_t cFull[2];  // the shortcut bytes of a tile have landed in its C/D tile
-    uint64_t cdEmpty[2]; // the store of a C/D tile has finished reading it: the tile may be loaded again
-    uint64_t tabFull;    // the residual table has landed in shared memory
-    uint32_t tmemBase;
-    uint32_t pad;
-};
-
-struct OcTile {
-    int c0, m0, batch;
-};
-
-// Plain (untiled) bulk copy global -> shared, completing on an mbarrier; both addresses and the size are
-// multiples of 16 bytes.
-__device__ __forceinline__ void bulkLoad(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smemAddr(dst)),
-                 "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smemAddr(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, const void *src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
-                     reinterpret_cast<uint64_t>(map)),
-                 "r"(smemAddr(src)), "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
-
-// High 32 bits of x * mult + round(x), x = value - input zero point: product and rounding of a RESCALE whose shift
-// is at least 32, where the result only depends on the high word.  Double rounding adds 2^30 for x >= 0 and
-// subtracts it for x < 0: that is rn = 2^(shift-1) - 2^30 plus 2^31 when the sign bit of x is clear, one logic
-// operation on x (bumpMask = 2^31, or 0 without double rounding) feeding the third input of the 64-bit addition.
-__device__ __forceinline__ int32_t scaleHigh(int32_t x, int32_t mult, uint64_t rn, uint32_t bumpMask) {
-    const uint64_t prod = uint64_t(int64_t(x) * int64_t(mult));
-    const uint32_t extra = ~uint32_t(x) & bumpMask;
-    const uint64_t sum = prod + rn + uint64_t(extra);
-    return int32_t(uint32_t(sum >> 32));
-}
-
-// Shared-memory accesses by 32-bit shared address (a pointer into dynamic shared memory that has been passed
-// through a few functions is otherwise accessed with generic 64-bit loads and stores).
-__device__ __forceinline__ uint32_t ldsU8(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void stsU8(uint32_t addr, int32_t v) {
-    asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-
-// The rest of such a RESCALE: remaining shift, output zero point (wrapping add), clamp.
-__device__ __forceinline__ int32_t finishHigh(int32_t high, int32_t s2, int32_t outZp, int32_t lo, int32_t hi) {
-    return min(__viaddmax_s32(high >> s2, outZp, lo), hi);
-}
-
-// Constants of one epilogue thread (one output channel) and of the per-tensor output stage.
-struct EpiConsts {
-    FastRescale fm;
-    uint64_t rnM;    // scaleHigh: rounding constant without the zero-point fold, for x < 0
-    uint32_t bumpM;  // scaleHigh: 2^31 with double rounding, else 0
-    int32_t corr0;   // correction of the most common border class
-    int32_t corrX;   // corr0 - input zero point: accumulator + corrX is x of scaleHigh
-    int32_t outZpMain, loMain, hiMain;
-    bool fast; // the shift is at least 32 and the corrections are small: see scaleHigh
-};
-
-// 16 pixels of one channel: accumulator slice -> bytes in the C/D tile (column `cd`, rows 128 bytes apart).
-// All shortcut bytes are read before the first result is written: the compiler must assume that a byte store
-// may alias any later load, and 16 load-compute-store chains in a row would run one after the other.
-template <bool RESIDUAL, bool FAST>
-__device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t tab128,
-                                                 uint32_t cd) {
-    constexpr int CH = 8; // pixels per group: enough independent chains, few enough live registers
-#pragma unroll
-    for (int g = 0; g < 16; g += CH) {
-        uint32_t sc[CH];
-        if (RESIDUAL) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-                sc[j] = ldsU8(cd + 128 * (g + j));
-            }
-        }
-        int32_t r[CH];
-#pragma unroll
-        for (int j = 0; j < CH; ++j) {
-            if (FAST) {
-                const int32_t x = int32_t(acc[g + j] + uint32_t(k.corrX));
-                const int32_t high = scaleHigh(x, k.fm.mult, k.rnM, k.bumpM);
-                if (RESIDUAL) {
-                    // the value is only used as a row number of the residual table: clamp(q + zp, lo, hi) - lo is one
-                    // add-min-relu, and the table's base address takes the - lo
-                    r[j] = __viaddmin_s32_relu(high >> k.fm.s2, k.outZpMain - k.loMain, k.hiMain - k.loMain);
-                } else {
-                    r[j] = finishHigh(high, k.fm.s2, k.outZpMain, k.loMain, k.hiMain);
-                }
-            } else {
-                const int32_t v = int32_t(acc[g + j] + uint32_t(k.corr0));
-                r[j] = fastRescale(k.fm, v, k.outZpMain, k.loMain, k.hiMain) - (RESIDUAL ? k.loMain : 0);
-            }
-        }
-        if (RESIDUAL) {
-            // the whole tail -- both input RESCALEs, the ADD, the output RESCALE and its clamp -- is one byte
-            // of the table, addressed by the main stage's value and the shortcut byte
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-                r[j] = int32_t(ldsU8(tab128 + sc[j] + uint32_t(r[j] * kResidualRowBytes)));
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < CH; ++j) {
-            stsU8(cd + 128 * (g + j), r[j]);
-        }
-    }
-}
-
-// cd: shared address of this thread's column of the C/D tile at the slice's first pixel; tab128: shared address
-// of the residual table's row for the lowest main-stage value.
-template <bool RESIDUAL>
-__device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t tab128, uint32_t cd) {
-    if (k.fast) {
-        rescaleSliceImpl<RESIDUAL, true>(acc, k, tab128, cd);
-    } else {
-        rescaleSliceImpl<RESIDUAL, false>(acc, k, tab128, cd);
-    }
-}
-
-// The epilogue warps.  Warp w owns TMEM lanes 32 * (w & 3) .. +31 (output channels) and half of the tile's
-// pixels, which it walks in slices of 16 pixels; the tcgen05.ld of the next slice is in flight while the
-// current one is rescaled.
-template <int BNP, int EW, bool RESIDUAL>
-__device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const GemmI8Params &p, OcBarriers *bars,
-                                                uint8_t *clsTab, const uint8_t *resTab, uint8_t *cdTiles,
-                                                uint32_t tmemBase, int warp, int lane, int64_t numTiles, int pTiles,
-                                                int cTiles) {
-    const int quarter = warp & 3;
-    const int part = warp >> 2;
-    constexpr int kColsPerWarp = BNP / (EW / 4);
-    constexpr int kSteps = kColsPerWarp / 16;
-    static_assert(EW % 4 == 0 && kColsPerWarp * (EW / 4) == BNP && kColsPerWarp % 16 == 0, "pixel shares of the warps");
-    static_assert(kSteps % 2 == 0, "slices are processed in pairs");
-    static_assert(EW * 32 >= BNP, "one thread per pixel fills the class table");
-    EpiConsts k{};
-    k.outZpMain = p.epi.main.outZp, k.loMain = p.epi.main.lo, k.hiMain = p.epi.main.hi;
-    // row of the lowest main-stage value: the element loop counts rows from there
-    const uint32_t tab128 = smemAddr(resTab) + uint32_t((128 + p.epi.main.lo) * kResidualRowBytes);
-    bool tableReady = !RESIDUAL;
-    int curC0 = -1, curBatch = -1;
-    const bool hasClasses = p.rowClass != nullptr;
-    const int baseClass = p.baseClass;
-    const bool storer = warp == 0 && lane == 0; // issues the tile stores and tracks their completion
-    uint32_t tileCount = 0;
-    for (int64_t t = blockIdx.x; t < numTiles; t += gridDim.x, ++tileCount) {
-        // pixel tile fastest, then channel tile: a CTA's consecutive tiles mostly share their channels, so the
-        // per-channel constants are reloaded rarely
-        // the launcher refuses 2^31 tiles and more: divisions by multiply-high (see FastDiv)
-        const uint32_t overP = fastDiv(uint32_t(t), p.divTiles0), overC = fastDiv(overP, p.divTiles1);
-        const int m0 = int(uint32_t(t) - overP * uint32_t(pTiles)) * BNP;
-        const int c0 = int(overP - overC * uint32_t(cTiles)) * kOcTile;
-        const int batch = int(overC);
-        const uint32_t buf = tileCount & 1u;
-        const uint32_t par = (tileCount >> 1) & 1u;
-        const int oc = c0 + quarter * 32 + lane;
-        const bool ocValid = oc < p.N;
-        const bool warpLive = c0 + quarter * 32 < p.N; // else all 32 channels of this warp are past the end
-        const int32_t *corrBatch = p.corr + (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0);
-        if (storer) {
-            // The previous tile's store has read its C/D tile (and so have all before it): that tile may be
-            // filled again, by the next shortcut load or by the epilogue of the next tile.
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-            if (RESIDUAL && tileCount > 0) {
-                mbarArrive(&bars->cdEmpty[buf ^ 1u]);
-            }
-        }
-        if (c0 != curC0 || (p.batchedCorr && batch != curBatch)) {
-            const int ci = (p.epi.main.perChannel && ocValid) ? oc : 0;
-            k.fm = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)), p.epi.main.inZp,
-                                   p.epi.main.doubleRound != 0);
-            k.corr0 = ocValid ? __ldg(corrBatch + int64_t(baseClass) * p.N + oc) : 0;
-            k.corrX = int32_t(uint32_t(k.corr0) - uint32_t(k.fm.zpIn));
-            // shift >= 32 here whenever the constants below are used
-            const bool twoRounds = p.epi.main.doubleRound != 0;
-            const int shiftM = k.fm.s1 + k.fm.s2;
-            k.rnM = (uint64_t(1) << ((shiftM > 0 ? shiftM : 1) - 1)) - (twoRounds ? (uint64_t(1) << 30) : 0);
-            k.bumpM = twoRounds ? 0x80000000u : 0u;
-            k.fast = __all_sync(0xffffffffu, k.fm.s1 == 32) && p.corrSmall != 0;
-            curC0 = c0;
-            curBatch = batch;
-        }
-        uint8_t *cls = clsTab + buf * BNP;
-        if (hasClasses) {
-            // border class of every pixel of the tile; the table alternates with the accumulator, so a warp that
-            // is a tile ahead never overwrites what a slower warp still reads
-            if (threadIdx.x < BNP) {
-                const int64_t m = int64_t(m0) + threadIdx.x;
-                int c = baseClass;
-                if (m < p.M) {
-                    const uint32_t rem = uint32_t(m) - fastDiv(uint32_t(m), p.divPlane) * p.divPlane.d; // pixel inside its image
-                    const uint32_t oy = fastDiv(rem, p.divOW);
-                    c = int(__ldg(p.rowClass + oy)) * p.numColClasses + int(__ldg(p.colClass + (rem - oy * uint32_t(p.OW))));
-                }
-                cls[threadIdx.x] = uint8_t(c);
-            }
-            ocEpilogueSync<EW>();
-        }
-        if (!tableReady) {
-            if (!mbarWait(&bars->tabFull, 0u, 7)) {
-                break;
-            }
-            tableReady = true;
-        }
-        if (RESIDUAL && !mbarWait(&bars->cFull[buf], par, 6)) {
-            break;
-        }
-        if (!mbarWait(&bars->accFull[buf], par, 4)) {
-            break;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t taddr = tmemBase + buf * uint32_t(BNP) + (uint32_t(quarter * 32) << 16) + uint32_t(part * kColsPerWarp);
-        // this thread's column of the C/D tile, at the first pixel of its half
-        const uint32_t cd = smemAddr(cdTiles + buf * (BNP * 128) + (part * kColsPerWarp) * 128 + quarter * 32 + lane);
-        const auto borderFix = [&](uint32_t (&acc)[16], int col) {
-            // pixels of this slice whose window crosses the border take their own class's correction
-            const uint32_t borderMask = __ballot_sync(0xffffffffu, lane < 16 && int(cls[col + (lane & 15)]) != baseClass);
-            if (borderMask != 0 && ocValid) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if ((borderMask >> j) & 1u) {
-                        const int c = int(cls[col + j]);
-                        acc[j] += uint32_t(__ldg(corrBatch + int64_t(c) * p.N + oc)) - uint32_t(k.corr0);
-                    }
-                }
-            }
-            __syncwarp();
-        };
-        uint32_t accA[16], accB[16];
-        // With 12 epilogue warps a thread has 128 registers, which the residual variant's shortcut bytes and a
-        // second accumulator slice in flight do not both fit into.
-        constexpr bool kOneSliceAtATime = RESIDUAL && EW > 8;
-        if (kOneSliceAtATime) {
-#pragma unroll 1
-            for (int st = 0; st < kSteps; ++st) {
-                tmemLoad16(taddr + uint32_t(16 * st), accA);
-                tmemWait16(accA);
-                if (st == kSteps - 1) {
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    if (lane == 0) {
-                        mbarArrive(&bars->accEmpty[buf]);
-                    }
-                }
-                if (hasClasses) {
-                    borderFix(accA, part * kColsPerWarp + 16 * st);
-                }
-                if (warpLive) {
-                    rescaleSlice<RESIDUAL>(accA, k, tab128, cd + uint32_t((16 * st) * 128));
-                }
-            }
-        } else {
-        tmemLoad16(taddr, accA);
-#pragma unroll 1
-        for (int st = 0; st < kSteps; st += 2) {
-            tmemWait16(accA);
-            tmemLoad16(taddr + uint32_t(16 * (st + 1)), accB);
-            if (hasClasses) {
-                borderFix(accA, part * kColsPerWarp + 16 * st);
-            }
-            if (warpLive) {
-                rescaleSlice<RESIDUAL>(accA, k, tab128, cd + uint32_t((16 * st) * 128));
-            }
-            tmemWait16(accB);
-            if (st + 2 < kSteps) {
-                tmemLoad16(taddr + uint32_t(16 * (st + 2)), accA);
-            } else {
-                // this warp's part of the accumulator is in registers: hand the buffer back to the MMA warp
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                if (lane == 0) {
-                    mbarArrive(&bars->accEmpty[buf]);
-                }
-            }
-            if (hasClasses) {
-                borderFix(accB, part * kColsPerWarp + 16 * (st + 1));
-            }
-            if (warpLive) {
-                rescaleSlice<RESIDUAL>(accB, k, tab128, cd + uint32_t((16 * (st + 1)) * 128));
-            }
-        }
-        }
-        // make the tile visible to the TMA unit, then one thread stores it (pixels and channels past the
-        // tensor's end are clipped by the tensor map)
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        ocEpilogueSync<EW>();
-        if (storer) {
-            tmaStore3d(tmapD, cdTiles + buf * (BNP * 128), c0, m0, 0);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-    }
-    if (storer) {
-        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    }
-}
 
 // X_MODE: how the pixel operand arrives: kXGather = gathered from the NHWC input described by p, kXTiled = tmapX
 // is a plain matrix, kXIm2col = tmapX is an im2col map of the NHWC input.
@@ -574,8 +249,10 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         }
     } else {
         // ---------------- epilogue ----------------
-        epilogueOcMajor<BNP, EW, RESIDUAL>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase, warp, lane, numTiles, pTiles,
-                                           cTiles);
+        EpiWalk walk{};
+        walk.first = blockIdx.x, walk.stride = gridDim.x;
+        epilogueOcMajor<BNP, EW, RESIDUAL, kOcTile>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase, warp, lane, numTiles,
+                                                    pTiles, cTiles, walk);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -601,13 +278,8 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &params, cudaStream_t s
                                  kTapTabEntries * sizeof(int32_t) + sizeof(OcBarriers) + 1024;
     static_assert(smemBytes <= 232448, "shared memory per CTA");
     auto kernel = gemmI8OcMajor<BNP, NSTAGE, EW, X_MODE, RESIDUAL>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smemBytes)) != cudaSuccess) {
-            setLastError("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
-            return MLEL_ERROR_DEVICE;
-        }
-        configured = true;
+    if (!allowDynamicSmem(reinterpret_cast<const void *>(kernel), smemBytes)) {
+        return MLEL_ERROR_DEVICE;
     }
     const int64_t tiles = int64_t((p.M + BNP - 1) / BNP) * ((p.N + kOcTile - 1) / kOcTile) * p.batches;
     if (tiles >= (int64_t(1) << 31)) {
@@ -667,6 +339,7 @@ bool gemmI8OcMajorApplies(const GemmI8Problem &q) {
 }
 
 int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
+    g_tensorCoreLaunches[1].fetch_add(1, std::memory_order_relaxed);
     GemmI8Params p = q.params;
     p.batches = q.batches;
     // Pixels per tile.  Wider tiles move less operand data per multiply-accumulate, narrower ones fill the last
@@ -676,10 +349,7 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
     // although single layers timed alone prefer 128 pixels at 7x7 and 256 at 56x56.  Problems of at most 128
     // pixels take the narrow tile.
     int width = p.M <= 128 ? 128 : 192;
-    static const int forced = [] {
-        const char *e = std::getenv("MLEL_OC_TILE_PIXELS");
-        return e != nullptr ? std::atoi(e) : 0;
-    }();
+    const int forced = tensorCoreTuning().ocTilePixels.load(std::memory_order_relaxed);
     if (forced == 128 || forced == 192 || forced == 256) {
         width = forced;
     }

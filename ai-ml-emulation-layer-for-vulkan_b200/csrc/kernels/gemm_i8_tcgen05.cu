@@ -698,13 +698,8 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8
         size_t(NSTAGE) * (BM * BK + BN * BK) + BN * sizeof(ColConst) + sizeof(PipeBarriers) + 1024 +
         (A_MODE != kAGather ? 0 : (kMaxGatherPieces + kTapTabEntries) * sizeof(int32_t) + 16);
     auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_MODE, B_MN>;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smemBytes)) != cudaSuccess) {
-            setLastError("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
-            return MLEL_ERROR_DEVICE;
-        }
-        configured = true;
+    if (!allowDynamicSmem(reinterpret_cast<const void *>(kernel), smemBytes)) {
+        return MLEL_ERROR_DEVICE;
     }
     const int64_t tiles = int64_t((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batches;
     if (tiles >= (int64_t(1) << 31)) {
@@ -722,7 +717,15 @@ int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8
 
 } // namespace
 
+std::atomic<long long> g_tensorCoreLaunches[3];
+
+TensorCoreTuning &tensorCoreTuning() {
+    static TensorCoreTuning t;
+    return t;
+}
+
 int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
+    g_tensorCoreLaunches[0].fetch_add(1, std::memory_order_relaxed);
     GemmI8Params p = q.params;
     p.batches = q.batches;
     CUtensorMap mapA{}, mapB{};
@@ -779,7 +782,11 @@ int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
 
 int tcgen05ErrorFlag() {
     const int v = tc::readErrorWord();
-    return v != 0 ? v : ocMajorErrorWord();
+    if (v != 0) {
+        return v;
+    }
+    const int w = ocMajorErrorWord();
+    return w != 0 ? w : pairErrorWord();
 }
 
 } // namespace mlel

@@ -3,6 +3,7 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 
 #include "kernels.hpp"
@@ -91,6 +92,26 @@ int gemmI8Launch(const GemmI8Problem &problem, cudaStream_t stream);
 bool gemmI8OcMajorApplies(const GemmI8Problem &problem);
 int gemmI8OcMajorLaunch(const GemmI8Problem &problem, cudaStream_t stream);
 int ocMajorErrorWord();
+
+// Paired variant (gemm_i8_pair.cu): two CTAs of a cluster share one 256-channel tile through
+// tcgen05.mma.cta_group::2.  `Applies` tells whether it can take q; Launch sets *taken to false (and returns
+// success) when the driver refuses the tensor maps, so that the caller can use another kernel.
+bool gemmI8PairApplies(const GemmI8Problem &problem);
+int gemmI8PairLaunch(const GemmI8Problem &problem, cudaStream_t stream, bool *taken);
+int pairErrorWord();
+
+// Kernel-selection knobs of the tensor-core launchers (mlel_set_tuning): 0 = the library's own choice.
+struct TensorCoreTuning {
+    std::atomic<int> pairKernel{1};        // 0: never use the paired kernel
+    std::atomic<int> pairTilePixels{0};    // 128, 192 or 256: pixels per tile of the paired kernel
+    std::atomic<int> ocTilePixels{0};      // 128, 192 or 256: pixels per tile of the channel-major kernel
+    std::atomic<int> dependentLaunch{1};   // 0: launch the tensor-core kernels without programmatic dependent launch
+};
+TensorCoreTuning &tensorCoreTuning();
+
+// Launches of the three tensor-core kernels since the library was loaded: 0 pixel-major (gemm_i8_tcgen05.cu),
+// 1 channel-major (gemm_i8_ocmajor.cu), 2 paired (gemm_i8_pair.cu).  Tests use them to see which kernel took a case.
+extern std::atomic<long long> g_tensorCoreLaunches[3];
 
 // Value of the device-side error word written by a bounded wait that ran out (0 = none).
 int tcgen05ErrorFlag();

@@ -108,14 +108,8 @@ int int8MmaPeak(int batches, cudaStream_t stream, float *msOut, double *opsOut) 
         return MLEL_ERROR_UNKNOWN;
     }
     constexpr size_t smemBytes = size_t(kPeakTileA + kPeakTileB) + sizeof(PeakBarriers) + 1024;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(int8MmaPeakKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smemBytes)) !=
-            cudaSuccess) {
-            setLastError("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
-            return MLEL_ERROR_DEVICE;
-        }
-        configured = true;
+    if (!allowDynamicSmem(reinterpret_cast<const void *>(int8MmaPeakKernel), smemBytes)) {
+        return MLEL_ERROR_DEVICE;
     }
     const int grid = smCount();
     cudaEvent_t start = nullptr, stop = nullptr;

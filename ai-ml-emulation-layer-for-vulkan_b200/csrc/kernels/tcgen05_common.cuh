@@ -7,7 +7,9 @@
 
 #include <cstdint>
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
+#include <set>
 #include <string>
 #include <utility>
 
@@ -84,6 +86,26 @@ __device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int cod
     unsigned polls = 0;
     while (!mbarTryWaitHint(bar, parity, 1000u)) {
         if ((++polls & 63u) == 0) {
+            if (clock64() - start > kWaitLimitCycles) {
+                atomicCAS(&g_tcgen05Error, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// The same for a barrier that another CTA of the cluster completes (a remote arrival, a commit issued by the
+// peer, a bulk copy of the peer): polls without a suspend-time hint, because a waiter suspended with a long hint
+// was seen to sleep through such completions until the hint ran out (about 1 us per wait).
+__device__ __forceinline__ bool mbarWaitRemote(uint64_t *bar, uint32_t parity, int code) {
+    if (mbarTryWait(bar, parity)) {
+        return true;
+    }
+    const long long start = clock64();
+    unsigned polls = 0;
+    while (!mbarTryWait(bar, parity)) {
+        if ((++polls & 1023u) == 0) {
             if (clock64() - start > kWaitLimitCycles) {
                 atomicCAS(&g_tcgen05Error, 0, code);
                 return false;
@@ -397,7 +419,7 @@ inline bool makeIm2colMap(CUtensorMap *map, const void *base, int N, int H, int 
 template <class... Params, class... Args>
 inline cudaError_t launchDependent(void (*kernel)(Params...), int grid, int threads, size_t smemBytes, cudaStream_t stream,
                                    Args &&...args) {
-    static const bool disabled = getenv("MLEL_NO_DEPENDENT_LAUNCH") != nullptr;
+    const bool disabled = tensorCoreTuning().dependentLaunch.load(std::memory_order_relaxed) == 0;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(grid));
     cfg.blockDim = dim3(unsigned(threads));
@@ -411,18 +433,43 @@ inline cudaError_t launchDependent(void (*kernel)(Params...), int grid, int thre
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// Number of SMs of the device that is current (cached per device).
 inline int smCount() {
-    static int count = 0;
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> counts[kMaxDevices];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const bool cached = dev >= 0 && dev < kMaxDevices;
+    int count = cached ? counts[dev].load(std::memory_order_relaxed) : 0;
     if (count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || count <= 0) {
             count = kNumSMs;
+        }
+        if (cached) {
+            counts[dev].store(count, std::memory_order_relaxed);
         }
     }
     return count;
 }
 
+// Opts `kernel` in to `bytes` of dynamic shared memory on the device that is current.  The attribute belongs to
+// the (kernel, device) pair, so it is set once for each; safe to call from several host threads.
+inline bool allowDynamicSmem(const void *kernel, size_t bytes) {
+    static std::mutex mutex;
+    static std::set<std::pair<const void *, int>> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mutex);
+    if (done.count({kernel, dev}) != 0) {
+        return true;
+    }
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess) {
+        setLastError("cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed");
+        return false;
+    }
+    done.insert({kernel, dev});
+    return true;
+}
 
 } // namespace tc
 } // namespace mlel

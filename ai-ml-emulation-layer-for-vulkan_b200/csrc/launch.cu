@@ -4,6 +4,7 @@
 // There is no CPU path: every branch ends in a CUDA launch or an error.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <string>
 
 #include "kernels/device_common.cuh"
@@ -25,6 +26,17 @@ ConvAttr convAttr(const OpDesc &op) {
     a.stride[0] = op.i[4], a.stride[1] = op.i[5], a.dilation[0] = op.i[6], a.dilation[1] = op.i[7];
     a.inZp = op.i[8], a.wZp = op.i[9];
     return a;
+}
+
+// Runs q on the paired tensor-core kernel when it applies; *rc is the launch status when the result is true.
+bool tryPairKernel(const GemmI8Problem &q, cudaStream_t s, int *rc) {
+    const bool enabled = tensorCoreTuning().pairKernel.load(std::memory_order_relaxed) != 0;
+    if (!enabled || !gemmI8PairApplies(q)) {
+        return false;
+    }
+    bool taken = false;
+    *rc = gemmI8PairLaunch(q, s, &taken);
+    return taken || *rc != MLEL_SUCCESS;
 }
 
 PoolAttr poolAttr(const OpDesc &op) {
@@ -156,6 +168,10 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     q.bRowBytes = uint64_t(p.K);
     q.bBatchBytes = 0;
     q.bMnMajor = false;
+    int rc = MLEL_SUCCESS;
+    if (tryPairKernel(q, s, &rc)) {
+        return rc;
+    }
     return gemmI8OcMajorApplies(q) ? gemmI8OcMajorLaunch(q, s) : gemmI8Launch(q, s);
 }
 
@@ -203,6 +219,10 @@ int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     q.bRowBytes = uint64_t(p.K);
     q.bBatchBytes = uint64_t(p.K) * uint64_t(p.N);
     q.bMnMajor = false;
+    int rc = MLEL_SUCCESS;
+    if (tryPairKernel(q, s, &rc)) {
+        return rc;
+    }
     return gemmI8Launch(q, s);
 }
 

@@ -294,6 +294,21 @@ int mlel_pipeline_clear_profile(mlel_pipeline *p);
  * denominator of tensor-bound roofline fractions.  Synchronises the stream. */
 int mlel_measure_int8_mma_peak(int batches, void *cuda_stream, float *ms, double *ops);
 
+/* Kernel selection of the tensor-core contractions (no counterpart in the reference; process-wide, takes
+ * effect for kernels enqueued afterwards, results are the same bits whatever is chosen):
+ *   "pair_kernel"       1 (default) lets contractions with more than 128 output channels run on the paired
+ *                       two-CTA kernel, 0 keeps them on the single-CTA kernels;
+ *   "pair_tile_pixels"  0 (default: chosen per problem), 128, 192 or 256 pixels per tile of the paired kernel;
+ *   "oc_tile_pixels"    the same for the channel-major single-CTA kernel;
+ *   "dependent_launch"  1 (default) launches the tensor-core kernels with programmatic dependent launch.
+ * Another key or value: MLEL_ERROR_UNKNOWN. */
+int mlel_set_tuning(const char *key, int value);
+
+/* Diagnostic (no counterpart in the reference): how often the library has enqueued tensor-core kernel
+ * `kernel` since it was loaded -- 0 the pixel-major tcgen05 kernel, 1 the channel-major one, 2 the paired
+ * (two-CTA) one; -1 for another index.  Tests use it to see which kernel took a case. */
+long long mlel_tensor_core_launches(int kernel);
+
 /* Number of kernels one dispatch launches. */
 int mlel_session_launch_count(const mlel_session *s);
 /* Host-buffer convenience used for end-to-end timing: copies `n_in` host inputs to their bound
