@@ -824,6 +824,14 @@ int mlel_cuda_rescale(const mlel_tensor *input, const mlel_tensor *output, const
     });
 }
 
+int mlel_cuda_interleave_columns(const void *staging, void *output, uint64_t rows, uint32_t blocks, uint32_t pitch_bytes,
+                                 const int32_t *first_byte, const int32_t *byte_count, void *cuda_stream) {
+    return guarded([&] {
+        return interleaveColumns(staging, output, int64_t(rows), int32_t(blocks), int32_t(pitch_bytes), first_byte,
+                                 byte_count, static_cast<cudaStream_t>(cuda_stream));
+    });
+}
+
 int mlel_cuda_matmul_rescale(const mlel_tensor *a, const mlel_tensor *b, const mlel_tensor *output, int32_t a_zp,
                              int32_t b_zp, const mlel_tensor *multiplier, const mlel_tensor *shift,
                              int32_t rescale_in_zp, int32_t output_zp, int double_round, int per_channel,

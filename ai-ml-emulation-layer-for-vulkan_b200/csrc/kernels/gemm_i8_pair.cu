@@ -14,10 +14,10 @@
 // window rows per multiply-accumulate.
 //
 // Protocol of a pair (rank 0 = leader, the only CTA that issues MMAs):
-//   full[s]     lives in the leader.  Both producers signal it: every load is the `.cta_group::2` form of the
-//               bulk tensor copy, which may complete on a barrier of the peer CTA; the leader's producer
-//               announces the bytes of both CTAs, the other producer arrives without bytes.  No load is shared
-//               between the CTAs: each fetches its own tiles into its own shared memory.
+//   full[s]     lives in the leader.  The loads of both CTAs complete on it: every load is the `.cta_group::2` form
+//               of the bulk tensor copy, which may complete on a barrier of the peer CTA; the leader's producer
+//               announces the bytes of both CTAs with its one arrival.  No load is shared between the CTAs:
+//               each fetches its own tiles into its own shared memory.
 //   empty[s]    one in each CTA, for that CTA's producer.  The leader commits the stage's MMAs to both, with one
 //               `tcgen05.commit` per barrier (the second one names the peer's barrier by its shared::cluster
 //               address).
@@ -48,6 +48,19 @@ namespace {
 using namespace tc;
 
 constexpr int kPairChannels = 2 * kOcTile; // output channels per tile
+
+#ifdef MLEL_PAIR_TRACE
+#define PAIR_TRACE(role, idx)                                                                                          \
+    do {                                                                                                               \
+        if (pairIdx == 0 && (idx) < 256) {                                                                             \
+            g_pairTrace[rank][role][idx] = clock64();                                                                  \
+        }                                                                                                              \
+    } while (0)
+#else
+#define PAIR_TRACE(role, idx)                                                                                          \
+    do {                                                                                                               \
+    } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t clusterCtaRank() {
     uint32_t r;
@@ -148,7 +161,7 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
-            mbarInit(&bars->full[s], 2u); // the two producers (used in the leader only)
+            mbarInit(&bars->full[s], 1u); // the leader's producer (the barrier is used in the leader only)
             mbarInit(&bars->empty[s], 1u);
         }
         for (int b = 0; b < 2; ++b) {
@@ -214,11 +227,16 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
                     if (!ok) {
                         break;
                     }
+                    PAIR_TRACE(0, 2 * it);
                     const uint32_t fullAddr = fullLeader + uint32_t(s) * uint32_t(sizeof(uint64_t));
                     if (rank == 0) {
+                        // The bytes of both CTAs.  The peer's copies need no arrival of their own: they are issued
+                        // after the peer's empty[s] completed, i.e. after the MMAs that read the stage's previous
+                        // contents, which themselves waited for the previous phase of this barrier; so they can only
+                        // count towards the phase this announcement belongs to (before it, the count of pending
+                        // bytes is transiently negative).  A release-arrival on the leader's barrier per stage was
+                        // measured at about 1000 cycles in the peer's producer, which then paced the whole pair.
                         mbarArriveExpectTx(&bars->full[s], uint32_t(2 * (kTileW + kTileX)));
-                    } else {
-                        mbarArriveCluster(fullAddr);
                     }
                     if (X_MODE == kXIm2col) {
                         tmaLoad3dPair(&tmapW, tilesW + s * kTileW, fullAddr, cb, ky * p.KW + kx, tc.c0);
@@ -240,6 +258,7 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
                         }
                         tmaLoad3dPair(&tmapX, tilesX + s * kTileX, fullAddr, kb * BK, mh, tc.batch);
                     }
+                    PAIR_TRACE(0, 2 * it + 1);
                 }
                 if (RESIDUAL && ok) {
                     // the shortcut bytes of this CTA's 128 channels, once the store that last used the C/D tile has read it
@@ -275,6 +294,7 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
                     if (!ok) {
                         break;
                     }
+                    PAIR_TRACE(1, 2 * it);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t wAddr = smemAddr(tilesW + s * kTileW);
                     const uint32_t xAddr = smemAddr(tilesX + s * kTileX);
@@ -288,6 +308,7 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
                     // the stage is free in both CTAs once these MMAs have read it
                     ummaCommitPair(emptyOwn + uint32_t(s) * 8u);
                     ummaCommitPair(emptyPeer + uint32_t(s) * 8u);
+                    PAIR_TRACE(1, 2 * it + 1);
                 }
                 if (ok) {
                     ummaCommitPair(accFullOwn + buf * 8u);
@@ -478,5 +499,11 @@ int gemmI8PairLaunch(const GemmI8Problem &q, cudaStream_t s, bool *taken) {
 }
 
 int pairErrorWord() { return tc::readErrorWord(); }
+
+#ifdef MLEL_PAIR_TRACE
+extern "C" int mlel_debug_pair_trace(unsigned long long *out) {
+    return cudaMemcpyFromSymbol(out, g_pairTrace, sizeof(g_pairTrace)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 } // namespace mlel

@@ -52,6 +52,8 @@ int padImageI8(const int8_t *in, int8_t *out, int N, int H, int W, int C, int Hp
                cudaStream_t s);
 // bt[n][w][c] = b[n][c][w]; corr[n][w] = -za * sum_c b[n][c][w] (mod 2^32).  C and W multiples of 16.
 int transposeForMatmul(const int8_t *b, int8_t *bt, int32_t *corr, int batches, int C, int W, int32_t za, cudaStream_t s);
+// corr[n][w] = -za * sum_c b[n][c][w] (mod 2^32) alone, for the kernel that reads b where it lies.  W a multiple of 16.
+int columnSumsForMatmul(const int8_t *b, int32_t *corr, int batches, int C, int W, int32_t za, cudaStream_t s);
 bool maxPoolI8Eligible(const TView &in, const TView &out);
 // packed int8 NHWC tensors (same conditions as maxPoolI8Eligible) with a window of at least 16 taps
 bool avgPoolI8Eligible(const TView &in, const TView &out, const PoolAttr &a);
@@ -70,6 +72,12 @@ bool vecRowReduce(int32_t op, const TView &in, const TView &out, uint32_t axis, 
 bool vecTransposeRows(const TView &in, const TView &out, const uint32_t *perms, cudaStream_t s, int *rc);
 // one-byte elements, the input's last axis becomes the output's second-to-last and another axis its last
 bool vecTransposeLast2Bytes(const TView &in, const TView &out, const uint32_t *perms, cudaStream_t s, int *rc);
+
+// Joins column blocks of byte rows: out[row][first[g] + j] = staging[(g * rows + row) * pitch + j], j < count[g].
+// The blocks follow one another (first[0] = 0, first[g + 1] = first[g] + count[g]); at most kMaxColumnBlocks.
+constexpr int kMaxColumnBlocks = 64;
+int interleaveColumns(const void *staging, void *out, int64_t rows, int32_t blocks, int32_t pitch, const int32_t *first,
+                      const int32_t *count, cudaStream_t s);
 
 // generic_ops.cu
 int genericConv2d(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,

@@ -74,9 +74,13 @@ __device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, const void *s
 }
 
 // High 32 bits of x * mult + round(x), x = value - input zero point: product and rounding of a RESCALE whose shift
-// is at least 32, where the result only depends on the high word.  Double rounding adds 2^30 for x >= 0 and
+// is at least 32, where the result only depends on the high word of the sum.  Double rounding adds 2^30 for x >= 0 and
 // subtracts it for x < 0: that is rn = 2^(shift-1) - 2^30 plus 2^31 when the sign bit of x is clear, one logic
 // operation on x (bumpMask = 2^31, or 0 without double rounding) feeding the third input of the 64-bit addition.
+// (Measured and not kept: the same value as acc * mult + (corrX * mult + rn) with the bump and the remaining shift
+// as multiply-high-adds.  It moves instructions from the general integer pipe to the multiply-add pipe, 56 % -> 43 %
+// and 14 % -> 19 % of their peaks, and ran 10 % slower: this epilogue issues one instruction every other cycle
+// whatever the mix.)
 __device__ __forceinline__ int32_t scaleHigh(int32_t x, int32_t mult, uint64_t rn, uint32_t bumpMask) {
     const uint64_t prod = uint64_t(int64_t(x) * int64_t(mult));
     const uint32_t extra = ~uint32_t(x) & bumpMask;
@@ -171,6 +175,10 @@ __device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const Ep
     }
 }
 
+#ifdef MLEL_PAIR_TRACE
+static __device__ unsigned long long g_pairTrace[2][3][256];
+#endif
+
 // Which tiles the epilogue warps of one CTA walk, and where they hand a drained accumulator back.  A CTA that
 // works alone walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... and arrives on its own barriers; the two CTAs
 // of a pair walk the pair's tiles, the second one 128 channels further on, and both arrive on the barriers of
@@ -233,11 +241,12 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         const bool ocValid = oc < p.N;
         const bool warpLive = c0 + quarter * 32 < p.N; // else all 32 channels of this warp are past the end
         const int32_t *corrBatch = p.corr + (p.batchedCorr ? int64_t(batch) * p.numClasses * p.N : 0);
-        if (storer) {
-            // The previous tile's store has read its C/D tile (and so have all before it): that tile may be
-            // filled again, by the next shortcut load or by the epilogue of the next tile.
+        if (RESIDUAL && storer) {
+            // The previous tile's store has read its C/D tile (and so have all before it): the shortcut bytes of the
+            // next tile may be loaded into it.  (This waits for a store that was issued a moment ago; without a
+            // shortcut to fetch the wait is put off to the end of the tile, see there.)
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-            if (RESIDUAL && tileCount > 0) {
+            if (tileCount > 0) {
                 mbarArrive(&bars->cdEmpty[buf ^ 1u]);
             }
         }
@@ -281,9 +290,19 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         if (RESIDUAL && !mbarWait(&bars->cFull[buf], par, 6)) {
             break;
         }
+#ifdef MLEL_PAIR_TRACE
+        if (PAIR && threadIdx.x == 0 && walk.first == 0 && tileCount < 32) {
+            g_pairTrace[walk.cOffset != 0][2][4 * tileCount] = clock64();
+        }
+#endif
         if (PAIR ? !mbarWaitRemote(&bars->accFull[buf], par, 4) : !mbarWait(&bars->accFull[buf], par, 4)) {
             break;
         }
+#ifdef MLEL_PAIR_TRACE
+        if (PAIR && threadIdx.x == 0 && walk.first == 0 && tileCount < 32) {
+            g_pairTrace[walk.cOffset != 0][2][4 * tileCount + 1] = clock64();
+        }
+#endif
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmemBase + buf * uint32_t(BNP) + (uint32_t(quarter * 32) << 16) + uint32_t(part * kColsPerWarp);
         // this thread's column of the C/D tile, at the first pixel of its half
@@ -356,7 +375,17 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         }
         // make the tile visible to the TMA unit, then one thread stores it (pixels and channels past the
         // tensor's end are clipped by the tensor map)
+#ifdef MLEL_PAIR_TRACE
+        if (PAIR && threadIdx.x == 0 && walk.first == 0 && tileCount < 32) {
+            g_pairTrace[walk.cOffset != 0][2][4 * tileCount + 2] = clock64();
+        }
+#endif
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (!RESIDUAL && storer) {
+            // The other C/D tile is written from the next tile on, by warps that have passed the barrier below: the
+            // store that last read it -- issued a whole tile ago, so normally long finished -- must be through.
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        }
         ocEpilogueSync<EW>();
         if (storer) {
             tmaStore3d(tmapD, cdTiles + buf * (BNP * 128), c0, m0, batch);

@@ -6,6 +6,7 @@
 // the same functions (device_common.cuh), so the results are the same bits.
 //
 // Every entry point returns false when it does not apply; the caller then runs the generic kernel.
+#include <algorithm>
 #include <string>
 
 #include "device_common.cuh"
@@ -565,6 +566,77 @@ bool vecTransposeLast2Bytes(const TView &in, const TView &out, const uint32_t *p
                                                    int(R), int(Ccols), inRowStride, p);
     *rc = finish("TRANSPOSE");
     return true;
+}
+
+namespace {
+
+// out[row][first[g] + j] = staging[g][row][j] for j < count[g]: joins the column blocks that an all-gather left
+// one after another (every block padded to `pitch` bytes per row) into rows of `total` bytes.  One thread moves
+// 16 bytes when every block starts and ends on a 16-byte boundary (VEC = 16), else one byte.
+struct ColumnBlocks {
+    int32_t first[kMaxColumnBlocks];
+    int32_t count[kMaxColumnBlocks];
+};
+
+template <int VEC>
+__global__ void interleaveColumnsKernel(const uint8_t *__restrict__ staging, uint8_t *__restrict__ out, int64_t rows,
+                                        int32_t blocks, int32_t pitch, int32_t total, ColumnBlocks cb) {
+    const int64_t unitsPerRow = total / VEC;
+    GRID_STRIDE(e, rows * unitsPerRow) {
+        const int64_t row = e / unitsPerRow;
+        const int32_t col = int32_t(e - row * unitsPerRow) * VEC;
+        int g = 0;
+        while (g + 1 < blocks && col >= cb.first[g + 1]) {
+            ++g;
+        }
+        const uint8_t *src = staging + (int64_t(g) * rows + row) * pitch + (col - cb.first[g]);
+        uint8_t *dst = out + row * int64_t(total) + col;
+        if (VEC == 16) {
+            *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
+        } else {
+            *dst = *src;
+        }
+    }
+}
+
+} // namespace
+
+int interleaveColumns(const void *staging, void *out, int64_t rows, int32_t blocks, int32_t pitch, const int32_t *first,
+                      const int32_t *count, cudaStream_t s) {
+    if (blocks < 1 || blocks > kMaxColumnBlocks || rows < 0 || pitch < 0) {
+        setLastError("interleave columns: bad block description");
+        return MLEL_ERROR_UNKNOWN;
+    }
+    ColumnBlocks cb{};
+    int64_t total = 0;
+    bool vec = (reinterpret_cast<uintptr_t>(staging) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
+               pitch % 16 == 0;
+    for (int g = 0; g < blocks; ++g) {
+        if (first[g] != total || count[g] < 0 || count[g] > pitch) {
+            setLastError("interleave columns: blocks must follow one another and fit the pitch");
+            return MLEL_ERROR_UNKNOWN;
+        }
+        cb.first[g] = first[g], cb.count[g] = count[g];
+        total += count[g];
+        vec = vec && first[g] % 16 == 0 && count[g] % 16 == 0;
+    }
+    if (total == 0 || rows == 0) {
+        return MLEL_SUCCESS;
+    }
+    if (total >= (int64_t(1) << 31)) {
+        setLastError("interleave columns: rows too long");
+        return MLEL_ERROR_UNKNOWN;
+    }
+    const int64_t units = rows * (total / (vec ? 16 : 1));
+    const int grid = int(std::min<int64_t>((units + 255) / 256, int64_t(kNumSMs) * 16));
+    if (vec) {
+        interleaveColumnsKernel<16><<<grid, 256, 0, s>>>(static_cast<const uint8_t *>(staging), static_cast<uint8_t *>(out),
+                                                         rows, blocks, pitch, int32_t(total), cb);
+    } else {
+        interleaveColumnsKernel<1><<<grid, 256, 0, s>>>(static_cast<const uint8_t *>(staging), static_cast<uint8_t *>(out),
+                                                        rows, blocks, pitch, int32_t(total), cb);
+    }
+    return finish("interleave columns");
 }
 
 } // namespace mlel

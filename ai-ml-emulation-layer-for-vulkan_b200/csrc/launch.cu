@@ -182,29 +182,13 @@ int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     GemmI8Params &p = q.params;
     p.M = int32_t(a.dims[1]);
     p.K = int32_t(a.dims[2]);
-    const void *bt = nullptr;
-    if (op.tc == 3) {
-        const TView &b = T[op.in[1]];
-        p.N = int32_t(b.dims[2]);
-        int8_t *scratch = reinterpret_cast<int8_t *>(T[op.scratch].ptr);
-        int32_t *corr = reinterpret_cast<int32_t *>(scratch + op.auxi[2]);
-        const int rc = transposeForMatmul(reinterpret_cast<const int8_t *>(b.ptr), scratch, corr, int(b.dims[0]), p.K, p.N,
-                                          op.i[0], s);
-        if (rc != MLEL_SUCCESS) {
-            return rc;
-        }
-        bt = scratch;
-        p.corr = corr;
-    } else {
-        p.N = int32_t(T[op.aux[3]].dims[1]);
-        bt = T[op.aux[3]].ptr;
-        p.corr = reinterpret_cast<const int32_t *>(T[op.aux[0]].ptr);
-    }
-    p.ldOut = p.N;
     p.batchedB = 1;
     p.numClasses = 1;
     p.numColClasses = 1;
     p.batchedCorr = 1;
+    // |correction| = |zero point of A| * |column sum of B| <= 128 * K * |zp|: small enough for the short RESCALE form
+    // whenever that bound is (see GemmI8Params::corrSmall)
+    p.corrSmall = int64_t(op.i[0] < 0 ? -op.i[0] : op.i[0]) * p.K * 128 <= (int64_t(1) << 30) - 256;
     if (op.kind == OP_FUSED_MATMUL) {
         p.out8 = reinterpret_cast<int8_t *>(out.ptr);
         p.epi = devEpilogue(op.epi, T);
@@ -215,6 +199,44 @@ int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     q.aMatrix = a.ptr;
     q.aRowBytes = uint64_t(p.K);
     q.aBatchBytes = uint64_t(p.K) * uint64_t(p.M);
+    const void *bt = nullptr;
+    if (op.tc == 3) {
+        const TView &b = T[op.in[1]];
+        p.N = int32_t(b.dims[2]);
+        p.ldOut = p.N;
+        int8_t *scratch = reinterpret_cast<int8_t *>(T[op.scratch].ptr);
+        int32_t *corr = reinterpret_cast<int32_t *>(scratch + op.auxi[2]);
+        p.corr = corr;
+        // The paired kernel reads the run-time operand where it lies ([C][W], the output column contiguous: an
+        // MN-major tensor-core operand) and only needs the column sums; the single-CTA kernel takes a transposed
+        // copy, made together with the sums.
+        q.bMatrix = b.ptr;
+        q.bRowBytes = uint64_t(p.N);
+        q.bBatchBytes = uint64_t(p.K) * uint64_t(p.N);
+        q.bMnMajor = true;
+        if (tensorCoreTuning().pairKernel.load(std::memory_order_relaxed) != 0 && gemmI8PairApplies(q)) {
+            int rc = columnSumsForMatmul(reinterpret_cast<const int8_t *>(b.ptr), corr, int(b.dims[0]), p.K, p.N, op.i[0], s);
+            if (rc != MLEL_SUCCESS) {
+                return rc;
+            }
+            bool taken = false;
+            rc = gemmI8PairLaunch(q, s, &taken);
+            if (taken || rc != MLEL_SUCCESS) {
+                return rc;
+            }
+        }
+        const int rc = transposeForMatmul(reinterpret_cast<const int8_t *>(b.ptr), scratch, corr, int(b.dims[0]), p.K, p.N,
+                                          op.i[0], s);
+        if (rc != MLEL_SUCCESS) {
+            return rc;
+        }
+        bt = scratch;
+    } else {
+        p.N = int32_t(T[op.aux[3]].dims[1]);
+        p.ldOut = p.N;
+        bt = T[op.aux[3]].ptr;
+        p.corr = reinterpret_cast<const int32_t *>(T[op.aux[0]].ptr);
+    }
     q.bMatrix = bt;
     q.bRowBytes = uint64_t(p.K);
     q.bBatchBytes = uint64_t(p.K) * uint64_t(p.N);

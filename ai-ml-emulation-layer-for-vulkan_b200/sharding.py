@@ -101,17 +101,38 @@ def shard_matmul_operands(b: np.ndarray, per_channel: Sequence[np.ndarray], worl
 def all_gather_columns(local: torch.Tensor, total: int, align: int = 16, group=None) -> torch.Tensor:
     """Joins every rank's ``[N, H, count]`` block along the last axis into ``[N, H, total]`` on every rank.
 
-    The column axis is the contiguous one, so the blocks are exchanged as whole tensors (padded to the widest
-    block) and interleaved locally."""
+    The column axis is the contiguous one, so the blocks cannot be gathered in place: one
+    ``all_gather_into_tensor`` brings them, each padded to the widest block, into a ``[world, N, H, widest]``
+    staging buffer, and one local pass interleaves them.  On CUDA tensors that pass is the library's own kernel
+    (``mlel_cuda_interleave_columns``, on the current stream); CPU ranks (the gloo tests of this logic) do the
+    same join on the host."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     first, count = shard_columns(total, world, rank, align)
     if local.shape[-1] != count:
         raise ValueError(f"rank {rank} holds {local.shape[-1]} columns, its block of {total} has {count}")
-    widest = max(shard_columns(total, world, r, align)[1] for r in range(world))
-    padded = torch.zeros(tuple(local.shape[:-1]) + (widest,), dtype=local.dtype, device=local.device)
-    padded[..., :count] = local
-    pieces = [torch.empty_like(padded) for _ in range(world)]
-    dist.all_gather(pieces, padded, group=group)
-    return torch.cat([pieces[r][..., :shard_columns(total, world, r, align)[1]] for r in range(world)], dim=-1)
+    blocks = [shard_columns(total, world, r, align) for r in range(world)]
+    widest = max(c for _, c in blocks)
+    if count == widest and local.is_contiguous():
+        padded = local
+    else:
+        padded = torch.zeros(tuple(local.shape[:-1]) + (widest,), dtype=local.dtype, device=local.device)
+        padded[..., :count] = local
+    staging = torch.empty((world,) + tuple(padded.shape), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(staging, padded, group=group)
+    if local.is_cuda:
+        import ctypes
 
+        from . import check, lib
+        item = local.element_size()
+        rows = int(np.prod(local.shape[:-1])) if local.dim() > 1 else 1
+        out = torch.empty(tuple(local.shape[:-1]) + (total,), dtype=local.dtype, device=local.device)
+        firsts = (ctypes.c_int32 * world)(*[f * item for f, _ in blocks])
+        counts = (ctypes.c_int32 * world)(*[c * item for _, c in blocks])
+        stream = torch.cuda.current_stream(local.device).cuda_stream
+        check(lib().mlel_cuda_interleave_columns(ctypes.c_void_p(staging.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                                 ctypes.c_uint64(rows), ctypes.c_uint32(world),
+                                                 ctypes.c_uint32(widest * item), firsts, counts,
+                                                 ctypes.c_void_p(stream)))
+        return out
+    return torch.cat([staging[r][..., :blocks[r][1]] for r in range(world)], dim=-1)

@@ -350,6 +350,15 @@ int mlel_cuda_conv2d_rescale(const mlel_tensor *input, const mlel_tensor *weight
                              int32_t output_zp, int double_round, int per_channel, int32_t clamp_min,
                              int32_t clamp_max, void *cuda_stream);
 
+/* Join of an output-channel-sharded MATMUL (no counterpart in the reference, which has no multi-device path):
+ * after an all-gather, `staging` holds `blocks` column blocks one after another, block g as `rows` rows of
+ * `pitch_bytes` bytes of which the first byte_count[g] are valid; this writes rows of sum(byte_count) bytes to
+ * `output` with block g at byte first_byte[g] of every row (first_byte[0] = 0, first_byte[g + 1] = first_byte[g] +
+ * byte_count[g]; at most 64 blocks).  Moves 16 bytes per thread when every block starts and ends on a 16-byte
+ * boundary. */
+int mlel_cuda_interleave_columns(const void *staging, void *output, uint64_t rows, uint32_t blocks, uint32_t pitch_bytes,
+                                 const int32_t *first_byte, const int32_t *byte_count, void *cuda_stream);
+
 /* CONV2D (int8 input, int8 OHWI weights with zero point 0, int32 bias, int32 output; same result as
  * mlel_cuda_conv2d) for callers that must not allocate device memory, such as a layer's dispatch hook
  * or code that runs inside another runtime's fixed memory budget.  It has no counterpart in the
