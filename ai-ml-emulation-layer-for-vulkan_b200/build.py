@@ -21,7 +21,7 @@ LIB = os.path.join(HERE, "libmlel_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CFLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-Wall", "--expt-relaxed-constexpr",
-          "-I", os.path.join(HERE, "..", "include")] + os.environ.get("MLEL_EXTRA_NVCC_FLAGS", "").split()
+          "-I", os.path.join(HERE, "..", "include")]
 
 
 def sources():

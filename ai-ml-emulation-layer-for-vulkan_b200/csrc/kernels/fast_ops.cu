@@ -106,16 +106,16 @@ __global__ void __launch_bounds__(256) transposeColsumKernel(const int8_t *__res
 }
 
 // ---- column sums of MATMUL's second input [N][C][W]: corr[n][w] = -za * sum_c b[n][c][w] --------------------
-// For the tensor-core path that reads the operand where it lies (no transposed copy).  A block owns 128 columns
-// of one batch: 8 lanes hold 16 columns each (one 16-byte load per row), 32 slices share the rows and add
-// their partial sums in shared memory.  Each byte goes through one dp4a against a one-hot selector, which
-// sign-extends and accumulates it.
+// For the tensor-core path that reads the operand where it lies (no transposed copy).  A block owns 64 columns
+// of one batch: 4 lanes hold 16 columns each (one 16-byte load per row), 64 slices share the rows, eight rows in
+// flight per thread, and add their partial sums in shared memory.  Each byte goes through one dp4a against a
+// one-hot selector, which sign-extends and accumulates it.
 __global__ void __launch_bounds__(256) columnSumKernel(const int8_t *__restrict__ b, int32_t *__restrict__ corr, int C, int W,
                                                        int32_t za) {
-    __shared__ int32_t part[32][128 + 4];
+    __shared__ int32_t part[64][64 + 1];
     const int n = blockIdx.y;
-    const int w0 = blockIdx.x * 128;
-    const int seg = threadIdx.x & 7, slice = threadIdx.x >> 3;
+    const int w0 = blockIdx.x * 64;
+    const int seg = threadIdx.x & 3, slice = threadIdx.x >> 2;
     const int w = w0 + seg * 16;
     const int8_t *src = b + int64_t(n) * C * W + w;
     int32_t acc[16];
@@ -124,15 +124,15 @@ __global__ void __launch_bounds__(256) columnSumKernel(const int8_t *__restrict_
         acc[i] = 0;
     }
     if (w < W) { // W is a multiple of 16: a 16-byte segment is inside or outside as a whole
-        for (int c0 = slice; c0 < C; c0 += 128) {
-            int4 v[4];
+        for (int c0 = slice; c0 < C; c0 += 8 * 64) {
+            int4 v[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) { // four rows in flight
-                const int c = c0 + 32 * u;
+            for (int u = 0; u < 8; ++u) {
+                const int c = c0 + 64 * u;
                 v[u] = c < C ? __ldg(reinterpret_cast<const int4 *>(src + int64_t(c) * W)) : make_int4(0, 0, 0, 0);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int words[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -146,10 +146,10 @@ __global__ void __launch_bounds__(256) columnSumKernel(const int8_t *__restrict_
         part[slice][seg * 16 + i] = acc[i];
     }
     __syncthreads();
-    if (threadIdx.x < 128 && w0 + threadIdx.x < W) {
+    if (threadIdx.x < 64 && w0 + threadIdx.x < W) {
         int32_t sum = 0;
-#pragma unroll
-        for (int sl = 0; sl < 32; ++sl) {
+#pragma unroll 8
+        for (int sl = 0; sl < 64; ++sl) {
             sum += part[sl][threadIdx.x];
         }
         corr[int64_t(n) * W + w0 + threadIdx.x] = int32_t(uint32_t(0) - uint32_t(za) * uint32_t(sum));
@@ -389,7 +389,7 @@ int transposeForMatmul(const int8_t *b, int8_t *bt, int32_t *corr, int batches, 
 }
 
 int columnSumsForMatmul(const int8_t *b, int32_t *corr, int batches, int C, int W, int32_t za, cudaStream_t s) {
-    const dim3 grid(unsigned((W + 127) / 128), unsigned(batches));
+    const dim3 grid(unsigned((W + 63) / 64), unsigned(batches));
     columnSumKernel<<<grid, 256, 0, s>>>(b, corr, C, W, za);
     return finish("MATMUL operand column sums");
 }

@@ -102,7 +102,7 @@ int pairErrorWord();
 
 // Kernel-selection knobs of the tensor-core launchers (mlel_set_tuning): 0 = the library's own choice.
 struct TensorCoreTuning {
-    std::atomic<int> pairKernel{1};        // 0: never use the paired kernel
+    std::atomic<int> pairKernel{1};        // paired kernel for: 0 nothing, 1 matrix products, 2 convolutions too
     std::atomic<int> pairTilePixels{0};    // 128, 192 or 256: pixels per tile of the paired kernel
     std::atomic<int> ocTilePixels{0};      // 128, 192 or 256: pixels per tile of the channel-major kernel
     std::atomic<int> dependentLaunch{1};   // 0: launch the tensor-core kernels without programmatic dependent launch

@@ -175,9 +175,6 @@ __device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const Ep
     }
 }
 
-#ifdef MLEL_PAIR_TRACE
-static __device__ unsigned long long g_pairTrace[2][3][256];
-#endif
 
 // Which tiles the epilogue warps of one CTA walk, and where they hand a drained accumulator back.  A CTA that
 // works alone walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... and arrives on its own barriers; the two CTAs
@@ -203,6 +200,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                                                 uint32_t tmemBase, int warp, int lane, int64_t numTiles, int pTiles,
                                                 int cTiles, const EpiWalk &walk) {
     constexpr bool PAIR = C_TILE != kOcTile;
+    const int epiThread = warp * 32 + lane; // index among the epilogue threads (`warp` counts from the first of them)
     const auto accDrained = [&](uint32_t buf) {
         if (PAIR) {
             mbarArriveCluster(walk.accEmpty[buf]);
@@ -269,15 +267,15 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         if (hasClasses) {
             // border class of every pixel of the tile; the table alternates with the accumulator, so a warp that
             // is a tile ahead never overwrites what a slower warp still reads
-            if (threadIdx.x < BNP) {
-                const int64_t m = int64_t(m0) + threadIdx.x;
+            if (epiThread < BNP) {
+                const int64_t m = int64_t(m0) + epiThread;
                 int c = baseClass;
                 if (m < p.M) {
                     const uint32_t rem = uint32_t(m) - fastDiv(uint32_t(m), p.divPlane) * p.divPlane.d; // pixel inside its image
                     const uint32_t oy = fastDiv(rem, p.divOW);
                     c = int(__ldg(p.rowClass + oy)) * p.numColClasses + int(__ldg(p.colClass + (rem - oy * uint32_t(p.OW))));
                 }
-                cls[threadIdx.x] = uint8_t(c);
+                cls[epiThread] = uint8_t(c);
             }
             ocEpilogueSync<EW>();
         }
@@ -290,19 +288,9 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         if (RESIDUAL && !mbarWait(&bars->cFull[buf], par, 6)) {
             break;
         }
-#ifdef MLEL_PAIR_TRACE
-        if (PAIR && threadIdx.x == 0 && walk.first == 0 && tileCount < 32) {
-            g_pairTrace[walk.cOffset != 0][2][4 * tileCount] = clock64();
-        }
-#endif
-        if (PAIR ? !mbarWaitRemote(&bars->accFull[buf], par, 4) : !mbarWait(&bars->accFull[buf], par, 4)) {
+        if (!mbarWait(&bars->accFull[buf], par, 4)) {
             break;
         }
-#ifdef MLEL_PAIR_TRACE
-        if (PAIR && threadIdx.x == 0 && walk.first == 0 && tileCount < 32) {
-            g_pairTrace[walk.cOffset != 0][2][4 * tileCount + 1] = clock64();
-        }
-#endif
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmemBase + buf * uint32_t(BNP) + (uint32_t(quarter * 32) << 16) + uint32_t(part * kColsPerWarp);
         // this thread's column of the C/D tile, at the first pixel of its half
@@ -375,11 +363,6 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         }
         // make the tile visible to the TMA unit, then one thread stores it (pixels and channels past the
         // tensor's end are clipped by the tensor map)
-#ifdef MLEL_PAIR_TRACE
-        if (PAIR && threadIdx.x == 0 && walk.first == 0 && tileCount < 32) {
-            g_pairTrace[walk.cOffset != 0][2][4 * tileCount + 2] = clock64();
-        }
-#endif
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         if (!RESIDUAL && storer) {
             // The other C/D tile is written from the next tile on, by warps that have passed the barrier below: the

@@ -28,10 +28,13 @@ ConvAttr convAttr(const OpDesc &op) {
     return a;
 }
 
-// Runs q on the paired tensor-core kernel when it applies; *rc is the launch status when the result is true.
-bool tryPairKernel(const GemmI8Problem &q, cudaStream_t s, int *rc) {
-    const bool enabled = tensorCoreTuning().pairKernel.load(std::memory_order_relaxed) != 0;
-    if (!enabled || !gemmI8PairApplies(q)) {
+// Runs q on the paired tensor-core kernel when it applies and the selection allows it; *rc is the launch status when
+// the result is true.  Matrix products take it by default; convolutions only on request ("pair_kernel" 2): on the
+// ResNet-50 layer shapes the single-CTA kernels measured as fast or faster (their tiles fill the SMs better and the
+// epilogue, not the main loop, bounds those layers).
+bool tryPairKernel(const GemmI8Problem &q, bool convolution, cudaStream_t s, int *rc) {
+    const int mode = tensorCoreTuning().pairKernel.load(std::memory_order_relaxed);
+    if (mode < (convolution ? 2 : 1) || !gemmI8PairApplies(q)) {
         return false;
     }
     bool taken = false;
@@ -169,7 +172,7 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     q.bBatchBytes = 0;
     q.bMnMajor = false;
     int rc = MLEL_SUCCESS;
-    if (tryPairKernel(q, s, &rc)) {
+    if (tryPairKernel(q, true, s, &rc)) {
         return rc;
     }
     return gemmI8OcMajorApplies(q) ? gemmI8OcMajorLaunch(q, s) : gemmI8Launch(q, s);
@@ -242,7 +245,7 @@ int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     q.bBatchBytes = uint64_t(p.K) * uint64_t(p.N);
     q.bMnMajor = false;
     int rc = MLEL_SUCCESS;
-    if (tryPairKernel(q, s, &rc)) {
+    if (tryPairKernel(q, false, s, &rc)) {
         return rc;
     }
     return gemmI8Launch(q, s);

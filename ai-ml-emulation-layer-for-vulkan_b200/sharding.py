@@ -118,8 +118,12 @@ def all_gather_columns(local: torch.Tensor, total: int, align: int = 16, group=N
     else:
         padded = torch.zeros(tuple(local.shape[:-1]) + (widest,), dtype=local.dtype, device=local.device)
         padded[..., :count] = local
-    staging = torch.empty((world,) + tuple(padded.shape), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(staging, padded, group=group)
+    if padded.dim() == 0:
+        padded = padded.reshape(1)
+    # the gathered tensor is the ranks' blocks concatenated along axis 0 (the form every backend accepts)
+    flat = torch.empty((world * padded.shape[0],) + tuple(padded.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(flat, padded, group=group)
+    staging = flat.view((world,) + tuple(padded.shape))
     if local.is_cuda:
         import ctypes
 

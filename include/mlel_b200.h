@@ -296,8 +296,8 @@ int mlel_measure_int8_mma_peak(int batches, void *cuda_stream, float *ms, double
 
 /* Kernel selection of the tensor-core contractions (no counterpart in the reference; process-wide, takes
  * effect for kernels enqueued afterwards, results are the same bits whatever is chosen):
- *   "pair_kernel"       1 (default) lets contractions with more than 128 output channels run on the paired
- *                       two-CTA kernel, 0 keeps them on the single-CTA kernels;
+ *   "pair_kernel"       which contractions with more than 128 output channels run on the paired two-CTA kernel:
+ *                       1 (default) matrix products, 2 convolutions as well, 0 none;
  *   "pair_tile_pixels"  0 (default: chosen per problem), 128, 192 or 256 pixels per tile of the paired kernel;
  *   "oc_tile_pixels"    the same for the channel-major single-CTA kernel;
  *   "dependent_launch"  1 (default) launches the tensor-core kernels with programmatic dependent launch.

@@ -15,6 +15,15 @@ from tests.graph_eval import evaluate
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _pair_kernel_for_convolutions(mlel):
+    """Convolutions take the paired kernel only on request; these tests request it."""
+    lib = mlel.lib()
+    assert lib.mlel_set_tuning(b"pair_kernel", 2) == 0
+    yield
+    assert lib.mlel_set_tuning(b"pair_kernel", 1) == 0
+
+
 def rng(seed):
     return np.random.Generator(np.random.PCG64(seed))
 
@@ -111,8 +120,9 @@ def test_pair_kernel_can_be_switched_off(mlel):
         run_and_compare(mlel, g, [r.integers(-128, 128, (n, h, w, ic), dtype=np.int8)], expect_pair=False)
         assert lib.mlel_tensor_core_launches(2) == before
     finally:
-        assert lib.mlel_set_tuning(b"pair_kernel", 1) == 0
+        assert lib.mlel_set_tuning(b"pair_kernel", 2) == 0
     assert lib.mlel_set_tuning(b"pair_tile_pixels", 100) != 0 and lib.mlel_set_tuning(b"no_such_key", 1) != 0
+    assert lib.mlel_set_tuning(b"pair_kernel", 3) != 0
 
 
 def residual_block_graph(r, n, hw, cin, cout, double_round=True):
