@@ -29,6 +29,7 @@
 
 #include <cstdint>
 #include <mutex>
+#include <exception>
 #include <string>
 
 #include "device_common.cuh"
@@ -166,6 +167,14 @@ int fail(const std::string &msg) {
 
 } // namespace mlel
 
+namespace mlel {
+namespace {
+int conv2dStaticScratch(const mlel_tensor *input, const mlel_tensor *weights, const mlel_tensor *biases,
+                        const mlel_tensor *output, const int32_t pad[4], const int32_t stride[2], const int32_t dilation[2],
+                        int32_t input_zp, int32_t weight_zp, void *cuda_stream);
+} // namespace
+} // namespace mlel
+
 using namespace mlel;
 
 extern "C" int mlel_cuda_conv2d_static_scratch(const mlel_tensor *input, const mlel_tensor *weights,
@@ -173,8 +182,29 @@ extern "C" int mlel_cuda_conv2d_static_scratch(const mlel_tensor *input, const m
                                                const int32_t pad[4], const int32_t stride[2],
                                                const int32_t dilation[2], int32_t input_zp, int32_t weight_zp,
                                                void *cuda_stream) {
-    if (input == nullptr || weights == nullptr || biases == nullptr || output == nullptr) {
-        return fail("null tensor argument");
+    // no exception may cross the C boundary (the messages below build strings)
+    try {
+        return conv2dStaticScratch(input, weights, biases, output, pad, stride, dilation, input_zp, weight_zp, cuda_stream);
+    } catch (const std::exception &e) {
+        try {
+            setLastError(std::string("conv2d_static_scratch: ") + e.what());
+        } catch (...) {
+        }
+        return MLEL_ERROR_UNKNOWN;
+    } catch (...) {
+        return MLEL_ERROR_UNKNOWN;
+    }
+}
+
+namespace mlel {
+namespace {
+
+int conv2dStaticScratch(const mlel_tensor *input, const mlel_tensor *weights, const mlel_tensor *biases,
+                        const mlel_tensor *output, const int32_t pad[4], const int32_t stride[2], const int32_t dilation[2],
+                        int32_t input_zp, int32_t weight_zp, void *cuda_stream) {
+    if (input == nullptr || weights == nullptr || biases == nullptr || output == nullptr || pad == nullptr ||
+        stride == nullptr || dilation == nullptr) {
+        return fail("null argument");
     }
     const mlel_tensor_desc &di = input->desc, &dw = weights->desc, &db = biases->desc, &dout = output->desc;
     if (di.dtype != MLEL_I8 || dw.dtype != MLEL_I8 || db.dtype != MLEL_I32 || dout.dtype != MLEL_I32 || di.rank != 4 ||
@@ -187,6 +217,10 @@ extern "C" int mlel_cuda_conv2d_static_scratch(const mlel_tensor *input, const m
     if (weight_zp != 0) {
         return fail("a weight zero point other than 0 is not supported");
     }
+    if (input_zp < -128 || input_zp > 127) {
+        // the working copy of the input is int8 and its padding is filled with the zero point
+        return fail("the input zero point must be in the int8 range");
+    }
     const int64_t N = di.dims[0], H = di.dims[1], W = di.dims[2], IC = di.dims[3];
     const int64_t OC = dw.dims[0], KH = dw.dims[1], KW = dw.dims[2];
     const int64_t OH = dout.dims[1], OW = dout.dims[2];
@@ -195,6 +229,14 @@ extern "C" int mlel_cuda_conv2d_static_scratch(const mlel_tensor *input, const m
     }
     if (stride[0] <= 0 || stride[1] <= 0 || dilation[0] <= 0 || dilation[1] <= 0 || OC % 16 != 0) {
         return fail("strides and dilations must be positive and the output channel count a multiple of 16");
+    }
+    const auto outDim = [](int64_t in, int64_t before, int64_t after, int64_t k, int64_t dil, int64_t st) {
+        return (in + before + after - (k - 1) * dil - 1) / st + 1;
+    };
+    if (pad[0] < 0 || pad[1] < 0 || pad[2] < 0 || pad[3] < 0 || KH <= 0 || KW <= 0 ||
+        OH != outDim(H, pad[0], pad[1], KH, dilation[0], stride[0]) ||
+        OW != outDim(W, pad[2], pad[3], KW, dilation[1], stride[1])) {
+        return fail("the output size does not follow from input size, padding, window, dilation and stride");
     }
     const int64_t K = KH * KW * IC, kPad = (K + 15) / 16 * 16, M = N * OH * OW;
     if (K > 65536 || M <= 0 || M >= (int64_t(1) << 31)) {
@@ -244,3 +286,6 @@ extern "C" int mlel_cuda_conv2d_static_scratch(const mlel_tensor *input, const m
     q.bMnMajor = false;
     return gemmI8Launch(q, s);
 }
+
+} // namespace
+} // namespace mlel

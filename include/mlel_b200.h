@@ -365,7 +365,10 @@ int mlel_cuda_interleave_columns(const void *staging, void *output, uint64_t row
  * reference.  All working memory is a 32 MiB array built into the library, so the call makes no
  * cudaMalloc/cudaFree and uses no allocating library routine; problems that need more
  * (pixels * kPad + OC * kPad + 4 * OC bytes, kPad = KH*KW*IC rounded up to 16) are rejected with
- * MLEL_ERROR_UNKNOWN.  The array is shared by every call on the device: calls whose GPU work may overlap
+ * MLEL_ERROR_UNKNOWN.  Also rejected, with a message: tensors that are not packed, an output channel count
+ * that is not a multiple of 16, KH*KW*IC above 65536, a weight zero point other than 0, an input zero point
+ * outside the int8 range, and an output size that does not follow from the other arguments.
+ * The array is shared by every call on the device: calls whose GPU work may overlap
  * must be serialised by the caller.  The first call on a device resolves the array's address and should
  * be made outside stream capture. */
 int mlel_cuda_conv2d_static_scratch(const mlel_tensor *input, const mlel_tensor *weights, const mlel_tensor *biases,

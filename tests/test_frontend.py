@@ -184,3 +184,38 @@ def test_mobilenet_lowers(mlel):
     p = lower(mlel, g.spvasm(), ext, list(g.constants.items()))
     names = p.exec_names()
     assert sum(n.startswith("DEPTHWISE_CONV2D+RESCALE") for n in names) == 17
+
+
+def _replicated_pattern_module(count):
+    """``x + k`` on int32 tensors of ``count`` elements where ``k`` is OpConstantCompositeReplicateEXT of the
+    two-element composite {1, 2}: the flattened constant holds a pattern of two values for ``count`` elements."""
+    shape = (count // 2, 2) if count % 2 == 0 else (count,)
+    g = GraphBuilder()
+    row = g._tensor_type(np.dtype(np.int32), (2,))
+    x = g.input(np.int32, shape)
+    k = g.inline(np.arange(1, count + 1, dtype=np.int32).reshape(shape))
+    g.output(g.add(x, k))
+    lines = []
+    for line in g.spvasm().splitlines():
+        if line.startswith(f"%{k.name} = OpConstantComposite "):
+            tensor_type = line.split()[3]
+            lines.append(f"%pattern_row = OpConstantComposite {row} %i32_1 %i32_2")
+            lines.append(f"%{k.name} = OpConstantCompositeReplicateEXT {tensor_type} %pattern_row")
+        else:
+            lines.append(line)
+    return "\n".join(lines) + "\n", shape
+
+
+def test_replicated_pattern_two_to_four_is_expanded(mlel):
+    # tests/graph/graph_ext_inst_context_tests.cpp:16-20: {1, 2} for four elements becomes {1, 2, 1, 2}
+    text, shape = _replicated_pattern_module(4)
+    p = lower(mlel, text, [(0, 0, 0, mlel.I32, shape), (0, 1, 0, mlel.I32, shape)])
+    assert p.op_names() == ["ADD"]
+
+
+def test_replicated_pattern_rejects_non_divisible_counts(mlel):
+    # tests/graph/graph_ext_inst_context_tests.cpp:22-26: {1, 2} cannot fill three elements
+    text, shape = _replicated_pattern_module(3)
+    with pytest.raises(mlel.MlelError) as e:
+        lower(mlel, text, [(0, 0, 0, mlel.I32, shape), (0, 1, 0, mlel.I32, shape)])
+    assert "replicated constant element count" in str(e.value)

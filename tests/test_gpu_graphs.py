@@ -218,6 +218,27 @@ def test_mobilenet_shaped_graph(mlel):
     np.testing.assert_array_equal(run(g, inputs, flags=0, use_cuda_graph=True)[0], want)
 
 
+def test_mobilenet_full_width_one_image(mlel):
+    """Configuration 2 at its real channel widths (24/144/960/1280 and so on) and image size, one image: fused with
+    graph replay, and unfused (the reference's operator list), against the oracle."""
+    g, inputs = mobilenet_v2_graph(seed=1, n=1, image=224, width_div=1)
+    want = evaluate(g, inputs)[0]
+    assert np.unique(want).size > 20
+    np.testing.assert_array_equal(run(g, inputs, flags=0, use_cuda_graph=True)[0], want)
+    np.testing.assert_array_equal(run(g, inputs, flags=1)[0], want)
+
+
+def test_bert_full_width_one_layer(mlel):
+    """One encoder layer of configuration 4 at its real sizes (hidden 768, 12 heads, FFN 3072, 384 tokens), one
+    sequence: the projections with K = 768 and 3072, both attention products, fused and unfused."""
+    g, inputs = bert_graph(seed=3, n=1, seq=384, hidden=768, heads=12, ffn=3072, layers=1)
+    want = evaluate(g, inputs)[0]
+    assert want.std() > 5.0 and np.unique(want).size > 50
+    np.testing.assert_array_equal(run(g, inputs, flags=0)[0], want)
+    np.testing.assert_array_equal(run(g, inputs, flags=1)[0], want)
+    np.testing.assert_array_equal(run(g, inputs, flags=0, use_cuda_graph=True)[0], want)
+
+
 def test_bert_shaped_graph(mlel):
     """Configuration 4 at reduced size: projections and both attention products on the tensor cores, the
     softmax / layer-norm chains (REDUCE_MAX, SUB, int16 TABLE, REDUCE_SUM, MUL), head split and merge
@@ -349,6 +370,69 @@ def test_direct_kernel_entry_points(mlel):
                                             ctypes.byref(tm), ctypes.byref(ts), 0, 3, 1, 0, 1, 0, stream))
     torch.cuda.synchronize()
     np.testing.assert_array_equal(out.cpu().numpy(), want)
+
+
+def test_direct_convolution_entry_points(mlel):
+    """mlel_cuda_conv2d, mlel_cuda_depthwise_conv2d and mlel_cuda_conv2d_rescale called directly, against the oracle."""
+    import torch
+    from oracle import oracle
+    r = np.random.Generator(np.random.PCG64(11))
+    T = mlel.device_tensor
+    lib = mlel.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    pad, st, dl = (ctypes.c_int32 * 4)(1, 1, 1, 1), (ctypes.c_int32 * 2)(2, 2), (ctypes.c_int32 * 2)(1, 1)
+    x = r.integers(-128, 128, (2, 13, 11, 24), dtype=np.int8)
+    w = r.integers(-128, 128, (32, 3, 3, 24), dtype=np.int8)
+    b = r.integers(-(1 << 14), 1 << 14, (32,), dtype=np.int32)
+    dx, dw, db = (torch.from_numpy(a).cuda() for a in (x, w, b))
+    want = oracle.conv2d(x, w, b, [1] * 4, [2, 2], [1, 1], -5, 0)
+    out = torch.zeros(want.shape, dtype=torch.int32, device="cuda")
+    tx, tw, tb = T(dx.data_ptr(), mlel.I8, x.shape), T(dw.data_ptr(), mlel.I8, w.shape), T(db.data_ptr(), mlel.I32, b.shape)
+    mlel.check(lib.mlel_cuda_conv2d(ctypes.byref(tx), ctypes.byref(tw), ctypes.byref(tb),
+                                    ctypes.byref(T(out.data_ptr(), mlel.I32, want.shape)), pad, st, dl, -5, 0, stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    # the fused form: CONV2D -> RESCALE (per channel, double rounding) -> CLAMP
+    mult = r.integers(1 << 30, (1 << 31) - 1, (32,), dtype=np.int64).astype(np.int32)
+    shift = r.integers(36, 42, (32,), dtype=np.int8)
+    dm, ds = torch.from_numpy(mult).cuda(), torch.from_numpy(shift).cuda()
+    want8 = oracle.clamp(oracle.rescale(want, mult, shift, 0, 4, np.int8, True, True, True), -10, 90)
+    out8 = torch.zeros(want.shape, dtype=torch.int8, device="cuda")
+    mlel.check(lib.mlel_cuda_conv2d_rescale(ctypes.byref(tx), ctypes.byref(tw), ctypes.byref(tb),
+                                            ctypes.byref(T(out8.data_ptr(), mlel.I8, want.shape)), pad, st, dl, -5, 0,
+                                            ctypes.byref(T(dm.data_ptr(), mlel.I32, (32,))),
+                                            ctypes.byref(T(ds.data_ptr(), mlel.I8, (32,))), 0, 4, 1, 1, -10, 90, stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out8.cpu().numpy(), want8)
+    # depthwise: weights [KH, KW, C, M]
+    wd = r.integers(-128, 128, (3, 3, 24, 2), dtype=np.int8)
+    bd = r.integers(-(1 << 14), 1 << 14, (48,), dtype=np.int32)
+    dwd, dbd = torch.from_numpy(wd).cuda(), torch.from_numpy(bd).cuda()
+    wantd = oracle.depthwise_conv2d(x, wd, bd, [1] * 4, [2, 2], [1, 1], 7, -2)
+    outd = torch.zeros(wantd.shape, dtype=torch.int32, device="cuda")
+    mlel.check(lib.mlel_cuda_depthwise_conv2d(ctypes.byref(tx), ctypes.byref(T(dwd.data_ptr(), mlel.I8, wd.shape)),
+                                              ctypes.byref(T(dbd.data_ptr(), mlel.I32, bd.shape)),
+                                              ctypes.byref(T(outd.data_ptr(), mlel.I32, wantd.shape)), pad, st, dl, 7, -2,
+                                              stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(outd.cpu().numpy(), wantd)
+
+
+def test_replicated_pattern_constant_values(mlel):
+    """{1, 2} replicated over four elements reaches the kernels as {1, 2, 1, 2}
+    (tests/graph/graph_ext_inst_context_tests.cpp:16-20), checked through x + k with x = 0."""
+    import torch
+    from tests.test_frontend import _replicated_pattern_module, lower
+    text, shape = _replicated_pattern_module(4)
+    p = lower(mlel, text, [(0, 0, 0, mlel.I32, shape), (0, 1, 0, mlel.I32, shape)])
+    s = mlel.Session(p)
+    x = torch.zeros(shape, dtype=torch.int32, device="cuda")
+    y = torch.full(shape, -1, dtype=torch.int32, device="cuda")
+    s.set_external(0, 0, x.data_ptr())
+    s.set_external(0, 1, y.data_ptr())
+    s.dispatch(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(y.cpu().numpy().reshape(-1), [1, 2, 1, 2])
 
 
 def test_graph_replay_follows_rebinding(mlel):
