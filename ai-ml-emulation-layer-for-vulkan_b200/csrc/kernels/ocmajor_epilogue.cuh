@@ -73,21 +73,6 @@ __device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, const void *s
                  : "memory");
 }
 
-// High 32 bits of x * mult + round(x), x = value - input zero point: product and rounding of a RESCALE whose shift
-// is at least 32, where the result only depends on the high word of the sum.  Double rounding adds 2^30 for x >= 0 and
-// subtracts it for x < 0: that is rn = 2^(shift-1) - 2^30 plus 2^31 when the sign bit of x is clear, one logic
-// operation on x (bumpMask = 2^31, or 0 without double rounding) feeding the third input of the 64-bit addition.
-// (Measured and not kept: the same value as acc * mult + (corrX * mult + rn) with the bump and the remaining shift
-// as multiply-high-adds.  It moves instructions from the general integer pipe to the multiply-add pipe, 56 % -> 43 %
-// and 14 % -> 19 % of their peaks, and ran 10 % slower: this epilogue issues one instruction every other cycle
-// whatever the mix.)
-__device__ __forceinline__ int32_t scaleHigh(int32_t x, int32_t mult, uint64_t rn, uint32_t bumpMask) {
-    const uint64_t prod = uint64_t(int64_t(x) * int64_t(mult));
-    const uint32_t extra = ~uint32_t(x) & bumpMask;
-    const uint64_t sum = prod + rn + uint64_t(extra);
-    return int32_t(uint32_t(sum >> 32));
-}
-
 // Shared-memory accesses by 32-bit shared address (a pointer into dynamic shared memory that has been passed
 // through a few functions is otherwise accessed with generic 64-bit loads and stores).
 __device__ __forceinline__ uint32_t ldsU8(uint32_t addr) {
