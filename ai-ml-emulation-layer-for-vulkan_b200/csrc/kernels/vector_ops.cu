@@ -10,6 +10,7 @@
 #include <string>
 
 #include "device_common.cuh"
+#include "gemm_i8_tcgen05.hpp"
 #include "kernels.hpp"
 
 namespace mlel {
@@ -110,32 +111,81 @@ template <typename T> __host__ __device__ constexpr int32_t highestOf() {
 }
 
 // ---- RESCALE (rescale.comp:27-72) -------------------------------------------------------------------------
+// A thread handles Q groups of four consecutive elements so that it writes 16 bytes at once (Q = 4 for int8
+// results, 2 for int16, 1 for int32): all of its loads are issued before the first result is computed.  Groups
+// past the last whole block of 4 Q elements are handled four elements at a time by the threads after it.
+template <typename IN, typename OUT> struct RescaleBlock {
+    static constexpr int Q = 4 / int(sizeof(OUT)) > 0 ? 4 / int(sizeof(OUT)) : 1;
+};
+
 template <typename IN, typename OUT>
-__global__ void rescaleVecKernel(const IN *__restrict__ in, OUT *__restrict__ out, int64_t groups,
+__device__ __forceinline__ void rescaleFour(const int32_t (&v)[4], int32_t (&r)[4], FastRescale f, const int32_t *mult,
+                                            const int8_t *shift, int perChannel, int c0, int32_t inZp, int32_t outZp,
+                                            int doubleRound) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (perChannel) {
+            f = makeFastRescale(__ldg(mult + c0 + k), int32_t(__ldg(shift + c0 + k)), inZp, doubleRound != 0);
+        }
+        r[k] = fastRescale(f, v[k], outZp, lowestOf<OUT>(), highestOf<OUT>());
+    }
+}
+
+template <typename IN, typename OUT>
+__global__ void rescaleVecKernel(const IN *__restrict__ in, OUT *__restrict__ out, int64_t blocks, int64_t tailGroups,
                                  const int32_t *__restrict__ mult, const int8_t *__restrict__ shift, int perChannel, int C,
                                  int32_t inZp, int32_t outZp, int doubleRound) {
-    FastRescale f = makeFastRescale(__ldg(mult), int32_t(__ldg(shift)), inZp, doubleRound != 0);
-    GRID_STRIDE(g, groups) {
-        int32_t v[4], r[4];
-        load4<IN>(in + 4 * g, v);
-        const int c0 = perChannel ? int((4 * g) % C) : 0;
+    constexpr int Q = RescaleBlock<IN, OUT>::Q;
+    const FastRescale f = makeFastRescale(__ldg(mult), int32_t(__ldg(shift)), inZp, doubleRound != 0);
+    GRID_STRIDE(g, blocks + tailGroups) {
+        if (g < blocks) {
+            const int64_t e0 = g * (4 * Q);
+            int32_t v[Q][4], r[Q][4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            if (perChannel) {
-                f = makeFastRescale(__ldg(mult + c0 + k), int32_t(__ldg(shift + c0 + k)), inZp, doubleRound != 0);
+            for (int q = 0; q < Q; ++q) {
+                load4<IN>(in + e0 + 4 * q, v[q]);
             }
-            r[k] = fastRescale(f, v[k], outZp, lowestOf<OUT>(), highestOf<OUT>());
+#pragma unroll
+            for (int q = 0; q < Q; ++q) {
+                // C is a multiple of 4 when the parameters are per channel: a group of four never wraps
+                const int c0 = perChannel ? int((e0 + 4 * q) % C) : 0;
+                rescaleFour<IN, OUT>(v[q], r[q], f, mult, shift, perChannel, c0, inZp, outZp, doubleRound);
+            }
+            if (Q == 4) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    w[q] = uint32_t(uint8_t(r[q][0])) | (uint32_t(uint8_t(r[q][1])) << 8) | (uint32_t(uint8_t(r[q][2])) << 16) |
+                           (uint32_t(uint8_t(r[q][3])) << 24);
+                }
+                *reinterpret_cast<uint4 *>(out + e0) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else if (Q == 2) {
+                *reinterpret_cast<uint4 *>(out + e0) =
+                    make_uint4(uint32_t(uint16_t(r[0][0])) | (uint32_t(uint16_t(r[0][1])) << 16),
+                               uint32_t(uint16_t(r[0][2])) | (uint32_t(uint16_t(r[0][3])) << 16),
+                               uint32_t(uint16_t(r[Q - 1][0])) | (uint32_t(uint16_t(r[Q - 1][1])) << 16),
+                               uint32_t(uint16_t(r[Q - 1][2])) | (uint32_t(uint16_t(r[Q - 1][3])) << 16));
+            } else {
+                store4<OUT>(out + e0, r[0]);
+            }
+        } else {
+            const int64_t e0 = blocks * (4 * Q) + (g - blocks) * 4;
+            int32_t v[4], r[4];
+            load4<IN>(in + e0, v);
+            rescaleFour<IN, OUT>(v, r, f, mult, shift, perChannel, perChannel ? int(e0 % C) : 0, inZp, outZp, doubleRound);
+            store4<OUT>(out + e0, r);
         }
-        store4<OUT>(out + 4 * g, r);
     }
 }
 
 template <typename IN, typename OUT>
 void launchRescale(const TView &in, const TView &out, const TView &mult, const TView &shift, const RescaleAttr &a,
                    int64_t n, cudaStream_t s) {
+    constexpr int Q = RescaleBlock<IN, OUT>::Q;
     const int C = int(out.dims[out.rank - 1]);
-    rescaleVecKernel<IN, OUT><<<gridFor(n / 4, kThreads, 16), kThreads, 0, s>>>(
-        reinterpret_cast<const IN *>(in.ptr), reinterpret_cast<OUT *>(out.ptr), n / 4,
+    const int64_t blocks = n / (4 * Q), tailGroups = (n - blocks * 4 * Q) / 4;
+    rescaleVecKernel<IN, OUT><<<gridFor(blocks + tailGroups, kThreads, 16), kThreads, 0, s>>>(
+        reinterpret_cast<const IN *>(in.ptr), reinterpret_cast<OUT *>(out.ptr), blocks, tailGroups,
         reinterpret_cast<const int32_t *>(mult.ptr), reinterpret_cast<const int8_t *>(shift.ptr), a.perChannel ? 1 : 0, C,
         int32_t(wrapTo(in.dtype, a.inZp)), int32_t(wrapTo(out.dtype, a.outZp)), (a.scale32 && a.doubleRound) ? 1 : 0);
 }
@@ -309,71 +359,96 @@ template <typename T> void launchRowReduce(int32_t op, const TView &in, const TV
 }
 
 // ---- TRANSPOSE that keeps the last axis (transpose.comp:19-32) -------------------------------------------------
-// Rows of the last axis move as wholes: a thread copies 16 bytes; only the row index is permuted.
+// Rows of the last axis move as wholes: a thread copies 16 bytes; only the row index is permuted.  The index is
+// taken apart with multiply-high divisions by constants made on the host (a 64-bit division per axis and thread was
+// most of this kernel's time).
 struct RowPermute {
-    uint32_t outDims[kMaxRank]; // output dims without the last axis
+    FastDiv outDims[kMaxRank];  // output dims without the last axis
     int64_t inStride[kMaxRank]; // input byte stride of the axis each output axis comes from
+    FastDiv chunksPerRow;
     int rank;                   // number of outer axes
 };
 
-__global__ void transposeRowsKernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int64_t chunks, int chunksPerRow,
-                                    RowPermute p) {
-    GRID_STRIDE(e, chunks) {
-        int64_t row = e / chunksPerRow;
-        const int chunk = int(e - row * chunksPerRow);
+__device__ __forceinline__ uint32_t divBy(uint32_t n, const FastDiv &f) { return f.mul == 0u ? n : __umulhi(n, f.mul) >> f.shift; }
+
+__global__ void transposeRowsKernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, int64_t chunks, RowPermute p) {
+    GRID_STRIDE(e, chunks) { // the launcher refuses 2^31 chunks and more
+        uint32_t row = divBy(uint32_t(e), p.chunksPerRow);
+        const uint32_t chunk = uint32_t(e) - row * p.chunksPerRow.d;
         int64_t src = 0;
 #pragma unroll
         for (int i = kMaxRank - 1; i >= 0; --i) {
             if (i < p.rank) {
-                src += int64_t(row % p.outDims[i]) * p.inStride[i];
-                row /= p.outDims[i];
+                const uint32_t q = divBy(row, p.outDims[i]);
+                src += int64_t(row - q * p.outDims[i].d) * p.inStride[i];
+                row = q;
             }
         }
-        *reinterpret_cast<int4 *>(out + 16 * e) = *reinterpret_cast<const int4 *>(in + src + 16 * int64_t(chunk));
+        *reinterpret_cast<int4 *>(out + 16 * e) = __ldg(reinterpret_cast<const int4 *>(in + src + 16 * int64_t(chunk)));
     }
 }
 
 // ---- TRANSPOSE that swaps the last axis with another one, one-byte elements ------------------------------------
 // out[..., c, r] = in[..., r (axis p), ..., c (last axis)]: per combination of the other axes a 2-D transpose of
-// an R x Ccols byte matrix whose rows are `inRowStride` bytes apart.  64 x 64 tiles through shared memory,
-// 16-byte loads and stores.
+// an R x Ccols byte matrix whose rows are `inRowStride` bytes apart.  No shared memory: a lane reads 4 rows x 32
+// bytes (two 16-byte loads per row, whole 32-byte sectors), transposes the eight 4 x 4 byte blocks in registers
+// with byte permutes, and writes 32 words, one to each of 32 output rows; the 32 lanes of a warp hold consecutive
+// row quads, so every such store of the warp is 128 contiguous bytes of one output row.
 struct BatchPermute {
-    uint32_t outDims[kMaxRank]; // output dims of the outer axes (all but the last two)
+    FastDiv outDims[kMaxRank];  // output dims of the outer axes (all but the last two)
     int64_t inStride[kMaxRank]; // input byte stride of the axis each of them comes from
+    FastDiv perBatch;           // warps per matrix
+    FastDiv colGroups;          // 32-column groups per matrix
     int rank;
 };
 
 __global__ void __launch_bounds__(256) transposeLast2BytesKernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out,
-                                                                 int R, int Ccols, int64_t inRowStride, BatchPermute p) {
-    __shared__ uint8_t tile[64][64 + 16]; // [r][c]
-    int64_t batch = blockIdx.z;
-    int64_t src = 0;
+                                                                 int R, int Ccols, int64_t inRowStride, int64_t warps,
+                                                                 BatchPermute p) {
+    const int lane = threadIdx.x & 31;
+    for (int64_t wid = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; wid < warps;
+         wid += (int64_t(gridDim.x) * blockDim.x) >> 5) {
+        uint32_t batch = divBy(uint32_t(wid), p.perBatch);
+        const uint32_t inMat = uint32_t(wid) - batch * p.perBatch.d;
+        const uint32_t rowGroup = divBy(inMat, p.colGroups);
+        const int c0 = int(inMat - rowGroup * p.colGroups.d) * 32;
+        const int r = (int(rowGroup) * 32 + lane) * 4;
+        uint8_t *dst = out + int64_t(batch) * R * Ccols;
+        int64_t src = 0;
 #pragma unroll
-    for (int i = kMaxRank - 1; i >= 0; --i) {
-        if (i < p.rank) {
-            src += int64_t(batch % p.outDims[i]) * p.inStride[i];
-            batch /= p.outDims[i];
+        for (int i = kMaxRank - 1; i >= 0; --i) {
+            if (i < p.rank) {
+                const uint32_t q = divBy(batch, p.outDims[i]);
+                src += int64_t(batch - q * p.outDims[i].d) * p.inStride[i];
+                batch = q;
+            }
         }
-    }
-    const uint8_t *mat = in + src;
-    uint8_t *dst = out + int64_t(blockIdx.z) * R * Ccols;
-    const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
-    const int t = threadIdx.x;
-    const int lr = t >> 2, ls = (t & 3) * 16; // load: row r0 + lr, bytes c0 + ls ..; store: row c0 + lr, bytes r0 + ls ..
-    int4 v = make_int4(0, 0, 0, 0);
-    if (r0 + lr < R && c0 + ls < Ccols) {
-        v = __ldg(reinterpret_cast<const int4 *>(mat + int64_t(r0 + lr) * inRowStride + c0 + ls));
-    }
-    *reinterpret_cast<int4 *>(&tile[lr][ls]) = v;
-    __syncthreads();
-    if (c0 + lr < Ccols && r0 + ls < R) {
-        uint32_t words[4] = {0, 0, 0, 0};
+        if (r >= R) { // R is a multiple of 4: a row quad is inside or outside as a whole
+            continue;
+        }
+        const bool second = c0 + 16 < Ccols; // Ccols is a multiple of 16
+        uint32_t w[4][8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            words[i >> 2] |= uint32_t(tile[ls + i][lr]) << (8 * (i & 3));
+        for (int i = 0; i < 4; ++i) {
+            const uint8_t *row = in + src + int64_t(r + i) * inRowStride + c0;
+            const int4 lo = __ldg(reinterpret_cast<const int4 *>(row));
+            const int4 hi = second ? __ldg(reinterpret_cast<const int4 *>(row + 16)) : make_int4(0, 0, 0, 0);
+            w[i][0] = uint32_t(lo.x), w[i][1] = uint32_t(lo.y), w[i][2] = uint32_t(lo.z), w[i][3] = uint32_t(lo.w);
+            w[i][4] = uint32_t(hi.x), w[i][5] = uint32_t(hi.y), w[i][6] = uint32_t(hi.z), w[i][7] = uint32_t(hi.w);
         }
-        *reinterpret_cast<int4 *>(dst + int64_t(c0 + lr) * R + r0 + ls) =
-            make_int4(int(words[0]), int(words[1]), int(words[2]), int(words[3]));
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            if (g < 4 || second) {
+                // rows r .. r+3, columns c0 + 4g .. +3  ->  output rows c0 + 4g + k, bytes r .. r+3
+                const uint32_t t0 = __byte_perm(w[0][g], w[1][g], 0x5140), t1 = __byte_perm(w[2][g], w[3][g], 0x5140);
+                const uint32_t t2 = __byte_perm(w[0][g], w[1][g], 0x7362), t3 = __byte_perm(w[2][g], w[3][g], 0x7362);
+                uint8_t *o = dst + int64_t(c0 + 4 * g) * R + r;
+                *reinterpret_cast<uint32_t *>(o) = __byte_perm(t0, t1, 0x5410);
+                *reinterpret_cast<uint32_t *>(o + R) = __byte_perm(t0, t1, 0x7632);
+                *reinterpret_cast<uint32_t *>(o + 2 * int64_t(R)) = __byte_perm(t2, t3, 0x5410);
+                *reinterpret_cast<uint32_t *>(o + 3 * int64_t(R)) = __byte_perm(t2, t3, 0x7632);
+            }
+        }
     }
 }
 
@@ -514,19 +589,22 @@ bool vecTransposeRows(const TView &in, const TView &out, const uint32_t *perms, 
     if (rowBytes % 16 != 0 || rowBytes / 16 > (1 << 24)) {
         return false;
     }
+    const int64_t chunks = n * dtypeSize(out.dtype) / 16;
+    if (chunks >= (int64_t(1) << 31)) {
+        return false;
+    }
     RowPermute p{};
     p.rank = rank - 1;
+    p.chunksPerRow = makeFastDiv(rowBytes / 16);
     for (int i = 0; i < rank - 1; ++i) {
         if (perms[i] >= uint32_t(rank - 1) || in.dims[perms[i]] != out.dims[i]) {
             return false;
         }
-        p.outDims[i] = out.dims[i];
+        p.outDims[i] = makeFastDiv(out.dims[i]);
         p.inStride[i] = in.strides[perms[i]];
     }
-    const int64_t chunks = n * dtypeSize(out.dtype) / 16;
     transposeRowsKernel<<<gridFor(chunks, kThreads, 16), kThreads, 0, s>>>(reinterpret_cast<const uint8_t *>(in.ptr),
-                                                                          reinterpret_cast<uint8_t *>(out.ptr), chunks,
-                                                                          int(rowBytes / 16), p);
+                                                                          reinterpret_cast<uint8_t *>(out.ptr), chunks, p);
     *rc = finish("TRANSPOSE");
     return true;
 }
@@ -541,7 +619,7 @@ bool vecTransposeLast2Bytes(const TView &in, const TView &out, const uint32_t *p
     const uint32_t pAxis = perms[rank - 1];
     const int64_t R = in.dims[pAxis], Ccols = in.dims[rank - 1];
     const int64_t inRowStride = in.strides[pAxis];
-    if (R % 16 != 0 || Ccols % 16 != 0 || inRowStride % 16 != 0 || out.dims[rank - 1] != R || out.dims[rank - 2] != Ccols) {
+    if (R % 4 != 0 || Ccols % 16 != 0 || inRowStride % 16 != 0 || out.dims[rank - 1] != R || out.dims[rank - 2] != Ccols) {
         return false;
     }
     BatchPermute p{};
@@ -551,19 +629,23 @@ bool vecTransposeLast2Bytes(const TView &in, const TView &out, const uint32_t *p
         if (perms[i] >= uint32_t(rank) || perms[i] == pAxis || int(perms[i]) == rank - 1 || in.dims[perms[i]] != out.dims[i]) {
             return false;
         }
-        p.outDims[i] = out.dims[i];
+        p.outDims[i] = makeFastDiv(out.dims[i]);
         p.inStride[i] = in.strides[perms[i]];
         if (p.inStride[i] % 16 != 0) {
             return false;
         }
         batches *= out.dims[i];
     }
-    if (batches > 65535 || (R + 63) / 64 > 65535) {
+    const int64_t colGroups = (Ccols + 31) / 32, rowGroups = (R + 127) / 128;
+    const int64_t warps = batches * colGroups * rowGroups;
+    if (warps >= (int64_t(1) << 31)) {
         return false;
     }
-    const dim3 grid(unsigned((Ccols + 63) / 64), unsigned((R + 63) / 64), unsigned(batches));
-    transposeLast2BytesKernel<<<grid, 256, 0, s>>>(reinterpret_cast<const uint8_t *>(in.ptr), reinterpret_cast<uint8_t *>(out.ptr),
-                                                   int(R), int(Ccols), inRowStride, p);
+    p.perBatch = makeFastDiv(colGroups * rowGroups);
+    p.colGroups = makeFastDiv(colGroups);
+    transposeLast2BytesKernel<<<gridFor(warps * 32, 256, 8), 256, 0, s>>>(reinterpret_cast<const uint8_t *>(in.ptr),
+                                                                        reinterpret_cast<uint8_t *>(out.ptr), int(R),
+                                                                        int(Ccols), inRowStride, warps, p);
     *rc = finish("TRANSPOSE");
     return true;
 }
