@@ -317,6 +317,8 @@ def test_avg_pool2d(mlel, case):
     # 3x3: stride 1, stride 2 with an odd output width (one output per thread), stride 2 without padding (two)
     ((1, 10, 10, 16), (3, 3), (1, 1), (1, 1, 1, 1)), ((1, 9, 9, 16), (3, 3), (2, 2), (1, 1, 1, 1)),
     ((2, 9, 13, 32), (3, 3), (2, 2), (0, 0, 0, 0)),
+    # stride 2, even output width and odd output height (two outputs per thread); even both ways with padding (four)
+    ((1, 11, 13, 16), (3, 3), (2, 2), (0, 0, 0, 0)), ((3, 12, 20, 48), (3, 3), (2, 2), (1, 1, 1, 1)),
 ])
 def test_max_pool2d(mlel, case):
     shape, k, s, p = case
