@@ -390,10 +390,11 @@ __global__ void transposeRowsKernel(const uint8_t *__restrict__ in, uint8_t *__r
 
 // ---- TRANSPOSE that swaps the last axis with another one, one-byte elements ------------------------------------
 // out[..., c, r] = in[..., r (axis p), ..., c (last axis)]: per combination of the other axes a 2-D transpose of
-// an R x Ccols byte matrix whose rows are `inRowStride` bytes apart.  No shared memory: a lane reads 4 rows x 32
-// bytes (two 16-byte loads per row, whole 32-byte sectors), transposes the eight 4 x 4 byte blocks in registers
-// with byte permutes, and writes 32 words, one to each of 32 output rows; the 32 lanes of a warp hold consecutive
-// row quads, so every such store of the warp is 128 contiguous bytes of one output row.
+// an R x Ccols byte matrix whose rows are `inRowStride` bytes apart.  No shared memory: a lane reads 8 rows x 16
+// bytes (neighbouring lanes take the two halves of a 32-byte sector), transposes the eight 4 x 4 byte blocks in
+// registers with byte permutes, and writes 16 double words, one to each of 16 output rows; the lanes of a warp
+// that share a column half hold consecutive row octets, so every such store of the warp is two runs of 128
+// contiguous bytes.
 struct BatchPermute {
     FastDiv outDims[kMaxRank];  // output dims of the outer axes (all but the last two)
     int64_t inStride[kMaxRank]; // input byte stride of the axis each of them comes from
@@ -411,8 +412,8 @@ __global__ void __launch_bounds__(256) transposeLast2BytesKernel(const uint8_t *
         uint32_t batch = divBy(uint32_t(wid), p.perBatch);
         const uint32_t inMat = uint32_t(wid) - batch * p.perBatch.d;
         const uint32_t rowGroup = divBy(inMat, p.colGroups);
-        const int c0 = int(inMat - rowGroup * p.colGroups.d) * 32;
-        const int r = (int(rowGroup) * 32 + lane) * 4;
+        const int c0 = int(inMat - rowGroup * p.colGroups.d) * 32 + (lane & 1) * 16;
+        const int r = (int(rowGroup) * 16 + (lane >> 1)) * 8;
         uint8_t *dst = out + int64_t(batch) * R * Ccols;
         int64_t src = 0;
 #pragma unroll
@@ -423,30 +424,32 @@ __global__ void __launch_bounds__(256) transposeLast2BytesKernel(const uint8_t *
                 batch = q;
             }
         }
-        if (r >= R) { // R is a multiple of 4: a row quad is inside or outside as a whole
+        if (r >= R || c0 >= Ccols) { // R is a multiple of 8 and Ccols of 16: a block is inside or outside as a whole
             continue;
         }
-        const bool second = c0 + 16 < Ccols; // Ccols is a multiple of 16
-        uint32_t w[4][8];
+        uint32_t w[8][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint8_t *row = in + src + int64_t(r + i) * inRowStride + c0;
-            const int4 lo = __ldg(reinterpret_cast<const int4 *>(row));
-            const int4 hi = second ? __ldg(reinterpret_cast<const int4 *>(row + 16)) : make_int4(0, 0, 0, 0);
-            w[i][0] = uint32_t(lo.x), w[i][1] = uint32_t(lo.y), w[i][2] = uint32_t(lo.z), w[i][3] = uint32_t(lo.w);
-            w[i][4] = uint32_t(hi.x), w[i][5] = uint32_t(hi.y), w[i][6] = uint32_t(hi.z), w[i][7] = uint32_t(hi.w);
+        for (int i = 0; i < 8; ++i) {
+            const int4 v = __ldg(reinterpret_cast<const int4 *>(in + src + int64_t(r + i) * inRowStride + c0));
+            w[i][0] = uint32_t(v.x), w[i][1] = uint32_t(v.y), w[i][2] = uint32_t(v.z), w[i][3] = uint32_t(v.w);
         }
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            if (g < 4 || second) {
-                // rows r .. r+3, columns c0 + 4g .. +3  ->  output rows c0 + 4g + k, bytes r .. r+3
-                const uint32_t t0 = __byte_perm(w[0][g], w[1][g], 0x5140), t1 = __byte_perm(w[2][g], w[3][g], 0x5140);
-                const uint32_t t2 = __byte_perm(w[0][g], w[1][g], 0x7362), t3 = __byte_perm(w[2][g], w[3][g], 0x7362);
-                uint8_t *o = dst + int64_t(c0 + 4 * g) * R + r;
-                *reinterpret_cast<uint32_t *>(o) = __byte_perm(t0, t1, 0x5410);
-                *reinterpret_cast<uint32_t *>(o + R) = __byte_perm(t0, t1, 0x7632);
-                *reinterpret_cast<uint32_t *>(o + 2 * int64_t(R)) = __byte_perm(t2, t3, 0x5410);
-                *reinterpret_cast<uint32_t *>(o + 3 * int64_t(R)) = __byte_perm(t2, t3, 0x7632);
+        for (int g = 0; g < 4; ++g) {
+            // rows r .. r+7, columns c0 + 4g .. +3  ->  output rows c0 + 4g + k, bytes r .. r+7
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t t0 = __byte_perm(w[4 * h][g], w[4 * h + 1][g], 0x5140);
+                const uint32_t t1 = __byte_perm(w[4 * h + 2][g], w[4 * h + 3][g], 0x5140);
+                const uint32_t t2 = __byte_perm(w[4 * h][g], w[4 * h + 1][g], 0x7362);
+                const uint32_t t3 = __byte_perm(w[4 * h + 2][g], w[4 * h + 3][g], 0x7362);
+                uint32_t *o = h == 0 ? lo : hi;
+                o[0] = __byte_perm(t0, t1, 0x5410), o[1] = __byte_perm(t0, t1, 0x7632);
+                o[2] = __byte_perm(t2, t3, 0x5410), o[3] = __byte_perm(t2, t3, 0x7632);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                *reinterpret_cast<uint2 *>(dst + int64_t(c0 + 4 * g + k) * R + r) = make_uint2(lo[k], hi[k]);
             }
         }
     }
@@ -619,7 +622,7 @@ bool vecTransposeLast2Bytes(const TView &in, const TView &out, const uint32_t *p
     const uint32_t pAxis = perms[rank - 1];
     const int64_t R = in.dims[pAxis], Ccols = in.dims[rank - 1];
     const int64_t inRowStride = in.strides[pAxis];
-    if (R % 4 != 0 || Ccols % 16 != 0 || inRowStride % 16 != 0 || out.dims[rank - 1] != R || out.dims[rank - 2] != Ccols) {
+    if (R % 8 != 0 || Ccols % 16 != 0 || inRowStride % 16 != 0 || out.dims[rank - 1] != R || out.dims[rank - 2] != Ccols) {
         return false;
     }
     BatchPermute p{};
