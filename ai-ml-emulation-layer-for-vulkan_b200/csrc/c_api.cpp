@@ -127,6 +127,10 @@ long long mlel_tensor_core_launches(int kernel) {
     return kernel >= 0 && kernel < 3 ? g_tensorCoreLaunches[kernel].load(std::memory_order_relaxed) : -1;
 }
 
+int mlel_selftest_wait_timeout(void *cuda_stream, int *recorded_code) {
+    return guarded([&] { return waitTimeoutSelfTest(static_cast<cudaStream_t>(cuda_stream), recorded_code); });
+}
+
 int mlel_pipeline_create(uint32_t flags, mlel_pipeline **out) {
     return guarded([&] {
         *out = new mlel_pipeline(flags);
@@ -220,6 +224,18 @@ const char *mlel_tosa_op_name(int index) {
     return index >= 0 && size_t(index) < names.size() ? names[size_t(index)].c_str() : nullptr;
 }
 int mlel_tosa_op_supported(const char *op_name) { return tosaOpSupported(op_name) ? 1 : 0; }
+int mlel_tosa_lookup(const char *import_name, const char *op_name) {
+    if (import_name == nullptr || op_name == nullptr || !extInstSetRegistered(import_name)) {
+        return -1;
+    }
+    const auto &names = tosaOpNames();
+    for (size_t i = 0; i < names.size(); ++i) {
+        if (names[i] == op_name) {
+            return tosaOpSupported(op_name) ? int(i) : -1;
+        }
+    }
+    return -1;
+}
 
 int mlel_pipeline_op_count(const mlel_pipeline *p) { return int(p->impl->getPipelines().size()); }
 const char *mlel_pipeline_op_name(const mlel_pipeline *p, int index) {
@@ -821,6 +837,135 @@ int mlel_cuda_rescale(const mlel_tensor *input, const mlel_tensor *output, const
         op.out = {3};
         op.i[0] = input_zp, op.i[1] = output_zp, op.i[2] = scale32, op.i[3] = double_round, op.i[4] = per_channel;
         return runSingle(op, {input, multiplier, shift, output}, static_cast<cudaStream_t>(cuda_stream));
+    });
+}
+
+int mlel_cuda_avg_pool2d(const mlel_tensor *input, const mlel_tensor *output, const int32_t kernel[2], const int32_t stride[2],
+                         const int32_t pad[4], int32_t input_zp, int32_t output_zp, void *cuda_stream) {
+    return guarded([&] {
+        OpDesc op;
+        op.kind = OP_AVG_POOL2D;
+        op.in = {0};
+        op.out = {1};
+        op.i[0] = kernel[0], op.i[1] = kernel[1], op.i[2] = stride[0], op.i[3] = stride[1];
+        for (int k = 0; k < 4; ++k) {
+            op.i[4 + k] = pad[k];
+        }
+        op.i[8] = input_zp, op.i[9] = output_zp;
+        return runSingle(op, {input, output}, static_cast<cudaStream_t>(cuda_stream));
+    });
+}
+
+int mlel_cuda_max_pool2d(const mlel_tensor *input, const mlel_tensor *output, const int32_t kernel[2], const int32_t stride[2],
+                         const int32_t pad[4], void *cuda_stream) {
+    return guarded([&] {
+        OpDesc op;
+        op.kind = OP_MAX_POOL2D;
+        op.in = {0};
+        op.out = {1};
+        op.i[0] = kernel[0], op.i[1] = kernel[1], op.i[2] = stride[0], op.i[3] = stride[1];
+        for (int k = 0; k < 4; ++k) {
+            op.i[4 + k] = pad[k];
+        }
+        return runSingle(op, {input, output}, static_cast<cudaStream_t>(cuda_stream));
+    });
+}
+
+int mlel_cuda_table(const mlel_tensor *input, const mlel_tensor *table, const mlel_tensor *output, void *cuda_stream) {
+    return guarded([&] {
+        OpDesc op;
+        op.kind = OP_TABLE;
+        op.in = {0, 1};
+        op.out = {2};
+        return runSingle(op, {input, table, output}, static_cast<cudaStream_t>(cuda_stream));
+    });
+}
+
+int mlel_cuda_transpose(const mlel_tensor *input, const mlel_tensor *output, const uint32_t *perms, uint32_t rank,
+                        void *cuda_stream) {
+    return guarded([&] {
+        if (rank > uint32_t(kMaxRank) || perms == nullptr) {
+            setLastError("mlel_cuda_transpose: bad permutation");
+            return int(MLEL_ERROR_UNKNOWN);
+        }
+        OpDesc op;
+        op.kind = OP_TRANSPOSE;
+        op.in = {0};
+        op.out = {1};
+        for (uint32_t k = 0; k < rank; ++k) {
+            op.i[k] = int32_t(perms[k]);
+        }
+        return runSingle(op, {input, output}, static_cast<cudaStream_t>(cuda_stream));
+    });
+}
+
+int mlel_cuda_concat(const mlel_tensor *const *inputs, uint32_t input_count, const mlel_tensor *output, uint32_t axis,
+                     void *cuda_stream) {
+    return guarded([&] {
+        // one pass per input, each writing at the offset accumulated along `axis` (concat.comp:20-34)
+        uint32_t offset = 0;
+        for (uint32_t k = 0; k < input_count; ++k) {
+            if (inputs == nullptr || inputs[k] == nullptr || axis >= uint32_t(inputs[k]->desc.rank)) {
+                setLastError("mlel_cuda_concat: bad input");
+                return int(MLEL_ERROR_UNKNOWN);
+            }
+            OpDesc op;
+            op.kind = OP_CONCAT;
+            op.in = {0};
+            op.out = {1};
+            op.i[0] = int32_t(axis), op.i[1] = int32_t(offset);
+            const int rc = runSingle(op, {inputs[k], output}, static_cast<cudaStream_t>(cuda_stream));
+            if (rc != MLEL_SUCCESS) {
+                return rc;
+            }
+            offset += uint32_t(inputs[k]->desc.dims[axis]);
+        }
+        return int(MLEL_SUCCESS);
+    });
+}
+
+int mlel_cuda_clamp(const mlel_tensor *input, const mlel_tensor *output, double min_value, double max_value,
+                    void *cuda_stream) {
+    return guarded([&] {
+        OpDesc op;
+        op.kind = OP_CLAMP;
+        op.in = {0};
+        op.out = {1};
+        op.d[0] = min_value, op.d[1] = max_value;
+        return runSingle(op, {input, output}, static_cast<cudaStream_t>(cuda_stream));
+    });
+}
+
+int mlel_cuda_binary(const char *op_name, const mlel_tensor *input1, const mlel_tensor *input2, const mlel_tensor *output,
+                     void *cuda_stream) {
+    return guarded([&] {
+        const auto it = kBinary.find(op_name != nullptr ? op_name : "");
+        if (it == kBinary.end()) {
+            throw UnsupportedError(std::string("unknown elementwise binary operator ") + (op_name != nullptr ? op_name : ""));
+        }
+        OpDesc op;
+        op.kind = OP_BINARY;
+        op.sub = it->second;
+        op.in = {0, 1};
+        op.out = {2};
+        return runSingle(op, {input1, input2, output}, static_cast<cudaStream_t>(cuda_stream));
+    });
+}
+
+int mlel_cuda_reduce(const char *op_name, const mlel_tensor *input, const mlel_tensor *output, uint32_t axis,
+                     void *cuda_stream) {
+    return guarded([&] {
+        const auto it = kReduce.find(op_name != nullptr ? op_name : "");
+        if (it == kReduce.end()) {
+            throw UnsupportedError(std::string("unknown reduce operator ") + (op_name != nullptr ? op_name : ""));
+        }
+        OpDesc op;
+        op.kind = OP_REDUCE;
+        op.sub = it->second;
+        op.in = {0};
+        op.out = {1};
+        op.i[0] = int32_t(axis);
+        return runSingle(op, {input, output}, static_cast<cudaStream_t>(cuda_stream));
     });
 }
 

@@ -780,6 +780,44 @@ int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
                                : launchVariant<128, 6, kAGather, false>(mapA, mapB, p, s);
 }
 
+namespace {
+// Self-test of the give-up path of the bounded waits: one thread waits on an mbarrier that nobody arrives at, with
+// a limit of about a millisecond instead of the kernels' two seconds, records the code and returns.
+__global__ void waitTimeoutSelfTestKernel(int code, long long limitCycles, int *gaveUp) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        tc::mbarInit(&bar, 1u);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *gaveUp = tc::mbarWaitLimit(&bar, 0u, code, limitCycles) ? 0 : 1;
+    }
+}
+} // namespace
+
+int waitTimeoutSelfTest(cudaStream_t s, int *codeOut) {
+    constexpr int kCode = 99;
+    int *flag = nullptr;
+    if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) {
+        setLastError("wait self-test: cudaMalloc failed");
+        return MLEL_ERROR_DEVICE;
+    }
+    cudaMemsetAsync(flag, 0xff, sizeof(int), s);
+    waitTimeoutSelfTestKernel<<<1, 32, 0, s>>>(kCode, 2000000ll, flag); // about 1 ms of SM clock
+    int gaveUp = -1;
+    const bool ok = cudaMemcpyAsync(&gaveUp, flag, sizeof(int), cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+                    cudaStreamSynchronize(s) == cudaSuccess;
+    cudaFree(flag);
+    if (!ok) {
+        setLastError("wait self-test: kernel or copy failed");
+        return MLEL_ERROR_DEVICE;
+    }
+    const int recorded = tc::readErrorWord();
+    if (recorded == kCode) {
+        tc::clearErrorWord(); // only the self-test's own code is cleared: a real time-out stays recorded
+    }
+    *codeOut = gaveUp == 1 ? recorded : 0;
+    return MLEL_SUCCESS;
+}
+
 int tcgen05ErrorFlag() {
     const int v = tc::readErrorWord();
     if (v != 0) {

@@ -115,5 +115,8 @@ extern std::atomic<long long> g_tensorCoreLaunches[3];
 
 // Value of the device-side error word written by a bounded wait that ran out (0 = none).
 int tcgen05ErrorFlag();
+// Runs a one-thread kernel whose bounded wait (limit about 1 ms) cannot be satisfied; *codeOut receives the code the
+// wait recorded (99), 0 if the wait did not give up.  The recorded code is cleared again.
+int waitTimeoutSelfTest(cudaStream_t stream, int *codeOut);
 
 } // namespace mlel

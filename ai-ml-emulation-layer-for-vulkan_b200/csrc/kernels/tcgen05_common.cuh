@@ -29,6 +29,10 @@ static inline int readErrorWord() {
     cudaMemcpyFromSymbol(&v, g_tcgen05Error, sizeof(int));
     return v;
 }
+static inline void clearErrorWord() {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_tcgen05Error, &zero, sizeof(int));
+}
 
 constexpr int BM = 128;    // rows per tile (UMMA M)
 constexpr int BK = 128;    // bytes (= int8 elements) of K per pipeline stage
@@ -78,7 +82,7 @@ __device__ __forceinline__ bool mbarTryWaitHint(uint64_t *bar, uint32_t parity, 
 // does not get through at once suspends in hardware between checks, so that a waiting role does not take issue
 // slots from the warps that share its scheduler (the epilogue warps do the arithmetic); the clock is read every
 // 64th check.
-__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int code) {
+__device__ __forceinline__ bool mbarWaitLimit(uint64_t *bar, uint32_t parity, int code, long long limitCycles) {
     if (mbarTryWait(bar, parity)) {
         return true;
     }
@@ -86,7 +90,7 @@ __device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int cod
     unsigned polls = 0;
     while (!mbarTryWaitHint(bar, parity, 1000u)) {
         if ((++polls & 63u) == 0) {
-            if (clock64() - start > kWaitLimitCycles) {
+            if (clock64() - start > limitCycles) {
                 atomicCAS(&g_tcgen05Error, 0, code);
                 return false;
             }
@@ -94,25 +98,8 @@ __device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int cod
     }
     return true;
 }
-
-// The same for a barrier that another CTA of the cluster completes (a remote arrival, a commit issued by the
-// peer, a bulk copy of the peer): polls without a suspend-time hint, because a waiter suspended with a long hint
-// was seen to sleep through such completions until the hint ran out (about 1 us per wait).
-__device__ __forceinline__ bool mbarWaitRemote(uint64_t *bar, uint32_t parity, int code) {
-    if (mbarTryWait(bar, parity)) {
-        return true;
-    }
-    const long long start = clock64();
-    unsigned polls = 0;
-    while (!mbarTryWait(bar, parity)) {
-        if ((++polls & 1023u) == 0) {
-            if (clock64() - start > kWaitLimitCycles) {
-                atomicCAS(&g_tcgen05Error, 0, code);
-                return false;
-            }
-        }
-    }
-    return true;
+__device__ __forceinline__ bool mbarWait(uint64_t *bar, uint32_t parity, int code) {
+    return mbarWaitLimit(bar, parity, code, kWaitLimitCycles);
 }
 
 __device__ __forceinline__ void tmaLoad3d(const CUtensorMap *map, void *dst, uint64_t *bar, int c0, int c1, int c2) {

@@ -422,7 +422,22 @@ int Session::dispatchGraph(cudaStream_t stream) {
     auto found = graphs_.find(key);
     if (found == graphs_.end()) {
         if (graphs_.size() >= kMaxCapturedGraphs) {
-            dropGraphs();
+            // Make room for one: the entry that was launched longest ago goes.  Its last launch may still be running
+            // on the caller's stream, so wait for that stream before the executable graph is destroyed.
+            auto oldest = graphs_.begin();
+            for (auto it = graphs_.begin(); it != graphs_.end(); ++it) {
+                if (it->second.lastUse < oldest->second.lastUse) {
+                    oldest = it;
+                }
+            }
+            cudaStreamSynchronize(stream);
+            if (oldest->second.exec != nullptr) {
+                cudaGraphExecDestroy(oldest->second.exec);
+            }
+            if (oldest->second.graph != nullptr) {
+                cudaGraphDestroy(oldest->second.graph);
+            }
+            graphs_.erase(oldest);
         }
         CapturedGraph captured;
         cudaStream_t capture = nullptr;
@@ -454,6 +469,7 @@ int Session::dispatchGraph(cudaStream_t stream) {
         }
         found = graphs_.emplace(key, captured).first;
     }
+    found->second.lastUse = ++useCounter_;
     if (cudaGraphLaunch(found->second.exec, stream) != cudaSuccess) {
         setLastError("cudaGraphLaunch failed");
         return MLEL_ERROR_DEVICE;

@@ -73,7 +73,9 @@ class Session {
     struct CapturedGraph {
         cudaGraph_t graph{nullptr};
         cudaGraphExec_t exec{nullptr};
+        uint64_t lastUse{0}; // value of useCounter_ at the last launch: the entry with the smallest one is evicted
     };
+    uint64_t useCounter_{0};
     std::map<std::vector<const void *>, CapturedGraph> graphs_;
     std::vector<const void *> bindingKey() const;
     void dropGraphs();

@@ -121,6 +121,12 @@ int mlel_ext_inst_set_registered(const char *import_name);
 int mlel_tosa_op_count(void);
 const char *mlel_tosa_op_name(int index);
 int mlel_tosa_op_supported(const char *op_name);
+/* The registry as one query, by names (the numeric opcodes live in a header the reference does not vendor):
+ * index of the handler of `op_name` in the instruction set imported as `import_name` ("TOSA.001000.1"), the same
+ * index mlel_tosa_op_name uses; -1 when the set is not registered or has no such operator
+ * (graph/graph_ext_inst_registry.cpp:53-59 selects the decoder by import string, graph_tosa_1_0_ext_inst.cpp:41-108
+ * the handler). */
+int mlel_tosa_lookup(const char *import_name, const char *op_name);
 
 /* Introspection of the lowered graph (the reference logs the same at Info severity). */
 int mlel_pipeline_op_count(const mlel_pipeline *p);
@@ -304,6 +310,13 @@ int mlel_measure_int8_mma_peak(int batches, void *cuda_stream, float *ms, double
  * Another key or value: MLEL_ERROR_UNKNOWN. */
 int mlel_set_tuning(const char *key, int value);
 
+/* Self-test of the bounded waits (no counterpart in the reference).  Every wait inside the tensor-core kernels has
+ * a limit (about two seconds), after which the kernel records a code that mlel_device_error() reports, leaves its
+ * loops and releases its tensor memory.  This runs a one-thread kernel that waits, with a limit of about a
+ * millisecond, on a barrier nobody arrives at: *recorded_code receives the code that wait recorded (99), or 0 if
+ * it did not give up.  The code is cleared again, so mlel_device_error() is 0 afterwards.  Synchronises the stream. */
+int mlel_selftest_wait_timeout(void *cuda_stream, int *recorded_code);
+
 /* Diagnostic (no counterpart in the reference): how often the library has enqueued tensor-core kernel
  * `kernel` since it was loaded -- 0 the pixel-major tcgen05 kernel, 1 the channel-major one, 2 the paired
  * (two-CTA) one; -1 for another index.  Tests use it to see which kernel took a case. */
@@ -334,6 +347,28 @@ int mlel_cuda_matmul(const mlel_tensor *a, const mlel_tensor *b, const mlel_tens
 int mlel_cuda_rescale(const mlel_tensor *input, const mlel_tensor *output, const mlel_tensor *multiplier,
                       const mlel_tensor *shift, int32_t input_zp, int32_t output_zp, int scale32, int double_round,
                       int per_channel, void *cuda_stream);
+
+/* The other operators of the path, one entry per reference shader (avgpool2d.comp, maxpool2d.comp, table.comp,
+ * transpose.comp, concat.comp, clamp.comp, elementwise_binary.comp, reduce.comp), with the argument meaning of
+ * the matching GraphPipeline::make<Op> (graph/compute_graph_op.hpp:1249-1483).  Each takes the kernel a graph
+ * would take for the same tensors.  `op_name` of mlel_cuda_binary / mlel_cuda_reduce is the TOSA name
+ * ("ADD", "MAXIMUM", ... / "REDUCE_SUM", "REDUCE_MAX", ...).  mlel_cuda_concat runs one pass per input, as the
+ * reference does. */
+int mlel_cuda_avg_pool2d(const mlel_tensor *input, const mlel_tensor *output, const int32_t kernel[2], const int32_t stride[2],
+                         const int32_t pad[4], int32_t input_zp, int32_t output_zp, void *cuda_stream);
+int mlel_cuda_max_pool2d(const mlel_tensor *input, const mlel_tensor *output, const int32_t kernel[2], const int32_t stride[2],
+                         const int32_t pad[4], void *cuda_stream);
+int mlel_cuda_table(const mlel_tensor *input, const mlel_tensor *table, const mlel_tensor *output, void *cuda_stream);
+int mlel_cuda_transpose(const mlel_tensor *input, const mlel_tensor *output, const uint32_t *perms, uint32_t rank,
+                        void *cuda_stream);
+int mlel_cuda_concat(const mlel_tensor *const *inputs, uint32_t input_count, const mlel_tensor *output, uint32_t axis,
+                     void *cuda_stream);
+int mlel_cuda_clamp(const mlel_tensor *input, const mlel_tensor *output, double min_value, double max_value,
+                    void *cuda_stream);
+int mlel_cuda_binary(const char *op_name, const mlel_tensor *input1, const mlel_tensor *input2, const mlel_tensor *output,
+                     void *cuda_stream);
+int mlel_cuda_reduce(const char *op_name, const mlel_tensor *input, const mlel_tensor *output, uint32_t axis,
+                     void *cuda_stream);
 
 /* Fused int8 contraction + RESCALE (+ CLAMP): what the fusion pass substitutes for
  * MATMUL -> RESCALE [-> CLAMP] (matmul.comp + rescale.comp + clamp.comp in one kernel).

@@ -31,6 +31,10 @@ def test_registry(mlel):
         assert op in names and mlel.tosa_op_supported(op)
     assert all(mlel.tosa_op_supported(op) for op in names)
     assert not mlel.tosa_op_supported("NOT_A_TOSA_OPERATOR")
+    lib = mlel.lib()
+    assert lib.mlel_tosa_lookup(b"TOSA.001000.1", b"CONV2D") == names.index("CONV2D")
+    assert lib.mlel_tosa_lookup(b"TOSA.000080.2", b"CONV2D") == -1
+    assert lib.mlel_tosa_lookup(b"TOSA.001000.1", b"NOT_A_TOSA_OPERATOR") == -1
 
 
 def test_errors_are_status_codes_not_exceptions(mlel):

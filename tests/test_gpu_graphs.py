@@ -418,6 +418,83 @@ def test_direct_convolution_entry_points(mlel):
     np.testing.assert_array_equal(outd.cpu().numpy(), wantd)
 
 
+def test_direct_entry_points_of_the_other_operators(mlel):
+    """Pools, TABLE, TRANSPOSE, CONCAT, CLAMP, an elementwise binary operator and a reduction called directly, each
+    against the oracle."""
+    import torch
+    from oracle import oracle
+    r = np.random.Generator(np.random.PCG64(12))
+    T = mlel.device_tensor
+    lib = mlel.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    keep = []
+
+    def dev(a):
+        t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        keep.append(t)
+        return ctypes.byref(T(t.data_ptr(), mlel.NP_TO_DTYPE[np.dtype(a.dtype)], a.shape)), t
+
+    def out_like(a):
+        return dev(np.zeros(a.shape, a.dtype))
+
+    x = r.integers(-128, 128, (2, 12, 12, 32), dtype=np.int8)
+    tx, _ = dev(x)
+    i2, i4 = ctypes.c_int32 * 2, ctypes.c_int32 * 4
+    want = oracle.avg_pool2d(x, [3, 3], [2, 2], [1, 1, 1, 1], -4, 7)
+    to, o = out_like(want)
+    mlel.check(lib.mlel_cuda_avg_pool2d(tx, to, i2(3, 3), i2(2, 2), i4(1, 1, 1, 1), -4, 7, stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o.cpu().numpy(), want)
+    want = oracle.max_pool2d(x, [3, 3], [2, 2], [1, 1, 1, 1])
+    to, o = out_like(want)
+    mlel.check(lib.mlel_cuda_max_pool2d(tx, to, i2(3, 3), i2(2, 2), i4(1, 1, 1, 1), stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o.cpu().numpy(), want)
+    table = r.integers(-128, 128, (256,), dtype=np.int8)
+    tt, _ = dev(table)
+    want = oracle.table(x, table)
+    to, o = out_like(want)
+    mlel.check(lib.mlel_cuda_table(tx, tt, to, stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o.cpu().numpy(), want)
+    want = oracle.transpose(x, (0, 2, 3, 1))
+    to, o = out_like(want)
+    mlel.check(lib.mlel_cuda_transpose(tx, to, (ctypes.c_uint32 * 4)(0, 2, 3, 1), 4, stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o.cpu().numpy(), want)
+    y = r.integers(-128, 128, (2, 12, 12, 16), dtype=np.int8)
+    ty, _ = dev(y)
+    want = oracle.concat([x, y, x], 3)
+    to, o = out_like(want)
+    ins = (ctypes.POINTER(mlel.Tensor) * 3)(ctypes.cast(tx, ctypes.POINTER(mlel.Tensor)),
+                                            ctypes.cast(ty, ctypes.POINTER(mlel.Tensor)),
+                                            ctypes.cast(tx, ctypes.POINTER(mlel.Tensor)))
+    mlel.check(lib.mlel_cuda_concat(ins, 3, to, 3, stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o.cpu().numpy(), want)
+    want = oracle.clamp(x, -20, 99)
+    to, o = out_like(want)
+    mlel.check(lib.mlel_cuda_clamp(tx, to, ctypes.c_double(-20), ctypes.c_double(99), stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o.cpu().numpy(), want)
+    a32 = r.integers(-2**30, 2**30, (3, 40, 64), dtype=np.int32)
+    b32 = r.integers(-2**30, 2**30, (3, 40, 64), dtype=np.int32)
+    ta, _ = dev(a32)
+    tb, _ = dev(b32)
+    want = oracle.binary("SUB", a32, b32, np.dtype(np.int32))
+    to, o = out_like(want)
+    mlel.check(lib.mlel_cuda_binary(b"SUB", ta, tb, to, stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o.cpu().numpy(), want)
+    want = oracle.reduce("REDUCE_SUM", a32, 2)
+    to, o = out_like(want)
+    mlel.check(lib.mlel_cuda_reduce(b"REDUCE_SUM", ta, to, 2, stream))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(o.cpu().numpy(), want)
+    with pytest.raises(mlel.MlelError):
+        mlel.check(lib.mlel_cuda_binary(b"NO_SUCH_OPERATOR", ta, tb, to, stream))
+
+
 def test_replicated_pattern_constant_values(mlel):
     """{1, 2} replicated over four elements reaches the kernels as {1, 2, 1, 2}
     (tests/graph/graph_ext_inst_context_tests.cpp:16-20), checked through x + k with x = 0."""
@@ -459,6 +536,19 @@ def test_graph_replay_follows_rebinding(mlel):
         torch.cuda.synchronize()
         got = dev_out[o].cpu().numpy().view(v_out.dtype).reshape(v_out.shape)
         np.testing.assert_array_equal(got, want[i])
+
+
+def test_a_bounded_wait_that_runs_out_is_reported(mlel):
+    """The give-up path of the kernels' bounded waits: a one-thread kernel waits about a millisecond on a barrier that
+    nobody arrives at; the wait records its code, the kernel returns, the context stays usable."""
+    import torch
+    lib = mlel.lib()
+    code = ctypes.c_int(-1)
+    mlel.check(lib.mlel_selftest_wait_timeout(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ctypes.byref(code)))
+    assert code.value == 99
+    assert lib.mlel_device_error() == 0  # the self-test clears its own code
+    x = torch.arange(8, device="cuda")
+    assert int(x.sum().item()) == 28     # the context still answers
 
 
 def test_int8_mma_peak_loop(mlel):
