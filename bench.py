@@ -220,49 +220,75 @@ def _time_dispatches(runner, stream, min_seconds=0.25, iters=20):
     return float(np.median(times))
 
 
-def measure_extras(mlel, stream, peaks, int8_peak_tops):
+def measure_extras(mlel, stream, peaks, int8_peak_tops, only=None):
+    """`only` = "cfg1" | "cfg2" | "cfg4" | "ops" restricts the measurement to one part (for a profiler capture)."""
     import torch
-    from mlel_b200.graph_builder import GraphBuilder
-    from mlel_b200.model_graphs import bert_graph, macs_of, matmul_rescale_graph, mobilenet_v2_graph
-    from mlel_b200.runtime import GraphRunner
     out = {}
     hbm = peaks["hbm_gbs"]
 
+    want = lambda part: only is None or only == part
+
     # configuration 1: [16,1024,1024]^2 MATMUL + per-tensor RESCALE, two run-time inputs
+    if want("cfg1"):
+        out["cfg1_matmul_rescale"] = _measure_cfg1(stream, hbm, int8_peak_tops)
+    if want("cfg2"):
+        out["cfg2_mobilenet_v2"] = _measure_cfg2(stream)
+    if want("cfg4"):
+        out["cfg4_bert_base"] = _measure_cfg4(stream)
+    torch.cuda.empty_cache()
+    if want("ops"):
+        out["memory_bound_ops"] = _measure_memory_bound_ops(stream, peaks)
+    torch.cuda.empty_cache()
+    return out
+
+
+def _measure_cfg1(stream, hbm, int8_peak_tops):
+    from mlel_b200.model_graphs import matmul_rescale_graph
+    from mlel_b200.runtime import GraphRunner
     g, inputs = matmul_rescale_graph(seed=0)
     r = GraphRunner(g)
     r.set_inputs(inputs)
     ms = _time_dispatches(r, stream)
     ops = 2.0 * 16 * 1024 ** 3
     nbytes = 3 * 16 * 1024 * 1024
-    out["cfg1_matmul_rescale"] = {
+    return {
         "workload": "BASELINE configs[1]: A,B [16,1024,1024] int8 (A_zp -7), RESCALE shift 38 -> int8; both inputs run-time",
         "ms": ms, "tops": ops / ms / 1e9, "frac_of_int8_peak": ops / ms / 1e9 / int8_peak_tops,
         "gbs": nbytes / ms / 1e6, "frac_of_hbm": nbytes / ms / 1e6 / hbm,
         "kernels": r.pipeline.exec_names(), "timing": "CUDA-graph replays back to back, inputs (32 MiB) resident"}
-    del r
 
-    # configuration 2: MobileNetV2-shaped graph, 32 images
+
+def _measure_cfg2(stream):
+    """Configuration 2: MobileNetV2-shaped graph, 32 images."""
+    from mlel_b200.model_graphs import macs_of, mobilenet_v2_graph
+    from mlel_b200.runtime import GraphRunner
     g, inputs = mobilenet_v2_graph(seed=0, n=32)
     r = GraphRunner(g)
     r.set_inputs(inputs)
     ms = _time_dispatches(r, stream)
-    out["cfg2_mobilenet_v2"] = {"workload": "BASELINE configs[2]: MobileNetV2-shaped int8 graph, 32 images, 224x224x3",
-                                "ms_per_dispatch": ms, "images_per_s": 32 / ms * 1e3,
-                                "gmac_per_image": macs_of(g) / 32 / 1e9, "kernels_per_dispatch": len(r.pipeline.exec_names())}
-    del r
+    return {"workload": "BASELINE configs[2]: MobileNetV2-shaped int8 graph, 32 images, 224x224x3",
+            "ms_per_dispatch": ms, "images_per_s": 32 / ms * 1e3,
+            "gmac_per_image": macs_of(g) / 32 / 1e9, "kernels_per_dispatch": len(r.pipeline.exec_names())}
 
-    # configuration 4: BERT-base-shaped encoder, 12 layers, 32 sequences of 384 tokens
+
+def _measure_cfg4(stream):
+    """Configuration 4: BERT-base-shaped encoder, 12 layers, 32 sequences of 384 tokens."""
+    from mlel_b200.model_graphs import bert_graph, macs_of
+    from mlel_b200.runtime import GraphRunner
     g, inputs = bert_graph(seed=0, n=32)
     r = GraphRunner(g)
     r.set_inputs(inputs)
     ms = _time_dispatches(r, stream, iters=5)
-    out["cfg4_bert_base"] = {"workload": "BASELINE configs[4]: BERT-base-shaped int8 encoder, 12 layers, 32 x 384 tokens",
-                             "ms_per_dispatch": ms, "sequences_per_s": 32 / ms * 1e3,
-                             "tops": 2.0 * macs_of(g) / ms / 1e9, "kernels_per_dispatch": len(r.pipeline.exec_names())}
-    del r
-    torch.cuda.empty_cache()
+    return {"workload": "BASELINE configs[4]: BERT-base-shaped int8 encoder, 12 layers, 32 x 384 tokens",
+            "ms_per_dispatch": ms, "sequences_per_s": 32 / ms * 1e3,
+            "tops": 2.0 * macs_of(g) / ms / 1e9, "kernels_per_dispatch": len(r.pipeline.exec_names())}
 
+
+def _measure_memory_bound_ops(stream, peaks):
+    import torch
+    from mlel_b200.graph_builder import GraphBuilder
+    from mlel_b200.runtime import GraphRunner
+    hbm = peaks["hbm_gbs"]
     # memory-bound operators: one-operator graphs on tensors larger than L2, the operator's kernel timed alone with
     # the session's per-kernel events (minimum of five); GB/s = algorithmic bytes (inputs read once, outputs
     # written once) / time
@@ -321,9 +347,7 @@ def measure_extras(mlel, stream, peaks, int8_peak_tops):
     mult = rng.integers(1 << 30, 1 << 31, (96,), dtype=np.int64).astype(np.int32)
     g.output(g.rescale(y, mult, np.full(96, 36, np.int8), 0, 0, np.int8, True, True, True))
     run("DEPTHWISE_CONV2D 3x3 + RESCALE", g, [xd], int(np.prod(D)) * 2, flags=0)
-    out["memory_bound_ops"] = {"peak_gbs": hbm, "peak_source": peaks["source"] + " copy bandwidth", "ops": ops_out}
-    torch.cuda.empty_cache()
-    return out
+    return {"peak_gbs": hbm, "peak_source": peaks["source"] + " copy bandwidth", "ops": ops_out}
 
 
 def measure_oc_sharded_matmul(mlel, device, stream, rank, world):
@@ -401,9 +425,21 @@ def main():
     ap.add_argument("--no-graph", action="store_true",
                     help="enqueue every kernel of every step instead of replaying one captured CUDA graph per bound buffer")
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the operator figures")
+    ap.add_argument("--only", choices=["cfg1", "cfg2", "cfg4", "ops"],
+                    help="run one of the side measurements alone and print it (a small case for a profiler capture); "
+                         "not a benchmark line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.only:
+        import torch
+        from __graft_entry__ import load_package
+        mlel = load_package()
+        mlel.lib()
+        torch.cuda.set_device(0)
+        peaks = load_peaks()
+        print(json.dumps(measure_extras(mlel, torch.cuda.current_stream(), peaks, float("nan"), only=args.only)))
         return
 
     import torch
