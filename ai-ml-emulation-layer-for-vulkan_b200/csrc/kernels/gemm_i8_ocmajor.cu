@@ -67,7 +67,6 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     static_assert(NSTAGE <= 6, "OcBarriers holds six stages");
     constexpr int kOcTmaWarp = EW, kOcMmaWarp = EW + 1, kOcGatherWarp0 = EW + 2;
     constexpr uint32_t kTmemCols = 2 * BNP <= 256 ? 256u : 512u; // two accumulators; allocations are powers of two
-    constexpr int kXBoxRows = BNP % 128 == 0 ? 128 : 64;         // rows of one tiled load of the pixel operand
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int numKb = X_MODE == kXIm2col ? p.KH * p.KW * p.kbPerTap : (p.K + BK - 1) / BK;
@@ -122,7 +121,10 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     if (warp == kOcTmaWarp) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t it = 0, tileCount = 0;
+            uint32_t tileCount = 0;
+            uint32_t ready = 0; // 1: the stage of the coming K block is known to be empty (see tmaStagePeekTiled)
+            int s = 0;
+            uint32_t phase = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileCount) {
                 const OcTile tc = tileOf(t);
@@ -135,29 +137,25 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                     h0 = oy * p.strideY - p.padTop;
                     w0 = (rem - oy * p.OW) * p.strideX - p.padLeft;
                 }
-                for (int kb = 0; kb < numKb; ++kb, ++it) {
-                    const int s = int(it % NSTAGE);
-                    const uint32_t phase = (it / NSTAGE) & 1u;
-                    ok = mbarWait(&bars->empty[s], phase ^ 1u, 11);
-                    if (!ok) {
-                        break;
-                    }
-                    mbarArriveExpectTx(&bars->full[s], uint32_t(kTileW + (X_TMA ? kTileX : 0)));
-                    if (X_MODE == kXIm2col) {
-                        tmaLoad3d(&tmapW, tilesW + s * kTileW, &bars->full[s], cb, ky * p.KW + kx, tc.c0);
-                    } else {
-                        tmaLoad3d(&tmapW, tilesW + s * kTileW, &bars->full[s], kb * BK, tc.c0, 0);
-                    }
-                    if (X_MODE == kXTiled) {
-                        // one copy per kXBoxRows pixels (the map's box)
-#pragma unroll
-                        for (int h = 0; h < BNP / kXBoxRows; ++h) {
-                            tmaLoad3d(&tmapX, tilesX + s * kTileX + h * kXBoxRows * BK, &bars->full[s], kb * BK,
-                                      tc.m0 + h * kXBoxRows, tc.batch);
+                for (int kb = 0; kb < numKb; ++kb) {
+                    if (ready == 0) {
+                        ok = mbarWait(&bars->empty[s], phase ^ 1u, 11);
+                        if (!ok) {
+                            break;
                         }
+                    }
+                    // the ring runs on across tiles: the next K block's stage follows this one whatever tile it is in
+                    const int sNext = s + 1 == NSTAGE ? 0 : s + 1;
+                    const uint32_t phaseNext = sNext == 0 ? phase ^ 1u : phase;
+                    if (X_MODE == kXTiled) {
+                        ready = tmaStagePeekTiled(&bars->full[s], uint32_t(kTileW + kTileX), &tmapW, tilesW + s * kTileW, kb * BK,
+                                                  tc.c0, 0, &tmapX, tilesX + s * kTileX, kb * BK, tc.m0, tc.batch,
+                                                  &bars->empty[sNext], phaseNext ^ 1u);
                     } else if (X_MODE == kXIm2col) {
-                        tmaLoadIm2col4d(&tmapX, tilesX + s * kTileX, &bars->full[s], cb, w0, h0, n0, uint16_t(kx * p.dilX),
-                                        uint16_t(ky * p.dilY));
+                        ready = tmaStagePeekIm2col(&bars->full[s], uint32_t(kTileW + kTileX), &tmapW, tilesW + s * kTileW, cb,
+                                                   ky * p.KW + kx, tc.c0, &tmapX, tilesX + s * kTileX, cb, w0, h0, n0,
+                                                   uint16_t(kx * p.dilX), uint16_t(ky * p.dilY), &bars->empty[sNext],
+                                                   phaseNext ^ 1u);
                         cb += BK;
                         if (cb >= p.IC) {
                             cb = 0;
@@ -166,7 +164,12 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                                 ++ky;
                             }
                         }
+                    } else {
+                        mbarArriveExpectTx(&bars->full[s], uint32_t(kTileW));
+                        tmaLoad3d(&tmapW, tilesW + s * kTileW, &bars->full[s], kb * BK, tc.c0, 0);
                     }
+                    s = sNext;
+                    phase = phaseNext;
                 }
                 if (RESIDUAL && ok) {
                     // the tile's shortcut bytes, once the store that last used this C/D tile has read it
@@ -183,7 +186,12 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = instrDesc(BNP, false);
+            static_assert(BK / UMMA_K == 4, "ummaBlockPeek issues the four MMAs of a K block");
+            const uint64_t descW0 = smemDesc(smemAddr(tilesW), 16, 1024), descX0 = smemDesc(smemAddr(tilesX), 16, 1024);
             uint32_t it = 0, tileCount = 0;
+            uint32_t ready = 0; // 1: the stage of the coming K block is known to be full (see ummaBlockPeek)
+            int s = 0;
+            uint32_t phase = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileCount) {
                 const uint32_t buf = tileCount & 1u;
@@ -193,22 +201,28 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmemD = tmemBase + buf * uint32_t(BNP);
+                int kLeft = X_MODE == kXIm2col ? p.IC : p.K;
                 for (int kb = 0; kb < numKb; ++kb, ++it) {
-                    const int s = int(it % NSTAGE);
-                    const uint32_t phase = (it / NSTAGE) & 1u;
-                    ok = mbarWait(&bars->full[s], phase, 12);
-                    if (!ok) {
-                        break;
+                    if (ready == 0) {
+                        ok = mbarWait(&bars->full[s], phase, 12);
+                        if (!ok) {
+                            break;
+                        }
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t wAddr = smemAddr(tilesW + s * kTileW);
-                    const uint32_t xAddr = smemAddr(tilesX + s * kTileX);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        umma(tmemD, smemDesc(wAddr + k * UMMA_K, 16, 1024), smemDesc(xAddr + k * UMMA_K, 16, 1024), idesc,
-                             (kb | k) != 0 ? 1u : 0u);
+                    // the ring runs on across tiles: the next K block's stage follows this one whatever tile it is in
+                    const int sNext = s + 1 == NSTAGE ? 0 : s + 1;
+                    const uint32_t phaseNext = sNext == 0 ? phase ^ 1u : phase;
+                    ready = ummaBlockPeek(tmemD, descW0 + uint64_t(uint32_t(s) * uint32_t(kTileW >> 4)), 2,
+                                          descX0 + uint64_t(uint32_t(s) * uint32_t(kTileX >> 4)), 2, idesc, kb != 0 ? 1u : 0u,
+                                          ummaCountFor(kLeft), &bars->empty[s], &bars->full[sNext], phaseNext);
+                    // bytes of K in the next block: the rest of the tap's channels (im2col) or of the whole K axis
+                    kLeft -= BK;
+                    if (kLeft <= 0) {
+                        kLeft = X_MODE == kXIm2col ? p.IC : 0;
                     }
-                    ummaCommit(&bars->empty[s]);
+                    s = sNext;
+                    phase = phaseNext;
                 }
                 if (ok) {
                     ummaCommit(&bars->accFull[buf]);
@@ -357,8 +371,9 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
     const uint32_t boxPixels = uint32_t(width);
     int xMode = kXGather;
     if (q.aMatrix != nullptr) {
+        // one box = the whole pixel tile of one K block
         if (!makeMap(&maps.x, q.aMatrix, uint64_t(p.K), uint64_t(p.M), uint64_t(q.batches), uint64_t(q.aRowBytes),
-                     uint64_t(q.aBatchBytes), BK, width % 128 == 0 ? 128 : 64)) {
+                     uint64_t(q.aBatchBytes), BK, uint32_t(width))) {
             return MLEL_ERROR_DEVICE;
         }
         xMode = kXTiled;

@@ -499,7 +499,9 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     if (warp == kTmaWarp) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t it = 0; // K blocks issued so far: the ring runs on across tiles
+            uint32_t ready = 0; // 1: the stage of the coming K block is known to be empty (see tmaStagePeekTiled)
+            int s = 0;          // the ring runs on across tiles
+            uint32_t phase = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
                 const TileCoord tc = tileOf(t);
@@ -512,21 +514,20 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                     h0 = oy * p.strideY - p.padTop;
                     w0 = (rem - oy * p.OW) * p.strideX - p.padLeft;
                 }
-                for (int kb = 0; kb < numKb; ++kb, ++it) {
-                    const int s = int(it % NSTAGE);
-                    const uint32_t phase = (it / NSTAGE) & 1u;
-                    ok = mbarWait(&bars->empty[s], phase ^ 1u, 1);
-                    if (!ok) {
-                        break;
+                for (int kb = 0; kb < numKb; ++kb) {
+                    if (ready == 0) {
+                        ok = mbarWait(&bars->empty[s], phase ^ 1u, 1);
+                        if (!ok) {
+                            break;
+                        }
                     }
-                    mbarArriveExpectTx(&bars->full[s], uint32_t((A_TMA ? kTileA : 0) + kTileB));
-                    if (A_MODE == kATiled) {
-                        tmaLoad3d(&tmapA, tilesA + s * kTileA, &bars->full[s], kb * BK, tc.m0, tc.batch);
-                    }
+                    const int sNext = s + 1 == NSTAGE ? 0 : s + 1;
+                    const uint32_t phaseNext = sNext == 0 ? phase ^ 1u : phase;
+                    uint8_t *dstA = tilesA + s * kTileA, *dstB = tilesB + s * kTileB;
                     if (A_MODE == kAIm2col) {
-                        tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], cb, ky * p.KW + kx, tc.n0);
-                        tmaLoadIm2col4d(&tmapA, tilesA + s * kTileA, &bars->full[s], cb, w0, h0, n0, uint16_t(kx * p.dilX),
-                                        uint16_t(ky * p.dilY));
+                        ready = tmaStagePeekIm2col(&bars->full[s], uint32_t(kTileA + kTileB), &tmapB, dstB, cb, ky * p.KW + kx,
+                                                   tc.n0, &tmapA, dstA, cb, w0, h0, n0, uint16_t(kx * p.dilX),
+                                                   uint16_t(ky * p.dilY), &bars->empty[sNext], phaseNext ^ 1u);
                         cb += BK;
                         if (cb >= p.IC) {
                             cb = 0;
@@ -535,11 +536,27 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                                 ++ky;
                             }
                         }
-                    } else if (B_MN) {
-                        tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], tc.n0, kb * BK, tc.batch);
+                    } else if (A_MODE == kATiled) {
+                        if (B_MN) {
+                            ready = tmaStagePeekTiled(&bars->full[s], uint32_t(kTileA + kTileB), &tmapB, dstB, tc.n0, kb * BK,
+                                                      tc.batch, &tmapA, dstA, kb * BK, tc.m0, tc.batch, &bars->empty[sNext],
+                                                      phaseNext ^ 1u);
+                        } else {
+                            ready = tmaStagePeekTiled(&bars->full[s], uint32_t(kTileA + kTileB), &tmapB, dstB, kb * BK, tc.n0,
+                                                      p.batchedB ? tc.batch : 0, &tmapA, dstA, kb * BK, tc.m0, tc.batch,
+                                                      &bars->empty[sNext], phaseNext ^ 1u);
+                        }
                     } else {
-                        tmaLoad3d(&tmapB, tilesB + s * kTileB, &bars->full[s], kb * BK, tc.n0, p.batchedB ? tc.batch : 0);
+                        // gathered pixel operand: only the weight tile comes by TMA
+                        mbarArriveExpectTx(&bars->full[s], uint32_t(kTileB));
+                        if (B_MN) {
+                            tmaLoad3d(&tmapB, dstB, &bars->full[s], tc.n0, kb * BK, tc.batch);
+                        } else {
+                            tmaLoad3d(&tmapB, dstB, &bars->full[s], kb * BK, tc.n0, p.batchedB ? tc.batch : 0);
+                        }
                     }
+                    s = sNext;
+                    phase = phaseNext;
                 }
             }
         }
@@ -547,7 +564,15 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = instrDesc(BN, B_MN);
-            uint32_t it = 0, tileCount = 0;
+            static_assert(BK / UMMA_K == 4, "ummaBlockPeek issues the four MMAs of a K block");
+            // K-major: step 32 bytes inside the 128-byte swizzle row; MN-major: step 32 K-rows of 128 bytes
+            const uint64_t descA0 = smemDesc(smemAddr(tilesA), 16, 1024);
+            const uint64_t descB0 = B_MN ? smemDesc(smemAddr(tilesB), BK * 128, 1024) : smemDesc(smemAddr(tilesB), 16, 1024);
+            constexpr uint64_t kStepB = B_MN ? uint64_t(UMMA_K * 128) >> 4 : 2;
+            uint32_t tileCount = 0;
+            uint32_t ready = 0; // 1: the stage of the coming K block is known to be full (see ummaBlockPeek)
+            int s = 0;
+            uint32_t phase = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++tileCount) {
                 const uint32_t buf = tileCount & 1u;
@@ -558,25 +583,27 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmemD = tmemBase + buf * uint32_t(BN);
-                for (int kb = 0; kb < numKb; ++kb, ++it) {
-                    const int s = int(it % NSTAGE);
-                    const uint32_t phase = (it / NSTAGE) & 1u;
-                    ok = mbarWait(&bars->full[s], phase, 2);
-                    if (!ok) {
-                        break;
+                int kLeft = A_MODE == kAIm2col ? p.IC : p.K; // bytes of K in the coming block's tap or K axis
+                for (int kb = 0; kb < numKb; ++kb) {
+                    if (ready == 0) {
+                        ok = mbarWait(&bars->full[s], phase, 2);
+                        if (!ok) {
+                            break;
+                        }
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t aAddr = smemAddr(tilesA + s * kTileA);
-                    const uint32_t bAddr = smemAddr(tilesB + s * kTileB);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // K-major: step 32 bytes inside the 128-byte swizzle row; MN-major: step 32 K-rows of 128 bytes
-                        const uint64_t da = smemDesc(aAddr + k * UMMA_K, 16, 1024);
-                        const uint64_t db = B_MN ? smemDesc(bAddr + k * UMMA_K * 128, BK * 128, 1024)
-                                                 : smemDesc(bAddr + k * UMMA_K, 16, 1024);
-                        umma(tmemD, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    // the ring runs on across tiles: the next K block's stage follows this one whatever tile it is in
+                    const int sNext = s + 1 == NSTAGE ? 0 : s + 1;
+                    const uint32_t phaseNext = sNext == 0 ? phase ^ 1u : phase;
+                    ready = ummaBlockPeek(tmemD, descA0 + uint64_t(uint32_t(s) * uint32_t(kTileA >> 4)), 2,
+                                          descB0 + uint64_t(uint32_t(s) * uint32_t(kTileB >> 4)), kStepB, idesc,
+                                          kb != 0 ? 1u : 0u, ummaCountFor(kLeft), &bars->empty[s], &bars->full[sNext], phaseNext);
+                    kLeft -= BK;
+                    if (kLeft <= 0) {
+                        kLeft = A_MODE == kAIm2col ? p.IC : 0;
                     }
-                    ummaCommit(&bars->empty[s]); // frees the stage once these MMAs have read it
+                    s = sNext;
+                    phase = phaseNext;
                 }
                 if (ok) {
                     ummaCommit(&bars->accFull[buf]);

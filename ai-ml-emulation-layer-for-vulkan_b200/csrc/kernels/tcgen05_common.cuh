@@ -122,6 +122,48 @@ __device__ __forceinline__ void tmaLoadIm2col4d(const CUtensorMap *map, void *ds
                  : "memory");
 }
 
+// The producer's side of ummaBlockPeek: the loads of one stage -- expected byte count, weight tile, pixel tile --
+// with a non-blocking test of the NEXT stage's `empty` barrier issued ahead of them, so that its answer arrives
+// while the loads go out instead of stalling the thread between two stages.  Returns 1 when that barrier's phase
+// `peekParity` is complete; 0 means "not yet known".
+__device__ __forceinline__ uint32_t tmaStagePeekTiled(uint64_t *fullBar, uint32_t bytes, const CUtensorMap *mapW, void *dstW,
+                                                      int w0, int w1, int w2, const CUtensorMap *mapX, void *dstX, int x0,
+                                                      int x1, int x2, uint64_t *peekBar, uint32_t peekParity) {
+    uint32_t ready;
+    asm volatile("{\n\t.reg .pred q;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+                 "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %4;\n\t"
+                 "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%5], [%6, {%7, %8, %9}], [%3];\n\t"
+                 "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%10], [%11, {%12, %13, %14}], [%3];\n\t"
+                 "selp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(ready)
+                 : "r"(smemAddr(peekBar)), "r"(peekParity), "r"(smemAddr(fullBar)), "r"(bytes), "r"(smemAddr(dstW)),
+                   "l"(reinterpret_cast<uint64_t>(mapW)), "r"(w0), "r"(w1), "r"(w2), "r"(smemAddr(dstX)),
+                   "l"(reinterpret_cast<uint64_t>(mapX)), "r"(x0), "r"(x1), "r"(x2)
+                 : "memory");
+    return ready;
+}
+// The same with the pixel tile fetched in im2col mode (see tmaLoadIm2col4d).
+__device__ __forceinline__ uint32_t tmaStagePeekIm2col(uint64_t *fullBar, uint32_t bytes, const CUtensorMap *mapW, void *dstW,
+                                                       int w0, int w1, int w2, const CUtensorMap *mapX, void *dstX, int c,
+                                                       int w, int h, int n, uint16_t offW, uint16_t offH, uint64_t *peekBar,
+                                                       uint32_t peekParity) {
+    uint32_t ready;
+    asm volatile("{\n\t.reg .pred q;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+                 "mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %4;\n\t"
+                 "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%5], [%6, {%7, %8, %9}], [%3];\n\t"
+                 "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+                 "[%10], [%11, {%12, %13, %14, %15}], [%3], {%16, %17};\n\t"
+                 "selp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(ready)
+                 : "r"(smemAddr(peekBar)), "r"(peekParity), "r"(smemAddr(fullBar)), "r"(bytes), "r"(smemAddr(dstW)),
+                   "l"(reinterpret_cast<uint64_t>(mapW)), "r"(w0), "r"(w1), "r"(w2), "r"(smemAddr(dstX)),
+                   "l"(reinterpret_cast<uint64_t>(mapX)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(offW), "h"(offH)
+                 : "memory");
+    return ready;
+}
+
 // Shared-memory matrix descriptor for a SWIZZLE_128B tile whose 8-row groups are 1024 bytes apart.
 // bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
 // [46,48) descriptor version (1 on sm_100), [61,64) layout type (2 = 128-byte swizzle).
@@ -153,6 +195,41 @@ __device__ __forceinline__ void ummaCommit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar))
                  : "memory");
 }
+// One 128-byte K block: up to four MMAs of 32 bytes of K each (`count` of them: the tail of a K block that only
+// holds zero fill is skipped; descriptors advance by stepA / stepB units of 16 bytes, 2 for a K-major SWIZZLE_128B
+// tile), the commit that hands the stage back, and -- issued AHEAD of them -- a non-blocking test of the barrier the
+// next K block will wait for.  Why in one statement: an mbarrier test issued after MMAs and a commit takes about 185
+// cycles to answer even when the phase has long completed (it queues behind them), and the thread that needs the
+// answer stalls for it; measured on a loop of this shape, 626 cycles per K block whatever N is, against 384 for the
+// four MMAs of N = 192 alone.  Asked before the MMAs are issued, the answer arrives while they and the commit go out
+// (463 cycles per K block; 513 = the pipe's own time at N = 256).  Returns 1 when the next barrier's phase
+// `peekParity` is complete; 0 means "not yet known": wait for it in the ordinary way.
+__device__ __forceinline__ uint32_t ummaBlockPeek(uint32_t tmemD, uint64_t descA, uint64_t stepA, uint64_t descB,
+                                                  uint64_t stepB, uint32_t idesc, uint32_t accumulateFirst, int count,
+                                                  uint64_t *commitBar, uint64_t *peekBar, uint32_t peekParity) {
+    uint32_t ready;
+    asm volatile("{\n\t.reg .pred q, a0, a1, g1, g2, g3;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+                 "setp.ne.b32 a0, %9, 0;\n\t"
+                 "setp.ne.b32 a1, %10, 0;\n\t"
+                 "setp.gt.s32 g1, %17, 1;\n\t"
+                 "setp.gt.s32 g2, %17, 2;\n\t"
+                 "setp.gt.s32 g3, %17, 3;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%3], %4, %5, %8, {%11, %11, %11, %11}, a0;\n\t"
+                 "@g1 tcgen05.mma.cta_group::1.kind::i8 [%3], %6, %7, %8, {%11, %11, %11, %11}, a1;\n\t"
+                 "@g2 tcgen05.mma.cta_group::1.kind::i8 [%3], %12, %13, %8, {%11, %11, %11, %11}, a1;\n\t"
+                 "@g3 tcgen05.mma.cta_group::1.kind::i8 [%3], %14, %15, %8, {%11, %11, %11, %11}, a1;\n\t"
+                 "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%16];\n\t"
+                 "selp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(ready)
+                 : "r"(smemAddr(peekBar)), "r"(peekParity), "r"(tmemD), "l"(descA), "l"(descB), "l"(descA + stepA),
+                   "l"(descB + stepB), "r"(idesc), "r"(accumulateFirst), "r"(1u), "r"(0u), "l"(descA + 2 * stepA),
+                   "l"(descB + 2 * stepB), "l"(descA + 3 * stepA), "l"(descB + 3 * stepB), "r"(smemAddr(commitBar)), "r"(count)
+                 : "memory");
+    return ready;
+}
+// How many of a K block's four MMAs have anything but zero fill to multiply: `valid` = bytes of K in the block.
+__device__ __forceinline__ int ummaCountFor(int valid) { return valid >= BK ? BK / UMMA_K : (valid + UMMA_K - 1) / UMMA_K; }
 __device__ __forceinline__ void tmemLoad16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"

@@ -199,7 +199,10 @@ def run_reference_arm(args):
 
 # ---- the other BASELINE configurations and the memory-bound operators, each timed alone (one GPU) -----------------
 
-def _time_dispatches(runner, stream, min_seconds=0.25, iters=20):
+SIDE_MIN_SECONDS = 0.25  # timed device time per side measurement; --only shortens it for profiler captures
+
+
+def _time_dispatches(runner, stream, min_seconds=None, iters=20):
     """Median milliseconds per dispatch over windows of `iters` replays of the session's captured graph."""
     import torch
     s = stream.cuda_stream
@@ -207,6 +210,7 @@ def _time_dispatches(runner, stream, min_seconds=0.25, iters=20):
         runner.session.dispatch_graph(s)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    min_seconds = SIDE_MIN_SECONDS if min_seconds is None else min_seconds
     times, total = [], 0.0
     while total < min_seconds * 1e3 and len(times) < 200:
         e0.record(stream)
@@ -425,6 +429,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true",
                     help="enqueue every kernel of every step instead of replaying one captured CUDA graph per bound buffer")
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the operator figures")
+    ap.add_argument("--windows", type=int, default=0,
+                    help="time exactly this many windows of --steps steps instead of as many as fill a second "
+                         "(for a run under a profiler; the default is what a benchmark line needs)")
     ap.add_argument("--only", choices=["cfg1", "cfg2", "cfg4", "ops"],
                     help="run one of the side measurements alone and print it (a small case for a profiler capture); "
                          "not a benchmark line")
@@ -439,6 +446,8 @@ def main():
         mlel.lib()
         torch.cuda.set_device(0)
         peaks = load_peaks()
+        global SIDE_MIN_SECONDS
+        SIDE_MIN_SECONDS = 0.01
         print(json.dumps(measure_extras(mlel, torch.cuda.current_stream(), peaks, float("nan"), only=args.only)))
         return
 
@@ -576,6 +585,8 @@ def main():
             fn(i)
         first = one_window(fn, warmup, steps)
         count = int(min(MAX_WINDOWS, max(1, math.ceil(min_seconds * 1e3 / max(first, 1e-3)))))
+        if args.windows > 0:
+            count = args.windows
         ms = [first] + [one_window(fn, warmup + (k + 1) * steps, steps) for k in range(count - 1)]
         return float(np.median(ms)), ms
 
