@@ -106,6 +106,82 @@ __device__ __forceinline__ void ummaCommitPair(uint32_t barAddr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barAddr) : "memory");
 }
 
+// One K block of the pair: the four MMAs, the two commits that hand the stage back to both CTAs and, issued ahead
+// of them, a non-blocking test of the barrier the next K block waits for (see ummaBlockPeek).
+__device__ __forceinline__ uint32_t ummaBlockPeekPair(uint32_t tmemD, uint64_t descA, uint64_t stepA, uint64_t descB,
+                                                      uint64_t stepB, uint32_t idesc, uint32_t accumulateFirst, int count,
+                                                      uint32_t commitOwn, uint32_t commitPeer, uint64_t *peekBar,
+                                                      uint32_t peekParity) {
+    uint32_t ready;
+    asm volatile("{\n\t.reg .pred q, a0, a1, g1, g2, g3;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+                 "setp.ne.b32 a0, %9, 0;\n\t"
+                 "setp.ne.b32 a1, %10, 0;\n\t"
+                 "setp.gt.s32 g1, %18, 1;\n\t"
+                 "setp.gt.s32 g2, %18, 2;\n\t"
+                 "setp.gt.s32 g3, %18, 3;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::i8 [%3], %4, %5, %8, {%11, %11, %11, %11, %11, %11, %11, %11}, a0;\n\t"
+                 "@g1 tcgen05.mma.cta_group::2.kind::i8 [%3], %6, %7, %8, {%11, %11, %11, %11, %11, %11, %11, %11}, a1;\n\t"
+                 "@g2 tcgen05.mma.cta_group::2.kind::i8 [%3], %12, %13, %8, {%11, %11, %11, %11, %11, %11, %11, %11}, a1;\n\t"
+                 "@g3 tcgen05.mma.cta_group::2.kind::i8 [%3], %14, %15, %8, {%11, %11, %11, %11, %11, %11, %11, %11}, a1;\n\t"
+                 "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%16];\n\t"
+                 "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%17];\n\t"
+                 "selp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(ready)
+                 : "r"(smemAddr(peekBar)), "r"(peekParity), "r"(tmemD), "l"(descA), "l"(descB), "l"(descA + stepA),
+                   "l"(descB + stepB), "r"(idesc), "r"(accumulateFirst), "r"(1u), "r"(0u), "l"(descA + 2 * stepA),
+                   "l"(descB + 2 * stepB), "l"(descA + 3 * stepA), "l"(descB + 3 * stepB), "r"(commitOwn), "r"(commitPeer),
+                   "r"(count)
+                 : "memory");
+    return ready;
+}
+
+// The producer's counterpart (see tmaStagePeekTiled): the stage's two loads of this CTA, completing on the leader's
+// barrier `fullAddr`; `expectBytes` != 0 (the leader only) announces the bytes of both CTAs on `fullOwn` first.
+__device__ __forceinline__ uint32_t tmaStagePeekTiledPair(uint64_t *fullOwn, uint32_t expectBytes, uint32_t fullAddr,
+                                                          const CUtensorMap *mapW, void *dstW, int w0, int w1, int w2,
+                                                          const CUtensorMap *mapX, void *dstX, int x0, int x1, int x2,
+                                                          uint64_t *peekBar, uint32_t peekParity) {
+    uint32_t ready;
+    asm volatile("{\n\t.reg .pred q, e;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+                 "setp.ne.b32 e, %4, 0;\n\t"
+                 "@e mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %4;\n\t"
+                 "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%5], [%6, {%7, %8, %9}], [%15];\n\t"
+                 "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%10], [%11, {%12, %13, %14}], [%15];\n\t"
+                 "selp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(ready)
+                 : "r"(smemAddr(peekBar)), "r"(peekParity), "r"(smemAddr(fullOwn)), "r"(expectBytes), "r"(smemAddr(dstW)),
+                   "l"(reinterpret_cast<uint64_t>(mapW)), "r"(w0), "r"(w1), "r"(w2), "r"(smemAddr(dstX)),
+                   "l"(reinterpret_cast<uint64_t>(mapX)), "r"(x0), "r"(x1), "r"(x2), "r"(fullAddr)
+                 : "memory");
+    return ready;
+}
+__device__ __forceinline__ uint32_t tmaStagePeekIm2colPair(uint64_t *fullOwn, uint32_t expectBytes, uint32_t fullAddr,
+                                                           const CUtensorMap *mapW, void *dstW, int w0, int w1, int w2,
+                                                           const CUtensorMap *mapX, void *dstX, int c, int w, int h, int n,
+                                                           uint16_t offW, uint16_t offH, uint64_t *peekBar,
+                                                           uint32_t peekParity) {
+    uint32_t ready;
+    asm volatile("{\n\t.reg .pred q, e;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+                 "setp.ne.b32 e, %4, 0;\n\t"
+                 "@e mbarrier.arrive.expect_tx.shared::cta.b64 _, [%3], %4;\n\t"
+                 "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%5], [%6, {%7, %8, %9}], [%18];\n\t"
+                 "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%10], [%11, {%12, %13, %14, %15}], [%18], {%16, %17};\n\t"
+                 "selp.u32 %0, 1, 0, q;\n\t}"
+                 : "=r"(ready)
+                 : "r"(smemAddr(peekBar)), "r"(peekParity), "r"(smemAddr(fullOwn)), "r"(expectBytes), "r"(smemAddr(dstW)),
+                   "l"(reinterpret_cast<uint64_t>(mapW)), "r"(w0), "r"(w1), "r"(w2), "r"(smemAddr(dstX)),
+                   "l"(reinterpret_cast<uint64_t>(mapX)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(offW), "h"(offH), "r"(fullAddr)
+                 : "memory");
+    return ready;
+}
+
 // X_MODE: kXTiled = tmapX is a K-major matrix {K, M, batches}; kXIm2col = tmapX is an im2col map of the NHWC input
 //         and tmapW the {IC, taps, OC} weight map.
 // W_MN  : tmapW is {N, K, batches}, N contiguous (kXTiled only).
@@ -195,7 +271,10 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
         // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
             const uint32_t fullLeader = mapToCta(smemAddr(&bars->full[0]), 0u);
-            uint32_t it = 0, tileCount = 0;
+            uint32_t tileCount = 0;
+            uint32_t ready = 0; // 1: the stage of the coming K block is known to be empty (see tmaStagePeekTiled)
+            int s = 0;
+            uint32_t phase = 0;
             bool ok = true;
             for (int64_t t = pairIdx; t < numTiles && ok; t += numPairs, ++tileCount) {
                 const OcTile tc = tileOf(t);
@@ -213,27 +292,28 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
                     h0 = oy * p.strideY - p.padTop;
                     w0 = (rem - oy * p.OW) * p.strideX - p.padLeft;
                 }
-                for (int kb = 0; kb < numKb; ++kb, ++it) {
-                    const int s = int(it % NSTAGE);
-                    const uint32_t phase = (it / NSTAGE) & 1u;
-                    ok = mbarWait(&bars->empty[s], phase ^ 1u, 21);
-                    if (!ok) {
-                        break;
+                for (int kb = 0; kb < numKb; ++kb) {
+                    if (ready == 0) {
+                        ok = mbarWait(&bars->empty[s], phase ^ 1u, 21);
+                        if (!ok) {
+                            break;
+                        }
                     }
+                    const int sNext = s + 1 == NSTAGE ? 0 : s + 1;
+                    const uint32_t phaseNext = sNext == 0 ? phase ^ 1u : phase;
                     const uint32_t fullAddr = fullLeader + uint32_t(s) * uint32_t(sizeof(uint64_t));
-                    if (rank == 0) {
-                        // The bytes of both CTAs.  The peer's copies need no arrival of their own: they are issued
-                        // after the peer's empty[s] completed, i.e. after the MMAs that read the stage's previous
-                        // contents, which themselves waited for the previous phase of this barrier; so they can only
-                        // count towards the phase this announcement belongs to (before it, the count of pending
-                        // bytes is transiently negative).  A release-arrival on the leader's barrier per stage was
-                        // measured at about 1000 cycles in the peer's producer, which then paced the whole pair.
-                        mbarArriveExpectTx(&bars->full[s], uint32_t(2 * (kTileW + kTileX)));
-                    }
+                    // The leader announces the bytes of both CTAs.  The peer's copies need no arrival of their own: they
+                    // are issued after the peer's empty[s] completed, i.e. after the MMAs that read the stage's previous
+                    // contents, which themselves waited for the previous phase of this barrier; so they can only count
+                    // towards the phase this announcement belongs to (before it, the count of pending bytes is
+                    // transiently negative).  A release-arrival on the leader's barrier per stage was measured at about
+                    // 1000 cycles in the peer's producer, which then paced the whole pair.
+                    const uint32_t expectBytes = rank == 0 ? uint32_t(2 * (kTileW + kTileX)) : 0u;
                     if (X_MODE == kXIm2col) {
-                        tmaLoad3dPair(&tmapW, tilesW + s * kTileW, fullAddr, cb, ky * p.KW + kx, tc.c0);
-                        tmaLoadIm2col4dPair(&tmapX, tilesX + s * kTileX, fullAddr, cb, w0, h0, n0, uint16_t(kx * p.dilX),
-                                            uint16_t(ky * p.dilY));
+                        ready = tmaStagePeekIm2colPair(&bars->full[s], expectBytes, fullAddr, &tmapW, tilesW + s * kTileW, cb,
+                                                       ky * p.KW + kx, tc.c0, &tmapX, tilesX + s * kTileX, cb, w0, h0, n0,
+                                                       uint16_t(kx * p.dilX), uint16_t(ky * p.dilY), &bars->empty[sNext],
+                                                       phaseNext ^ 1u);
                         cb += BK;
                         if (cb >= p.IC) {
                             cb = 0;
@@ -242,14 +322,17 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
                                 ++ky;
                             }
                         }
+                    } else if (W_MN) {
+                        ready = tmaStagePeekTiledPair(&bars->full[s], expectBytes, fullAddr, &tmapW, tilesW + s * kTileW, tc.c0,
+                                                      kb * BK, tc.batch, &tmapX, tilesX + s * kTileX, kb * BK, mh, tc.batch,
+                                                      &bars->empty[sNext], phaseNext ^ 1u);
                     } else {
-                        if (W_MN) {
-                            tmaLoad3dPair(&tmapW, tilesW + s * kTileW, fullAddr, tc.c0, kb * BK, tc.batch);
-                        } else {
-                            tmaLoad3dPair(&tmapW, tilesW + s * kTileW, fullAddr, kb * BK, tc.c0, p.batchedB ? tc.batch : 0);
-                        }
-                        tmaLoad3dPair(&tmapX, tilesX + s * kTileX, fullAddr, kb * BK, mh, tc.batch);
+                        ready = tmaStagePeekTiledPair(&bars->full[s], expectBytes, fullAddr, &tmapW, tilesW + s * kTileW,
+                                                      kb * BK, tc.c0, p.batchedB ? tc.batch : 0, &tmapX, tilesX + s * kTileX,
+                                                      kb * BK, mh, tc.batch, &bars->empty[sNext], phaseNext ^ 1u);
                     }
+                    s = sNext;
+                    phase = phaseNext;
                 }
                 if (RESIDUAL && ok) {
                     // the shortcut bytes of this CTA's 128 channels, once the store that last used the C/D tile has read it
@@ -278,6 +361,7 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
             const uint32_t accFullOwn = smemAddr(&bars->accFull[0]), accFullPeer = mapToCta(accFullOwn, 1u);
             uint64_t dw = descW0, dx = descX0;
             uint32_t s = 0, phase = 0, tileCount = 0;
+            uint32_t ready = 0; // 1: the stage of the coming K block is known to be full (see ummaBlockPeek)
             bool ok = true;
             for (int64_t t = pairIdx; t < numTiles && ok; t += numPairs, ++tileCount) {
                 const uint32_t buf = tileCount & 1u;
@@ -287,28 +371,31 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmemD = tmemBase + buf * uint32_t(BNP);
-                uint32_t accumulate = 0u;
+                int kLeft = X_MODE == kXIm2col ? p.IC : p.K; // bytes of K in the coming block's tap or K axis
                 for (int kb = 0; kb < numKb; ++kb) {
-                    ok = mbarWait(&bars->full[s], phase, 22);
-                    if (!ok) {
-                        break;
+                    if (ready == 0) {
+                        ok = mbarWait(&bars->full[s], phase, 22);
+                        if (!ok) {
+                            break;
+                        }
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    ummaPair(tmemD, dw, dx, idesc, accumulate);
-                    ummaPair(tmemD, dw + kStepW, dx + kStepX, idesc, 1u);
-                    ummaPair(tmemD, dw + 2 * kStepW, dx + 2 * kStepX, idesc, 1u);
-                    ummaPair(tmemD, dw + 3 * kStepW, dx + 3 * kStepX, idesc, 1u);
-                    accumulate = 1u;
+                    const uint32_t sNext = s + 1 == uint32_t(NSTAGE) ? 0u : s + 1;
+                    const uint32_t phaseNext = sNext == 0 ? phase ^ 1u : phase;
                     // the stage is free in both CTAs once these MMAs have read it
-                    ummaCommitPair(emptyOwn0 + s * 8u);
-                    ummaCommitPair(emptyPeer0 + s * 8u);
-                    if (++s == uint32_t(NSTAGE)) {
-                        s = 0;
-                        phase ^= 1u;
+                    ready = ummaBlockPeekPair(tmemD, dw, kStepW, dx, kStepX, idesc, kb != 0 ? 1u : 0u, ummaCountFor(kLeft),
+                                              emptyOwn0 + s * 8u, emptyPeer0 + s * 8u, &bars->full[sNext], phaseNext);
+                    kLeft -= BK;
+                    if (kLeft <= 0) {
+                        kLeft = X_MODE == kXIm2col ? p.IC : 0;
+                    }
+                    if (sNext == 0) {
                         dw = descW0, dx = descX0;
                     } else {
                         dw += uint64_t(kTileW >> 4), dx += uint64_t(kTileX >> 4);
                     }
+                    s = sNext;
+                    phase = phaseNext;
                 }
                 if (ok) {
                     ummaCommitPair(accFullOwn + buf * 8u);
