@@ -109,6 +109,8 @@ int mlel_set_tuning(const char *key, int value) {
         const bool width = value == 0 || value == 128 || value == 192 || value == 256;
         if (k == "pair_kernel" && value >= 0 && value <= 2) {
             t.pairKernel = value;
+        } else if (k == "tile_progress" && value >= 0 && value <= 7) {
+            t.tileProgress = value;
         } else if (k == "dependent_launch") {
             t.dependentLaunch = value != 0;
         } else if (k == "pair_tile_pixels" && width) {

@@ -43,11 +43,14 @@ namespace {
 using namespace tc;
 
 
+// Threads per CTA: the TMA variants have a store warp where the gather variants have their two gather warps' first.
+constexpr int ocThreadsFor(int ew, int xMode) { return xMode == kXGather ? ocThreads(ew, true) : (ew + 3) * 32; }
+
 // X_MODE: how the pixel operand arrives: kXGather = gathered from the NHWC input described by p, kXTiled = tmapX
 // is a plain matrix, kXIm2col = tmapX is an im2col map of the NHWC input.
 // RESIDUAL: the fused residual tail is present (tmapC describes the shortcut tensor).
 template <int BNP, int NSTAGE, int EW, int X_MODE, bool RESIDUAL>
-__global__ void __launch_bounds__(ocThreads(EW, X_MODE == kXGather), 1)
+__global__ void __launch_bounds__(ocThreadsFor(EW, X_MODE), 1)
 gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CUtensorMap tmapW,
               const __grid_constant__ CUtensorMap tmapC, const __grid_constant__ CUtensorMap tmapD, const GemmI8Params p) {
     extern __shared__ uint8_t rawSmem[];
@@ -65,7 +68,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
 
     constexpr bool X_TMA = X_MODE != kXGather;
     static_assert(NSTAGE <= 6, "OcBarriers holds six stages");
-    constexpr int kOcTmaWarp = EW, kOcMmaWarp = EW + 1, kOcGatherWarp0 = EW + 2;
+    constexpr int kOcTmaWarp = EW, kOcMmaWarp = EW + 1, kOcGatherWarp0 = EW + 2; // TMA variants: EW + 2 = store warp
     constexpr uint32_t kTmemCols = 2 * BNP <= 256 ? 256u : 512u; // two accumulators; allocations are powers of two
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -74,12 +77,11 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     const int cTiles = (p.N + kOcTile - 1) / kOcTile;
     const int64_t numTiles = int64_t(pTiles) * cTiles * p.batches;
     const auto tileOf = [&](int64_t tile) {
-        // the launcher refuses 2^31 tiles and more: divisions by multiply-high (see FastDiv)
-        const uint32_t overP = fastDiv(uint32_t(tile), p.divTiles0), overC = fastDiv(overP, p.divTiles1);
+        const TileIndex ti = decodeTile(p, tile, pTiles, cTiles);
         OcTile c;
-        c.m0 = int(uint32_t(tile) - overP * uint32_t(pTiles)) * BNP;
-        c.c0 = int(overP - overC * uint32_t(cTiles)) * kOcTile;
-        c.batch = int(overC);
+        c.m0 = int(ti.pix) * BNP;
+        c.c0 = int(ti.chan) * kOcTile;
+        c.batch = int(ti.batch);
         return c;
     };
 
@@ -93,6 +95,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
             mbarInit(&bars->accEmpty[b], uint32_t(EW));
             mbarInit(&bars->cFull[b], 1u);
             mbarInit(&bars->cdEmpty[b], 1u);
+            mbarInit(&bars->cdFull[b], uint32_t(EW));
         }
         mbarInit(&bars->tabFull, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -116,7 +119,15 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         mbarArriveExpectTx(&bars->tabFull, uint32_t(kResidualTableBytes));
         bulkLoad(resTab, p.residualTable, uint32_t(kResidualTableBytes), &bars->tabFull);
     }
-    gridDependencySync(); // from here on activations are read and written
+    // From here on activations are read and written.  With a progress table of the launch before (TMA variants
+    // only) the producer lane waits per tile for the pixel tiles it reads and the storing thread waits for the whole
+    // grid before its first store; nobody else touches activations.
+    const bool byTiles = X_TMA && p.progressIn != nullptr;
+    if (!byTiles) {
+        gridDependencySync();
+    } else {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
 
     if (warp == kOcTmaWarp) {
         // ---------------- TMA producer ----------------
@@ -136,6 +147,28 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
                     const int oy = int(fastDiv(uint32_t(rem), p.divOW));
                     h0 = oy * p.strideY - p.padTop;
                     w0 = (rem - oy * p.OW) * p.strideX - p.padLeft;
+                }
+                if (byTiles) {
+                    // input pixels this tile reads, as a range of the producing launch's pixel index (whole input rows
+                    // from the first window's first row to the last window's last row)
+                    const int mLast = min(tc.m0 + BNP, p.M) - 1;
+                    int64_t lo = tc.m0, hi = mLast;
+                    if (X_MODE == kXIm2col) {
+                        const int n1 = int(fastDiv(uint32_t(mLast), p.divPlane));
+                        const int oy0 = int(fastDiv(uint32_t(tc.m0 - n0 * p.OH * p.OW), p.divOW));
+                        const int oy1 = int(fastDiv(uint32_t(mLast - n1 * p.OH * p.OW), p.divOW));
+                        const int yLo = max(oy0 * p.strideY - p.padTop, 0);
+                        const int yHi = min(oy1 * p.strideY - p.padTop + (p.KH - 1) * p.dilY, p.H - 1);
+                        lo = (int64_t(n0) * p.H + yLo) * p.W;
+                        hi = (int64_t(n1) * p.H + yHi) * p.W + p.W - 1;
+                    }
+                    if (lo <= hi) {
+                        ok = waitTiles(p.progressIn, uint32_t(lo / p.progressInTilePixels), uint32_t(hi / p.progressInTilePixels),
+                                       p.progressInTarget, 17);
+                        if (!ok) {
+                            break;
+                        }
+                    }
                 }
                 for (int kb = 0; kb < numKb; ++kb) {
                     if (ready == 0) {
@@ -230,6 +263,14 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
             }
         }
     } else if (warp >= kOcGatherWarp0) {
+        if (X_TMA) {
+            // ---------------- store warp ----------------
+            if (lane == 0) {
+                EpiWalk walk{};
+                walk.first = blockIdx.x, walk.stride = gridDim.x;
+                storeWarpOcMajor<BNP, EW, kOcTile>(&tmapD, p, bars, cdTiles, numTiles, pTiles, cTiles, walk);
+            }
+        }
         // ---------------- pixel gather (implicit GEMM): BNP / 64 tile rows per thread ----------------
         if (!X_TMA) {
             constexpr int kRows = BNP / kOcGatherThreads;
@@ -265,8 +306,8 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         // ---------------- epilogue ----------------
         EpiWalk walk{};
         walk.first = blockIdx.x, walk.stride = gridDim.x;
-        epilogueOcMajor<BNP, EW, RESIDUAL, kOcTile>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase, warp, lane, numTiles,
-                                                    pTiles, cTiles, walk);
+        epilogueOcMajor<BNP, EW, RESIDUAL, kOcTile, X_TMA>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase, warp, lane,
+                                                           numTiles, pTiles, cTiles, walk);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -286,7 +327,9 @@ template <int BNP, int NSTAGE, int EW, int X_MODE, bool RESIDUAL>
 int launchOcMajor(const OcMaps &maps, const GemmI8Params &params, cudaStream_t s) {
     GemmI8Params p = params;
     p.divPlane = makeFastDiv(int64_t(p.OH) * p.OW), p.divOW = makeFastDiv(p.OW);
-    p.divTiles0 = makeFastDiv((p.M + BNP - 1) / BNP), p.divTiles1 = makeFastDiv((p.N + kOcTile - 1) / kOcTile);
+    const int pixelTiles = (p.M + BNP - 1) / BNP, channelTiles = (p.N + kOcTile - 1) / kOcTile;
+    p.divTiles0 = makeFastDiv(p.channelFastest != 0 ? channelTiles : pixelTiles);
+    p.divTiles1 = makeFastDiv(p.channelFastest != 0 ? pixelTiles : channelTiles);
     constexpr size_t smemBytes = size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * size_t(BNP) * 128 +
                                  (RESIDUAL ? size_t(kResidualTableBytes) : 0) + 2 * BNP +
                                  kTapTabEntries * sizeof(int32_t) + sizeof(OcBarriers) + 1024;
@@ -301,7 +344,7 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &params, cudaStream_t s
         return MLEL_ERROR_UNKNOWN;
     }
     const int grid = int(tiles < smCount() ? tiles : smCount());
-    const cudaError_t err = launchDependent(kernel, grid, ocThreads(EW, X_MODE == kXGather), smemBytes, s, maps.x, maps.w,
+    const cudaError_t err = launchDependent(kernel, grid, ocThreadsFor(EW, X_MODE), smemBytes, s, maps.x, maps.w,
                                             maps.c, maps.d, p);
     if (err != cudaSuccess) {
         setLastError(std::string("tcgen05 channel-major convolution launch: ") + cudaGetErrorString(err));
@@ -352,10 +395,27 @@ bool gemmI8OcMajorApplies(const GemmI8Problem &q) {
             p.epi.main.lo >= -128 && p.epi.main.hi <= 127 && (reinterpret_cast<uintptr_t>(p.epi.shortcut) & 15u) == 0);
 }
 
-int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
+// Tile-level hand-over between consecutive launches (GemmI8Params::progressOut / progressIn, LaunchChain).
+//
+// Why it is safe.  Launch C follows launch B in the stream, both with programmatic dependent launch, and C's pixel
+// operand is B's output.  (1) C's CTAs only become resident once every CTA of B has started (that is when B has
+// triggered its dependents), and one CTA fills an SM, so a CTA of C never keeps a CTA of B from running: B's
+// counters always advance.  (2) A counter is incremented after the tile's store has completed, with release
+// semantics; C acquires it before the TMA loads of the pixels under it.  (3) Before its first store B itself has
+// waited for the whole grid before it (at its start, or before that store if it reads by tiles too); so a counter
+// of B also tells C that every launch before B has finished, which covers C's other activation input, the shortcut
+// tensor of a residual tail.  (4) The session may place C's output where B's input lay: C does not store before
+// griddepcontrol.wait has returned, i.e. before B has ended.  (5) The counters are zeroed by a memset at the start of
+// the dispatch, which is ordered after the previous dispatch like any other operation of the stream.
+int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s, LaunchChain *chain, const LaunchChain *consumed) {
     g_tensorCoreLaunches[1].fetch_add(1, std::memory_order_relaxed);
     GemmI8Params p = q.params;
     p.batches = q.batches;
+    p.progressOut = nullptr, p.progressIn = nullptr, p.channelFastest = 0;
+    LaunchChain before{}; // what the launch before this one publishes
+    if (consumed != nullptr) {
+        before = *consumed;
+    }
     // Pixels per tile.  Wider tiles move less operand data per multiply-accumulate, narrower ones fill the last
     // wave of CTAs better; a rule that weighed the two (least waves x width) was measured against one width for
     // every layer on the ResNet-50 shapes, and 192 pixels everywhere -- the variant with twelve epilogue warps --
@@ -397,6 +457,32 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s) {
     if (p.epi.hasResidual &&
         !makeMap(&maps.c, p.epi.shortcut, uint64_t(p.N), uint64_t(p.M), 1, uint64_t(p.ldOut), plane, kOcTile, boxPixels, false)) {
         return MLEL_ERROR_DEVICE;
+    }
+    const int progressMode = tensorCoreTuning().tileProgress.load(std::memory_order_relaxed);
+    const bool handOver = chain != nullptr && xMode != kXGather && progressMode != 0 &&
+                          tensorCoreTuning().dependentLaunch.load(std::memory_order_relaxed) != 0;
+    if (handOver && before.prevCounters != nullptr && (progressMode & 1)) {
+        // read by tiles when the launch before this one wrote exactly this launch's pixel operand
+        const void *input = q.aMatrix != nullptr ? q.aMatrix : static_cast<const void *>(p.in);
+        const int64_t inputPixels = q.aMatrix != nullptr ? int64_t(p.M) : int64_t(p.M / (p.OH * p.OW)) * p.H * p.W;
+        if (before.prevTensor == input && before.prevPixels == inputPixels) {
+            p.progressIn = before.prevCounters;
+            p.progressInTilePixels = before.prevTilePixels;
+            p.progressInTarget = before.prevTarget;
+        }
+    }
+    if (handOver && chain->publishNext && (progressMode & 2)) {
+        const size_t pixelTiles = size_t((p.M + width - 1) / width);
+        if (chain->used + pixelTiles <= chain->capacity) {
+            p.progressOut = chain->words + chain->used;
+            p.channelFastest = (progressMode & 4) ? 1 : 0;
+            chain->used += pixelTiles;
+            chain->prevTensor = p.out8;
+            chain->prevCounters = p.progressOut;
+            chain->prevTilePixels = width;
+            chain->prevTarget = uint32_t((p.N + kOcTile - 1) / kOcTile);
+            chain->prevPixels = p.M;
+        }
     }
     if (width == 256) {
         return launchOcMajorShape<256, 3, 8>(maps, p, xMode, s);

@@ -205,11 +205,11 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
 
     static_assert(NSTAGE <= 6, "OcBarriers holds six stages");
     static_assert(BK / UMMA_K == 4, "the MMA loop issues four instructions per K block");
-    // Warp roles: 0 MMA issuer (leader CTA) and TMEM owner, 1 TMA producer, 2 and 3 idle, 4 .. EW + 3 epilogue (a warp
+    // Warp roles: 0 MMA issuer (leader CTA) and TMEM owner, 1 TMA producer, 2 tile stores, 3 idle, 4 .. EW + 3 epilogue (a warp
     // reads the TMEM lane quarter given by its index modulo 4, so the epilogue starts on a multiple of four).  The two
     // single-lane roles come first: where the warp schedulers prefer older warps, their few instructions, which pace
     // the whole pair, are not held up by the epilogue warps that share their schedulers.
-    constexpr int kMmaWarpP = 0, kTmaWarpP = 1, kFirstEpiWarp = 4;
+    constexpr int kMmaWarpP = 0, kTmaWarpP = 1, kStoreWarpP = 2, kFirstEpiWarp = 4;
     constexpr uint32_t kTmemCols = 2 * BNP <= 256 ? 256u : 512u;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -238,6 +238,7 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
             mbarInit(&bars->accEmpty[b], uint32_t(2 * EW)); // epilogue warps of both CTAs (used in the leader only)
             mbarInit(&bars->cFull[b], 1u);
             mbarInit(&bars->cdEmpty[b], 1u);
+            mbarInit(&bars->cdFull[b], uint32_t(EW));
         }
         mbarInit(&bars->tabFull, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -351,8 +352,9 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
             constexpr uint32_t idesc = instrDescPair(BNP, W_MN);
             // Everything the loop needs per K block is kept in registers and stepped, not recomputed: the stage's two
             // operand descriptors (the address field counts 16-byte units and never leaves its 14 bits), its barrier
-            // addresses in both CTAs, its phase.  This one thread's instruction stream paces the pair: about 630
-            // cycles per K block were measured with or without the copies, against 512 that the MMAs take.
+            // addresses in both CTAs, its phase.  This one thread's instruction stream paces the pair: with the
+            // barrier tested after the MMAs and commits about 630 cycles per K block were measured, with or without
+            // the copies, against 512 that the MMAs take; hence the test ahead of them (ummaBlockPeekPair).
             const uint64_t descW0 =
                 W_MN ? smemDesc(smemAddr(tilesW), BK * 128, 1024) : smemDesc(smemAddr(tilesW), 16, 1024);
             const uint64_t descX0 = smemDesc(smemAddr(tilesX), 16, 1024);
@@ -403,6 +405,14 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
                 }
             }
         }
+    } else if (warp == kStoreWarpP) {
+        // ---------------- store warp (both CTAs) ----------------
+        if (lane == 0) {
+            EpiWalk walk{};
+            walk.first = pairIdx, walk.stride = numPairs;
+            walk.cOffset = int(rank) * kOcTile;
+            storeWarpOcMajor<BNP, EW, kPairChannels>(&tmapD, p, bars, cdTiles, numTiles, pTiles, cTiles, walk);
+        }
     } else if (warp >= kFirstEpiWarp) {
         // ---------------- epilogue (both CTAs, each on its own 128 channels) ----------------
         EpiWalk walk{};
@@ -410,8 +420,8 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
         walk.cOffset = int(rank) * kOcTile;
         walk.accEmpty[0] = mapToCta(smemAddr(&bars->accEmpty[0]), 0u);
         walk.accEmpty[1] = mapToCta(smemAddr(&bars->accEmpty[1]), 0u);
-        epilogueOcMajor<BNP, EW, RESIDUAL, kPairChannels>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase,
-                                                          warp - kFirstEpiWarp, lane, numTiles, pTiles, cTiles, walk);
+        epilogueOcMajor<BNP, EW, RESIDUAL, kPairChannels, true>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase,
+                                                                warp - kFirstEpiWarp, lane, numTiles, pTiles, cTiles, walk);
     }
 
     // Neither CTA may leave (or release tensor memory) while the other's MMAs, commits or arrivals can still

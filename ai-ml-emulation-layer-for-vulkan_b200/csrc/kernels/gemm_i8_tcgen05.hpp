@@ -69,6 +69,36 @@ struct GemmI8Params {
     // null when the node has none.
     static constexpr int kResidualRowBytes = 260;
     const uint8_t *residualTable;
+    // Tile-level hand-over between two consecutive channel-major launches of one stream (see LaunchChain; null
+    // pointers: off).  progressOut[j] counts the channel tiles of this launch's pixel tile j whose bytes have reached
+    // memory.  A launch with progressIn reads its pixel operand as soon as the counters of the producer's pixel tiles
+    // that cover it have reached progressInTarget, instead of waiting for the whole producing grid; it still waits
+    // for that grid before its first store.
+    uint32_t *progressOut;
+    const uint32_t *progressIn;
+    int32_t progressInTilePixels; // pixels per tile of the producing launch
+    uint32_t progressInTarget;    // its channel tiles per pixel tile
+    int32_t channelFastest;       // tile order: 1 = a pixel tile's channel tiles are consecutive tile indices
+};
+
+// What one dispatch keeps between consecutive launches so that a channel-major convolution can start on the finished
+// pixel tiles of the convolution before it.  `words` is zeroed when the dispatch starts; every publishing launch takes
+// its counters from it.  `prev*` describe what the launch just enqueued publishes; launchOp() takes them away before
+// every operator, so only the immediately preceding launch is ever consumed (see the ordering argument in
+// gemm_i8_ocmajor.cu).
+struct LaunchChain {
+    uint32_t *words = nullptr;
+    size_t capacity = 0, used = 0;
+    bool publishNext = false; // the operator enqueued next reads this operator's output as its pixel operand
+    const void *prevTensor = nullptr;
+    uint32_t *prevCounters = nullptr;
+    int32_t prevTilePixels = 0;
+    uint32_t prevTarget = 0;
+    int64_t prevPixels = 0;
+    void forget() {
+        prevTensor = nullptr;
+        prevCounters = nullptr;
+    }
 };
 
 struct GemmI8Problem {
@@ -90,7 +120,10 @@ int gemmI8Launch(const GemmI8Problem &problem, cudaStream_t stream);
 // Channel-major variant (gemm_i8_ocmajor.cu) for fused int8 convolutions with more than 64 output channels:
 // same problem description, weights as the tensor-core A operand.  `Applies` tells whether it can take q.
 bool gemmI8OcMajorApplies(const GemmI8Problem &problem);
-int gemmI8OcMajorLaunch(const GemmI8Problem &problem, cudaStream_t stream);
+// `chain` (may be null): where the launch records what it publishes; `consumed` (may be null): what the launch before it
+// in the stream published.
+int gemmI8OcMajorLaunch(const GemmI8Problem &problem, cudaStream_t stream, LaunchChain *chain = nullptr,
+                        const LaunchChain *consumed = nullptr);
 int ocMajorErrorWord();
 
 // Paired variant (gemm_i8_pair.cu): two CTAs of a cluster share one 256-channel tile through
@@ -106,6 +139,7 @@ struct TensorCoreTuning {
     std::atomic<int> pairTilePixels{0};    // 128, 192 or 256: pixels per tile of the paired kernel
     std::atomic<int> ocTilePixels{0};      // 128, 192 or 256: pixels per tile of the channel-major kernel
     std::atomic<int> dependentLaunch{1};   // 0: launch the tensor-core kernels without programmatic dependent launch
+    std::atomic<int> tileProgress{7};      // tile-level hand-over: bit 0 read by tiles, 1 publish, 2 channel tiles first
 };
 TensorCoreTuning &tensorCoreTuning();
 

@@ -104,7 +104,7 @@ int64_t padBits(const OpDesc &op, int32_t dtype) {
 }
 
 // CONV2D / fused CONV2D on the tensor cores (the node was prepared by GraphPipeline::prepareTensorCore).
-int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
+int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s, LaunchChain *chain, const LaunchChain *consumed) {
     const TView &in = T[op.in[0]], &w = T[op.in[1]], &out = T[op.out[0]];
     GemmI8Problem q{};
     GemmI8Params &p = q.params;
@@ -175,7 +175,7 @@ int launchConvTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     if (tryPairKernel(q, true, s, &rc)) {
         return rc;
     }
-    return gemmI8OcMajorApplies(q) ? gemmI8OcMajorLaunch(q, s) : gemmI8Launch(q, s);
+    return gemmI8OcMajorApplies(q) ? gemmI8OcMajorLaunch(q, s, chain, consumed) : gemmI8Launch(q, s);
 }
 
 // MATMUL / fused MATMUL: second input constant and pre-transposed (tc == 1), or transposed here (tc == 3).
@@ -256,15 +256,22 @@ int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
 void setLastError(const std::string &msg) { g_lastError = msg; }
 const std::string &lastError() { return g_lastError; }
 
-int launchOp(const OpDesc &op, const TView *T, cudaStream_t s) {
+int launchOp(const OpDesc &op, const TView *T, cudaStream_t s, LaunchChain *chain) {
     const auto in = [&](size_t k) -> const TView & { return T[op.in[k]]; };
     const TView &out = T[op.out[0]];
     int rc = MLEL_SUCCESS; // status of a vectorised kernel that took the operator
+    // What the launch before this operator publishes may only be used by this operator: take it away from the chain,
+    // so that any kernel but the channel-major convolution (which records its own) leaves nothing behind.
+    LaunchChain consumed{};
+    if (chain != nullptr) {
+        consumed = *chain;
+        chain->forget();
+    }
     if (op.tc) {
         // Addresses are only known here: pointers that are not 16-byte aligned go to the generic kernels.
         const bool aligned = ((reinterpret_cast<uintptr_t>(in(0).ptr) | reinterpret_cast<uintptr_t>(out.ptr)) & 15u) == 0;
         if (aligned && (op.kind == OP_CONV2D || op.kind == OP_FUSED_CONV2D)) {
-            return launchConvTensorCore(op, T, s);
+            return launchConvTensorCore(op, T, s, chain, &consumed);
         }
         if (aligned && (op.kind == OP_MATMUL || op.kind == OP_FUSED_MATMUL) &&
             (op.tc != 3 || (reinterpret_cast<uintptr_t>(in(1).ptr) & 15u) == 0)) {

@@ -205,7 +205,8 @@ struct OpDesc {
 
 // Launches one operator.  `tensors` is indexed by tensor id (op.in / op.out / op.epi hold ids).
 // Returns 0 or a negative mlel_status and sets the thread's last-error message.
-int launchOp(const OpDesc &op, const TView *tensors, cudaStream_t stream);
+struct LaunchChain; // kernels/gemm_i8_tcgen05.hpp: tile-level hand-over between consecutive tensor-core launches
+int launchOp(const OpDesc &op, const TView *tensors, cudaStream_t stream, LaunchChain *chain = nullptr);
 
 void setLastError(const std::string &msg);
 int elemSize(int32_t dtype);

@@ -1,5 +1,7 @@
 #include "session.hpp"
 
+#include "kernels/gemm_i8_tcgen05.hpp"
+
 #include <algorithm>
 #include <cstdlib>
 #include <set>
@@ -14,9 +16,40 @@ uint64_t roundUp(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
 Session::Session(GraphPipeline *pipeline) : pipeline_(pipeline) {
     pipeline_->finalize();
     plan();
+    // Counters of the tile-level hand-over, if two tensor-core convolutions follow each other anywhere in the list.
+    // Made here and not at the first dispatch, which may run inside a stream capture.  Without them (no
+    // device, no memory) the dispatch simply does without the hand-over.
+    const auto &exec = pipeline_->getExecList();
+    // one counter per 128 output pixels (the narrowest tile) of every convolution whose output the next one reads
+    size_t words = 0;
+    for (size_t k = 0; k + 1 < exec.size(); ++k) {
+        if (exec[k].tc != 0 && exec[k + 1].tc != 0 && !exec[k].out.empty() && !exec[k + 1].in.empty() &&
+            exec[k + 1].in[0] == exec[k].out[0]) {
+            const TensorDescriptor &out = pipeline_->tensor(exec[k].out[0]);
+            int64_t pixels = 1;
+            for (int i = 0; i + 1 < out.rank(); ++i) {
+                pixels *= out.dims[size_t(i)];
+            }
+            words += size_t((pixels + 127) / 128);
+        }
+    }
+    if (words != 0 && (cudaMalloc(&progressWords_, words * sizeof(uint32_t)) != cudaSuccess ||
+                       cudaMemset(progressWords_, 0, words * sizeof(uint32_t)) != cudaSuccess)) {
+        if (progressWords_ != nullptr) {
+            cudaFree(progressWords_);
+        }
+        progressWords_ = nullptr;
+        cudaGetLastError();
+    }
+    progressCapacity_ = progressWords_ != nullptr ? words : 0;
 }
 
-Session::~Session() { dropGraphs(); }
+Session::~Session() {
+    dropGraphs();
+    if (progressWords_ != nullptr) {
+        cudaFree(progressWords_);
+    }
+}
 
 void Session::dropGraphs() {
     for (auto &entry : graphs_) {
@@ -366,8 +399,24 @@ int Session::dispatch(cudaStream_t stream) {
         }
         return MLEL_SUCCESS;
     }
-    for (const auto &op : exec) {
-        const int r = launchOp(op, views_.data(), stream);
+    // Consecutive convolutions hand their output over tile by tile where the kernels can (LaunchChain).  The
+    // counters are the session's own (allocated with the session), zeroed in stream order before the first kernel.
+    LaunchChain chain{};
+    if (progressWords_ != nullptr) {
+        if (cudaMemsetAsync(progressWords_, 0, progressCapacity_ * sizeof(uint32_t), stream) != cudaSuccess) {
+            setLastError("cudaMemsetAsync of the progress counters failed");
+            return MLEL_ERROR_DEVICE;
+        }
+        chain.words = progressWords_;
+        chain.capacity = progressCapacity_;
+    }
+    for (size_t k = 0; k < exec.size(); ++k) {
+        const OpDesc &op = exec[k];
+        // does the next operator read this one's output as the pixel operand of a tensor-core convolution?
+        chain.publishNext = k + 1 < exec.size() && exec[k + 1].tc != 0 &&
+                            (exec[k + 1].kind == OP_CONV2D || exec[k + 1].kind == OP_FUSED_CONV2D) && !op.out.empty() &&
+                            !exec[k + 1].in.empty() && exec[k + 1].in[0] == op.out[0];
+        const int r = launchOp(op, views_.data(), stream, chain.words != nullptr ? &chain : nullptr);
         if (r != MLEL_SUCCESS) {
             return r;
         }

@@ -75,6 +75,10 @@ class Session {
         cudaGraphExec_t exec{nullptr};
         uint64_t lastUse{0}; // value of useCounter_ at the last launch: the entry with the smallest one is evicted
     };
+    // Counters of the tile-level hand-over between consecutive tensor-core launches (LaunchChain): a small device
+    // allocation of the session, made at its first dispatch and zeroed at the start of every dispatch.
+    uint32_t *progressWords_{nullptr};
+    size_t progressCapacity_{0}; // words: one per 128 output pixels of every convolution that can publish
     uint64_t useCounter_{0};
     std::map<std::vector<const void *>, CapturedGraph> graphs_;
     std::vector<const void *> bindingKey() const;
