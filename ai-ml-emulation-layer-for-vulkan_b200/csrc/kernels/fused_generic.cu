@@ -5,7 +5,10 @@
 //
 // Arithmetic: conv2d.comp:59-112 / depthwise_conv2d.comp:47-75 / matmul.comp:42-69 followed per
 // element by rescale.comp:27-72 and clamp.comp:24-53.
+#include <utility>
+
 #include "device_common.cuh"
+#include "gemm_i8_tcgen05.hpp"
 #include "kernels.hpp"
 
 namespace mlel {
@@ -229,6 +232,10 @@ __global__ void __launch_bounds__(128) depthwise3x3RowsKernel(const int8_t *__re
     constexpr int PX = 4;
     constexpr int COLS = (PX - 1) * SX + 3; // input pixels under the four windows of a row: 6 or 9
     constexpr int NT = SX == 1 ? 2 : 4;     // transposed groups of four pixels per input row
+    // Launched so that it may be scheduled while the kernel before it in the stream drains, and lets the kernel after
+    // it do the same (programmatic dependent launch): nothing is read or written before the wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int cw = C >> 2;
     const int groupsX = (OW + PX - 1) / PX, groupsY = (OH + R - 1) / R;
     const int64_t total = int64_t(N) * groupsY * groupsX * cw;
@@ -459,6 +466,22 @@ bool depthwise3x3Eligible(const TView &in, const TView &w, const TView &bias, co
     return (ptrs & 3u) == 0 && (reinterpret_cast<uintptr_t>(out.ptr) & (fused ? 3u : 15u)) == 0;
 }
 
+// Launch with programmatic stream serialization (the kernel must execute griddepcontrol.wait before it touches
+// memory): its blocks may be scheduled while the previous kernel of the stream drains.
+template <class... Params, class... Args>
+static void launchOverlapping(void (*kernel)(Params...), int grid, int threads, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(unsigned(threads));
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = tensorCoreTuning().dependentLaunch.load(std::memory_order_relaxed) != 0 ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 int depthwise3x3(const TView &in, const TView &w, const TView &bias, const TView &out, const ConvAttr &a,
                  const DevEpilogue *epi, cudaStream_t s) {
     constexpr int PX = 4;
@@ -478,7 +501,7 @@ int depthwise3x3(const TView &in, const TView &w, const TView &bias, const TView
         const int64_t total = int64_t(N) * ((OH + R - 1) / R) * ((OW + PX - 1) / PX) * (C / 4);
         const int grid = gridFor(total, 128, 16);
 #define MLEL_LAUNCH_ROWS(RR, SS, O8) \
-    depthwise3x3RowsKernel<RR, SS, O8><<<grid, 128, 0, s>>>(pi, pw, pb, nb, out.ptr, N, H, W, C, OH, OW, a, e)
+    launchOverlapping(depthwise3x3RowsKernel<RR, SS, O8>, grid, 128, s, pi, pw, pb, nb, out.ptr, N, H, W, C, OH, OW, a, e)
         if (epi != nullptr) {
             if (a.stride[1] == 1) {
                 if (four) { MLEL_LAUNCH_ROWS(4, 1, true); } else { MLEL_LAUNCH_ROWS(2, 1, true); }

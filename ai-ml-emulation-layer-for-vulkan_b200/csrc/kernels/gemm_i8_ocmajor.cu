@@ -423,6 +423,15 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s, LaunchChain *cha
     // although single layers timed alone prefer 128 pixels at 7x7 and 256 at 56x56.  Problems of at most 128
     // pixels take the narrow tile.
     int width = p.M <= 128 ? 128 : 192;
+    {
+        // a layer that leaves a quarter of the SMs without a tile takes the narrow tile if that fills more of them
+        const int64_t cT = (p.N + kOcTile - 1) / kOcTile;
+        const int64_t tiles192 = int64_t((p.M + 191) / 192) * cT, tiles128 = int64_t((p.M + 127) / 128) * cT;
+        if (tensorCoreTuning().ocTileRule.load(std::memory_order_relaxed) != 0 && tiles192 * 4 <= int64_t(smCount()) * 3 &&
+            tiles128 <= int64_t(smCount())) {
+            width = 128;
+        }
+    }
     const int forced = tensorCoreTuning().ocTilePixels.load(std::memory_order_relaxed);
     if (forced == 128 || forced == 192 || forced == 256) {
         width = forced;

@@ -76,6 +76,12 @@ CONV_CASES = [
     (1, 10, 10, 32, 40, 3, 1, 1, 1, 4, 0),
     (1, 6, 6, 16, 1, 1, 0, 1, 1, 0, 0),
     (2, 9, 9, 128, 72, 3, 1, 1, 1, 7, 0),
+    # 1x1 convolutions whose input channel count is not a multiple of 16 (MobileNet's 24 -> 144 expansions): the
+    # input goes through a copy with padded channels, which the TMA kernels then read as a plain matrix
+    (3, 14, 14, 24, 144, 1, 0, 1, 1, -6, 0),
+    (2, 9, 9, 40, 80, 1, 0, 1, 1, 11, 0),
+    (1, 7, 7, 24, 32, 1, 0, 1, 1, 2, 0),
+    (2, 8, 8, 20, 96, 1, 0, 2, 1, -3, 0),   # stride 2: stays on the table gather
 ]
 
 
