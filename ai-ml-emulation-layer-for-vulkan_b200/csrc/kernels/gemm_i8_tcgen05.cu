@@ -404,10 +404,16 @@ __device__ __forceinline__ void epilogueWarps(const GemmI8Params &p, PipeBarrier
 
 // Table gather of one 128-byte K block of one tile row: BK / G pieces of G bytes, piece j from origin + tab[j],
 // written to its place in the SWIZZLE_128B row at dstRow (swz = row & 7).
+// Only the first `bytes` bytes of the row are gathered (in groups of four pieces): the MMAs of a K block's zero-filled
+// tail are not issued (ummaCountFor), so nothing reads the rest of the row.
 template <int G>
-__device__ __forceinline__ void gatherPieces(const int8_t *origin, const int32_t *tab, uint32_t dstRow, uint32_t swz) {
+__device__ __forceinline__ void gatherPieces(const int8_t *origin, const int32_t *tab, uint32_t dstRow, uint32_t swz,
+                                             int bytes) {
 #pragma unroll
     for (int j4 = 0; j4 < BK / G; j4 += 4) {
+        if (j4 * G >= bytes) {
+            break;
+        }
         const int4 off = *reinterpret_cast<const int4 *>(tab + j4);
         const int offs[4] = {off.x, off.y, off.z, off.w};
 #pragma unroll
@@ -662,12 +668,14 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
                         // every tap is in range (zero-padded copy): pieces at tabulated offsets from the origin
                         const int8_t *origin =
                             rowValid ? base + (int64_t(oy * p.strideY) * p.W + ox * p.strideX) * p.IC : p.in;
+                        // bytes of K this block holds, rounded up to the MMAs that will read them
+                        const int blockBytes = ummaCountFor(p.K - kb * BK) * UMMA_K;
                         if (p.chunkBytes == 4) {
-                            gatherPieces<4>(origin, gatherTab + kb * (BK / 4), dstRow, swz);
+                            gatherPieces<4>(origin, gatherTab + kb * (BK / 4), dstRow, swz, blockBytes);
                         } else if (p.chunkBytes == 8) {
-                            gatherPieces<8>(origin, gatherTab + kb * (BK / 8), dstRow, swz);
+                            gatherPieces<8>(origin, gatherTab + kb * (BK / 8), dstRow, swz, blockBytes);
                         } else {
-                            gatherPieces<16>(origin, gatherTab + kb * (BK / 16), dstRow, swz);
+                            gatherPieces<16>(origin, gatherTab + kb * (BK / 16), dstRow, swz, blockBytes);
                         }
                         asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(smemAddr(&bars->full[s]))
                                      : "memory");

@@ -61,3 +61,27 @@ def test_library_has_no_oracle_dependency():
     out = subprocess.run(["ldd", os.path.join(ROOT, "ai-ml-emulation-layer-for-vulkan_b200", "libmlel_b200.so")],
                          capture_output=True, text=True).stdout
     assert "oracle" not in out
+
+
+def test_tuning_keys_and_values(mlel):
+    """mlel_set_tuning takes exactly the documented keys and values; anything else is an error and changes nothing.
+    (No GPU needed: the settings are read when a kernel is launched.)"""
+    lib = mlel.lib()
+    defaults = {b"pair_kernel": 1, b"pair_tile_pixels": 0, b"oc_tile_pixels": 0, b"oc_tile_rule": 1,
+                b"dependent_launch": 1, b"tile_progress": 7}
+    allowed = {b"pair_kernel": [0, 1, 2], b"pair_tile_pixels": [0, 128, 192, 256], b"oc_tile_pixels": [0, 128, 192, 256],
+               b"oc_tile_rule": [0, 1], b"dependent_launch": [0, 1], b"tile_progress": list(range(8))}
+    refused = {b"pair_kernel": [-1, 3], b"pair_tile_pixels": [64, 100], b"oc_tile_pixels": [96, 512],
+               b"oc_tile_rule": [2, -1], b"tile_progress": [8, -1]}
+    try:
+        for key, values in allowed.items():
+            for v in values:
+                assert lib.mlel_set_tuning(key, v) == 0, (key, v)
+        for key, values in refused.items():
+            for v in values:
+                assert lib.mlel_set_tuning(key, v) != 0, (key, v)
+        assert lib.mlel_set_tuning(b"no_such_key", 1) != 0
+        assert lib.mlel_set_tuning(None, 1) != 0
+    finally:
+        for key, v in defaults.items():
+            assert lib.mlel_set_tuning(key, v) == 0
