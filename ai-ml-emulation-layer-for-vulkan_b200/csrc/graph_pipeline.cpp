@@ -787,6 +787,110 @@ void GraphPipeline::fuse() {
             fused.push_back(std::move(g));
             continue;
         }
+        // A per-tensor RESCALE with constant parameters and signed operands, as the fused kernels evaluate it.
+        const auto plainRescale = [&](const OpDesc &r, int32_t inDtype, int32_t outDtype) {
+            return r.kind == OP_RESCALE && tensor(r.in[0]).dtype == inDtype && tensor(r.out[0]).dtype == outDtype && r.i[2] &&
+                   !r.i[4] && !r.i[5] && !r.i[6] && isConst(r.in[1]) && isConst(r.in[2]) && tensor(r.in[1]).dtype == MLEL_I32 &&
+                   tensor(r.out[0]).packed();
+        };
+        // REDUCE_MAX(x) -> SUB(x, max) -> RESCALE(int16) -> TABLE, and REDUCE_SUM of the TABLE's output: the row-wise
+        // exponentials of a quantised softmax.  One kernel reads a row of x once and writes the TABLE's output and the
+        // row sum, instead of five passes over tensors of x's size.
+        if (op.kind == OP_REDUCE && op.sub == RED_MAX && tensor(op.in[0]).dtype == MLEL_I32 && tensor(op.in[0]).packed()) {
+            const TensorDescriptor &x = tensor(op.in[0]);
+            const int rank = x.rank();
+            const int sb = soleConsumer(op.out[0]);
+            if (rank < 1 || op.i[0] != rank - 1 || x.dims.back() % 4 != 0 || sb < 0 || group[size_t(sb)] >= 0) {
+                continue;
+            }
+            const OpDesc &sub = ops_[size_t(sb)];
+            if (sub.kind != OP_BINARY || sub.sub != BIN_SUB || sub.in[0] != op.in[0] || sub.in[1] != op.out[0] ||
+                tensor(sub.out[0]).dims != x.dims) {
+                continue;
+            }
+            const int rsI = soleConsumer(sub.out[0]);
+            if (rsI < 0 || group[size_t(rsI)] >= 0 || !plainRescale(ops_[size_t(rsI)], MLEL_I32, MLEL_I16)) {
+                continue;
+            }
+            const OpDesc &rs = ops_[size_t(rsI)];
+            const int tbI = soleConsumer(rs.out[0]);
+            if (tbI < 0 || group[size_t(tbI)] >= 0 || ops_[size_t(tbI)].kind != OP_TABLE) {
+                continue;
+            }
+            const OpDesc &tb = ops_[size_t(tbI)];
+            const TensorDescriptor &e = tensor(tb.out[0]);
+            if (tb.in[0] != rs.out[0] || !isConst(tb.in[1]) || tensor(tb.in[1]).dtype != MLEL_I16 ||
+                tensor(tb.in[1]).numel() != 513 || e.dtype != MLEL_I32 || !e.packed() || e.cls != TensorClass::Session ||
+                uses[size_t(tb.out[0])].producers != 1) {
+                continue;
+            }
+            // the TABLE's output stays in memory (the softmax multiplies it later); its row sum joins the kernel if it
+            // is taken right away, i.e. before any other reader of the TABLE's output
+            int sumI = -1;
+            int firstOther = n;
+            for (int c : uses[size_t(tb.out[0])].consumers) {
+                const OpDesc &co = ops_[size_t(c)];
+                if (sumI < 0 && co.kind == OP_REDUCE && co.sub == RED_SUM && co.i[0] == rank - 1 && group[size_t(c)] < 0) {
+                    sumI = c;
+                } else {
+                    firstOther = std::min(firstOther, c);
+                }
+            }
+            if (sumI < 0 || sumI > firstOther || !tensor(ops_[size_t(sumI)].out[0]).packed()) {
+                continue;
+            }
+            Group g;
+            g.node = op;
+            g.node.kind = OP_FUSED_ROW_EXP;
+            g.node.name = "REDUCE_MAX+SUB+RESCALE+TABLE+REDUCE_SUM";
+            g.node.in = {op.in[0], tb.in[1]};
+            g.node.out = {tb.out[0], ops_[size_t(sumI)].out[0]};
+            g.node.fusedOps.clear();
+            g.last = i;
+            const int gi = int(fused.size());
+            for (int k : {i, sb, rsI, tbI, sumI}) {
+                absorb(g, gi, k);
+            }
+            g.node.epi.hasMain = true;
+            g.node.epi.main = toFusedRescale(*this, rs);
+            fused.push_back(std::move(g));
+            continue;
+        }
+        // MUL(a, b, shift) -> RESCALE [-> CLAMP] on int32: the last step of a quantised softmax or layer norm
+        if (op.kind == OP_MUL && tensor(op.out[0]).dtype == MLEL_I32 && tensor(op.in[0]).dtype == MLEL_I32 &&
+            tensor(op.in[1]).dtype == MLEL_I32 && tensor(op.in[0]).packed() && tensor(op.in[1]).packed() &&
+            tensor(op.in[0]).dims == tensor(op.out[0]).dims && tensor(op.out[0]).dims.back() % 4 == 0) {
+            const auto &da = tensor(op.in[0]).dims, &db = tensor(op.in[1]).dims;
+            bool perRow = db.size() == da.size() && db.back() == 1;
+            for (size_t k = 0; perRow && k + 1 < da.size(); ++k) {
+                perRow = da[k] == db[k];
+            }
+            const bool oneValue = tensor(op.in[1]).numel() == 1;
+            const int rsI = soleConsumer(op.out[0]);
+            if (!(db == da || perRow || oneValue) || rsI < 0 || group[size_t(rsI)] >= 0 ||
+                !(plainRescale(ops_[size_t(rsI)], MLEL_I32, MLEL_I8) || plainRescale(ops_[size_t(rsI)], MLEL_I32, MLEL_I16))) {
+                continue;
+            }
+            const OpDesc &rs = ops_[size_t(rsI)];
+            Group g;
+            g.node = op;
+            g.node.kind = OP_FUSED_MUL_RESCALE;
+            g.node.name = "MUL+RESCALE";
+            g.node.fusedOps.clear();
+            g.last = i;
+            const int gi = int(fused.size());
+            absorb(g, gi, i);
+            absorb(g, gi, rsI);
+            g.node.epi.hasMain = true;
+            g.node.epi.main = toFusedRescale(*this, rs);
+            int32_t tail = tryClamp(g, gi, rs.out[0], g.node.epi.main);
+            if (tail != rs.out[0]) {
+                g.node.name += "+CLAMP";
+            }
+            g.node.out = {tail};
+            fused.push_back(std::move(g));
+            continue;
+        }
         // RESCALE(a) + RESCALE(b) -> ADD -> RESCALE [-> CLAMP]  (quantised residual add)
         if (op.kind == OP_BINARY && op.sub == BIN_ADD && tensor(op.out[0]).dtype == MLEL_I32) {
             const int pa = producer[size_t(op.in[0])], pb = producer[size_t(op.in[1])];

@@ -66,6 +66,9 @@ bool vecRescale(const TView &in, const TView &out, const TView &mult, const TVie
                 int *rc);
 bool vecTable(const TView &in, const TView &out, const TView &table, cudaStream_t s, int *rc);
 // op: BIN_ADD or BIN_SUB, or -1 for MUL with `shift`
+// Fused nodes of the fusion pass (OP_FUSED_ROW_EXP, OP_FUSED_MUL_RESCALE): see vector_ops.cu.
+int rowExpFused(const TView &x, const TView &table, const TView &e, const TView &sums, const DevRescale &r, cudaStream_t s);
+int mulRescaleFused(const TView &a, const TView &b, const TView &out, uint32_t shift, const DevRescale &r, cudaStream_t s);
 bool vecBinaryI32(int32_t op, const TView &a, const TView &b, const TView &out, uint32_t shift, cudaStream_t s, int *rc);
 bool vecClampI8(const TView &in, const TView &out, int64_t lo, int64_t hi, cudaStream_t s, int *rc);
 bool vecRowReduce(int32_t op, const TView &in, const TView &out, uint32_t axis, cudaStream_t s, int *rc);

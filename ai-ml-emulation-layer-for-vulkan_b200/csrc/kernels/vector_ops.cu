@@ -303,6 +303,110 @@ __global__ void clampI8Kernel(const int8_t *__restrict__ in, int8_t *__restrict_
     }
 }
 
+// ---- fused rows of a quantised softmax ---------------------------------------------------------------------------
+// Element access of the two fused kernels below: 16-byte vectors where the tensors allow it, single elements where
+// an application tensor sits at an odd address.
+template <bool VEC> __device__ __forceinline__ void loadFourI32(const int32_t *p, int32_t (&v)[4]) {
+    if (VEC) {
+        load4<int32_t>(p, v);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            v[k] = p[k];
+        }
+    }
+}
+template <bool VEC, typename T> __device__ __forceinline__ void storeFour(T *p, const int32_t (&v)[4]) {
+    if (VEC) {
+        store4<T>(p, v);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            p[k] = T(v[k]);
+        }
+    }
+}
+
+// REDUCE_MAX(x) -> SUB(x, max) -> RESCALE (to int16) -> TABLE (int16 -> int32), and REDUCE_SUM of the TABLE's output
+// (reduce.comp:24-70, elementwise_binary.comp:146-173, rescale.comp:27-72, table.comp): one warp per row, the row read
+// twice (the second time from cache), every step with the arithmetic of the operator's own kernel above.
+template <bool VEC>
+__global__ void rowExpKernel(const int32_t *__restrict__ x, int32_t *__restrict__ e, int32_t *__restrict__ sums, int64_t rows,
+                             int len, const int16_t *__restrict__ table, DevRescale r) {
+    __shared__ int16_t lut[513];
+    for (int i = threadIdx.x; i < 513; i += blockDim.x) {
+        lut[i] = table[i];
+    }
+    __syncthreads();
+    const FastRescale f = makeFastRescale(__ldg(r.mult), int32_t(__ldg(r.shift)), r.inZp, r.doubleRound != 0);
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t row = warp; row < rows; row += warps) {
+        const int32_t *src = x + row * len;
+        int32_t *dst = e + row * len;
+        int32_t top = lowestOf<int32_t>();
+        for (int i = lane * 4; i < len; i += 128) {
+            int32_t v[4];
+            loadFourI32<VEC>(src + i, v);
+            top = max(max(top, v[0]), max(v[1], max(v[2], v[3])));
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            top = max(top, __shfl_xor_sync(0xffffffffu, top, d));
+        }
+        int32_t acc = 0;
+        for (int i = lane * 4; i < len; i += 128) {
+            int32_t v[4], out[4];
+            loadFourI32<VEC>(src + i, v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int32_t diff = int32_t(uint32_t(v[k]) - uint32_t(top));
+                const int32_t q = fastRescale(f, diff, r.outZp, r.lo, r.hi); // an int16 value
+                const int32_t index = (q + 32768) >> 7;
+                const int32_t fraction = q & 0x7f;
+                const int32_t base = lut[index], next = lut[index + 1];
+                out[k] = int32_t((uint32_t(base) << 7) + uint32_t(next - base) * uint32_t(fraction));
+                acc = int32_t(uint32_t(acc) + uint32_t(out[k]));
+            }
+            storeFour<VEC, int32_t>(dst + i, out);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            acc = int32_t(uint32_t(acc) + uint32_t(__shfl_xor_sync(0xffffffffu, acc, d)));
+        }
+        if (lane == 0) {
+            sums[row] = acc;
+        }
+    }
+}
+
+// MUL(a, b, shift) -> RESCALE [-> CLAMP] (mul.comp:24-59, rescale.comp:27-72).  B_MODE as in binaryI32Kernel.
+template <typename OUT, int B_MODE, bool VEC>
+__global__ void mulRescaleKernel(const int32_t *__restrict__ a, const int32_t *__restrict__ b, OUT *__restrict__ out,
+                                 int64_t groups, int rowLen, uint32_t shift, DevRescale r) {
+    const FastRescale f = makeFastRescale(__ldg(r.mult), int32_t(__ldg(r.shift)), r.inZp, r.doubleRound != 0);
+    GRID_STRIDE(g, groups) {
+        int32_t x[4], y[4], res[4];
+        loadFourI32<VEC>(a + 4 * g, x);
+        if (B_MODE == 0) {
+            loadFourI32<VEC>(b + 4 * g, y);
+        } else {
+            const int32_t v = __ldg(b + (B_MODE == 1 ? (4 * g) / rowLen : 0));
+            y[0] = y[1] = y[2] = y[3] = v;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int64_t p = int64_t(x[k]) * int64_t(y[k]);
+            if (shift > 0) {
+                p = int64_t(uint64_t(p) + (1ull << ((shift - 1) & 63))) >> (shift & 63);
+            }
+            res[k] = fastRescale(f, int32_t(uint32_t(uint64_t(p))), r.outZp, r.lo, r.hi);
+        }
+        storeFour<VEC, OUT>(out + 4 * g, res);
+    }
+}
+
 // ---- REDUCE_SUM / MAX / MIN along the last axis (reduce.comp:24-70) ------------------------------------------
 // One warp per row: lanes stride through the row four elements at a time, then combine with shuffles.  Integer
 // addition wraps, so the order of the partial sums does not change the result.
@@ -722,6 +826,78 @@ int interleaveColumns(const void *staging, void *out, int64_t rows, int32_t bloc
                                                         rows, blocks, pitch, int32_t(total), cb);
     }
     return finish("interleave columns");
+}
+
+
+int rowExpFused(const TView &x, const TView &table, const TView &e, const TView &sums, const DevRescale &r, cudaStream_t s) {
+    const int len = int(x.dims[x.rank - 1]);
+    const int64_t n = packedNumel(x);
+    if (n <= 0 || len <= 0 || len % 4 != 0 || packedNumel(e) != n || packedNumel(sums) != n / len || packedNumel(table) != 513) {
+        setLastError("fused softmax rows: operands do not match");
+        return MLEL_ERROR_UNKNOWN;
+    }
+    const int64_t rows = n / len;
+    const int grid = gridFor(rows * 32, kThreads, 16);
+    const auto *px = reinterpret_cast<const int32_t *>(x.ptr);
+    auto *pe = reinterpret_cast<int32_t *>(e.ptr);
+    auto *ps = reinterpret_cast<int32_t *>(sums.ptr);
+    const auto *pt = reinterpret_cast<const int16_t *>(table.ptr);
+    if (aligned16(x.ptr) && aligned16(e.ptr)) {
+        rowExpKernel<true><<<grid, kThreads, 0, s>>>(px, pe, ps, rows, len, pt, r);
+    } else {
+        rowExpKernel<false><<<grid, kThreads, 0, s>>>(px, pe, ps, rows, len, pt, r);
+    }
+    return finish("REDUCE_MAX+SUB+RESCALE+TABLE+REDUCE_SUM");
+}
+
+namespace {
+template <typename OUT>
+void launchMulRescale(const TView &a, const TView &b, const TView &out, int64_t n, int mode, int rowLen, uint32_t shift,
+                      const DevRescale &r, cudaStream_t s) {
+    const int grid = gridFor(n / 4, kThreads, 16);
+    const auto *pa = reinterpret_cast<const int32_t *>(a.ptr);
+    const auto *pb = reinterpret_cast<const int32_t *>(b.ptr);
+    auto *po = reinterpret_cast<OUT *>(out.ptr);
+    const bool vec = aligned16(a.ptr) && (mode != 0 || aligned16(b.ptr)) &&
+                     (reinterpret_cast<uintptr_t>(out.ptr) & (4 * sizeof(OUT) - 1)) == 0;
+#define MLEL_MUL_RESCALE(MODE)                                                                                     \
+    if (vec) {                                                                                                     \
+        mulRescaleKernel<OUT, MODE, true><<<grid, kThreads, 0, s>>>(pa, pb, po, n / 4, rowLen, shift, r);         \
+    } else {                                                                                                       \
+        mulRescaleKernel<OUT, MODE, false><<<grid, kThreads, 0, s>>>(pa, pb, po, n / 4, rowLen, shift, r);        \
+    }
+    if (mode == 0) {
+        MLEL_MUL_RESCALE(0)
+    } else if (mode == 1) {
+        MLEL_MUL_RESCALE(1)
+    } else {
+        MLEL_MUL_RESCALE(2)
+    }
+#undef MLEL_MUL_RESCALE
+}
+} // namespace
+
+int mulRescaleFused(const TView &a, const TView &b, const TView &out, uint32_t shift, const DevRescale &r, cudaStream_t s) {
+    const int64_t n = packedNumel(a), nb = packedNumel(b);
+    const int rowLen = int(a.dims[a.rank - 1]);
+    if (n <= 0 || n % 4 != 0 || rowLen % 4 != 0 || packedNumel(out) != n || nb <= 0) {
+        setLastError("fused MUL+RESCALE: operands do not match");
+        return MLEL_ERROR_UNKNOWN;
+    }
+    const int mode = nb == n ? 0 : (nb == 1 ? 2 : 1);
+    if (mode == 1 && nb != n / rowLen) {
+        setLastError("fused MUL+RESCALE: second operand is neither per row nor a single value");
+        return MLEL_ERROR_UNKNOWN;
+    }
+    if (out.dtype == MLEL_I8) {
+        launchMulRescale<int8_t>(a, b, out, n, mode, rowLen, shift, r, s);
+    } else if (out.dtype == MLEL_I16) {
+        launchMulRescale<int16_t>(a, b, out, n, mode, rowLen, shift, r, s);
+    } else {
+        setLastError("fused MUL+RESCALE: output type");
+        return MLEL_ERROR_UNKNOWN;
+    }
+    return finish("MUL+RESCALE");
 }
 
 } // namespace mlel

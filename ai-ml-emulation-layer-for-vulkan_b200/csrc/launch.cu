@@ -447,6 +447,10 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s, LaunchChain *chai
     }
     case OP_FUSED_MATMUL:
         return fusedMatmulGeneric(in(0), in(1), out, op.i[0], op.i[1], devEpilogue(op.epi, T), s);
+    case OP_FUSED_ROW_EXP:
+        return rowExpFused(in(0), in(1), T[op.out[0]], T[op.out[1]], devRescale(op.epi.main, T), s);
+    case OP_FUSED_MUL_RESCALE:
+        return mulRescaleFused(in(0), in(1), out, uint32_t(op.i[0]), devRescale(op.epi.main, T), s);
     case OP_FUSED_ADD:
         return fusedAdd(reinterpret_cast<const int8_t *>(in(0).ptr), reinterpret_cast<const int8_t *>(in(1).ptr),
                         reinterpret_cast<int8_t *>(out.ptr), numelOf(out), devEpilogue(op.epi, T), s);

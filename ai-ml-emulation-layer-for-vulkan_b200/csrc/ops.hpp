@@ -64,6 +64,12 @@ enum OpKind : int32_t {
     OP_FUSED_DEPTHWISE,  // DEPTHWISE_CONV2D -> RESCALE [-> CLAMP]
     OP_FUSED_MATMUL,     // MATMUL -> RESCALE [-> CLAMP]
     OP_FUSED_ADD,        // RESCALE(a), RESCALE(b) -> ADD -> RESCALE [-> CLAMP]
+    // Row-wise exponentials of a quantised softmax: REDUCE_MAX(x) -> SUB(x, max) -> RESCALE -> TABLE, and the
+    // REDUCE_SUM of the TABLE's output.  in = {x, table}, out = {table output, row sums}; epi.main is the RESCALE.
+    OP_FUSED_ROW_EXP,
+    // MUL(a, b, shift) -> RESCALE [-> CLAMP] on int32 operands (b: same shape, one value per row, or one value).
+    // in = {a, b}, i[0] = shift, epi.main is the RESCALE.
+    OP_FUSED_MUL_RESCALE,
     OP_KIND_COUNT
 };
 

@@ -160,7 +160,11 @@ def test_emitted_bert_lowers_and_fuses(mlel):
     # every projection and the context product carry their RESCALE; the score product feeds REDUCE_MAX and SUB
     # as int32 and stays a plain MATMUL
     assert names.count("MATMUL+RESCALE") == 2 * 7 and names.count("MATMUL") == 2
-    assert names.count("TABLE") == 2 * 5 and names.count("TRANSPOSE") == 2 * 4
+    assert names.count("TRANSPOSE") == 2 * 4
+    # the softmax's row maximum, subtraction, RESCALE, exponential TABLE and row sum are one node per layer, and the
+    # MUL + RESCALE that ends the softmax and each of the two layer norms another
+    assert names.count("REDUCE_MAX+SUB+RESCALE+TABLE+REDUCE_SUM") == 2 and names.count("MUL+RESCALE") == 2 * 3
+    assert names.count("TABLE") == 2 * 4 and "REDUCE_MAX" not in names
 
 
 def test_graph_outputs_are_never_elided(mlel):

@@ -132,3 +132,87 @@ def test_transpose_that_swaps_the_last_axis_of_bytes(mlel, shape, perms):
     x = g.input(np.int8, shape)
     g.output(g.transpose(x, perms))
     check(g, [full_range(r, np.int8, shape)])
+
+
+def check_fused(mlel, g, inputs, expect_names):
+    """Runs with the fusion pass on; checks that the expected fused nodes were made and compares with the oracle."""
+    from mlel_b200.runtime import GraphRunner
+    want = evaluate(g, inputs)
+    runner = GraphRunner(g)
+    names = runner.pipeline.exec_names()
+    for name in expect_names:
+        assert name in names, (name, names)
+    for use_cuda_graph in (False, True):
+        got = runner.run(inputs, use_cuda_graph=use_cuda_graph)
+        for k, (a, b) in enumerate(zip(got, want)):
+            assert a.dtype == b.dtype and a.shape == b.shape
+            if not np.array_equal(a, b):
+                bad = np.argwhere(a != b)
+                raise AssertionError(f"output {k}: {len(bad)} of {a.size} differ, first at {bad[0].tolist()}: "
+                                     f"got {a[tuple(bad[0])]} want {b[tuple(bad[0])]}")
+
+
+def _lut16(r):
+    return r.integers(-32768, 32768, (513,), dtype=np.int64).astype(np.int16)
+
+
+@pytest.mark.parametrize("shape", [(5, 7, 384), (3, 1, 4), (2, 9, 36), (1, 33, 388), (4, 16, 128)])
+@pytest.mark.parametrize("shift,double_round", [(31, False), (38, True), (30, False)])
+def test_fused_softmax_rows(mlel, shape, shift, double_round):
+    """REDUCE_MAX -> SUB -> RESCALE -> TABLE with the REDUCE_SUM of the TABLE's output as one node: row lengths that are
+    and are not multiples of a warp's 128 elements, differences that overflow int16 (they clamp), a row sum that
+    wraps, and a second reader of the TABLE's output after the sum."""
+    r = rng(shape[-1] + shift)
+    g = GraphBuilder()
+    x = g.input(np.int32, shape)
+    diff = g.sub(x, g.reduce("REDUCE_MAX", x, 2))
+    d16 = g.rescale(diff, [int(r.integers(1 << 30, (1 << 31) - 1))], [shift], 0, 11, np.int16, True, double_round)
+    e = g.table(d16, _lut16(r))
+    total = g.reduce("REDUCE_SUM", e, 2)
+    g.output(g.mul(e, total, 9))      # reads both results of the fused node
+    g.output(total)
+    data = r.integers(-(1 << 22), 1 << 22, shape, dtype=np.int64).astype(np.int32)
+    data.reshape(-1)[:3] = [np.iinfo(np.int32).max, np.iinfo(np.int32).min, 0]
+    check_fused(mlel, g, [data], ["REDUCE_MAX+SUB+RESCALE+TABLE+REDUCE_SUM"])
+
+
+def test_softmax_rows_are_not_fused_when_the_sum_comes_after_another_reader(mlel):
+    r = rng(3)
+    g = GraphBuilder()
+    x = g.input(np.int32, (2, 6, 32))
+    diff = g.sub(x, g.reduce("REDUCE_MAX", x, 2))
+    e = g.table(g.rescale(diff, [1 << 30], [33], 0, 0, np.int16), _lut16(r))
+    first = g.clamp(g.rescale(e, [1 << 30], [40], 0, 0, np.int8), -100, 100)   # reads e before the sum is taken
+    total = g.reduce("REDUCE_SUM", e, 2)
+    g.output(first)
+    g.output(total)
+    from mlel_b200.runtime import GraphRunner
+    data = r.integers(-(1 << 20), 1 << 20, (2, 6, 32), dtype=np.int64).astype(np.int32)
+    runner = GraphRunner(g)
+    assert "REDUCE_MAX+SUB+RESCALE+TABLE+REDUCE_SUM" not in runner.pipeline.exec_names()
+    for a, b in zip(runner.run([data]), evaluate(g, [data])):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("b_shape", ["same", "row", "one"])
+@pytest.mark.parametrize("out_dtype,shift,rshift,clamp", [(np.int8, 22, 37, None), (np.int8, 0, 33, (-20, 90)),
+                                                         (np.int16, 12, 45, None), (np.int8, 31, 30, None)])
+def test_fused_mul_rescale(mlel, b_shape, out_dtype, shift, rshift, clamp):
+    """MUL(a, b, shift) -> RESCALE [-> CLAMP] as one node: second operand of the same shape, one value per row, one
+    value; products that need all 64 bits before the shift; int8 and int16 results."""
+    r = rng(shift + rshift)
+    shape = (3, 50, 36)
+    g = GraphBuilder()
+    a = g.input(np.int32, shape)
+    bs = {"same": shape, "row": shape[:-1] + (1,), "one": (1, 1, 1)}[b_shape]
+    b = g.input(np.int32, bs)
+    y = g.rescale(g.mul(a, b, shift), [int(r.integers(1 << 30, (1 << 31) - 1))], [rshift], -5, 3, out_dtype, True,
+                  rshift > 31)
+    if clamp is not None:
+        y = g.clamp(y, *clamp)
+    g.output(y)
+    lim = 1 << 30 if shift >= 22 else 1 << 15
+    da = r.integers(-lim, lim, shape, dtype=np.int64).astype(np.int32)
+    db = r.integers(-lim, lim, bs, dtype=np.int64).astype(np.int32)
+    da.reshape(-1)[:2] = [lim - 1, -lim]
+    check_fused(mlel, g, [da, db], ["MUL+RESCALE+CLAMP" if clamp is not None else "MUL+RESCALE"])
