@@ -40,6 +40,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <map>
+#include <functional>
 #include <cstring>
 #include <queue>
 #include <set>
@@ -651,11 +653,6 @@ void GraphPipeline::makeConv3D(int32_t input, int32_t output, int32_t weights, i
 
 namespace {
 
-struct UseInfo {
-    std::vector<int> consumers; // op indices reading the tensor
-    int producers{0};
-};
-
 FusedRescale toFusedRescale(const GraphPipeline &p, const OpDesc &r) {
     FusedRescale f;
     f.multTensor = r.in[1];
@@ -673,6 +670,386 @@ FusedRescale toFusedRescale(const GraphPipeline &p, const OpDesc &r) {
 }
 
 } // namespace
+
+// Contiguous runs of row-wise integer operators -> OP_FUSED_ROWS nodes (see RowProgram in ops.hpp and
+// kernels/row_machine.cu).  A run is a maximal stretch of consecutive, not yet grouped operators of the kinds RESCALE
+// (per tensor, constant parameters), TABLE (constant table), ADD, SUB, MUL on int32, REDUCE_SUM/MAX/MIN along the last
+// axis of an int32 tensor and CLAMP, whose tensors all have the run's full shape F = [..., L] (L a multiple of 4), F
+// with a last dimension of 1, or one constant element.  Because the run is contiguous in creation order, everything it
+// reads from outside exists before its first operator and nothing outside it runs between its operators, so the node
+// can stand at the position of the last one.  Tensors used only inside the run are never written to memory.
+void GraphPipeline::fuseRowRuns(std::vector<int> &group, const std::vector<UseInfo> &uses,
+                                const std::function<void(OpDesc, const std::vector<int> &)> &emit) {
+    const int n = int(ops_.size());
+    enum { kNone = 0, kFull, kValue, kOne };
+    const auto shapeKind = [&](int32_t t, const std::vector<int64_t> &F) {
+        const TensorDescriptor &td = tensor(t);
+        if (!td.packed()) {
+            return int(kNone);
+        }
+        if (td.dims == F) {
+            return int(kFull);
+        }
+        if (td.dims.size() == F.size() && td.dims.back() == 1 &&
+            std::equal(F.begin(), F.end() - 1, td.dims.begin())) {
+            return int(kValue);
+        }
+        return td.numel() == 1 ? int(kOne) : int(kNone);
+    };
+    const auto intType = [](int32_t d) { return d == MLEL_I8 || d == MLEL_I16 || d == MLEL_I32; };
+    const auto isConst = [&](int32_t t) { return tensor(t).cls == TensorClass::Constant; };
+    // Whether `op` can be an instruction of a run of shape F (operand shapes are checked by the caller's build).
+    const auto accepted = [&](const OpDesc &op, const std::vector<int64_t> &F) {
+        const auto kindOf = [&](int32_t t) { return shapeKind(t, F); };
+        switch (op.kind) {
+        case OP_RESCALE: {
+            const int32_t di = tensor(op.in[0]).dtype, dout = tensor(op.out[0]).dtype;
+            return intType(di) && intType(dout) && op.i[2] && !op.i[4] && !op.i[5] && !op.i[6] && isConst(op.in[1]) &&
+                   isConst(op.in[2]) && tensor(op.in[1]).dtype == MLEL_I32 && tensor(op.in[1]).hostData.size() >= 4 &&
+                   !tensor(op.in[2]).hostData.empty() && kindOf(op.in[0]) != kNone && kindOf(op.in[0]) != kOne &&
+                   kindOf(op.out[0]) == kindOf(op.in[0]);
+        }
+        case OP_TABLE: {
+            const TensorDescriptor &tb = tensor(op.in[1]);
+            const int32_t di = tensor(op.in[0]).dtype, dout = tensor(op.out[0]).dtype;
+            const bool t8 = di == MLEL_I8 && dout == MLEL_I8 && tb.dtype == MLEL_I8 && tb.numel() == 256;
+            const bool t16 = di == MLEL_I16 && dout == MLEL_I32 && tb.dtype == MLEL_I16 && tb.numel() == 513;
+            return isConst(op.in[1]) && (t8 || t16) && kindOf(op.in[0]) != kNone && kindOf(op.in[0]) != kOne &&
+                   kindOf(op.out[0]) == kindOf(op.in[0]);
+        }
+        case OP_BINARY:
+        case OP_MUL: {
+            if (op.kind == OP_BINARY && op.sub != BIN_ADD && op.sub != BIN_SUB) {
+                return false;
+            }
+            if (op.kind == OP_MUL && (op.i[0] < 0 || op.i[0] > 62)) {
+                return false;
+            }
+            const int ka = kindOf(op.in[0]), kb = kindOf(op.in[1]), ko = kindOf(op.out[0]);
+            if (tensor(op.in[0]).dtype != MLEL_I32 || tensor(op.in[1]).dtype != MLEL_I32 ||
+                tensor(op.out[0]).dtype != MLEL_I32 || ka == kNone || kb == kNone) {
+                return false;
+            }
+            if ((ka == kOne && !isConst(op.in[0])) || (kb == kOne && !isConst(op.in[1]))) {
+                return false; // a single run-time value is neither per row nor an immediate
+            }
+            const int widest = (ka == kFull || kb == kFull) ? kFull : kValue;
+            return ko == widest && (ka != kOne || kb != kOne);
+        }
+        case OP_REDUCE:
+            return (op.sub == RED_SUM || op.sub == RED_MAX || op.sub == RED_MIN) && tensor(op.in[0]).dtype == MLEL_I32 &&
+                   tensor(op.out[0]).dtype == MLEL_I32 && op.i[0] == int(F.size()) - 1 && kindOf(op.in[0]) == kFull &&
+                   kindOf(op.out[0]) == kValue;
+        case OP_CLAMP:
+            return intType(tensor(op.in[0]).dtype) && tensor(op.in[0]).dtype == tensor(op.out[0]).dtype &&
+                   kindOf(op.in[0]) != kNone && kindOf(op.in[0]) != kOne && kindOf(op.out[0]) == kindOf(op.in[0]);
+        default:
+            return false;
+        }
+    };
+    // Translates ops_[first .. last] into a program, unless it needs more instructions, values or shared memory than the
+    // kernel has (kTooLarge) or does not pay (kNotWorthIt: saves no pass over a full-shaped tensor, or costs more in
+    // the row kernel than as separate kernels).
+    enum { kBuilt = 0, kTooLarge, kNotWorthIt };
+    const auto build = [&](int first, int last, const std::vector<int64_t> &F, OpDesc *node) -> int {
+        auto prog = std::make_shared<RowProgram>();
+        prog->len = int32_t(F.back());
+        prog->rows = 1;
+        for (size_t k = 0; k + 1 < F.size(); ++k) {
+            prog->rows *= F[k];
+        }
+        std::map<int32_t, RowOperand> where; // tensor -> slot, per-row word or immediate
+        std::map<int32_t, int> lastUse;      // tensor -> last operator of the run that reads it
+        for (int k = first; k <= last; ++k) {
+            for (int32_t t : ops_[size_t(k)].in) {
+                lastUse[t] = k;
+            }
+        }
+        std::vector<int> freeSlots, freeValues;
+        int slots = 0, values = 0, elided = 0;
+        std::vector<int32_t> reads, writes;
+        const auto take = [&](int kind) {
+            RowOperand o;
+            o.kind = kind == kFull ? ROW_FULL : ROW_VALUE;
+            std::vector<int> &pool = kind == kFull ? freeSlots : freeValues;
+            if (!pool.empty()) {
+                o.index = pool.back();
+                pool.pop_back();
+            } else {
+                o.index = kind == kFull ? slots++ : values++;
+            }
+            return o;
+        };
+        const auto release = [&](const RowOperand &o) {
+            if (o.kind == ROW_FULL) {
+                freeSlots.push_back(o.index);
+            } else if (o.kind == ROW_VALUE) {
+                freeValues.push_back(o.index);
+            }
+        };
+        const auto operand = [&](int32_t t) -> RowOperand {
+            const auto it = where.find(t);
+            if (it != where.end()) {
+                return it->second;
+            }
+            const TensorDescriptor &td = tensor(t);
+            const int kind = shapeKind(t, F);
+            RowOperand o;
+            if (kind == kOne && isConst(t)) {
+                o.kind = ROW_IMMEDIATE;
+                int64_t v = 0;
+                const uint8_t *d = td.hostData.data();
+                if (td.dtype == MLEL_I8) {
+                    v = int8_t(d[0]);
+                } else if (td.dtype == MLEL_I16) {
+                    int16_t x;
+                    std::memcpy(&x, d, 2);
+                    v = x;
+                } else {
+                    int32_t x;
+                    std::memcpy(&x, d, 4);
+                    v = x;
+                }
+                o.imm = int32_t(v);
+            } else {
+                o = take(kind == kFull ? kFull : kValue);
+                RowInst ld;
+                ld.op = ROW_LOAD;
+                ld.dst = o;
+                ld.tensor = t;
+                ld.dtype = td.dtype;
+                prog->insts.push_back(ld);
+                reads.push_back(t);
+            }
+            where[t] = o;
+            return o;
+        };
+        for (int k = first; k <= last; ++k) {
+            const OpDesc &op = ops_[size_t(k)];
+            RowInst in;
+            const int dataInputs = (op.kind == OP_BINARY || op.kind == OP_MUL) ? 2 : 1;
+            in.a = operand(op.in[0]);
+            if (dataInputs == 2) {
+                in.b = operand(op.in[1]);
+            }
+            switch (op.kind) {
+            case OP_RESCALE: {
+                const TensorDescriptor &m = tensor(op.in[1]), &sh = tensor(op.in[2]);
+                const int32_t di = tensor(op.in[0]).dtype, dout = tensor(op.out[0]).dtype;
+                int32_t mult;
+                std::memcpy(&mult, m.hostData.data(), 4);
+                in.op = ROW_RESCALE;
+                in.p[0] = mult;
+                in.p[1] = int32_t(int8_t(sh.hostData[0]));
+                in.p[2] = int32_t(wrapTo(di, op.i[0]));
+                in.p[3] = int32_t(wrapTo(dout, op.i[1]));
+                in.p[4] = int32_t(typeLowest(dout));
+                in.p[5] = int32_t(typeMax(dout));
+                in.p[6] = (op.i[2] && op.i[3]) ? 1 : 0;
+                break;
+            }
+            case OP_TABLE:
+                in.op = tensor(op.in[0]).dtype == MLEL_I8 ? ROW_TABLE8 : ROW_TABLE16;
+                in.tensor = op.in[1];
+                reads.push_back(op.in[1]);
+                break;
+            case OP_BINARY:
+                in.op = op.sub == BIN_ADD ? ROW_ADD : ROW_SUB;
+                break;
+            case OP_MUL:
+                in.op = ROW_MUL;
+                in.p[0] = op.i[0];
+                break;
+            case OP_REDUCE:
+                in.op = op.sub == RED_SUM ? ROW_REDUCE_SUM : (op.sub == RED_MAX ? ROW_REDUCE_MAX : ROW_REDUCE_MIN);
+                break;
+            default: { // OP_CLAMP
+                const int32_t dt = tensor(op.in[0]).dtype;
+                const double lo = std::max(op.d[0], double(typeLowest(dt))), hi = std::min(op.d[1], double(typeMax(dt)));
+                in.op = ROW_CLAMP;
+                in.p[0] = int32_t(lo);
+                in.p[1] = int32_t(hi);
+                break;
+            }
+            }
+            // operands that nobody reads after this operator give their place back before the result takes one (an
+            // element-wise result may overwrite its own operand: a lane only touches its own elements)
+            for (int32_t t : {op.in[0], dataInputs == 2 ? op.in[1] : int32_t(-1)}) {
+                if (t >= 0 && lastUse[t] == k && where.count(t)) {
+                    release(where[t]);
+                    where.erase(t);
+                }
+            }
+            const int32_t out = op.out[0];
+            const int outKind = shapeKind(out, F);
+            in.dst = take(outKind == kFull ? kFull : kValue);
+            where[out] = in.dst;
+            prog->insts.push_back(in);
+            // written to memory if anything outside the run reads it (or the application does)
+            const TensorDescriptor &od = tensor(out);
+            bool needed = od.cls != TensorClass::Session || od.isGraphOutput || uses[size_t(out)].producers != 1;
+            for (int c : uses[size_t(out)].consumers) {
+                needed = needed || c < first || c > last;
+            }
+            if (needed) {
+                RowInst st;
+                st.op = ROW_STORE;
+                st.a = in.dst;
+                st.tensor = out;
+                st.dtype = od.dtype;
+                prog->insts.push_back(st);
+                writes.push_back(out);
+            } else if (outKind == kFull) {
+                ++elided;
+            }
+            if (!lastUse.count(out) || lastUse[out] <= k) {
+                release(in.dst); // no reader inside the run
+                where.erase(out);
+            }
+        }
+        prog->slots = slots;
+        prog->values = values;
+        if (prog->insts.size() > size_t(kMaxRowInsts) || values > kMaxRowValues || rowMachineWarps(slots, prog->len) < 2) {
+            return kTooLarge;
+        }
+        if (elided == 0 || writes.empty()) {
+            return kNotWorthIt;
+        }
+        // Is the run worth it?  In the row kernel every instruction costs issue slots (it is bound by instructions, at
+        // about half an instruction per cycle and scheduler); as kernels of their own the same operators are bound by
+        // the bytes they move, or by the same arithmetic.  Picoseconds per element of the full shape, measured on a
+        // B200 with softmax rows of 384 and layer-norm rows of 768 elements (the row kernel's figures include its
+        // per-instruction overhead):
+        const auto machineCost = [](int op) {
+            switch (op) {
+            case ROW_RESCALE:
+            case ROW_TABLE16:
+                return 1.2;
+            case ROW_MUL:
+                return 0.8;
+            case ROW_TABLE8:
+                return 0.5;
+            case ROW_LOAD:
+            case ROW_STORE:
+            case ROW_REDUCE_SUM:
+            case ROW_REDUCE_MAX:
+            case ROW_REDUCE_MIN:
+                return 0.2;
+            default:
+                return 0.27; // ADD, SUB, CLAMP
+            }
+        };
+        double fusedCost = 0.0;
+        for (const RowInst &in : prog->insts) {
+            const bool full = in.dst.kind == ROW_FULL || in.a.kind == ROW_FULL;
+            fusedCost += full ? machineCost(in.op) : 0.0;
+        }
+        // The alternative: one kernel per operator at 0.18 ps per byte of full-shaped operand or result (5.5 TB/s), not
+        // below 0.6 of its arithmetic in the row kernel; the two smaller fused nodes of this pass (the exponential rows
+        // of a softmax, MUL + RESCALE) count as one kernel each.
+        const auto fullBytes = [&](int32_t t) { return shapeKind(t, F) == kFull ? double(dtypeSize(tensor(t).dtype)) : 0.0; };
+        const auto kindAt = [&](int k, OpKind kind, int sub) {
+            return k <= last && ops_[size_t(k)].kind == kind && (sub < 0 || ops_[size_t(k)].sub == sub);
+        };
+        const auto rowOpOf = [&](const OpDesc &op) {
+            switch (op.kind) {
+            case OP_RESCALE:
+                return int(ROW_RESCALE);
+            case OP_TABLE:
+                return tensor(op.in[0]).dtype == MLEL_I8 ? int(ROW_TABLE8) : int(ROW_TABLE16);
+            case OP_MUL:
+                return int(ROW_MUL);
+            case OP_REDUCE:
+                return int(ROW_REDUCE_SUM);
+            default:
+                return int(ROW_ADD);
+            }
+        };
+        double separateCost = 0.0;
+        for (int k = first; k <= last; ++k) {
+            int span = 1;
+            if (kindAt(k, OP_REDUCE, RED_MAX) && kindAt(k + 1, OP_BINARY, BIN_SUB) && kindAt(k + 2, OP_RESCALE, -1) &&
+                kindAt(k + 3, OP_TABLE, -1) && kindAt(k + 4, OP_REDUCE, RED_SUM)) {
+                span = 5;
+            } else if (kindAt(k, OP_MUL, -1) && kindAt(k + 1, OP_RESCALE, -1)) {
+                span = 2;
+            }
+            // bytes: what the span reads from outside itself and its last full-shaped result (a softmax's exponentials
+            // are written as well: the TABLE's result)
+            double bytes = 0.0, arithmetic = 0.0;
+            for (int m = k; m < k + span; ++m) {
+                const OpDesc &op = ops_[size_t(m)];
+                const int dataInputs = (op.kind == OP_BINARY || op.kind == OP_MUL) ? 2 : 1;
+                for (int q = 0; q < dataInputs; ++q) {
+                    bool inside = false;
+                    for (int w = k; w < m; ++w) {
+                        inside = inside || ops_[size_t(w)].out[0] == op.in[size_t(q)];
+                    }
+                    bytes += inside ? 0.0 : fullBytes(op.in[size_t(q)]);
+                }
+                const bool lastOfSpan = m == k + span - 1, tableOfSoftmax = span == 5 && m == k + 3;
+                bytes += (lastOfSpan || tableOfSoftmax) ? fullBytes(op.out[0]) : 0.0;
+                const bool full = shapeKind(op.out[0], F) == kFull || shapeKind(op.in[0], F) == kFull;
+                arithmetic += full ? machineCost(rowOpOf(op)) : 0.0;
+            }
+            separateCost += std::max(0.18 * bytes, 0.6 * arithmetic);
+            k += span - 1;
+        }
+        if (fusedCost >= separateCost) {
+            return kNotWorthIt;
+        }
+        std::sort(reads.begin(), reads.end());
+        reads.erase(std::unique(reads.begin(), reads.end()), reads.end());
+        node->kind = OP_FUSED_ROWS;
+        node->in = reads;
+        node->out = writes;
+        node->rows = prog;
+        node->name = "ROWS";
+        for (int k = first; k <= last; ++k) {
+            node->name += (k == first ? "(" : "+") + ops_[size_t(k)].name;
+        }
+        node->name += ")";
+        return kBuilt;
+    };
+    for (int i = 0; i < n; ++i) {
+        if (group[size_t(i)] >= 0) {
+            continue;
+        }
+        const OpDesc &head = ops_[size_t(i)];
+        if (head.kind != OP_RESCALE && head.kind != OP_TABLE && head.kind != OP_BINARY && head.kind != OP_MUL &&
+            head.kind != OP_REDUCE && head.kind != OP_CLAMP) {
+            continue;
+        }
+        // the run's full shape: what its first operator reads (a reduction) or writes
+        const std::vector<int64_t> F = head.kind == OP_REDUCE ? tensor(head.in[0]).dims : tensor(head.out[0]).dims;
+        if (F.empty() || F.back() < 4 || F.back() % 4 != 0 || F.back() > (int64_t(1) << 20)) {
+            continue;
+        }
+        int j = i;
+        while (j < n && group[size_t(j)] < 0 && accepted(ops_[size_t(j)], F)) {
+            ++j;
+        }
+        // The whole stretch, or -- only if the kernel cannot hold it -- its longest prefix that fits.  A stretch that is
+        // not worth fusing is left alone as a whole: cutting it elsewhere would also cut the smaller patterns in it.
+        for (int last = j - 1; last > i; --last) {
+            OpDesc node = ops_[size_t(last)];
+            const int verdict = build(i, last, F, &node);
+            if (verdict == kBuilt) {
+                std::vector<int> members;
+                for (int k = i; k <= last; ++k) {
+                    members.push_back(k);
+                }
+                emit(std::move(node), members);
+                i = last;
+                break;
+            }
+            if (verdict == kNotWorthIt) {
+                i = j - 1;
+                break;
+            }
+        }
+    }
+}
 
 // Fusion keeps the arithmetic of every absorbed operator unchanged (the same integer steps run
 // back to back in registers), so results stay bit-identical to the one-kernel-per-op list; it only
@@ -748,6 +1125,22 @@ void GraphPipeline::fuse() {
         return cl.out[0];
     };
 
+    // Phase 0: contractions with their RESCALE and the quantised residual add.  Between the phases: contiguous runs of
+    // row-wise operators (fuseRowRuns).  Phase 1: the two smaller row patterns, for what the runs left over.
+    for (int phase = 0; phase < 2; ++phase) {
+    if (phase == 1) {
+        fuseRowRuns(group, uses, [&](OpDesc node, const std::vector<int> &members) {
+            Group g;
+            g.node = std::move(node);
+            g.node.fusedOps.clear();
+            g.last = members.back();
+            const int gi = int(fused.size());
+            for (int k : members) {
+                absorb(g, gi, k);
+            }
+            fused.push_back(std::move(g));
+        });
+    }
     for (int i = 0; i < n; ++i) {
         if (group[size_t(i)] >= 0) {
             continue;
@@ -796,7 +1189,8 @@ void GraphPipeline::fuse() {
         // REDUCE_MAX(x) -> SUB(x, max) -> RESCALE(int16) -> TABLE, and REDUCE_SUM of the TABLE's output: the row-wise
         // exponentials of a quantised softmax.  One kernel reads a row of x once and writes the TABLE's output and the
         // row sum, instead of five passes over tensors of x's size.
-        if (op.kind == OP_REDUCE && op.sub == RED_MAX && tensor(op.in[0]).dtype == MLEL_I32 && tensor(op.in[0]).packed()) {
+        if (phase == 1 && op.kind == OP_REDUCE && op.sub == RED_MAX && tensor(op.in[0]).dtype == MLEL_I32 &&
+            tensor(op.in[0]).packed()) {
             const TensorDescriptor &x = tensor(op.in[0]);
             const int rank = x.rank();
             const int sb = soleConsumer(op.out[0]);
@@ -857,7 +1251,7 @@ void GraphPipeline::fuse() {
             continue;
         }
         // MUL(a, b, shift) -> RESCALE [-> CLAMP] on int32: the last step of a quantised softmax or layer norm
-        if (op.kind == OP_MUL && tensor(op.out[0]).dtype == MLEL_I32 && tensor(op.in[0]).dtype == MLEL_I32 &&
+        if (phase == 1 && op.kind == OP_MUL && tensor(op.out[0]).dtype == MLEL_I32 && tensor(op.in[0]).dtype == MLEL_I32 &&
             tensor(op.in[1]).dtype == MLEL_I32 && tensor(op.in[0]).packed() && tensor(op.in[1]).packed() &&
             tensor(op.in[0]).dims == tensor(op.out[0]).dims && tensor(op.out[0]).dims.back() % 4 == 0) {
             const auto &da = tensor(op.in[0]).dims, &db = tensor(op.in[1]).dims;
@@ -944,6 +1338,7 @@ void GraphPipeline::fuse() {
             fused.push_back(std::move(g));
         }
     }
+    } // phases
     // Residual tail into the producing convolution: when one operand of a fused add is the (otherwise
     // unused) output of a fused CONV2D, the add and its three RESCALEs run in that convolution's epilogue
     // on the value still in registers; the other operand (the shortcut) is read there.  The merged node

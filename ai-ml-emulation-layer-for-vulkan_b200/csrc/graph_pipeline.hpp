@@ -6,6 +6,7 @@
 #pragma once
 
 #include <cstdint>
+#include <functional>
 #include <map>
 #include <memory>
 #include <stdexcept>
@@ -44,6 +45,12 @@ struct TensorDescriptor {
 class UnsupportedError : public std::runtime_error {
   public:
     using std::runtime_error::runtime_error;
+};
+
+// Who reads and writes a tensor, by operator index (the fusion pass).
+struct UseInfo {
+    std::vector<int> consumers; // op indices reading the tensor
+    int producers{0};
 };
 
 class GraphPipeline {
@@ -149,6 +156,8 @@ class GraphPipeline {
     OpDesc &pushOp(OpKind kind, const std::string &name, std::vector<int32_t> in, std::vector<int32_t> out);
     void requireMutable() const;
     void fuse();
+    void fuseRowRuns(std::vector<int> &group, const std::vector<UseInfo> &uses,
+                     const std::function<void(OpDesc, const std::vector<int> &)> &emit);
     void prepareTensorCore();
     void buildResidualTable(OpDesc &op);
     int32_t addDerivedConstant(int32_t dtype, const std::vector<int64_t> &dims, const void *data);

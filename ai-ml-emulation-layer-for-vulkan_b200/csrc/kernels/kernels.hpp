@@ -66,6 +66,10 @@ bool vecRescale(const TView &in, const TView &out, const TView &mult, const TVie
                 int *rc);
 bool vecTable(const TView &in, const TView &out, const TView &table, cudaStream_t s, int *rc);
 // op: BIN_ADD or BIN_SUB, or -1 for MUL with `shift`
+// A fused run of row-wise operators (OP_FUSED_ROWS): row_machine.cu.  rowMachineWarps tells how many rows a block can
+// hold at once for `slots` full-shaped values of `len` elements (0: the run cannot be fused).
+int rowMachineWarps(int slots, int len);
+int rowMachine(const RowProgram &program, const TView *tensors, cudaStream_t s);
 // Fused nodes of the fusion pass (OP_FUSED_ROW_EXP, OP_FUSED_MUL_RESCALE): see vector_ops.cu.
 int rowExpFused(const TView &x, const TView &table, const TView &e, const TView &sums, const DevRescale &r, cudaStream_t s);
 int mulRescaleFused(const TView &a, const TView &b, const TView &out, uint32_t shift, const DevRescale &r, cudaStream_t s);

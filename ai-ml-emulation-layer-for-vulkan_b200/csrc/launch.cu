@@ -447,6 +447,12 @@ int launchOp(const OpDesc &op, const TView *T, cudaStream_t s, LaunchChain *chai
     }
     case OP_FUSED_MATMUL:
         return fusedMatmulGeneric(in(0), in(1), out, op.i[0], op.i[1], devEpilogue(op.epi, T), s);
+    case OP_FUSED_ROWS:
+        if (!op.rows) {
+            setLastError("fused rows: no program");
+            return MLEL_ERROR_UNKNOWN;
+        }
+        return rowMachine(*op.rows, T, s);
     case OP_FUSED_ROW_EXP:
         return rowExpFused(in(0), in(1), T[op.out[0]], T[op.out[1]], devRescale(op.epi.main, T), s);
     case OP_FUSED_MUL_RESCALE:

@@ -6,6 +6,7 @@
 #pragma once
 
 #include <cstdint>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -70,6 +71,9 @@ enum OpKind : int32_t {
     // MUL(a, b, shift) -> RESCALE [-> CLAMP] on int32 operands (b: same shape, one value per row, or one value).
     // in = {a, b}, i[0] = shift, epi.main is the RESCALE.
     OP_FUSED_MUL_RESCALE,
+    // A contiguous run of row-wise integer operators (RESCALE, TABLE, ADD, SUB, MUL, last-axis REDUCE, CLAMP) as one
+    // kernel: see RowProgram.  in = every tensor read from memory (tables included), out = every tensor written.
+    OP_FUSED_ROWS,
     OP_KIND_COUNT
 };
 
@@ -182,6 +186,45 @@ struct FusedEpilogue {
     FusedRescale a, b, out;
 };
 
+// A run of row-wise integer operators fused into one kernel (OP_FUSED_ROWS): every tensor of the run has the run's
+// full shape [..., L], the same shape with a last dimension of 1 (one value per row) or one element.  A warp owns
+// a row, keeps the full-shaped values in shared-memory slots and the per-row values in a few words beside them, and
+// executes the instructions in order, each with the arithmetic of the operator's own kernel.
+enum RowOpcode : int32_t {
+    ROW_LOAD = 0,   // dst <- tensor (full: a row of `dtype` elements; per-row value: element `row`)
+    ROW_STORE,      // tensor <- a
+    ROW_RESCALE,    // p = {mult, shift, inZp, outZp, lo, hi, doubleRound}
+    ROW_TABLE8,     // int8 -> int8 by 256 entries
+    ROW_TABLE16,    // int16 -> int32 by 513 entries with interpolation
+    ROW_ADD,
+    ROW_SUB,
+    ROW_MUL,        // p[0] = shift
+    ROW_REDUCE_SUM, // full -> per-row value
+    ROW_REDUCE_MAX,
+    ROW_REDUCE_MIN,
+    ROW_CLAMP,      // p = {lo, hi}
+};
+enum RowOperandKind : int32_t { ROW_NONE = 0, ROW_FULL, ROW_VALUE, ROW_IMMEDIATE };
+struct RowOperand {
+    int32_t kind{ROW_NONE};
+    int32_t index{0}; // slot (ROW_FULL) or per-row word (ROW_VALUE)
+    int32_t imm{0};   // ROW_IMMEDIATE
+};
+struct RowInst {
+    int32_t op{ROW_LOAD};
+    RowOperand dst, a, b;
+    int32_t tensor{-1}; // LOAD / STORE: the tensor; TABLE: the table
+    int32_t dtype{MLEL_I32};
+    int32_t p[7]{};
+};
+struct RowProgram {
+    std::vector<RowInst> insts;
+    int32_t slots{0}, values{0};
+    int64_t rows{0};
+    int32_t len{0};
+};
+constexpr int kMaxRowInsts = 40, kMaxRowValues = 16;
+
 struct OpDesc {
     OpKind kind{OP_CAST};
     int32_t sub{0};          // BinaryOp / UnaryOp / ReduceOp
@@ -192,6 +235,7 @@ struct OpDesc {
     std::vector<int32_t> out;
     FusedEpilogue epi;              // fused kinds only
     std::vector<int32_t> fusedOps;  // indices of the logical ops an exec node stands for
+    std::shared_ptr<RowProgram> rows; // OP_FUSED_ROWS only
     // Tensor-core path (set by GraphPipeline::prepareTensorCore when the node qualifies):
     //   CONV2D kinds: aux[0] correction table int32 [classes][OC], aux[1] row classes u8 [OH],
     //                 aux[2] column classes u8 [OW]; auxi[0] = number of column classes, auxi[1] = classes,

@@ -161,10 +161,15 @@ def test_emitted_bert_lowers_and_fuses(mlel):
     # as int32 and stays a plain MATMUL
     assert names.count("MATMUL+RESCALE") == 2 * 7 and names.count("MATMUL") == 2
     assert names.count("TRANSPOSE") == 2 * 4
-    # the softmax's row maximum, subtraction, RESCALE, exponential TABLE and row sum are one node per layer, and the
-    # MUL + RESCALE that ends the softmax and each of the two layer norms another
-    assert names.count("REDUCE_MAX+SUB+RESCALE+TABLE+REDUCE_SUM") == 2 and names.count("MUL+RESCALE") == 2 * 3
-    assert names.count("TABLE") == 2 * 4 and "REDUCE_MAX" not in names
+    # The thirteen operators of each residual add with its layer norm are one row-wise node.  The softmax's are not
+    # (its RESCALEs, exponential TABLE and MUL cost more in the row kernel than the passes it would save): its row
+    # maximum, subtraction, RESCALE, TABLE and row sum are one node and its final MUL + RESCALE another, with the
+    # reciprocal's RESCALE and TABLE on the row sums between them.  The other TABLE is the GELU.
+    norm = "ROWS(RESCALE+RESCALE+ADD+REDUCE_SUM+MUL+SUB+MUL+REDUCE_SUM+MUL+RESCALE+TABLE+MUL+RESCALE)"
+    assert names.count(norm) == 2 * 2
+    assert names.count("REDUCE_MAX+SUB+RESCALE+TABLE+REDUCE_SUM") == 2 and names.count("MUL+RESCALE") == 2
+    assert names.count("TABLE") == 2 * 2 and names.count("RESCALE") == 2
+    assert "REDUCE_MAX" not in names and "MUL" not in names and len(names) == 2 * 27
 
 
 def test_graph_outputs_are_never_elided(mlel):

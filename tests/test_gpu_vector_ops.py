@@ -140,8 +140,8 @@ def check_fused(mlel, g, inputs, expect_names):
     want = evaluate(g, inputs)
     runner = GraphRunner(g)
     names = runner.pipeline.exec_names()
-    for name in expect_names:
-        assert name in names, (name, names)
+    for name in expect_names:  # as a node of its own or as part of a longer row-wise run
+        assert any(name in n for n in names), (name, names)
     for use_cuda_graph in (False, True):
         got = runner.run(inputs, use_cuda_graph=use_cuda_graph)
         for k, (a, b) in enumerate(zip(got, want)):
