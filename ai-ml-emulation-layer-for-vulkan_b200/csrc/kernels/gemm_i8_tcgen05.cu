@@ -313,9 +313,15 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
 }
 
 // int32 output: accumulator + correction, no RESCALE.
+// `staging` (or null): 32 rows x 16 int32 per epilogue warp, rows kStageInts words apart.  A thread holds 16 columns of
+// ONE row, so a warp's 16-byte stores would go to 32 different rows (32 lines per instruction); through the staging
+// block four lanes write one row's 64 bytes and an instruction touches 8 lines.  (The attention-score product of the
+// BERT-shaped encoder, 226 MB of int32 per layer: 140 -> about 85 us.)
+constexpr int kStageInts = 20;                      // 16 values + 4 words of padding: no shared-memory bank conflicts
+constexpr int kStageBytesPerWarp = 32 * kStageInts * 4;
 template <int BN, int NSTAGE>
 __device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarriers *bars, uint32_t tmemBase, int warp,
-                                              int lane, int64_t numTiles, int mTiles, int nTiles) {
+                                              int lane, int64_t numTiles, int mTiles, int nTiles, int32_t *staging) {
     const int quarter = warp & 3;
     const int half = warp >> 2;
     constexpr int kColsPerWarp = BN / (kEpilogueWarps / 4);
@@ -360,6 +366,34 @@ __device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarrier
                 }
             }
             const int col0 = n0 + cl;
+            if (staging != nullptr && col0 + 16 <= p.N) {
+                // whole 16-column block inside the matrix (rows past the end are dropped below): the warp's 32 x 16
+                // block goes through shared memory so that four lanes write one row's 64 bytes
+                if (corr != nullptr && rowValid) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        acc[j] += uint32_t(__ldg(corr + col0 + j));
+                    }
+                }
+                int32_t *mine = staging + warp * (32 * kStageInts);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    *reinterpret_cast<int4 *>(mine + lane * kStageInts + 4 * q) =
+                        make_int4(int(acc[4 * q]), int(acc[4 * q + 1]), int(acc[4 * q + 2]), int(acc[4 * q + 3]));
+                }
+                __syncwarp();
+                const int64_t firstRow = int64_t(m0) + quarter * 32;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = 8 * j + (lane >> 2), piece = lane & 3;
+                    if (firstRow + r < p.M) {
+                        const int4 v = *reinterpret_cast<const int4 *>(mine + r * kStageInts + 4 * piece);
+                        *reinterpret_cast<int4 *>(p.out32 + (int64_t(batch) * p.M + firstRow + r) * p.ldOut + col0 + 4 * piece) = v;
+                    }
+                }
+                __syncwarp();
+                continue;
+            }
             if (!rowValid || col0 >= p.N) {
                 continue;
             }
@@ -392,9 +426,11 @@ __device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarrier
 template <int BN, int NSTAGE>
 __device__ __forceinline__ void epilogueWarps(const GemmI8Params &p, PipeBarriers *bars, ColConst *colTab,
                                               uint32_t tmemBase, int warp, int lane, int64_t numTiles, int mTiles,
-                                              int nTiles) {
+                                              int nTiles, int32_t *staging) {
     if (p.out32 != nullptr) {
-        epilogueInt32<BN, NSTAGE>(p, bars, tmemBase, warp, lane, numTiles, mTiles, nTiles);
+        // the staged stores need 16-byte aligned rows
+        const bool staged = staging != nullptr && p.ldOut % 4 == 0 && (reinterpret_cast<uintptr_t>(p.out32) & 15u) == 0;
+        epilogueInt32<BN, NSTAGE>(p, bars, tmemBase, warp, lane, numTiles, mTiles, nTiles, staged ? staging : nullptr);
     } else if (p.epi.hasResidual) {
         epilogueInt8<BN, NSTAGE, true>(p, bars, colTab, tmemBase, warp, lane, numTiles, mTiles, nTiles);
     } else {
@@ -435,7 +471,8 @@ __device__ __forceinline__ void gatherPieces(const int8_t *origin, const int32_t
 // A_MODE: how the A (pixel) operand arrives: kAGather = gathered from the NHWC input described by p, kATiled =
 // tmapA is a plain matrix, kAIm2col = tmapA is an im2col map of the NHWC input and tmapB a {IC, taps, OC} map.
 // B_MN : B is an N-contiguous [K][N] matrix (MN-major operand), otherwise a K-contiguous [N][K] matrix.
-template <int BN, int NSTAGE, int A_MODE, bool B_MN>
+// STAGE32: shared memory for the staged int32 stores of epilogueInt32 is set aside (see there).
+template <int BN, int NSTAGE, int A_MODE, bool B_MN, bool STAGE32 = false>
 __global__ void __launch_bounds__(A_MODE != kAGather ? kThreadsTma : kThreadsGather, 1)
 gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const GemmI8Params p) {
     constexpr bool A_TMA = A_MODE != kAGather;
@@ -452,6 +489,8 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
     int32_t *gatherTab = reinterpret_cast<int32_t *>(
         (reinterpret_cast<uintptr_t>(bars) + sizeof(PipeBarriers) + 15) & ~uintptr_t(15));
     int32_t *tapTab = gatherTab + kMaxGatherPieces; // tap offsets of the segment gather
+    // STAGE32 (TMA variants only: no gather tables): the epilogue warps' staging blocks follow the barriers
+    int32_t *staging = STAGE32 ? gatherTab : nullptr;
     const bool fastGather = !A_TMA && fastGatherApplies(p);
 
     const int warp = threadIdx.x >> 5;
@@ -710,7 +749,7 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
         }
     } else {
         // ---------------- epilogue: warps 0-15 ----------------
-        epilogueWarps<BN, NSTAGE>(p, bars, colTab, tmemBase, warp, lane, numTiles, mTiles, nTiles);
+        epilogueWarps<BN, NSTAGE>(p, bars, colTab, tmemBase, warp, lane, numTiles, mTiles, nTiles, staging);
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -724,15 +763,18 @@ gemmI8Tcgen05(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__
 
 // ---- host side --------------------------------------------------------------------------------------------
 
-template <int BN, int NSTAGE, int A_MODE, bool B_MN>
+template <int BN, int NSTAGE, int A_MODE, bool B_MN, bool STAGE32 = false>
 int launchVariant(const CUtensorMap &mapA, const CUtensorMap &mapB, const GemmI8Params &params, cudaStream_t s) {
+    static_assert(!STAGE32 || A_MODE != kAGather, "the staging blocks take the place of the gather tables");
     GemmI8Params p = params;
     p.divPlane = makeFastDiv(int64_t(p.OH) * p.OW), p.divOW = makeFastDiv(p.OW);
     p.divTiles0 = makeFastDiv((p.N + BN - 1) / BN), p.divTiles1 = makeFastDiv((p.M + BM - 1) / BM);
     constexpr size_t smemBytes =
         size_t(NSTAGE) * (BM * BK + BN * BK) + BN * sizeof(ColConst) + sizeof(PipeBarriers) + 1024 +
-        (A_MODE != kAGather ? 0 : (kMaxGatherPieces + kTapTabEntries) * sizeof(int32_t) + 16);
-    auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_MODE, B_MN>;
+        (A_MODE != kAGather ? 0 : (kMaxGatherPieces + kTapTabEntries) * sizeof(int32_t) + 16) +
+        (STAGE32 ? size_t(kEpilogueWarps) * kStageBytesPerWarp + 16 : 0);
+    static_assert(smemBytes <= 232448, "shared memory per CTA");
+    auto kernel = gemmI8Tcgen05<BN, NSTAGE, A_MODE, B_MN, STAGE32>;
     if (!allowDynamicSmem(reinterpret_cast<const void *>(kernel), smemBytes)) {
         return MLEL_ERROR_DEVICE;
     }
@@ -809,6 +851,10 @@ int gemmI8Launch(const GemmI8Problem &q, cudaStream_t s) {
         return aMode == kATiled    ? launchVariant<64, 8, kATiled, false>(mapA, mapB, p, s)
                : aMode == kAIm2col ? launchVariant<64, 8, kAIm2col, false>(mapA, mapB, p, s)
                                    : launchVariant<64, 8, kAGather, false>(mapA, mapB, p, s);
+    }
+    if (aMode == kATiled && p.out32 != nullptr) {
+        // a matrix product with an int32 result (attention scores): one stage fewer, staged stores
+        return launchVariant<128, 5, kATiled, false, true>(mapA, mapB, p, s);
     }
     return aMode == kATiled    ? launchVariant<128, 6, kATiled, false>(mapA, mapB, p, s)
            : aMode == kAIm2col ? launchVariant<128, 6, kAIm2col, false>(mapA, mapB, p, s)
