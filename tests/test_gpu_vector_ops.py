@@ -216,3 +216,68 @@ def test_fused_mul_rescale(mlel, b_shape, out_dtype, shift, rshift, clamp):
     db = r.integers(-lim, lim, bs, dtype=np.int64).astype(np.int32)
     da.reshape(-1)[:2] = [lim - 1, -lim]
     check_fused(mlel, g, [da, db], ["MUL+RESCALE+CLAMP" if clamp is not None else "MUL+RESCALE"])
+
+
+def _norm_chain(g, r, t32, hidden, out_dtype=np.int8, lut=None):
+    """The layer-norm chain of the BERT-shaped graph on an int32 tensor with the rows along the last axis."""
+    total = g.reduce("REDUCE_SUM", t32, 2)
+    inv = g.inline(np.asarray([(1 << 20) // hidden], np.int32).reshape(1, 1, 1))
+    cen = g.sub(t32, g.mul(total, inv, 20))
+    var = g.mul(g.reduce("REDUCE_SUM", g.mul(cen, cen, 8), 2), inv, 20)
+    rs = g.table(g.rescale(var, [1 << 30], [34], 0, -32768, np.int16), lut if lut is not None else _lut16(r))
+    return g.rescale(g.mul(cen, rs, 12), [1 << 30], [45], 0, 3, out_dtype, True, True), cen, total
+
+
+@pytest.mark.parametrize("shape", [(3, 17, 768), (1, 5, 4), (2, 33, 132), (1, 3, 2048), (4, 8, 64)])
+def test_fused_row_run_layer_norm(mlel, shape):
+    """A residual add with its layer norm as one row-wise node: two int8 inputs, rows of 4 to 2048 elements (a multiple
+    of a warp's 128 or not), the int8 result and, as further outputs, a full-shaped intermediate and the row sums."""
+    r = rng(shape[-1])
+    g = GraphBuilder()
+    a = g.input(np.int8, shape)
+    b = g.input(np.int8, shape)
+    t32 = g.add(g.rescale(a, [1 << 30], [24], -3, 0, np.int32), g.rescale(b, [1 << 30], [24], 5, 0, np.int32))
+    y, cen, total = _norm_chain(g, r, t32, shape[-1])
+    g.output(y)
+    g.output(cen)
+    g.output(total)
+    check_fused(mlel, g, [full_range(r, np.int8, shape), full_range(r, np.int8, shape)], ["ROWS(RESCALE+RESCALE+ADD+REDUCE_SUM"])
+
+
+def test_fused_row_run_with_int8_table_clamp_and_int16(mlel):
+    """TABLE on int8, CLAMP, MIN and MAX reductions, an int16 result, a constant operand of one element and a
+    row-shaped input from outside the run."""
+    r = rng(77)
+    shape = (2, 21, 96)
+    g = GraphBuilder()
+    x = g.input(np.int8, shape)
+    bias = g.input(np.int32, shape[:-1] + (1,))
+    t = g.clamp(g.table(x, r.integers(-128, 128, (256,), dtype=np.int64).astype(np.int8)), -100, 90)
+    v = g.rescale(t, [1 << 30], [20], 0, 0, np.int32)
+    lo, hi = g.reduce("REDUCE_MIN", v, 2), g.reduce("REDUCE_MAX", v, 2)
+    span = g.add(g.sub(hi, lo), g.inline(np.asarray([1], np.int32).reshape(1, 1, 1)))
+    w = g.add(g.sub(v, lo), bias)
+    g.output(g.rescale(g.mul(w, span, 3), [int(r.integers(1 << 30, (1 << 31) - 1))], [33], 0, -7, np.int16, True, True))
+    g.output(span)
+    data = [full_range(r, np.int8, shape), r.integers(-5000, 5000, shape[:-1] + (1,), dtype=np.int64).astype(np.int32)]
+    check_fused(mlel, g, data, ["ROWS(TABLE+CLAMP+RESCALE+REDUCE_MIN+REDUCE_MAX"])
+
+
+def test_row_run_is_left_alone_when_it_does_not_pay(mlel):
+    """A softmax's nine operators: the row kernel would cost more than the two smaller fused nodes."""
+    r = rng(5)
+    shape = (6, 12, 64)
+    g = GraphBuilder()
+    x = g.input(np.int32, shape)
+    d16 = g.rescale(g.sub(x, g.reduce("REDUCE_MAX", x, 2)), [1 << 30], [33], 0, 0, np.int16)
+    e = g.table(d16, _lut16(r))
+    den = g.table(g.rescale(g.reduce("REDUCE_SUM", e, 2), [1 << 30], [40], 0, -32768, np.int16), _lut16(r))
+    g.output(g.rescale(g.mul(e, den, 22), [1 << 30], [37], 0, -128, np.int8))
+    from mlel_b200.runtime import GraphRunner
+    runner = GraphRunner(g)
+    names = runner.pipeline.exec_names()
+    assert not any(n.startswith("ROWS") for n in names), names
+    assert "REDUCE_MAX+SUB+RESCALE+TABLE+REDUCE_SUM" in names and "MUL+RESCALE" in names
+    data = [r.integers(-(1 << 20), 1 << 20, shape, dtype=np.int64).astype(np.int32)]
+    for a, b in zip(runner.run(data), evaluate(g, data)):
+        assert np.array_equal(a, b)
