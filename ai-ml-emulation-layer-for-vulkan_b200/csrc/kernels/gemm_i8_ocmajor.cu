@@ -62,8 +62,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
     uint8_t *tilesX = smem + NSTAGE * kTileW;
     uint8_t *cdTiles = smem + NSTAGE * (kTileW + kTileX);
     uint8_t *resTab = cdTiles + 2 * kTileCd; // the residual tail as a table (RESIDUAL only)
-    uint8_t *clsTab = resTab + (RESIDUAL ? kResidualTableBytes : 0);
-    int32_t *tapTab = reinterpret_cast<int32_t *>(clsTab + 2 * BNP);
+    int32_t *tapTab = reinterpret_cast<int32_t *>(resTab + (RESIDUAL ? kResidualTableBytes : 0));
     OcBarriers *bars = reinterpret_cast<OcBarriers *>(tapTab + kTapTabEntries);
 
     constexpr bool X_TMA = X_MODE != kXGather;
@@ -306,7 +305,7 @@ gemmI8OcMajor(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__
         // ---------------- epilogue ----------------
         EpiWalk walk{};
         walk.first = blockIdx.x, walk.stride = gridDim.x;
-        epilogueOcMajor<BNP, EW, RESIDUAL, kOcTile, X_TMA>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase, warp, lane,
+        epilogueOcMajor<BNP, EW, RESIDUAL, kOcTile, X_TMA>(&tmapD, p, bars, resTab, cdTiles, tmemBase, warp, lane,
                                                            numTiles, pTiles, cTiles, walk);
     }
 
@@ -331,7 +330,7 @@ int launchOcMajor(const OcMaps &maps, const GemmI8Params &params, cudaStream_t s
     p.divTiles0 = makeFastDiv(p.channelFastest != 0 ? channelTiles : pixelTiles);
     p.divTiles1 = makeFastDiv(p.channelFastest != 0 ? pixelTiles : channelTiles);
     constexpr size_t smemBytes = size_t(NSTAGE) * (kOcTile * BK + BNP * BK) + 2 * size_t(BNP) * 128 +
-                                 (RESIDUAL ? size_t(kResidualTableBytes) : 0) + 2 * BNP +
+                                 (RESIDUAL ? size_t(kResidualTableBytes) : 0) +
                                  kTapTabEntries * sizeof(int32_t) + sizeof(OcBarriers) + 1024;
     static_assert(smemBytes <= 232448, "shared memory per CTA");
     auto kernel = gemmI8OcMajor<BNP, NSTAGE, EW, X_MODE, RESIDUAL>;

@@ -200,8 +200,7 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
     uint8_t *tilesX = smem + NSTAGE * kTileW;
     uint8_t *cdTiles = smem + NSTAGE * (kTileW + kTileX);
     uint8_t *resTab = cdTiles + 2 * kTileCd;
-    uint8_t *clsTab = resTab + (RESIDUAL ? kResidualTableBytes : 0);
-    OcBarriers *bars = reinterpret_cast<OcBarriers *>(clsTab + 2 * BNP);
+    OcBarriers *bars = reinterpret_cast<OcBarriers *>(resTab + (RESIDUAL ? kResidualTableBytes : 0));
 
     static_assert(NSTAGE <= 6, "OcBarriers holds six stages");
     static_assert(BK / UMMA_K == 4, "the MMA loop issues four instructions per K block");
@@ -420,7 +419,7 @@ gemmI8Pair(const __grid_constant__ CUtensorMap tmapX, const __grid_constant__ CU
         walk.cOffset = int(rank) * kOcTile;
         walk.accEmpty[0] = mapToCta(smemAddr(&bars->accEmpty[0]), 0u);
         walk.accEmpty[1] = mapToCta(smemAddr(&bars->accEmpty[1]), 0u);
-        epilogueOcMajor<BNP, EW, RESIDUAL, kPairChannels, true>(&tmapD, p, bars, clsTab, resTab, cdTiles, tmemBase,
+        epilogueOcMajor<BNP, EW, RESIDUAL, kPairChannels, true>(&tmapD, p, bars, resTab, cdTiles, tmemBase,
                                                                 warp - kFirstEpiWarp, lane, numTiles, pTiles, cTiles, walk);
     }
 
@@ -444,7 +443,7 @@ int launchPair(const PairMaps &maps, const GemmI8Params &params, cudaStream_t s)
     p.divPlane = makeFastDiv(int64_t(p.OH) * p.OW), p.divOW = makeFastDiv(p.OW);
     p.divTiles0 = makeFastDiv((p.M + BNP - 1) / BNP), p.divTiles1 = makeFastDiv((p.N + kPairChannels - 1) / kPairChannels);
     constexpr size_t smemBytes = size_t(NSTAGE) * (kOcTile * BK + (BNP / 2) * BK) + 2 * size_t(BNP) * 128 +
-                                 (RESIDUAL ? size_t(kResidualTableBytes) : 0) + 2 * BNP + sizeof(OcBarriers) + 1024;
+                                 (RESIDUAL ? size_t(kResidualTableBytes) : 0) + sizeof(OcBarriers) + 1024;
     static_assert(smemBytes <= 232448, "shared memory per CTA");
     auto kernel = gemmI8Pair<BNP, NSTAGE, EW, X_MODE, W_MN, RESIDUAL>;
     if (!allowDynamicSmem(reinterpret_cast<const void *>(kernel), smemBytes)) {

@@ -236,11 +236,10 @@ __device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr) {
 // current one is rescaled.  C_TILE: output channels per tile (128, or 256 for a pair of CTAs).
 template <int BNP, int EW, bool RESIDUAL, int C_TILE, bool STORE_WARP = false>
 __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const GemmI8Params &p, OcBarriers *bars,
-                                                uint8_t *clsTab, const uint8_t *resTab, uint8_t *cdTiles,
+                                                const uint8_t *resTab, uint8_t *cdTiles,
                                                 uint32_t tmemBase, int warp, int lane, int64_t numTiles, int pTiles,
                                                 int cTiles, const EpiWalk &walk) {
     constexpr bool PAIR = C_TILE != kOcTile;
-    const int epiThread = warp * 32 + lane; // index among the epilogue threads (`warp` counts from the first of them)
     const auto accDrained = [&](uint32_t buf) {
         if (PAIR) {
             mbarArriveCluster(walk.accEmpty[buf]);
@@ -254,7 +253,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
     constexpr int kSteps = kColsPerWarp / 16;
     static_assert(EW % 4 == 0 && kColsPerWarp * (EW / 4) == BNP && kColsPerWarp % 16 == 0, "pixel shares of the warps");
     static_assert(kSteps % 2 == 0, "slices are processed in pairs");
-    static_assert(EW * 32 >= BNP, "one thread per pixel fills the class table");
+    static_assert(kColsPerWarp % 32 == 0, "a lane holds the classes of whole pixels of its warp's share");
     EpiConsts k{};
     k.outZpMain = p.epi.main.outZp, k.loMain = p.epi.main.lo, k.hiMain = p.epi.main.hi;
     // row of the lowest main-stage value: the element loop counts rows from there
@@ -303,21 +302,23 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             curC0 = c0;
             curBatch = batch;
         }
-        uint8_t *cls = clsTab + buf * BNP;
+        // Border class of every pixel of this warp's share of the tile, in registers: lane l holds the classes of the
+        // share's pixels l, l + 32, ...  (A table in shared memory for all warps needed a barrier among the epilogue
+        // warps in every tile.)
+        constexpr int kClassRegs = kColsPerWarp / 32;
+        int clsReg[kClassRegs];
         if (hasClasses) {
-            // border class of every pixel of the tile; the table alternates with the accumulator, so a warp that
-            // is a tile ahead never overwrites what a slower warp still reads
-            if (epiThread < BNP) {
-                const int64_t m = int64_t(m0) + epiThread;
+#pragma unroll
+            for (int q = 0; q < kClassRegs; ++q) {
+                const int64_t m = int64_t(m0) + part * kColsPerWarp + q * 32 + lane;
                 int c = baseClass;
                 if (m < p.M) {
                     const uint32_t rem = uint32_t(m) - fastDiv(uint32_t(m), p.divPlane) * p.divPlane.d; // pixel inside its image
                     const uint32_t oy = fastDiv(rem, p.divOW);
                     c = int(__ldg(p.rowClass + oy)) * p.numColClasses + int(__ldg(p.colClass + (rem - oy * uint32_t(p.OW))));
                 }
-                cls[epiThread] = uint8_t(c);
+                clsReg[q] = c;
             }
-            ocEpilogueSync<EW>();
         }
         if (!tableReady) {
             if (!mbarWait(&bars->tabFull, 0u, 7)) {
@@ -339,18 +340,25 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         // this thread's column of the C/D tile, at the first pixel of its half
         const uint32_t cd = smemAddr(cdTiles + buf * (BNP * 128) + (part * kColsPerWarp) * 128 + quarter * 32 + lane);
         const auto borderFix = [&](uint32_t (&acc)[16], int col) {
-            // pixels of this slice whose window crosses the border take their own class's correction
-            const uint32_t borderMask = __ballot_sync(0xffffffffu, lane < 16 && int(cls[col + (lane & 15)]) != baseClass);
-            if (borderMask != 0 && ocValid) {
+            // pixels of this slice (col .. col + 15 of the warp's share) whose window crosses the border take their own
+            // class's correction; their classes sit in lanes col % 32 .. of register col / 32
+            int mine = clsReg[0];
+#pragma unroll
+            for (int q = 1; q < kClassRegs; ++q) {
+                mine = (col >> 5) == q ? clsReg[q] : mine;
+            }
+            const uint32_t borderMask = (__ballot_sync(0xffffffffu, mine != baseClass) >> (col & 31)) & 0xffffu;
+            if (borderMask != 0) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     if ((borderMask >> j) & 1u) {
-                        const int c = int(cls[col + j]);
-                        acc[j] += uint32_t(__ldg(corrBatch + int64_t(c) * p.N + oc)) - uint32_t(k.corr0);
+                        const int c = __shfl_sync(0xffffffffu, mine, (col & 31) + j);
+                        if (ocValid) {
+                            acc[j] += uint32_t(__ldg(corrBatch + int64_t(c) * p.N + oc)) - uint32_t(k.corr0);
+                        }
                     }
                 }
             }
-            __syncwarp();
         };
         uint32_t accA[16], accB[16];
         // With 12 epilogue warps a thread has 128 registers, which the residual variant's shortcut bytes and a
@@ -368,7 +376,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                     }
                 }
                 if (hasClasses) {
-                    borderFix(accA, part * kColsPerWarp + 16 * st);
+                    borderFix(accA, 16 * st);
                 }
                 if (warpLive) {
                     rescaleSlice<RESIDUAL>(accA, k, tab128, cd + uint32_t((16 * st) * 128));
@@ -381,7 +389,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             tmemWait16(accA);
             tmemLoad16(taddr + uint32_t(16 * (st + 1)), accB);
             if (hasClasses) {
-                borderFix(accA, part * kColsPerWarp + 16 * st);
+                borderFix(accA, 16 * st);
             }
             if (warpLive) {
                 rescaleSlice<RESIDUAL>(accA, k, tab128, cd + uint32_t((16 * st) * 128));
@@ -397,7 +405,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
                 }
             }
             if (hasClasses) {
-                borderFix(accB, part * kColsPerWarp + 16 * (st + 1));
+                borderFix(accB, 16 * (st + 1));
             }
             if (warpLive) {
                 rescaleSlice<RESIDUAL>(accB, k, tab128, cd + uint32_t((16 * (st + 1)) * 128));
