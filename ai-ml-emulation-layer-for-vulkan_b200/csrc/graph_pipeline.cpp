@@ -1597,11 +1597,15 @@ void GraphPipeline::prepareTensorCore() {
                 // With corrections this small, accumulator + correction - zero point cannot leave int32 (the raw sum
                 // of at most 65536 products is at most 2^30 in size): the epilogue may then fold the three terms into
                 // one 32-bit addition without changing the reference's 64-bit arithmetic.
-                bool small = true;
+                // Level 2: the three terms together stay below 2^29 in size (a product is at most 2^14), which the
+                // epilogue's RESCALE from 32-bit words asks for.
+                bool small = true, tiny = true;
+                const int64_t rawBound = KH * KW * IC * (int64_t(1) << 14) + 256;
                 for (const int32_t c : corr) {
                     small = small && c >= -((1 << 30) - 256) && c <= (1 << 30) - 256;
+                    tiny = tiny && (c < 0 ? -int64_t(c) : int64_t(c)) + rawBound < (int64_t(1) << 29);
                 }
-                op.auxi[4] = small ? 1 : 0;
+                op.auxi[4] = tiny ? 2 : (small ? 1 : 0);
             }
             op.aux[0] = addDerivedConstant(MLEL_I32, {int64_t(corr.size())}, corr.data());
             op.aux[1] = addDerivedConstant(MLEL_U8, {OH}, rowCls.data());

@@ -277,4 +277,14 @@ __device__ __forceinline__ int32_t scaleHigh(int32_t x, int32_t mult, uint64_t r
     return int32_t(uint32_t(sum >> 32));
 }
 
+// The same RESCALE from 32-bit words only, for shifts of 32 to 60 and |x| < 2^29 (x = value - input zero point).
+// Four times the sum is (4x) * mult + 2^(shift+1) +- 2^32: both rounding terms are whole units of the product's high
+// word, and what the low word holds cannot change floor(sum / 2^shift) = (high + 2^(shift-31) +- 1) >> (shift - 30).
+// x4 = 4x; c32 = 2^(shift-31), plus 1 with double rounding.  SIGNED: double rounding with the sign of x looked at
+// (-1 instead of +1 for x < 0); callers leave it out where every x < 0 ends at the lower clamp bound either way.
+template <bool SIGNED> __device__ __forceinline__ int32_t scaleHigh32(int32_t x4, int32_t mult, int32_t c32) {
+    const int32_t t = __mulhi(x4, mult) + c32;
+    return SIGNED ? t + ((x4 >> 31) << 1) : t;
+}
+
 } // namespace mlel

@@ -588,7 +588,7 @@ int gemmI8PairLaunch(const GemmI8Problem &q, cudaStream_t s, bool *taken) {
     *taken = true;
     g_tensorCoreLaunches[2].fetch_add(1, std::memory_order_relaxed);
     if (width == 256) {
-        return launchPairShape<256, 4, 3, 8>(maps, p, xMode, q.bMnMajor, s);
+        return launchPairShape<256, 4, 3, 16>(maps, p, xMode, q.bMnMajor, s);
     }
     return width == 192 ? launchPairShape<192, 5, 4, 12>(maps, p, xMode, q.bMnMajor, s)
                         : launchPairShape<128, 6, 4, 8>(maps, p, xMode, q.bMnMajor, s);

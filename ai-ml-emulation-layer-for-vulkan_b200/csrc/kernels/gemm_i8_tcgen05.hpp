@@ -58,7 +58,8 @@ struct GemmI8Params {
     const uint8_t *colClass; // [OW]
     int32_t numColClasses, numClasses, batchedCorr;
     int32_t baseClass;       // the most common class: its correction row is staged in shared memory
-    int32_t corrSmall;       // every |corr| <= 2^30 - 256: accumulator + correction - zero point stays inside int32
+    int32_t corrSmall;       // 1: every |corr| <= 2^30 - 256: accumulator + correction - zero point stays inside int32;
+                             // 2: it even stays below 2^29 in size
     // outputs: exactly one of out32 / out8 is set
     int32_t *out32;
     int8_t *out8;

@@ -153,12 +153,15 @@ struct EpiConsts {
     int32_t corrX;   // corr0 - input zero point: accumulator + corrX is x of scaleHigh
     int32_t outZpMain, loMain, hiMain;
     bool fast; // the shift is at least 32 and the corrections are small: see scaleHigh
+    // 0: the 64-bit forms above; 1: scaleHigh32 with the sign of x; 2: scaleHigh32 without it
+    int words32;
+    int32_t corrX4, c32, shift32; // scaleHigh32: 4 * corrX, rounding units, shift - 30
 };
 
 // 16 pixels of one channel: accumulator slice -> bytes in the C/D tile (column `cd`, rows 128 bytes apart).
 // All shortcut bytes are read before the first result is written: the compiler must assume that a byte store
 // may alias any later load, and 16 load-compute-store chains in a row would run one after the other.
-template <bool RESIDUAL, bool FAST>
+template <bool RESIDUAL, bool FAST, int WORDS32 = 0>
 __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t tab128,
                                                  uint32_t cd) {
     constexpr int CH = 8; // pixels per group: enough independent chains, few enough live registers
@@ -174,7 +177,15 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
         int32_t r[CH];
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
-            if (FAST) {
+            if (WORDS32 != 0) {
+                const int32_t x4 = int32_t(acc[g + j] * 4u + uint32_t(k.corrX4));
+                const int32_t q = scaleHigh32<WORDS32 == 1>(x4, k.fm.mult, k.c32) >> k.shift32;
+                if (RESIDUAL) {
+                    r[j] = __viaddmin_s32_relu(q, k.outZpMain - k.loMain, k.hiMain - k.loMain);
+                } else {
+                    r[j] = min(__viaddmax_s32(q, k.outZpMain, k.loMain), k.hiMain);
+                }
+            } else if (FAST) {
                 const int32_t x = int32_t(acc[g + j] + uint32_t(k.corrX));
                 const int32_t high = scaleHigh(x, k.fm.mult, k.rnM, k.bumpM);
                 if (RESIDUAL) {
@@ -208,7 +219,11 @@ __device__ __forceinline__ void rescaleSliceImpl(const uint32_t (&acc)[16], cons
 // of the residual table's row for the lowest main-stage value.
 template <bool RESIDUAL>
 __device__ __forceinline__ void rescaleSlice(const uint32_t (&acc)[16], const EpiConsts &k, uint32_t tab128, uint32_t cd) {
-    if (k.fast) {
+    if (k.words32 == 2) {
+        rescaleSliceImpl<RESIDUAL, true, 2>(acc, k, tab128, cd);
+    } else if (k.words32 == 1) {
+        rescaleSliceImpl<RESIDUAL, true, 1>(acc, k, tab128, cd);
+    } else if (k.fast) {
         rescaleSliceImpl<RESIDUAL, true>(acc, k, tab128, cd);
     } else {
         rescaleSliceImpl<RESIDUAL, false>(acc, k, tab128, cd);
@@ -299,6 +314,17 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             k.rnM = (uint64_t(1) << ((shiftM > 0 ? shiftM : 1) - 1)) - (twoRounds ? (uint64_t(1) << 30) : 0);
             k.bumpM = twoRounds ? 0x80000000u : 0u;
             k.fast = __all_sync(0xffffffffu, k.fm.s1 == 32) && p.corrSmall != 0;
+            // 32-bit words only: every lane's shift is 32..60 and the host has bounded |x| below 2^29.  The sign of x is
+            // left out without double rounding, and where every x < 0 ends at the lower clamp bound whichever way it was
+            // rounded (no negative multiplier, bound not below the output zero point).
+            k.words32 = 0;
+            if (p.corrSmall >= 2 && __all_sync(0xffffffffu, shiftM >= 32 && shiftM <= 60)) {
+                const bool signFree = !twoRounds || (k.loMain >= k.outZpMain && __all_sync(0xffffffffu, k.fm.mult >= 0));
+                k.words32 = signFree ? 2 : 1;
+                k.corrX4 = int32_t(uint32_t(k.corrX) * 4u);
+                k.c32 = (shiftM >= 32 ? int32_t(1) << ((shiftM - 31) & 31) : 0) + (twoRounds ? 1 : 0);
+                k.shift32 = shiftM - 30;
+            }
             curC0 = c0;
             curBatch = batch;
         }
@@ -363,7 +389,7 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
         uint32_t accA[16], accB[16];
         // With 12 epilogue warps a thread has 128 registers, which the residual variant's shortcut bytes and a
         // second accumulator slice in flight do not both fit into.
-        constexpr bool kOneSliceAtATime = RESIDUAL && EW > 8;
+        constexpr bool kOneSliceAtATime = (RESIDUAL && EW > 8) || EW > 12;
         if (kOneSliceAtATime) {
 #pragma unroll 1
             for (int st = 0; st < kSteps; ++st) {

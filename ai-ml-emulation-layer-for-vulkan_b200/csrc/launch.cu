@@ -205,7 +205,11 @@ int launchMatmulTensorCore(const OpDesc &op, const TView *T, cudaStream_t s) {
     p.batchedCorr = 1;
     // |correction| = |zero point of A| * |column sum of B| <= 128 * K * |zp|: small enough for the short RESCALE form
     // whenever that bound is (see GemmI8Params::corrSmall)
-    p.corrSmall = int64_t(op.i[0] < 0 ? -op.i[0] : op.i[0]) * p.K * 128 <= (int64_t(1) << 30) - 256;
+    {
+        const int64_t corrBound = int64_t(op.i[0] < 0 ? -op.i[0] : op.i[0]) * p.K * 128;
+        const bool tiny = corrBound + int64_t(p.K) * (int64_t(1) << 14) + 256 < (int64_t(1) << 29);
+        p.corrSmall = tiny ? 2 : (corrBound <= (int64_t(1) << 30) - 256 ? 1 : 0);
+    }
     if (op.kind == OP_FUSED_MATMUL) {
         p.out8 = reinterpret_cast<int8_t *>(out.ptr);
         p.epi = devEpilogue(op.epi, T);

@@ -239,7 +239,8 @@ struct OpDesc {
     // Tensor-core path (set by GraphPipeline::prepareTensorCore when the node qualifies):
     //   CONV2D kinds: aux[0] correction table int32 [classes][OC], aux[1] row classes u8 [OH],
     //                 aux[2] column classes u8 [OW]; auxi[0] = number of column classes, auxi[1] = classes,
-    //                 auxi[3] = the most common class, auxi[4] = 1 when every correction is below 2^30 - 256 in size
+    //                 auxi[3] = the most common class, auxi[4] = 1 when every correction is below 2^30 - 256 in size,
+    //                 2 when correction + raw sum stay below 2^29
     //                 with a fused residual tail and tc == 1: aux[3] = the tail as a table of 256 x 256 bytes
     //   MATMUL kinds with a constant second input: aux[0] correction int32 [batches][W],
     //                 aux[3] the second input transposed to [batches][W][C]

@@ -157,6 +157,46 @@ def test_conv2d_channel_major_bias_range_and_rounding(mlel, bias_bits, double_ro
         check(mlel, g, [data])
 
 
+@pytest.mark.parametrize("clamp", [None, (-9, 127), (-3, 100), (-20, 127)])
+@pytest.mark.parametrize("double_round", [False, True])
+def test_conv2d_rescale_from_32_bit_words(mlel, double_round, clamp):
+    """Small corrections and shifts of 32 to 60 in all 32 channels of an epilogue warp take the RESCALE form that
+    only uses the high word of (4x) * multiplier; with a lower clamp bound at or above the output zero point it also
+    drops the sign of x from the double rounding.  Groups of 32 channels: shifts at both ends of the range, shifts
+    outside it (those warps take the 64-bit form), negative, tiny and zero multipliers; accumulators of both signs
+    and of zero (bias 0, zero weights)."""
+    r = rng(40 + double_round + (0 if clamp is None else clamp[0] + clamp[1]))
+    oc = 288
+    for k, pad in ((1, 0), (3, 1)):
+        g = GraphBuilder()
+        x = g.input(np.int8, (3, 12, 12, 64))
+        w = r.integers(-128, 128, (oc, k, k, 64), dtype=np.int8)
+        w[40:44] = 0
+        bias = r.integers(-(1 << 16), 1 << 16, (oc,), dtype=np.int32)
+        bias[40:42] = 0
+        y = g.conv2d(x, g.constant(w), g.constant(bias), [pad] * 4, [1, 1], [1, 1], -5, 0)
+        mult = r.integers(1 << 30, (1 << 31) - 1, (oc,), dtype=np.int64).astype(np.int32)
+        shift = r.integers(32, 47, (oc,), dtype=np.int8)
+        shift[32:64] = 32
+        shift[64:96] = r.integers(55, 61, (32,))
+        shift[64:66] = 60
+        shift[96:128] = r.integers(30, 64, (32,))    # a warp with shifts outside 32..60
+        mult[128:160] = -mult[128:160]               # negative multipliers: the sign of x stays
+        mult[160:192] = r.integers(0, 1 << 20, (32,))
+        mult[160:163] = [0, 1, 2]
+        shift[160:192] = r.integers(32, 40, (32,))
+        shift[192:224] = 33
+        mult[192:224] = (1 << 31) - 1
+        shift[224:256] = 61                          # just past the range
+        y = g.rescale(y, mult, shift, 0, -9, np.int8, True, double_round, True)
+        if clamp is not None:
+            y = g.clamp(y, clamp[0], clamp[1])
+        g.output(y)
+        data = r.integers(-128, 128, (3, 12, 12, 64), dtype=np.int8)
+        data[0, :3] = -5  # x - zero point = 0: accumulators of exactly the bias
+        check(mlel, g, [data])
+
+
 def test_conv2d_int16_int64(mlel):
     r = rng(2)
     g = GraphBuilder()
