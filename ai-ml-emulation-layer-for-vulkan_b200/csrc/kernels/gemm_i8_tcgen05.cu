@@ -65,7 +65,8 @@ struct __align__(8) PipeBarriers {
 // element, by shared address.  A table is built in one of two forms.  General: {mult, corr0, rnLo, rnHi} with the
 // rounding constant for v < zpIn (input zero point folded in).  High-word form, when every shift of the table is
 // at least 32 and the corrections are small (see scaleHigh): {mult, corr0 - zpIn, rnM} with the rounding constant
-// without the zero-point fold.
+// without the zero-point fold.  32-bit form, when in addition every shift is at most 60 and the host has bounded
+// |x| below 2^29 (see scaleHigh32): {mult, 4 * (corr0 - zpIn), rounding units, shift - 30} -- one read per element.
 struct __align__(16) ColConst {
     int32_t mult;
     int32_t corr;        // general: correction of the most common border class; high-word form: that minus zpIn
@@ -132,8 +133,10 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
     }
     const int32_t zpMain = p.epi.main.inZp, outZpMain = p.epi.main.outZp;
     const uint32_t tabAddr = smemAddr(colTab);
-    volatile uint32_t *fastFlag = &bars->pad; // 1: every column of the table has a shift of at least 32
-    bool fast = false, high = false; // forms of the table: see ColConst
+    // what holds for every column of the table -- bit 0: a shift of at least 32; bit 1: a shift of 32..60; bit 2: no
+    // negative multiplier
+    volatile uint32_t *fastFlag = &bars->pad;
+    bool fast = false, high = false, words32 = false, signFree = false; // forms of the table: see ColConst
     const uint32_t bumpMask = p.epi.main.doubleRound != 0 ? 0x80000000u : 0u;
     const int32_t loMain = p.epi.main.lo, hiMain = p.epi.main.hi;
     uint32_t tileCount = 0;
@@ -151,7 +154,7 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
         if (n0 != tabN0 || (p.batchedCorr && batch != tabBatch)) {
             epilogueSync(); // everyone is done with the previous table
             if (threadIdx.x == 0) {
-                *fastFlag = 1;
+                *fastFlag = 7;
             }
             epilogueSync();
             FastRescale f{};
@@ -161,19 +164,31 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                 const int ci = (p.epi.main.perChannel && col < p.N) ? col : 0;
                 f = makeFastRescale(__ldg(p.epi.main.mult + ci), int32_t(__ldg(p.epi.main.shift + ci)), zpMain,
                                     p.epi.main.doubleRound != 0);
-                if (f.s1 != 32) {
-                    *fastFlag = 0; // a shift below 32 in this tile: the low word of the product matters
+                const int shift = f.s1 + f.s2;
+                // (a shift below 32 in this tile: the low word of the product matters)
+                const uint32_t fails = (f.s1 != 32 ? 1u : 0u) | ((shift < 32 || shift > 60) ? 2u : 0u) | (f.mult < 0 ? 4u : 0u);
+                if (fails != 0) {
+                    atomicAnd(const_cast<uint32_t *>(fastFlag), ~fails);
                 }
                 corr0 = col < p.N ? __ldg(corrBatch + int64_t(p.baseClass) * p.N + col) : 0;
             }
             epilogueSync();
-            fast = *fastFlag != 0;
+            const uint32_t holds = *fastFlag;
+            fast = (holds & 1u) != 0;
             high = fast && p.corrSmall != 0 && !RESIDUAL;
+            words32 = high && p.corrSmall >= 2 && (holds & 2u) != 0;
+            // the sign of x only matters to double rounding, and not where every x < 0 ends at the lower clamp bound
+            signFree = p.epi.main.doubleRound == 0 || (loMain >= outZpMain && (holds & 4u) != 0);
             if (threadIdx.x < BN) {
                 ColConst c;
                 c.mult = f.mult, c.s1 = f.s1, c.s2 = f.s2, c.corr0 = corr0;
                 c.bump = f.rpLo - f.rnLo; // (rp - rn) mod 2^32: 0 or 2^31
-                if (high) {
+                if (words32) {
+                    const int shift = f.s1 + f.s2;
+                    c.corr = int32_t((uint32_t(corr0) - uint32_t(f.zpIn)) * 4u);
+                    c.rnLo = (1u << ((shift - 31) & 31)) + (p.epi.main.doubleRound != 0 ? 1u : 0u);
+                    c.rnHi = uint32_t(shift - 30);
+                } else if (high) {
                     const bool twoRounds = p.epi.main.doubleRound != 0;
                     const uint64_t rn = (uint64_t(1) << (f.s1 + f.s2 - 1)) - (twoRounds ? (uint64_t(1) << 30) : 0);
                     c.corr = int32_t(uint32_t(corr0) - uint32_t(f.zpIn));
@@ -248,7 +263,23 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
                 }
             }
             uint32_t packed[4];
-            if (!RESIDUAL && high) {
+            if (!RESIDUAL && words32) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    int32_t y[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = 4 * q + e;
+                        uint32_t mult, corrX4, c32, shift32;
+                        ldsV4(tabAddr + uint32_t(cl + j) * 32u, mult, corrX4, c32, shift32);
+                        const int32_t x4 = int32_t(acc[j] * 4u + corrX4);
+                        const int32_t h = signFree ? scaleHigh32<false>(x4, int32_t(mult), int32_t(c32))
+                                                   : scaleHigh32<true>(x4, int32_t(mult), int32_t(c32));
+                        y[e] = min(__viaddmax_s32(h >> shift32, outZpMain, loMain), hiMain);
+                    }
+                    packed[q] = pack4(y[0], y[1], y[2], y[3]);
+                }
+            } else if (!RESIDUAL && high) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     int32_t y[4];

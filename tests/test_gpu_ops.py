@@ -197,6 +197,41 @@ def test_conv2d_rescale_from_32_bit_words(mlel, double_round, clamp):
         check(mlel, g, [data])
 
 
+@pytest.mark.parametrize("clamp", [None, (-9, 127), (-20, 100)])
+@pytest.mark.parametrize("double_round", [False, True])
+@pytest.mark.parametrize("odd_one", [None, "shift 61", "shift 31", "negative multiplier"])
+def test_conv2d_64_channels_rescale_from_32_bit_words(mlel, odd_one, double_round, clamp):
+    """The same form in the pixel-major kernel (at most 64 output channels), where all columns of a tile share one
+    form of the constants table: every shift in 32..60, or one column just outside the range, or one negative
+    multiplier (which keeps the sign of x in the double rounding)."""
+    r = rng(70 + double_round + (0 if clamp is None else clamp[0]) + (0 if odd_one is None else len(odd_one)))
+    for oc, k, pad in ((64, 1, 0), (48, 3, 1)):
+        g = GraphBuilder()
+        x = g.input(np.int8, (2, 13, 13, 32))
+        w = r.integers(-128, 128, (oc, k, k, 32), dtype=np.int8)
+        w[7] = 0
+        bias = r.integers(-(1 << 16), 1 << 16, (oc,), dtype=np.int32)
+        bias[7] = 0
+        y = g.conv2d(x, g.constant(w), g.constant(bias), [pad] * 4, [1, 1], [1, 1], -5, 0)
+        mult = r.integers(1 << 30, (1 << 31) - 1, (oc,), dtype=np.int64).astype(np.int32)
+        mult[:3] = [0, 1, (1 << 31) - 1]
+        shift = r.integers(32, 61, (oc,), dtype=np.int8)
+        shift[3:6] = [32, 33, 60]
+        if odd_one == "shift 61":
+            shift[20] = 61
+        elif odd_one == "shift 31":
+            shift[20] = 31
+        elif odd_one == "negative multiplier":
+            mult[20] = -mult[20]
+        y = g.rescale(y, mult, shift, 0, -9, np.int8, True, double_round, True)
+        if clamp is not None:
+            y = g.clamp(y, clamp[0], clamp[1])
+        g.output(y)
+        data = r.integers(-128, 128, (2, 13, 13, 32), dtype=np.int8)
+        data[0, :3] = -5
+        check(mlel, g, [data])
+
+
 def test_conv2d_int16_int64(mlel):
     r = rng(2)
     g = GraphBuilder()
