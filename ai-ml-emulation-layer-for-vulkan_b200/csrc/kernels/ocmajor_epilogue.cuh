@@ -387,9 +387,9 @@ __device__ __forceinline__ void epilogueOcMajor(const CUtensorMap *tmapD, const 
             }
         };
         uint32_t accA[16], accB[16];
-        // With 12 epilogue warps a thread has 128 registers, which the residual variant's shortcut bytes and a
-        // second accumulator slice in flight do not both fit into.
-        constexpr bool kOneSliceAtATime = (RESIDUAL && EW > 8) || EW > 12;
+        // With sixteen epilogue warps a thread has about a hundred registers: too few for a second accumulator slice
+        // in flight.
+        constexpr bool kOneSliceAtATime = EW > 12;
         if (kOneSliceAtATime) {
 #pragma unroll 1
             for (int st = 0; st < kSteps; ++st) {
