@@ -115,6 +115,26 @@ __device__ __forceinline__ uint32_t pack4(int32_t e0, int32_t e1, int32_t e2, in
 
 // The epilogue of the persistent kernel (warps 0-15).  Each warp owns 32 TMEM lanes (tile rows) and a quarter
 // of the tile's columns, which it walks in 16-column steps: one tcgen05.ld, 16 RESCALEs, one 16-byte store.
+// 16 columns of one row in the 32-bit form of the constants table (see ColConst), packed four results to a word.
+template <bool SIGNED>
+__device__ __forceinline__ void rescale16Words32(const uint32_t (&acc)[16], uint32_t tabAddr, int32_t outZp, int32_t lo,
+                                                 int32_t hi, uint32_t (&packed)[4]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        int32_t y[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int j = 4 * q + e;
+            uint32_t mult, corrX4, c32, shift32;
+            ldsV4(tabAddr + uint32_t(j) * 32u, mult, corrX4, c32, shift32);
+            const int32_t x4 = int32_t(acc[j] * 4u + corrX4);
+            const int32_t h = scaleHigh32<SIGNED>(x4, int32_t(mult), int32_t(c32));
+            y[e] = min(__viaddmax_s32(h >> shift32, outZp, lo), hi);
+        }
+        packed[q] = pack4(y[0], y[1], y[2], y[3]);
+    }
+}
+
 template <int BN, int NSTAGE, bool RESIDUAL>
 __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers *bars, ColConst *colTab,
                                              uint32_t tmemBase, int warp, int lane, int64_t numTiles, int mTiles,
@@ -264,20 +284,12 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
             }
             uint32_t packed[4];
             if (!RESIDUAL && words32) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    int32_t y[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int j = 4 * q + e;
-                        uint32_t mult, corrX4, c32, shift32;
-                        ldsV4(tabAddr + uint32_t(cl + j) * 32u, mult, corrX4, c32, shift32);
-                        const int32_t x4 = int32_t(acc[j] * 4u + corrX4);
-                        const int32_t h = signFree ? scaleHigh32<false>(x4, int32_t(mult), int32_t(c32))
-                                                   : scaleHigh32<true>(x4, int32_t(mult), int32_t(c32));
-                        y[e] = min(__viaddmax_s32(h >> shift32, outZpMain, loMain), hiMain);
-                    }
-                    packed[q] = pack4(y[0], y[1], y[2], y[3]);
+                // (two copies of the loop behind one branch: as a select per element the compiler computed the sign
+                // term for every element and dropped it afterwards)
+                if (signFree) {
+                    rescale16Words32<false>(acc, tabAddr + uint32_t(cl) * 32u, outZpMain, loMain, hiMain, packed);
+                } else {
+                    rescale16Words32<true>(acc, tabAddr + uint32_t(cl) * 32u, outZpMain, loMain, hiMain, packed);
                 }
             } else if (!RESIDUAL && high) {
 #pragma unroll
