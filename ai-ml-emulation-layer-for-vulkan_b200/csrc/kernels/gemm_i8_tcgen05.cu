@@ -242,7 +242,7 @@ __device__ __forceinline__ void epilogueInt8(const GemmI8Params &p, PipeBarriers
             const int cl = half * kColsPerWarp + st * 16; // column inside the tile
             uint32_t acc[16];
             tmemLoad16(taddr + uint32_t(cl), acc);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tmemWait16(acc);
             if (st == kSteps - 1) {
                 // this warp's part of the accumulator is in registers: hand the buffer back to the MMA warp
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -401,7 +401,7 @@ __device__ __forceinline__ void epilogueInt32(const GemmI8Params &p, PipeBarrier
             const int cl = half * kColsPerWarp + st * 16;
             uint32_t acc[16];
             tmemLoad16(taddr + uint32_t(cl), acc);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tmemWait16(acc);
             if (st == kSteps - 1) {
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 if (lane == 0) {
