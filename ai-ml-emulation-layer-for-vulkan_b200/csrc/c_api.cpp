@@ -111,7 +111,7 @@ int mlel_set_tuning(const char *key, int value) {
             t.pairKernel = value;
         } else if (k == "tile_progress" && value >= 0 && value <= 7) {
             t.tileProgress = value;
-        } else if (k == "oc_tile_rule" && (value == 0 || value == 1)) {
+        } else if (k == "oc_tile_rule" && value >= 0 && value <= 8) {
             t.ocTileRule = value;
         } else if (k == "dependent_launch") {
             t.dependentLaunch = value != 0;

@@ -415,20 +415,26 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s, LaunchChain *cha
     if (consumed != nullptr) {
         before = *consumed;
     }
-    // Pixels per tile.  Wider tiles move less operand data per multiply-accumulate, narrower ones fill the last
-    // wave of CTAs better; a rule that weighed the two (least waves x width) was measured against one width for
-    // every layer on the ResNet-50 shapes, and 192 pixels everywhere -- the variant with twelve epilogue warps --
-    // won by 2.5 % (1.149 against 1.178 ms per 64-image dispatch; 128 and 256 everywhere: 1.32 and 1.33 ms),
-    // although single layers timed alone prefer 128 pixels at 7x7 and 256 at 56x56.  Problems of at most 128
-    // pixels take the narrow tile.
+    // Pixels per tile.  Wider tiles move less operand data per multiply-accumulate and spread a tile's fixed work over
+    // more outputs, narrower ones fill the last round of CTAs better.  192 pixels (twelve epilogue warps) is the
+    // base: measured on the ResNet-50 shapes it beat 128 and 256 pixels for every layer and a rule that weighed
+    // waves against width.  Two exceptions follow: layers that underfill the GPU, and layers with many rounds of
+    // tiles.  Problems of at most 128 pixels take the narrow tile.
     int width = p.M <= 128 ? 128 : 192;
     {
         // a layer that leaves a quarter of the SMs without a tile takes the narrow tile if that fills more of them
         const int64_t cT = (p.N + kOcTile - 1) / kOcTile;
         const int64_t tiles192 = int64_t((p.M + 191) / 192) * cT, tiles128 = int64_t((p.M + 127) / 128) * cT;
-        if (tensorCoreTuning().ocTileRule.load(std::memory_order_relaxed) != 0 && tiles192 * 4 <= int64_t(smCount()) * 3 &&
-            tiles128 <= int64_t(smCount())) {
+        const int rule = tensorCoreTuning().ocTileRule.load(std::memory_order_relaxed);
+        if (rule != 0 && tiles192 * 4 <= int64_t(smCount()) * 3 && tiles128 <= int64_t(smCount())) {
             width = 128;
+        }
+        // a layer with at least `rule` (default three) rounds of 192-pixel tiles per SM takes the wide tile with its
+        // sixteen epilogue warps: what a warp does per tile beside the elements is spread over a third more of them,
+        // and the partly filled last round weighs little (0.977 against 1.009 ms per ResNet-50 dispatch; with two the
+        // same, with four or more rounds less gain; 256 pixels for every layer: 1.014 ms)
+        if (rule >= 2 && tiles192 >= int64_t(smCount()) * rule) {
+            width = 256;
         }
     }
     const int forced = tensorCoreTuning().ocTilePixels.load(std::memory_order_relaxed);
@@ -493,7 +499,7 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s, LaunchChain *cha
         }
     }
     if (width == 256) {
-        return launchOcMajorShape<256, 3, 8>(maps, p, xMode, s);
+        return launchOcMajorShape<256, 3, 16>(maps, p, xMode, s);
     }
     return width == 192 ? launchOcMajorShape<192, 4, 12>(maps, p, xMode, s)
                         : launchOcMajorShape<128, 5, 8>(maps, p, xMode, s);

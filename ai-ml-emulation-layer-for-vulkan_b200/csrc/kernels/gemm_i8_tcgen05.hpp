@@ -139,7 +139,8 @@ struct TensorCoreTuning {
     std::atomic<int> pairKernel{1};        // paired kernel for: 0 nothing, 1 matrix products, 2 convolutions too
     std::atomic<int> pairTilePixels{0};    // 128, 192 or 256: pixels per tile of the paired kernel
     std::atomic<int> ocTilePixels{0};      // 128, 192 or 256: pixels per tile of the channel-major kernel
-    std::atomic<int> ocTileRule{1};        // 1: narrow tiles for layers that would leave a quarter of the SMs idle
+    std::atomic<int> ocTileRule{3};        // >= 1: narrow tiles for layers that would leave a quarter of the SMs idle;
+                                           // r >= 2: 256-pixel tiles for layers with at least r rounds of tiles per SM
     std::atomic<int> dependentLaunch{1};   // 0: launch the tensor-core kernels without programmatic dependent launch
     std::atomic<int> tileProgress{7};      // tile-level hand-over: bit 0 read by tiles, 1 publish, 2 channel tiles first
 };

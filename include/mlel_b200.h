@@ -306,8 +306,10 @@ int mlel_measure_int8_mma_peak(int batches, void *cuda_stream, float *ms, double
  *                       1 (default) matrix products, 2 convolutions as well, 0 none;
  *   "pair_tile_pixels"  0 (default: chosen per problem), 128, 192 or 256 pixels per tile of the paired kernel;
  *   "oc_tile_pixels"    the same for the channel-major single-CTA kernel;
- *   "oc_tile_rule"      1 (default): a layer whose 192-pixel tiles would leave a quarter of the SMs without work takes
- *                       128-pixel tiles if those fit in one round; 0: 192 pixels for every layer above 128 pixels;
+ *   "oc_tile_rule"      0..8, default 3.  From 1 on: a layer whose 192-pixel tiles would leave a quarter of the SMs
+ *                       without work takes 128-pixel tiles if those fit in one round.  r >= 2: a layer with at least r
+ *                       rounds of 192-pixel tiles per SM takes 256-pixel tiles.  0: 192 pixels for every layer above
+ *                       128 pixels;
  *   "dependent_launch"  1 (default) launches the tensor-core kernels with programmatic dependent launch;
  *   "tile_progress"     7 (default): a convolution whose input the convolution before it wrote starts on that launch's
  *                       finished pixel tiles; bit 0 read by tiles, bit 1 publish, bit 2 channel tiles first; 0 off.

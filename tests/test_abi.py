@@ -67,12 +67,12 @@ def test_tuning_keys_and_values(mlel):
     """mlel_set_tuning takes exactly the documented keys and values; anything else is an error and changes nothing.
     (No GPU needed: the settings are read when a kernel is launched.)"""
     lib = mlel.lib()
-    defaults = {b"pair_kernel": 1, b"pair_tile_pixels": 0, b"oc_tile_pixels": 0, b"oc_tile_rule": 1,
+    defaults = {b"pair_kernel": 1, b"pair_tile_pixels": 0, b"oc_tile_pixels": 0, b"oc_tile_rule": 3,
                 b"dependent_launch": 1, b"tile_progress": 7}
     allowed = {b"pair_kernel": [0, 1, 2], b"pair_tile_pixels": [0, 128, 192, 256], b"oc_tile_pixels": [0, 128, 192, 256],
-               b"oc_tile_rule": [0, 1], b"dependent_launch": [0, 1], b"tile_progress": list(range(8))}
+               b"oc_tile_rule": list(range(9)), b"dependent_launch": [0, 1], b"tile_progress": list(range(8))}
     refused = {b"pair_kernel": [-1, 3], b"pair_tile_pixels": [64, 100], b"oc_tile_pixels": [96, 512],
-               b"oc_tile_rule": [2, -1], b"tile_progress": [8, -1]}
+               b"oc_tile_rule": [9, -1], b"tile_progress": [8, -1]}
     try:
         for key, values in allowed.items():
             for v in values:

@@ -68,6 +68,9 @@ CASES = [
     (3, 3, 30, 128, 1, 2),    # stride 2 in the 3x3 and in the projection; 2700 pixels end inside a tile
     (4, 5, 14, 256, 2, 1),    # 980 pixels: six pixel tiles, 2 and 8 channel tiles
     (5, 33, 7, 256, 1, 1),    # 1617 pixels of 7x7 images: windows of a tile span many images
+    # 50176 pixels: the layers with 512 output channels have more than three rounds of tiles per SM and take 256-pixel
+    # tiles, the others 192-pixel ones -- producer and consumer of a hand-over count in different tile widths
+    (7, 16, 56, 128, 2, 1),
 ]
 
 
