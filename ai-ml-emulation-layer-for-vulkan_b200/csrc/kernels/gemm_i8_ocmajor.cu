@@ -502,7 +502,7 @@ int gemmI8OcMajorLaunch(const GemmI8Problem &q, cudaStream_t s, LaunchChain *cha
         return launchOcMajorShape<256, 3, 16>(maps, p, xMode, s);
     }
     return width == 192 ? launchOcMajorShape<192, 4, 12>(maps, p, xMode, s)
-                        : launchOcMajorShape<128, 5, 8>(maps, p, xMode, s);
+                        : launchOcMajorShape<128, 5, 16>(maps, p, xMode, s);
 }
 
 int ocMajorErrorWord() { return tc::readErrorWord(); }
